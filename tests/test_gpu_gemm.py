@@ -1,0 +1,100 @@
+"""tcgen05 GEMM vs an fp32 PyTorch reference, all operand major-ness combinations and epilogues."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn):
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    return A @ B
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 320), (1000, 520, 136),
+                                   (4096, 4096, 1024)])
+def test_gemm_majors(M, N, K, a_mn, b_mn):
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.ops.gemm import gemm
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    a = torch.randn((K, M) if a_mn else (M, K), device=dev).bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device=dev).bfloat16()
+    d = gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn)
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    ref = _ref(a, b, a_mn, b_mn)
+    err = (d.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 1e-2 * scale + 1e-3, (err, scale)
+
+
+def test_gemm_fp32_out_and_accumulate():
+    from turbo_dllm_b200.ops.gemm import gemm
+
+    torch.manual_seed(1)
+    M, N, K = 512, 768, 512
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    ref = a.float() @ b.float().t()
+    out = gemm(a, b, out_dtype=torch.float32)
+    assert torch.allclose(out, ref, rtol=1e-3, atol=1e-2)
+    gemm(a, b, out=out, accumulate=True)
+    assert torch.allclose(out, 2 * ref, rtol=1e-3, atol=2e-2)
+    ob = torch.ones(M, N, device="cuda", dtype=torch.bfloat16)
+    gemm(a, b, out=ob, accumulate=True)
+    assert torch.allclose(ob.float(), ref + 1, rtol=2e-2, atol=0.5)
+
+
+def test_gemm_swiglu_epilogue():
+    from turbo_dllm_b200.ops.gemm import gemm
+
+    torch.manual_seed(2)
+    M, N, K = 640, 1024, 256
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    acc = a.float() @ b.float().t()
+    ref = torch.nn.functional.silu(acc[:, 0::2]) * acc[:, 1::2]
+    out = gemm(a, b, swiglu=True)
+    assert out.shape == (M, N // 2)
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_linear_autograd_matches_reference():
+    from turbo_dllm_b200.ops.gemm import linear
+
+    torch.manual_seed(3)
+    x = torch.randn(4, 200, 256, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(384, 256, device="cuda") * 0.05).bfloat16().requires_grad_()
+    y = linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = xr @ wr.t()
+    yr.backward(g.float())
+    assert torch.allclose(y.float(), yr, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(w.grad.float(), wr.grad, rtol=2e-2, atol=1e-1)
+
+
+def test_bounded_wait_returns_error_status():
+    """A wait on a barrier nobody signals must give up, record ERR_WAIT_TIMEOUT and leave the
+    context usable (host-made failure; nothing traps or hangs)."""
+    from turbo_dllm_b200.kernels import native
+
+    lib = native.lib()
+    lib.tdllm_clear_error()
+    native.check(lib.tdllm_set_wait_timeout_ns(2_000_000), "set timeout")  # 2 ms
+    try:
+        native.check(lib.tdllm_test_wait_timeout(None), "launch")
+        torch.cuda.synchronize()
+        err = native.device_error()
+        assert err["code"] == 1 and err["kernel"] == 99 and err["detail"] == 7
+    finally:
+        lib.tdllm_clear_error()
+        lib.tdllm_set_wait_timeout_ns(2_000_000_000)
+    x = torch.ones(8, device="cuda")
+    assert float(x.sum()) == 8.0

@@ -1,0 +1,68 @@
+// C ABI of the sm_100a kernel library (libtdllm_kernels.so). Python binds it with ctypes;
+// every function takes raw device pointers and a cudaStream_t passed as void*.
+// Functions return 0 on success; tdllm_last_error() describes a non-zero return.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- runtime -------------------------------------------------------------
+const char* tdllm_last_error(void);
+int tdllm_num_sms(void);
+// copies the 8-word device error record to out (synchronises the device)
+int tdllm_get_error(int* out8);
+int tdllm_clear_error(void);
+// budget of every bounded device-side wait, in nanoseconds (default 2 s)
+int tdllm_set_wait_timeout_ns(unsigned long long ns);
+// test hook: a kernel that waits on an mbarrier nobody arrives on; must come back with
+// ERR_WAIT_TIMEOUT in the error record and leave the context usable
+int tdllm_test_wait_timeout(void* stream);
+
+// ---- GEMM ----------------------------------------------------------------
+int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
+                    long long ldb, long long ldd, int a_mn_major, int b_mn_major, int out_fp32,
+                    int accumulate, int mode, const int* labels, const float* lse,
+                    const float* rowscale, float* stats, int exclude_index, float softcap,
+                    int max_ctas, void* stream);
+int tdllm_gemm_n_tiles(int N);
+
+// ---- normalisation / rotary / activation ---------------------------------
+int tdllm_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out,
+                      float* rstd, int rows, int H, float eps, void* stream);
+int tdllm_rmsnorm_bwd_parts(void);
+int tdllm_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd,
+                      const void* dres_in, void* dx, void* dw, int dw_fp32, int dw_accumulate,
+                      float* scratch, int rows, int H, void* stream);
+int tdllm_qk_norm_rope_fwd(const void* in, void* out, const int* pos, const float* inv_freq,
+                           const void* qw, const void* kw, int rows, int Hq, int Hkv, int D,
+                           float eps, void* stream);
+int tdllm_qk_bwd_parts(void);
+int tdllm_qk_norm_rope_bwd(const void* dout, const void* in_raw, void* din, const int* pos,
+                           const float* inv_freq, const void* qw, const void* kw, void* dqw,
+                           void* dkw, int dw_fp32, int dw_accumulate, float* scratch, int rows,
+                           int Hq, int Hkv, int D, float eps, void* stream);
+int tdllm_swiglu_fwd(const void* gu, void* out, long long rows, int inter, void* stream);
+int tdllm_swiglu_bwd(const void* dy, const void* gu, void* dgu, long long rows, int inter,
+                     void* stream);
+
+// ---- optimizer / loss reductions / attention-state merge -------------------
+int tdllm_sumsq_bf16(const void* g, long long n, float* out, void* stream);
+int tdllm_adamw(float* master, float* m, float* v, const void* grad, void* param, long long n,
+                float lr, float beta1, float beta2, float eps, float wd, int step,
+                float grad_scale, const float* sumsq, float max_norm, void* stream);
+int tdllm_ce_finalize(const float* stats, int M, int n_tiles, const int* labels,
+                      const float* weights, float* lse_out, float* loss_rows, float* out2,
+                      void* stream);
+int tdllm_attn_merge(float* num, float* mrun, float* lrun, const void* o_s, const float* lse_s,
+                     long long nrh, int D, int initial, void* stream);
+int tdllm_attn_merge_finalize(const float* num, const float* mrun, const float* lrun, void* out,
+                              float* lse, long long nrh, int D, void* stream);
+int tdllm_attn_merge_bwd(const void* go, const void* out, const float* lse, const void* o_s,
+                         const float* lse_s, void* go_s, float* dlse_s, long long nrh, int D,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,505 @@
+// Persistent bf16 GEMM for sm_100a: TMA (local memory) -> 128B-swizzled shared memory ->
+// tcgen05.mma (one issuing thread) -> fp32 accumulators in TMEM (double buffered) ->
+// tcgen05.ld epilogue -> shared staging -> TMA store.
+//
+//   D[M,N] (+)= A * B with  A given as [M,K] (K-major) or [K,M] (MN-major)
+//                           B given as [N,K] (K-major) or [K,N] (MN-major)
+//
+// That covers the three products of a linear layer y = x W^T without any transpose
+// copy: forward (K,K), input gradient (K,MN), weight gradient (MN,MN).
+//
+// Epilogues: plain store (bf16 or fp32, optional accumulate into the destination),
+// SwiGLU on interleaved gate/up columns, cross-entropy row statistics (no logits
+// written), and cross-entropy gradient of the logits (written as bf16).
+//
+// This replaces the library GEMMs the reference calls (cublasGemmEx in
+// dllm_parallel/core/csrc/fused_linear_ce/fused_linear_ce_cuda.cu:618-791 and the
+// torch / Transformer Engine linears of
+// dllm_parallel/core/models/backbones/nemotron/model.py:3727-4190).
+#include "common.cuh"
+#include "api.h"
+
+namespace tdllm {
+
+constexpr int GEMM_KERNEL_ID = 1;
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int EPI_WARPS = 4;
+constexpr int EPI_BUF_BYTES = 32 * 128;  // one warp: 32 rows x 128 bytes
+constexpr int GEMM_THREADS = 32 * (2 + EPI_WARPS);
+constexpr int SMEM_TILES = STAGES * STAGE_BYTES;
+constexpr int SMEM_EPI = EPI_WARPS * 2 * EPI_BUF_BYTES;
+constexpr int GEMM_SMEM_BYTES = SMEM_TILES + SMEM_EPI + 256 + 1024;  // + barriers + align slack
+
+enum EpilogueMode : int {
+  EPI_STORE = 0,     // D = acc (bf16 or fp32), optional D += acc
+  EPI_SWIGLU = 1,    // D[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1], bf16, N_out = N/2
+  EPI_CE_STATS = 2,  // per (row, n-tile): max, sum exp, target logit -> fp32 scratch
+  EPI_CE_GRAD = 3,   // D = (exp(acc - lse[row]) - onehot(label[row])) * rowscale[row], bf16
+};
+
+struct GemmParams {
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  int mode;
+  int out_fp32;
+  int accumulate;
+  int m_tiles, n_tiles;
+  // plain accumulate path reads the destination directly
+  void* d_ptr;
+  long long ldd;  // elements
+  // cross-entropy epilogues
+  const int* labels;      // [M], negative = ignored row
+  const float* lse;       // [M]
+  const float* rowscale;  // [M]
+  float* stats;           // [M, n_tiles, 3]
+  int exclude_index;      // column removed from the softmax (-1 = none)
+  float softcap;          // 0 = off
+};
+
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& m, int& n) {
+  constexpr int G = 8;
+  const int per_group = G * n_tiles;
+  const int g = t / per_group;
+  const int first_m = g * G;
+  const int gsz = min(m_tiles - first_m, G);
+  const int r = t - g * per_group;
+  m = first_m + r % gsz;
+  n = r / gsz;
+}
+
+__device__ __forceinline__ float apply_softcap(float x, float cap) {
+  return cap > 0.f ? cap * tanhf(x / cap) : x;
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                 const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* epi_smem = smem + SMEM_TILES;
+  uint64_t* bars = (uint64_t*)(epi_smem + SMEM_EPI);
+  // bars: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem base word
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * STAGES;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.m_tiles * p.n_tiles;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, EPI_WARPS);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, GEMM_KERNEL_ID, 10)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, STAGE_BYTES);
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          if (!p.a_mn_major) {
+            tma_load_2d(sa, &tmap_a, full, kb * BK, tm * BM);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(sa + c * (BK * 128), &tmap_a, full, tm * BM + c * 64, kb * BK);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d(sb, &tmap_b, full, kb * BK, tn * BN);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (BK * 128), &tmap_b, full, tn * BN + c * 64, kb * BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn_major, p.b_mn_major);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t tphase = (it >> 1) & 1;
+        if (!mbar_wait(bar_tempty + 8 * buf, tphase ^ 1, GEMM_KERNEL_ID, 20)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, GEMM_KERNEL_ID, 21)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: step 32 bytes inside the 128-byte swizzled row.
+            // MN-major: step 16 rows of 128 bytes.
+            const uint64_t ad = p.a_mn_major
+                                    ? make_smem_desc_sw128(sa + k * (UMMA_K * 128), BK * 128, 1024)
+                                    : make_smem_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t bd = p.b_mn_major
+                                    ? make_smem_desc_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024)
+                                    : make_smem_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
+            tc_mma_ss(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+          }
+          tc_commit(bar_empty + 8 * stage);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(bar_tfull + 8 * buf);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue warps ----------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;
+    uint8_t* my_stage = epi_smem + (warp - 2) * 2 * EPI_BUF_BYTES;
+    int sbuf = 0;
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      int tm, tn;
+      tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+      const int buf = it & 1;
+      const uint32_t tphase = (it >> 1) & 1;
+      if (!mbar_wait(bar_tfull + 8 * buf, tphase, GEMM_KERNEL_ID, 30)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+      const int gm = tm * BM + row;
+      const int n0 = tn * BN;
+      uint32_t r[32];
+
+      if (p.mode == EPI_CE_STATS) {
+        float mx = -INFINITY, sum = 0.f, tgt = 0.f;
+        const int label = (gm < p.M) ? p.labels[gm] : -1;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          float cmx = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = n0 + c * 32 + j;
+            float v = apply_softcap(__uint_as_float(r[j]), p.softcap);
+            if (col == label) tgt = v;
+            v = (col < p.N && col != p.exclude_index) ? v : -INFINITY;
+            r[j] = __float_as_uint(v);
+            cmx = fmaxf(cmx, v);
+          }
+          const float nmx = fmaxf(mx, cmx);
+          if (nmx > -INFINITY) {
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) s += __expf(__uint_as_float(r[j]) - nmx);
+            sum = sum * __expf(mx - nmx) + s;
+            mx = nmx;
+          }
+        }
+        if (gm < p.M) {
+          float* o = p.stats + ((size_t)gm * p.n_tiles + tn) * 3;
+          o[0] = mx;
+          o[1] = sum;
+          o[2] = (label >= n0 && label < n0 + BN) ? tgt : 0.f;
+        }
+      } else if (p.mode == EPI_SWIGLU) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 128; ++c) {
+          uint8_t* st = my_stage + sbuf * EPI_BUF_BYTES;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+#pragma unroll 1
+          for (int h = 0; h < 4; ++h) {
+            tmem_ld32(taddr + c * 128 + h * 32, r);
+            tmem_ld_wait();
+            uint32_t o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float g0 = __uint_as_float(r[4 * j]), u0 = __uint_as_float(r[4 * j + 1]);
+              const float g1 = __uint_as_float(r[4 * j + 2]), u1 = __uint_as_float(r[4 * j + 3]);
+              o[j] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              *reinterpret_cast<uint4*>(st + sw128_offset(lane, h * 2 + i)) =
+                  make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_d, smem_u32(st), tn * (BN / 2) + c * 64, tm * BM + q * 32);
+            tma_store_commit();
+          }
+          sbuf ^= 1;
+        }
+      } else if (p.out_fp32) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint8_t* st = my_stage + sbuf * EPI_BUF_BYTES;
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (p.accumulate && gm < p.M) {
+            const float* dp = (const float*)p.d_ptr + (size_t)gm * p.ldd + n0 + c * 32;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (n0 + c * 32 + j < p.N) {
+                const float4 v = *reinterpret_cast<const float4*>(dp + j);
+                r[j] = __float_as_uint(__uint_as_float(r[j]) + v.x);
+                r[j + 1] = __float_as_uint(__uint_as_float(r[j + 1]) + v.y);
+                r[j + 2] = __float_as_uint(__uint_as_float(r[j + 2]) + v.z);
+                r[j + 3] = __float_as_uint(__uint_as_float(r[j + 3]) + v.w);
+              }
+            }
+          }
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<uint4*>(st + sw128_offset(lane, i)) =
+                make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_d, smem_u32(st), n0 + c * 32, tm * BM + q * 32);
+            tma_store_commit();
+          }
+          sbuf ^= 1;
+        }
+      } else {
+        // bf16 destination: plain store, accumulate, or cross-entropy logit gradient
+        float row_lse = 0.f, row_scale = 0.f;
+        int label = -1;
+        if (p.mode == EPI_CE_GRAD && gm < p.M) {
+          row_lse = p.lse[gm];
+          row_scale = p.rowscale[gm];
+          label = p.labels[gm];
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint8_t* st = my_stage + sbuf * EPI_BUF_BYTES;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            const int cbase = n0 + c * 64 + h * 32;
+            tmem_ld32(taddr + c * 64 + h * 32, r);
+            tmem_ld_wait();
+            if (p.mode == EPI_CE_GRAD) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = cbase + j;
+                const float x = __uint_as_float(r[j]);
+                float v = x, dcap = 1.f;
+                if (p.softcap > 0.f) {
+                  const float th = tanhf(x / p.softcap);
+                  v = p.softcap * th;
+                  dcap = 1.f - th * th;
+                }
+                float g = (col == p.exclude_index) ? 0.f : __expf(v - row_lse);
+                if (col == label) g -= 1.f;
+                r[j] = __float_as_uint(g * row_scale * dcap);
+              }
+            } else if (p.accumulate && gm < p.M) {
+              const __nv_bfloat16* dp = (const __nv_bfloat16*)p.d_ptr + (size_t)gm * p.ldd + cbase;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (cbase + j < p.N) {
+                  const uint4 v = *reinterpret_cast<const uint4*>(dp + j);
+                  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(h2[e]);
+                    r[j + 2 * e] = __float_as_uint(__uint_as_float(r[j + 2 * e]) + f.x);
+                    r[j + 2 * e + 1] = __float_as_uint(__uint_as_float(r[j + 2 * e + 1]) + f.y);
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t a0 = pack_bf16x2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]));
+              const uint32_t a1 = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+              const uint32_t a2 = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+              const uint32_t a3 = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+              *reinterpret_cast<uint4*>(st + sw128_offset(lane, h * 4 + i)) = make_uint4(a0, a1, a2, a3);
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_d, smem_u32(st), n0 + c * 64, tm * BM + q * 32);
+            tma_store_commit();
+          }
+          sbuf ^= 1;
+        }
+      }
+      // accumulator buffer is free again
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  // common exit: every role arrives here, also after a failed wait
+  tc_fence_before();
+  __syncthreads();
+  if (error_is_set()) {
+    // loads that were issued before an abort may still be landing in shared memory
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace tdllm
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+using namespace tdllm;
+
+extern "C" int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K,
+                               long long lda, long long ldb, long long ldd, int a_mn_major,
+                               int b_mn_major, int out_fp32, int accumulate, int mode,
+                               const int* labels, const float* lse, const float* rowscale,
+                               float* stats, int exclude_index, float softcap, int max_ctas,
+                               void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || ((uintptr_t)A % 16) || ((uintptr_t)B % 16)) {
+    tdllm_host::set_last_error("gemm: operands need 16-byte aligned base and row stride");
+    return 1;
+  }
+  if (mode == EPI_SWIGLU && (N % 2 || out_fp32 || accumulate)) {
+    tdllm_host::set_last_error("gemm: swiglu epilogue needs even N and a bf16 plain store");
+    return 1;
+  }
+  if (mode == EPI_CE_GRAD && (out_fp32 || accumulate)) {
+    tdllm_host::set_last_error("gemm: ce-grad epilogue writes bf16 without accumulate");
+    return 1;
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GEMM_SMEM_BYTES);
+    if (e != cudaSuccess) {
+      tdllm_host::set_last_error("gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return 2;
+    }
+    attr_set = true;
+  }
+  CUtensorMap ta, tb, td;
+  {
+    uint64_t dims[2], strides[1];
+    uint32_t box[2];
+    if (!a_mn_major) {
+      dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = BK; box[1] = BM;
+    } else {
+      dims[0] = (uint64_t)M; dims[1] = (uint64_t)K; box[0] = 64; box[1] = BK;
+    }
+    strides[0] = (uint64_t)lda * 2;
+    if (tdllm_host::encode_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B)) return 3;
+    if (!b_mn_major) {
+      dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = BK; box[1] = BN;
+    } else {
+      dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 64; box[1] = BK;
+    }
+    strides[0] = (uint64_t)ldb * 2;
+    if (tdllm_host::encode_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B)) return 3;
+    if (mode == EPI_CE_STATS) {
+      td = ta;  // unused by this epilogue
+    } else {
+      const int n_out = (mode == EPI_SWIGLU) ? N / 2 : N;
+      const int esz = out_fp32 ? 4 : 2;
+      if (((uint64_t)ldd * esz) % 16 || ((uintptr_t)D % 16)) {
+        tdllm_host::set_last_error("gemm: destination needs 16-byte aligned base and row stride");
+        return 1;
+      }
+      dims[0] = (uint64_t)n_out; dims[1] = (uint64_t)M;
+      box[0] = out_fp32 ? 32 : 64; box[1] = 32;
+      strides[0] = (uint64_t)ldd * esz;
+      if (tdllm_host::encode_tmap(&td, out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                                  2, D, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return 3;
+    }
+  }
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+  p.mode = mode; p.out_fp32 = out_fp32; p.accumulate = accumulate;
+  p.m_tiles = (M + BM - 1) / BM; p.n_tiles = (N + BN - 1) / BN;
+  p.d_ptr = D; p.ldd = ldd;
+  p.labels = labels; p.lse = lse; p.rowscale = rowscale; p.stats = stats;
+  p.exclude_index = exclude_index; p.softcap = softcap;
+  const int tiles = p.m_tiles * p.n_tiles;
+  int ctas = max_ctas > 0 ? max_ctas : tdllm_num_sms();
+  if (ctas > tiles) ctas = tiles;
+  gemm_bf16_kernel<<<ctas, GEMM_THREADS, GEMM_SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, td, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    tdllm_host::set_last_error("gemm launch: %s", cudaGetErrorString(e));
+    return 4;
+  }
+  return 0;
+}
+
+extern "C" int tdllm_gemm_n_tiles(int N) { return (N + BN - 1) / BN; }

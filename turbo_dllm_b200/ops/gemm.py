@@ -1,0 +1,136 @@
+"""bf16 GEMM on tcgen05 tensor cores, and the linear layer built on it.
+
+`gemm(a, b)` computes D[M,N] = A·B where `a` is given as [M,K] (or [K,M] with
+`a_mn_major=True`) and `b` as [N,K] (or [K,N] with `b_mn_major=True`), so the forward,
+input-gradient and weight-gradient products of y = x Wᵀ need no transpose copies.
+
+The reference reaches cuBLAS through torch / Transformer Engine linears
+(dllm_parallel/core/models/backbones/nemotron/model.py:3727-4190) and `cublasGemmEx`
+(dllm_parallel/core/csrc/fused_linear_ce/fused_linear_ce_cuda.cu:618-791).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import native
+from ._util import grad_sink, mark_grad_written, ptr, stream, use_native
+
+EPI_STORE, EPI_SWIGLU, EPI_CE_STATS, EPI_CE_GRAD = 0, 1, 2, 3
+
+
+def _as2d(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dim() == 2 else t.reshape(-1, t.shape[-1])
+
+
+def gemm_reference(a, b, a_mn_major=False, b_mn_major=False):
+    A = a.t() if a_mn_major else a
+    B = b if b_mn_major else b.t()
+    return A.float() @ B.float()
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
+         accumulate: bool = False, swiglu: bool = False, max_ctas: int = 0) -> torch.Tensor:
+    a = _as2d(a)
+    b = _as2d(b)
+    M, K = (a.shape[1], a.shape[0]) if a_mn_major else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn_major else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"gemm: contraction mismatch {K} vs {Kb}")
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty(M, n_out, dtype=out_dtype or a.dtype, device=a.device)
+        accumulate = False
+    if not use_native(a, b):
+        res = gemm_reference(a, b, a_mn_major, b_mn_major)
+        if swiglu:
+            res = torch.nn.functional.silu(res[:, 0::2]) * res[:, 1::2]
+        if accumulate:
+            out.add_(res.to(out.dtype))
+        else:
+            out.copy_(res.to(out.dtype))
+        return out
+    if a.stride(-1) != 1 or b.stride(-1) != 1 or out.stride(-1) != 1:
+        raise ValueError("gemm: innermost stride must be 1")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("gemm: destination must be bf16 or fp32")
+    rc = native.lib().tdllm_gemm_bf16(
+        ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+        int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate),
+        EPI_SWIGLU if swiglu else EPI_STORE, None, None, None, None, -1, 0.0, max_ctas, stream())
+    native.check(rc, "gemm_bf16")
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    """y = x Wᵀ with W [out, in]. The weight gradient goes straight into the parameter's
+    slice of the flat gradient buffer when it has one (no .grad tensor, no extra add)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        ctx.wref = w
+        y = gemm(x, w)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = _as2d(dy.contiguous())
+        x2 = _as2d(x)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn_major=True).view_as(x)
+        if ctx.needs_input_grad[1]:
+            sink, acc = grad_sink(ctx.wref)
+            if sink is not None:
+                gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out=sink, accumulate=acc)
+                mark_grad_written(ctx.wref)
+            else:
+                dw = gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out_dtype=w.dtype)
+        return dx, dw
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    return _Linear.apply(x, w)
+
+
+class _LinearSwiGLU(torch.autograd.Function):
+    """act = silu(g) * u where [g0,u0,g1,u1,...] = x W_guᵀ with interleaved gate/up rows.
+    Without grad the activation is applied in the GEMM epilogue and the [rows, 2I]
+    pre-activation never reaches HBM; with grad it is kept for the backward pass."""
+
+    @staticmethod
+    def forward(ctx, x, w_gu):
+        from .activation import swiglu_forward
+
+        gu = gemm(x, w_gu)
+        act = swiglu_forward(gu)
+        ctx.save_for_backward(x, w_gu, gu)
+        ctx.wref = w_gu
+        return act.view(*x.shape[:-1], w_gu.shape[0] // 2)
+
+    @staticmethod
+    def backward(ctx, dact):
+        from .activation import swiglu_backward
+
+        x, w, gu = ctx.saved_tensors
+        dgu = swiglu_backward(_as2d(dact.contiguous()), gu)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dgu, w, b_mn_major=True).view_as(x)
+        if ctx.needs_input_grad[1]:
+            sink, acc = grad_sink(ctx.wref)
+            if sink is not None:
+                gemm(dgu, _as2d(x), a_mn_major=True, b_mn_major=True, out=sink, accumulate=acc)
+                mark_grad_written(ctx.wref)
+            else:
+                dw = gemm(dgu, _as2d(x), a_mn_major=True, b_mn_major=True, out_dtype=w.dtype)
+        return dx, dw
+
+
+def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor) -> torch.Tensor:
+    if not (torch.is_grad_enabled() and (x.requires_grad or w_gu.requires_grad)):
+        y = gemm(x, w_gu, swiglu=True)
+        return y.view(*x.shape[:-1], w_gu.shape[0] // 2)
+    return _LinearSwiGLU.apply(x, w_gu)
