@@ -1,0 +1,69 @@
+"""tcgen05 block-diffusion attention vs the dense-mask fp32 reference."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(layout, nq, nk, Hq, Hkv, seed=0, self_attn=True):
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.ops.attention import attention_forward_native, attention_reference
+
+    torch.manual_seed(seed)
+    D = 128
+    qkv = torch.randn(max(nq, nk), (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+    q = qkv[:nq, : Hq * D].view(nq, Hq, D)
+    k = qkv[:nk, Hq * D:(Hq + Hkv) * D].view(nk, Hkv, D)
+    v = qkv[:nk, (Hq + Hkv) * D:].view(nk, Hkv, D)
+    scale = 1.0 / math.sqrt(D)
+    out, lse = attention_forward_native(q, k, v, layout, scale)
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    ref, ref_lse = attention_reference(q.float(), k.float(), v.float(), layout, scale)
+    err = (out.float() - ref).abs().max().item()
+    assert err < 3e-2, err
+    fin = torch.isfinite(ref_lse)
+    got = lse[:, :nq]
+    assert torch.equal(torch.isfinite(got), fin)
+    assert (got[fin] - ref_lse[fin]).abs().max().item() < 2e-2
+    return out, lse
+
+
+@pytest.mark.parametrize("L,bs,views", [(256, 32, 1), (512, 64, 1), (640, 32, 2), (1024, 32, 1)])
+@pytest.mark.parametrize("Hq,Hkv", [(2, 1), (4, 2), (8, 2)])
+def test_block_diffusion_full_sequence(L, bs, views, Hq, Hkv):
+    from turbo_dllm_b200.ops.attention import single_sequence_layout
+
+    layout = single_sequence_layout(L, bs, "cuda", views)
+    n = (views + 1) * L
+    _run(layout, n, n, Hq, Hkv)
+
+
+def test_ragged_rows_and_sparse_keys():
+    """Row counts that are not multiples of 128, keys that are a strided subset (a CP shard),
+    and query rows that see no key at all."""
+    from turbo_dllm_b200.ops.attention import block_diffusion_layout
+
+    dev = "cuda"
+    L, bs = 600, 24
+    pos = torch.arange(L, device=dev)
+    act = pos[(pos // bs) % 3 == 1]                 # some noisy blocks only
+    kpos = pos[(pos // 50) % 2 == 1]                # clean keys owned by "this rank"
+    layout = block_diffusion_layout(act, act // bs, pos[:333], bs, key_clean_pos=kpos)
+    nq = act.numel() + 333
+    nk = act.numel() + kpos.numel()
+    _run(layout, nq, nk, 4, 2)
+
+
+def test_two_sequences_and_window():
+    from turbo_dllm_b200.ops.attention import block_diffusion_layout
+
+    dev = "cuda"
+    L, bs = 384, 32
+    pos = torch.arange(L, device=dev).repeat(2)
+    seq = torch.arange(2, device=dev).repeat_interleave(L)
+    grp = pos // bs + seq * (L // bs)
+    layout = block_diffusion_layout(pos, grp, pos, bs, noisy_seq=seq, clean_seq=seq, window=96)
+    _run(layout, 4 * L, 4 * L, 4, 2)

@@ -63,6 +63,13 @@ int tdllm_attn_merge_bwd(const void* go, const void* out, const float* lse, cons
                          const float* lse_s, void* go_s, float* dlse_s, long long nrh, int D,
                          void* stream);
 
+// ---- block-diffusion attention (head_dim 128) ------------------------------
+int tdllm_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int nq,
+                   int nk, int Hq, int Hkv, long long ldq, long long ldk, long long ldv,
+                   long long ldo, const int* q_lo, const int* q_hi, const int* q_grp,
+                   const int* k_code, const int* tile_ptr, const int* tile_idx, const int* order,
+                   int n_qtiles, float scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
