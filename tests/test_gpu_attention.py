@@ -67,3 +67,49 @@ def test_two_sequences_and_window():
     grp = pos // bs + seq * (L // bs)
     layout = block_diffusion_layout(pos, grp, pos, bs, noisy_seq=seq, clean_seq=seq, window=96)
     _run(layout, 4 * L, 4 * L, 4, 2)
+
+
+def _run_bwd(layout, nq, nk, Hq, Hkv, seed=0):
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.ops.attention import attention_reference, block_attention
+
+    torch.manual_seed(seed)
+    D = 128
+    q = torch.randn(nq, Hq, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(nk, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(nk, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    scale = 1.0 / math.sqrt(D)
+    out = block_attention(q, k, v, layout, scale)
+    g = torch.randn_like(out)
+    out.backward(g)
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref, _ = attention_reference(qr, kr, vr, layout, scale)
+    ref.backward(g.float())
+    for name, a, b in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
+        err = (a.float() - b).abs().max().item()
+        scale_ = b.abs().max().item()
+        assert err <= 5e-2 * max(scale_, 1.0), (name, err, scale_)
+
+
+@pytest.mark.parametrize("L,bs,views", [(256, 32, 1), (640, 32, 2), (1024, 64, 1)])
+@pytest.mark.parametrize("Hq,Hkv", [(2, 1), (8, 2)])
+def test_backward_full_sequence(L, bs, views, Hq, Hkv):
+    from turbo_dllm_b200.ops.attention import single_sequence_layout
+
+    layout = single_sequence_layout(L, bs, "cuda", views)
+    n = (views + 1) * L
+    _run_bwd(layout, n, n, Hq, Hkv)
+
+
+def test_backward_ragged_sparse_keys():
+    from turbo_dllm_b200.ops.attention import block_diffusion_layout
+
+    dev = "cuda"
+    L, bs = 600, 24
+    pos = torch.arange(L, device=dev)
+    act = pos[(pos // bs) % 3 == 1]
+    kpos = pos[(pos // 50) % 2 == 1]
+    layout = block_diffusion_layout(act, act // bs, pos[:333], bs, key_clean_pos=kpos)
+    _run_bwd(layout, act.numel() + 333, act.numel() + kpos.numel(), 4, 2)

@@ -70,6 +70,17 @@ int tdllm_attn_fwd(const void* q, const void* k, const void* v, void* o, float* 
                    const int* k_code, const int* tile_ptr, const int* tile_idx, const int* order,
                    int n_qtiles, float scale, void* stream);
 
+// dq/dk/dv may point into one packed [rows, (Hq+2Hkv)*128] buffer; delta is fp32 scratch
+// [Hq, n_qtiles*128]; f_* lists are per query tile, b_* lists per key tile.
+int tdllm_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                   void* dq, void* dk, void* dv, const float* lse, float* delta, int nq, int nk,
+                   int Hq, int Hkv, long long ldq, long long ldk, long long ldv, long long ldo,
+                   long long lddo, long long lddq, long long lddk, long long lddv,
+                   const int* q_lo, const int* q_hi, const int* q_grp, const int* k_code,
+                   const int* f_ptr, const int* f_idx, const int* f_order, const int* b_ptr,
+                   const int* b_idx, const int* b_order, int n_qtiles, int n_ktiles, float scale,
+                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif

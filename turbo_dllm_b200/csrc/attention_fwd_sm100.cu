@@ -359,10 +359,10 @@ using namespace tdllm;
 
 namespace tdllm_host {
 int encode_rows_tmap(CUtensorMap* out, const void* base, long long cols, long long rows,
-                     long long ld_elems) {
+                     long long ld_elems, int box_rows) {
   uint64_t dims[2] = {(uint64_t)cols, (uint64_t)rows};
   uint64_t strides[1] = {(uint64_t)ld_elems * 2};
-  uint32_t box[2] = {64, 128};
+  uint32_t box[2] = {64, (uint32_t)box_rows};
   return encode_tmap(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box,
                      CU_TENSOR_MAP_SWIZZLE_128B);
 }
@@ -398,10 +398,10 @@ extern "C" int tdllm_attn_fwd(const void* q, const void* k, const void* v, void*
     attr_set = true;
   }
   CUtensorMap tq, tk, tv, to;
-  if (tdllm_host::encode_rows_tmap(&tq, q, (long long)Hq * HD, nq, ldq)) return 3;
-  if (tdllm_host::encode_rows_tmap(&tk, k, (long long)Hkv * HD, nk, ldk)) return 3;
-  if (tdllm_host::encode_rows_tmap(&tv, v, (long long)Hkv * HD, nk, ldv)) return 3;
-  if (tdllm_host::encode_rows_tmap(&to, o, (long long)Hq * HD, nq, ldo)) return 3;
+  if (tdllm_host::encode_rows_tmap(&tq, q, (long long)Hq * HD, nq, ldq, 128)) return 3;
+  if (tdllm_host::encode_rows_tmap(&tk, k, (long long)Hkv * HD, nk, ldk, 128)) return 3;
+  if (tdllm_host::encode_rows_tmap(&tv, v, (long long)Hkv * HD, nk, ldv, 128)) return 3;
+  if (tdllm_host::encode_rows_tmap(&to, o, (long long)Hq * HD, nq, ldo, 128)) return 3;
   FwdParams p;
   p.nq_pad = n_qtiles * BQ;
   p.Hq = Hq; p.Hkv = Hkv;

@@ -320,7 +320,7 @@ int encode_tmap(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* 
                 const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                 CUtensorMapSwizzle swz);
 int encode_rows_tmap(CUtensorMap* out, const void* base, long long cols, long long rows,
-                     long long ld_elems);
+                     long long ld_elems, int box_rows);
 const char* last_error();
 void set_last_error(const char* fmt, ...);
 }  // namespace tdllm_host

@@ -40,8 +40,15 @@ def find_nvcc() -> str:
     return cand
 
 
+INCLUDED_ONLY = {"attention_bwd_dq_sm100.cu", "attention_bwd_dkv_sm100.cu"}  # pulled in by attention_bwd_host.cu
+
+
 def sources() -> list[Path]:
-    return sorted(CSRC.glob("*.cu"))
+    return [p for p in sorted(CSRC.glob("*.cu")) if p.name not in INCLUDED_ONLY]
+
+
+def all_source_files() -> list[Path]:
+    return sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
 
 
 def _sha256(path: Path) -> str:
@@ -53,8 +60,7 @@ def _sha256(path: Path) -> str:
 
 
 def source_hashes() -> dict[str, str]:
-    files = sources() + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
-    return {f.name: _sha256(f) for f in files}
+    return {f.name: _sha256(f) for f in all_source_files()}
 
 
 def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> tuple[str, str]:

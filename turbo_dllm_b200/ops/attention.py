@@ -216,3 +216,73 @@ def single_sequence_layout(seq_len: int, block_size: int, device="cpu", views: i
     ngrp = (pos // block_size).repeat(views) + torch.arange(views, device=device).repeat_interleave(seq_len) * (
         seq_len // block_size)
     return block_diffusion_layout(npos, ngrp, pos, block_size)
+
+
+native.register_signatures({
+    "tdllm_attn_bwd": (native.c_int, [native.c_void_p] * 10 + [native.c_int] * 4 + [native.c_ll] * 8
+                       + [native.c_void_p] * 10 + [native.c_int, native.c_int, native.c_float,
+                                                   native.c_void_p]),
+})
+
+
+def attention_backward_native(q, k, v, out, dout, lse, layout: MaskLayout, scale: float,
+                              dqkv: torch.Tensor | None = None):
+    """Returns (dq, dk, dv) as [rows, heads, 128] tensors. When q, k and v index the same rows
+    (self-attention over a packed projection) the three gradients are views of one packed
+    [rows, (Hq + 2·Hkv)·128] buffer, ready for the fused q/k-norm + RoPE backward."""
+    nq, Hq, D = q.shape
+    nk, Hkv, _ = k.shape
+    L = layout.tile_lists()
+    dev = q.device
+    if dout.stride(2) != 1 or dout.stride(1) != D:
+        dout = dout.contiguous()
+    if nq == nk:
+        if dqkv is None:
+            dqkv = torch.empty(nq, (Hq + 2 * Hkv) * D, dtype=q.dtype, device=dev)
+        dq = dqkv[:, : Hq * D].view(nq, Hq, D)
+        dk = dqkv[:, Hq * D:(Hq + Hkv) * D].view(nk, Hkv, D)
+        dv = dqkv[:, (Hq + Hkv) * D:].view(nk, Hkv, D)
+    else:
+        dq = torch.empty(nq, Hq, D, dtype=q.dtype, device=dev)
+        dk = torch.empty(nk, Hkv, D, dtype=q.dtype, device=dev)
+        dv = torch.empty(nk, Hkv, D, dtype=q.dtype, device=dev)
+    if lse.shape[1] != L["nq_pad"]:
+        padded = torch.full((Hq, L["nq_pad"]), float("-inf"), dtype=torch.float32, device=dev)
+        padded[:, :nq] = lse[:, :nq]
+        lse = padded
+    delta = torch.empty(Hq, L["nq_pad"], dtype=torch.float32, device=dev)
+    rc = native.lib().tdllm_attn_bwd(
+        ptr(q), ptr(k), ptr(v), ptr(out), ptr(dout), ptr(dq), ptr(dk), ptr(dv), ptr(lse), ptr(delta),
+        nq, nk, Hq, Hkv, _rows_view(q), _rows_view(k), _rows_view(v), _rows_view(out),
+        dout.stride(0), dq.stride(0), dk.stride(0), dv.stride(0),
+        ptr(L["q_lo"]), ptr(L["q_hi"]), ptr(L["q_grp"]), ptr(L["k_code"]),
+        ptr(L["f_ptr"]), ptr(L["f_idx"]), ptr(L["f_order"]), ptr(L["b_ptr"]), ptr(L["b_idx"]),
+        ptr(L["b_order"]), L["nqt"], L["nkt"], float(scale), stream())
+    native.check(rc, "attn_bwd")
+    return dq, dk, dv
+
+
+class _BlockAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, layout, scale):
+        out, lse = attention_forward_native(q, k, v, layout, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.layout, ctx.scale = layout, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = attention_backward_native(q, k, v, out, dout, lse, ctx.layout, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def block_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layout: MaskLayout,
+                    scale: float | None = None) -> torch.Tensor:
+    """q [nq,Hq,D], k/v [nk,Hkv,D] -> out [nq,Hq,D] under the layout's mask."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if use_native(q, k, v) and q.shape[-1] == 128:
+        return _BlockAttention.apply(q, k, v, layout, scale)
+    if q.is_cuda and q.dtype == torch.bfloat16:
+        raise native.NativeKernelError("bf16 CUDA attention needs head_dim 128 (no silent fallback)")
+    return attention_reference(q, k, v, layout, scale)[0]
