@@ -1,0 +1,172 @@
+"""Headline benchmark: training tokens/s (+ MFU) of a Qwen3-8B-shaped block-diffusion model with the
+Fast-dLLM v2 objective, bf16, synthetic tokens, random-init weights, on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 3 --warmup 3
+
+Prints ONE JSON line on rank 0. `value` is the whole-job tokens/s of K complete optimizer steps
+(data on the device), timed with CUDA events, max over ranks. `e2e` repeats the measurement
+through the public `TrainingSession` API with every step's tokens copied from pinned host memory
+and the step loss read back to the host. `--impl reference` runs the unmodified reference
+package from baseline/_ref through its own trainer instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="synthetic:qwen3-8b")
+    ap.add_argument("--seq-len", type=int, default=32768)
+    ap.add_argument("--block-size", type=int, default=32)
+    ap.add_argument("--batch-per-gpu", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=None, help="debug only: truncating makes the result invalid")
+    ap.add_argument("--skip-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def build_spec(args):
+    from turbo_dllm_b200.config.run_spec import RunSpec
+
+    mapping = {
+        "model": {"id": args.model, "seq_len": args.seq_len, "dtype": "bf16", "family": "causal_lm"},
+        "objective": {"name": "fast_dllm_v2", "block_size": args.block_size, "noise_schedule_epsilon": 0.1},
+        "data": {"input_mode": "random"},
+        "training": {"batch_size": args.batch_per_gpu, "steps": args.steps + args.warmup,
+                     "activation_checkpointing": True},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1, "tensor_parallel_size": 1},
+        "optimizer": {"backend": "auto", "lr": 1e-5, "gradient_clip_norm": 1.0},
+    }
+    if args.layers is not None:
+        mapping["model"]["num_layers"] = args.layers
+    return RunSpec.from_mapping(mapping).validate()
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.profiling.perf import (block_diffusion_pairs, measured_peaks,
+                                                model_flops_utilization_pct, transformer_step_flops)
+    from turbo_dllm_b200.training.session import TrainingSession
+    from turbo_dllm_b200.utils.clocks import ClockSampler
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    spec = build_spec(args)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(session, steps, read_loss):
+        """K steps between CUDA events; returns ms per step as max over ranks and the last loss."""
+        barrier()
+        native.LAUNCHES["kernels"] = 0
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        loss, d2h = None, 0
+        for _ in range(steps):
+            r = session.step()
+            if read_loss:
+                loss = float(r.loss_sum) / r.denominator      # device -> host every step
+                d2h = r.loss_sum.element_size()
+        stop.record()
+        barrier()
+        ms = torch.tensor([start.elapsed_time(stop)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        if loss is None:
+            loss = float(r.loss_sum) / r.denominator
+        return float(ms) / steps, loss, native.LAUNCHES["kernels"], r, d2h
+
+    session = TrainingSession(spec, device=f"cuda:{local_rank}")
+    cfg = session.cfg
+    for _ in range(args.warmup):
+        session.step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, loss, launches, last, _ = timed(session, args.steps, read_loss=False)
+    clocks = sampler.stop() if rank == 0 else None
+    native.raise_on_device_error()
+    tokens_per_step = args.batch_per_gpu * args.seq_len * world
+    value = tokens_per_step / (ms / 1e3)
+
+    e2e = None
+    if not args.skip_e2e:
+        del session
+        torch.cuda.empty_cache()
+        session = TrainingSession(spec, device=f"cuda:{local_rank}", host_staged_data=True)
+        for _ in range(max(args.warmup, 3)):
+            session.step()
+        ms2, loss2, _, last2, d2h = timed(session, args.steps, read_loss=True)
+        e2e = {"value": tokens_per_step / (ms2 / 1e3), "unit": "tokens/s", "ms_per_step": ms2,
+               "h2d_bytes_per_step": last2.h2d_bytes, "d2h_bytes_per_step": d2h, "loss": loss2}
+
+    if rank == 0:
+        views = session.objective.views
+        rows = (views + 1) * args.seq_len * args.batch_per_gpu * world
+        pairs = block_diffusion_pairs(args.seq_len, args.block_size, views) * args.batch_per_gpu * world
+        vocab_rows = args.batch_per_gpu * world * (args.seq_len - 1)
+        fl = transformer_step_flops(cfg, rows=rows, pairs=pairs, vocab_rows=vocab_rows)
+        peaks = measured_peaks() or {}
+        out = {
+            "metric": "train tokens/sec (box, max over ranks) + MFU, Qwen3-8B shape 32k-128k ctx, 1/2/4/8 GPU",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+            "impl": "ours",
+            "config": {"model": args.model, "layers": cfg.num_layers, "hidden": cfg.hidden_size,
+                       "objective": "fast_dllm_v2", "block_size": args.block_size,
+                       "global_batch": args.batch_per_gpu * world, "seq_len": args.seq_len,
+                       "parallelism": f"dp{world}" + ("_zero_sharded_optimizer" if world > 1 else ""),
+                       "activation_checkpointing": True, "optimizer": "AdamW fp32 master, clip 1.0",
+                       "l2": "inputs larger than L2 (16 GB of bf16 weights and >2 GB activations per layer stream "
+                             "through HBM every step); no flush needed",
+                       "noisy_views_share_clean_copy": True},
+            "model_tflop_per_step": fl.total / 1e12,
+            "mfu_pct_of_nominal_2250": model_flops_utilization_pct(fl.total, ms / 1e3, world, 2250.0),
+            "gpu_launches": launches, "loss": loss, "clocks": clocks, "e2e": e2e,
+        }
+        if peaks.get("bf16_tflops_sustained"):
+            out["mfu_pct_of_measured_sustained"] = model_flops_utilization_pct(
+                fl.total, ms / 1e3, world, peaks["bf16_tflops_sustained"])
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    from baseline.reference_arm import run as run_ref
+
+    print(json.dumps(run_ref(args)), flush=True)
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -1,0 +1,81 @@
+"""Times the block-diffusion attention kernels (forward, backward) on one GPU.
+
+    python -m turbo_dllm_b200.benchmarks.attention_bench --seq 32768 --block 32 --heads 32 --kv-heads 8
+
+FLOPs are counted on the exactly visible query-key pairs (4·pairs·D per head forward,
+10·pairs·D backward), the convention of the reference's exact attention-pair counters
+(dllm_parallel/core/profiling/perf.py:872-878). Prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+
+def main(argv=None):
+    from turbo_dllm_b200.ops.attention import (attention_backward_native, attention_forward_native,
+                                               single_sequence_layout)
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--seq", type=int, default=32768)
+    ap.add_argument("--block", type=int, default=32)
+    ap.add_argument("--views", type=int, default=1)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--fwd-only", action="store_true")
+    args = ap.parse_args(argv)
+    D = 128
+    dev = "cuda"
+    layout = single_sequence_layout(args.seq, args.block, dev, args.views)
+    n = (args.views + 1) * args.seq
+    B = args.seq // args.block
+    pairs = args.views * (args.block ** 2) * B * (B + 1) // 2 + (args.block ** 2) * B * (B + 1) // 2
+    qkv = (torch.randn(n, (args.heads + 2 * args.kv_heads) * D, device=dev) * 0.5).bfloat16()
+    q = qkv[:, : args.heads * D].view(n, args.heads, D)
+    k = qkv[:, args.heads * D:(args.heads + args.kv_heads) * D].view(n, args.kv_heads, D)
+    v = qkv[:, (args.heads + args.kv_heads) * D:].view(n, args.kv_heads, D)
+    scale = 1 / math.sqrt(D)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    layout.tile_lists()
+
+    def timeit(fn):
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(args.iters):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    out, lse = attention_forward_native(q, k, v, layout, scale)
+    fwd_ms = timeit(lambda: attention_forward_native(q, k, v, layout, scale))
+    rec = {"seq": args.seq, "block": args.block, "views": args.views, "heads": args.heads,
+           "kv_heads": args.kv_heads, "pairs": pairs,
+           "visited_tile_pairs": layout.tile_lists()["visited_tiles"],
+           "fwd_ms": round(fwd_ms, 3),
+           "fwd_tflops_exact_pairs": round(4.0 * pairs * D * args.heads / fwd_ms / 1e9, 1),
+           "fwd_tflops_visited_tiles": round(4.0 * layout.tile_lists()["visited_tiles"] * 128 * 128 * D
+                                             * args.heads / fwd_ms / 1e9, 1)}
+    if not args.fwd_only:
+        dout = torch.randn_like(out)
+        dqkv = torch.empty_like(qkv)
+        bwd_ms = timeit(lambda: attention_backward_native(q, k, v, out, dout, lse, layout, scale, dqkv))
+        rec["bwd_ms"] = round(bwd_ms, 3)
+        rec["bwd_tflops_exact_pairs"] = round(10.0 * pairs * D * args.heads / bwd_ms / 1e9, 1)
+    print(json.dumps(rec), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -156,7 +156,13 @@ def lib() -> ctypes.CDLL:
         return _lib
 
 
+LAUNCHES = {"kernels": 0}
+# device kernels launched by one successful call of each entry point
+_KERNELS_PER_CALL = {"rmsnorm_bwd": 2, "qk_norm_rope_bwd": 4, "attn_bwd": 3}
+
+
 def check(rc: int, what: str) -> None:
+    LAUNCHES["kernels"] += _KERNELS_PER_CALL.get(what, 1)
     if rc != 0:
         msg = lib().tdllm_last_error()
         raise NativeKernelError(f"{what} failed (code {rc}): {msg.decode() if msg else ''}")

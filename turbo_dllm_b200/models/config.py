@@ -1,0 +1,124 @@
+"""Architecture description of the first-party decoder and named shape presets.
+
+The reference reads architectures from Hugging Face configs
+(dllm_parallel/core/models/hf_loader.py:50-78); here the same fields can also come from the
+run spec (`model.random_init` with explicit sizes) or from a preset id such as
+`synthetic:qwen3-8b`, because benchmarks and tests run without network access.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, replace
+
+
+@dataclass(frozen=True)
+class ModelConfig:
+    vocab_size: int
+    hidden_size: int
+    num_layers: int
+    num_attention_heads: int
+    num_key_value_heads: int
+    head_dim: int
+    intermediate_size: int
+    rope_theta: float = 1.0e6
+    rms_norm_eps: float = 1.0e-6
+    qk_norm: bool = True
+    tie_word_embeddings: bool = False
+    mask_token_id: int | None = None
+    # mixture of experts (num_experts = 0 means dense FFN)
+    num_experts: int = 0
+    num_experts_per_token: int = 0
+    moe_intermediate_size: int = 0
+    sliding_window: int | None = None
+    family: str = "causal_lm"
+
+    @property
+    def q_dim(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    @property
+    def qkv_dim(self) -> int:
+        return self.q_dim + 2 * self.kv_dim
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def layer_params(self) -> int:
+        h = self.hidden_size
+        attn = h * self.qkv_dim + self.q_dim * h + (2 * self.head_dim if self.qk_norm else 0)
+        if self.is_moe:
+            ffn = self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
+        else:
+            ffn = 3 * h * self.intermediate_size
+        return attn + ffn + 2 * h
+
+    def num_params(self) -> int:
+        emb = self.vocab_size * self.hidden_size
+        head = 0 if self.tie_word_embeddings else emb
+        return emb + head + self.num_layers * self.layer_params() + self.hidden_size
+
+
+PRESETS: dict[str, ModelConfig] = {
+    # BASELINE config 1 (CPU plumbing model)
+    "synthetic:tiny-qwen3": ModelConfig(vocab_size=1024, hidden_size=256, num_layers=4, num_attention_heads=4,
+                                        num_key_value_heads=2, head_dim=64, intermediate_size=704,
+                                        mask_token_id=1023),
+    # a small head_dim-128 model for GPU smoke tests
+    "synthetic:tiny-hd128": ModelConfig(vocab_size=2048, hidden_size=512, num_layers=2, num_attention_heads=4,
+                                        num_key_value_heads=2, head_dim=128, intermediate_size=1024,
+                                        mask_token_id=2047),
+    "synthetic:qwen3-1.7b": ModelConfig(vocab_size=151936, hidden_size=2048, num_layers=28, num_attention_heads=16,
+                                        num_key_value_heads=8, head_dim=128, intermediate_size=6144,
+                                        tie_word_embeddings=True, mask_token_id=151935),
+    "synthetic:qwen3-8b": ModelConfig(vocab_size=151936, hidden_size=4096, num_layers=36, num_attention_heads=32,
+                                      num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+                                      mask_token_id=151935),
+    "synthetic:moe-48l": ModelConfig(vocab_size=151936, hidden_size=2048, num_layers=48, num_attention_heads=32,
+                                     num_key_value_heads=4, head_dim=128, intermediate_size=0, num_experts=128,
+                                     num_experts_per_token=8, moe_intermediate_size=768, mask_token_id=151935,
+                                     family="diffusion_gemma"),
+    "synthetic:dflash-draft-5l": ModelConfig(vocab_size=151936, hidden_size=4096, num_layers=5,
+                                             num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                                             intermediate_size=12288, mask_token_id=151935, family="dflash"),
+}
+
+
+def model_config_from_run_spec(spec) -> ModelConfig:
+    """Preset named by `model.id` (when it is one) overridden by explicit shape fields."""
+    m = spec.model
+    base = PRESETS.get(m.id)
+    if base is None:
+        if not m.random_init:
+            raise ValueError(
+                f"model.id {m.id!r} is not a built-in preset ({', '.join(PRESETS)}); loading Hugging Face "
+                "checkpoints needs `turbo_dllm_b200.models.hf_loader` and a local path, or set "
+                "model.random_init=true with explicit shape fields")
+        need = ("vocab_size", "hidden_size", "num_layers", "num_attention_heads")
+        missing = [n for n in need if getattr(m, n) is None]
+        if missing:
+            raise ValueError(f"model.random_init needs model.{', model.'.join(missing)}")
+        heads = m.num_attention_heads
+        base = ModelConfig(vocab_size=m.vocab_size, hidden_size=m.hidden_size, num_layers=m.num_layers,
+                           num_attention_heads=heads, num_key_value_heads=m.num_key_value_heads or heads,
+                           head_dim=m.head_dim or m.hidden_size // heads,
+                           intermediate_size=m.intermediate_size or 4 * m.hidden_size)
+    over = {}
+    for name in ("vocab_size", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
+                 "intermediate_size", "rope_theta", "mask_token_id", "num_experts", "num_experts_per_token",
+                 "moe_intermediate_size"):
+        v = getattr(m, name)
+        if v is not None:
+            over[name] = v
+    if m.num_layers is not None:
+        over["num_layers"] = m.num_layers
+    if m.max_layers is not None:
+        over["num_layers"] = min(over.get("num_layers", base.num_layers), m.max_layers)
+    over["qk_norm"] = m.qk_norm and base.qk_norm
+    cfg = replace(base, **over)
+    if cfg.mask_token_id is None:
+        cfg = replace(cfg, mask_token_id=cfg.vocab_size - 1)
+    return cfg

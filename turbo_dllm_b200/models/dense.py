@@ -1,0 +1,197 @@
+"""First-party block-diffusion decoder (Qwen3-style dense transformer) over packed rows.
+
+A rank processes rows `[noisy rows of its blocks ; its clean rows]` (see `parallel.layout`).
+Each layer is RMSNorm → fused QKV GEMM → per-head q/k RMSNorm + RoPE → block-diffusion
+attention → O GEMM → (residual add + RMSNorm fused) → gate/up GEMM with SwiGLU → down GEMM,
+built from this package's own ops so that on a B200 every step is an sm_100a kernel. All
+parameters are views of one flat buffer and gradients land in one flat gradient buffer
+(`FlatParams`), which is what the sharded optimizer and its collectives operate on.
+
+The reference wraps a Hugging Face decoder instead
+(`NemotronLabsDiffusionPackedBlockDiffusionModel`, dllm_parallel/core/models/backbones/nemotron/model.py:532-878,
+layer body :2946-3211, loss :2046-2151); the generic causal-LM family reuses that wrapper
+(dllm_parallel/core/models/backbones/causal_lm/executor.py:76-113).
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from ..ops.attention import MaskLayout, packed_block_attention
+from ..ops.embedding import embedding
+from ..ops.gemm import linear, linear_swiglu
+from ..ops.linear_ce import linear_cross_entropy
+from ..ops.norm import rmsnorm
+from ..ops.rope import qk_norm_rope, rope_inv_freq
+from .config import ModelConfig
+
+ALIGN = 128  # elements; keeps every parameter 256-byte aligned inside the flat buffer
+
+
+class FlatParams:
+    """One flat parameter buffer and one flat gradient buffer; parameters are views.
+
+    Decayed parameters (matrices) come first, then the non-decayed ones (norm weights), so the
+    optimizer handles weight decay with two contiguous ranges. `zero_grad()` only clears the
+    "already written" flags: the first gradient write of a step overwrites its slice.
+    """
+
+    def __init__(self, specs: list[tuple[str, tuple[int, ...], bool]], dtype, device,
+                 grad_dtype=None):
+        specs = sorted(specs, key=lambda s: (not s[2],))  # stable: decay first
+        offs, total = {}, 0
+        for name, shape, decay in specs:
+            n = math.prod(shape)
+            offs[name] = (total, n, shape, decay)
+            total += (n + ALIGN - 1) // ALIGN * ALIGN
+        self.numel = total
+        self.decay_numel = 0
+        for name, (o, n, shape, decay) in offs.items():
+            if decay:
+                self.decay_numel = max(self.decay_numel, (o + n + ALIGN - 1) // ALIGN * ALIGN)
+        self.data = torch.zeros(total, dtype=dtype, device=device)
+        self.grad = torch.zeros(total, dtype=grad_dtype or dtype, device=device)
+        self.offsets = offs
+        self.params: dict[str, nn.Parameter] = {}
+        for name, (o, n, shape, decay) in offs.items():
+            p = nn.Parameter(self.data[o:o + n].view(shape))
+            p.main_grad = self.grad[o:o + n].view(shape)
+            p.grad_acc = False
+            p.flat_offset = o
+            p.decay = decay
+            self.params[name] = p
+
+    def zero_grad(self) -> None:
+        for p in self.params.values():
+            p.grad_acc = False
+            p.grad = None
+
+    def collect_grads(self) -> None:
+        """Folds `.grad` tensors produced by plain autograd into the flat buffer and zeroes the
+        slices of parameters that received no gradient at all this step."""
+        for p in self.params.values():
+            if p.grad is not None:
+                if p.grad_acc:
+                    p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                else:
+                    p.main_grad.copy_(p.grad)
+                p.grad_acc = True
+                p.grad = None
+            elif not p.grad_acc:
+                p.main_grad.zero_()
+
+
+def _layer_specs(cfg: ModelConfig, i: int):
+    h, p = cfg.hidden_size, f"layers.{i}."
+    out = [(p + "input_norm", (h,), False), (p + "w_qkv", (cfg.qkv_dim, h), True),
+           (p + "w_o", (h, cfg.q_dim), True), (p + "post_norm", (h,), False),
+           (p + "w_gate_up", (2 * cfg.intermediate_size, h), True),
+           (p + "w_down", (h, cfg.intermediate_size), True)]
+    if cfg.qk_norm:
+        out += [(p + "q_norm", (cfg.head_dim,), False), (p + "k_norm", (cfg.head_dim,), False)]
+    return out
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, idx: int, flat: FlatParams):
+        super().__init__()
+        self.cfg, self.idx = cfg, idx
+        g = lambda n: flat.params[f"layers.{idx}.{n}"]
+        self.input_norm, self.w_qkv, self.w_o = g("input_norm"), g("w_qkv"), g("w_o")
+        self.post_norm, self.w_gate_up, self.w_down = g("post_norm"), g("w_gate_up"), g("w_down")
+        self.q_norm = g("q_norm") if cfg.qk_norm else None
+        self.k_norm = g("k_norm") if cfg.qk_norm else None
+
+    def forward(self, x, residual, positions, inv_freq, attend: Callable):
+        """x: output of the previous sub-layer, residual: running stream (None for layer 0).
+        Returns (mlp_out, residual) — the add happens inside the next norm."""
+        cfg = self.cfg
+        y, res = rmsnorm(x, self.input_norm, cfg.rms_norm_eps, residual)
+        qkv = linear(y, self.w_qkv)
+        qkv = qk_norm_rope(qkv, positions, inv_freq, self.q_norm, self.k_norm, cfg.num_attention_heads,
+                           cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
+        a = attend(qkv, self.idx)          # [rows, Hq·D]
+        o = linear(a, self.w_o)
+        y2, res = rmsnorm(o, self.post_norm, cfg.rms_norm_eps, res)
+        act = linear_swiglu(y2, self.w_gate_up)
+        return linear(act, self.w_down), res
+
+
+class LocalAttention:
+    """Keys are the rank's own rows (single rank, or pure data parallelism)."""
+
+    def __init__(self, cfg: ModelConfig, mask: MaskLayout):
+        self.cfg, self.mask = cfg, mask
+
+    def __call__(self, qkv, layer_idx):
+        c = self.cfg
+        return packed_block_attention(qkv, c.num_attention_heads, c.num_key_value_heads, c.head_dim, self.mask)
+
+
+class BlockDiffusionTransformer(nn.Module):
+    def __init__(self, cfg: ModelConfig, *, dtype=torch.bfloat16, device="cpu", grad_dtype=None,
+                 activation_checkpointing: bool = True, seed: int = 0, init_std: float = 0.02):
+        super().__init__()
+        self.cfg = cfg
+        self.activation_checkpointing = activation_checkpointing
+        h = cfg.hidden_size
+        specs = [("embed", (cfg.vocab_size, h), True), ("final_norm", (h,), False)]
+        if not cfg.tie_word_embeddings:
+            specs.append(("lm_head", (cfg.vocab_size, h), True))
+        for i in range(cfg.num_layers):
+            specs += _layer_specs(cfg, i)
+        self.flat = FlatParams(specs, dtype, device, grad_dtype)
+        for name, p in self.flat.params.items():
+            self.register_parameter(name.replace(".", "_"), p)
+        self.embed = self.flat.params["embed"]
+        self.final_norm = self.flat.params["final_norm"]
+        self.lm_head = self.flat.params.get("lm_head", self.embed)
+        self.layers = nn.ModuleList(DecoderLayer(cfg, i, self.flat) for i in range(cfg.num_layers))
+        self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device), persistent=False)
+        self.reset_parameters(seed, init_std)
+
+    @torch.no_grad()
+    def reset_parameters(self, seed: int, std: float) -> None:
+        gen = torch.Generator(device=self.flat.data.device)
+        gen.manual_seed(seed)
+        for name, p in self.flat.params.items():
+            if p.decay:
+                # generate in fp32 chunks to bound temporary memory for the large matrices
+                flat = p.view(-1)
+                step = 1 << 26
+                for s in range(0, flat.numel(), step):
+                    e = min(s + step, flat.numel())
+                    flat[s:e] = (torch.randn(e - s, device=flat.device, generator=gen) * std).to(flat.dtype)
+            else:
+                p.fill_(1.0)
+
+    def forward(self, tokens: torch.Tensor, positions: torch.Tensor, attend: Callable) -> torch.Tensor:
+        """tokens, positions: [rows]; returns final-norm hidden states [rows, H]."""
+        x = embedding(tokens, self.embed)
+        res = None
+        positions = positions.to(torch.int32)
+        for layer in self.layers:
+            if self.activation_checkpointing and torch.is_grad_enabled():
+                x, res = checkpoint(layer, x, res, positions, self.inv_freq, attend, use_reentrant=False)
+            else:
+                x, res = layer(x, res, positions, self.inv_freq, attend)
+        y, _ = rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps, res)
+        return y
+
+    def loss(self, hidden_rows: torch.Tensor, labels: torch.Tensor, weights: torch.Tensor | None,
+             exclude_mask_token: bool):
+        """Σ weighted CE over rows with label >= 0 (rows are already compacted to supervised ones)."""
+        ex = self.cfg.mask_token_id if exclude_mask_token else -1
+        return linear_cross_entropy(hidden_rows, self.lm_head, labels, weights, exclude_index=ex)
+
+
+def compact_supervised_rows(hidden: torch.Tensor, labels: torch.Tensor, weights: torch.Tensor | None):
+    """Keeps only rows with a label (masked positions): the LM head runs on those alone
+    (dllm_parallel/core/models/backbones/nemotron/model.py:4234)."""
+    idx = (labels >= 0).nonzero(as_tuple=True)[0]
+    h = hidden.index_select(0, idx)
+    return h, labels.index_select(0, idx), (None if weights is None else weights.index_select(0, idx)), idx

@@ -1,0 +1,219 @@
+"""Corruption runtimes of the block-diffusion objectives.
+
+standard_block_diffusion: one diffusion time t per (sample, block), antithetic-stratified by
+default (one uniform draw, strata rotated by it), scaled to [eps_min, eps_max]; a token is
+masked iff rand <= t; labels are the clean token on masked positions and -100 elsewhere; the
+per-block loss weight is 1/t (or 1).
+fast_dllm_v2: t ~ U(0,1) per (sample, block), move chance (1-eps)·t + eps, two complementary
+views (mask, ~mask) share the clean copy, labels are shifted left by one, weights are 1 and the
+denominator is batch·(L-1).
+
+Semantics follow dllm_parallel/core/objectives/runtime.py:112-212 and
+dllm_parallel/core/objectives/fast_dllm_v2.py:66-179; generator state is part of the
+checkpoint (`state_dict`, cf. runtime.py:214-282).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+LABEL_IGNORE_INDEX = -100
+STATE_VERSION = 3
+
+
+@dataclass
+class CorruptedBatch:
+    clean_input_ids: torch.Tensor   # [B, L]
+    noisy_input_ids: torch.Tensor   # [B, V, L]  (V noisy views per sample)
+    labels: torch.Tensor            # [B, V, L]  clean token or -100
+    diffusion_times: torch.Tensor   # [B, nblocks]
+    noise_levels: torch.Tensor      # [B, nblocks]
+    loss_weights: torch.Tensor      # [B, V, nblocks]
+    active_tokens: torch.Tensor     # scalar int64 tensor: supervised positions
+    valid_tokens: int
+    loss_denominator: float
+
+    @property
+    def views(self) -> int:
+        return int(self.noisy_input_ids.shape[1])
+
+
+@dataclass(frozen=True)
+class TokenAccountingPolicy:
+    """Which token counts feed throughput numbers."""
+
+    count_clean_copy: bool = False
+
+    def input_tokens(self, batch: CorruptedBatch) -> int:
+        b, l = batch.clean_input_ids.shape
+        return b * l
+
+
+class _ObjectiveRuntime:
+    name = "base"
+    views = 1
+    exclude_mask_token = True
+
+    def __init__(self, *, block_size: int, mask_token_id: int, max_seq_len: int, seed: int,
+                 device="cpu"):
+        if block_size <= 0:
+            raise ValueError("block_size must be positive")
+        self.block_size = int(block_size)
+        self.mask_token_id = int(mask_token_id)
+        self.max_seq_len = int(max_seq_len)
+        self.device = torch.device(device)
+        self.generator = torch.Generator(device=self.device)
+        self.generator.manual_seed(int(seed))
+        self.seed = int(seed)
+        self.batches_corrupted = 0
+        self.loss_tokens_seen = 0
+        self.valid_tokens_seen = 0
+
+    # -- helpers
+    def _check(self, x0: torch.Tensor, min_len: int = 1) -> tuple[int, int, int]:
+        if x0.ndim != 2:
+            raise ValueError(f"expected rank-2 input_ids, got {tuple(x0.shape)}")
+        b, l = map(int, x0.shape)
+        if not min_len <= l <= self.max_seq_len:
+            raise ValueError(f"sequence length {l} outside [{min_len}, {self.max_seq_len}]")
+        if l % self.block_size:
+            raise ValueError("input sequence length must divide evenly by block_size")
+        return b, l, l // self.block_size
+
+    def _rand(self, shape) -> torch.Tensor:
+        return torch.rand(shape, dtype=torch.float32, device=self.device, generator=self.generator)
+
+    def skip(self, steps: int, batch_shape: tuple[int, int]) -> None:
+        """Advances the generator as `steps` calls of corrupt() on this shape would."""
+        x = torch.zeros(batch_shape, dtype=torch.long, device=self.device)
+        for _ in range(int(steps)):
+            self.corrupt(x)
+
+    def state_dict(self) -> dict[str, Any]:
+        return {"version": STATE_VERSION, "name": self.name, "seed": self.seed,
+                "generator_state": self.generator.get_state().cpu(),
+                "batches_corrupted": self.batches_corrupted,
+                "loss_tokens_seen": int(self.loss_tokens_seen),
+                "valid_tokens_seen": int(self.valid_tokens_seen)}
+
+    def load_state_dict(self, state: dict[str, Any]) -> None:
+        if state.get("version") != STATE_VERSION or state.get("name") != self.name:
+            raise ValueError(f"objective state mismatch: have {self.name} v{STATE_VERSION}, "
+                             f"checkpoint has {state.get('name')} v{state.get('version')}")
+        self.generator.set_state(state["generator_state"].to("cpu"))
+        self.batches_corrupted = int(state["batches_corrupted"])
+        self.loss_tokens_seen = int(state["loss_tokens_seen"])
+        self.valid_tokens_seen = int(state["valid_tokens_seen"])
+
+
+class StandardBlockDiffusionRuntime(_ObjectiveRuntime):
+    name = "standard_block_diffusion"
+    views = 1
+    exclude_mask_token = True
+
+    def __init__(self, *, loss_weighting="inverse_move_chance", noise_schedule_epsilon=1e-3,
+                 sampling_epsilon_min=1e-3, sampling_epsilon_max=1.0, antithetic_sampling=True, **kw):
+        super().__init__(**kw)
+        if loss_weighting not in ("inverse_move_chance", "unit"):
+            raise ValueError(f"unknown loss_weighting {loss_weighting!r}")
+        self.loss_weighting = loss_weighting
+        self.noise_schedule_epsilon = float(noise_schedule_epsilon)
+        self.eps_min, self.eps_max = float(sampling_epsilon_min), float(sampling_epsilon_max)
+        self.antithetic = bool(antithetic_sampling)
+
+    def sample_times(self, b: int, nblk: int) -> torch.Tensor:
+        if self.antithetic:
+            n = b * nblk
+            u = self._rand((1,))
+            strata = torch.arange(n, dtype=torch.float32, device=self.device).view(b, nblk) / float(n)
+            t = (u + strata).remainder(1.0)
+        else:
+            t = self._rand((b, nblk))
+        return t * (self.eps_max - self.eps_min) + self.eps_min
+
+    def corrupt(self, x0, *, supervision_mask=None, supervision_count=None) -> CorruptedBatch:
+        b, l, nblk = self._check(x0)
+        x0 = x0.to(self.device)
+        if supervision_mask is None:
+            if supervision_count is not None:
+                raise ValueError("supervision_count requires an explicit supervision_mask")
+            eligible, valid = None, b * l
+        else:
+            if supervision_mask.shape != x0.shape:
+                raise ValueError("supervision_mask must match input_ids")
+            eligible = supervision_mask.to(self.device, torch.bool)
+            valid = int(eligible.sum()) if supervision_count is None else int(supervision_count)
+        if valid <= 0:
+            raise ValueError("each training batch must contain supervised tokens")
+        t = self.sample_times(b, nblk)
+        weights = torch.ones_like(t) if self.loss_weighting == "unit" else t.reciprocal()
+        noise = (-torch.log1p(-t)).clamp(max=-math.log(self.noise_schedule_epsilon))
+        mask = self._rand(x0.shape) <= t.repeat_interleave(self.block_size, dim=1)
+        if eligible is not None:
+            mask &= eligible
+        xt = torch.where(mask, torch.full_like(x0, self.mask_token_id), x0)
+        labels = torch.where(mask, x0, torch.full_like(x0, LABEL_IGNORE_INDEX))
+        active = mask.sum(dtype=torch.int64)
+        self.batches_corrupted += 1
+        self.valid_tokens_seen += valid
+        return CorruptedBatch(x0, xt[:, None], labels[:, None], t, noise, weights[:, None], active,
+                              valid, float(valid))
+
+
+class FastDLLMv2Runtime(_ObjectiveRuntime):
+    name = "fast_dllm_v2"
+    views = 2
+    exclude_mask_token = False
+
+    def __init__(self, *, noise_schedule_epsilon=1e-3, **kw):
+        super().__init__(**kw)
+        self.noise_schedule_epsilon = float(noise_schedule_epsilon)
+
+    def corrupt(self, x0, *, supervision_mask=None, supervision_count=None) -> CorruptedBatch:
+        b, l, nblk = self._check(x0, min_len=2)
+        x0 = x0.to(self.device)
+        if supervision_mask is None:
+            if supervision_count is not None:
+                raise ValueError("supervision_count requires an explicit supervision_mask")
+            eligible = torch.ones_like(x0, dtype=torch.bool)
+            valid = b * (l - 1)  # position 0 has no preceding query under the shifted loss
+        else:
+            if supervision_mask.shape != x0.shape:
+                raise ValueError("supervision_mask must match input_ids")
+            eligible = supervision_mask.to(self.device, torch.bool)
+            valid = (int(eligible[:, 1:].sum()) if supervision_count is None
+                     else int(supervision_count) - int(eligible[:, 0].sum()))
+        if valid <= 0:
+            raise ValueError("each training batch must contain shifted supervised tokens")
+        t = self._rand((b, nblk))
+        move = (1.0 - self.noise_schedule_epsilon) * t + self.noise_schedule_epsilon
+        sampled = self._rand(x0.shape) < move.repeat_interleave(self.block_size, dim=1)
+        masks = torch.stack([sampled & eligible, (~sampled) & eligible], dim=1)      # [B, 2, L]
+        x0v = x0[:, None].expand(-1, 2, -1)
+        noisy = torch.where(masks, torch.full_like(x0v, self.mask_token_id), x0v)
+        targets = torch.where(masks, x0v, torch.full_like(x0v, LABEL_IGNORE_INDEX))
+        labels = torch.full_like(targets, LABEL_IGNORE_INDEX)
+        labels[:, :, :-1] = targets[:, :, 1:]
+        active = (labels != LABEL_IGNORE_INDEX).sum(dtype=torch.int64)
+        self.batches_corrupted += 1
+        self.valid_tokens_seen += valid
+        return CorruptedBatch(x0, noisy, labels, t, move, torch.ones(b, 2, nblk, device=self.device),
+                              active, valid, float(valid))
+
+
+def build_objective_runtime(spec, *, mask_token_id: int, seed: int, device="cpu"):
+    """spec: RunSpec. Returns the corruption runtime of `objective.name`."""
+    o = spec.objective
+    common = dict(block_size=o.block_size, mask_token_id=mask_token_id, max_seq_len=spec.model.seq_len,
+                  seed=seed, device=device)
+    if o.name == "standard_block_diffusion":
+        return StandardBlockDiffusionRuntime(
+            loss_weighting=o.loss_weighting, noise_schedule_epsilon=o.noise_schedule_epsilon,
+            sampling_epsilon_min=o.sampling_epsilon_min, sampling_epsilon_max=o.sampling_epsilon_max,
+            antithetic_sampling=o.antithetic_sampling, **common)
+    if o.name == "fast_dllm_v2":
+        return FastDLLMv2Runtime(noise_schedule_epsilon=o.noise_schedule_epsilon, **common)
+    raise ValueError(f"no corruption runtime for objective {o.name!r}")

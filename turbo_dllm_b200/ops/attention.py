@@ -286,3 +286,45 @@ def block_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layout: M
     if q.is_cuda and q.dtype == torch.bfloat16:
         raise native.NativeKernelError("bf16 CUDA attention needs head_dim 128 (no silent fallback)")
     return attention_reference(q, k, v, layout, scale)[0]
+
+
+def split_packed_qkv(qkv: torch.Tensor, Hq: int, Hkv: int, D: int):
+    rows = qkv.shape[0]
+    q = qkv[:, : Hq * D].view(rows, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(rows, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(rows, Hkv, D)
+    return q, k, v
+
+
+class _PackedBlockAttention(torch.autograd.Function):
+    """Self-attention over a packed [rows, (Hq+2Hkv)·D] projection; the backward writes the three
+    gradients into one packed buffer, so no slice-gradient copies are needed."""
+
+    @staticmethod
+    def forward(ctx, qkv, Hq, Hkv, D, layout, scale):
+        q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
+        out, lse = attention_forward_native(q, k, v, layout, scale)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.meta = (Hq, Hkv, D, layout, scale)
+        return out.view(qkv.shape[0], Hq * D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse = ctx.saved_tensors
+        Hq, Hkv, D, layout, scale = ctx.meta
+        q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
+        dqkv = torch.empty_like(qkv)
+        attention_backward_native(q, k, v, out, dout.contiguous().view(-1, Hq, D), lse, layout, scale, dqkv)
+        return dqkv, None, None, None, None, None
+
+
+def packed_block_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, layout: MaskLayout,
+                           scale: float | None = None) -> torch.Tensor:
+    """qkv [rows, (Hq+2Hkv)·D] -> [rows, Hq·D]; queries and keys are the same rows."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if use_native(qkv) and D == 128:
+        return _PackedBlockAttention.apply(qkv, Hq, Hkv, D, layout, scale)
+    if qkv.is_cuda and qkv.dtype == torch.bfloat16:
+        raise native.NativeKernelError("bf16 CUDA attention needs head_dim 128 (no silent fallback)")
+    q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
+    return attention_reference(q, k, v, layout, scale)[0].reshape(qkv.shape[0], Hq * D)

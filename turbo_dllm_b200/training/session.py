@@ -1,0 +1,203 @@
+"""TrainingSession: everything one rank needs to run optimizer steps from a RunSpec.
+
+This is the public programmatic entry point (`turbo_dllm_b200.train` builds one and loops it;
+`bench.py` drives it directly): model, objective runtime, data runtime, packed row layout,
+attention transport, sharded optimizer and LR schedule. `step()` performs zero-grad → data →
+corruption → forward → fused linear-CE loss → backward → gradient sync → clip → AdamW, and
+returns the step's loss numerator/denominator as device tensors (no host sync inside).
+
+It plays the role of the set-up half of the reference trainer
+(dllm_parallel/training/block_diffusion_trainer.py:501-1265) plus one iteration of its step loop
+(:1265-1545).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from ..config.run_spec import RunSpec
+from ..data.runtimes import DataBatch, HostStagedRandomRuntime, RandomTokenDataRuntime
+from ..models.config import ModelConfig, model_config_from_run_spec
+from ..models.dense import BlockDiffusionTransformer, LocalAttention, compact_supervised_rows
+from ..objectives.runtime import CorruptedBatch, build_objective_runtime
+from ..optim.flat_adamw import FlatAdamW
+from ..optim.schedule import RunSpecLRScheduler
+from ..parallel.layout import (PackedLayout, build_packed_layout, clean_positions_for_rank,
+                               runtime_clean_layout)
+
+_DTYPES = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
+
+
+@dataclass
+class StepResult:
+    loss_sum: torch.Tensor        # Σ weighted CE over this rank's supervised rows (device scalar)
+    denominator: float            # global loss denominator of the step
+    supervised_rows: torch.Tensor
+    input_tokens: int             # tokens of this rank's micro-batches (clean copy not counted)
+    h2d_bytes: int
+
+
+class TrainingSession:
+    def __init__(self, spec: RunSpec, *, device: str | torch.device | None = None, runtime=None,
+                 host_staged_data: bool = False):
+        self.spec = spec
+        self.runtime = runtime  # parallel runtime (None = single rank)
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        if device is None:
+            device = f"cuda:{int(os.environ.get('LOCAL_RANK', 0))}" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        if self.device.type == "cuda":
+            if self.device.index is None:
+                self.device = torch.device("cuda", torch.cuda.current_device())
+            torch.cuda.set_device(self.device)
+        self.dtype = _DTYPES[spec.model.dtype]
+        if self.device.type == "cpu" and self.dtype != torch.float32:
+            raise ValueError("CPU runs use model.dtype=fp32 (the reference path is the fp32 oracle)")
+        self.cfg: ModelConfig = model_config_from_run_spec(spec)
+        seed = spec.launch.seed
+        self.model = BlockDiffusionTransformer(
+            self.cfg, dtype=self.dtype, device=self.device,
+            activation_checkpointing=spec.training.activation_checkpointing, seed=seed)
+        dp_rank = runtime.data_parallel_rank if runtime is not None else self.rank
+        self.dp_size = runtime.data_parallel_size if runtime is not None else self.world
+        self.objective = build_objective_runtime(spec, mask_token_id=self.cfg.mask_token_id,
+                                                 seed=seed + 7919 * (dp_rank + 1), device=self.device)
+        data_kw = dict(batch_size=spec.training.batch_size, seq_len=spec.model.seq_len,
+                       vocab_size=self.cfg.vocab_size, mask_token_id=self.cfg.mask_token_id,
+                       seed=seed + 104729 * (dp_rank + 1), vocab_sample_size=spec.data.vocab_sample_size)
+        if spec.data.input_mode == "random":
+            self.data = (HostStagedRandomRuntime(device=self.device, **data_kw) if host_staged_data
+                         else RandomTokenDataRuntime(device=self.device, **data_kw))
+        else:
+            from ..data.artifact_runtimes import build_artifact_runtime
+
+            self.data = build_artifact_runtime(spec, device=self.device, dp_rank=dp_rank, dp_size=self.dp_size)
+        self.layout = self._build_layout()
+        self.attend = self._build_attention()
+        group = runtime.optimizer_group if runtime is not None else (dist.group.WORLD if self.world > 1 else None)
+        o = spec.optimizer
+        self.optimizer = FlatAdamW(self.model.flat, lr=o.lr, betas=(o.adam_beta1, o.adam_beta2), eps=o.adam_eps,
+                                   weight_decay=o.weight_decay, group=group,
+                                   fused_sync=self._build_fused_sync(group))
+        self.scheduler = RunSpecLRScheduler.from_run_spec(spec)
+        self.steps_done = 0
+
+    # ---------------------------------------------------------------- set-up
+    def _build_layout(self) -> PackedLayout:
+        s, rt = self.spec, self.runtime
+        owned, clean = None, None
+        if rt is not None and rt.block_parallel_size > 1:
+            owned = rt.owned_blocks
+        if rt is not None and rt.context_parallel_size > 1:
+            lay = runtime_clean_layout(s.kernel.cp_bp_clean_kv_layout, rt.block_parallel_size)
+            clean = clean_positions_for_rank(s.model.seq_len, rt.context_parallel_size, rt.context_parallel_rank,
+                                             lay, s.objective.block_size, self.device)
+        elif rt is not None and rt.block_parallel_size > 1 and s.topology.replicate_clean_prefix:
+            last = max(owned)
+            clean = torch.arange(0, last * s.objective.block_size, device=self.device)
+        return build_packed_layout(seq_len=s.model.seq_len, block_size=s.objective.block_size,
+                                   batch=s.training.batch_size, views=self.objective.views,
+                                   owned_blocks=owned, clean_pos=clean, device=self.device)
+
+    def _build_attention(self):
+        rt = self.runtime
+        if rt is not None and rt.context_parallel_size > 1:
+            from ..parallel.context_attention import ContextParallelAttention
+
+            return ContextParallelAttention(self.cfg, self.layout, rt, self.spec)
+        return LocalAttention(self.cfg, self.layout.mask)
+
+    def _build_fused_sync(self, group):
+        if group is None or self.device.type != "cuda" or self.spec.kernel.impl in ("cpu_reference", "nccl_baseline"):
+            return None
+        if self.spec.optimizer.backend not in ("auto", "zero_fused"):
+            return None
+        try:
+            from ..parallel.fused_zero import FusedZeroSync
+
+            return FusedZeroSync.create(self.model.flat, group)
+        except Exception as e:  # no peer access, IPC refused, ...: keep the NCCL path, say why
+            if self.spec.optimizer.backend == "zero_fused":
+                raise
+            if self.rank == 0:
+                print(f"[turbo_dllm_b200] fused ZeRO sync unavailable ({e}); using NCCL collectives", flush=True)
+            return None
+
+    # ------------------------------------------------------------------ rows
+    def assemble_rows(self, cb: CorruptedBatch):
+        """Gathers this rank's packed rows from a corrupted batch.
+        Returns (tokens [rows], labels [rows], weights [rows] or None)."""
+        lay = self.layout
+        bs = lay.block_size
+        noisy = cb.noisy_input_ids[lay.noisy_seq, lay.noisy_view, lay.noisy_pos]
+        clean = cb.clean_input_ids[lay.clean_seq, lay.clean_pos]
+        tokens = torch.cat([noisy, clean])
+        nlab = cb.labels[lay.noisy_seq, lay.noisy_view, lay.noisy_pos]
+        labels = torch.cat([nlab, torch.full_like(clean, -100)])
+        w = cb.loss_weights[lay.noisy_seq, lay.noisy_view, lay.noisy_pos // bs]
+        weights = torch.cat([w, torch.zeros(clean.shape[0], device=w.device)])
+        return tokens, labels, weights
+
+    # ------------------------------------------------------------------ step
+    def forward_backward(self, batch: DataBatch, denominator: float):
+        cb = self.objective.corrupt(batch.input_ids, supervision_mask=batch.supervision_mask,
+                                    supervision_count=batch.supervision_count)
+        tokens, labels, weights = self.assemble_rows(cb)
+        hidden = self.model(tokens, self.layout.positions, self.attend)
+        h, l, w, _ = compact_supervised_rows(hidden, labels, weights)
+        loss_sum, _ = self.model.loss(h, l, w, self.objective.exclude_mask_token)
+        (loss_sum / denominator).backward()
+        return loss_sum.detach(), l.shape[0], cb
+
+    def global_denominator(self, batches: list[DataBatch]) -> float:
+        """Loss denominator of the whole optimizer step over all data-parallel ranks."""
+        b, l = batches[0].input_ids.shape
+        per = (l - 1) if self.objective.name == "fast_dllm_v2" else l
+        if all(x.supervision_mask is None for x in batches):
+            return float(b * per * len(batches) * self.dp_size)
+        cnt = torch.zeros(1, dtype=torch.float64, device=self.device)
+        for x in batches:
+            m = x.supervision_mask
+            cnt += (m[:, 1:] if self.objective.name == "fast_dllm_v2" else m).sum()
+        if self.world > 1:
+            dist.all_reduce(cnt)
+            bpcp = (self.runtime.local_parallel_size * self.runtime.tensor_parallel_size) if self.runtime else 1
+            cnt /= bpcp
+        return float(cnt)
+
+    def step(self) -> StepResult:
+        spec = self.spec
+        self.model.flat.zero_grad()
+        batches = self.data.next_optimizer_step_batches(spec.training.gradient_accumulation_steps)
+        denom = self.global_denominator(batches)
+        total = torch.zeros((), dtype=torch.float32, device=self.device)
+        rows = 0
+        for b in batches:
+            ls, n, _ = self.forward_backward(b, denom)
+            total += ls.float()
+            rows += n
+        self.model.flat.collect_grads()
+        lr, wd = self.scheduler.step()
+        if not spec.training.skip_optimizer_step:
+            self.optimizer.step(lr=lr, weight_decay=wd, max_grad_norm=spec.optimizer.gradient_clip_norm)
+        self.steps_done += 1
+        return StepResult(total, denom, torch.tensor(rows), sum(int(b.input_ids.numel()) for b in batches),
+                          sum(b.h2d_bytes for b in batches))
+
+    # ------------------------------------------------------------- checkpoint
+    def state_dict(self) -> dict:
+        return {"model": self.model.flat.data, "optimizer": self.optimizer.state_dict(),
+                "scheduler": self.scheduler.state_dict(), "objective": self.objective.state_dict(),
+                "data": self.data.state_dict(), "steps_done": self.steps_done}
+
+    def load_state_dict(self, state: dict) -> None:
+        self.model.flat.data.copy_(state["model"])
+        self.optimizer.load_state_dict(state["optimizer"])
+        self.scheduler.load_state_dict(state["scheduler"])
+        self.objective.load_state_dict(state["objective"])
+        self.data.load_state_dict(state["data"])
+        self.steps_done = int(state["steps_done"])
