@@ -1,0 +1,85 @@
+"""Spawn + deadline harness for multi-rank tests: runs `fn(rank, world, *args)` in `world` child
+processes with a gloo (or nccl) process group on 127.0.0.1, collects ("ok" | "error", payload)
+per rank through a queue, and terminates stragglers when the deadline passes — a hung or failed
+rank becomes a test failure, never a hung test session."""
+from __future__ import annotations
+
+import os
+import socket
+import time
+import traceback
+
+import torch.multiprocessing as mp
+
+
+def _free_port() -> int:
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _plain(obj):
+    """Tensors cross the queue as numpy arrays: a torch tensor in a queue needs its sender alive
+    until the receiver has mapped it, and ranks exit as soon as they are done."""
+    import torch
+
+    if torch.is_tensor(obj):
+        return obj.detach().cpu().numpy()
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_plain(o) for o in obj)
+    if isinstance(obj, dict):
+        return {k: _plain(v) for k, v in obj.items()}
+    return obj
+
+
+def _child(rank, world, port, backend, fn, args, queue):
+    try:
+        import torch.distributed as dist
+
+        os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank),
+                           "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank)})
+        if backend is not None:
+            dist.init_process_group(backend, rank=rank, world_size=world)
+        out = fn(rank, world, *args)
+        if backend is not None and dist.is_initialized():
+            dist.destroy_process_group()
+        queue.put((rank, "ok", _plain(out)))
+    except BaseException:
+        queue.put((rank, "error", traceback.format_exc()))
+
+
+def run_ranks(fn, world: int, args=(), backend: str | None = "gloo", deadline_s: float = 120.0):
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_child, args=(r, world, port, backend, fn, args, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results, t0 = {}, time.time()
+    try:
+        while len(results) < world and time.time() - t0 < deadline_s:
+            try:
+                rank, status, payload = queue.get(timeout=0.5)
+                results[rank] = (status, payload)
+                if status == "error":
+                    break
+            except Exception:
+                if all(not p.is_alive() for p in procs) and queue.empty():
+                    break
+    finally:
+        for p in procs:
+            p.join(timeout=0.1 if len(results) < world else 10)
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=5)
+                if p.is_alive():
+                    p.kill()
+    errors = {r: pl for r, (st, pl) in results.items() if st == "error"}
+    if errors:
+        raise AssertionError("rank failure:\n" + "\n".join(f"[rank {r}]\n{tb}" for r, tb in errors.items()))
+    if len(results) < world:
+        missing = sorted(set(range(world)) - set(results))
+        raise AssertionError(f"ranks {missing} did not finish within {deadline_s}s (terminated)")
+    return [results[r][1] for r in range(world)]

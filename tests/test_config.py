@@ -1,0 +1,89 @@
+import json
+
+import pytest
+import yaml
+
+from turbo_dllm_b200.config.run_spec import (RunSpec, RunSpecError, build_run_spec_arg_parser, load_run_spec,
+                                             run_spec_from_args)
+from turbo_dllm_b200.config.schema import SECTIONS
+
+
+def base(**over):
+    m = {"model": {"id": "synthetic:tiny-qwen3", "seq_len": 512, "dtype": "fp32"},
+         "objective": {"name": "standard_block_diffusion", "block_size": 32},
+         "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}
+    for k, v in over.items():
+        m.setdefault(k, {}).update(v)
+    return m
+
+
+def test_sections_and_defaults_match_the_public_schema():
+    assert list(SECTIONS) == ["model", "objective", "data", "training", "evaluation", "adapter", "topology",
+                              "optimizer", "scheduler", "checkpointing", "profiler", "logging", "debug", "kernel",
+                              "launch"]
+    s = RunSpec.default()
+    assert s.model.seq_len == 1024 and s.model.attention_backend == "flex"
+    assert s.topology.context_parallel_size == 4 and s.topology.block_parallel_size == 4
+    assert s.optimizer.lr == 1e-6 and s.optimizer.adam_eps == 1e-5 and s.launch.seed == 2026
+    assert s.objective.noise_schedule == "loglinear" and s.objective.antithetic_sampling is True
+    assert s.checkpointing.checkpoint_tag == "latest" and s.evaluation.seed == 314159
+
+
+def test_unknown_section_and_field_are_rejected():
+    with pytest.raises(RunSpecError, match="unknown run-spec section"):
+        RunSpec.from_mapping({"modle": {}})
+    with pytest.raises(RunSpecError, match="unknown field"):
+        RunSpec.from_mapping({"model": {"sequence_length": 4}})
+    with pytest.raises(RunSpecError, match="cannot interpret"):
+        RunSpec.from_mapping({"model": {"seq_len": "many"}})
+
+
+def test_validate_rules():
+    RunSpec.from_mapping(base()).validate()
+    with pytest.raises(RunSpecError, match="multiple of objective.block_size"):
+        RunSpec.from_mapping(base(model={"seq_len": 500})).validate()
+    with pytest.raises(RunSpecError, match="replicate_clean_prefix"):
+        RunSpec.from_mapping(base(topology={"block_parallel_size": 2})).validate()
+    with pytest.raises(RunSpecError, match="multiple of"):
+        RunSpec.from_mapping(base(topology={"context_parallel_size": 4, "block_parallel_size": 6})).validate()
+    with pytest.raises(RunSpecError, match="sequence_parallel needs"):
+        RunSpec.from_mapping(base(topology={"sequence_parallel": True})).validate()
+    with pytest.raises(RunSpecError, match="pipeline"):
+        RunSpec.from_mapping(base(topology={"pipeline_parallel_size": 2})).validate()
+    with pytest.raises(RunSpecError, match="not supported by family"):
+        RunSpec.from_mapping(base(model={"family": "qwen3_8"})).validate()
+    with pytest.raises(RunSpecError, match="production recipes"):
+        RunSpec.from_mapping(base(launch={"recipe_kind": "prod"})).validate()
+    with pytest.raises(RunSpecError, match="world size"):
+        RunSpec.from_mapping(base(topology={"context_parallel_size": 2, "block_parallel_size": 2})).validate(world_size=3)
+
+
+def test_yaml_roundtrip_and_cli_overrides(tmp_path):
+    p = tmp_path / "train.yaml"
+    p.write_text(yaml.safe_dump(base(optimizer={"lr": 3e-4})))
+    spec = load_run_spec(p)
+    assert spec.optimizer.lr == 3e-4
+    again = RunSpec.from_mapping(yaml.safe_load(spec.to_yaml()))
+    assert again == spec
+    ap = build_run_spec_arg_parser()
+    args = ap.parse_args(["--config", str(p), "--seq-len", "256", "--no-activation-checkpointing",
+                          "--model-id", "synthetic:tiny-hd128", "--target-layer-ids", "1", "3", "--lr", "1e-3"])
+    s2 = run_spec_from_args(args)
+    assert s2.model.seq_len == 256 and s2.training.activation_checkpointing is False
+    assert s2.model.id == "synthetic:tiny-hd128" and s2.model.target_layer_ids == (1, 3) and s2.optimizer.lr == 1e-3
+    pj = tmp_path / "train.json"
+    pj.write_text(json.dumps(base()))
+    assert load_run_spec(pj).model.seq_len == 512
+
+
+def test_every_field_has_a_cli_flag():
+    ap = build_run_spec_arg_parser()
+    dests = {a.dest for a in ap._actions}
+    for section, rows in SECTIONS.items():
+        for r in rows:
+            assert f"{section}__{r.name}" in dests
+
+
+def test_global_batch_rule():
+    s = RunSpec.from_mapping(base(training={"batch_size": 2, "gradient_accumulation_steps": 3}))
+    assert s.global_batch(4) == 24

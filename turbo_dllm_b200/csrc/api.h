@@ -25,7 +25,7 @@ int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, 
                     long long ldb, long long ldd, int a_mn_major, int b_mn_major, int out_fp32,
                     int accumulate, int mode, const int* labels, const float* lse,
                     const float* rowscale, float* stats, int exclude_index, float softcap,
-                    int max_ctas, void* stream);
+                    int max_ctas, const void* c_src, long long ldc, void* stream);
 int tdllm_gemm_n_tiles(int N);
 
 // ---- normalisation / rotary / activation ---------------------------------

@@ -51,9 +51,10 @@ struct GemmParams {
   int out_fp32;
   int accumulate;
   int m_tiles, n_tiles;
-  // plain accumulate path reads the destination directly
-  void* d_ptr;
-  long long ldd;  // elements
+  // accumulate path: D = acc + C, where C is the destination itself or a separate tensor
+  // of the destination's dtype (fused residual add)
+  const void* c_ptr;
+  long long ldc;  // elements
   // cross-entropy epilogues
   const int* labels;      // [M], negative = ignored row
   const float* lse;       // [M]
@@ -290,7 +291,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tmem_ld32(taddr + c * 32, r);
           tmem_ld_wait();
           if (p.accumulate && gm < p.M) {
-            const float* dp = (const float*)p.d_ptr + (size_t)gm * p.ldd + n0 + c * 32;
+            const float* dp = (const float*)p.c_ptr + (size_t)gm * p.ldc + n0 + c * 32;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               if (n0 + c * 32 + j < p.N) {
@@ -351,7 +352,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 r[j] = __float_as_uint(g * row_scale * dcap);
               }
             } else if (p.accumulate && gm < p.M) {
-              const __nv_bfloat16* dp = (const __nv_bfloat16*)p.d_ptr + (size_t)gm * p.ldd + cbase;
+              const __nv_bfloat16* dp = (const __nv_bfloat16*)p.c_ptr + (size_t)gm * p.ldc + cbase;
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 if (cbase + j < p.N) {
@@ -420,7 +421,7 @@ extern "C" int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int
                                int b_mn_major, int out_fp32, int accumulate, int mode,
                                const int* labels, const float* lse, const float* rowscale,
                                float* stats, int exclude_index, float softcap, int max_ctas,
-                               void* stream) {
+                               const void* c_src, long long ldc, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A % 16) || ((uintptr_t)B % 16)) {
     tdllm_host::set_last_error("gemm: operands need 16-byte aligned base and row stride");
@@ -487,7 +488,12 @@ extern "C" int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
   p.mode = mode; p.out_fp32 = out_fp32; p.accumulate = accumulate;
   p.m_tiles = (M + BM - 1) / BM; p.n_tiles = (N + BN - 1) / BN;
-  p.d_ptr = D; p.ldd = ldd;
+  p.c_ptr = c_src ? c_src : D;
+  p.ldc = c_src ? ldc : ldd;
+  if (accumulate && ((uintptr_t)p.c_ptr % 16 || (p.ldc * (out_fp32 ? 4 : 2)) % 16)) {
+    tdllm_host::set_last_error("gemm: accumulate source needs 16-byte aligned base and row stride");
+    return 1;
+  }
   p.labels = labels; p.lse = lse; p.rowscale = rowscale; p.stats = stats;
   p.exclude_index = exclude_index; p.softcap = softcap;
   const int tiles = p.m_tiles * p.n_tiles;

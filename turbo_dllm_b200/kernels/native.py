@@ -92,7 +92,7 @@ _SIGS = {
     "tdllm_test_wait_timeout": (c_int, [c_void_p]),
     "tdllm_gemm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll,
                                 c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                c_void_p, c_int, c_float, c_int, c_void_p]),
+                                c_void_p, c_int, c_float, c_int, c_void_p, c_ll, c_void_p]),
     "tdllm_gemm_n_tiles": (c_int, [c_int]),
     "tdllm_rmsnorm_fwd": (c_int, [c_void_p] * 6 + [c_int, c_int, c_float, c_void_p]),
     "tdllm_rmsnorm_bwd_parts": (c_int, []),

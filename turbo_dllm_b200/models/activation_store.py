@@ -1,0 +1,94 @@
+"""Per-layer activation checkpointing with optional host offload.
+
+Only the residual stream entering each layer is kept for the backward pass; everything inside a
+layer is recomputed. With `offload=True` that tensor is copied to pinned host memory on a side
+stream right after the layer ran and brought back (prefetched one layer ahead) during the
+backward pass, so a long sequence costs one layer's activations of HBM instead of `num_layers`.
+The copies run on their own CUDA stream and overlap the GEMMs; per-step PCIe traffic is
+2 × rows × hidden × 2 bytes × layers.
+
+The reference checkpoints each layer with torch.utils.checkpoint and keeps all layer inputs on
+the device (dllm_parallel/core/models/backbones/nemotron/model.py:2373-2445).
+"""
+from __future__ import annotations
+
+import torch
+
+
+class ActivationStore:
+    def __init__(self, device: torch.device, offload: bool = False):
+        self.device = torch.device(device)
+        self.offload = bool(offload) and self.device.type == "cuda"
+        self.kept: dict[int, torch.Tensor] = {}
+        self.host: dict[int, torch.Tensor] = {}
+        self.ready: dict[int, torch.cuda.Event] = {}
+        self.inflight: dict[int, tuple[torch.Tensor, torch.cuda.Event]] = {}
+        self.stream = torch.cuda.Stream(device=self.device) if self.offload else None
+        self.bytes_offloaded = 0
+
+    def stash(self, idx: int, x: torch.Tensor) -> None:
+        if not self.offload:
+            self.kept[idx] = x
+            return
+        buf = self.host.get(idx)
+        if buf is None or buf.shape != x.shape or buf.dtype != x.dtype:
+            buf = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
+            self.host[idx] = buf
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.stream):
+            buf.copy_(x, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+        x.record_stream(self.stream)  # keep the device block alive until the copy has read it
+        self.ready[idx] = ev
+        self.bytes_offloaded += x.numel() * x.element_size()
+
+    def prefetch(self, idx: int) -> None:
+        if not self.offload or idx < 0 or idx in self.inflight or idx not in self.host:
+            return
+        with torch.cuda.stream(self.stream):
+            self.ready[idx].wait(self.stream)
+            dev = torch.empty(self.host[idx].shape, dtype=self.host[idx].dtype, device=self.device)
+            dev.copy_(self.host[idx], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+        self.inflight[idx] = (dev, ev)
+
+    def fetch(self, idx: int) -> torch.Tensor:
+        if not self.offload:
+            return self.kept.pop(idx)
+        self.prefetch(idx)
+        dev, ev = self.inflight.pop(idx)
+        cur = torch.cuda.current_stream(self.device)
+        cur.wait_event(ev)
+        dev.record_stream(cur)
+        return dev
+
+
+class _LayerCheckpoint(torch.autograd.Function):
+    """Runs `layer(h, *args)` without building a graph; the backward pass re-runs it with grad and
+    back-propagates. Parameter gradients are written by the ops themselves (flat gradient
+    buffer), so only the gradient of `h` is returned."""
+
+    @staticmethod
+    def forward(ctx, h, layer, store, idx, args):
+        ctx.layer, ctx.store, ctx.idx, ctx.args = layer, store, idx, args
+        with torch.no_grad():
+            out = layer(h, *args)
+        store.stash(idx, h)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        store, idx = ctx.store, ctx.idx
+        h = store.fetch(idx)
+        store.prefetch(idx - 1)
+        h = h.detach().requires_grad_(True)
+        with torch.enable_grad():
+            out = ctx.layer(h, *ctx.args)
+        torch.autograd.backward(out, dout)
+        return h.grad, None, None, None, None
+
+
+def checkpointed_layer(layer, h, store: ActivationStore, idx: int, *args):
+    return _LayerCheckpoint.apply(h, layer, store, idx, args)

@@ -19,14 +19,14 @@ from typing import Callable
 
 import torch
 import torch.nn as nn
-from torch.utils.checkpoint import checkpoint
 
 from ..ops.attention import MaskLayout, packed_block_attention
 from ..ops.embedding import embedding
-from ..ops.gemm import linear, linear_swiglu
+from ..ops.gemm import linear, linear_residual, linear_swiglu
 from ..ops.linear_ce import linear_cross_entropy
 from ..ops.norm import rmsnorm
 from ..ops.rope import qk_norm_rope, rope_inv_freq
+from .activation_store import ActivationStore, checkpointed_layer
 from .config import ModelConfig
 
 ALIGN = 128  # elements; keeps every parameter 256-byte aligned inside the flat buffer
@@ -106,19 +106,19 @@ class DecoderLayer(nn.Module):
         self.q_norm = g("q_norm") if cfg.qk_norm else None
         self.k_norm = g("k_norm") if cfg.qk_norm else None
 
-    def forward(self, x, residual, positions, inv_freq, attend: Callable):
-        """x: output of the previous sub-layer, residual: running stream (None for layer 0).
-        Returns (mlp_out, residual) — the add happens inside the next norm."""
+    def forward(self, h, positions, inv_freq, attend: Callable):
+        """h: residual stream [rows, H] -> residual stream. Both residual adds happen in the
+        epilogues of the O and down projections."""
         cfg = self.cfg
-        y, res = rmsnorm(x, self.input_norm, cfg.rms_norm_eps, residual)
+        y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
         qkv = linear(y, self.w_qkv)
         qkv = qk_norm_rope(qkv, positions, inv_freq, self.q_norm, self.k_norm, cfg.num_attention_heads,
                            cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
         a = attend(qkv, self.idx)          # [rows, Hq·D]
-        o = linear(a, self.w_o)
-        y2, res = rmsnorm(o, self.post_norm, cfg.rms_norm_eps, res)
+        h = linear_residual(a, self.w_o, h)
+        y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
         act = linear_swiglu(y2, self.w_gate_up)
-        return linear(act, self.w_down), res
+        return linear_residual(act, self.w_down, h)
 
 
 class LocalAttention:
@@ -134,10 +134,12 @@ class LocalAttention:
 
 class BlockDiffusionTransformer(nn.Module):
     def __init__(self, cfg: ModelConfig, *, dtype=torch.bfloat16, device="cpu", grad_dtype=None,
-                 activation_checkpointing: bool = True, seed: int = 0, init_std: float = 0.02):
+                 activation_checkpointing: bool = True, activation_offload: bool = False, seed: int = 0,
+                 init_std: float = 0.02):
         super().__init__()
         self.cfg = cfg
         self.activation_checkpointing = activation_checkpointing
+        self.store = ActivationStore(torch.device(device), offload=activation_offload)
         h = cfg.hidden_size
         specs = [("embed", (cfg.vocab_size, h), True), ("final_norm", (h,), False)]
         if not cfg.tie_word_embeddings:
@@ -171,15 +173,14 @@ class BlockDiffusionTransformer(nn.Module):
 
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor, attend: Callable) -> torch.Tensor:
         """tokens, positions: [rows]; returns final-norm hidden states [rows, H]."""
-        x = embedding(tokens, self.embed)
-        res = None
+        h = embedding(tokens, self.embed)
         positions = positions.to(torch.int32)
-        for layer in self.layers:
+        for i, layer in enumerate(self.layers):
             if self.activation_checkpointing and torch.is_grad_enabled():
-                x, res = checkpoint(layer, x, res, positions, self.inv_freq, attend, use_reentrant=False)
+                h = checkpointed_layer(layer, h, self.store, i, positions, self.inv_freq, attend)
             else:
-                x, res = layer(x, res, positions, self.inv_freq, attend)
-        y, _ = rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps, res)
+                h = layer(h, positions, self.inv_freq, attend)
+        y, _ = rmsnorm(h, self.final_norm, self.cfg.rms_norm_eps)
         return y
 
     def loss(self, hidden_rows: torch.Tensor, labels: torch.Tensor, weights: torch.Tensor | None,

@@ -30,7 +30,9 @@ def gemm_reference(a, b, a_mn_major=False, b_mn_major=False):
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
          out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
-         accumulate: bool = False, swiglu: bool = False, max_ctas: int = 0) -> torch.Tensor:
+         accumulate: bool = False, swiglu: bool = False, max_ctas: int = 0,
+         residual: torch.Tensor | None = None) -> torch.Tensor:
+    """`residual` (same shape and dtype as the result) is added in the epilogue: D = A·B + residual."""
     a = _as2d(a)
     b = _as2d(b)
     M, K = (a.shape[1], a.shape[0]) if a_mn_major else (a.shape[0], a.shape[1])
@@ -45,19 +47,26 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
         res = gemm_reference(a, b, a_mn_major, b_mn_major)
         if swiglu:
             res = torch.nn.functional.silu(res[:, 0::2]) * res[:, 1::2]
+        if residual is not None:
+            res = res + residual.float()
         if accumulate:
             out.add_(res.to(out.dtype))
         else:
             out.copy_(res.to(out.dtype))
         return out
+    if residual is not None:
+        if accumulate or swiglu or residual.dtype != out.dtype or residual.shape != out.shape:
+            raise ValueError("gemm: residual needs the result's shape and dtype, without accumulate/swiglu")
+        residual = _as2d(residual)
     if a.stride(-1) != 1 or b.stride(-1) != 1 or out.stride(-1) != 1:
         raise ValueError("gemm: innermost stride must be 1")
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise ValueError("gemm: destination must be bf16 or fp32")
     rc = native.lib().tdllm_gemm_bf16(
         ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
-        int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate),
-        EPI_SWIGLU if swiglu else EPI_STORE, None, None, None, None, -1, 0.0, max_ctas, stream())
+        int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32),
+        int(accumulate or residual is not None), EPI_SWIGLU if swiglu else EPI_STORE, None, None, None, None,
+        -1, 0.0, max_ctas, ptr(residual), residual.stride(0) if residual is not None else 0, stream())
     native.check(rc, "gemm_bf16")
     return out
 
@@ -93,6 +102,36 @@ class _Linear(torch.autograd.Function):
 
 def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return _Linear.apply(x, w)
+
+
+class _LinearResidual(torch.autograd.Function):
+    """h = res + x Wᵀ with the add done in the GEMM epilogue (no separate pass over the stream)."""
+
+    @staticmethod
+    def forward(ctx, x, w, res):
+        ctx.save_for_backward(x, w)
+        ctx.wref = w
+        return gemm(x, w, residual=_as2d(res)).view(res.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = _as2d(dy.contiguous())
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn_major=True).view_as(x)
+        if ctx.needs_input_grad[1]:
+            sink, acc = grad_sink(ctx.wref)
+            if sink is not None:
+                gemm(dy2, _as2d(x), a_mn_major=True, b_mn_major=True, out=sink, accumulate=acc)
+                mark_grad_written(ctx.wref)
+            else:
+                dw = gemm(dy2, _as2d(x), a_mn_major=True, b_mn_major=True, out_dtype=w.dtype)
+        return dx, dw, (dy if ctx.needs_input_grad[2] else None)
+
+
+def linear_residual(x: torch.Tensor, w: torch.Tensor, res: torch.Tensor) -> torch.Tensor:
+    return _LinearResidual.apply(x, w, res)
 
 
 class _LinearSwiGLU(torch.autograd.Function):

@@ -70,7 +70,7 @@ class _LinearCE(torch.autograd.Function):
         labels32 = labels.to(torch.int32).contiguous()
         rc = lib.tdllm_gemm_bf16(ptr(h), ptr(w), None, rows, V, H, h.stride(0), w.stride(0), 0, 0, 0, 0, 0,
                                  EPI_CE_STATS, ptr(labels32), None, None, ptr(stats), int(exclude_index),
-                                 float(softcap), 0, stream())
+                                 float(softcap), 0, None, 0, stream())
         native.check(rc, "linear_ce stats gemm")
         lse = torch.empty(rows, dtype=torch.float32, device=dev)
         per_row = torch.empty(rows, dtype=torch.float32, device=dev)
@@ -109,7 +109,7 @@ class _LinearCE(torch.autograd.Function):
             hc = h[r0:r1]
             rc = lib.tdllm_gemm_bf16(ptr(hc), ptr(w), ptr(dlog), n, V, H, h.stride(0), w.stride(0), V, 0, 0,
                                      0, 0, EPI_CE_GRAD, ptr(labels32[r0:r1]), ptr(lse[r0:r1]),
-                                     ptr(rowscale[r0:r1]), None, exclude_index, softcap, 0, stream())
+                                     ptr(rowscale[r0:r1]), None, exclude_index, softcap, 0, None, 0, stream())
             native.check(rc, "linear_ce grad gemm")
             d = dlog[:n]
             if dh is not None:

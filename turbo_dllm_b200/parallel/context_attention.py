@@ -1,0 +1,103 @@
+"""Context-sharded block parallel (CSBP) attention.
+
+A rank holds `[noisy rows of its blocks ; its clean shard]`. Queries are all of its rows; keys are
+its own noisy rows plus the clean rows of EVERY rank of its context-parallel group. Only clean
+K/V cross GPUs in the forward pass and only clean dK/dV in the backward pass:
+
+  collective transport : all-gather clean K|V  → one attention call → reduce-scatter clean dK|dV
+  streaming transport  : one attention call per owner shard, (out, lse) merged with the
+                         online-softmax merge, gradients returned to each owner
+
+The all-gather and reduce-scatter are autograd functions over torch.distributed (NCCL on GPUs,
+gloo on CPU ranks); the peer-memory pull kernels replace them on NVSwitch machines.
+
+Counterparts: `fused_block_context_attention_bshd` and `_CollectiveWithLocalKVAttentionBSHD`
+(dllm_parallel/core/attention/context_parallel_attention.py:443-490, :2315-2691), gather/scatter
+helpers (:701-817), streaming ring variant (:1434-1669).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..models.config import ModelConfig
+from ..ops.attention import attention_reference, block_attention, block_diffusion_layout, split_packed_qkv
+from .layout import PackedLayout, clean_positions_for_rank, runtime_clean_layout
+
+
+class _AllGatherRows(torch.autograd.Function):
+    """[n_local, C] → [Σ n_r, C] (ranks may hold different row counts); backward reduce-scatters."""
+
+    @staticmethod
+    def forward(ctx, x, group, counts):
+        ctx.group, ctx.counts = group, counts
+        world = len(counts)
+        rank = dist.get_rank(group)
+        nmax = max(counts)
+        pad = x if x.shape[0] == nmax else torch.cat([x, x.new_zeros(nmax - x.shape[0], x.shape[1])])
+        out = x.new_empty(world * nmax, x.shape[1])
+        dist.all_gather_into_tensor(out, pad.contiguous(), group=group)
+        ctx.rank, ctx.nmax = rank, nmax
+        if all(c == nmax for c in counts):
+            return out
+        return torch.cat([out[r * nmax: r * nmax + c] for r, c in enumerate(counts)])
+
+    @staticmethod
+    def backward(ctx, g):
+        counts, nmax, group = ctx.counts, ctx.nmax, ctx.group
+        world = len(counts)
+        if all(c == nmax for c in counts):
+            full = g.contiguous()
+        else:
+            full = g.new_zeros(world * nmax, g.shape[1])
+            off = 0
+            for r, c in enumerate(counts):
+                full[r * nmax: r * nmax + c] = g[off: off + c]
+                off += c
+        out = g.new_empty(nmax, g.shape[1])
+        if g.is_cuda:
+            dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.SUM, group=group)
+        else:  # gloo: all-reduce then slice
+            dist.all_reduce(full, op=dist.ReduceOp.SUM, group=group)
+            out = full[ctx.rank * nmax: (ctx.rank + 1) * nmax]
+        return out[: counts[ctx.rank]], None, None
+
+
+class ContextParallelAttention:
+    def __init__(self, cfg: ModelConfig, layout: PackedLayout, runtime, spec):
+        self.cfg, self.layout, self.rt = cfg, layout, runtime
+        self.group = runtime.context_group
+        cp = runtime.context_parallel_size
+        seq_len, bs = spec.model.seq_len, spec.objective.block_size
+        batch = spec.training.batch_size
+        lay = runtime_clean_layout(spec.kernel.cp_bp_clean_kv_layout, runtime.block_parallel_size)
+        dev = layout.positions.device
+        # clean key coordinates in gather order: for each CP rank, for each sequence, its positions
+        kpos, kseq, counts = [], [], []
+        for r in range(cp):
+            pos = clean_positions_for_rank(seq_len, cp, r, lay, bs, dev)
+            kpos.append(pos.repeat(batch))
+            kseq.append(torch.arange(batch, device=dev).repeat_interleave(pos.numel()))
+            counts.append(pos.numel() * batch)
+        self.counts = counts
+        self.transport = spec.kernel.cp_bp_clean_kv_transport
+        self.mask = block_diffusion_layout(layout.noisy_pos, layout.noisy_group, layout.clean_pos,
+                                           layout.block_size, noisy_seq=layout.noisy_seq,
+                                           clean_seq=layout.clean_seq, key_clean_pos=torch.cat(kpos),
+                                           key_clean_seq=torch.cat(kseq))
+
+    def __call__(self, qkv, layer_idx):
+        c = self.cfg
+        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        n_noisy = self.layout.n_noisy
+        q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
+        rows = qkv.shape[0]
+        kv_clean = qkv[n_noisy:, Hq * D:]                       # [n_clean, 2·Hkv·D], K | V
+        gathered = _AllGatherRows.apply(kv_clean.contiguous(), self.group, self.counts)
+        kv_noisy = qkv[:n_noisy, Hq * D:]
+        kv_all = torch.cat([kv_noisy, gathered], dim=0)
+        nk = kv_all.shape[0]
+        k_all = kv_all[:, : Hkv * D].view(nk, Hkv, D)
+        v_all = kv_all[:, Hkv * D:].view(nk, Hkv, D)
+        out = block_attention(q, k_all, v_all, self.mask)
+        return out.reshape(rows, Hq * D)

@@ -61,7 +61,8 @@ class TrainingSession:
         seed = spec.launch.seed
         self.model = BlockDiffusionTransformer(
             self.cfg, dtype=self.dtype, device=self.device,
-            activation_checkpointing=spec.training.activation_checkpointing, seed=seed)
+            activation_checkpointing=spec.training.activation_checkpointing,
+            activation_offload=self._want_activation_offload(), seed=seed)
         dp_rank = runtime.data_parallel_rank if runtime is not None else self.rank
         self.dp_size = runtime.data_parallel_size if runtime is not None else self.world
         self.objective = build_objective_runtime(spec, mask_token_id=self.cfg.mask_token_id,
@@ -87,6 +88,23 @@ class TrainingSession:
         self.steps_done = 0
 
     # ---------------------------------------------------------------- set-up
+    def _want_activation_offload(self) -> bool:
+        """Offload layer checkpoints to pinned host memory when keeping them in HBM would not leave
+        room for parameters, gradients, optimizer state and one layer's working set."""
+        env = os.environ.get("TDLLM_ACTIVATION_OFFLOAD")
+        if env is not None:
+            return env == "1"
+        if self.device.type != "cuda" or not self.spec.training.activation_checkpointing:
+            return False
+        cfg, s = self.cfg, self.spec
+        rows = 3 * s.model.seq_len * s.training.batch_size  # upper bound: two noisy views + clean
+        ckpt = rows * cfg.hidden_size * 2 * cfg.num_layers
+        work = rows * 2 * (6 * cfg.hidden_size + 2 * cfg.qkv_dim + 5 * max(cfg.intermediate_size, 1))
+        shard = max(self.world, 1)
+        static = cfg.num_params() * (2 + 2 + 12 / shard)
+        total = torch.cuda.get_device_properties(self.device).total_memory
+        return static + ckpt + work > 0.9 * total
+
     def _build_layout(self) -> PackedLayout:
         s, rt = self.spec, self.runtime
         owned, clean = None, None

@@ -1,0 +1,236 @@
+"""The training loop (`dllm-train`, `turbo_dllm_b200.train`).
+
+One canonical loop: initialise distributed state (NCCL with a device id, plus a gloo group for
+Python objects), build the parallel runtime and a `TrainingSession`, resume from a checkpoint
+when asked, then run optimizer steps. Rank 0 prints one JSON line per event (`run_start`, `step`,
+`checkpoint`, `summary`, `fatal_exception`), sorted keys, same field names as the reference's
+events so log tooling carries over. Step timing excludes `profiler.warmup_steps`; the summary
+reports the max over ranks of the mean timed step, tokens/s and MFU.
+
+Counterpart of `run_block_diffusion_training` (dllm_parallel/training/block_diffusion_trainer.py:501-1978;
+step loop :1265-1734, loss readback :157-233, summary :1807-1935, failure path :1938-1978).
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import time
+import traceback
+from typing import Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..config.run_spec import RunSpec, RunSpecError, build_run_spec_arg_parser, run_spec_from_args
+from ..profiling.perf import (block_diffusion_pairs, hardware_peak_tflops, model_flops_utilization_pct,
+                              transformer_step_flops)
+from . import checkpointing as ckpt_policy
+from .fault_tolerance import install_fault_handlers, write_fatal_marker
+from .session import TrainingSession
+
+
+def emit(event: dict) -> None:
+    print(json.dumps(event, sort_keys=True, default=str), flush=True)
+
+
+def init_distributed(device_type: str):
+    """Returns (rank, world, local_rank, gloo_group)."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    gloo = None
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        if device_type == "cuda":
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            gloo = dist.new_group(backend="gloo")
+        else:
+            dist.init_process_group("gloo")
+            gloo = dist.group.WORLD
+    return rank, world, local_rank, gloo
+
+
+class AsyncLossReadback:
+    """Accumulates (loss numerator, supervised rows) on the device; one small all-reduce and one
+    non-blocking copy to pinned memory per step, read when the step event is written."""
+
+    def __init__(self, device, world: int):
+        self.device, self.world = device, world
+        self.buf = torch.zeros(2, dtype=torch.float64, device=device)
+        self.host = torch.zeros(2, dtype=torch.float64, pin_memory=(device.type == "cuda"))
+        self.event = torch.cuda.Event() if device.type == "cuda" else None
+
+    def enqueue(self, loss_sum: torch.Tensor, rows: int) -> None:
+        self.buf[0] = loss_sum.double()
+        self.buf[1] = float(rows)
+        if self.world > 1:
+            dist.all_reduce(self.buf)
+        self.host.copy_(self.buf, non_blocking=True)
+        if self.event is not None:
+            self.event.record()
+
+    def resolve(self) -> tuple[float, float]:
+        if self.event is not None:
+            self.event.synchronize()
+        return float(self.host[0]), float(self.host[1])
+
+
+def run_training(spec: RunSpec) -> dict:
+    """Runs the spec to completion on this rank. Returns the summary dict (rank 0) or {}."""
+    use_cuda = torch.cuda.is_available() and spec.model.dtype != "fp32" or \
+        (torch.cuda.is_available() and os.environ.get("TDLLM_FORCE_CUDA") == "1")
+    device_type = "cuda" if use_cuda else "cpu"
+    rank, world, local_rank, gloo = init_distributed(device_type)
+    device = torch.device("cuda", local_rank) if use_cuda else torch.device("cpu")
+    install_fault_handlers()
+    spec.validate(world_size=world)
+    run_dir = os.environ.get("DLLM_RUN_DIR")
+    session = None
+    runtime = None
+    try:
+        if world > 1:
+            from ..parallel.runtime import build_parallel_runtime
+
+            runtime = build_parallel_runtime(spec, device=device, rank=rank, world_size=world)
+            runtime.warm_collectives()
+        session = TrainingSession(spec, device=device, runtime=runtime,
+                                  host_staged_data=(spec.data.input_mode == "random" and use_cuda
+                                                    and os.environ.get("TDLLM_HOST_STAGED", "0") == "1"))
+        start_step = 0
+        load_dir, tag = ckpt_policy.resolve_load_checkpoint(spec)
+        if load_dir is not None:
+            from ..checkpoint import load_training_checkpoint
+
+            meta = load_training_checkpoint(load_dir, tag, session, rank=rank, world_size=world, runtime=runtime)
+            start_step = int(meta["step"])
+        if spec.objective.skip_rng_steps:
+            session.objective.skip(spec.objective.skip_rng_steps, (spec.training.batch_size, spec.model.seq_len))
+        if rank == 0:
+            emit({"event": "run_start", "world_size": world, "device": str(device), "model_id": spec.model.id,
+                  "parameters": session.cfg.num_params(), "objective": spec.objective.name,
+                  "layout": runtime.plan.layout if runtime else "dp", "resume_step": start_step,
+                  "config": spec.to_dict()})
+        readback = AsyncLossReadback(device, world)
+        timed_ms: list[float] = []
+        t_train0 = time.monotonic()
+        dp = session.dp_size
+        tokens_per_step = spec.global_batch(dp) * spec.model.seq_len
+        total_steps = spec.training.steps
+        last_loss = float("nan")
+        for step in range(start_step + 1, total_steps + 1):
+            if use_cuda:
+                torch.cuda.reset_peak_memory_stats(device)
+            t0 = time.perf_counter()
+            res = session.step()
+            readback.enqueue(res.loss_sum, int(res.supervised_rows))
+            if use_cuda:
+                torch.cuda.synchronize(device)
+            ms = (time.perf_counter() - t0) * 1e3
+            loss_sum, rows = readback.resolve()
+            last_loss = loss_sum / res.denominator
+            if last_loss != last_loss or abs(last_loss) == float("inf"):
+                raise FloatingPointError(f"non-finite loss at step {step}: {last_loss}")
+            timed = step - start_step > spec.profiler.warmup_steps
+            if timed:
+                timed_ms.append(ms)
+            if rank == 0:
+                emit({"event": "step", "step": step, "completed_steps": step, "target_total_steps": total_steps,
+                      "timed": timed, "loss": last_loss, "lr": session.scheduler.lr_at(session.scheduler.step_count),
+                      "grad_norm": session.optimizer.grad_norm(), "gradient_clip_norm": spec.optimizer.gradient_clip_norm,
+                      "ms": ms, "active_tokens": rows, "valid_tokens": res.denominator, "input_tokens": tokens_per_step,
+                      "perf": {"input_tokens_per_second": tokens_per_step / (ms / 1e3),
+                               "input_tokens_per_second_per_gpu": tokens_per_step / (ms / 1e3) / world},
+                      "optimizer_step": not spec.training.skip_optimizer_step,
+                      "gradient_accumulation_steps": spec.training.gradient_accumulation_steps,
+                      "optimizer_backend": "zero_fused" if session.optimizer.fused_sync else "flat_adamw",
+                      "peak_mib": (torch.cuda.max_memory_allocated(device) / 2 ** 20) if use_cuda else None})
+            elapsed = time.monotonic() - t_train0
+            if ckpt_policy.should_save(spec, step, total_steps, elapsed):
+                from ..checkpoint import save_training_checkpoint
+
+                tagname = save_training_checkpoint(spec.checkpointing.save_checkpoint_dir, session, step=step,
+                                                   rank=rank, world_size=world, runtime=runtime, spec=spec,
+                                                   control_group=gloo)
+                if rank == 0:
+                    emit({"event": "checkpoint", "step": step, "tag": tagname,
+                          "dir": spec.checkpointing.save_checkpoint_dir})
+            if spec.training.max_duration_seconds and elapsed >= spec.training.max_duration_seconds:
+                break
+        mean_ms = sum(timed_ms) / len(timed_ms) if timed_ms else float("nan")
+        if world > 1:
+            t = torch.tensor([mean_ms], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            mean_ms = float(t)
+        summary = {}
+        if rank == 0:
+            views = session.objective.views
+            gb = spec.global_batch(dp)
+            fl = transformer_step_flops(
+                session.cfg, rows=(views + 1) * spec.model.seq_len * gb,
+                pairs=block_diffusion_pairs(spec.model.seq_len, spec.objective.block_size, views) * gb,
+                vocab_rows=gb * spec.model.seq_len)
+            mfu = None
+            if use_cuda and mean_ms == mean_ms:
+                try:
+                    peak = hardware_peak_tflops(torch.cuda.get_device_name(device))
+                    mfu = model_flops_utilization_pct(fl.total, mean_ms / 1e3, world, peak)
+                except ValueError:
+                    mfu = None
+            summary = {"event": "summary", "model_id": spec.model.id, "seq_len": spec.model.seq_len,
+                       "batch_size": spec.training.batch_size, "steps": total_steps, "final_loss": last_loss,
+                       "step_time_ms": mean_ms, "measured_steps": len(timed_ms),
+                       "input_tokens_per_second": tokens_per_step / (mean_ms / 1e3) if mean_ms == mean_ms else None,
+                       "model_tflop_per_step": fl.total / 1e12, "mfu_pct": mfu, "world_size": world,
+                       "parallel_layout": runtime.plan.layout if runtime else "dp",
+                       "training_elapsed_seconds": time.monotonic() - t_train0}
+            emit(summary)
+        return summary
+    except Exception as e:
+        info = {"event": "fatal_exception", "rank": rank, "error": f"{type(e).__name__}: {e}",
+                "traceback": traceback.format_exc()[-4000:]}
+        emit(info)
+        if run_dir:
+            write_fatal_marker(run_dir, rank, info)
+        raise
+    finally:
+        if runtime is not None:
+            runtime.destroy()
+        if dist.is_initialized() and world > 1:
+            dist.destroy_process_group()
+
+
+def train(argv_or_spec: Sequence[str] | RunSpec | None = None) -> dict:
+    """Public entry: a RunSpec, or dllm-train style arguments (`--config train.yaml --flag value`)."""
+    if isinstance(argv_or_spec, RunSpec):
+        return run_training(argv_or_spec)
+    return main(argv_or_spec)
+
+
+def main(argv: Sequence[str] | None = None):
+    ap = build_run_spec_arg_parser("dllm-train")
+    args = ap.parse_args(list(sys.argv[1:] if argv is None else argv))
+    if args.print_supported_configs:
+        from ..models.registry import describe_supported_configs
+
+        print(json.dumps(describe_supported_configs(), indent=1))
+        return {}
+    try:
+        spec = run_spec_from_args(args)
+        spec.validate()
+    except RunSpecError as e:
+        print(f"error: {e}", file=sys.stderr)
+        raise SystemExit(2)
+    if args.print_config:
+        print(spec.to_yaml())
+        return {}
+    if args.validate_only:
+        print(json.dumps({"valid": True, "model_id": spec.model.id, "objective": spec.objective.name}))
+        return {}
+    return run_training(spec)
+
+
+if __name__ == "__main__":
+    main()
