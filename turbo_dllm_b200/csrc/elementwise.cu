@@ -545,3 +545,65 @@ extern "C" int tdllm_swiglu_bwd(const void* dy, const void* gu, void* dgu, long 
   TD_CHECK_LAUNCH("swiglu_bwd");
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (declared and documented in noalloc.h).
+// ---------------------------------------------------------------------------
+#include "noalloc.h"
+
+// Partial weight-gradient sums of the allocation-free entry point: one row of H floats per
+// thread block. File scope, so the memory belongs to the library image on every device.
+static __device__ __align__(256) float g_noalloc_scratch[TDLLM_NOALLOC_PARTS * TDLLM_NOALLOC_MAX_HIDDEN];
+
+// In host code `g_noalloc_scratch` is only a stand-in for the symbol, not a device address,
+// so the address is queried once per device and cached here.
+static float* noalloc_scratch_for_current_device() {
+  static float* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    tdllm_host::set_last_error("rmsnorm_bwd_noalloc: cannot identify the current device");
+    return nullptr;
+  }
+  if (!cached[dev]) {
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      tdllm_host::set_last_error("rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s",
+                                 cudaGetErrorString(e));
+      return nullptr;
+    }
+    cached[dev] = p;
+  }
+  return cached[dev];
+}
+
+extern "C" int tdllm_rmsnorm_bwd_noalloc(const void* dy, const void* h, const void* w,
+                                         const float* rstd, const void* dres_in, void* dx,
+                                         void* dw, int dw_fp32, int dw_accumulate, int rows, int H,
+                                         void* stream) {
+  if (rows <= 0) return 0;
+  if (H % 8 || H <= 0 || H > TDLLM_NOALLOC_MAX_HIDDEN) {
+    tdllm_host::set_last_error(
+        "rmsnorm_bwd_noalloc: hidden size %d is outside the built-in scratch area (multiple of 8, at most %d)",
+        H, TDLLM_NOALLOC_MAX_HIDDEN);
+    return 1;
+  }
+  float* scratch = noalloc_scratch_for_current_device();
+  if (!scratch) return 2;
+  int vpt;
+  const int threads = norm_threads(H, vpt);
+  int parts = TDLLM_NOALLOC_PARTS;
+  if (parts > rows) parts = rows;
+  cudaStream_t s = (cudaStream_t)stream;
+  auto a = (const __nv_bfloat16*)dy; auto b = (const __nv_bfloat16*)h;
+  auto c = (const __nv_bfloat16*)w; auto d = (const __nv_bfloat16*)dres_in;
+  auto o = (__nv_bfloat16*)dx;
+  // every block writes its full row of partial sums, so the array needs no clearing
+  if (vpt == 1) ew::rmsnorm_bwd_kernel<1><<<parts, threads, 0, s>>>(a, b, c, rstd, d, o, scratch, rows, H);
+  else if (vpt == 2) ew::rmsnorm_bwd_kernel<2><<<parts, threads, 0, s>>>(a, b, c, rstd, d, o, scratch, rows, H);
+  else ew::rmsnorm_bwd_kernel<4><<<parts, threads, 0, s>>>(a, b, c, rstd, d, o, scratch, rows, H);
+  TD_CHECK_LAUNCH("rmsnorm_bwd_noalloc");
+  ew::colsum_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, parts, H, dw, dw_fp32, dw_accumulate);
+  TD_CHECK_LAUNCH("rmsnorm_bwd_noalloc colsum");
+  return 0;
+}
