@@ -81,6 +81,19 @@ int tdllm_attn_bwd(const void* q, const void* k, const void* v, const void* o, c
                    const int* b_idx, const int* b_order, int n_qtiles, int n_ktiles, float scale,
                    void* stream);
 
+// ---- peer memory and the fused ZeRO step -----------------------------------
+int tdllm_symm_alloc(long long bytes, void** out);
+int tdllm_symm_free(void* p);
+int tdllm_ipc_get_handle(void* p, void* handle_out64);
+int tdllm_ipc_open(const void* handle64, void** out);
+int tdllm_ipc_close(void* p);
+int tdllm_symm_barrier(void* const* flag_ptrs, int rank, int world, int epoch, void* stream);
+int tdllm_zero_fused_step(void* const* grad_ptrs, void* const* param_ptrs, void* const* sumsq_ptrs,
+                          void* const* flag_ptrs, float* master, float* m, float* v, int rank,
+                          int world, long long start, long long n, long long decay_end, float lr,
+                          float beta1, float beta2, float eps, float wd, int step, float grad_scale,
+                          float max_norm, float* norm_out, int epoch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

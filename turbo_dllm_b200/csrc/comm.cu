@@ -1,0 +1,253 @@
+// Peer-memory substrate and the fused ZeRO step over NVLink / NVSwitch.
+//
+// Symmetric buffers: every rank cudaMalloc's the same sizes, exports IPC handles, and maps every
+// peer's buffers, so kernels address peers with plain loads and stores (never TMA, never a
+// library kernel given a peer pointer).
+//
+// Cross-rank ordering uses an epoch barrier in symmetric memory: rank r writes the epoch into
+// slot r of every peer's flag array (release, system scope) and waits until all slots of its own
+// array reached the epoch (acquire, bounded by the library's wait budget; on expiry the error
+// record is set and the kernel returns, so a missing peer gives an exception, not a hang).
+//
+// Fused optimizer step (one process per GPU, each rank owns one contiguous shard of the flat
+// parameter / gradient buffers):
+//   zero_reduce_kernel : reduce-scatter by pulling — sums the shard's gradient slice from every
+//                        peer (bf16 -> fp32), stores the sum to the local gradient buffer and
+//                        accumulates Σ g² for the global norm
+//   zero_update_kernel : reads every rank's Σ g², clips, applies AdamW to the fp32 master shard
+//                        and all-gathers by pushing — writes the new bf16 parameters into every
+//                        peer's parameter buffer
+// This replaces reduce-scatter + FusedAdam + all-gather of DeepSpeed ZeRO-2 / FSDP in the
+// reference (dllm_parallel/core/optim/zero.py:93-211, :402-462; dllm_parallel/core/optim/fsdp.py:56-114).
+#include <cstring>
+#include "common.cuh"
+#include "api.h"
+
+namespace tdllm {
+namespace comm {
+
+constexpr int KID_BARRIER = 10;
+constexpr int MAX_RANKS = 16;
+
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+// One block, one thread per rank.
+__global__ void barrier_kernel(PeerPtrs flags, int rank, int world, int epoch) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  flag_store_release((int*)flags.p[r] + rank, epoch);       // tell peer r that we arrived
+  flag_wait_geq((const int*)flags.p[rank] + r, epoch, KID_BARRIER, r);  // wait for peer r
+}
+
+__device__ __forceinline__ void acc8(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] += t.x;
+    f[2 * i + 1] += t.y;
+  }
+}
+
+// grads.p[r] = base of rank r's flat gradient buffer. Elements [start, start+n) are this rank's shard.
+__global__ void zero_reduce_kernel(PeerPtrs grads, int rank, int world, long long start, long long n,
+                                   float* sumsq_out) {
+  float ss = 0.f;
+  const long long n8 = n / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * blockDim.x) {
+    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+    for (int k = 0; k < world; ++k) {
+      const int r = (rank + 1 + k) % world;  // stagger peers so links are used evenly
+      const uint4 v = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)grads.p[r] + start + i * 8);
+      acc8(v, f);
+    }
+    uint4 o;
+    o.x = pack_bf16x2(f[0], f[1]);
+    o.y = pack_bf16x2(f[2], f[3]);
+    o.z = pack_bf16x2(f[4], f[5]);
+    o.w = pack_bf16x2(f[6], f[7]);
+    *reinterpret_cast<uint4*>((__nv_bfloat16*)grads.p[rank] + start + i * 8) = o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+  ss = warp_sum(ss);
+  __shared__ float red[32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  if (warp == 0) {
+    ss = (lane < (blockDim.x >> 5)) ? red[lane] : 0.f;
+    ss = warp_sum(ss);
+    if (lane == 0) atomicAdd(sumsq_out, ss);
+  }
+}
+
+// sumsq.p[r] = address of rank r's Σ g² scalar (symmetric memory). params.p[r] = rank r's flat
+// parameter buffer. [start, start+n) is this rank's shard; decay applies to global element
+// indices below decay_end.
+__global__ void zero_update_kernel(PeerPtrs params, PeerPtrs sumsq, const __nv_bfloat16* grad_local,
+                                   float* master, float* m, float* v, int rank, int world,
+                                   long long start, long long n, long long decay_end, float lr,
+                                   float beta1, float beta2, float eps, float wd, float bias1,
+                                   float bias2, float grad_scale, float max_norm,
+                                   float* norm_out) {
+  float total = 0.f;
+  for (int r = 0; r < world; ++r) total += *(const volatile float*)sumsq.p[r];
+  const float norm = sqrtf(total) * grad_scale;
+  if (norm_out && blockIdx.x == 0 && threadIdx.x == 0) *norm_out = norm;
+  float gs = grad_scale;
+  if (max_norm > 0.f && norm > max_norm) gs *= max_norm / (norm + 1e-6f);
+  const float inv_b1 = 1.f / bias1;
+  const float inv_sqrt_b2 = rsqrtf(bias2);
+  const long long n8 = n / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long e0 = i * 8;
+    const uint4 gv = *reinterpret_cast<const uint4*>(grad_local + start + e0);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    float g[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 t = __bfloat1622float2(gh[j]);
+      g[2 * j] = t.x * gs;
+      g[2 * j + 1] = t.y * gs;
+    }
+    float p[8], mm[8], vv[8];
+    *reinterpret_cast<float4*>(p) = *reinterpret_cast<const float4*>(master + e0);
+    *reinterpret_cast<float4*>(p + 4) = *reinterpret_cast<const float4*>(master + e0 + 4);
+    *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(m + e0);
+    *reinterpret_cast<float4*>(mm + 4) = *reinterpret_cast<const float4*>(m + e0 + 4);
+    *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(v + e0);
+    *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(v + e0 + 4);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float w = (start + e0 + j < decay_end) ? wd : 0.f;
+      mm[j] = beta1 * mm[j] + (1.f - beta1) * g[j];
+      vv[j] = beta2 * vv[j] + (1.f - beta2) * g[j] * g[j];
+      p[j] = p[j] * (1.f - lr * w) - lr * (mm[j] * inv_b1) / (sqrtf(vv[j]) * inv_sqrt_b2 + eps);
+    }
+    *reinterpret_cast<float4*>(master + e0) = *reinterpret_cast<float4*>(p);
+    *reinterpret_cast<float4*>(master + e0 + 4) = *reinterpret_cast<float4*>(p + 4);
+    *reinterpret_cast<float4*>(m + e0) = *reinterpret_cast<float4*>(mm);
+    *reinterpret_cast<float4*>(m + e0 + 4) = *reinterpret_cast<float4*>(mm + 4);
+    *reinterpret_cast<float4*>(v + e0) = *reinterpret_cast<float4*>(vv);
+    *reinterpret_cast<float4*>(v + e0 + 4) = *reinterpret_cast<float4*>(vv + 4);
+    uint4 o;
+    o.x = pack_bf16x2(p[0], p[1]);
+    o.y = pack_bf16x2(p[2], p[3]);
+    o.z = pack_bf16x2(p[4], p[5]);
+    o.w = pack_bf16x2(p[6], p[7]);
+#pragma unroll 1
+    for (int k = 0; k < world; ++k) {
+      const int r = (rank + k) % world;
+      *reinterpret_cast<uint4*>((__nv_bfloat16*)params.p[r] + start + e0) = o;
+    }
+  }
+}
+
+}  // namespace comm
+}  // namespace tdllm
+
+using namespace tdllm;
+
+#define TD_CUDA(call, what)                                                     \
+  do {                                                                          \
+    cudaError_t e_ = (call);                                                    \
+    if (e_ != cudaSuccess) {                                                    \
+      tdllm_host::set_last_error(what ": %s", cudaGetErrorString(e_));          \
+      return 5;                                                                 \
+    }                                                                           \
+  } while (0)
+
+extern "C" int tdllm_symm_alloc(long long bytes, void** out) {
+  TD_CUDA(cudaMalloc(out, (size_t)bytes), "symm_alloc");
+  TD_CUDA(cudaMemset(*out, 0, (size_t)bytes), "symm_alloc memset");
+  return 0;
+}
+extern "C" int tdllm_symm_free(void* p) {
+  TD_CUDA(cudaFree(p), "symm_free");
+  return 0;
+}
+// handle_out: 64 bytes
+extern "C" int tdllm_ipc_get_handle(void* p, void* handle_out) {
+  cudaIpcMemHandle_t h;
+  TD_CUDA(cudaIpcGetMemHandle(&h, p), "ipc_get_handle");
+  memcpy(handle_out, &h, sizeof(h));
+  return 0;
+}
+extern "C" int tdllm_ipc_open(const void* handle, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  TD_CUDA(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess), "ipc_open");
+  return 0;
+}
+extern "C" int tdllm_ipc_close(void* p) {
+  TD_CUDA(cudaIpcCloseMemHandle(p), "ipc_close");
+  return 0;
+}
+
+static int fill_peers(comm::PeerPtrs& pp, void* const* ptrs, int world) {
+  if (world < 1 || world > comm::MAX_RANKS) {
+    tdllm_host::set_last_error("comm: world size %d outside [1, %d]", world, comm::MAX_RANKS);
+    return 1;
+  }
+  for (int i = 0; i < comm::MAX_RANKS; ++i) pp.p[i] = i < world ? ptrs[i] : nullptr;
+  return 0;
+}
+
+extern "C" int tdllm_symm_barrier(void* const* flag_ptrs, int rank, int world, int epoch, void* stream) {
+  comm::PeerPtrs f;
+  if (fill_peers(f, flag_ptrs, world)) return 1;
+  comm::barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, rank, world, epoch);
+  TD_CUDA(cudaGetLastError(), "symm_barrier launch");
+  return 0;
+}
+
+// Whole fused step: barrier, pull-reduce, barrier, clip + AdamW + push, barrier.
+// epoch is the first of three consecutive barrier epochs used by this call.
+extern "C" int tdllm_zero_fused_step(void* const* grad_ptrs, void* const* param_ptrs,
+                                     void* const* sumsq_ptrs, void* const* flag_ptrs, float* master,
+                                     float* m, float* v, int rank, int world, long long start,
+                                     long long n, long long decay_end, float lr, float beta1,
+                                     float beta2, float eps, float wd, int step, float grad_scale,
+                                     float max_norm, float* norm_out, int epoch, void* stream) {
+  comm::PeerPtrs g, p, s, f;
+  if (fill_peers(g, grad_ptrs, world) || fill_peers(p, param_ptrs, world) ||
+      fill_peers(s, sumsq_ptrs, world) || fill_peers(f, flag_ptrs, world))
+    return 1;
+  if (n % 8 || start % 8) {
+    tdllm_host::set_last_error("zero_fused_step: shard bounds must be multiples of 8 elements");
+    return 1;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  TD_CUDA(cudaMemsetAsync(sumsq_ptrs[rank], 0, sizeof(float), st), "zero sumsq");
+  comm::barrier_kernel<<<1, 32, 0, st>>>(f, rank, world, epoch);
+  if (n > 0) {
+    const int threads = 256;
+    long long blocks = (n / 8 + threads - 1) / threads;
+    const long long cap = (long long)tdllm_num_sms() * 8;
+    if (blocks > cap) blocks = cap;
+    comm::zero_reduce_kernel<<<(unsigned)blocks, threads, 0, st>>>(g, rank, world, start, n,
+                                                                  (float*)sumsq_ptrs[rank]);
+  }
+  comm::barrier_kernel<<<1, 32, 0, st>>>(f, rank, world, epoch + 1);
+  if (n > 0) {
+    const int threads = 256;
+    long long blocks = (n / 8 + threads - 1) / threads;
+    const long long cap = (long long)tdllm_num_sms() * 8;
+    if (blocks > cap) blocks = cap;
+    const float bias1 = 1.f - powf(beta1, (float)step);
+    const float bias2 = 1.f - powf(beta2, (float)step);
+    comm::zero_update_kernel<<<(unsigned)blocks, threads, 0, st>>>(
+        p, s, (const __nv_bfloat16*)grad_ptrs[rank], master, m, v, rank, world, start, n, decay_end,
+        lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale, max_norm, norm_out);
+  }
+  comm::barrier_kernel<<<1, 32, 0, st>>>(f, rank, world, epoch + 2);
+  TD_CUDA(cudaGetLastError(), "zero_fused_step launch");
+  return 0;
+}
