@@ -71,7 +71,7 @@ int tdllm_attn_fwd(const void* q, const void* k, const void* v, void* o, float* 
                    int n_qtiles, float scale, void* stream);
 
 // dq/dk/dv may point into one packed [rows, (Hq+2Hkv)*128] buffer; delta is fp32 scratch
-// [Hq, n_qtiles*128]; f_* lists are per query tile, b_* lists per key tile.
+// [2, Hq, n_qtiles*128]; f_* lists are per query tile, b_* lists per key tile.
 int tdllm_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
                    void* dq, void* dk, void* dv, const float* lse, float* delta, int nq, int nk,
                    int Hq, int Hkv, long long ldq, long long ldk, long long ldv, long long ldo,

@@ -28,7 +28,8 @@ constexpr int HD = 128;
 constexpr int TILE_BYTES = 128 * HD * 2;  // 32 KiB
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int THREADS = 320;
-constexpr int SMEM_BYTES = 6 * TILE_BYTES + 512 + 1024;
+constexpr int ROWSTAT_BYTES = 2 * 2 * 128 * 4;  // 2 stages x (lse2[128], delta_s[128])
+constexpr int SMEM_BYTES = 6 * TILE_BYTES + 512 + ROWSTAT_BYTES + 1024;
 
 struct Params {
   int nq_pad, Hq, Hkv;
@@ -39,8 +40,8 @@ struct Params {
   const int* tile_ptr;  // per key tile: query tiles that see it
   const int* tile_idx;  // q_tile * 2 + needs_mask
   const int* order;     // key tiles, heaviest first
-  const float* lse;
-  const float* delta;
+  const float* lse2;   // [Hq, nq_pad] lse·log2e (+inf = row without keys)
+  const float* delta;  // [Hq, nq_pad] scale · rowsum(dO∘O)
   float scale_log2, scale;
 };
 
@@ -81,6 +82,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const uint32_t bar_done = b0 + 72;
   const uint32_t bar_epi = b0 + 80;  // [2]
   uint32_t* tmem_slot = (uint32_t*)(bars + 13);
+  float* sStat = (float*)((uint8_t*)bars + 512);  // [stage][lse2 128 | delta_s 128]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -130,7 +132,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const int h = kvh * G + it / n;
         const int qt = list[it % n] >> 1;
         if (!mbar_wait(bar_qempty + 8 * s, ((it >> 1) & 1) ^ 1, KID, 10)) break;
-        mbar_expect_tx(bar_qfull + 8 * s, 2 * TILE_BYTES);
+        mbar_expect_tx(bar_qfull + 8 * s, 2 * TILE_BYTES + 1024);
+        bulk_load_1d(smem_u32(sStat + s * 256), p.lse2 + (size_t)h * p.nq_pad + qt * 128, 512,
+                     bar_qfull + 8 * s);
+        bulk_load_1d(smem_u32(sStat + s * 256 + 128), p.delta + (size_t)h * p.nq_pad + qt * 128, 512,
+                     bar_qfull + 8 * s);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           tma_load_2d(smem_u32(sQ + s * TILE_BYTES + c * HALF_BYTES), &tm_q, bar_qfull + 8 * s,
@@ -204,46 +210,63 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int row = qd * 32 + lane;   // key row inside the tile
     const int kcode = p.k_code[kt * 128 + row];
     const uint32_t t_s = tmem_base + ((uint32_t)(qd * 32) << 16) + b * 128;
-    uint32_t rs[32], rp[32];
+    uint32_t rs[64], rp[64];
     bool ok = true;
     for (int it = 0; it < items; ++it) {
-      const int h = kvh * G + it / n;
       const int ent = list[it % n];
       const int qrow0 = (ent >> 1) * 128 + b * 64;
-      const bool masked = ent & 1;
-      const float* lse = p.lse + (size_t)h * p.nq_pad + qrow0;
-      const float* dl = p.delta + (size_t)h * p.nq_pad + qrow0;
+      const float* sl = sStat + (it & 1) * 256 + b * 64;   // lse2 of this half's 64 queries
+      const float* sd = sl + 128;                          // delta_s
       if (!mbar_wait(bar_sfull + 8 * b, it & 1, KID, 30)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld32(t_s + c * 32, rs);
-        tmem_ld32(t_s + 64 + c * 32, rp);
-        tmem_ld_wait();
-        uint32_t pk[16], dk[16];
+      tmem_ld32(t_s, rs);
+      tmem_ld32(t_s + 32, rs + 32);
+      tmem_ld32(t_s + 64, rp);
+      tmem_ld32(t_s + 96, rp + 32);
+      tmem_ld_wait();
+      uint32_t pk[32], dk[32];
+      if (ent & 1) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2], dv[2];
+        for (int e = 0; e < 64; e += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(sl + e);
+          const float4 d4 = *reinterpret_cast<const float4*>(sd + e);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], ds[4];
 #pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            const int qi = c * 32 + e + t;
-            const float l = __ldg(lse + qi);
-            float pr = (l > -INFINITY)
-                           ? fast_exp2(__uint_as_float(rs[e + t]) * p.scale_log2 - l * 1.4426950408889634f)
-                           : 0.f;
-            if (masked) {
-              const int g = qrow0 + qi;
-              if (!key_visible(kcode, __ldg(p.q_lo + g), __ldg(p.q_hi + g), __ldg(p.q_grp + g))) pr = 0.f;
-            }
+          for (int t = 0; t < 4; ++t) {
+            const int g = qrow0 + e + t;
+            float pr = fast_exp2(fmaf(__uint_as_float(rs[e + t]), p.scale_log2, -lv[t]));
+            if (!key_visible(kcode, __ldg(p.q_lo + g), __ldg(p.q_hi + g), __ldg(p.q_grp + g))) pr = 0.f;
             pv[t] = pr;
-            dv[t] = pr * (__uint_as_float(rp[e + t]) - __ldg(dl + qi)) * p.scale;
+            ds[t] = pr * fmaf(__uint_as_float(rp[e + t]), p.scale, -dv[t]);
           }
           pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
-          dk[e >> 1] = pack_bf16x2(dv[0], dv[1]);
+          pk[(e >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
+          dk[e >> 1] = pack_bf16x2(ds[0], ds[1]);
+          dk[(e >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
         }
-        tmem_st16(t_s + c * 16, pk);
-        tmem_st16(t_s + 64 + c * 16, dk);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 64; e += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(sl + e);
+          const float4 d4 = *reinterpret_cast<const float4*>(sd + e);
+          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -l4.x));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, -l4.y));
+          const float p2 = fast_exp2(fmaf(__uint_as_float(rs[e + 2]), p.scale_log2, -l4.z));
+          const float p3 = fast_exp2(fmaf(__uint_as_float(rs[e + 3]), p.scale_log2, -l4.w));
+          pk[e >> 1] = pack_bf16x2(p0, p1);
+          pk[(e >> 1) + 1] = pack_bf16x2(p2, p3);
+          dk[e >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[e]), p.scale, -d4.x),
+                                   p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, -d4.y));
+          dk[(e >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(rp[e + 2]), p.scale, -d4.z),
+                                         p3 * fmaf(__uint_as_float(rp[e + 3]), p.scale, -d4.w));
+        }
       }
+      tmem_st16(t_s, pk);
+      tmem_st16(t_s + 16, pk + 16);
+      tmem_st16(t_s + 64, dk);
+      tmem_st16(t_s + 80, dk + 16);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar_pfull + 8 * b);

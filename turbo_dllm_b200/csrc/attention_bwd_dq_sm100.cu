@@ -39,8 +39,8 @@ struct Params {
   const int* tile_ptr;
   const int* tile_idx;
   const int* order;
-  const float* lse;    // [Hq, nq_pad]
-  const float* delta;  // [Hq, nq_pad]
+  const float* lse2;   // [Hq, nq_pad] lse·log2e (+inf = row without keys)
+  const float* delta;  // [Hq, nq_pad] scale · rowsum(dO∘O)
   float scale_log2, scale;
 };
 
@@ -218,41 +218,44 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int row = qd * 32 + lane;
     const int grow = qt * BQ + row;
     const int lo = p.q_lo[grow], hi = p.q_hi[grow], grp = p.q_grp[grow];
-    const float lse = p.lse[(size_t)(h0 + i) * p.nq_pad + grow];
+    const float lse2 = p.lse2[(size_t)(h0 + i) * p.nq_pad + grow];
     const float delta = p.delta[(size_t)(h0 + i) * p.nq_pad + grow];
-    const bool dead = !(lse > -INFINITY);
-    const float lse2 = dead ? 0.f : lse * 1.4426950408889634f;
     const uint32_t t_s = tmem_base + ((uint32_t)(qd * 32) << 16) + i * 128;
     const uint32_t t_dq = tmem_base + ((uint32_t)(qd * 32) << 16) + 256 + i * 128;
-    uint32_t rs[32], rp[32];
+    uint32_t rs[64], rp[64];
     bool ok = true;
     for (int u = 0; u < U; ++u) {
       const int ent = list[u >> 1];
       const int* kc = p.k_code + (ent >> 1) * 128 + (u & 1) * SUB;
-      const bool masked = ent & 1;
       if (!mbar_wait(bar_sfull + 8 * i, u & 1, KID, 30)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld32(t_s + c * 32, rs);
-        tmem_ld32(t_s + 64 + c * 32, rp);
-        tmem_ld_wait();
-        uint32_t pk[16];
+      tmem_ld32(t_s, rs);
+      tmem_ld32(t_s + 32, rs + 32);
+      tmem_ld32(t_s + 64, rp);
+      tmem_ld32(t_s + 96, rp + 32);
+      tmem_ld_wait();
+      uint32_t pk[32];
+      if (ent & 1) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0 = fast_exp2(__uint_as_float(rs[e]) * p.scale_log2 - lse2);
-          float p1 = fast_exp2(__uint_as_float(rs[e + 1]) * p.scale_log2 - lse2);
-          if (masked) {
-            if (!key_visible(__ldg(kc + c * 32 + e), lo, hi, grp)) p0 = 0.f;
-            if (!key_visible(__ldg(kc + c * 32 + e + 1), lo, hi, grp)) p1 = 0.f;
-          }
-          if (dead) p0 = p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(rp[e]) - delta) * p.scale;
-          const float d1 = p1 * (__uint_as_float(rp[e + 1]) - delta) * p.scale;
-          pk[e >> 1] = pack_bf16x2(d0, d1);
+        for (int e = 0; e < 64; e += 2) {
+          float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -lse2));
+          float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, -lse2));
+          if (!key_visible(__ldg(kc + e), lo, hi, grp)) p0 = 0.f;
+          if (!key_visible(__ldg(kc + e + 1), lo, hi, grp)) p1 = 0.f;
+          pk[e >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[e]), p.scale, -delta),
+                                   p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, -delta));
         }
-        tmem_st16(t_s + c * 16, pk);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 64; e += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -lse2));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, -lse2));
+          pk[e >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[e]), p.scale, -delta),
+                                   p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, -delta));
+        }
       }
+      tmem_st16(t_s, pk);
+      tmem_st16(t_s + 16, pk + 16);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar_pfull + 8 * i);
@@ -309,9 +312,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   }
 }
 
-// delta[h, row] = sum_d dO[row, h, d] * O[row, h, d]; one warp per (row, head); pad rows get 0
+// Per (row, head): delta_s = scale * sum_d dO·O and lse2 = lse·log2(e), with lse2 = +inf for rows
+// that saw no key (and for padding rows) so that exp2(x − lse2) is exactly 0 there.
+// One warp per (row, head). Output layout: delta_s [Hq, nq_pad], lse2 [Hq, nq_pad].
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
-                                  const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
+                                  const __nv_bfloat16* __restrict__ dout,
+                                  const float* __restrict__ lse, float* __restrict__ delta,
+                                  float* __restrict__ lse2, float scale,
                                   int nq, int nq_pad, int Hq, long long ldo, long long lddo) {
   const int lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -330,7 +337,12 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
     }
   }
   s = warp_sum(s);
-  if (lane == 0) delta[(size_t)h * nq_pad + row] = s;
+  if (lane == 0) {
+    const size_t at = (size_t)h * nq_pad + row;
+    const float l = lse[at];
+    delta[at] = s * scale;
+    lse2[at] = (row < nq && l > -INFINITY) ? l * 1.4426950408889634f : INFINITY;
+  }
 }
 
 }  // namespace attn_dq

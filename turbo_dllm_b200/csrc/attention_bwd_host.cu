@@ -1,4 +1,5 @@
-// Host entry point of the attention backward: delta = rowsum(dO∘O), then the dQ kernel
+// Host entry point of the attention backward: row statistics (delta·scale, lse·log2e) into the
+// caller's scratch [2, Hq, n_qtiles*128], then the dQ kernel
 // (per query tile) and the dK/dV kernel (per key tile).
 #include "attention_bwd_dq_sm100.cu"
 #include "attention_bwd_dkv_sm100.cu"
@@ -45,7 +46,8 @@ extern "C" int tdllm_attn_bwd(const void* q, const void* k, const void* v, const
   {
     const long long items = (long long)nq_pad * Hq;
     attn_dq::attn_delta_kernel<<<(unsigned)((items + 7) / 8), 256, 0, s>>>(
-        (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, nq, nq_pad, Hq, ldo, lddo);
+        (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, lse, delta, delta + (size_t)Hq * nq_pad, scale,
+        nq, nq_pad, Hq, ldo, lddo);
   }
   CUtensorMap tq, tdo, tk, tv, tk64, tv64, tdq, tdk, tdv;
   const long long qc = (long long)Hq * 128, kc = (long long)Hkv * 128;
@@ -64,7 +66,7 @@ extern "C" int tdllm_attn_bwd(const void* q, const void* k, const void* v, const
     p.nq_pad = nq_pad; p.Hq = Hq; p.Hkv = Hkv;
     p.q_lo = q_lo; p.q_hi = q_hi; p.q_grp = q_grp; p.k_code = k_code;
     p.tile_ptr = f_ptr; p.tile_idx = f_idx; p.order = f_order;
-    p.lse = lse; p.delta = delta;
+    p.lse2 = delta + (size_t)Hq * nq_pad; p.delta = delta;
     p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
     const int grid = n_qtiles * Hkv * (Hq / Hkv / 2);
     attn_dq::attn_bwd_dq_kernel<<<grid, attn_dq::THREADS, attn_dq::SMEM_BYTES, s>>>(
@@ -75,7 +77,7 @@ extern "C" int tdllm_attn_bwd(const void* q, const void* k, const void* v, const
     p.nq_pad = nq_pad; p.Hq = Hq; p.Hkv = Hkv;
     p.q_lo = q_lo; p.q_hi = q_hi; p.q_grp = q_grp; p.k_code = k_code;
     p.tile_ptr = b_ptr; p.tile_idx = b_idx; p.order = b_order;
-    p.lse = lse; p.delta = delta;
+    p.lse2 = delta + (size_t)Hq * nq_pad; p.delta = delta;
     p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
     const int grid = n_ktiles * Hkv;
     attn_dkv::attn_bwd_dkv_kernel<<<grid, attn_dkv::THREADS, attn_dkv::SMEM_BYTES, s>>>(

@@ -1,7 +1,8 @@
 """Per-layer activation checkpointing with optional host offload.
 
-Only the residual stream entering each layer is kept for the backward pass; everything inside a
-layer is recomputed. With `offload=True` that tensor is copied to pinned host memory on a side
+Only the residual stream entering each layer is kept for the backward pass, plus (optionally) the
+attention output and log-sum-exp of the layer so that the recomputation can skip the attention
+forward kernel; everything else inside a layer is recomputed. With `offload=True` that tensor is copied to pinned host memory on a side
 stream right after the layer ran and brought back (prefetched one layer ahead) during the
 backward pass, so a long sequence costs one layer's activations of HBM instead of `num_layers`.
 The copies run on their own CUDA stream and overlap the GEMMs; per-step PCIe traffic is
@@ -25,8 +26,14 @@ class ActivationStore:
         self.inflight: dict[int, tuple[torch.Tensor, torch.cuda.Event]] = {}
         self.stream = torch.cuda.Stream(device=self.device) if self.offload else None
         self.bytes_offloaded = 0
+        self.recording = False      # True while a checkpointed layer runs its no-grad forward
+        self.replaying = False      # True while a checkpointed layer is recomputed for backward
+        self.keep_attention = True  # stash (out, lse) of the attention op across the boundary
 
-    def stash(self, idx: int, x: torch.Tensor) -> None:
+    def has(self, idx) -> bool:
+        return idx in self.kept or idx in self.ready
+
+    def stash(self, idx, x: torch.Tensor) -> None:
         if not self.offload:
             self.kept[idx] = x
             return
@@ -43,8 +50,8 @@ class ActivationStore:
         self.ready[idx] = ev
         self.bytes_offloaded += x.numel() * x.element_size()
 
-    def prefetch(self, idx: int) -> None:
-        if not self.offload or idx < 0 or idx in self.inflight or idx not in self.host:
+    def prefetch(self, idx) -> None:
+        if not self.offload or idx in self.inflight or idx not in self.host or idx not in self.ready:
             return
         with torch.cuda.stream(self.stream):
             self.ready[idx].wait(self.stream)
@@ -54,11 +61,12 @@ class ActivationStore:
             ev.record(self.stream)
         self.inflight[idx] = (dev, ev)
 
-    def fetch(self, idx: int) -> torch.Tensor:
+    def fetch(self, idx) -> torch.Tensor:
         if not self.offload:
             return self.kept.pop(idx)
         self.prefetch(idx)
         dev, ev = self.inflight.pop(idx)
+        self.ready.pop(idx, None)
         cur = torch.cuda.current_stream(self.device)
         cur.wait_event(ev)
         dev.record_stream(cur)
@@ -73,8 +81,12 @@ class _LayerCheckpoint(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, layer, store, idx, args):
         ctx.layer, ctx.store, ctx.idx, ctx.args = layer, store, idx, args
-        with torch.no_grad():
-            out = layer(h, *args)
+        store.recording = True
+        try:
+            with torch.no_grad():
+                out = layer(h, *args)
+        finally:
+            store.recording = False
         store.stash(idx, h)
         return out
 
@@ -82,10 +94,15 @@ class _LayerCheckpoint(torch.autograd.Function):
     def backward(ctx, dout):
         store, idx = ctx.store, ctx.idx
         h = store.fetch(idx)
-        store.prefetch(idx - 1)
+        for key in (idx - 1, (idx - 1, "attn_out"), (idx - 1, "attn_lse")):
+            store.prefetch(key)
         h = h.detach().requires_grad_(True)
-        with torch.enable_grad():
-            out = ctx.layer(h, *ctx.args)
+        store.replaying = True
+        try:
+            with torch.enable_grad():
+                out = ctx.layer(h, *ctx.args)
+        finally:
+            store.replaying = False
         torch.autograd.backward(out, dout)
         return h.grad, None, None, None, None
 

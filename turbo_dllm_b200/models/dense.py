@@ -124,12 +124,13 @@ class DecoderLayer(nn.Module):
 class LocalAttention:
     """Keys are the rank's own rows (single rank, or pure data parallelism)."""
 
-    def __init__(self, cfg: ModelConfig, mask: MaskLayout):
-        self.cfg, self.mask = cfg, mask
+    def __init__(self, cfg: ModelConfig, mask: MaskLayout, store=None):
+        self.cfg, self.mask, self.store = cfg, mask, store
 
     def __call__(self, qkv, layer_idx):
         c = self.cfg
-        return packed_block_attention(qkv, c.num_attention_heads, c.num_key_value_heads, c.head_dim, self.mask)
+        return packed_block_attention(qkv, c.num_attention_heads, c.num_key_value_heads, c.head_dim, self.mask,
+                                      store=self.store, key=layer_idx)
 
 
 class BlockDiffusionTransformer(nn.Module):

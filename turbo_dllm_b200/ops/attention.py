@@ -250,7 +250,7 @@ def attention_backward_native(q, k, v, out, dout, lse, layout: MaskLayout, scale
         padded = torch.full((Hq, L["nq_pad"]), float("-inf"), dtype=torch.float32, device=dev)
         padded[:, :nq] = lse[:, :nq]
         lse = padded
-    delta = torch.empty(Hq, L["nq_pad"], dtype=torch.float32, device=dev)
+    delta = torch.empty(2, Hq, L["nq_pad"], dtype=torch.float32, device=dev)
     rc = native.lib().tdllm_attn_bwd(
         ptr(q), ptr(k), ptr(v), ptr(out), ptr(dout), ptr(dq), ptr(dk), ptr(dv), ptr(lse), ptr(delta),
         nq, nk, Hq, Hkv, _rows_view(q), _rows_view(k), _rows_view(v), _rows_view(out),
@@ -301,9 +301,13 @@ class _PackedBlockAttention(torch.autograd.Function):
     gradients into one packed buffer, so no slice-gradient copies are needed."""
 
     @staticmethod
-    def forward(ctx, qkv, Hq, Hkv, D, layout, scale):
+    def forward(ctx, qkv, Hq, Hkv, D, layout, scale, precomputed=None):
         q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
-        out, lse = attention_forward_native(q, k, v, layout, scale)
+        if precomputed is not None:
+            out, lse = precomputed      # results of an earlier forward on the same inputs
+            out = out.view(qkv.shape[0], Hq, D)
+        else:
+            out, lse = attention_forward_native(q, k, v, layout, scale)
         ctx.save_for_backward(qkv, out, lse)
         ctx.meta = (Hq, Hkv, D, layout, scale)
         return out.view(qkv.shape[0], Hq * D)
@@ -315,14 +319,29 @@ class _PackedBlockAttention(torch.autograd.Function):
         q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
         dqkv = torch.empty_like(qkv)
         attention_backward_native(q, k, v, out, dout.contiguous().view(-1, Hq, D), lse, layout, scale, dqkv)
-        return dqkv, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None
 
 
 def packed_block_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, layout: MaskLayout,
-                           scale: float | None = None) -> torch.Tensor:
-    """qkv [rows, (Hq+2Hkv)·D] -> [rows, Hq·D]; queries and keys are the same rows."""
+                           scale: float | None = None, store=None, key=None) -> torch.Tensor:
+    """qkv [rows, (Hq+2Hkv)·D] -> [rows, Hq·D]; queries and keys are the same rows.
+
+    `store` / `key` connect the op to activation checkpointing: during the no-grad forward of a
+    checkpointed layer the output and log-sum-exp are stashed under `key`; when the layer is
+    recomputed for its backward pass they are reused instead of running the forward kernel again."""
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if use_native(qkv) and D == 128:
+        if store is not None and store.keep_attention:
+            ko, kl = (key, "attn_out"), (key, "attn_lse")
+            if store.recording and not torch.is_grad_enabled():
+                q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
+                out, lse = attention_forward_native(q, k, v, layout, scale)
+                store.stash(ko, out)
+                store.stash(kl, lse)
+                return out.view(qkv.shape[0], Hq * D)
+            if store.replaying and store.has(ko):
+                pre = (store.fetch(ko), store.fetch(kl))
+                return _PackedBlockAttention.apply(qkv, Hq, Hkv, D, layout, scale, pre)
         return _PackedBlockAttention.apply(qkv, Hq, Hkv, D, layout, scale)
     if qkv.is_cuda and qkv.dtype == torch.bfloat16:
         raise native.NativeKernelError("bf16 CUDA attention needs head_dim 128 (no silent fallback)")

@@ -63,6 +63,9 @@ class TrainingSession:
             self.cfg, dtype=self.dtype, device=self.device,
             activation_checkpointing=spec.training.activation_checkpointing,
             activation_offload=self._want_activation_offload(), seed=seed)
+        keep = os.environ.get("TDLLM_KEEP_ATTENTION")
+        self.model.store.keep_attention = (keep == "1") if keep is not None else (
+            self.model.store.offload or getattr(self, "_keep_attention_on_device", False))
         dp_rank = runtime.data_parallel_rank if runtime is not None else self.rank
         self.dp_size = runtime.data_parallel_size if runtime is not None else self.world
         self.objective = build_objective_runtime(spec, mask_token_id=self.cfg.mask_token_id,
@@ -103,6 +106,7 @@ class TrainingSession:
         shard = max(self.world, 1)
         static = cfg.num_params() * (2 + 2 + 12 / shard)
         total = torch.cuda.get_device_properties(self.device).total_memory
+        self._keep_attention_on_device = static + 2 * ckpt + work < 0.8 * total
         return static + ckpt + work > 0.9 * total
 
     def _build_layout(self) -> PackedLayout:
@@ -127,7 +131,7 @@ class TrainingSession:
             from ..parallel.context_attention import ContextParallelAttention
 
             return ContextParallelAttention(self.cfg, self.layout, rt, self.spec)
-        return LocalAttention(self.cfg, self.layout.mask)
+        return LocalAttention(self.cfg, self.layout.mask, store=self.model.store)
 
     def _build_fused_sync(self, group):
         if group is None or self.device.type != "cuda" or self.spec.kernel.impl in ("cpu_reference", "nccl_baseline"):
