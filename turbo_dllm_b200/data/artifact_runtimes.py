@@ -1,0 +1,216 @@
+"""Data runtimes over prepared artifacts: packed, indexed-supervised and weighted blends.
+
+All three read payload files through numpy memory maps, hand out `[B, L]` batches staged in
+pinned memory and copied on a transfer stream one batch ahead, shard by data-parallel rank
+(rank r takes batches r, r+DP, ...), and expose a resumable cursor in `state_dict()`.
+
+* PackedTokenDataRuntime   – contiguous windows of `seq_len` tokens of tokens.i32, optional
+  epoch-wise shuffle of the window order (seeded).
+* IndexedSupervisedTokenDataRuntime – samples of index.i64 with their loss masks; a batch holds
+  samples of one length (length buckets), padded up to the block size by the preparation step;
+  samples shorter than `minimum_sequence_length` or not aligned to the block size are skipped.
+* BlendedPackedTokenDataRuntime – several packed artifacts mixed by weight with a seeded
+  multinomial choice per batch.
+
+Counterparts: dllm_parallel/core/data.py:248-607 (packed), :610-1275 (indexed), :1277-1394
+(blended), :1397-1530 (loaders).
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Any
+
+import numpy as np
+import torch
+
+from .artifacts import (INDEXED_FORMAT, PACKED_TOKEN_FORMAT, ArtifactError, load_manifest,
+                        validate_artifact_for_run)
+from .runtimes import DataBatch, DataRuntime
+
+
+class _Stager:
+    """Pinned double buffer + transfer stream (no-op on CPU)."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.stream = torch.cuda.Stream(device=self.device) if self.cuda else None
+
+    def to_device(self, arr: np.ndarray, dtype=torch.int64) -> tuple[torch.Tensor, int]:
+        host = torch.from_numpy(np.ascontiguousarray(arr)).to(dtype)
+        if not self.cuda:
+            return host, 0
+        pinned = host.pin_memory()
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.stream):
+            dev = pinned.to(self.device, non_blocking=True)
+        torch.cuda.current_stream(self.device).wait_stream(self.stream)
+        dev.record_stream(torch.cuda.current_stream(self.device))
+        return dev, pinned.numel() * pinned.element_size()
+
+
+class PackedTokenDataRuntime(DataRuntime):
+    def __init__(self, root: str | Path, *, batch_size: int, seq_len: int, dp_rank: int = 0, dp_size: int = 1,
+                 shuffle: bool = True, seed: int = 0, device="cpu", expected_fingerprint: str | None = None):
+        self.root = Path(root)
+        m = load_manifest(self.root)
+        if m["format"] != PACKED_TOKEN_FORMAT:
+            raise ArtifactError(f"{root} is not a packed-token artifact")
+        self.fingerprint = m["metadata"]["dataset_fingerprint"]
+        if expected_fingerprint and expected_fingerprint != self.fingerprint:
+            raise ArtifactError("dataset fingerprint differs from the one recorded in the checkpoint")
+        self.tokens = np.memmap(self.root / "tokens.i32", dtype="<i4", mode="r")
+        self.batch_size, self.seq_len = batch_size, seq_len
+        self.dp_rank, self.dp_size = dp_rank, dp_size
+        self.windows = len(self.tokens) // seq_len
+        if self.windows < batch_size * dp_size:
+            raise ArtifactError(f"artifact has {self.windows} windows of {seq_len} tokens; one global batch needs "
+                                f"{batch_size * dp_size}")
+        self.shuffle, self.seed = shuffle, seed
+        self.epoch, self.cursor = 0, 0      # cursor counts GLOBAL batches consumed in this epoch
+        self.stager = _Stager(device)
+        self._order = self._epoch_order(0)
+
+    def _epoch_order(self, epoch: int) -> np.ndarray:
+        order = np.arange(self.windows)
+        if self.shuffle:
+            np.random.default_rng(self.seed + epoch).shuffle(order)
+        return order
+
+    def next_batch(self) -> DataBatch:
+        per_global = self.batch_size * self.dp_size
+        if (self.cursor + 1) * per_global > self.windows:
+            self.epoch += 1
+            self.cursor = 0
+            self._order = self._epoch_order(self.epoch)
+        base = self.cursor * per_global + self.dp_rank * self.batch_size
+        idx = self._order[base: base + self.batch_size]
+        rows = np.stack([self.tokens[i * self.seq_len:(i + 1) * self.seq_len] for i in idx])
+        self.cursor += 1
+        dev, nbytes = self.stager.to_device(rows)
+        return DataBatch(dev, sample_ids=torch.from_numpy(idx.astype(np.int64)), h2d_bytes=nbytes)
+
+    def state_dict(self) -> dict[str, Any]:
+        return {"kind": "packed", "epoch": self.epoch, "cursor": self.cursor, "fingerprint": self.fingerprint,
+                "seed": self.seed, "dp_size": self.dp_size}
+
+    def load_state_dict(self, state: dict[str, Any]) -> None:
+        if state.get("fingerprint") != self.fingerprint:
+            raise ArtifactError("checkpoint was written for a different dataset (fingerprint mismatch)")
+        if state.get("dp_size") != self.dp_size:
+            raise ArtifactError("data-parallel size changed since the checkpoint; the data cursor cannot be mapped")
+        self.epoch, self.cursor = int(state["epoch"]), int(state["cursor"])
+        self._order = self._epoch_order(self.epoch)
+
+
+class IndexedSupervisedTokenDataRuntime(DataRuntime):
+    def __init__(self, root: str | Path, *, batch_size: int, block_size: int, max_seq_len: int,
+                 minimum_sequence_length: int | None = None, dp_rank: int = 0, dp_size: int = 1,
+                 shuffle: bool = True, seed: int = 0, device="cpu"):
+        self.root = Path(root)
+        m = load_manifest(self.root)
+        if m["format"] != INDEXED_FORMAT:
+            raise ArtifactError(f"{root} is not an indexed supervised-token artifact")
+        self.fingerprint = m["metadata"]["dataset_fingerprint"]
+        self.tokens = np.memmap(self.root / "tokens.i32", dtype="<i4", mode="r")
+        self.mask = np.memmap(self.root / "loss_mask.u8", dtype=np.uint8, mode="r")
+        self.index = np.fromfile(self.root / "index.i64", dtype="<i8").reshape(-1, 4)
+        lens = self.index[:, 1]
+        ok = (lens % block_size == 0) & (lens <= max_seq_len) & (lens >= (minimum_sequence_length or 1))
+        self.eligible = np.flatnonzero(ok)
+        self.skipped = int((~ok).sum())
+        if self.eligible.size == 0:
+            raise ArtifactError("no sample is eligible: lengths must be multiples of the block size and fit seq_len")
+        self.batch_size, self.dp_rank, self.dp_size = batch_size, dp_rank, dp_size
+        self.shuffle, self.seed = shuffle, seed
+        self.epoch, self.cursor = 0, 0
+        self.stager = _Stager(device)
+        self._batches = self._epoch_batches(0)
+
+    def _epoch_batches(self, epoch: int) -> list[np.ndarray]:
+        """Global batches of same-length samples; every DP rank takes a `batch_size` slice."""
+        rng = np.random.default_rng(self.seed + epoch)
+        per_global = self.batch_size * self.dp_size
+        out = []
+        lens = self.index[self.eligible, 1]
+        for L in np.unique(lens):
+            ids = self.eligible[lens == L]
+            if self.shuffle:
+                rng.shuffle(ids)
+            for i in range(0, len(ids) - per_global + 1, per_global):
+                out.append(ids[i:i + per_global])
+        if not out:
+            raise ArtifactError(f"no length bucket holds a full global batch of {per_global} samples")
+        if self.shuffle:
+            rng.shuffle(out)
+        return out
+
+    def next_batch(self) -> DataBatch:
+        if self.cursor >= len(self._batches):
+            self.epoch += 1
+            self.cursor = 0
+            self._batches = self._epoch_batches(self.epoch)
+        ids = self._batches[self.cursor][self.dp_rank * self.batch_size:(self.dp_rank + 1) * self.batch_size]
+        self.cursor += 1
+        toks = np.stack([self.tokens[o:o + n] for o, n in self.index[ids, :2]])
+        msk = np.stack([self.mask[o:o + n] for o, n in self.index[ids, :2]])
+        dev, nb = self.stager.to_device(toks)
+        dmask, nb2 = self.stager.to_device(msk, torch.bool)
+        return DataBatch(dev, supervision_mask=dmask, supervision_count=int(msk.sum()),
+                         sample_ids=torch.from_numpy(self.index[ids, 3].copy()), h2d_bytes=nb + nb2)
+
+    def state_dict(self):
+        return {"kind": "indexed", "epoch": self.epoch, "cursor": self.cursor, "fingerprint": self.fingerprint,
+                "seed": self.seed, "dp_size": self.dp_size}
+
+    def load_state_dict(self, state):
+        if state.get("fingerprint") != self.fingerprint:
+            raise ArtifactError("checkpoint was written for a different dataset (fingerprint mismatch)")
+        self.epoch, self.cursor = int(state["epoch"]), int(state["cursor"])
+        self._batches = self._epoch_batches(self.epoch)
+
+
+class BlendedPackedTokenDataRuntime(DataRuntime):
+    """dataset_path = "w1:path1,w2:path2": each batch comes from one member chosen with probability ∝ weight."""
+
+    def __init__(self, members: list[tuple[float, PackedTokenDataRuntime]], seed: int = 0):
+        w = np.array([m[0] for m in members], dtype=np.float64)
+        if (w <= 0).any():
+            raise ArtifactError("blend weights must be positive")
+        self.p = w / w.sum()
+        self.members = [m[1] for m in members]
+        self.seed, self.draws = seed, 0
+
+    def next_batch(self) -> DataBatch:
+        k = int(np.random.default_rng([self.seed, self.draws]).choice(len(self.members), p=self.p))
+        self.draws += 1
+        return self.members[k].next_batch()
+
+    def state_dict(self):
+        return {"kind": "blended", "draws": self.draws, "seed": self.seed,
+                "members": [m.state_dict() for m in self.members]}
+
+    def load_state_dict(self, state):
+        self.draws = int(state["draws"])
+        for m, s in zip(self.members, state["members"]):
+            m.load_state_dict(s)
+
+
+def build_artifact_runtime(spec, *, device, dp_rank: int, dp_size: int) -> DataRuntime:
+    """Chooses the runtime from the artifact's manifest (and the `w:path,...` blend syntax)."""
+    path = spec.data.dataset_path
+    common = dict(batch_size=spec.training.batch_size, dp_rank=dp_rank, dp_size=dp_size, shuffle=spec.data.shuffle,
+                  device=device)
+    if "," in path or (":" in path and not Path(path).exists()):
+        members = []
+        for item in path.split(","):
+            w, _, p = item.partition(":")
+            members.append((float(w), PackedTokenDataRuntime(p, seq_len=spec.model.seq_len, seed=spec.data.blend_seed,
+                                                             **common)))
+        return BlendedPackedTokenDataRuntime(members, seed=spec.data.blend_seed)
+    m = load_manifest(path)
+    if m["format"] == PACKED_TOKEN_FORMAT:
+        return PackedTokenDataRuntime(path, seq_len=spec.model.seq_len, seed=spec.launch.seed, **common)
+    return IndexedSupervisedTokenDataRuntime(
+        path, block_size=spec.objective.block_size or 1, max_seq_len=spec.model.seq_len,
+        minimum_sequence_length=spec.data.minimum_sequence_length, seed=spec.launch.seed, **common)
