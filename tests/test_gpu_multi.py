@@ -87,3 +87,48 @@ def test_barrier_wait_runs_out_and_reports():
         lib.tdllm_clear_error()
         lib.tdllm_set_wait_timeout_ns(2_000_000_000)
     assert float(torch.ones(4, device="cuda").sum()) == 4.0
+
+
+def _csbp(rank, world, transport, steps):
+    import os
+
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    cp = 2 if world > 1 else 1
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-hd128", "seq_len": 1024, "dtype": "bf16"},
+        "objective": {"name": "standard_block_diffusion", "block_size": 32, "sampling_epsilon_min": 0.1},
+        "training": {"batch_size": 2, "steps": steps},
+        "topology": {"context_parallel_size": cp, "block_parallel_size": cp},
+        "kernel": {"cp_bp_clean_kv_transport": transport, "impl": "nccl_baseline"},
+        "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
+    rt = build_parallel_runtime(spec, device=f"cuda:{rank}", rank=rank, world_size=world) if world > 1 else None
+    s = TrainingSession(spec, device=f"cuda:{rank}", runtime=rt)
+    losses = []
+    for _ in range(steps):
+        r = s.step()
+        t = r.loss_sum.double().clone()
+        if world > 1:
+            dist.all_reduce(t)
+        losses.append(float(t) / r.denominator)
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    return losses, s.model.flat.data.float().cpu()
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("transport", ["collective", "peer_pull"])
+def test_csbp2_on_gpus_matches_single_gpu(transport):
+    _need(2)
+    ref = run_ranks(_csbp, 1, args=("collective", 3), backend=None, deadline_s=300)[0]
+    outs = run_ranks(_csbp, 2, args=(transport, 3), backend="nccl", deadline_s=300)
+    for losses, params in outs:
+        assert losses == pytest.approx(ref[0], rel=3e-2)
+        assert (torch.from_numpy(params) - torch.from_numpy(ref[1])).abs().max().item() < 3e-2

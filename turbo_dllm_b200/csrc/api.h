@@ -94,6 +94,11 @@ int tdllm_zero_fused_step(void* const* grad_ptrs, void* const* param_ptrs, void*
                           float beta1, float beta2, float eps, float wd, int step, float grad_scale,
                           float max_norm, float* norm_out, int epoch, void* stream);
 
+int tdllm_kv_gather(void* const* staging_ptrs, void* const* flag_ptrs, const long long* counts, int rank,
+                    int world, int row_bytes, void* out, int epoch, void* stream);
+int tdllm_kv_scatter_reduce(void* const* partial_ptrs, void* const* flag_ptrs, const long long* counts,
+                            int rank, int world, int row_bytes, void* out, int epoch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -150,6 +150,57 @@ __global__ void zero_update_kernel(PeerPtrs params, PeerPtrs sumsq, const __nv_b
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// Clean K/V exchange of context-sharded block parallelism over peer memory.
+//
+// gather: every rank owns `count[r]` rows of `row_bytes` bytes in its symmetric staging buffer;
+// this rank pulls all of them (its own included) into one local buffer laid out
+// [rows of rank 0 ; rows of rank 1 ; ...], so each remote row crosses NVLink exactly once and
+// the attention kernel then reads local memory with TMA.
+// scatter-reduce: the transpose for gradients — every rank holds partial dK|dV for ALL gathered
+// rows in its symmetric buffer (same layout); the owner pulls its slice from every peer, sums
+// in fp32 and writes bf16.
+// ---------------------------------------------------------------------------
+struct RowPlan {
+  long long offset[MAX_RANKS + 1];  // prefix sums of rows per rank
+};
+
+__global__ void kv_gather_kernel(PeerPtrs staging, RowPlan plan, int rank, int world, int row_vec16,
+                                 uint4* __restrict__ out) {
+  const long long total = plan.offset[world] * row_vec16;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / row_vec16;
+    int r = 0;
+    while (row >= plan.offset[r + 1]) ++r;
+    const long long local = i - plan.offset[r] * row_vec16;
+    out[i] = reinterpret_cast<const uint4*>(staging.p[r])[local];
+  }
+}
+
+// partial.p[r]: rank r's [total_rows, row_bytes] bf16 partial gradients. Writes this rank's rows.
+__global__ void kv_scatter_reduce_kernel(PeerPtrs partial, RowPlan plan, int rank, int world, int row_vec16,
+                                         uint4* __restrict__ out) {
+  const long long first = plan.offset[rank] * row_vec16;
+  const long long n = (plan.offset[rank + 1] - plan.offset[rank]) * row_vec16;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+    for (int k = 0; k < world; ++k) {
+      const int r = (rank + 1 + k) % world;
+      acc8(reinterpret_cast<const uint4*>(partial.p[r])[first + i], f);
+    }
+    uint4 o;
+    o.x = pack_bf16x2(f[0], f[1]);
+    o.y = pack_bf16x2(f[2], f[3]);
+    o.z = pack_bf16x2(f[4], f[5]);
+    o.w = pack_bf16x2(f[6], f[7]);
+    out[i] = o;
+  }
+}
+
 }  // namespace comm
 }  // namespace tdllm
 
@@ -249,5 +300,62 @@ extern "C" int tdllm_zero_fused_step(void* const* grad_ptrs, void* const* param_
   }
   comm::barrier_kernel<<<1, 32, 0, st>>>(f, rank, world, epoch + 2);
   TD_CUDA(cudaGetLastError(), "zero_fused_step launch");
+  return 0;
+}
+
+static int fill_plan(comm::RowPlan& plan, const long long* counts, int world) {
+  plan.offset[0] = 0;
+  for (int r = 0; r < comm::MAX_RANKS; ++r)
+    plan.offset[r + 1] = plan.offset[r] + (r < world ? counts[r] : 0);
+  return 0;
+}
+
+// Barrier (epoch), then pull every rank's staged rows into `out`. row_bytes % 16 == 0.
+extern "C" int tdllm_kv_gather(void* const* staging_ptrs, void* const* flag_ptrs, const long long* counts,
+                               int rank, int world, int row_bytes, void* out, int epoch, void* stream) {
+  comm::PeerPtrs st, f;
+  comm::RowPlan plan;
+  if (fill_peers(st, staging_ptrs, world) || fill_peers(f, flag_ptrs, world)) return 1;
+  if (row_bytes % 16) {
+    tdllm_host::set_last_error("kv_gather: row_bytes must be a multiple of 16");
+    return 1;
+  }
+  fill_plan(plan, counts, world);
+  cudaStream_t s = (cudaStream_t)stream;
+  comm::barrier_kernel<<<1, 32, 0, s>>>(f, rank, world, epoch);
+  const long long total = plan.offset[world] * (row_bytes / 16);
+  if (total > 0) {
+    long long blocks = (total + 255) / 256;
+    const long long cap = (long long)tdllm_num_sms() * 8;
+    if (blocks > cap) blocks = cap;
+    comm::kv_gather_kernel<<<(unsigned)blocks, 256, 0, s>>>(st, plan, rank, world, row_bytes / 16, (uint4*)out);
+  }
+  TD_CUDA(cudaGetLastError(), "kv_gather launch");
+  return 0;
+}
+
+// Barrier (epoch), pull-and-sum this rank's slice of every peer's partial gradients into `out`,
+// barrier (epoch + 1) so that nobody overwrites its partial buffer while a peer still reads it.
+extern "C" int tdllm_kv_scatter_reduce(void* const* partial_ptrs, void* const* flag_ptrs, const long long* counts,
+                                       int rank, int world, int row_bytes, void* out, int epoch, void* stream) {
+  comm::PeerPtrs pp, f;
+  comm::RowPlan plan;
+  if (fill_peers(pp, partial_ptrs, world) || fill_peers(f, flag_ptrs, world)) return 1;
+  if (row_bytes % 16) {
+    tdllm_host::set_last_error("kv_scatter_reduce: row_bytes must be a multiple of 16");
+    return 1;
+  }
+  fill_plan(plan, counts, world);
+  cudaStream_t s = (cudaStream_t)stream;
+  comm::barrier_kernel<<<1, 32, 0, s>>>(f, rank, world, epoch);
+  const long long n = counts[rank] * (long long)(row_bytes / 16);
+  if (n > 0) {
+    long long blocks = (n + 255) / 256;
+    const long long cap = (long long)tdllm_num_sms() * 8;
+    if (blocks > cap) blocks = cap;
+    comm::kv_scatter_reduce_kernel<<<(unsigned)blocks, 256, 0, s>>>(pp, plan, rank, world, row_bytes / 16, (uint4*)out);
+  }
+  comm::barrier_kernel<<<1, 32, 0, s>>>(f, rank, world, epoch + 1);
+  TD_CUDA(cudaGetLastError(), "kv_scatter_reduce launch");
   return 0;
 }

@@ -63,6 +63,74 @@ class _AllGatherRows(torch.autograd.Function):
         return out[: counts[ctx.rank]], None, None
 
 
+class PeerKVExchange:
+    """Clean K|V gather and gradient scatter-reduce through peer memory (csrc/comm.cu): two staging
+    buffers alternate so that a fast rank never overwrites rows a slower peer is still pulling."""
+
+    def __init__(self, group, device, counts: list[int], row_elems: int):
+        import ctypes
+
+        from ..kernels import native
+        from .symm import SymmetricBarrier, SymmetricBuffer
+
+        native.register_signatures({
+            "tdllm_kv_gather": (native.c_int, [native.c_void_p] * 3 + [native.c_int] * 3 + [native.c_void_p,
+                                                                                           native.c_int,
+                                                                                           native.c_void_p]),
+            "tdllm_kv_scatter_reduce": (native.c_int, [native.c_void_p] * 3 + [native.c_int] * 3
+                                        + [native.c_void_p, native.c_int, native.c_void_p]),
+        })
+        self.native = native
+        self.counts, self.row_elems = counts, row_elems
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.total = sum(counts)
+        row_bytes = row_elems * 2
+        self.row_bytes = row_bytes
+        self.staging = [SymmetricBuffer(max(counts) * row_bytes, group, device) for _ in range(2)]
+        self.partial = SymmetricBuffer(self.total * row_bytes, group, device)
+        self.barrier = SymmetricBarrier(group, device)
+        self.counts_arr = (ctypes.c_longlong * self.world)(*counts)
+        self.flip = 0
+        self.device = device
+
+    def gather(self, x: torch.Tensor) -> torch.Tensor:
+        from ..ops._util import ptr, stream
+
+        buf = self.staging[self.flip]
+        self.flip ^= 1
+        n = self.counts[self.rank]
+        buf.as_tensor(torch.bfloat16, n * self.row_elems).view(n, self.row_elems).copy_(x)
+        out = torch.empty(self.total, self.row_elems, dtype=torch.bfloat16, device=self.device)
+        e = self.barrier.reserve(1)
+        self.native.check(self.native.lib().tdllm_kv_gather(
+            buf.ptr_array, self.barrier.buf.ptr_array, self.counts_arr, self.rank, self.world, self.row_bytes,
+            ptr(out), e, stream()), "kv_gather")
+        return out
+
+    def scatter_reduce(self, g: torch.Tensor) -> torch.Tensor:
+        from ..ops._util import ptr, stream
+
+        self.partial.as_tensor(torch.bfloat16, self.total * self.row_elems).view(self.total, self.row_elems).copy_(g)
+        out = torch.empty(self.counts[self.rank], self.row_elems, dtype=torch.bfloat16, device=self.device)
+        e = self.barrier.reserve(2)
+        self.native.check(self.native.lib().tdllm_kv_scatter_reduce(
+            self.partial.ptr_array, self.barrier.buf.ptr_array, self.counts_arr, self.rank, self.world,
+            self.row_bytes, ptr(out), e, stream()), "kv_scatter_reduce")
+        return out
+
+
+class _PeerGatherRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, exchange):
+        ctx.exchange = exchange
+        return exchange.gather(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.exchange.scatter_reduce(g.contiguous()), None
+
+
 class ContextParallelAttention:
     def __init__(self, cfg: ModelConfig, layout: PackedLayout, runtime, spec):
         self.cfg, self.layout, self.rt = cfg, layout, runtime
@@ -81,6 +149,11 @@ class ContextParallelAttention:
             counts.append(pos.numel() * batch)
         self.counts = counts
         self.transport = spec.kernel.cp_bp_clean_kv_transport
+        self.exchange = None
+        if self.transport == "peer_pull":
+            if dev.type != "cuda":
+                raise ValueError("kernel.cp_bp_clean_kv_transport=peer_pull needs CUDA devices with peer access")
+            self.exchange = PeerKVExchange(self.group, dev, counts, 2 * cfg.num_key_value_heads * cfg.head_dim)
         self.mask = block_diffusion_layout(layout.noisy_pos, layout.noisy_group, layout.clean_pos,
                                            layout.block_size, noisy_seq=layout.noisy_seq,
                                            clean_seq=layout.clean_seq, key_clean_pos=torch.cat(kpos),
@@ -93,7 +166,10 @@ class ContextParallelAttention:
         q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
         rows = qkv.shape[0]
         kv_clean = qkv[n_noisy:, Hq * D:]                       # [n_clean, 2·Hkv·D], K | V
-        gathered = _AllGatherRows.apply(kv_clean.contiguous(), self.group, self.counts)
+        if self.exchange is not None:
+            gathered = _PeerGatherRows.apply(kv_clean.contiguous(), self.exchange)
+        else:
+            gathered = _AllGatherRows.apply(kv_clean.contiguous(), self.group, self.counts)
         kv_noisy = qkv[:n_noisy, Hq * D:]
         kv_all = torch.cat([kv_noisy, gathered], dim=0)
         nk = kv_all.shape[0]
