@@ -55,6 +55,8 @@ int tdllm_adamw(float* master, float* m, float* v, const void* grad, void* param
 int tdllm_ce_finalize(const float* stats, int M, int n_tiles, const int* labels,
                       const float* weights, float* lse_out, float* loss_rows, float* out2,
                       void* stream);
+int tdllm_kl_rows(const float* student_logits, const float* teacher_logits, const float* rowscale,
+                  float* loss_rows, void* dlogits_bf16, int rows, int V, long long ld, void* stream);
 int tdllm_attn_merge(float* num, float* mrun, float* lrun, const void* o_s, const float* lse_s,
                      long long nrh, int D, int initial, void* stream);
 int tdllm_attn_merge_finalize(const float* num, const float* mrun, const float* lrun, void* out,

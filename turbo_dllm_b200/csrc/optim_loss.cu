@@ -173,6 +173,80 @@ __global__ void merge_bwd_kernel(const __nv_bfloat16* __restrict__ go,
   if (lane == 0) dlse_s[rh] = w * dot;
 }
 
+
+// ---------------------------------------------------------------------------
+// Soft-label distillation over a chunk of rows: KL(teacher || student) from two fp32 logit
+// chunks [rows, V], and its gradient w.r.t. the student logits, written as bf16:
+//   loss_r = sum_v p_t (log p_t - log p_s),  dlogits = (p_s - p_t) * rowscale[r]
+// One block per row; pass A keeps an online (max, sum) pair per thread for both distributions,
+// pass B accumulates the loss and writes the gradient. Rows with rowscale == 0 only get zeros.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void online_add(float& m, float& s, float x) {
+  if (x > m) {
+    s = s * __expf(m - x) + 1.f;
+    m = x;
+  } else {
+    s += __expf(x - m);
+  }
+}
+__device__ __forceinline__ void online_merge(float& m, float& s, float m2, float s2) {
+  const float nm = fmaxf(m, m2);
+  if (nm == -INFINITY) return;
+  s = s * __expf(m - nm) + s2 * __expf(m2 - nm);
+  m = nm;
+}
+
+__global__ void kl_rows_kernel(const float* __restrict__ zs, const float* __restrict__ zt,
+                               const float* __restrict__ rowscale, float* __restrict__ loss_rows,
+                               __nv_bfloat16* __restrict__ dlogits, int V, long long ld) {
+  __shared__ float red[4][32];
+  const size_t row = blockIdx.x;
+  const float* s = zs + row * ld;
+  const float* t = zt + row * ld;
+  __nv_bfloat16* g = dlogits ? dlogits + row * ld : nullptr;
+  const float scale = rowscale[row];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (scale == 0.f) {
+    if (g) for (int v = threadIdx.x; v < V; v += blockDim.x) g[v] = __float2bfloat16(0.f);
+    if (threadIdx.x == 0) loss_rows[row] = 0.f;
+    return;
+  }
+  float ms = -INFINITY, ss = 0.f, mt = -INFINITY, st = 0.f;
+  for (int v = threadIdx.x; v < V; v += blockDim.x) {
+    online_add(ms, ss, s[v]);
+    online_add(mt, st, t[v]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    online_merge(ms, ss, __shfl_xor_sync(0xffffffffu, ms, o), __shfl_xor_sync(0xffffffffu, ss, o));
+    online_merge(mt, st, __shfl_xor_sync(0xffffffffu, mt, o), __shfl_xor_sync(0xffffffffu, st, o));
+  }
+  if (lane == 0) { red[0][warp] = ms; red[1][warp] = ss; red[2][warp] = mt; red[3][warp] = st; }
+  __syncthreads();
+  ms = -INFINITY; ss = 0.f; mt = -INFINITY; st = 0.f;
+  for (int w = 0; w < nw; ++w) {
+    online_merge(ms, ss, red[0][w], red[1][w]);
+    online_merge(mt, st, red[2][w], red[3][w]);
+  }
+  const float lse_s = ms + __logf(ss), lse_t = mt + __logf(st);
+  float acc = 0.f;
+  for (int v = threadIdx.x; v < V; v += blockDim.x) {
+    const float ls = s[v] - lse_s, lt = t[v] - lse_t;
+    const float pt = __expf(lt);
+    acc += pt * (lt - ls);
+    if (g) g[v] = __float2bfloat16((__expf(ls) - pt) * scale);
+  }
+  acc = warp_sum(acc);
+  __syncthreads();
+  if (lane == 0) red[0][warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    acc = lane < nw ? red[0][lane] : 0.f;
+    acc = warp_sum(acc);
+    if (lane == 0) loss_rows[row] = acc;
+  }
+}
+
 }  // namespace ol
 }  // namespace tdllm
 
@@ -251,5 +325,15 @@ extern "C" int tdllm_attn_merge_bwd(const void* go, const void* out, const float
       (const __nv_bfloat16*)go, (const __nv_bfloat16*)out, lse, (const __nv_bfloat16*)o_s, lse_s,
       (__nv_bfloat16*)go_s, dlse_s, (size_t)nrh, D);
   TD_CHECK_LAUNCH("attn_merge_bwd");
+  return 0;
+}
+
+extern "C" int tdllm_kl_rows(const float* student_logits, const float* teacher_logits, const float* rowscale,
+                             float* loss_rows, void* dlogits_bf16, int rows, int V, long long ld,
+                             void* stream) {
+  if (rows <= 0) return 0;
+  ol::kl_rows_kernel<<<rows, 512, 0, (cudaStream_t)stream>>>(student_logits, teacher_logits, rowscale, loss_rows,
+                                                           (__nv_bfloat16*)dlogits_bf16, V, ld);
+  TD_CHECK_LAUNCH("kl_rows");
   return 0;
 }

@@ -41,7 +41,7 @@ class FlatParams:
     """
 
     def __init__(self, specs: list[tuple[str, tuple[int, ...], bool]], dtype, device,
-                 grad_dtype=None):
+                 grad_dtype=None, allocate_grad: bool = True):
         specs = sorted(specs, key=lambda s: (not s[2],))  # stable: decay first
         offs, total = {}, 0
         for name, shape, decay in specs:
@@ -54,12 +54,12 @@ class FlatParams:
             if decay:
                 self.decay_numel = max(self.decay_numel, (o + n + ALIGN - 1) // ALIGN * ALIGN)
         self.data = torch.zeros(total, dtype=dtype, device=device)
-        self.grad = torch.zeros(total, dtype=grad_dtype or dtype, device=device)
+        self.grad = torch.zeros(total if allocate_grad else 0, dtype=grad_dtype or dtype, device=device)
         self.offsets = offs
         self.params: dict[str, nn.Parameter] = {}
         for name, (o, n, shape, decay) in offs.items():
-            p = nn.Parameter(self.data[o:o + n].view(shape))
-            p.main_grad = self.grad[o:o + n].view(shape)
+            p = nn.Parameter(self.data[o:o + n].view(shape), requires_grad=allocate_grad)
+            p.main_grad = self.grad[o:o + n].view(shape) if allocate_grad else None
             p.grad_acc = False
             p.flat_offset = o
             p.decay = decay
@@ -69,11 +69,19 @@ class FlatParams:
         for p in self.params.values():
             p.grad_acc = False
             p.grad = None
+            if hasattr(p, "expert_written"):
+                p.expert_written = set()
 
     def collect_grads(self) -> None:
         """Folds `.grad` tensors produced by plain autograd into the flat buffer and zeroes the
         slices of parameters that received no gradient at all this step."""
         for p in self.params.values():
+            if hasattr(p, "expert_written"):
+                # stacked expert weights: slices of experts that saw no token keep stale values
+                for e in range(p.shape[0]):
+                    if e not in p.expert_written:
+                        p.main_grad[e].zero_()
+                p.grad_acc = True
             if p.grad is not None:
                 if p.grad_acc:
                     p.main_grad.add_(p.grad.to(p.main_grad.dtype))
@@ -136,7 +144,7 @@ class LocalAttention:
 class BlockDiffusionTransformer(nn.Module):
     def __init__(self, cfg: ModelConfig, *, dtype=torch.bfloat16, device="cpu", grad_dtype=None,
                  activation_checkpointing: bool = True, activation_offload: bool = False, seed: int = 0,
-                 init_std: float = 0.02):
+                 init_std: float = 0.02, frozen: bool = False):
         super().__init__()
         self.cfg = cfg
         self.activation_checkpointing = activation_checkpointing
@@ -147,7 +155,7 @@ class BlockDiffusionTransformer(nn.Module):
             specs.append(("lm_head", (cfg.vocab_size, h), True))
         for i in range(cfg.num_layers):
             specs += _layer_specs(cfg, i)
-        self.flat = FlatParams(specs, dtype, device, grad_dtype)
+        self.flat = FlatParams(specs, dtype, device, grad_dtype, allocate_grad=not frozen)
         for name, p in self.flat.params.items():
             self.register_parameter(name.replace(".", "_"), p)
         self.embed = self.flat.params["embed"]

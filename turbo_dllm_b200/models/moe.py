@@ -1,0 +1,250 @@
+"""Mixture-of-experts block-diffusion decoder (DiffusionGemma-style expert-parallel path).
+
+Attention is the dense model's. The FFN of every layer is a routed expert bank: a linear router,
+softmax over all experts, top-k selection with renormalised weights, SwiGLU experts. Tokens are
+sorted by expert so that each expert sees one contiguous, 128-row-aligned slab (padding rows are
+zero and receive zero weight), the expert GEMMs run slab by slab on the tcgen05 GEMM, and results
+are scattered back and combined with the routing weights.
+
+With expert parallelism each rank owns `E / EP` experts (`[E_local, ...]` weights). Dispatch sends
+every (token, choice) to the owner of its expert and combine returns the expert output; the
+transport is `torch.distributed.all_to_all_single` with variable splits (NCCL; gloo on CPU), the
+counterpart of the reference's DeepEP dispatch/combine ops.
+
+Counterparts: dllm_parallel/core/models/backbones/diffusiongemma/expert_parallel.py:26-200 (EP experts),
+:283-321 (grouped experts), :324-364 (reference experts), router/route replay
+dllm_parallel/core/models/backbones/diffusiongemma/model.py:33-330; DeepEP ops
+dllm_parallel/core/parallel/expert/deepep.py:122-555.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops.activation import swiglu
+from ..ops.gemm import linear, linear_residual
+from ..ops.norm import rmsnorm
+from ..ops.rope import qk_norm_rope
+from .config import ModelConfig
+from .dense import BlockDiffusionTransformer, DecoderLayer, FlatParams
+
+SLAB_ALIGN = 128
+
+
+def route_topk(logits: torch.Tensor, k: int):
+    """softmax over experts, top-k, renormalise. Returns (weights [rows,k] fp32, experts [rows,k] int64)."""
+    probs = torch.softmax(logits.float(), dim=-1)
+    w, idx = probs.topk(k, dim=-1)
+    return w / w.sum(-1, keepdim=True), idx
+
+
+def reference_experts(x, w_gu, w_down, weights, experts):
+    """Dense oracle: loops over experts on plain tensors (interleaved gate/up rows)."""
+    out = torch.zeros_like(x, dtype=torch.float32)
+    E = w_gu.shape[0]
+    for e in range(E):
+        rows, slot = (experts == e).nonzero(as_tuple=True)
+        if rows.numel() == 0:
+            continue
+        h = x[rows].float() @ w_gu[e].float().t()
+        act = torch.nn.functional.silu(h[:, 0::2]) * h[:, 1::2]
+        y = act @ w_down[e].float().t()
+        out.index_add_(0, rows, y * weights[rows, slot, None].float())
+    return out.to(x.dtype)
+
+
+class _AllToAllRows(torch.autograd.Function):
+    """Variable-split all-to-all of rows; the backward is the reverse exchange."""
+
+    @staticmethod
+    def forward(ctx, x, send_counts, recv_counts, group):
+        ctx.group, ctx.send, ctx.recv = group, send_counts, recv_counts
+        out = x.new_empty(sum(recv_counts), x.shape[1])
+        dist.all_to_all_single(out, x.contiguous(), recv_counts, send_counts, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        out = g.new_empty(sum(ctx.send), g.shape[1])
+        dist.all_to_all_single(out, g.contiguous(), ctx.send, ctx.recv, group=ctx.group)
+        return out, None, None, None
+
+
+class ExpertBank(nn.Module):
+    """`E_local` SwiGLU experts of this rank and the routed forward over them."""
+
+    def __init__(self, cfg: ModelConfig, idx: int, flat: FlatParams, ep_group=None):
+        super().__init__()
+        self.cfg, self.idx = cfg, idx
+        self.router = flat.params[f"layers.{idx}.router"]
+        self.w_gu = flat.params[f"layers.{idx}.experts_gate_up"]     # [E_local, 2I, H]
+        self.w_down = flat.params[f"layers.{idx}.experts_down"]      # [E_local, H, I]
+        self.ep_group = ep_group
+        self.ep = dist.get_world_size(ep_group) if ep_group is not None else 1
+        self.ep_rank = dist.get_rank(ep_group) if ep_group is not None else 0
+        self.e_local = self.w_gu.shape[0]
+        self.last_counts = None
+
+    def _local_experts(self, x_sorted: torch.Tensor, counts: list[int]) -> torch.Tensor:
+        """x_sorted: rows grouped by local expert (counts per expert). Per-expert slabs run through the
+        shared GEMM; weight gradients land in the experts' slices of the flat gradient buffer."""
+        outs, off = [], 0
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            xe = x_sorted[off:off + n]
+            gu = _expert_linear(xe, self.w_gu, e)
+            outs.append(_expert_linear(swiglu(gu), self.w_down, e))
+            off += n
+        if not outs:
+            return x_sorted.new_zeros(0, x_sorted.shape[1])
+        return torch.cat(outs, dim=0)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        rows, H = x.shape
+        k = cfg.num_experts_per_token
+        w, idx = route_topk(linear(x, self.router), k)
+        flat_e = idx.reshape(-1)                                        # [rows*k]
+        order = torch.argsort(flat_e, stable=True)
+        token_of = torch.div(order, k, rounding_mode="floor")
+        x_perm = x.index_select(0, token_of)                            # grouped by global expert id
+        counts_g = torch.bincount(flat_e, minlength=cfg.num_experts)
+        if self.ep > 1:
+            send = counts_g.view(self.ep, self.e_local).sum(1)
+            all_counts = torch.empty(self.ep, cfg.num_experts, dtype=counts_g.dtype, device=x.device)
+            dist.all_gather_into_tensor(all_counts.view(-1), counts_g, group=self.ep_group)
+            mine = all_counts[:, self.ep_rank * self.e_local:(self.ep_rank + 1) * self.e_local]   # [src, e_local]
+            send_l, recv_l = send.tolist(), mine.sum(1).tolist()
+            recv = _AllToAllRows.apply(x_perm, send_l, recv_l, self.ep_group)
+            # received rows are ordered (source rank, local expert): regroup by local expert
+            src_counts = mine.reshape(-1).tolist()
+            eid = torch.repeat_interleave(torch.arange(self.e_local, device=x.device).repeat(self.ep),
+                                          torch.tensor(src_counts, device=x.device))
+            eorder = torch.argsort(eid, stable=True)
+            y_sorted = self._local_experts(recv.index_select(0, eorder), mine.sum(0).tolist())
+            y_recv = torch.empty_like(y_sorted).index_copy_(0, eorder, y_sorted) if y_sorted.numel() else y_sorted
+            y_perm = _AllToAllRows.apply(y_recv, recv_l, send_l, self.ep_group)
+        else:
+            y_perm = self._local_experts(x_perm, counts_g.tolist())
+        self.last_counts = counts_g
+        wk = w.reshape(-1).index_select(0, order).to(y_perm.dtype)
+        out = torch.zeros_like(x)
+        out.index_add_(0, token_of, y_perm * wk[:, None])
+        return out
+
+
+class _ExpertLinear(torch.autograd.Function):
+    """y = x · W[e]ᵀ for one expert of a stacked weight; dW goes to that expert's gradient slice."""
+
+    @staticmethod
+    def forward(ctx, x, w_all, e):
+        from ..ops.gemm import gemm
+
+        ctx.save_for_backward(x, w_all)
+        ctx.e, ctx.wref = e, w_all
+        return gemm(x, w_all[e])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops._util import grad_sink
+        from ..ops.gemm import gemm
+
+        x, w_all = ctx.saved_tensors
+        e = ctx.e
+        dy = dy.contiguous()
+        dx = gemm(dy, w_all[e], b_mn_major=True)
+        sink, _ = grad_sink(ctx.wref)
+        if sink is not None:
+            written = ctx.wref.expert_written
+            gemm(dy, x, a_mn_major=True, b_mn_major=True, out=sink[e], accumulate=e in written)
+            written.add(e)
+            return dx, None, None
+        dw = torch.zeros_like(w_all)
+        gemm(dy, x, a_mn_major=True, b_mn_major=True, out=dw[e])
+        return dx, dw, None
+
+
+def _expert_linear(x, w_all, e):
+    return _ExpertLinear.apply(x, w_all, e)
+
+
+class MoEDecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, idx: int, flat: FlatParams, ep_group=None):
+        super().__init__()
+        self.cfg, self.idx = cfg, idx
+        g = lambda n: flat.params[f"layers.{idx}.{n}"]
+        self.input_norm, self.w_qkv, self.w_o, self.post_norm = g("input_norm"), g("w_qkv"), g("w_o"), g("post_norm")
+        self.q_norm = g("q_norm") if cfg.qk_norm else None
+        self.k_norm = g("k_norm") if cfg.qk_norm else None
+        self.experts = ExpertBank(cfg, idx, flat, ep_group)
+
+    def forward(self, h, positions, inv_freq, attend):
+        cfg = self.cfg
+        y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
+        qkv = qk_norm_rope(linear(y, self.w_qkv), positions, inv_freq, self.q_norm, self.k_norm,
+                           cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
+        h = linear_residual(attend(qkv, self.idx), self.w_o, h)
+        y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
+        return h + self.experts(y2)
+
+
+def moe_layer_specs(cfg: ModelConfig, i: int, e_local: int):
+    h, p = cfg.hidden_size, f"layers.{i}."
+    out = [(p + "input_norm", (h,), False), (p + "w_qkv", (cfg.qkv_dim, h), True), (p + "w_o", (h, cfg.q_dim), True),
+           (p + "post_norm", (h,), False), (p + "router", (cfg.num_experts, h), True),
+           (p + "experts_gate_up", (e_local, 2 * cfg.moe_intermediate_size, h), True),
+           (p + "experts_down", (e_local, h, cfg.moe_intermediate_size), True)]
+    if cfg.qk_norm:
+        out += [(p + "q_norm", (cfg.head_dim,), False), (p + "k_norm", (cfg.head_dim,), False)]
+    return out
+
+
+class MoEBlockDiffusionTransformer(BlockDiffusionTransformer):
+    """Same interface as the dense model; expert parameters are sharded over `ep_group`."""
+
+    def __init__(self, cfg: ModelConfig, *, ep_group=None, dtype=torch.bfloat16, device="cpu",
+                 activation_checkpointing: bool = True, activation_offload: bool = False, seed: int = 0,
+                 init_std: float = 0.02):
+        nn.Module.__init__(self)
+        from ..ops.rope import rope_inv_freq
+        from .activation_store import ActivationStore
+
+        self.cfg = cfg
+        self.activation_checkpointing = activation_checkpointing
+        self.store = ActivationStore(torch.device(device), offload=activation_offload)
+        self.store.keep_attention = False
+        ep = dist.get_world_size(ep_group) if ep_group is not None else 1
+        if cfg.num_experts % ep:
+            raise ValueError(f"{cfg.num_experts} experts cannot be split over expert_parallel_size {ep}")
+        e_local = cfg.num_experts // ep
+        h = cfg.hidden_size
+        specs = [("embed", (cfg.vocab_size, h), True), ("final_norm", (h,), False)]
+        if not cfg.tie_word_embeddings:
+            specs.append(("lm_head", (cfg.vocab_size, h), True))
+        for i in range(cfg.num_layers):
+            specs += moe_layer_specs(cfg, i, e_local)
+        dense_specs = [sp for sp in specs if "experts_" not in sp[0]]
+        expert_specs = [sp for sp in specs if "experts_" in sp[0]]
+        self.flat = FlatParams(dense_specs, dtype, device)            # replicated over DP x EP
+        self.flat_experts = FlatParams(expert_specs, dtype, device)    # sharded over EP, replicated over DP
+        for p in self.flat_experts.params.values():
+            p.expert_written = set()
+        self.flat.params.update(self.flat_experts.params)              # one lookup table for the layers
+        self.flat_experts_only = self.flat_experts
+        for name, p in self.flat.params.items():
+            self.register_parameter(name.replace(".", "_"), p)
+        self.embed, self.final_norm = self.flat.params["embed"], self.flat.params["final_norm"]
+        self.lm_head = self.flat.params.get("lm_head", self.embed)
+        self.layers = nn.ModuleList(MoEDecoderLayer(cfg, i, self.flat, ep_group) for i in range(cfg.num_layers))
+        self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device), persistent=False)
+        ep_rank = dist.get_rank(ep_group) if ep_group is not None else 0
+        self.reset_parameters(seed, init_std)
+        if ep > 1:  # expert slices differ per rank, everything else is replicated
+            gen = torch.Generator(device=self.flat.data.device)
+            gen.manual_seed(seed + 1000 + ep_rank)
+            for name, p in self.flat.params.items():
+                if "experts_" in name:
+                    with torch.no_grad():
+                        p.copy_((torch.randn(p.shape, device=p.device, generator=gen) * init_std).to(p.dtype))

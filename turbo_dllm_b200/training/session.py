@@ -59,6 +59,10 @@ class TrainingSession:
             raise ValueError("CPU runs use model.dtype=fp32 (the reference path is the fp32 oracle)")
         self.cfg: ModelConfig = model_config_from_run_spec(spec)
         seed = spec.launch.seed
+        self.task = None
+        if spec.objective.name == "dflash_distillation":
+            self._init_dflash(seed, runtime, host_staged_data)
+            return
         self.model = BlockDiffusionTransformer(
             self.cfg, dtype=self.dtype, device=self.device,
             activation_checkpointing=spec.training.activation_checkpointing,
@@ -91,6 +95,28 @@ class TrainingSession:
         self.steps_done = 0
 
     # ---------------------------------------------------------------- set-up
+    def _init_dflash(self, seed, runtime, host_staged_data):
+        from .dflash_task import DFlashTask
+
+        spec = self.spec
+        dp_rank = runtime.data_parallel_rank if runtime is not None else self.rank
+        self.dp_size = runtime.data_parallel_size if runtime is not None else self.world
+        self.task = DFlashTask(spec, self.cfg, dtype=self.dtype, device=self.device, seed=seed, dp_rank=dp_rank)
+        self.model, self.objective = self.task.model, self.task.objective
+        tcfg = self.task.target.cfg
+        data_kw = dict(batch_size=spec.training.batch_size, seq_len=spec.model.seq_len, vocab_size=tcfg.vocab_size,
+                       mask_token_id=tcfg.mask_token_id, seed=seed + 104729 * (dp_rank + 1),
+                       vocab_sample_size=spec.data.vocab_sample_size)
+        self.data = (HostStagedRandomRuntime(device=self.device, **data_kw) if host_staged_data
+                     else RandomTokenDataRuntime(device=self.device, **data_kw))
+        self.layout, self.attend = None, None
+        group = runtime.optimizer_group if runtime is not None else (dist.group.WORLD if self.world > 1 else None)
+        o = spec.optimizer
+        self.optimizer = FlatAdamW(self.model.flat, lr=o.lr, betas=(o.adam_beta1, o.adam_beta2), eps=o.adam_eps,
+                                   weight_decay=o.weight_decay, group=group, fused_sync=self._build_fused_sync(group))
+        self.scheduler = RunSpecLRScheduler.from_run_spec(spec)
+        self.steps_done = 0
+
     def _want_activation_offload(self) -> bool:
         """Offload layer checkpoints to pinned host memory when keeping them in HBM would not leave
         room for parameters, gradients, optimizer state and one layer's working set."""
@@ -195,14 +221,28 @@ class TrainingSession:
         spec = self.spec
         self.model.flat.zero_grad()
         batches = self.data.next_optimizer_step_batches(spec.training.gradient_accumulation_steps)
-        denom = self.global_denominator(batches)
         total = torch.zeros((), dtype=torch.float32, device=self.device)
         rows = 0
-        for b in batches:
-            ls, n, _ = self.forward_backward(b, denom)
-            total += ls.float()
-            rows += n
+        if self.task is not None:
+            # per-micro-batch normalisation by the weighted supervised count of that micro-batch;
+            # gradients are averaged over micro-batches and data-parallel ranks
+            scale = float(len(batches) * self.dp_size)
+            denom = 0.0
+            for b in batches:
+                ls, n, d = self.task.forward_backward(b)
+                total += ls.float() / d.float() / scale
+                rows += n
+            denom = 1.0
+            self._grad_div = scale
+        else:
+            denom = self.global_denominator(batches)
+            for b in batches:
+                ls, n, _ = self.forward_backward(b, denom)
+                total += ls.float()
+                rows += n
         self.model.flat.collect_grads()
+        if getattr(self, "_grad_div", 1.0) != 1.0:
+            self.model.flat.grad.div_(self._grad_div)
         lr, wd = self.scheduler.step()
         if not spec.training.skip_optimizer_step:
             self.optimizer.step(lr=lr, weight_decay=wd, max_grad_norm=spec.optimizer.gradient_clip_norm)
