@@ -52,9 +52,9 @@ def _atomic_write_json(path: str, payload: dict) -> None:
 
 def _atomic_torch_save(obj: Any, path: str) -> None:
     d = os.path.dirname(path)
-    fd, tmp = tempfile.mkstemp(prefix=".tmp_", dir=d)
-    os.close(fd)
-    torch.save(obj, tmp)
+    fd, tmp = tempfile.mkstemp(prefix="tmp_", suffix=".partial", dir=d)
+    with os.fdopen(fd, "wb") as f:
+        torch.save(obj, f)
     os.replace(tmp, path)
 
 
@@ -132,8 +132,11 @@ def save_training_checkpoint(directory: str, session, *, step: int, rank: int, w
         "profiler_metadata": {}, "backbone_state": {"family": session.cfg.family},
         "rng_state": capture_rng_state(),
     }
-    payload = {"model": session.model.flat.data, "optimizer": session.optimizer.state_dict(),
-               "client_state": client_state}
+    st = session.state_dict()
+    payload = {"model": st["model"], "optimizer": st["optimizer"], "client_state": client_state}
+    for key in ("expert_model", "expert_optimizer"):
+        if key in st:
+            payload[key] = st[key]
     path = os.path.join(tag_dir, shard_name(rank, world_size))
     err_path = os.path.join(tag_dir, f"rank_{rank:05d}.error")
     use_async = spec.checkpointing.async_checkpoint_save if async_save is None else async_save
@@ -240,7 +243,8 @@ def load_training_checkpoint(directory: str, tag: str, session, *, rank: int, wo
         raise FileNotFoundError(f"missing checkpoint shard {path}")
     payload = torch.load(path, map_location=session.device, weights_only=False)
     cs = payload["client_state"]
-    session.load_state_dict({"model": payload["model"], "optimizer": payload["optimizer"],
+    session.load_state_dict({**{k: payload[k] for k in ("expert_model", "expert_optimizer") if k in payload},
+                             "model": payload["model"], "optimizer": payload["optimizer"],
                              "scheduler": cs["scheduler_state"], "objective": cs["objective_state"],
                              "data": cs["dataloader_state"], "steps_done": cs["step"]})
     if restore_rng:

@@ -122,3 +122,12 @@ def model_config_from_run_spec(spec) -> ModelConfig:
     if cfg.mask_token_id is None:
         cfg = replace(cfg, mask_token_id=cfg.vocab_size - 1)
     return cfg
+
+PRESETS["synthetic:tiny-moe"] = ModelConfig(vocab_size=1024, hidden_size=128, num_layers=2, num_attention_heads=4,
+                                            num_key_value_heads=2, head_dim=64, intermediate_size=0, num_experts=8,
+                                            num_experts_per_token=2, moe_intermediate_size=96, mask_token_id=1023,
+                                            family="diffusion_gemma")
+PRESETS["synthetic:tiny-moe-hd128"] = ModelConfig(vocab_size=2048, hidden_size=256, num_layers=2, num_attention_heads=2,
+                                                  num_key_value_heads=1, head_dim=128, intermediate_size=0,
+                                                  num_experts=8, num_experts_per_token=2, moe_intermediate_size=128,
+                                                  mask_token_id=2047, family="diffusion_gemma")

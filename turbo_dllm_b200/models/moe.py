@@ -2,9 +2,9 @@
 
 Attention is the dense model's. The FFN of every layer is a routed expert bank: a linear router,
 softmax over all experts, top-k selection with renormalised weights, SwiGLU experts. Tokens are
-sorted by expert so that each expert sees one contiguous, 128-row-aligned slab (padding rows are
-zero and receive zero weight), the expert GEMMs run slab by slab on the tcgen05 GEMM, and results
-are scattered back and combined with the routing weights.
+sorted by expert so that each expert sees one contiguous slab of rows, the expert GEMMs run slab
+by slab on the tcgen05 GEMM (TMA clips the ragged last tile of a slab), and results are scattered
+back and combined with the routing weights.
 
 With expert parallelism each rank owns `E / EP` experts (`[E_local, ...]` weights). Dispatch sends
 every (token, choice) to the owner of its expert and combine returns the expert output; the
@@ -28,9 +28,6 @@ from ..ops.norm import rmsnorm
 from ..ops.rope import qk_norm_rope
 from .config import ModelConfig
 from .dense import BlockDiffusionTransformer, DecoderLayer, FlatParams
-
-SLAB_ALIGN = 128
-
 
 def route_topk(logits: torch.Tensor, k: int):
     """softmax over experts, top-k, renormalise. Returns (weights [rows,k] fp32, experts [rows,k] int64)."""

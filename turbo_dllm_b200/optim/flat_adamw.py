@@ -88,20 +88,39 @@ class FlatAdamW:
     # ------------------------------------------------------------------ step
     @torch.no_grad()
     def step(self, *, lr: float | None = None, weight_decay: float | None = None,
-             grad_scale: float = 1.0, max_grad_norm: float = 0.0) -> float | None:
-        """One optimizer step on gradients already present in flat.grad. Returns the global
-        gradient norm when clipping or norm reporting is enabled (a device tensor read lazily)."""
+             grad_scale: float = 1.0, max_grad_norm: float = 0.0) -> None:
+        """One optimizer step on gradients already present in flat.grad."""
+        if self.fused_sync is not None and self.world > 1:
+            self.step_count += 1
+            self.fused_sync.step(self, self.lr if lr is None else lr,
+                                 self.weight_decay if weight_decay is None else weight_decay, grad_scale,
+                                 max_grad_norm)
+            return
+        sumsq = self.reduce_gradients()
+        self.apply_update(sumsq, lr=lr, weight_decay=weight_decay, grad_scale=grad_scale,
+                          max_grad_norm=max_grad_norm)
+
+    @torch.no_grad()
+    def reduce_gradients(self) -> torch.Tensor:
+        """Phase 1: gradient sync. Returns Σ g² of the synchronised gradient over this optimizer's
+        whole buffer (already summed over the group's shards) as a 1-element device tensor."""
+        self._gshard = self._reduce_scatter_grads()
+        sumsq = self._grad_sumsq(self._gshard).clone()
+        if self.world > 1:
+            dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=self.group)
+        return sumsq
+
+    @torch.no_grad()
+    def apply_update(self, sumsq: torch.Tensor, *, lr=None, weight_decay=None, grad_scale: float = 1.0,
+                     max_grad_norm: float = 0.0) -> None:
+        """Phase 2: clip against `sumsq` (which may include other optimizers' buffers), AdamW on the
+        shard, parameter all-gather."""
         lr = self.lr if lr is None else lr
         wd = self.weight_decay if weight_decay is None else weight_decay
         self.step_count += 1
-        if self.fused_sync is not None and self.world > 1:
-            return self.fused_sync.step(self, lr, wd, grad_scale, max_grad_norm)
-        gshard = self._reduce_scatter_grads()
-        n = self.stop - self.start
-        sumsq = self._grad_sumsq(gshard)  # one extra pass over the shard; also feeds the step event
-        if self.world > 1:
-            dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=self.group)
+        gshard = self._gshard
         self.last_grad_norm = sumsq
+        n = self.stop - self.start
         pshard = self.flat.data[self.start:self.stop]
         split = min(max(self.flat.decay_numel - self.start, 0), n)  # [0, split) decayed, rest not
         b1, b2 = self.betas
@@ -115,8 +134,8 @@ class FlatAdamW:
                     ptr(sumsq), max_grad_norm, stream()), "adamw")
             else:
                 self._reference_update(lo, hi, gshard, pshard, lr, w, grad_scale, sumsq, max_grad_norm)
+        self._gshard = None
         self._all_gather_params()
-        return None
 
     def _grad_sumsq(self, gshard: torch.Tensor) -> torch.Tensor:
         if gshard.is_cuda and gshard.dtype == torch.bfloat16:

@@ -19,7 +19,8 @@ import torch.distributed as dist
 from .topology import ParallelPlan, RankAssignment
 
 AXES = ("data_parallel", "dense_data_parallel", "context_block_parallel", "clean_replica",
-        "tensor", "pipeline", "expert", "model_input", "model_parallel", "optimizer_data_parallel")
+        "tensor", "pipeline", "expert", "model_input", "model_parallel", "optimizer_data_parallel",
+        "dense_optimizer")
 
 
 def parse_group_timeouts(entries, default_seconds: float | None = None) -> dict[str, float]:
@@ -33,6 +34,14 @@ def parse_group_timeouts(entries, default_seconds: float | None = None) -> dict[
             raise ValueError(f"unknown process group {name!r} in timeout setting; known: {AXES}")
         out[name] = float(secs)
     return out
+
+
+def dense_optimizer_ranks(plan: ParallelPlan, a: RankAssignment) -> list[int]:
+    """Ranks holding the same replicated (non-expert) parameter shard: equal PP and TP coordinates,
+    any DP / CP-BP / EP coordinate."""
+    return sorted(b.rank for b in plan.rank_assignments
+                  if (b.pipeline_parallel_rank, b.tensor_parallel_rank)
+                  == (a.pipeline_parallel_rank, a.tensor_parallel_rank))
 
 
 def optimizer_data_parallel_ranks(plan: ParallelPlan, a: RankAssignment) -> list[int]:
@@ -61,14 +70,15 @@ class ProcessGroupCollection:
                     "expert": "expert_parallel_group", "model_input": "model_input_group",
                     "model_parallel": "model_parallel_group"}
         for axis in AXES:
-            if axis == "optimizer_data_parallel":
+            if axis in ("optimizer_data_parallel", "dense_optimizer"):
+                fn = optimizer_data_parallel_ranks if axis == "optimizer_data_parallel" else dense_optimizer_ranks
                 all_lists, seen = [], set()
                 for a in plan.rank_assignments:
-                    g = tuple(optimizer_data_parallel_ranks(plan, a))
+                    g = tuple(fn(plan, a))
                     if g not in seen:
                         seen.add(g)
                         all_lists.append(list(g))
-                my_list = optimizer_data_parallel_ranks(plan, mine)
+                my_list = fn(plan, mine)
             else:
                 all_lists = plan.groups(field_of[axis])
                 my_list = list(getattr(mine, field_of[axis]))

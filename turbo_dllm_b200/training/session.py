@@ -63,15 +63,24 @@ class TrainingSession:
         if spec.objective.name == "dflash_distillation":
             self._init_dflash(seed, runtime, host_staged_data)
             return
-        self.model = BlockDiffusionTransformer(
-            self.cfg, dtype=self.dtype, device=self.device,
-            activation_checkpointing=spec.training.activation_checkpointing,
-            activation_offload=self._want_activation_offload(), seed=seed)
+        ep = runtime.expert_parallel_size if runtime is not None else 1
+        if self.cfg.is_moe:
+            from ..models.moe import MoEBlockDiffusionTransformer
+
+            self.model = MoEBlockDiffusionTransformer(
+                self.cfg, ep_group=runtime.group("expert") if ep > 1 else None, dtype=self.dtype, device=self.device,
+                activation_checkpointing=spec.training.activation_checkpointing,
+                activation_offload=self._want_activation_offload(), seed=seed)
+        else:
+            self.model = BlockDiffusionTransformer(
+                self.cfg, dtype=self.dtype, device=self.device,
+                activation_checkpointing=spec.training.activation_checkpointing,
+                activation_offload=self._want_activation_offload(), seed=seed)
         keep = os.environ.get("TDLLM_KEEP_ATTENTION")
         self.model.store.keep_attention = (keep == "1") if keep is not None else (
             self.model.store.offload or getattr(self, "_keep_attention_on_device", False))
-        dp_rank = runtime.data_parallel_rank if runtime is not None else self.rank
-        self.dp_size = runtime.data_parallel_size if runtime is not None else self.world
+        dp_rank = runtime.sample_parallel_rank if runtime is not None else self.rank
+        self.dp_size = runtime.data_parallel_size * ep if runtime is not None else self.world
         self.objective = build_objective_runtime(spec, mask_token_id=self.cfg.mask_token_id,
                                                  seed=seed + 7919 * (dp_rank + 1), device=self.device)
         data_kw = dict(batch_size=spec.training.batch_size, seq_len=spec.model.seq_len,
@@ -86,13 +95,27 @@ class TrainingSession:
             self.data = build_artifact_runtime(spec, device=self.device, dp_rank=dp_rank, dp_size=self.dp_size)
         self.layout = self._build_layout()
         self.attend = self._build_attention()
-        group = runtime.optimizer_group if runtime is not None else (dist.group.WORLD if self.world > 1 else None)
         o = spec.optimizer
-        self.optimizer = FlatAdamW(self.model.flat, lr=o.lr, betas=(o.adam_beta1, o.adam_beta2), eps=o.adam_eps,
-                                   weight_decay=o.weight_decay, group=group,
-                                   fused_sync=self._build_fused_sync(group))
+        okw = dict(lr=o.lr, betas=(o.adam_beta1, o.adam_beta2), eps=o.adam_eps, weight_decay=o.weight_decay)
+        self.expert_optimizer = None
+        if self.cfg.is_moe:
+            dense_group = runtime.group("dense_optimizer") if runtime is not None else (
+                dist.group.WORLD if self.world > 1 else None)
+            expert_group = runtime.optimizer_group if runtime is not None else dense_group
+            self.optimizer = FlatAdamW(self.model.flat, group=dense_group, **okw)
+            self.expert_optimizer = FlatAdamW(self.model.flat_experts, group=expert_group, **okw)
+            self.ep_group = runtime.group("expert") if ep > 1 else None
+        else:
+            group = runtime.optimizer_group if runtime is not None else (dist.group.WORLD if self.world > 1 else None)
+            self.optimizer = FlatAdamW(self.model.flat, group=group, fused_sync=self._build_fused_sync(group), **okw)
         self.scheduler = RunSpecLRScheduler.from_run_spec(spec)
         self.steps_done = 0
+
+    def flats(self):
+        out = [self.model.flat]
+        if getattr(self.model, "flat_experts", None) is not None:
+            out.append(self.model.flat_experts)
+        return out
 
     # ---------------------------------------------------------------- set-up
     def _init_dflash(self, seed, runtime, host_staged_data):
@@ -110,6 +133,7 @@ class TrainingSession:
         self.data = (HostStagedRandomRuntime(device=self.device, **data_kw) if host_staged_data
                      else RandomTokenDataRuntime(device=self.device, **data_kw))
         self.layout, self.attend = None, None
+        self.expert_optimizer = None
         group = runtime.optimizer_group if runtime is not None else (dist.group.WORLD if self.world > 1 else None)
         o = spec.optimizer
         self.optimizer = FlatAdamW(self.model.flat, lr=o.lr, betas=(o.adam_beta1, o.adam_beta2), eps=o.adam_eps,
@@ -219,7 +243,8 @@ class TrainingSession:
 
     def step(self) -> StepResult:
         spec = self.spec
-        self.model.flat.zero_grad()
+        for f in self.flats():
+            f.zero_grad()
         batches = self.data.next_optimizer_step_batches(spec.training.gradient_accumulation_steps)
         total = torch.zeros((), dtype=torch.float32, device=self.device)
         rows = 0
@@ -240,25 +265,44 @@ class TrainingSession:
                 ls, n, _ = self.forward_backward(b, denom)
                 total += ls.float()
                 rows += n
-        self.model.flat.collect_grads()
+        for f in self.flats():
+            f.collect_grads()
         if getattr(self, "_grad_div", 1.0) != 1.0:
             self.model.flat.grad.div_(self._grad_div)
         lr, wd = self.scheduler.step()
-        if not spec.training.skip_optimizer_step:
-            self.optimizer.step(lr=lr, weight_decay=wd, max_grad_norm=spec.optimizer.gradient_clip_norm)
+        clip = spec.optimizer.gradient_clip_norm
+        if spec.training.skip_optimizer_step:
+            pass
+        elif self.expert_optimizer is None:
+            self.optimizer.step(lr=lr, weight_decay=wd, max_grad_norm=clip)
+        else:
+            # one global norm over replicated and expert-sharded parameters
+            dense_sq = self.optimizer.reduce_gradients()
+            expert_sq = self.expert_optimizer.reduce_gradients()
+            if self.ep_group is not None:
+                dist.all_reduce(expert_sq, group=self.ep_group)
+            total_sq = dense_sq + expert_sq
+            self.optimizer.apply_update(total_sq, lr=lr, weight_decay=wd, max_grad_norm=clip)
+            self.expert_optimizer.apply_update(total_sq, lr=lr, weight_decay=wd, max_grad_norm=clip)
         self.steps_done += 1
         return StepResult(total, denom, torch.tensor(rows), sum(int(b.input_ids.numel()) for b in batches),
                           sum(b.h2d_bytes for b in batches))
 
     # ------------------------------------------------------------- checkpoint
     def state_dict(self) -> dict:
-        return {"model": self.model.flat.data, "optimizer": self.optimizer.state_dict(),
+        extra = {}
+        if self.expert_optimizer is not None:
+            extra = {"expert_model": self.model.flat_experts.data, "expert_optimizer": self.expert_optimizer.state_dict()}
+        return {**extra, "model": self.model.flat.data, "optimizer": self.optimizer.state_dict(),
                 "scheduler": self.scheduler.state_dict(), "objective": self.objective.state_dict(),
                 "data": self.data.state_dict(), "steps_done": self.steps_done}
 
     def load_state_dict(self, state: dict) -> None:
         self.model.flat.data.copy_(state["model"])
         self.optimizer.load_state_dict(state["optimizer"])
+        if self.expert_optimizer is not None and "expert_model" in state:
+            self.model.flat_experts.data.copy_(state["expert_model"])
+            self.expert_optimizer.load_state_dict(state["expert_optimizer"])
         self.scheduler.load_state_dict(state["scheduler"])
         self.objective.load_state_dict(state["objective"])
         self.data.load_state_dict(state["data"])
