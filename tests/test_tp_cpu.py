@@ -1,0 +1,50 @@
+"""Tensor parallelism over gloo ranks reproduces the single-process model (fp32, CPU)."""
+import copy
+
+import pytest
+import torch
+
+from tests._harness import run_ranks
+
+MAPPING = {
+    "model": {"id": "synthetic:tiny-qwen3", "seq_len": 128, "dtype": "fp32", "num_layers": 2},
+    "objective": {"name": "standard_block_diffusion", "block_size": 32, "sampling_epsilon_min": 0.1},
+    "training": {"batch_size": 2, "steps": 3},
+    "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
+    "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0},
+}
+
+
+def _run(rank, world, tp, steps):
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    torch.set_num_threads(2)
+    m = copy.deepcopy(MAPPING)
+    m["topology"]["tensor_parallel_size"] = tp
+    spec = RunSpec.from_mapping(m).validate(world_size=world)
+    rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
+    s = TrainingSession(spec, device="cpu", runtime=rt)
+    losses, norms = [], []
+    for _ in range(steps):
+        r = s.step()
+        losses.append(float(r.loss_sum) / r.denominator)
+        norms.append(s.optimizer.grad_norm())
+    names = {n: p.detach().clone() for n, p in s.model.flat.params.items()}
+    return losses, norms, names["final_norm"], names["layers.1.w_down"], names["layers.0.w_qkv"]
+
+
+@pytest.mark.distributed
+def test_tp2_matches_single_process():
+    ref = _run(0, 1, 1, 3)
+    outs = run_ranks(_run, 2, args=(2, 3), deadline_s=240)
+    for r, (losses, norms, fnorm, w_down, w_qkv) in enumerate(outs):
+        assert losses == pytest.approx(ref[0], rel=2e-4, abs=2e-4)
+        assert norms == pytest.approx(ref[1], rel=2e-3)
+        assert torch.allclose(torch.from_numpy(fnorm), ref[2], rtol=1e-3, atol=2e-5)
+        full = ref[3]
+        n = full.shape[1] // 2
+        assert torch.allclose(torch.from_numpy(w_down), full[:, r * n:(r + 1) * n], rtol=1e-3, atol=1e-4)

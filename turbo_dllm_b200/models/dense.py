@@ -22,10 +22,12 @@ import torch.nn as nn
 
 from ..ops.attention import MaskLayout, packed_block_attention
 from ..ops.embedding import embedding
-from ..ops.gemm import linear, linear_residual, linear_swiglu
+from ..ops.gemm import linear, linear_residual, linear_swiglu, row_parallel_linear_residual
 from ..ops.linear_ce import linear_cross_entropy
 from ..ops.norm import rmsnorm
 from ..ops.rope import qk_norm_rope, rope_inv_freq
+from ..parallel.tensor_parallel import (TPContext, copy_to_tensor_parallel, vocab_parallel_embedding,
+                                        vocab_parallel_linear_cross_entropy)
 from .activation_store import ActivationStore, checkpointed_layer
 from .config import ModelConfig
 
@@ -93,7 +95,22 @@ class FlatParams:
                 p.main_grad.zero_()
 
 
+def local_config(cfg: ModelConfig, tp: int) -> ModelConfig:
+    """Per-rank shapes under tensor parallelism: heads and FFN width are divided by `tp`."""
+    if tp == 1:
+        return cfg
+    from dataclasses import replace
+
+    if cfg.num_attention_heads % tp or cfg.num_key_value_heads % tp or cfg.intermediate_size % tp or cfg.vocab_size % tp:
+        raise ValueError(f"heads ({cfg.num_attention_heads}/{cfg.num_key_value_heads}), FFN width "
+                         f"({cfg.intermediate_size}) and vocabulary ({cfg.vocab_size}) must divide by "
+                         f"tensor_parallel_size {tp}")
+    return replace(cfg, num_attention_heads=cfg.num_attention_heads // tp,
+                   num_key_value_heads=cfg.num_key_value_heads // tp, intermediate_size=cfg.intermediate_size // tp)
+
+
 def _layer_specs(cfg: ModelConfig, i: int):
+    """cfg: per-rank (local) shapes."""
     h, p = cfg.hidden_size, f"layers.{i}."
     out = [(p + "input_norm", (h,), False), (p + "w_qkv", (cfg.qkv_dim, h), True),
            (p + "w_o", (h, cfg.q_dim), True), (p + "post_norm", (h,), False),
@@ -105,9 +122,9 @@ def _layer_specs(cfg: ModelConfig, i: int):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: ModelConfig, idx: int, flat: FlatParams):
+    def __init__(self, cfg: ModelConfig, idx: int, flat: FlatParams, tp=None):
         super().__init__()
-        self.cfg, self.idx = cfg, idx
+        self.cfg, self.idx, self.tp = cfg, idx, tp
         g = lambda n: flat.params[f"layers.{idx}.{n}"]
         self.input_norm, self.w_qkv, self.w_o = g("input_norm"), g("w_qkv"), g("w_o")
         self.post_norm, self.w_gate_up, self.w_down = g("post_norm"), g("w_gate_up"), g("w_down")
@@ -117,16 +134,17 @@ class DecoderLayer(nn.Module):
     def forward(self, h, positions, inv_freq, attend: Callable):
         """h: residual stream [rows, H] -> residual stream. Both residual adds happen in the
         epilogues of the O and down projections."""
-        cfg = self.cfg
+        cfg, tp = self.cfg, self.tp
+        tpg = tp.group if tp is not None and tp.size > 1 else None
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
-        qkv = linear(y, self.w_qkv)
+        qkv = linear(copy_to_tensor_parallel(y, tpg), self.w_qkv)
         qkv = qk_norm_rope(qkv, positions, inv_freq, self.q_norm, self.k_norm, cfg.num_attention_heads,
                            cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
-        a = attend(qkv, self.idx)          # [rows, Hq·D]
-        h = linear_residual(a, self.w_o, h)
+        a = attend(qkv, self.idx)          # [rows, Hq_local·D]
+        h = row_parallel_linear_residual(a, self.w_o, h, tp)
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
-        act = linear_swiglu(y2, self.w_gate_up)
-        return linear_residual(act, self.w_down, h)
+        act = linear_swiglu(copy_to_tensor_parallel(y2, tpg), self.w_gate_up)
+        return row_parallel_linear_residual(act, self.w_down, h, tp)
 
 
 class LocalAttention:
@@ -144,45 +162,72 @@ class LocalAttention:
 class BlockDiffusionTransformer(nn.Module):
     def __init__(self, cfg: ModelConfig, *, dtype=torch.bfloat16, device="cpu", grad_dtype=None,
                  activation_checkpointing: bool = True, activation_offload: bool = False, seed: int = 0,
-                 init_std: float = 0.02, frozen: bool = False):
+                 init_std: float = 0.02, frozen: bool = False, tp: TPContext | None = None):
         super().__init__()
-        self.cfg = cfg
+        self.cfg = cfg                      # global architecture
+        self.tp = tp if tp is not None and tp.size > 1 else None
+        tps = self.tp.size if self.tp is not None else 1
+        self.lcfg = local_config(cfg, tps)  # per-rank shapes
         self.activation_checkpointing = activation_checkpointing
         self.store = ActivationStore(torch.device(device), offload=activation_offload)
         h = cfg.hidden_size
-        specs = [("embed", (cfg.vocab_size, h), True), ("final_norm", (h,), False)]
+        specs = [("embed", (cfg.vocab_size // tps, h), True), ("final_norm", (h,), False)]
         if not cfg.tie_word_embeddings:
-            specs.append(("lm_head", (cfg.vocab_size, h), True))
+            specs.append(("lm_head", (cfg.vocab_size // tps, h), True))
         for i in range(cfg.num_layers):
-            specs += _layer_specs(cfg, i)
+            specs += _layer_specs(self.lcfg, i)
         self.flat = FlatParams(specs, dtype, device, grad_dtype, allocate_grad=not frozen)
         for name, p in self.flat.params.items():
             self.register_parameter(name.replace(".", "_"), p)
         self.embed = self.flat.params["embed"]
         self.final_norm = self.flat.params["final_norm"]
         self.lm_head = self.flat.params.get("lm_head", self.embed)
-        self.layers = nn.ModuleList(DecoderLayer(cfg, i, self.flat) for i in range(cfg.num_layers))
+        self.layers = nn.ModuleList(DecoderLayer(self.lcfg, i, self.flat, self.tp) for i in range(cfg.num_layers))
         self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device), persistent=False)
         self.reset_parameters(seed, init_std)
 
     @torch.no_grad()
     def reset_parameters(self, seed: int, std: float) -> None:
-        gen = torch.Generator(device=self.flat.data.device)
-        gen.manual_seed(seed)
+        """Normal(0, std) matrices, unit norm weights. Every parameter has its own seed derived from
+        its name and the full (unsharded) tensor is generated before this rank's slice is taken, so
+        a tensor-parallel model starts from exactly the weights of the single-rank model."""
+        import zlib
+
+        dev = self.flat.data.device
+        gen = torch.Generator(device=dev)
+        tp = getattr(self, "tp", None)
+        cfg = self.cfg
         for name, p in self.flat.params.items():
-            if p.decay:
-                # generate in fp32 chunks to bound temporary memory for the large matrices
-                flat = p.view(-1)
-                step = 1 << 26
-                for s in range(0, flat.numel(), step):
-                    e = min(s + step, flat.numel())
-                    flat[s:e] = (torch.randn(e - s, device=flat.device, generator=gen) * std).to(flat.dtype)
-            else:
+            if not p.decay:
                 p.fill_(1.0)
+                continue
+            gen.manual_seed((seed * 1000003 + zlib.crc32(name.encode())) % (2 ** 63))
+            if tp is None:
+                p.copy_((torch.randn(p.shape, device=dev, generator=gen) * std).to(p.dtype))
+                continue
+            leaf = name.split(".")[-1]
+            D, Hq, Hkv, t = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, tp.size
+            if leaf in ("embed", "lm_head", "w_gate_up"):
+                full = torch.randn((p.shape[0] * t, p.shape[1]), device=dev, generator=gen)
+                shard = tp.shard(full, 0)
+            elif leaf in ("w_o", "w_down"):
+                full = torch.randn((p.shape[0], p.shape[1] * t), device=dev, generator=gen)
+                shard = tp.shard(full, 1)
+            elif leaf == "w_qkv":
+                full = torch.randn(((Hq + 2 * Hkv) * D, p.shape[1]), device=dev, generator=gen)
+                q, k, v = full[: Hq * D], full[Hq * D:(Hq + Hkv) * D], full[(Hq + Hkv) * D:]
+                shard = torch.cat([tp.shard(q, 0), tp.shard(k, 0), tp.shard(v, 0)], dim=0)
+            else:
+                full = torch.randn(p.shape, device=dev, generator=gen)
+                shard = full
+            p.copy_((shard * std).to(p.dtype))
 
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor, attend: Callable) -> torch.Tensor:
         """tokens, positions: [rows]; returns final-norm hidden states [rows, H]."""
-        h = embedding(tokens, self.embed)
+        if self.tp is not None:
+            h = vocab_parallel_embedding(tokens, self.embed, self.tp, self.cfg.vocab_size)
+        else:
+            h = embedding(tokens, self.embed)
         positions = positions.to(torch.int32)
         for i, layer in enumerate(self.layers):
             if self.activation_checkpointing and torch.is_grad_enabled():
@@ -196,6 +241,9 @@ class BlockDiffusionTransformer(nn.Module):
              exclude_mask_token: bool):
         """Σ weighted CE over rows with label >= 0 (rows are already compacted to supervised ones)."""
         ex = self.cfg.mask_token_id if exclude_mask_token else -1
+        if self.tp is not None:
+            return vocab_parallel_linear_cross_entropy(hidden_rows, self.lm_head, labels, weights, self.tp,
+                                                       self.cfg.vocab_size, exclude_index=ex)
         return linear_cross_entropy(hidden_rows, self.lm_head, labels, weights, exclude_index=ex)
 
 

@@ -209,6 +209,8 @@ class MoEBlockDiffusionTransformer(BlockDiffusionTransformer):
         from .activation_store import ActivationStore
 
         self.cfg = cfg
+        self.lcfg = cfg
+        self.tp = None
         self.activation_checkpointing = activation_checkpointing
         self.store = ActivationStore(torch.device(device), offload=activation_offload)
         self.store.keep_attention = False

@@ -134,6 +134,44 @@ def linear_residual(x: torch.Tensor, w: torch.Tensor, res: torch.Tensor) -> torc
     return _LinearResidual.apply(x, w, res)
 
 
+class _RowParallelResidual(torch.autograd.Function):
+    """h = res + Σ_ranks x_r W_rᵀ for a weight split along its input columns. The residual is added in
+    the GEMM epilogue of rank 0 only, then one all-reduce finishes the sum; every rank receives the
+    full gradient of the (replicated) residual stream."""
+
+    @staticmethod
+    def forward(ctx, x, w, res, group, rank):
+        import torch.distributed as dist
+
+        ctx.save_for_backward(x, w)
+        ctx.wref = w
+        out = gemm(x, w, residual=_as2d(res) if rank == 0 else None)
+        dist.all_reduce(out, group=group)
+        return out.view(res.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = _as2d(dy.contiguous())
+        dx = gemm(dy2, w, b_mn_major=True).view_as(x) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            sink, acc = grad_sink(ctx.wref)
+            if sink is not None:
+                gemm(dy2, _as2d(x), a_mn_major=True, b_mn_major=True, out=sink, accumulate=acc)
+                mark_grad_written(ctx.wref)
+            else:
+                dw = gemm(dy2, _as2d(x), a_mn_major=True, b_mn_major=True, out_dtype=w.dtype)
+        return dx, dw, (dy if ctx.needs_input_grad[2] else None), None, None
+
+
+def row_parallel_linear_residual(x, w_shard, res, tp) -> torch.Tensor:
+    """`tp`: parallel.tensor_parallel.TPContext (or None / size 1 for no tensor parallelism)."""
+    if tp is None or tp.size == 1:
+        return _LinearResidual.apply(x, w_shard, res)
+    return _RowParallelResidual.apply(x, w_shard, res, tp.group, tp.rank)
+
+
 class _LinearSwiGLU(torch.autograd.Function):
     """act = silu(g) * u where [g0,u0,g1,u1,...] = x W_guᵀ with interleaved gate/up rows.
     Without grad the activation is applied in the GEMM epilogue and the [rows, 2I]

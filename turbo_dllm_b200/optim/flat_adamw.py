@@ -37,8 +37,10 @@ def shard_bounds(numel: int, parts: int, index: int) -> tuple[int, int]:
 
 class FlatAdamW:
     def __init__(self, flat: FlatParams, *, lr: float, betas=(0.9, 0.999), eps: float = 1e-8,
-                 weight_decay: float = 0.0, group=None, sync_impl: str = "nccl", fused_sync=None):
+                 weight_decay: float = 0.0, group=None, sync_impl: str = "nccl", fused_sync=None,
+                 tp_group=None):
         self.flat = flat
+        self.tp_group = tp_group   # matrices are sharded over it, norm weights replicated
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.group = group
         self.world = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
@@ -105,7 +107,18 @@ class FlatAdamW:
         """Phase 1: gradient sync. Returns Σ g² of the synchronised gradient over this optimizer's
         whole buffer (already summed over the group's shards) as a 1-element device tensor."""
         self._gshard = self._reduce_scatter_grads()
-        sumsq = self._grad_sumsq(self._gshard).clone()
+        if self.tp_group is None:
+            sumsq = self._grad_sumsq(self._gshard).clone()
+        else:
+            # tensor-parallel shards of the matrices add up over the TP group; replicated norm
+            # weights (the non-decayed tail of the buffer) must be counted once
+            n = self.stop - self.start
+            split = min(max(self.flat.decay_numel - self.start, 0), n)
+            sharded = self._grad_sumsq(self._gshard[:split]).clone() if split > 0 else torch.zeros(
+                1, device=self._gshard.device)
+            dist.all_reduce(sharded, op=dist.ReduceOp.SUM, group=self.tp_group)
+            repl = self._grad_sumsq(self._gshard[split:]).clone() if n > split else torch.zeros_like(sharded)
+            sumsq = sharded + repl
         if self.world > 1:
             dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=self.group)
         return sumsq

@@ -1,0 +1,284 @@
+"""Tensor parallelism: Megatron-style column / row parallel projections, vocab-parallel embedding
+and vocab-parallel fused linear cross-entropy, plus sequence-parallel gather / scatter.
+
+* column-parallel (QKV, gate/up): the weight is split along its output rows; the input is
+  replicated, so the forward needs no communication and the input gradient is all-reduced.
+* row-parallel (O, down): the weight is split along its input columns; partial outputs are
+  summed with an all-reduce. The residual stream is added in the GEMM epilogue of TP rank 0
+  only, so the all-reduce produces `residual + Σ partials` without an extra pass.
+* vocab-parallel embedding: masked lookup in the local vocabulary shard + all-reduce.
+* vocab-parallel cross-entropy: local (max, Σexp, target) statistics from the tcgen05 GEMM
+  epilogue on the local vocabulary shard, combined across ranks with one all-gather of the local
+  log-sum-exp and one all-reduce of the target logit; the backward recomputes the local logits
+  with the global log-sum-exp and all-reduces the hidden gradient.
+* sequence parallel: rows are scattered along the sequence inside the TP group between
+  blocks (reduce-scatter instead of all-reduce, all-gather before column-parallel GEMMs).
+
+Counterparts: dllm_parallel/core/parallel/tensor_parallel/mappings.py:40-449,
+layers.py:39-365, cross_entropy.py:18-276, sequence_parallel.py:22-379.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops.gemm import EPI_CE_GRAD, EPI_CE_STATS, gemm
+from ..ops.linear_ce import linear_ce_reference
+
+
+# ---------------------------------------------------------------- mappings
+class _CopyToTP(torch.autograd.Function):
+    """Identity forward, all-reduce backward (input of a column-parallel projection)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class _ReduceFromTP(torch.autograd.Function):
+    """All-reduce forward, identity backward (output of a row-parallel projection)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class _GatherRowsSP(torch.autograd.Function):
+    """Sequence parallel: all-gather rows forward, reduce-scatter backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        world = dist.get_world_size(group)
+        out = x.new_empty(world * x.shape[0], *x.shape[1:])
+        dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        world = dist.get_world_size(ctx.group)
+        out = g.new_empty(g.shape[0] // world, *g.shape[1:])
+        if g.is_cuda:
+            dist.reduce_scatter_tensor(out, g.contiguous(), group=ctx.group)
+        else:
+            full = g.contiguous().clone()
+            dist.all_reduce(full, group=ctx.group)
+            r = dist.get_rank(ctx.group)
+            out = full[r * out.shape[0]:(r + 1) * out.shape[0]]
+        return out, None
+
+
+class _ScatterRowsSP(torch.autograd.Function):
+    """Sequence parallel: reduce-scatter rows forward, all-gather backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        world = dist.get_world_size(group)
+        n = x.shape[0] // world
+        if x.is_cuda:
+            out = x.new_empty(n, *x.shape[1:])
+            dist.reduce_scatter_tensor(out, x.contiguous(), group=group)
+            return out
+        full = x.contiguous().clone()
+        dist.all_reduce(full, group=group)
+        r = dist.get_rank(group)
+        return full[r * n:(r + 1) * n].clone()
+
+    @staticmethod
+    def backward(ctx, g):
+        world = dist.get_world_size(ctx.group)
+        out = g.new_empty(world * g.shape[0], *g.shape[1:])
+        dist.all_gather_into_tensor(out, g.contiguous(), group=ctx.group)
+        return out, None
+
+
+def copy_to_tensor_parallel(x, group):
+    return x if group is None else _CopyToTP.apply(x, group)
+
+
+def reduce_from_tensor_parallel(x, group):
+    return x if group is None else _ReduceFromTP.apply(x, group)
+
+
+def gather_sequence_parallel(x, group):
+    return x if group is None else _GatherRowsSP.apply(x, group)
+
+
+def scatter_sequence_parallel(x, group):
+    return x if group is None else _ScatterRowsSP.apply(x, group)
+
+
+class TPContext:
+    """Group handle plus the shard arithmetic the model needs."""
+
+    def __init__(self, group=None, sequence_parallel: bool = False):
+        self.group = group
+        self.size = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.sequence_parallel = bool(sequence_parallel) and self.size > 1
+
+    def shard(self, full: torch.Tensor, dim: int) -> torch.Tensor:
+        n = full.shape[dim] // self.size
+        return full.narrow(dim, self.rank * n, n)
+
+    def vocab_range(self, vocab: int) -> tuple[int, int]:
+        n = vocab // self.size
+        return self.rank * n, (self.rank + 1) * n
+
+
+# ------------------------------------------------------- vocab-parallel ops
+class _VocabParallelEmbedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tokens, weight, v0, v1, group):
+        from ..ops._util import grad_sink
+
+        inside = (tokens >= v0) & (tokens < v1)
+        local = (tokens - v0).clamp(0, v1 - v0 - 1)
+        out = weight.index_select(0, local)
+        out = out * inside[:, None].to(out.dtype)
+        dist.all_reduce(out, group=group)
+        ctx.save_for_backward(local, inside)
+        ctx.wref = weight
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops._util import grad_sink, mark_grad_written
+
+        local, inside = ctx.saved_tensors
+        dy = dy * inside[:, None].to(dy.dtype)
+        sink, acc = grad_sink(ctx.wref)
+        if sink is None:
+            dw = torch.zeros_like(ctx.wref)
+            dw.index_add_(0, local, dy.to(dw.dtype))
+            return None, dw, None, None, None
+        if not acc:
+            sink.zero_()
+        sink.index_add_(0, local, dy.to(sink.dtype))
+        mark_grad_written(ctx.wref)
+        return None, None, None, None, None
+
+
+def vocab_parallel_embedding(tokens, weight_shard, tp: TPContext, vocab: int):
+    v0, v1 = tp.vocab_range(vocab)
+    return _VocabParallelEmbedding.apply(tokens, weight_shard, v0, v1, tp.group)
+
+
+class _VocabParallelLinearCE(torch.autograd.Function):
+    """Native path: h [rows,H] bf16 (replicated), w_shard [V/tp, H]."""
+
+    @staticmethod
+    def forward(ctx, h, w, labels, weights, v0, exclude_index, group, chunk_rows):
+        from ..kernels import native
+        from ..ops._util import ptr, stream
+
+        rows, H = h.shape
+        Vl = w.shape[0]
+        lib = native.lib()
+        dev = h.device
+        local_labels = torch.where((labels >= v0) & (labels < v0 + Vl), labels - v0,
+                                   torch.full_like(labels, -1)).to(torch.int32).contiguous()
+        ex = exclude_index - v0 if v0 <= exclude_index < v0 + Vl else -1
+        nt = lib.tdllm_gemm_n_tiles(Vl)
+        stats = torch.empty(rows, nt, 3, dtype=torch.float32, device=dev)
+        native.check(lib.tdllm_gemm_bf16(ptr(h), ptr(w), None, rows, Vl, H, h.stride(0), w.stride(0), 0, 0, 0, 0, 0,
+                                         EPI_CE_STATS, ptr(local_labels), None, None, ptr(stats), int(ex), 0.0, 0,
+                                         None, 0, stream()), "vocab-parallel ce stats")
+        s = stats.view(rows, nt, 3)
+        mx = s[:, :, 0].amax(1)
+        lse_local = mx + torch.log((s[:, :, 1] * torch.exp(s[:, :, 0] - mx[:, None])).sum(1))
+        tgt = s[:, :, 2].sum(1)
+        world = dist.get_world_size(group)
+        all_lse = torch.empty(world, rows, dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(all_lse.view(-1), lse_local.contiguous(), group=group)
+        lse = torch.logsumexp(all_lse, dim=0)
+        dist.all_reduce(tgt, group=group)
+        valid = labels >= 0
+        per_row = torch.where(valid, lse - tgt, torch.zeros_like(lse))
+        wts = torch.ones_like(per_row) if weights is None else weights.float()
+        ctx.save_for_backward(h, w, local_labels, lse, (wts * valid.float()).contiguous())
+        ctx.meta = (int(ex), group, int(chunk_rows))
+        ctx.wref = w
+        ctx.mark_non_differentiable(per_row)
+        return (per_row * wts).sum(), per_row
+
+    @staticmethod
+    def backward(ctx, gsum, _g):
+        from ..kernels import native
+        from ..ops._util import grad_sink, mark_grad_written, ptr, stream
+
+        h, w, local_labels, lse, rowscale = ctx.saved_tensors
+        ex, group, chunk_rows = ctx.meta
+        rows, H = h.shape
+        Vl = w.shape[0]
+        lib = native.lib()
+        rowscale = (rowscale * gsum.float()).contiguous()
+        dh = torch.empty_like(h)
+        sink, acc = grad_sink(ctx.wref)
+        dw = None if sink is not None else torch.zeros(Vl, H, dtype=torch.float32, device=h.device)
+        chunk = min(rows, chunk_rows)
+        dlog = torch.empty(chunk, Vl, dtype=torch.bfloat16, device=h.device)
+        first = True
+        for r0 in range(0, rows, chunk):
+            r1 = min(r0 + chunk, rows)
+            n = r1 - r0
+            native.check(lib.tdllm_gemm_bf16(ptr(h[r0:r1]), ptr(w), ptr(dlog), n, Vl, H, h.stride(0), w.stride(0), Vl,
+                                             0, 0, 0, 0, EPI_CE_GRAD, ptr(local_labels[r0:r1]), ptr(lse[r0:r1]),
+                                             ptr(rowscale[r0:r1]), None, ex, 0.0, 0, None, 0, stream()),
+                         "vocab-parallel ce grad")
+            gemm(dlog[:n], w, b_mn_major=True, out=dh[r0:r1])
+            if sink is not None:
+                gemm(dlog[:n], h[r0:r1], a_mn_major=True, b_mn_major=True, out=sink, accumulate=acc or not first)
+            else:
+                gemm(dlog[:n], h[r0:r1], a_mn_major=True, b_mn_major=True, out=dw, accumulate=not first)
+            first = False
+        dist.all_reduce(dh, group=group)
+        if sink is not None:
+            mark_grad_written(ctx.wref)
+        else:
+            dw = dw.to(w.dtype)
+        return dh, dw, None, None, None, None, None, None
+
+
+def vocab_parallel_linear_cross_entropy(h, w_shard, labels, weights, tp: TPContext, vocab: int,
+                                        exclude_index: int = -1, chunk_rows: int = 8192):
+    """Returns (Σ weighted loss, per-row loss); identical on every TP rank."""
+    from ..ops._util import use_native
+
+    v0, v1 = tp.vocab_range(vocab)
+    if use_native(h, w_shard):
+        return _VocabParallelLinearCE.apply(h.contiguous(), w_shard, labels, weights, v0, exclude_index, tp.group,
+                                            chunk_rows)
+    # reference path (CPU / fp32): gather the shards' logits statistics with autograd-aware ops
+    hc = copy_to_tensor_parallel(h, tp.group)
+    z = hc.float() @ w_shard.float().t()
+    if v0 <= exclude_index < v1:
+        z = z.clone()
+        z[:, exclude_index - v0] = float("-inf")
+    m_local = z.max(dim=1).values.detach()
+    m = m_local.clone()
+    dist.all_reduce(m, op=dist.ReduceOp.MAX, group=tp.group)
+    se = reduce_from_tensor_parallel(torch.exp(z - m[:, None]).sum(1), tp.group)
+    inside = (labels >= v0) & (labels < v1)
+    loc = (labels - v0).clamp(0, v1 - v0 - 1)
+    zt = hc.float() @ w_shard.float().t() if v0 <= exclude_index < v1 else z
+    tgt = reduce_from_tensor_parallel(torch.where(inside, zt.gather(1, loc[:, None])[:, 0], torch.zeros_like(m)),
+                                      tp.group)
+    valid = labels >= 0
+    per_row = torch.where(valid, m + torch.log(se) - tgt, torch.zeros_like(m))
+    wts = torch.ones_like(per_row) if weights is None else weights.float()
+    return (per_row * wts).sum(), per_row.detach()

@@ -72,10 +72,15 @@ class TrainingSession:
                 activation_checkpointing=spec.training.activation_checkpointing,
                 activation_offload=self._want_activation_offload(), seed=seed)
         else:
+            from ..parallel.tensor_parallel import TPContext
+
+            tp = None
+            if runtime is not None and runtime.tensor_parallel_size > 1:
+                tp = TPContext(runtime.tensor_group, spec.topology.sequence_parallel)
             self.model = BlockDiffusionTransformer(
                 self.cfg, dtype=self.dtype, device=self.device,
                 activation_checkpointing=spec.training.activation_checkpointing,
-                activation_offload=self._want_activation_offload(), seed=seed)
+                activation_offload=self._want_activation_offload(), seed=seed, tp=tp)
         keep = os.environ.get("TDLLM_KEEP_ATTENTION")
         self.model.store.keep_attention = (keep == "1") if keep is not None else (
             self.model.store.offload or getattr(self, "_keep_attention_on_device", False))
@@ -107,7 +112,10 @@ class TrainingSession:
             self.ep_group = runtime.group("expert") if ep > 1 else None
         else:
             group = runtime.optimizer_group if runtime is not None else (dist.group.WORLD if self.world > 1 else None)
-            self.optimizer = FlatAdamW(self.model.flat, group=group, fused_sync=self._build_fused_sync(group), **okw)
+            tp_group = runtime.tensor_group if (runtime is not None and runtime.tensor_parallel_size > 1) else None
+            self.optimizer = FlatAdamW(self.model.flat, group=group, tp_group=tp_group,
+                                       fused_sync=None if tp_group is not None else self._build_fused_sync(group),
+                                       **okw)
         self.scheduler = RunSpecLRScheduler.from_run_spec(spec)
         self.steps_done = 0
 
@@ -180,8 +188,8 @@ class TrainingSession:
         if rt is not None and rt.context_parallel_size > 1:
             from ..parallel.context_attention import ContextParallelAttention
 
-            return ContextParallelAttention(self.cfg, self.layout, rt, self.spec)
-        return LocalAttention(self.cfg, self.layout.mask, store=self.model.store)
+            return ContextParallelAttention(getattr(self.model, "lcfg", self.cfg), self.layout, rt, self.spec)
+        return LocalAttention(getattr(self.model, "lcfg", self.cfg), self.layout.mask, store=self.model.store)
 
     def _build_fused_sync(self, group):
         if group is None or self.device.type != "cuda" or self.spec.kernel.impl in ("cpu_reference", "nccl_baseline"):
