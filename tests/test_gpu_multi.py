@@ -132,3 +132,43 @@ def test_csbp2_on_gpus_matches_single_gpu(transport):
     for losses, params in outs:
         assert losses == pytest.approx(ref[0], rel=3e-2)
         assert (torch.from_numpy(params) - torch.from_numpy(ref[1])).abs().max().item() < 3e-2
+
+
+def _tp(rank, world, tp, steps):
+    import os
+
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-hd128", "seq_len": 512, "dtype": "bf16"},
+        "objective": {"name": "fast_dllm_v2", "block_size": 32, "noise_schedule_epsilon": 0.1},
+        "training": {"batch_size": 2, "steps": steps},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1, "tensor_parallel_size": tp},
+        "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
+    rt = build_parallel_runtime(spec, device=f"cuda:{rank}", rank=rank, world_size=world) if world > 1 else None
+    s = TrainingSession(spec, device=f"cuda:{rank}", runtime=rt)
+    losses = []
+    for _ in range(steps):
+        r = s.step()
+        losses.append(float(r.loss_sum) / r.denominator)
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    return losses, s.optimizer.grad_norm(), s.model.flat.params["final_norm"].float().cpu()
+
+
+@pytest.mark.distributed
+def test_tp2_on_gpus_matches_single_gpu():
+    _need(2)
+    ref = run_ranks(_tp, 1, args=(1, 3), backend=None, deadline_s=300)[0]
+    outs = run_ranks(_tp, 2, args=(2, 3), backend="nccl", deadline_s=300)
+    for losses, norm, fnorm in outs:
+        assert losses == pytest.approx(ref[0], rel=3e-2)
+        assert norm == pytest.approx(ref[1], rel=5e-2)
+        assert (torch.from_numpy(fnorm) - torch.from_numpy(ref[2])).abs().max().item() < 2e-2

@@ -136,6 +136,8 @@ class DecoderLayer(nn.Module):
         epilogues of the O and down projections."""
         cfg, tp = self.cfg, self.tp
         tpg = tp.group if tp is not None and tp.size > 1 else None
+        if getattr(self, "lora", None) is not None:
+            return self._forward_lora(h, positions, inv_freq, attend)
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
         qkv = linear(copy_to_tensor_parallel(y, tpg), self.w_qkv)
         qkv = qk_norm_rope(qkv, positions, inv_freq, self.q_norm, self.k_norm, cfg.num_attention_heads,
@@ -145,6 +147,25 @@ class DecoderLayer(nn.Module):
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
         act = linear_swiglu(copy_to_tensor_parallel(y2, tpg), self.w_gate_up)
         return row_parallel_linear_residual(act, self.w_down, h, tp)
+
+    def _forward_lora(self, h, positions, inv_freq, attend):
+        """Same layer with low-rank updates on the adapted projections (single tensor-parallel rank)."""
+        from ..adapters.lora import lora_delta
+        from ..ops.activation import swiglu
+
+        cfg, st = self.cfg, self.lora
+
+        def proj(x, name):
+            out = linear(x, getattr(self, name))
+            pair = st.pair(self.idx, name)
+            return out if pair is None else out + lora_delta(x, pair[0], pair[1], st.scale, st.dropout)
+
+        y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
+        qkv = qk_norm_rope(proj(y, "w_qkv"), positions, inv_freq, self.q_norm, self.k_norm, cfg.num_attention_heads,
+                           cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
+        h = h + proj(attend(qkv, self.idx), "w_o")
+        y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
+        return h + proj(swiglu(proj(y2, "w_gate_up")), "w_down")
 
 
 class LocalAttention:
@@ -229,6 +250,8 @@ class BlockDiffusionTransformer(nn.Module):
         else:
             h = embedding(tokens, self.embed)
         positions = positions.to(torch.int32)
+        if torch.is_grad_enabled() and not h.requires_grad:
+            h = h.detach().requires_grad_(True)   # frozen embedding (adapters): keep the checkpoint chain alive
         for i, layer in enumerate(self.layers):
             if self.activation_checkpointing and torch.is_grad_enabled():
                 h = checkpointed_layer(layer, h, self.store, i, positions, self.inv_freq, attend)

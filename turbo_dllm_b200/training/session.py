@@ -81,6 +81,15 @@ class TrainingSession:
                 self.cfg, dtype=self.dtype, device=self.device,
                 activation_checkpointing=spec.training.activation_checkpointing,
                 activation_offload=self._want_activation_offload(), seed=seed, tp=tp)
+        self.lora = None
+        if spec.adapter.type == "lora":
+            from ..adapters.lora import apply_lora
+
+            if self.cfg.is_moe or getattr(self.model, "tp", None) is not None:
+                raise ValueError("LoRA adapters support dense models on one tensor-parallel rank")
+            self.lora = apply_lora(self.model, rank=spec.adapter.rank, alpha=spec.adapter.alpha,
+                                   dropout=spec.adapter.dropout, targets=spec.adapter.targets or ("attention", "mlp"),
+                                   seed=seed)
         keep = os.environ.get("TDLLM_KEEP_ATTENTION")
         self.model.store.keep_attention = (keep == "1") if keep is not None else (
             self.model.store.offload or getattr(self, "_keep_attention_on_device", False))
@@ -113,13 +122,16 @@ class TrainingSession:
         else:
             group = runtime.optimizer_group if runtime is not None else (dist.group.WORLD if self.world > 1 else None)
             tp_group = runtime.tensor_group if (runtime is not None and runtime.tensor_parallel_size > 1) else None
-            self.optimizer = FlatAdamW(self.model.flat, group=group, tp_group=tp_group,
+            self.optimizer = FlatAdamW(self.lora.flat if self.lora is not None else self.model.flat, group=group,
+                                       tp_group=tp_group,
                                        fused_sync=None if tp_group is not None else self._build_fused_sync(group),
                                        **okw)
         self.scheduler = RunSpecLRScheduler.from_run_spec(spec)
         self.steps_done = 0
 
     def flats(self):
+        if getattr(self, "lora", None) is not None:
+            return [self.lora.flat]
         out = [self.model.flat]
         if getattr(self.model, "flat_experts", None) is not None:
             out.append(self.model.flat_experts)
