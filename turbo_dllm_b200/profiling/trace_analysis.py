@@ -1,0 +1,126 @@
+"""Analysis of exported traces: kernel classes, per-operator and per-communication-label time
+and bytes, and exposed (not overlapped by compute) communication time.
+
+Works on Kineto chrome traces (`rank_*.trace.json[.gz]`) and on `nsys export --type sqlite` files.
+Kernels are classified by name into nccl / peer_comm / attention_fwd / attention_bwd / moe_transport /
+grouped_gemm / dense_gemm / optimizer / elementwise / other, using this package's kernel names and the
+usual library patterns. Communication labels follow `operator_trace.communication_label`.
+
+Counterpart of dllm_parallel/core/profiling/trace_analysis.py:28-602.
+"""
+from __future__ import annotations
+
+import gzip
+import json
+import re
+import sqlite3
+from collections import defaultdict
+
+from .operator_trace import parse_communication_label
+
+KERNEL_CLASSES = [
+    ("nccl", re.compile(r"nccl", re.I)),
+    ("peer_comm", re.compile(r"zero_reduce|zero_update|kv_gather|kv_scatter|barrier_kernel")),
+    ("attention_fwd", re.compile(r"attn_fwd|flash.*fwd|fmha.*fwd", re.I)),
+    ("attention_bwd", re.compile(r"attn_bwd|attn_delta|flash.*bwd|fmha.*bwd", re.I)),
+    ("moe_transport", re.compile(r"dispatch|combine|all_to_all|alltoall", re.I)),
+    ("grouped_gemm", re.compile(r"grouped", re.I)),
+    ("dense_gemm", re.compile(r"gemm_bf16|gemm|cutlass|cublas|sm100.*mma", re.I)),
+    ("optimizer", re.compile(r"adamw|sumsq", re.I)),
+    ("elementwise", re.compile(r"rmsnorm|swiglu|qk_norm_rope|colsum|ce_finalize|kl_rows|merge|elementwise", re.I)),
+]
+
+
+def classify_kernel(name: str) -> str:
+    for cls, pat in KERNEL_CLASSES:
+        if pat.search(name):
+            return cls
+    return "other"
+
+
+def _union_length(intervals) -> float:
+    total, end = 0.0, None
+    for s, e in sorted(intervals):
+        if end is None or s > end:
+            total += e - s
+            end = e
+        elif e > end:
+            total += e - end
+            end = e
+    return total
+
+
+def _subtract(a, b) -> float:
+    """Length of the union of intervals `a` not covered by the union of `b`."""
+    both = _union_length(list(a) + list(b))
+    return both - _union_length(b)
+
+
+def summarize(kernels: list[tuple[str, float, float]], ranges: list[tuple[str, float, float]]) -> dict:
+    """kernels / ranges: (name, start_us, end_us)."""
+    by_class = defaultdict(lambda: {"count": 0, "time_us": 0.0})
+    comm, compute = [], []
+    for name, s, e in kernels:
+        c = classify_kernel(name)
+        by_class[c]["count"] += 1
+        by_class[c]["time_us"] += e - s
+        (comm if c in ("nccl", "peer_comm", "moe_transport") else compute).append((s, e))
+    labels = defaultdict(lambda: {"count": 0, "time_us": 0.0, "input_bytes": 0, "logical_bytes": 0})
+    operators = defaultdict(lambda: {"count": 0, "time_us": 0.0})
+    for name, s, e in ranges:
+        info = parse_communication_label(name)
+        if info is not None:
+            key = f"{info.get('domain')}/{info.get('phase')}/{info.get('collective')}"
+            labels[key]["count"] += 1
+            labels[key]["time_us"] += e - s
+            labels[key]["input_bytes"] += int(info.get("input_bytes", 0))
+            labels[key]["logical_bytes"] += int(info.get("logical_bytes", 0))
+        elif name.startswith("dllm.operator.") or name.startswith("dllm.phase."):
+            operators[name]["count"] += 1
+            operators[name]["time_us"] += e - s
+    return {"kernel_classes": dict(by_class), "communication_labels": dict(labels), "operators": dict(operators),
+            "compute_time_us": _union_length(compute), "communication_time_us": _union_length(comm),
+            "exposed_communication_us": _subtract(comm, compute)}
+
+
+def analyze_kineto_trace(path: str) -> dict:
+    opener = gzip.open if path.endswith(".gz") else open
+    with opener(path, "rt") as f:
+        data = json.load(f)
+    events = data["traceEvents"] if isinstance(data, dict) else data
+    kernels, ranges = [], []
+    for ev in events:
+        if ev.get("ph") != "X":
+            continue
+        s, d = float(ev.get("ts", 0)), float(ev.get("dur", 0))
+        cat = str(ev.get("cat", ""))
+        if cat in ("kernel", "gpu_memcpy", "gpu_memset"):
+            kernels.append((ev.get("name", ""), s, s + d))
+        elif cat in ("user_annotation", "gpu_user_annotation", "cpu_op") and str(ev.get("name", "")).startswith("dllm."):
+            ranges.append((ev["name"], s, s + d))
+    return summarize(kernels, ranges)
+
+
+def analyze_nsys_sqlite(path: str) -> dict:
+    con = sqlite3.connect(path)
+    try:
+        cur = con.cursor()
+        names = dict(cur.execute("SELECT id, value FROM StringIds"))
+        kernels = [(names.get(n, str(n)), s / 1e3, e / 1e3) for n, s, e in
+                   cur.execute("SELECT demangledName, start, end FROM CUPTI_ACTIVITY_KIND_KERNEL")]
+        ranges = []
+        try:
+            for text, tid, s, e in cur.execute("SELECT text, textId, start, end FROM NVTX_EVENTS WHERE end IS NOT NULL"):
+                label = text if text is not None else names.get(tid, "")
+                if label and label.startswith("dllm."):
+                    ranges.append((label, s / 1e3, e / 1e3))
+        except sqlite3.Error:
+            pass
+    finally:
+        con.close()
+    return summarize(kernels, ranges)
+
+
+def write_summary(summary: dict, path: str) -> None:
+    with open(path, "w") as f:
+        json.dump(summary, f, indent=1, sort_keys=True)

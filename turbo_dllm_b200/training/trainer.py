@@ -28,6 +28,9 @@ from ..profiling.perf import (block_diffusion_pairs, hardware_peak_tflops, model
 from . import checkpointing as ckpt_policy
 from .fault_tolerance import install_fault_handlers, write_fatal_marker
 from .session import TrainingSession
+from ..profiling.system_trace import SystemTrace
+from .metrics import WandBRunLogger
+from .token_accounting import TokenCounters, collect_run_context
 
 
 def emit(event: dict) -> None:
@@ -114,6 +117,10 @@ def run_training(spec: RunSpec) -> dict:
                   "layout": runtime.plan.layout if runtime else "dp", "resume_step": start_step,
                   "config": spec.to_dict()})
         readback = AsyncLossReadback(device, world)
+        wb = WandBRunLogger(spec, rank)
+        counters = TokenCounters()
+        trace = SystemTrace.from_run_spec(spec, rank, barrier=(dist.barrier if world > 1 else None))
+        run_ctx = collect_run_context(world)
         timed_ms: list[float] = []
         t_train0 = time.monotonic()
         dp = session.dp_size
@@ -124,11 +131,17 @@ def run_training(spec: RunSpec) -> dict:
             if use_cuda:
                 torch.cuda.reset_peak_memory_stats(device)
             t0 = time.perf_counter()
+            trace.begin_step(step)
             res = session.step()
             readback.enqueue(res.loss_sum, int(res.supervised_rows))
             if use_cuda:
                 torch.cuda.synchronize(device)
             ms = (time.perf_counter() - t0) * 1e3
+            trace.end_step(step)
+            if use_cuda:
+                from ..kernels import native
+
+                native.raise_on_device_error()   # bounded device waits report here instead of hanging
             loss_sum, rows = readback.resolve()
             last_loss = loss_sum / res.denominator
             if last_loss != last_loss or abs(last_loss) == float("inf"):
@@ -136,8 +149,9 @@ def run_training(spec: RunSpec) -> dict:
             timed = step - start_step > spec.profiler.warmup_steps
             if timed:
                 timed_ms.append(ms)
+            counters.add(input_tokens=tokens_per_step, supervised_tokens=float(res.denominator), active_tokens=rows)
             if rank == 0:
-                emit({"event": "step", "step": step, "completed_steps": step, "target_total_steps": total_steps,
+                ev = ({"event": "step", "step": step, "completed_steps": step, "target_total_steps": total_steps,
                       "timed": timed, "loss": last_loss, "lr": session.scheduler.lr_at(session.scheduler.step_count),
                       "grad_norm": session.optimizer.grad_norm(), "gradient_clip_norm": spec.optimizer.gradient_clip_norm,
                       "ms": ms, "active_tokens": rows, "valid_tokens": res.denominator, "input_tokens": tokens_per_step,
@@ -147,6 +161,8 @@ def run_training(spec: RunSpec) -> dict:
                       "gradient_accumulation_steps": spec.training.gradient_accumulation_steps,
                       "optimizer_backend": "zero_fused" if session.optimizer.fused_sync else "flat_adamw",
                       "peak_mib": (torch.cuda.max_memory_allocated(device) / 2 ** 20) if use_cuda else None})
+                emit(ev)
+                wb.log_event(ev)
             elapsed = time.monotonic() - t_train0
             if ckpt_policy.should_save(spec, step, total_steps, elapsed):
                 from ..checkpoint import save_training_checkpoint
@@ -164,9 +180,14 @@ def run_training(spec: RunSpec) -> dict:
             t = torch.tensor([mean_ms], dtype=torch.float64, device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             mean_ms = float(t)
+        eval_metrics = {}
+        if spec.evaluation.batches > 0:
+            from .evaluation import evaluate_masked_token_accuracy
+
+            eval_metrics = evaluate_masked_token_accuracy(session, spec.evaluation.batches, spec.evaluation.seed)
         summary = {}
         if rank == 0:
-            views = session.objective.views
+            views = getattr(session.objective, "views", 1)
             gb = spec.global_batch(dp)
             fl = transformer_step_flops(
                 session.cfg, rows=(views + 1) * spec.model.seq_len * gb,
@@ -185,8 +206,12 @@ def run_training(spec: RunSpec) -> dict:
                        "input_tokens_per_second": tokens_per_step / (mean_ms / 1e3) if mean_ms == mean_ms else None,
                        "model_tflop_per_step": fl.total / 1e12, "mfu_pct": mfu, "world_size": world,
                        "parallel_layout": runtime.plan.layout if runtime else "dp",
-                       "training_elapsed_seconds": time.monotonic() - t_train0}
+                       "training_elapsed_seconds": time.monotonic() - t_train0, "run_context": run_ctx.to_dict(),
+                       "system_trace": trace.exported, **eval_metrics,
+                       **counters.throughput(sum(timed_ms) / 1e3, world)}
             emit(summary)
+            wb.log_event(summary)
+        wb.finish()
         return summary
     except Exception as e:
         info = {"event": "fatal_exception", "rank": rank, "error": f"{type(e).__name__}: {e}",
