@@ -1,0 +1,165 @@
+import gzip
+import json
+
+import pytest
+import torch
+
+
+def test_release_gates_pass_on_this_tree():
+    from turbo_dllm_b200.profiling.release_gates import run_gates
+
+    res = run_gates()
+    assert all(r.ok for r in res), [(r.name, r.detail) for r in res if not r.ok]
+
+
+def test_communication_labels_roundtrip_and_trace_summary(tmp_path):
+    from turbo_dllm_b200.profiling.operator_trace import communication_label, parse_communication_label
+    from turbo_dllm_b200.profiling.trace_analysis import analyze_kineto_trace, classify_kernel
+
+    lab = communication_label("context_parallel", "forward", "all_gather", 1024, 8192)
+    assert parse_communication_label(lab) == {"domain": "context_parallel", "phase": "forward",
+                                              "collective": "all_gather", "input_bytes": 1024, "logical_bytes": 8192}
+    assert classify_kernel("tdllm::gemm_bf16_kernel(...)") == "dense_gemm"
+    assert classify_kernel("attn_dkv::attn_bwd_dkv_kernel") == "attention_bwd"
+    assert classify_kernel("ncclDevKernel_AllGather_RING_LL") == "nccl"
+    events = [{"ph": "X", "cat": "kernel", "name": "tdllm::gemm_bf16_kernel", "ts": 0, "dur": 100},
+              {"ph": "X", "cat": "kernel", "name": "ncclDevKernel_AllGather", "ts": 50, "dur": 100},
+              {"ph": "X", "cat": "user_annotation", "name": lab, "ts": 50, "dur": 100}]
+    p = tmp_path / "rank_0.trace.json.gz"
+    with gzip.open(p, "wt") as f:
+        json.dump({"traceEvents": events}, f)
+    s = analyze_kineto_trace(str(p))
+    assert s["exposed_communication_us"] == 50.0
+    assert s["communication_labels"]["context_parallel/forward/all_gather"]["logical_bytes"] == 8192
+
+
+def test_scopes_are_inert_outside_a_trace_window():
+    import contextlib
+
+    from turbo_dllm_b200.profiling.operator_trace import communication_scope, operator_scope
+
+    assert isinstance(operator_scope("x"), contextlib.nullcontext)
+    assert isinstance(communication_scope("a", "b", "c"), contextlib.nullcontext)
+
+
+def test_wandb_sanitising_and_fake_module():
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.training.metrics import WandBRunLogger, sanitize_wandb_id, sanitize_wandb_tags
+
+    assert sanitize_wandb_id(" my run/№1 ") == "my-run-1"
+    assert sanitize_wandb_tags(["a b", "a b", "", "x"]) == ["a-b", "x"]
+
+    class Run:
+        def __init__(self):
+            self.logged, self.finished = [], False
+
+        def log(self, payload, step=None):
+            self.logged.append((step, payload))
+
+        def finish(self, exit_code=0):
+            self.finished = True
+
+    class Fake:
+        def __init__(self):
+            self.kw, self.run = None, Run()
+
+        def init(self, **kw):
+            self.kw = kw
+            return self.run
+
+    spec = RunSpec.from_mapping({"logging": {"wandb": True, "wandb_mode": "offline", "wandb_tags": ["t 1"],
+                                             "wandb_id": "id!"}})
+    fake = Fake()
+    lg = WandBRunLogger(spec, 0, module=fake)
+    lg.log_event({"event": "step", "step": 3, "loss": 1.5, "perf": {"tps": 10.0}, "note": "x"})
+    lg.finish()
+    assert fake.kw["tags"] == ["t-1"] and fake.kw["id"] == "id"
+    assert fake.run.logged == [(3, {"step/step": 3, "step/loss": 1.5, "step/perf/tps": 10.0})] and fake.run.finished
+    assert WandBRunLogger(spec, 1, module=fake).run is None
+
+
+def test_bundle_catalog_selection_and_hash_check(tmp_path):
+    from turbo_dllm_b200.kernels import bundle_manifest as bm
+
+    wheel = tmp_path / "turbo_dllm_b200-0.1.0-cp312-linux_x86_64.whl"
+    wheel.write_bytes(b"not really a wheel")
+    env = {"python": "cp312", "cuda": "128", "arch": "sm100"}
+    cat = {"format": bm.CATALOG_FORMAT, "bundles": [{"key": bm.bundle_key(env), "assets": [
+        {"name": wheel.name, "url": str(wheel), "sha256": bm._sha256(str(wheel))}]}]}
+    path = tmp_path / "catalog.json"
+    path.write_text(json.dumps(cat))
+    b = bm.select_bundle(bm.load_catalog(str(path)), env)
+    out = bm.fetch_asset(b["assets"][0], str(tmp_path / "dl") if (tmp_path / "dl").mkdir() is None else "")
+    assert out.endswith(".whl")
+    b["assets"][0]["sha256"] = "0" * 64
+    with pytest.raises(bm.BundleError, match="sha256"):
+        bm.fetch_asset(b["assets"][0], str(tmp_path / "dl"))
+    with pytest.raises(bm.BundleError, match="no bundle"):
+        bm.select_bundle(cat, {"python": "cp39", "cuda": "118", "arch": "sm80"})
+
+
+def test_hf_export_and_reload_roundtrip(tmp_path):
+    from turbo_dllm_b200.models.config import PRESETS
+    from turbo_dllm_b200.models.dense import BlockDiffusionTransformer
+    from turbo_dllm_b200.models.hf_loader import export_hf_checkpoint, load_hf_config, load_hf_weights
+
+    cfg = PRESETS["synthetic:tiny-qwen3"]
+    a = BlockDiffusionTransformer(cfg, dtype=torch.float32, seed=5)
+    export_hf_checkpoint(a, str(tmp_path / "hf"))
+    cfg2 = load_hf_config(str(tmp_path / "hf"))
+    assert cfg2.hidden_size == cfg.hidden_size and cfg2.num_key_value_heads == cfg.num_key_value_heads and cfg2.qk_norm
+    b = BlockDiffusionTransformer(cfg2, dtype=torch.float32, seed=99)
+    load_hf_weights(b, str(tmp_path / "hf"))
+    assert torch.equal(a.flat.data, b.flat.data)
+
+
+def test_serving_command_builders_and_acceptance_parsing():
+    from turbo_dllm_b200.serving import dflash_servers as srv
+
+    cmd = srv.build_vllm_command(target_model="T", draft_export="D", num_speculative_tokens=7)
+    assert cmd[:3] == ["vllm", "serve", "T"] and json.loads(cmd[4])["num_speculative_tokens"] == 7
+    assert "--speculative-draft-model-path" in srv.build_sglang_command(target_model="T", draft_export="D")
+    assert srv.parse_acceptance_length("vllm:spec_decode_mean_acceptance_length 2.75\n") == 2.75
+    txt = "spec_decode_num_accepted_tokens_total 30\nspec_decode_num_drafts_total 20\n"
+    assert srv.parse_acceptance_length(txt) == 2.5
+    res = srv.verify_acceptance("http://x", "m", ["p"], 2.0, post=lambda u, p: {}, fetch_metrics=lambda: txt)
+    assert res["ok"] and res["acceptance_length"] == 2.5
+
+
+def test_fault_marker_and_doctor(tmp_path):
+    from turbo_dllm_b200.diagnostics import inspect_training_runtime
+    from turbo_dllm_b200.training.fault_tolerance import fatal_marker_path, write_fatal_marker
+
+    p = write_fatal_marker(str(tmp_path), 3, {"event": "fatal_exception", "error": "boom"})
+    assert p == fatal_marker_path(str(tmp_path), 3) and p.endswith("fatal_rank_00003.json")
+    assert json.load(open(p))["error"] == "boom"
+    rep = inspect_training_runtime(portable_only=True)
+    assert rep.ready and any(c.name == "torch" for c in rep.checks)
+
+
+def test_launch_command_and_environment(tmp_path):
+    import argparse
+
+    from turbo_dllm_b200.cli.launch import (add_launch_arguments, build_launch_command, build_launch_environment,
+                                            parse_nnodes, require_idle_assigned_gpus)
+    from turbo_dllm_b200.config.run_spec import RunSpecError
+
+    ap = argparse.ArgumentParser()
+    add_launch_arguments(ap)
+    a = ap.parse_args(["--config", "t.yaml", "--nproc-per-node", "8", "--max-restarts", "2"])
+    cmd = build_launch_command(a, "t.yaml", ["--steps", "5"])
+    assert "torch.distributed.run" in cmd and "--nproc-per-node=8" in cmd and "--max-restarts=2" in cmd
+    assert cmd[-4:] == ["--config", "t.yaml", "--steps", "5"]
+    a1 = ap.parse_args(["--config", "t.yaml"])
+    assert build_launch_command(a1, "t.yaml", [])[1:3] == ["-m", "turbo_dllm_b200.training"]
+    with pytest.raises(RunSpecError, match="rdzv"):
+        build_launch_command(ap.parse_args(["--config", "t.yaml", "--nnodes", "1:2"]), "t.yaml", [])
+    assert parse_nnodes("2:4") == (2, 4)
+    env = build_launch_environment(ap.parse_args(["--config", "t", "--run-dir", str(tmp_path)]), base_env={})
+    assert env["DLLM_RUN_DIR"] == str(tmp_path) and env["PYTORCH_CUDA_ALLOC_CONF"] == "expandable_segments:True"
+
+    class R:
+        returncode, stdout, stderr = 0, "GPU-1, 123, 400 MiB\n", ""
+
+    with pytest.raises(RunSpecError, match="not idle"):
+        require_idle_assigned_gpus(1, command_runner=lambda cmd: R())

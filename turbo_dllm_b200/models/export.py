@@ -1,0 +1,144 @@
+"""Export CLIs: merged Hugging Face checkpoints from training checkpoints (dense and MoE models,
+LoRA adapters folded in), and DFlash drafter exports for speculative-decoding servers.
+
+`dllm-export-diffusiongemma --checkpoint DIR --config train.yaml --output OUT` rebuilds the model
+from the run spec, loads rank 0's shard and writes `OUT/config.json` + safetensors plus an
+`export_manifest.json` with SHA-256 of every file. The DFlash export adds `dflash_config.json`
+(block size, target layer ids, mask token id, draft vocabulary) next to the drafter weights.
+
+Counterparts: dllm_parallel/core/models/backbones/diffusiongemma/export.py:63-449, :1130 (CLI);
+dllm_parallel/core/models/backbones/dflash/executor.py:412-566 (speculators / SGLang export + validation).
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import json
+import os
+import sys
+
+import torch
+
+
+def _sha(path):
+    h = hashlib.sha256()
+    with open(path, "rb") as f:
+        for c in iter(lambda: f.read(1 << 20), b""):
+            h.update(c)
+    return h.hexdigest()
+
+
+def write_export_manifest(out: str, extra: dict | None = None) -> dict:
+    files = {f: {"bytes": os.path.getsize(os.path.join(out, f)), "sha256": _sha(os.path.join(out, f))}
+             for f in sorted(os.listdir(out)) if f != "export_manifest.json"}
+    man = {"format": "turbo_dllm_b200.export.v1", "files": files, **(extra or {})}
+    json.dump(man, open(os.path.join(out, "export_manifest.json"), "w"), indent=1, sort_keys=True)
+    return man
+
+
+def export_training_checkpoint(spec, checkpoint_dir: str, output: str, tag: str = "latest") -> dict:
+    from ..checkpoint import load_training_checkpoint
+    from ..training.session import TrainingSession
+    from .hf_loader import export_hf_checkpoint
+
+    session = TrainingSession(spec, device="cpu" if spec.model.dtype == "fp32" or not torch.cuda.is_available()
+                              else "cuda")
+    meta = load_training_checkpoint(checkpoint_dir, tag, session, rank=0, world_size=1, restore_rng=False)
+    if session.cfg.is_moe:
+        export_moe_checkpoint(session.model, output)
+    else:
+        export_hf_checkpoint(session.model, output)
+    return write_export_manifest(output, {"step": meta["step"], "source_checkpoint": os.path.abspath(checkpoint_dir)})
+
+
+@torch.no_grad()
+def export_moe_checkpoint(model, path: str) -> str:
+    """Dense parts in HF naming, experts as `model.layers.i.mlp.experts.{e}.{gate,up,down}_proj.weight`."""
+    from safetensors.torch import save_file
+
+    from .hf_loader import deinterleave_gate_up, hf_config_dict
+
+    cfg = model.cfg
+    os.makedirs(path, exist_ok=True)
+    out = {"model.embed_tokens.weight": model.embed, "model.norm.weight": model.final_norm}
+    if not cfg.tie_word_embeddings:
+        out["lm_head.weight"] = model.lm_head
+    for i, layer in enumerate(model.layers):
+        p = f"model.layers.{i}."
+        qd, kd = cfg.q_dim, cfg.kv_dim
+        out[p + "self_attn.q_proj.weight"], out[p + "self_attn.k_proj.weight"] = layer.w_qkv[:qd], layer.w_qkv[qd:qd + kd]
+        out[p + "self_attn.v_proj.weight"], out[p + "self_attn.o_proj.weight"] = layer.w_qkv[qd + kd:], layer.w_o
+        out[p + "input_layernorm.weight"], out[p + "post_attention_layernorm.weight"] = layer.input_norm, layer.post_norm
+        if layer.q_norm is not None:
+            out[p + "self_attn.q_norm.weight"], out[p + "self_attn.k_norm.weight"] = layer.q_norm, layer.k_norm
+        out[p + "mlp.router.weight"] = layer.experts.router
+        for e in range(layer.experts.w_gu.shape[0]):
+            g, u = deinterleave_gate_up(layer.experts.w_gu[e])
+            q = p + f"mlp.experts.{e}."
+            out[q + "gate_proj.weight"], out[q + "up_proj.weight"], out[q + "down_proj.weight"] = g, u, layer.experts.w_down[e]
+    save_file({k: v.detach().cpu().contiguous() for k, v in out.items()}, os.path.join(path, "model.safetensors"))
+    c = hf_config_dict(cfg)
+    c.update({"num_experts": cfg.num_experts, "num_experts_per_tok": cfg.num_experts_per_token,
+              "moe_intermediate_size": cfg.moe_intermediate_size, "model_type": "turbo_dllm_moe"})
+    json.dump(c, open(os.path.join(path, "config.json"), "w"), indent=1)
+    return path
+
+
+@torch.no_grad()
+def export_dflash_drafter(draft_model, spec, path: str) -> dict:
+    """Drafter weights (flat parameter names) + dflash_config.json for SGLang / vLLM draft loading."""
+    from safetensors.torch import save_file
+
+    os.makedirs(path, exist_ok=True)
+    tensors = {name: p.detach().cpu().contiguous() for name, p in draft_model.flat.params.items()}
+    save_file(tensors, os.path.join(path, "model.safetensors"))
+    cfg = draft_model.cfg
+    json.dump({"architectures": ["DFlashDraftModel"], "model_type": "dflash", "hidden_size": cfg.hidden_size,
+               "num_hidden_layers": cfg.num_layers, "num_attention_heads": cfg.num_attention_heads,
+               "num_key_value_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+               "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,
+               "block_size": spec.objective.block_size, "target_layer_ids": list(spec.model.target_layer_ids),
+               "conditioning_dim": draft_model.conditioning_dim, "mask_token_id": cfg.mask_token_id,
+               "verifier": spec.model.verifier_id, "gate_up_layout": "interleaved"},
+              open(os.path.join(path, "dflash_config.json"), "w"), indent=1)
+    return write_export_manifest(path, {"kind": "dflash_drafter"})
+
+
+def validate_dflash_export(path: str) -> list[str]:
+    problems = []
+    for f in ("model.safetensors", "dflash_config.json", "export_manifest.json"):
+        if not os.path.exists(os.path.join(path, f)):
+            problems.append(f"missing {f}")
+    if problems:
+        return problems
+    man = json.load(open(os.path.join(path, "export_manifest.json")))
+    for f, meta in man["files"].items():
+        if _sha(os.path.join(path, f)) != meta["sha256"]:
+            problems.append(f"{f}: sha256 mismatch")
+    cfg = json.load(open(os.path.join(path, "dflash_config.json")))
+    for k in ("block_size", "target_layer_ids", "conditioning_dim", "mask_token_id"):
+        if cfg.get(k) in (None, []):
+            problems.append(f"dflash_config.json lacks {k}")
+    return problems
+
+
+def main(argv=None) -> int:
+    from ..config.run_spec import RunSpecError, load_run_spec
+
+    ap = argparse.ArgumentParser(prog="dllm-export-diffusiongemma")
+    ap.add_argument("--config", required=True)
+    ap.add_argument("--checkpoint", required=True)
+    ap.add_argument("--output", required=True)
+    ap.add_argument("--tag", default="latest")
+    a = ap.parse_args(argv)
+    try:
+        man = export_training_checkpoint(load_run_spec(a.config).validate(), a.checkpoint, a.output, a.tag)
+    except (RunSpecError, FileNotFoundError, ValueError) as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 2
+    print(json.dumps({"output": a.output, "files": sorted(man["files"])}))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,146 @@
+"""Hugging Face interchange: read a local model directory into this package's decoder and write
+one back (config.json + safetensors), for dense Qwen3-style checkpoints.
+
+Name mapping (per layer i):
+  self_attn.{q,k,v}_proj.weight → rows of `w_qkv` in that order     self_attn.o_proj.weight → `w_o`
+  self_attn.{q,k}_norm.weight   → `q_norm` / `k_norm`               input_layernorm / post_attention_layernorm
+  mlp.gate_proj / mlp.up_proj   → `w_gate_up`, rows interleaved (g0,u0,g1,u1,…) so the GEMM epilogue can
+                                   apply SwiGLU;                     mlp.down_proj → `w_down`
+  model.embed_tokens, lm_head, model.norm → `embed`, `lm_head`, `final_norm`
+`max_layers` truncates; tensor-parallel ranks load their slice of each matrix.
+
+Counterparts: dllm_parallel/core/models/hf_loader.py:50-210 (config + weights through transformers) and the
+export side of dllm_parallel/core/models/backbones/qwen3_8/export.py:70-512.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+from .config import ModelConfig
+
+
+def load_hf_config(path: str, max_layers: int | None = None) -> ModelConfig:
+    cfg_path = os.path.join(path, "config.json")
+    if not os.path.exists(cfg_path):
+        raise FileNotFoundError(f"{path} has no config.json (model loading works from local directories)")
+    c = json.load(open(cfg_path))
+    heads = c["num_attention_heads"]
+    layers = c["num_hidden_layers"]
+    if max_layers is not None:
+        layers = min(layers, max_layers)
+    arch = " ".join(c.get("architectures", []))
+    return ModelConfig(
+        vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], num_layers=layers, num_attention_heads=heads,
+        num_key_value_heads=c.get("num_key_value_heads", heads), head_dim=c.get("head_dim", c["hidden_size"] // heads),
+        intermediate_size=c["intermediate_size"], rope_theta=float(c.get("rope_theta", 1e6)),
+        rms_norm_eps=float(c.get("rms_norm_eps", 1e-6)), qk_norm="Qwen3" in arch or bool(c.get("qk_norm", False)),
+        tie_word_embeddings=bool(c.get("tie_word_embeddings", False)), mask_token_id=c.get("mask_token_id"))
+
+
+def hf_config_dict(cfg: ModelConfig) -> dict:
+    return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": cfg.vocab_size,
+            "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
+            "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "intermediate_size": cfg.intermediate_size, "rope_theta": cfg.rope_theta,
+            "rms_norm_eps": cfg.rms_norm_eps, "tie_word_embeddings": cfg.tie_word_embeddings,
+            "mask_token_id": cfg.mask_token_id, "hidden_act": "silu", "torch_dtype": "bfloat16"}
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    return torch.stack([gate, up], dim=1).reshape(2 * gate.shape[0], gate.shape[1])
+
+
+def deinterleave_gate_up(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    return w[0::2].contiguous(), w[1::2].contiguous()
+
+
+def _open_weights(path: str) -> dict:
+    from safetensors import safe_open
+
+    index = os.path.join(path, "model.safetensors.index.json")
+    files = sorted(set(json.load(open(index))["weight_map"].values())) if os.path.exists(index) else \
+        [f for f in sorted(os.listdir(path)) if f.endswith(".safetensors")]
+    if not files:
+        raise FileNotFoundError(f"{path} has no .safetensors weights")
+    handles = [safe_open(os.path.join(path, f), framework="pt", device="cpu") for f in files]
+    table = {}
+    for h in handles:
+        for k in h.keys():
+            table[k] = h
+    return table
+
+
+@torch.no_grad()
+def load_hf_weights(model, path: str) -> None:
+    """Fills `model` (a dense BlockDiffusionTransformer, possibly tensor-parallel) from `path`."""
+    table = _open_weights(path)
+    cfg, tp = model.cfg, model.tp
+
+    def get(name):
+        if name not in table:
+            raise KeyError(f"checkpoint lacks {name}")
+        return table[name].get_tensor(name)
+
+    def put(param, tensor):
+        param.copy_(tensor.to(param.device, param.dtype))
+
+    def shard(t, dim):
+        return tp.shard(t, dim) if tp is not None else t
+
+    put(model.embed, shard(get("model.embed_tokens.weight"), 0))
+    put(model.final_norm, get("model.norm.weight"))
+    if not cfg.tie_word_embeddings:
+        name = "lm_head.weight" if "lm_head.weight" in table else "model.embed_tokens.weight"
+        put(model.lm_head, shard(get(name), 0))
+    for i, layer in enumerate(model.layers):
+        p = f"model.layers.{i}."
+        q, k, v = (get(p + f"self_attn.{n}_proj.weight") for n in "qkv")
+        put(layer.w_qkv, torch.cat([shard(q, 0), shard(k, 0), shard(v, 0)], dim=0))
+        put(layer.w_o, shard(get(p + "self_attn.o_proj.weight"), 1))
+        put(layer.input_norm, get(p + "input_layernorm.weight"))
+        put(layer.post_norm, get(p + "post_attention_layernorm.weight"))
+        if layer.q_norm is not None:
+            put(layer.q_norm, get(p + "self_attn.q_norm.weight"))
+            put(layer.k_norm, get(p + "self_attn.k_norm.weight"))
+        put(layer.w_gate_up, interleave_gate_up(shard(get(p + "mlp.gate_proj.weight"), 0),
+                                                shard(get(p + "mlp.up_proj.weight"), 0)))
+        put(layer.w_down, shard(get(p + "mlp.down_proj.weight"), 1))
+
+
+@torch.no_grad()
+def export_hf_checkpoint(model, path: str, merge_adapters: bool = True) -> str:
+    """Writes config.json + model.safetensors in Hugging Face naming (single tensor-parallel rank)."""
+    from safetensors.torch import save_file
+
+    if model.tp is not None:
+        raise ValueError("export from a tensor-parallel model: gather the shards first")
+    if merge_adapters and getattr(model, "lora", None) is not None:
+        from ..adapters.lora import merge_lora
+
+        merge_lora(model)
+    cfg = model.cfg
+    os.makedirs(path, exist_ok=True)
+    out = {"model.embed_tokens.weight": model.embed, "model.norm.weight": model.final_norm}
+    if not cfg.tie_word_embeddings:
+        out["lm_head.weight"] = model.lm_head
+    for i, layer in enumerate(model.layers):
+        p = f"model.layers.{i}."
+        qd, kd = cfg.q_dim, cfg.kv_dim
+        out[p + "self_attn.q_proj.weight"] = layer.w_qkv[:qd]
+        out[p + "self_attn.k_proj.weight"] = layer.w_qkv[qd:qd + kd]
+        out[p + "self_attn.v_proj.weight"] = layer.w_qkv[qd + kd:]
+        out[p + "self_attn.o_proj.weight"] = layer.w_o
+        out[p + "input_layernorm.weight"] = layer.input_norm
+        out[p + "post_attention_layernorm.weight"] = layer.post_norm
+        if layer.q_norm is not None:
+            out[p + "self_attn.q_norm.weight"] = layer.q_norm
+            out[p + "self_attn.k_norm.weight"] = layer.k_norm
+        g, u = deinterleave_gate_up(layer.w_gate_up)
+        out[p + "mlp.gate_proj.weight"], out[p + "mlp.up_proj.weight"] = g, u
+        out[p + "mlp.down_proj.weight"] = layer.w_down
+    save_file({k: v.detach().cpu().contiguous() for k, v in out.items()}, os.path.join(path, "model.safetensors"))
+    json.dump(hf_config_dict(cfg), open(os.path.join(path, "config.json"), "w"), indent=1)
+    return path
