@@ -90,7 +90,7 @@ def run_ours(args):
         for _ in range(steps):
             r = session.step()
             if read_loss:
-                loss = float(r.loss_sum) / r.denominator      # device -> host every step
+                loss = float(r.loss_sum) / r.denominator * world   # device -> host every step (rank-local part)
                 d2h = r.loss_sum.element_size()
         stop.record()
         barrier()
@@ -98,7 +98,10 @@ def run_ours(args):
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         if loss is None:
-            loss = float(r.loss_sum) / r.denominator
+            t = r.loss_sum.double().clone()
+            if world > 1:
+                dist.all_reduce(t)
+            loss = float(t) / r.denominator
         return float(ms) / steps, loss, native.LAUNCHES["kernels"], r, d2h
 
     session = TrainingSession(spec, device=f"cuda:{local_rank}")

@@ -75,3 +75,20 @@ def test_swiglu():
     ref.backward(g.float())
     assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
     assert torch.allclose(gu.grad.float(), r.grad, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("views,shift", [(1, False), (2, True)])
+def test_noising_kernel_matches_host_twin(views, shift):
+    from turbo_dllm_b200.objectives.runtime import fused_corrupt
+
+    torch.manual_seed(0)
+    B, L, bs = 3, 256, 32
+    x0 = torch.randint(0, 1000, (B, L), device="cuda")
+    t = torch.rand(B, L // bs, device="cuda") * 0.9 + 0.1
+    el = torch.rand(B, L, device="cuda") > 0.2
+    kw = dict(block_size=bs, views=views, shift=shift, mask_id=1023, seed=0x1234567890ABCDEF, offset=7)
+    xt, lab = fused_corrupt(x0, t, el, **kw)
+    xt_ref, lab_ref = fused_corrupt(x0.cpu(), t.cpu(), el.cpu(), **kw)
+    assert torch.equal(xt.cpu(), xt_ref) and torch.equal(lab.cpu(), lab_ref)
+    frac = (xt == 1023).float().mean().item()
+    assert 0.2 < frac < 0.8

@@ -124,7 +124,7 @@ def _csbp(rank, world, transport, steps):
 
 
 @pytest.mark.distributed
-@pytest.mark.parametrize("transport", ["collective", "peer_pull"])
+@pytest.mark.parametrize("transport", ["collective", "peer_pull", "streaming"])
 def test_csbp2_on_gpus_matches_single_gpu(transport):
     _need(2)
     ref = run_ranks(_csbp, 1, args=("collective", 3), backend=None, deadline_s=300)[0]

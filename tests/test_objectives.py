@@ -1,0 +1,90 @@
+import pytest
+import torch
+
+from turbo_dllm_b200.objectives.dflash import DFlashObjectiveRuntime, document_starts, reference_dflash_loss
+from turbo_dllm_b200.objectives.runtime import FastDLLMv2Runtime, StandardBlockDiffusionRuntime
+
+KW = dict(block_size=8, mask_token_id=99, max_seq_len=64, seed=11)
+
+
+def test_standard_corruption_rules_and_determinism():
+    rt = StandardBlockDiffusionRuntime(sampling_epsilon_min=0.1, **KW)
+    x0 = torch.randint(0, 90, (3, 64))
+    cb = rt.corrupt(x0)
+    assert cb.noisy_input_ids.shape == (3, 1, 64) and cb.loss_weights.shape == (3, 1, 8)
+    m = cb.noisy_input_ids[:, 0] == 99
+    assert torch.equal(cb.labels[:, 0][m], x0[m]) and (cb.labels[:, 0][~m] == -100).all()
+    assert torch.equal(cb.noisy_input_ids[:, 0][~m], x0[~m])
+    assert torch.allclose(cb.loss_weights[:, 0], 1.0 / cb.diffusion_times)
+    assert (cb.diffusion_times >= 0.1).all() and (cb.diffusion_times <= 1.0).all()
+    assert cb.valid_tokens == 192 and int(cb.active_tokens) == int(m.sum())
+    # antithetic strata: sorted times are evenly spaced by 1/N of the sampling range
+    ts = ((cb.diffusion_times.flatten() - 0.1) / 0.9).sort().values
+    assert torch.allclose(ts[1:] - ts[:-1], torch.full((23,), 1 / 24), atol=1e-5)
+    rt2 = StandardBlockDiffusionRuntime(sampling_epsilon_min=0.1, **KW)
+    assert torch.equal(rt2.corrupt(x0).noisy_input_ids, cb.noisy_input_ids)
+    assert not torch.equal(rt2.corrupt(x0).noisy_input_ids, cb.noisy_input_ids)
+
+
+def test_state_dict_roundtrip_resumes_the_stream():
+    a = StandardBlockDiffusionRuntime(**KW)
+    x0 = torch.randint(0, 90, (2, 64))
+    a.corrupt(x0)
+    st = a.state_dict()
+    want = a.corrupt(x0).noisy_input_ids
+    b = StandardBlockDiffusionRuntime(**KW)
+    b.load_state_dict(st)
+    assert torch.equal(b.corrupt(x0).noisy_input_ids, want)
+    with pytest.raises(ValueError):
+        FastDLLMv2Runtime(**KW).load_state_dict(st)
+
+
+def test_fast_dllm_v2_complementary_views_and_shifted_labels():
+    rt = FastDLLMv2Runtime(noise_schedule_epsilon=0.1, **KW)
+    x0 = torch.randint(0, 90, (2, 64))
+    cb = rt.corrupt(x0)
+    a, b = cb.noisy_input_ids[:, 0] == 99, cb.noisy_input_ids[:, 1] == 99
+    assert (a ^ b).all()                                   # every position masked in exactly one view
+    assert cb.valid_tokens == 2 * 63 and cb.loss_denominator == 126.0
+    assert (cb.labels[:, :, -1] == -100).all()
+    for v, m in enumerate((a, b)):
+        lab = cb.labels[:, v, :-1]
+        assert torch.equal(lab[m[:, 1:]], x0[:, 1:][m[:, 1:]]) and (lab[~m[:, 1:]] == -100).all()
+    assert int(cb.active_tokens) == 126                   # the two views together supervise every position once
+    assert (cb.loss_weights == 1).all() and rt.exclude_mask_token is False
+
+
+def test_supervision_mask_limits_masking():
+    rt = StandardBlockDiffusionRuntime(**KW)
+    x0 = torch.randint(0, 90, (2, 64))
+    sup = torch.zeros(2, 64, dtype=torch.bool)
+    sup[:, 32:] = True
+    cb = rt.corrupt(x0, supervision_mask=sup)
+    assert (cb.noisy_input_ids[:, 0, :32] != 99).all() and cb.valid_tokens == 64
+    with pytest.raises(ValueError):
+        rt.corrupt(x0[:, :60])
+
+
+def test_dflash_anchor_blocks_and_document_boundaries():
+    rt = DFlashObjectiveRuntime(block_size=4, max_anchors=6, mask_token_id=99, seed=3, decay_gamma=2.0)
+    x = torch.randint(0, 90, (2, 40))
+    docs = torch.zeros(2, 40, dtype=torch.long)
+    docs[:, 20:] = 1
+    assert document_starts(docs)[0, 25] == 20
+    b = rt.prepare(x, document_ids=docs)
+    assert b.draft_input_ids.shape == (2, 24) and b.supervised_mask.shape == (2, 24)
+    d = b.draft_input_ids.view(2, 6, 4)
+    assert torch.equal(d[:, :, 0], x.gather(1, b.anchor_positions)) and (d[:, :, 1:] == 99).all()
+    sup = b.supervised_mask.view(2, 6, 4)
+    assert not sup[:, :, 0].any()
+    # no supervision across a document boundary or past the end
+    tgt_doc = document_starts(docs).gather(1, b.target_token_positions.view(2, -1)).view(2, 6, 4)
+    anchor_doc = document_starts(docs).gather(1, b.anchor_positions)[:, :, None]
+    assert (tgt_doc[sup] == anchor_doc.expand_as(tgt_doc)[sup]).all()
+    assert torch.equal(b.context_stops[b.anchor_valid].long(), b.anchor_positions[b.anchor_valid])
+    assert (b.anchor_positions[:, 1:] >= b.anchor_positions[:, :-1])[b.anchor_valid[:, 1:]].all()
+    w = b.position_weights.view(2, 6, 4)[0, 0]
+    assert w[1] == 1.0 and w[3] < w[2] < w[1]
+    s, t = torch.randn(24, 50), torch.randn(24, 50)
+    loss, per = reference_dflash_loss(s, t, sup.view(2, -1)[0], b.position_weights[0])
+    assert loss >= 0 and per.shape == (24,)

@@ -101,6 +101,11 @@ int tdllm_kv_gather(void* const* staging_ptrs, void* const* flag_ptrs, const lon
 int tdllm_kv_scatter_reduce(void* const* partial_ptrs, void* const* flag_ptrs, const long long* counts,
                             int rank, int world, int row_bytes, void* out, int epoch, void* stream);
 
+// ---- noising ---------------------------------------------------------------
+int tdllm_corrupt(const long long* x0, const float* t, const unsigned char* eligible, long long* xt,
+                  long long* labels, int B, int L, int block_size, int views, int shift_labels,
+                  long long mask_id, unsigned long long seed, unsigned long long offset, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

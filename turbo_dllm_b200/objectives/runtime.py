@@ -1,5 +1,9 @@
 """Corruption runtimes of the block-diffusion objectives.
 
+Randomness is counter-based (Philox, `objectives/philox.py` and `csrc/noising.cu`): batch k of a
+runtime with seed s uses offsets 2k (block times) and 2k+1 (token uniforms), so CPU and GPU runs
+corrupt identically and the resumable state is just the batch counter.
+
 standard_block_diffusion: one diffusion time t per (sample, block), antithetic-stratified by
 default (one uniform draw, strata rotated by it), scaled to [eps_min, eps_max]; a token is
 masked iff rand <= t; labels are the clean token on masked positions and -100 elsewhere; the
@@ -86,6 +90,17 @@ class _ObjectiveRuntime:
     def _rand(self, shape) -> torch.Tensor:
         return torch.rand(shape, dtype=torch.float32, device=self.device, generator=self.generator)
 
+    def _block_uniforms(self, n: int) -> torch.Tensor:
+        """Counter-based uniforms for the per-block diffusion times of the current batch (identical on
+        every device type; the token-level stream uses the next offset)."""
+        from .philox import uniform01
+
+        return torch.from_numpy(uniform01(self.seed, 2 * self.batches_corrupted, n)).to(self.device)
+
+    def _tokens(self, x0, move_chance, eligible, shift: bool):
+        return fused_corrupt(x0, move_chance, eligible, block_size=self.block_size, views=self.views, shift=shift,
+                             mask_id=self.mask_token_id, seed=self.seed, offset=2 * self.batches_corrupted + 1)
+
     def skip(self, steps: int, batch_shape: tuple[int, int]) -> None:
         """Advances the generator as `steps` calls of corrupt() on this shape would."""
         x = torch.zeros(batch_shape, dtype=torch.long, device=self.device)
@@ -127,11 +142,11 @@ class StandardBlockDiffusionRuntime(_ObjectiveRuntime):
     def sample_times(self, b: int, nblk: int) -> torch.Tensor:
         if self.antithetic:
             n = b * nblk
-            u = self._rand((1,))
+            u = self._block_uniforms(1)
             strata = torch.arange(n, dtype=torch.float32, device=self.device).view(b, nblk) / float(n)
             t = (u + strata).remainder(1.0)
         else:
-            t = self._rand((b, nblk))
+            t = self._block_uniforms(b * nblk).view(b, nblk)
         return t * (self.eps_max - self.eps_min) + self.eps_min
 
     def corrupt(self, x0, *, supervision_mask=None, supervision_count=None) -> CorruptedBatch:
@@ -151,16 +166,11 @@ class StandardBlockDiffusionRuntime(_ObjectiveRuntime):
         t = self.sample_times(b, nblk)
         weights = torch.ones_like(t) if self.loss_weighting == "unit" else t.reciprocal()
         noise = (-torch.log1p(-t)).clamp(max=-math.log(self.noise_schedule_epsilon))
-        mask = self._rand(x0.shape) <= t.repeat_interleave(self.block_size, dim=1)
-        if eligible is not None:
-            mask &= eligible
-        xt = torch.where(mask, torch.full_like(x0, self.mask_token_id), x0)
-        labels = torch.where(mask, x0, torch.full_like(x0, LABEL_IGNORE_INDEX))
-        active = mask.sum(dtype=torch.int64)
+        xt, labels = self._tokens(x0, t, eligible, shift=False)
+        active = (labels != LABEL_IGNORE_INDEX).sum(dtype=torch.int64)
         self.batches_corrupted += 1
         self.valid_tokens_seen += valid
-        return CorruptedBatch(x0, xt[:, None], labels[:, None], t, noise, weights[:, None], active,
-                              valid, float(valid))
+        return CorruptedBatch(x0, xt, labels, t, noise, weights[:, None], active, valid, float(valid))
 
 
 class FastDLLMv2Runtime(_ObjectiveRuntime):
@@ -188,20 +198,37 @@ class FastDLLMv2Runtime(_ObjectiveRuntime):
                      else int(supervision_count) - int(eligible[:, 0].sum()))
         if valid <= 0:
             raise ValueError("each training batch must contain shifted supervised tokens")
-        t = self._rand((b, nblk))
+        t = self._block_uniforms(b * nblk).view(b, nblk)
         move = (1.0 - self.noise_schedule_epsilon) * t + self.noise_schedule_epsilon
-        sampled = self._rand(x0.shape) < move.repeat_interleave(self.block_size, dim=1)
-        masks = torch.stack([sampled & eligible, (~sampled) & eligible], dim=1)      # [B, 2, L]
-        x0v = x0[:, None].expand(-1, 2, -1)
-        noisy = torch.where(masks, torch.full_like(x0v, self.mask_token_id), x0v)
-        targets = torch.where(masks, x0v, torch.full_like(x0v, LABEL_IGNORE_INDEX))
-        labels = torch.full_like(targets, LABEL_IGNORE_INDEX)
-        labels[:, :, :-1] = targets[:, :, 1:]
+        noisy, labels = self._tokens(x0, move, None if supervision_mask is None else eligible, shift=True)
         active = (labels != LABEL_IGNORE_INDEX).sum(dtype=torch.int64)
         self.batches_corrupted += 1
         self.valid_tokens_seen += valid
         return CorruptedBatch(x0, noisy, labels, t, move, torch.ones(b, 2, nblk, device=self.device),
                               active, valid, float(valid))
+
+
+def fused_corrupt(x0: torch.Tensor, t: torch.Tensor, eligible, *, block_size: int, views: int, shift: bool,
+                  mask_id: int, seed: int, offset: int):
+    """Noisy ids and labels [B, V, L] from per-block move chances `t` with the counter-based
+    generator: one sm_100a kernel on CUDA tensors, the bit-identical host twin elsewhere."""
+    b, l = x0.shape
+    if x0.is_cuda:
+        from ..kernels import native
+        from ..ops._util import ptr, stream
+
+        native.register_signatures({"tdllm_corrupt": (native.c_int, [native.c_void_p] * 5 + [native.c_int] * 5
+                                                      + [native.c_ll, native.c_ull, native.c_ull, native.c_void_p])})
+        xt = torch.empty(b, views, l, dtype=torch.int64, device=x0.device)
+        labels = torch.empty_like(xt)
+        el = None if eligible is None else eligible.to(torch.uint8).contiguous()
+        native.check(native.lib().tdllm_corrupt(ptr(x0.contiguous()), ptr(t.float().contiguous()), ptr(el), ptr(xt),
+                                                ptr(labels), b, l, block_size, views, int(shift), mask_id, seed,
+                                                offset, stream()), "corrupt")
+        return xt, labels
+    from .philox import corrupt_reference
+
+    return corrupt_reference(x0, t, eligible, block_size, views, shift, mask_id, seed, offset)
 
 
 def build_objective_runtime(spec, *, mask_token_id: int, seed: int, device="cpu"):

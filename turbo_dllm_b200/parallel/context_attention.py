@@ -131,6 +131,67 @@ class _PeerGatherRows(torch.autograd.Function):
         return ctx.exchange.scatter_reduce(g.contiguous()), None
 
 
+class _StreamingAttention(torch.autograd.Function):
+    """Streaming transport: one owner shard of clean K|V is resident at a time. Forward: for every
+    owner, broadcast its shard, run the attention kernel on it and fold (out, lse) into the
+    online-softmax state. Backward: the shards are streamed again and each shard's backward runs
+    against the MERGED (out, lse) — which yields the exact gradients without per-shard lse
+    gradients — with clean dK|dV reduced to their owner."""
+
+    @staticmethod
+    def forward(ctx, qkv, cpa):
+        from ..ops.attention import attention_forward_native
+        from ..ops.merge import MergeState
+
+        c = cpa.cfg
+        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        n_noisy = cpa.layout.n_noisy
+        q, _, _ = split_packed_qkv(qkv, Hq, Hkv, D)
+        rows = qkv.shape[0]
+        st = MergeState(rows, Hq, D, qkv.device)
+        scale = 1.0 / D ** 0.5
+        for r in range(cpa.cp):
+            kv = cpa.shard_kv(qkv, r)
+            k, v = cpa.kv_views(kv)
+            st.merge(*attention_forward_native(q, k, v, cpa.shard_masks[r], scale))
+        out, lse = st.finalize(qkv.dtype)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.cpa = cpa
+        return out.reshape(rows, Hq * D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops.attention import attention_backward_native
+
+        qkv, out, lse = ctx.saved_tensors
+        cpa = ctx.cpa
+        c = cpa.cfg
+        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        n_noisy = cpa.layout.n_noisy
+        rows = qkv.shape[0]
+        q, _, _ = split_packed_qkv(qkv, Hq, Hkv, D)
+        dqkv = torch.zeros_like(qkv)
+        dq_acc = torch.zeros(rows, Hq, D, dtype=torch.float32, device=qkv.device)
+        dout3 = dout.contiguous().view(rows, Hq, D)
+        scale = 1.0 / D ** 0.5
+        for r in range(cpa.cp):
+            kv = cpa.shard_kv(qkv, r)
+            k, v = cpa.kv_views(kv)
+            dq, dk, dv = attention_backward_native(q, k, v, out, dout3, lse, cpa.shard_masks[r], scale)
+            dq_acc += dq.float()
+            dkv = torch.cat([dk.reshape(k.shape[0], -1), dv.reshape(v.shape[0], -1)], dim=1)
+            off = 0
+            if r == 0:   # shard 0 also carries this rank's noisy keys
+                dqkv[:n_noisy, Hq * D:] += dkv[:n_noisy]
+                off = n_noisy
+            clean = dkv[off:].contiguous()
+            dist.reduce(clean, dst=cpa.group_ranks[r], op=dist.ReduceOp.SUM, group=cpa.group)
+            if r == cpa.cp_rank:
+                dqkv[n_noisy:, Hq * D:] += clean
+        dqkv[:, : Hq * D] = dq_acc.reshape(rows, Hq * D).to(dqkv.dtype)
+        return dqkv, None
+
+
 class ContextParallelAttention:
     def __init__(self, cfg: ModelConfig, layout: PackedLayout, runtime, spec):
         self.cfg, self.layout, self.rt = cfg, layout, runtime
@@ -148,7 +209,23 @@ class ContextParallelAttention:
             kseq.append(torch.arange(batch, device=dev).repeat_interleave(pos.numel()))
             counts.append(pos.numel() * batch)
         self.counts = counts
+        self.cp, self.cp_rank = cp, runtime.context_parallel_rank
+        self.group_ranks = runtime.groups.ranks["context_block_parallel"]
         self.transport = spec.kernel.cp_bp_clean_kv_transport
+        self.shard_masks = None
+        if self.transport == "streaming":
+            if dev.type != "cuda":
+                self.transport = "collective"   # the streaming path drives the sm_100a kernels directly
+            else:
+                self.shard_masks = []
+                for r in range(cp):
+                    m = block_diffusion_layout(layout.noisy_pos, layout.noisy_group, layout.clean_pos,
+                                               layout.block_size, noisy_seq=layout.noisy_seq,
+                                               clean_seq=layout.clean_seq, key_clean_pos=kpos[r],
+                                               key_clean_seq=kseq[r])
+                    if r > 0:   # only the first shard carries the noisy keys
+                        m.k_code = m.k_code[layout.n_noisy:].contiguous()
+                    self.shard_masks.append(m)
         self.exchange = None
         if self.transport == "peer_pull":
             if dev.type != "cuda":
@@ -159,7 +236,28 @@ class ContextParallelAttention:
                                            clean_seq=layout.clean_seq, key_clean_pos=torch.cat(kpos),
                                            key_clean_seq=torch.cat(kseq))
 
+    def shard_kv(self, qkv, r: int) -> torch.Tensor:
+        """K|V rows attended in streaming step r: (noisy rows if r == 0) + owner r's clean rows."""
+        c = self.cfg
+        qd = c.num_attention_heads * c.head_dim
+        n_noisy = self.layout.n_noisy
+        if r == self.cp_rank:
+            clean = qkv[n_noisy:, qd:].contiguous()
+        else:
+            clean = qkv.new_empty(self.counts[r], qkv.shape[1] - qd)
+        dist.broadcast(clean, src=self.group_ranks[r], group=self.group)
+        return torch.cat([qkv[:n_noisy, qd:], clean], dim=0) if r == 0 else clean
+
+    def kv_views(self, kv):
+        c = self.cfg
+        n = kv.shape[0]
+        kd = c.num_key_value_heads * c.head_dim
+        return (kv[:, :kd].view(n, c.num_key_value_heads, c.head_dim),
+                kv[:, kd:].view(n, c.num_key_value_heads, c.head_dim))
+
     def __call__(self, qkv, layer_idx):
+        if self.transport == "streaming":
+            return _StreamingAttention.apply(qkv, self)
         c = self.cfg
         Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
         n_noisy = self.layout.n_noisy

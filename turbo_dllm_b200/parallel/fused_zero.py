@@ -55,6 +55,7 @@ class FusedZeroSync:
             p.data = new_data[o:o + n].view(shape)
             p.main_grad = new_grad[o:o + n].view(shape)
         torch.cuda.synchronize()
+        torch.cuda.empty_cache()   # the buffers the parameters came from go back to the driver
         dist.barrier(group=group)
         return cls(flat, group, params_buf, grads_buf, scalar_buf, barrier)
 

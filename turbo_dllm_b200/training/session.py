@@ -176,8 +176,11 @@ class TrainingSession:
         shard = max(self.world, 1)
         static = cfg.num_params() * (2 + 2 + 12 / shard)
         total = torch.cuda.get_device_properties(self.device).total_memory
+        # layer inputs and attention (out, lse) both stay in HBM when they fit; otherwise both go to
+        # pinned host memory (the copies hide behind the GEMMs), which is still cheaper than
+        # recomputing the attention forward
         self._keep_attention_on_device = static + 2 * ckpt + work < 0.8 * total
-        return static + ckpt + work > 0.9 * total
+        return not self._keep_attention_on_device
 
     def _build_layout(self) -> PackedLayout:
         s, rt = self.spec, self.runtime
