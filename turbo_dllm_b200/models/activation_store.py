@@ -17,14 +17,17 @@ import torch
 
 
 class ActivationStore:
-    def __init__(self, device: torch.device, offload: bool = False):
+    def __init__(self, device: torch.device, offload: bool = False, offload_attention: bool | None = None):
         self.device = torch.device(device)
-        self.offload = bool(offload) and self.device.type == "cuda"
+        self.offload = bool(offload) and self.device.type == "cuda"            # layer inputs
+        self.offload_attention = (self.offload if offload_attention is None
+                                  else bool(offload_attention) and self.device.type == "cuda")
         self.kept: dict[int, torch.Tensor] = {}
         self.host: dict[int, torch.Tensor] = {}
         self.ready: dict[int, torch.cuda.Event] = {}
         self.inflight: dict[int, tuple[torch.Tensor, torch.cuda.Event]] = {}
-        self.stream = torch.cuda.Stream(device=self.device) if self.offload else None
+        self.stream = (torch.cuda.Stream(device=self.device)
+                       if (self.offload or self.offload_attention) else None)
         self.bytes_offloaded = 0
         self.recording = False      # True while a checkpointed layer runs its no-grad forward
         self.replaying = False      # True while a checkpointed layer is recomputed for backward
@@ -33,8 +36,11 @@ class ActivationStore:
     def has(self, idx) -> bool:
         return idx in self.kept or idx in self.ready
 
+    def _to_host(self, idx) -> bool:
+        return self.offload_attention if isinstance(idx, tuple) else self.offload
+
     def stash(self, idx, x: torch.Tensor) -> None:
-        if not self.offload:
+        if not self._to_host(idx):
             self.kept[idx] = x
             return
         buf = self.host.get(idx)
@@ -51,7 +57,7 @@ class ActivationStore:
         self.bytes_offloaded += x.numel() * x.element_size()
 
     def prefetch(self, idx) -> None:
-        if not self.offload or idx in self.inflight or idx not in self.host or idx not in self.ready:
+        if not self._to_host(idx) or idx in self.inflight or idx not in self.host or idx not in self.ready:
             return
         with torch.cuda.stream(self.stream):
             self.ready[idx].wait(self.stream)
@@ -62,7 +68,7 @@ class ActivationStore:
         self.inflight[idx] = (dev, ev)
 
     def fetch(self, idx) -> torch.Tensor:
-        if not self.offload:
+        if not self._to_host(idx):
             return self.kept.pop(idx)
         self.prefetch(idx)
         dev, ev = self.inflight.pop(idx)

@@ -91,8 +91,11 @@ class TrainingSession:
                                    dropout=spec.adapter.dropout, targets=spec.adapter.targets or ("attention", "mlp"),
                                    seed=seed)
         keep = os.environ.get("TDLLM_KEEP_ATTENTION")
-        self.model.store.keep_attention = (keep == "1") if keep is not None else (
-            self.model.store.offload or getattr(self, "_keep_attention_on_device", False))
+        _, off_attn, keep_attn = self._memory_plan()
+        self.model.store.keep_attention = (keep == "1") if keep is not None else keep_attn
+        self.model.store.offload_attention = off_attn and self.device.type == "cuda"
+        if self.model.store.offload_attention and self.model.store.stream is None:
+            self.model.store.stream = torch.cuda.Stream(device=self.device)
         dp_rank = runtime.sample_parallel_rank if runtime is not None else self.rank
         self.dp_size = runtime.data_parallel_size * ep if runtime is not None else self.world
         self.objective = build_objective_runtime(spec, mask_token_id=self.cfg.mask_token_id,
@@ -161,26 +164,32 @@ class TrainingSession:
         self.scheduler = RunSpecLRScheduler.from_run_spec(spec)
         self.steps_done = 0
 
-    def _want_activation_offload(self) -> bool:
-        """Offload layer checkpoints to pinned host memory when keeping them in HBM would not leave
-        room for parameters, gradients, optimizer state and one layer's working set."""
+    def _memory_plan(self) -> tuple[bool, bool, bool]:
+        """(offload layer inputs, offload attention out/lse, keep attention out/lse at all).
+
+        Keeping the attention output of every layer saves the forward kernel in the recomputation.
+        Everything stays in HBM when it fits next to parameters, gradients, optimizer shard and one
+        layer's working set; otherwise the attention outputs go to pinned host memory first, and the
+        layer inputs follow only if that is still not enough (the copies hide behind the GEMMs)."""
         env = os.environ.get("TDLLM_ACTIVATION_OFFLOAD")
         if env is not None:
-            return env == "1"
+            return env == "1", env == "1", True
         if self.device.type != "cuda" or not self.spec.training.activation_checkpointing:
-            return False
+            return False, False, self.device.type == "cuda"
         cfg, s = self.cfg, self.spec
         rows = 3 * s.model.seq_len * s.training.batch_size  # upper bound: two noisy views + clean
         ckpt = rows * cfg.hidden_size * 2 * cfg.num_layers
         work = rows * 2 * (6 * cfg.hidden_size + 2 * cfg.qkv_dim + 5 * max(cfg.intermediate_size, 1))
-        shard = max(self.world, 1)
-        static = cfg.num_params() * (2 + 2 + 12 / shard)
-        total = torch.cuda.get_device_properties(self.device).total_memory
-        # layer inputs and attention (out, lse) both stay in HBM when they fit; otherwise both go to
-        # pinned host memory (the copies hide behind the GEMMs), which is still cheaper than
-        # recomputing the attention forward
-        self._keep_attention_on_device = static + 2 * ckpt + work < 0.8 * total
-        return not self._keep_attention_on_device
+        static = cfg.num_params() * (2 + 2 + 12 / max(self.world, 1))
+        budget = 0.85 * torch.cuda.get_device_properties(self.device).total_memory
+        if static + 2 * ckpt + work < budget:
+            return False, False, True
+        if static + ckpt + work < budget:
+            return False, True, True
+        return True, True, True
+
+    def _want_activation_offload(self) -> bool:
+        return self._memory_plan()[0]
 
     def _build_layout(self) -> PackedLayout:
         s, rt = self.spec, self.runtime
