@@ -119,7 +119,11 @@ def run_ours(args):
 
     e2e = None
     if not args.skip_e2e:
-        del session
+        session.close()
+        del session, last
+        import gc
+
+        gc.collect()
         torch.cuda.empty_cache()
         session = TrainingSession(spec, device=f"cuda:{local_rank}", host_staged_data=True)
         for _ in range(max(args.warmup, 3)):

@@ -93,19 +93,33 @@ def _run_bwd(layout, nq, nk, Hq, Hkv, seed=0):
         assert err <= 5e-2 * max(scale_, 1.0), (name, err, scale_)
 
 
+@pytest.mark.parametrize("mode", ["fused", "split"])
 @pytest.mark.parametrize("L,bs,views", [(256, 32, 1), (640, 32, 2), (1024, 64, 1)])
 @pytest.mark.parametrize("Hq,Hkv", [(2, 1), (8, 2)])
-def test_backward_full_sequence(L, bs, views, Hq, Hkv):
+def test_backward_full_sequence(L, bs, views, Hq, Hkv, mode, monkeypatch):
     from turbo_dllm_b200.ops.attention import single_sequence_layout
 
+    monkeypatch.setenv("TDLLM_ATTN_BWD", mode)
     layout = single_sequence_layout(L, bs, "cuda", views)
     n = (views + 1) * L
     _run_bwd(layout, n, n, Hq, Hkv)
 
 
-def test_backward_ragged_sparse_keys():
+def test_backward_one_pass_odd_group_and_long_walk(monkeypatch):
+    """Three query heads per KV head (the split kernels need an even count) and enough query tiles
+    per key tile that every barrier of the one-pass kernel wraps its phase several times."""
+    from turbo_dllm_b200.ops.attention import single_sequence_layout
+
+    monkeypatch.setenv("TDLLM_ATTN_BWD", "fused")
+    layout = single_sequence_layout(1536, 32, "cuda", 2)
+    _run_bwd(layout, 3 * 1536, 3 * 1536, 3, 1)
+
+
+@pytest.mark.parametrize("mode", ["fused", "split"])
+def test_backward_ragged_sparse_keys(mode, monkeypatch):
     from turbo_dllm_b200.ops.attention import block_diffusion_layout
 
+    monkeypatch.setenv("TDLLM_ATTN_BWD", mode)
     dev = "cuda"
     L, bs = 600, 24
     pos = torch.arange(L, device=dev)

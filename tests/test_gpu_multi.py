@@ -46,7 +46,17 @@ def _train(rank, world, backend, steps):
         losses.append(float(t) / r.denominator)
     torch.cuda.synchronize()
     native.raise_on_device_error()
-    return losses, s.model.flat.data.float().cpu(), s.optimizer.grad_norm()
+    out = losses, s.model.flat.data.float().cpu(), s.optimizer.grad_norm()
+    if backend == "fused":
+        # closing hands the symmetric buffers back and leaves a session that still trains (NCCL path)
+        used_before = torch.cuda.mem_get_info()[0]
+        s.close()
+        assert s.optimizer.fused_sync is None
+        assert (s.model.flat.data.float().cpu() == out[1]).all()
+        r = s.step()
+        assert torch.isfinite(r.loss_sum).item()
+        del used_before
+    return out
 
 
 @pytest.mark.distributed

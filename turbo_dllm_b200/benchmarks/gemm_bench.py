@@ -35,12 +35,24 @@ def time_fn(fn, iters, warmup, flush):
     return times[len(times) // 2], times[0]
 
 
+def layer_shapes(rows: int, hidden: int, qkv: int, ffn: int) -> list[tuple[str, str]]:
+    """(MxNxK, layout) of every GEMM one decoder layer runs: forward, input gradient, weight gradient."""
+    out = []
+    for n_out, k_in in ((qkv, hidden), (hidden, hidden), (2 * ffn, hidden), (hidden, ffn)):
+        out.append((f"{rows}x{n_out}x{k_in}", "kk"))      # y = x W^T
+        out.append((f"{rows}x{k_in}x{n_out}", "kn"))      # dx = dy W
+        out.append((f"{n_out}x{k_in}x{rows}", "nn"))      # dW = dy^T x
+    return out
+
+
 def main(argv=None):
     from turbo_dllm_b200.ops.gemm import gemm
 
     ap = argparse.ArgumentParser()
     ap.add_argument("--shapes", default="8192x8192x8192,16384x12288x4096,16384x4096x12288")
     ap.add_argument("--layouts", default="kk,kn,nn")
+    ap.add_argument("--layer", default=None,
+                    help="rows,hidden,qkv_dim,ffn: time every GEMM of one decoder layer instead of --shapes")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)
@@ -50,9 +62,13 @@ def main(argv=None):
     if os.path.exists(pk):
         peak = json.load(open(pk)).get("bf16_tflops")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    for shp in args.shapes.split(","):
+    if args.layer:
+        work = layer_shapes(*(int(v) for v in args.layer.split(",")))
+    else:
+        work = [(shp, lay) for shp in args.shapes.split(",") for lay in args.layouts.split(",")]
+    for shp, lay in work:
         M, N, K = (int(v) for v in shp.split("x"))
-        for lay in args.layouts.split(","):
+        if True:
             a_mn, b_mn = lay[0] == "n", lay[1] == "n"
             a = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
             b = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()

@@ -83,6 +83,16 @@ int tdllm_attn_bwd(const void* q, const void* k, const void* v, const void* o, c
                    const int* b_idx, const int* b_order, int n_qtiles, int n_ktiles, float scale,
                    void* stream);
 
+// One-pass backward (five tensor-core products per tile pair instead of seven): dQ is summed over
+// key tiles in `dq_acc`, fp32 scratch [n_qtiles*128, Hq, 128] that this call zeroes, then cast.
+int tdllm_attn_bwd_fused(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                         void* dq, void* dk, void* dv, const float* lse, float* delta, float* dq_acc,
+                         int nq, int nk, int Hq, int Hkv, long long ldq, long long ldk, long long ldv,
+                         long long ldo, long long lddo, long long lddq, long long lddk,
+                         long long lddv, const int* q_lo, const int* q_hi, const int* q_grp,
+                         const int* k_code, const int* b_ptr, const int* b_idx, const int* b_order,
+                         int n_qtiles, int n_ktiles, float scale, void* stream);
+
 // ---- peer memory and the fused ZeRO step -----------------------------------
 int tdllm_symm_alloc(long long bytes, void** out);
 int tdllm_symm_free(void* p);

@@ -40,7 +40,7 @@ def find_nvcc() -> str:
     return cand
 
 
-INCLUDED_ONLY = {"attention_bwd_dq_sm100.cu", "attention_bwd_dkv_sm100.cu"}  # pulled in by attention_bwd_host.cu
+INCLUDED_ONLY = {"attention_bwd_dq_sm100.cu", "attention_bwd_dkv_sm100.cu", "attention_bwd_fused_sm100.cu"}  # pulled in by attention_bwd_host.cu
 
 
 def sources() -> list[Path]:

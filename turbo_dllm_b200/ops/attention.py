@@ -19,12 +19,13 @@ run; they consume per-query-tile lists of visible key tiles built once per layou
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 
 import torch
 
 from ..kernels import native
-from ._util import ptr, stream, use_native
+from ._util import ptr, scratch, stream, use_native
 
 TILE = 128
 INT_MIN = -(2 ** 31)
@@ -222,7 +223,21 @@ native.register_signatures({
     "tdllm_attn_bwd": (native.c_int, [native.c_void_p] * 10 + [native.c_int] * 4 + [native.c_ll] * 8
                        + [native.c_void_p] * 10 + [native.c_int, native.c_int, native.c_float,
                                                    native.c_void_p]),
+    "tdllm_attn_bwd_fused": (native.c_int, [native.c_void_p] * 11 + [native.c_int] * 4 + [native.c_ll] * 8
+                             + [native.c_void_p] * 7 + [native.c_int, native.c_int, native.c_float,
+                                                        native.c_void_p]),
 })
+
+
+def backward_mode() -> str:
+    """"fused": one pass per key tile, dQ summed in fp32 (five tensor-core products per tile pair;
+    the sum over key tiles is not bitwise repeatable). "split": a dQ kernel per query tile and a dK/dV
+    kernel per key tile (seven products, deterministic; needs an even number of query heads per KV head).
+    TDLLM_ATTN_BWD selects; fused is the default."""
+    mode = os.environ.get("TDLLM_ATTN_BWD", "fused")
+    if mode not in ("fused", "split"):
+        raise ValueError(f"TDLLM_ATTN_BWD must be 'fused' or 'split', got {mode!r}")
+    return mode
 
 
 def attention_backward_native(q, k, v, out, dout, lse, layout: MaskLayout, scale: float,
@@ -251,6 +266,16 @@ def attention_backward_native(q, k, v, out, dout, lse, layout: MaskLayout, scale
         padded[:, :nq] = lse[:, :nq]
         lse = padded
     delta = torch.empty(2, Hq, L["nq_pad"], dtype=torch.float32, device=dev)
+    if backward_mode() == "fused":
+        acc = scratch(dev, L["nq_pad"] * Hq * D, key="attn_dq_acc")
+        rc = native.lib().tdllm_attn_bwd_fused(
+            ptr(q), ptr(k), ptr(v), ptr(out), ptr(dout), ptr(dq), ptr(dk), ptr(dv), ptr(lse), ptr(delta), ptr(acc),
+            nq, nk, Hq, Hkv, _rows_view(q), _rows_view(k), _rows_view(v), _rows_view(out),
+            dout.stride(0), dq.stride(0), dk.stride(0), dv.stride(0),
+            ptr(L["q_lo"]), ptr(L["q_hi"]), ptr(L["q_grp"]), ptr(L["k_code"]),
+            ptr(L["b_ptr"]), ptr(L["b_idx"]), ptr(L["b_order"]), L["nqt"], L["nkt"], float(scale), stream())
+        native.check(rc, "attn_bwd_fused")
+        return dq, dk, dv
     rc = native.lib().tdllm_attn_bwd(
         ptr(q), ptr(k), ptr(v), ptr(out), ptr(dout), ptr(dq), ptr(dk), ptr(dv), ptr(lse), ptr(delta),
         nq, nk, Hq, Hkv, _rows_view(q), _rows_view(k), _rows_view(v), _rows_view(out),

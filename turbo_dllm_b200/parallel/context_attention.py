@@ -94,6 +94,10 @@ class PeerKVExchange:
         self.flip = 0
         self.device = device
 
+    def close(self) -> None:
+        for b in (*self.staging, self.partial, self.barrier.buf):
+            b.close()
+
     def gather(self, x: torch.Tensor) -> torch.Tensor:
         from ..ops._util import ptr, stream
 

@@ -81,6 +81,7 @@ class TrainingSession:
                 self.cfg, dtype=self.dtype, device=self.device,
                 activation_checkpointing=spec.training.activation_checkpointing,
                 activation_offload=self._want_activation_offload(), seed=seed, tp=tp)
+        self.memory_report("model built")
         self.lora = None
         if spec.adapter.type == "lora":
             from ..adapters.lora import apply_lora
@@ -131,6 +132,31 @@ class TrainingSession:
                                        **okw)
         self.scheduler = RunSpecLRScheduler.from_run_spec(spec)
         self.steps_done = 0
+        self.memory_report("session built")
+
+    def close(self) -> None:
+        """Returns symmetric (peer-visible) buffers to the driver. They are allocated outside the
+        caching allocator, so dropping the session alone does not free them. Collective: every rank of
+        the optimizer group closes at the same point, after the last step has finished."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        sync = getattr(getattr(self, "optimizer", None), "fused_sync", None)
+        if sync is not None:
+            if dist.is_initialized():
+                dist.barrier(group=sync.group)   # no peer may still be reading this rank's buffers
+            flat = sync.flat
+            data, grad = flat.data.clone(), torch.zeros_like(flat.grad)
+            flat.data, flat.grad = data, grad
+            for name, (o, n, shape, decay) in flat.offsets.items():
+                p = flat.params[name]
+                p.data = data[o:o + n].view(shape)
+                p.main_grad = grad[o:o + n].view(shape)
+            sync.close()
+            self.optimizer.fused_sync = None
+        exchange = getattr(getattr(self, "attend", None), "exchange", None)
+        if exchange is not None and hasattr(exchange, "close"):
+            exchange.close()
+            self.attend.exchange = None
 
     def flats(self):
         if getattr(self, "lora", None) is not None:
@@ -246,15 +272,31 @@ class TrainingSession:
         weights = torch.cat([w, torch.zeros(clean.shape[0], device=w.device)])
         return tokens, labels, weights
 
+    def memory_report(self, tag: str) -> None:
+        """With TDLLM_MEMORY_REPORT=1, every rank writes one line of device-memory figures to stderr."""
+        if self.device.type != "cuda" or os.environ.get("TDLLM_MEMORY_REPORT") != "1":
+            return
+        import sys
+
+        free, total = torch.cuda.mem_get_info(self.device)
+        gib = 2.0 ** 30
+        print(f"[memory rank {self.rank}] {tag}: torch allocated {torch.cuda.memory_allocated(self.device) / gib:.2f} "
+              f"peak {torch.cuda.max_memory_allocated(self.device) / gib:.2f} reserved "
+              f"{torch.cuda.memory_reserved(self.device) / gib:.2f} GiB; device in use {(total - free) / gib:.2f} "
+              f"of {total / gib:.2f} GiB", file=sys.stderr, flush=True)
+
     # ------------------------------------------------------------------ step
     def forward_backward(self, batch: DataBatch, denominator: float):
         cb = self.objective.corrupt(batch.input_ids, supervision_mask=batch.supervision_mask,
                                     supervision_count=batch.supervision_count)
         tokens, labels, weights = self.assemble_rows(cb)
         hidden = self.model(tokens, self.layout.positions, self.attend)
+        self.memory_report("after forward")
         h, l, w, _ = compact_supervised_rows(hidden, labels, weights)
         loss_sum, _ = self.model.loss(h, l, w, self.objective.exclude_mask_token)
+        self.memory_report("after loss")
         (loss_sum / denominator).backward()
+        self.memory_report("after backward")
         return loss_sum.detach(), l.shape[0], cb
 
     def global_denominator(self, batches: list[DataBatch]) -> float:

@@ -212,6 +212,7 @@ def run_training(spec: RunSpec) -> dict:
             emit(summary)
             wb.log_event(summary)
         wb.finish()
+        session.close()
         return summary
     except Exception as e:
         info = {"event": "fatal_exception", "rank": rank, "error": f"{type(e).__name__}: {e}",
