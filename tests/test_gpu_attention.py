@@ -105,14 +105,14 @@ def test_backward_full_sequence(L, bs, views, Hq, Hkv, mode, monkeypatch):
     _run_bwd(layout, n, n, Hq, Hkv)
 
 
-def test_backward_one_pass_odd_group_and_long_walk(monkeypatch):
-    """Three query heads per KV head (the split kernels need an even count) and enough query tiles
-    per key tile that every barrier of the one-pass kernel wraps its phase several times."""
+def test_backward_one_pass_long_walk(monkeypatch):
+    """Enough (query head, query tile) pairs per key tile that every barrier of the one-pass kernel
+    wraps its phase many times."""
     from turbo_dllm_b200.ops.attention import single_sequence_layout
 
     monkeypatch.setenv("TDLLM_ATTN_BWD", "fused")
     layout = single_sequence_layout(1536, 32, "cuda", 2)
-    _run_bwd(layout, 3 * 1536, 3 * 1536, 3, 1)
+    _run_bwd(layout, 3 * 1536, 3 * 1536, 4, 1)
 
 
 @pytest.mark.parametrize("mode", ["fused", "split"])

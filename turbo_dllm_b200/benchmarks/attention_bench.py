@@ -28,6 +28,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--fwd-only", action="store_true")
+    ap.add_argument("--bwd-modes", default="fused,split", help="backward variants to time (TDLLM_ATTN_BWD values)")
     args = ap.parse_args(argv)
     D = 128
     dev = "cuda"
@@ -71,9 +72,13 @@ def main(argv=None):
     if not args.fwd_only:
         dout = torch.randn_like(out)
         dqkv = torch.empty_like(qkv)
-        bwd_ms = timeit(lambda: attention_backward_native(q, k, v, out, dout, lse, layout, scale, dqkv))
-        rec["bwd_ms"] = round(bwd_ms, 3)
-        rec["bwd_tflops_exact_pairs"] = round(10.0 * pairs * D * args.heads / bwd_ms / 1e9, 1)
+        import os
+
+        for mode in args.bwd_modes.split(","):
+            os.environ["TDLLM_ATTN_BWD"] = mode
+            bwd_ms = timeit(lambda: attention_backward_native(q, k, v, out, dout, lse, layout, scale, dqkv))
+            rec[f"bwd_{mode}_ms"] = round(bwd_ms, 3)
+            rec[f"bwd_{mode}_tflops_exact_pairs"] = round(10.0 * pairs * D * args.heads / bwd_ms / 1e9, 1)
     print(json.dumps(rec), flush=True)
 
 

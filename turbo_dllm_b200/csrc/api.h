@@ -93,6 +93,11 @@ int tdllm_attn_bwd_fused(const void* q, const void* k, const void* v, const void
                          const int* k_code, const int* b_ptr, const int* b_idx, const int* b_order,
                          int n_qtiles, int n_ktiles, float scale, void* stream);
 
+// Issue-rate probe of tcgen05.mma (128 x n x 16, bf16): out[0] = cycles in the issue loop of one
+// thread, out[1] = cycles until the last MMA completed.
+int tdllm_mma_issue_probe(int n, int iters, int a_from_tmem, int accs, int uniform, int ctas,
+                          long long* out, void* stream);
+
 // ---- peer memory and the fused ZeRO step -----------------------------------
 int tdllm_symm_alloc(long long bytes, void** out);
 int tdllm_symm_free(void* p);

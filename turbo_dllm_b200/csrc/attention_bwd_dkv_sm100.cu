@@ -147,7 +147,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
     }
   } else if (warp == 9) {
-    if (lane == 0 && items > 0) {
+    // whole warp, identical values; one elected lane issues (keeps descriptors in uniform registers)
+    if (items > 0) {
+      const bool leader = elect_one();
       const uint32_t idesc_st = make_idesc_bf16(128, 64, 0, 0);    // [128 keys] x [64 q], K = d
       const uint32_t idesc_acc = make_idesc_bf16(128, HD, 0, 1);   // [128 keys] x [128 d], K = q
       const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
@@ -159,18 +161,24 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          tc_mma_ss(tmem_base + b * 128, make_smem_desc_sw128(ka + off, 16, 1024),
-                    make_smem_desc_sw128(qa + off, 16, 1024), idesc_st, k ? 1u : 0u);
+          {
+            const uint64_t ad_ = make_smem_desc_sw128(ka + off, 16, 1024);
+            const uint64_t bd_ = make_smem_desc_sw128(qa + off, 16, 1024);
+            if (leader) tc_mma_ss(tmem_base + b * 128, ad_, bd_, idesc_st, k ? 1u : 0u);
+          }
         }
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          tc_mma_ss(tmem_base + b * 128 + 64, make_smem_desc_sw128(va + off, 16, 1024),
-                    make_smem_desc_sw128(da + off, 16, 1024), idesc_st, k ? 1u : 0u);
+          {
+            const uint64_t ad_ = make_smem_desc_sw128(va + off, 16, 1024);
+            const uint64_t bd_ = make_smem_desc_sw128(da + off, 16, 1024);
+            if (leader) tc_mma_ss(tmem_base + b * 128 + 64, ad_, bd_, idesc_st, k ? 1u : 0u);
+          }
         }
-        tc_commit(bar_sfull + 8 * b);
+        if (leader) tc_commit(bar_sfull + 8 * b);
       };
-      bool ok = mbar_wait(bar_kv, 0, KID, 20) && mbar_wait(bar_qfull, 0, KID, 21);
+      bool ok = __all_sync(0xffffffffu, mbar_wait(bar_kv, 0, KID, 20)) && __all_sync(0xffffffffu, mbar_wait(bar_qfull, 0, KID, 21));
       if (ok) {
         tc_fence_after();
         issue_st(0);
@@ -178,31 +186,36 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       for (int u = 0; u < U && ok; ++u) {
         const int s = (u >> 1) & 1, b = u & 1;
-        if (!mbar_wait(bar_pfull + 8 * b, (u >> 1) & 1, KID, 22)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_pfull + 8 * b, (u >> 1) & 1, KID, 22))) break;
         tc_fence_after();
         const uint32_t qa = smem_u32(sQ + s * TILE_BYTES) + b * 64 * 128;
         const uint32_t da = smem_u32(sdO + s * TILE_BYTES) + b * 64 * 128;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          tc_mma_ts(tmem_base + 256, tmem_base + b * 128 + k * 8,
-                    make_smem_desc_sw128(da + k * 2048, HALF_BYTES, 1024), idesc_acc,
+          {
+            const uint64_t bd_ = make_smem_desc_sw128(da + k * 2048, HALF_BYTES, 1024);
+            if (leader) tc_mma_ts(tmem_base + 256, tmem_base + b * 128 + k * 8, bd_, idesc_acc,
                     (u | k) ? 1u : 0u);
+          }
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          tc_mma_ts(tmem_base + 384, tmem_base + b * 128 + 64 + k * 8,
-                    make_smem_desc_sw128(qa + k * 2048, HALF_BYTES, 1024), idesc_acc,
+          {
+            const uint64_t bd_ = make_smem_desc_sw128(qa + k * 2048, HALF_BYTES, 1024);
+            if (leader) tc_mma_ts(tmem_base + 384, tmem_base + b * 128 + 64 + k * 8, bd_, idesc_acc,
                     (u | k) ? 1u : 0u);
-        if (b == 1) tc_commit(bar_qempty + 8 * s);
-        if (u + 1 == U) tc_commit(bar_done);
+          }
+        if (leader && b == 1) tc_commit(bar_qempty + 8 * s);
+        if (leader && u + 1 == U) tc_commit(bar_done);
         if (u + 2 < U) {
           if (b == 0) {
             const int it1 = (u + 2) >> 1;
-            if (!mbar_wait(bar_qfull + 8 * (it1 & 1), (it1 >> 1) & 1, KID, 23)) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_qfull + 8 * (it1 & 1), (it1 >> 1) & 1, KID, 23))) break;
             tc_fence_after();
           }
           issue_st(u + 2);
         }
       }
+      __syncwarp();
     }
   } else {
     const int b = warp >> 2;   // which 64-query half this group handles

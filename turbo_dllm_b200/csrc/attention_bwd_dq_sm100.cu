@@ -153,7 +153,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
     }
   } else if (warp == 9) {
-    if (lane == 0 && n > 0) {
+    // whole warp, identical values; one elected lane issues (keeps descriptors in uniform registers)
+    if (n > 0) {
+      const bool leader = elect_one();
       const uint32_t idesc_s = make_idesc_bf16(BQ, SUB, 0, 0);   // [128 q] x [64 keys], K = d
       const uint32_t idesc_dq = make_idesc_bf16(BQ, HD, 0, 1);   // [128 q] x [128 d],  K = keys
       auto issue_s_dp = [&](int i, int s) {
@@ -165,52 +167,61 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t qoff = (k >> 2) * QHALF_BYTES + (k & 3) * 32;
           const uint32_t koff = (k >> 2) * KHALF_BYTES + (k & 3) * 32;
-          tc_mma_ss(tmem_base + i * 128, make_smem_desc_sw128(qa + qoff, 16, 1024),
-                    make_smem_desc_sw128(ka + koff, 16, 1024), idesc_s, k ? 1u : 0u);
+          {
+            const uint64_t ad_ = make_smem_desc_sw128(qa + qoff, 16, 1024);
+            const uint64_t bd_ = make_smem_desc_sw128(ka + koff, 16, 1024);
+            if (leader) tc_mma_ss(tmem_base + i * 128, ad_, bd_, idesc_s, k ? 1u : 0u);
+          }
         }
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t qoff = (k >> 2) * QHALF_BYTES + (k & 3) * 32;
           const uint32_t koff = (k >> 2) * KHALF_BYTES + (k & 3) * 32;
-          tc_mma_ss(tmem_base + i * 128 + 64, make_smem_desc_sw128(da + qoff, 16, 1024),
-                    make_smem_desc_sw128(va + koff, 16, 1024), idesc_s, k ? 1u : 0u);
+          {
+            const uint64_t ad_ = make_smem_desc_sw128(da + qoff, 16, 1024);
+            const uint64_t bd_ = make_smem_desc_sw128(va + koff, 16, 1024);
+            if (leader) tc_mma_ss(tmem_base + i * 128 + 64, ad_, bd_, idesc_s, k ? 1u : 0u);
+          }
         }
-        tc_commit(bar_sfull + 8 * i);
+        if (leader) tc_commit(bar_sfull + 8 * i);
       };
-      bool ok = mbar_wait(bar_q, 0, KID, 20) && mbar_wait(bar_kfull, 0, KID, 21) &&
-                mbar_wait(bar_vfull, 0, KID, 22);
+      bool ok = __all_sync(0xffffffffu, mbar_wait(bar_q, 0, KID, 20)) && __all_sync(0xffffffffu, mbar_wait(bar_kfull, 0, KID, 21)) &&
+                __all_sync(0xffffffffu, mbar_wait(bar_vfull, 0, KID, 22));
       if (ok) {
         tc_fence_after();
         issue_s_dp(0, 0);
         issue_s_dp(1, 0);
-        tc_commit(bar_vempty);
+        if (leader) tc_commit(bar_vempty);
       }
       for (int u = 0; u < U && ok; ++u) {
         const int s = u & 1;
         const uint32_t ka = smem_u32(sK + s * KSUB_BYTES);
         for (int i = 0; i < 2; ++i) {
-          if (!mbar_wait(bar_pfull + 8 * i, u & 1, KID, 23)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_pfull + 8 * i, u & 1, KID, 23))) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < SUB / 16; ++k)
-            tc_mma_ts(tmem_base + 256 + i * 128, tmem_base + i * 128 + k * 8,
-                      make_smem_desc_sw128(ka + k * 2048, KHALF_BYTES, 1024), idesc_dq,
+            {
+              const uint64_t bd_ = make_smem_desc_sw128(ka + k * 2048, KHALF_BYTES, 1024);
+              if (leader) tc_mma_ts(tmem_base + 256 + i * 128, tmem_base + i * 128 + k * 8, bd_, idesc_dq,
                       (u | k) ? 1u : 0u);
-          if (u + 1 == U) tc_commit(bar_odone + 8 * i);
-          if (i == 1) tc_commit(bar_kempty + 8 * s);
+            }
+          if (leader && u + 1 == U) tc_commit(bar_odone + 8 * i);
+          if (leader && i == 1) tc_commit(bar_kempty + 8 * s);
           if (u + 1 < U) {
             const int s1 = (u + 1) & 1;
             if (i == 0) {
               const uint32_t ph1 = ((u + 1) >> 1) & 1;
-              if (!mbar_wait(bar_kfull + 8 * s1, ph1, KID, 24) ||
-                  !mbar_wait(bar_vfull + 8 * s1, ph1, KID, 25)) { ok = false; break; }
+              if (!__all_sync(0xffffffffu, mbar_wait(bar_kfull + 8 * s1, ph1, KID, 24)) ||
+                  !__all_sync(0xffffffffu, mbar_wait(bar_vfull + 8 * s1, ph1, KID, 25))) { ok = false; break; }
               tc_fence_after();
             }
             issue_s_dp(i, s1);
-            if (i == 1) tc_commit(bar_vempty + 8 * s1);
+            if (leader && i == 1) tc_commit(bar_vempty + 8 * s1);
           }
         }
       }
+      __syncwarp();
     }
   } else {
     const int i = warp >> 2;

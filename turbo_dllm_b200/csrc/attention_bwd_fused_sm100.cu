@@ -13,8 +13,8 @@
 // added to an fp32 accumulator in global memory with warp-coalesced reductions (lanes = d).
 // A small kernel afterwards casts the accumulator to bf16.
 //
-// TMEM, per half b at column 128·b: [0,64) Sᵀ fp32, rewritten in place as Pᵀ bf16 [0,32) and
-// dSᵀ bf16 [32,64) (A operands of the dV and dK products); [64,128) dPᵀ fp32, reused as the
+// TMEM, per half b at column 128·b: [0,64) Sᵀ fp32, rewritten in place as bf16 (per 32-query group:
+// Pᵀ in 16 columns, dSᵀ in the next 16; A operands of the dV and dK products); [64,128) dPᵀ fp32, reused as the
 // dQᵀ accumulator once its values are in registers. dV at 256, dK at 384. dSᵀ also goes to
 // shared memory as bf16 (one 128-byte swizzled row of 64 queries per key): the B operand of
 // the dQᵀ product, whose A operand is the K tile read MN-major (same bytes as the Sᵀ product).
@@ -33,7 +33,7 @@ constexpr int KID = 5;
 constexpr int HD = 128;
 constexpr int TILE_BYTES = 128 * HD * 2;  // 32 KiB
 constexpr int HALF_BYTES = TILE_BYTES / 2;
-constexpr int THREADS = 320;
+constexpr int THREADS = 576;   // 16 exponentiation warps (4 groups), TMA warp 16, MMA warp 17
 constexpr int ROWSTAT_BYTES = 2 * 2 * 128 * 4;  // 2 stages x (lse2[128], delta_s[128])
 // no alignment slack: the kernel checks that its dynamic shared memory starts 1 KiB aligned
 constexpr int SMEM_BYTES = 6 * TILE_BYTES + 2 * HALF_BYTES + 512 + ROWSTAT_BYTES;
@@ -115,15 +115,15 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       mbar_init(bar_qfull + 8 * s, 1);
       mbar_init(bar_qempty + 8 * s, 1);
       mbar_init(bar_sfull + 8 * s, 1);
-      mbar_init(bar_pfull + 8 * s, 128);
-      mbar_init(bar_epi + 8 * s, 128);
+      mbar_init(bar_pfull + 8 * s, 256);
+      mbar_init(bar_epi + 8 * s, 256);
       mbar_init(bar_dqfull + 8 * s, 1);
-      mbar_init(bar_dqread + 8 * s, 128);
+      mbar_init(bar_dqread + 8 * s, 256);
     }
     mbar_init(bar_done, 1);
     fence_mbar_init();
   }
-  if (warp == 9) {
+  if (warp == 17) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
@@ -133,7 +133,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
   // columns: ST_b at b*128, dPT_b / dQT_b at b*128+64 (b = half), dV at 256, dK at 384
 
-  if (warp == 8) {
+  if (warp == 16) {
     if (lane == 0 && items > 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_do);
@@ -162,12 +162,19 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
       }
     }
-  } else if (warp == 9) {
-    if (lane == 0 && items > 0) {
+  } else if (warp == 17) {
+    // The whole warp runs this loop with identical values and one elected lane issues: descriptors
+    // then live in uniform registers. Issuing from a divergent `lane == 0` branch costs about 130
+    // cycles per MMA on the issuing thread (measured), more than these small MMAs take to execute.
+    if (items > 0) {
+      const bool leader = elect_one();
       const uint32_t idesc_st = make_idesc_bf16(128, 64, 0, 0);    // [128 keys] x [64 q], K = d
       const uint32_t idesc_acc = make_idesc_bf16(128, HD, 0, 1);   // [128 keys] x [128 d], K = q
       const uint32_t idesc_dq = make_idesc_bf16(HD, 64, 1, 1);     // [128 d] x [64 q], K = keys
       const uint32_t ka = smem_u32(sK), va = smem_u32(sV), sa = smem_u32(sdS);
+      auto wait_all = [&](uint32_t bar, uint32_t parity, int detail) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, KID, detail));
+      };
       // half-tile u: item u>>1, query rows 64*(u&1).. of that item's tile
       auto issue_s = [&](int u) {
         const int s = (u >> 1) & 1, b = u & 1;
@@ -175,24 +182,26 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          tc_mma_ss(tmem_base + b * 128, make_smem_desc_sw128(ka + off, 16, 1024),
-                    make_smem_desc_sw128(qa + off, 16, 1024), idesc_st, k ? 1u : 0u);
+          const uint64_t ad = make_smem_desc_sw128(ka + off, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(qa + off, 16, 1024);
+          if (leader) tc_mma_ss(tmem_base + b * 128, ad, bd, idesc_st, k ? 1u : 0u);
         }
       };
       // dPᵀ overwrites the columns that held the previous dQᵀ of this half: issue only after
-      // the half's warp group has read that dQᵀ back. Completes the pair (Sᵀ, dPᵀ) of unit u.
+      // the half's warp groups have read that dQᵀ back. Completes the pair (Sᵀ, dPᵀ) of unit u.
       auto issue_dp = [&](int u) {
         const int s = (u >> 1) & 1, b = u & 1;
         const uint32_t da = smem_u32(sdO + s * TILE_BYTES) + b * 64 * 128;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          tc_mma_ss(tmem_base + b * 128 + 64, make_smem_desc_sw128(va + off, 16, 1024),
-                    make_smem_desc_sw128(da + off, 16, 1024), idesc_st, k ? 1u : 0u);
+          const uint64_t ad = make_smem_desc_sw128(va + off, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(da + off, 16, 1024);
+          if (leader) tc_mma_ss(tmem_base + b * 128 + 64, ad, bd, idesc_st, k ? 1u : 0u);
         }
-        tc_commit(bar_sfull + 8 * b);
+        if (leader) tc_commit(bar_sfull + 8 * b);
       };
-      bool ok = mbar_wait(bar_kv, 0, KID, 20) && mbar_wait(bar_qfull, 0, KID, 21);
+      bool ok = wait_all(bar_kv, 0, 20) && wait_all(bar_qfull, 0, 21);
       if (ok) {
         tc_fence_after();
         issue_s(0);
@@ -202,69 +211,77 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       }
       for (int u = 0; u < U && ok; ++u) {
         const int s = (u >> 1) & 1, b = u & 1;
-        if (!mbar_wait(bar_pfull + 8 * b, (u >> 1) & 1, KID, 22)) break;
+        if (!wait_all(bar_pfull + 8 * b, (u >> 1) & 1, 22)) break;
         tc_fence_after();
         const uint32_t qa = smem_u32(sQ + s * TILE_BYTES) + b * 64 * 128;
         const uint32_t da = smem_u32(sdO + s * TILE_BYTES) + b * 64 * 128;
+        // dQᵀ first: its read-back by the warp groups then overlaps the dV and dK products, and
+        // the next dPᵀ of this half (which reuses the columns) can follow in the same round
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ts(tmem_base + 256, tmem_base + b * 128 + k * 8,
-                    make_smem_desc_sw128(da + k * 2048, HALF_BYTES, 1024), idesc_acc,
-                    (u | k) ? 1u : 0u);
+        for (int k = 0; k < 8; ++k) {
+          const uint64_t ad = make_smem_desc_sw128(ka + k * 2048, HALF_BYTES, 1024);
+          const uint64_t bd = make_smem_desc_sw128(sa + b * HALF_BYTES + k * 2048, HALF_BYTES, 1024);
+          if (leader) tc_mma_ss(tmem_base + b * 128 + 64, ad, bd, idesc_dq, k ? 1u : 0u);
+        }
+        if (leader) tc_commit(bar_dqfull + 8 * b);
+        // A operands in TMEM: queries 16k..16k+15 of the half sit in 8 columns; the two 32-query
+        // groups of a half each own 32 columns (Pᵀ in the first 16, dSᵀ in the last 16)
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ts(tmem_base + 384, tmem_base + b * 128 + 32 + k * 8,
-                    make_smem_desc_sw128(qa + k * 2048, HALF_BYTES, 1024), idesc_acc,
-                    (u | k) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t bd = make_smem_desc_sw128(da + k * 2048, HALF_BYTES, 1024);
+          if (leader)
+            tc_mma_ts(tmem_base + 256, tmem_base + b * 128 + (k >> 1) * 32 + (k & 1) * 8, bd, idesc_acc,
+                      (u | k) ? 1u : 0u);
+        }
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          tc_mma_ss(tmem_base + b * 128 + 64, make_smem_desc_sw128(ka + k * 2048, HALF_BYTES, 1024),
-                    make_smem_desc_sw128(sa + b * HALF_BYTES + k * 2048, HALF_BYTES, 1024), idesc_dq,
-                    k ? 1u : 0u);
-        tc_commit(bar_dqfull + 8 * b);
-        if (b == 1) tc_commit(bar_qempty + 8 * s);
-        if (u + 1 == U) tc_commit(bar_done);
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t bd = make_smem_desc_sw128(qa + k * 2048, HALF_BYTES, 1024);
+          if (leader)
+            tc_mma_ts(tmem_base + 384, tmem_base + b * 128 + 16 + (k >> 1) * 32 + (k & 1) * 8, bd, idesc_acc,
+                      (u | k) ? 1u : 0u);
+        }
+        if (leader) {
+          if (b == 1) tc_commit(bar_qempty + 8 * s);
+          if (u + 1 == U) tc_commit(bar_done);
+        }
         if (u + 2 < U) {
           if (b == 0) {
             const int it1 = (u + 2) >> 1;
-            if (!mbar_wait(bar_qfull + 8 * (it1 & 1), (it1 >> 1) & 1, KID, 23)) break;
+            if (!wait_all(bar_qfull + 8 * (it1 & 1), (it1 >> 1) & 1, 23)) break;
             tc_fence_after();
           }
           issue_s(u + 2);
-        }
-        // unit u+1 (the other half): its Sᵀ was issued one round ago; dPᵀ follows once that
-        // half's previous dQᵀ (unit u-1) has been read back, which had a whole round to happen
-        if (u >= 1 && u + 1 < U) {
-          if (!mbar_wait(bar_dqread + 8 * (b ^ 1), ((u - 1) >> 1) & 1, KID, 24)) break;
+          if (!wait_all(bar_dqread + 8 * b, (u >> 1) & 1, 24)) break;
           tc_fence_after();
-          issue_dp(u + 1);
+          issue_dp(u + 2);
         }
       }
+      __syncwarp();
     }
   } else {
-    const int b = warp >> 2;   // which 64-query half this group handles
+    // four groups of four warps: half b of the query tile, and within it 32 of the 64 queries
+    const int b = warp >> 3;
+    const int sub = (warp >> 2) & 1;
     const int qd = warp & 3;
     const int row = qd * 32 + lane;   // key row inside the tile
     const int kcode = p.k_code[kt * 128 + row];
     const uint32_t t_s = tmem_base + ((uint32_t)(qd * 32) << 16) + b * 128;
-    uint32_t rs[64], rp[64];
+    uint32_t rs[32], rp[32];
     bool ok = true;
     for (int it = 0; it < items; ++it) {
       const int ent = list[it % n];
-      const int qrow0 = (ent >> 1) * 128 + b * 64;
-      const float* sl = sStat + (it & 1) * 256 + b * 64;   // lse2 of this half's 64 queries
-      const float* sd = sl + 128;                          // delta_s
+      const int qrow0 = (ent >> 1) * 128 + b * 64 + sub * 32;
+      const float* sl = sStat + (it & 1) * 256 + b * 64 + sub * 32;   // lse2 of this group's 32 queries
+      const float* sd = sl + 128;                                     // delta_s
       if (!mbar_wait(bar_sfull + 8 * b, it & 1, KID, 30)) { ok = false; break; }
       tc_fence_after();
-      tmem_ld32(t_s, rs);
-      tmem_ld32(t_s + 32, rs + 32);
-      tmem_ld32(t_s + 64, rp);
-      tmem_ld32(t_s + 96, rp + 32);
+      tmem_ld32(t_s + sub * 32, rs);
+      tmem_ld32(t_s + 64 + sub * 32, rp);
       tmem_ld_wait();
-      uint32_t pk[32], dk[32];
+      uint32_t pk[16], dk[16];
       if (ent & 1) {
 #pragma unroll
-        for (int e = 0; e < 64; e += 4) {
+        for (int e = 0; e < 32; e += 4) {
           const float4 l4 = *reinterpret_cast<const float4*>(sl + e);
           const float4 d4 = *reinterpret_cast<const float4*>(sd + e);
           const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
@@ -285,7 +302,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
       } else {
 #pragma unroll
-        for (int e = 0; e < 64; e += 4) {
+        for (int e = 0; e < 32; e += 4) {
           const float4 l4 = *reinterpret_cast<const float4*>(sl + e);
           const float4 d4 = *reinterpret_cast<const float4*>(sd + e);
           const float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -l4.x));
@@ -300,15 +317,15 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                                          p3 * fmaf(__uint_as_float(rp[e + 3]), p.scale, -d4.w));
         }
       }
-      tmem_st16(t_s, pk);
-      tmem_st16(t_s + 16, pk + 16);
-      tmem_st16(t_s + 32, dk);
-      tmem_st16(t_s + 48, dk + 16);
+      // in place over the 32 Sᵀ columns this group has just read (the other group of the half may
+      // still be reading its own): Pᵀ in the first 16, dSᵀ in the last 16
+      tmem_st16(t_s + sub * 32, pk);
+      tmem_st16(t_s + sub * 32 + 16, dk);
       {
         uint8_t* srow = sdS + b * HALF_BYTES;   // this key's 64 queries: one swizzled 128-byte row
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<uint4*>(srow + sw128_offset(row, j)) =
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(srow + sw128_offset(row, sub * 4 + j)) =
               make_uint4(dk[4 * j], dk[4 * j + 1], dk[4 * j + 2], dk[4 * j + 3]);
       }
       tmem_st_wait();
@@ -318,8 +335,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       // dQᵀ of this (half, key tile): lanes = d, columns = the half's 64 queries
       if (!mbar_wait(bar_dqfull + 8 * b, it & 1, KID, 33)) { ok = false; break; }
       tc_fence_after();
-      tmem_ld32(t_s + 64, rs);
-      tmem_ld32(t_s + 96, rs + 32);
+      tmem_ld32(t_s + 64 + sub * 32, rs);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(bar_dqread + 8 * b);
@@ -328,17 +344,17 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         float* dst = p.dq_acc + ((size_t)qrow0 * p.Hq + h) * HD + row;
         const size_t step = (size_t)p.Hq * HD;
 #pragma unroll
-        for (int j = 0; j < 64; ++j) atomicAdd(dst + j * step, __uint_as_float(rs[j]));
+        for (int j = 0; j < 32; ++j) atomicAdd(dst + j * step, __uint_as_float(rs[j]));
       }
     }
-    // epilogue: group 0 stores dV, group 1 stores dK
+    // epilogue: half 0's groups store dV, half 1's store dK; each group converts 64 of the 128 columns
     if (ok && items > 0) ok = mbar_wait(bar_done, 0, KID, 31);
     if (ok) {
       tc_fence_after();
       const uint32_t t_acc = tmem_base + ((uint32_t)(qd * 32) << 16) + 256 + b * 128;
       uint8_t* st = sQ + b * TILE_BYTES;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * sub; c < 2 * sub + 2; ++c) {
         if (items > 0) {
           tmem_ld32(t_acc + c * 32, rs);
           tmem_ld_wait();
@@ -359,7 +375,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       }
       fence_proxy_async_smem();
       mbar_arrive(bar_epi + 8 * b);
-      if (row == 0) {
+      if (row == 0 && sub == 0) {
         if (mbar_wait(bar_epi + 8 * b, 0, KID, 32)) {
           const CUtensorMap* tm = b ? &tm_dk : &tm_dv;
 #pragma unroll
@@ -379,7 +395,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 9) {
+  if (warp == 17) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);

@@ -168,53 +168,64 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else if (warp == 9) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0 && n > 0) {
+    // whole warp, identical values, one elected lane issues (descriptors stay in uniform registers;
+    // issuing from a divergent lane-0 branch costs ~130 cycles per MMA on the issuing thread)
+    if (n > 0) {
+      const bool leader = elect_one();
       const uint32_t idesc_qk = make_idesc_bf16(BQ, BKV, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(BQ, HD, 0, 1);
+      auto wait_all = [&](uint32_t bar, uint32_t parity, int detail) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, KID, detail));
+      };
       auto issue_qk = [&](int i, int s) {
         const uint32_t qa = smem_u32(sQ + i * TILE_BYTES);
         const uint32_t ka = smem_u32(sK + s * TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          tc_mma_ss(tmem_base + i * 128, make_smem_desc_sw128(qa + off, 16, 1024),
-                    make_smem_desc_sw128(ka + off, 16, 1024), idesc_qk, k ? 1u : 0u);
+          const uint64_t ad = make_smem_desc_sw128(qa + off, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(ka + off, 16, 1024);
+          if (leader) tc_mma_ss(tmem_base + i * 128, ad, bd, idesc_qk, k ? 1u : 0u);
         }
-        tc_commit(bar_sfull + 8 * i);
+        if (leader) tc_commit(bar_sfull + 8 * i);
       };
-      bool ok = mbar_wait(bar_q, 0, KID, 20) && mbar_wait(bar_kfull, 0, KID, 21);
+      bool ok = wait_all(bar_q, 0, 20) && wait_all(bar_kfull, 0, 21);
       if (ok) {
         tc_fence_after();
         issue_qk(0, 0);
         issue_qk(1, 0);
-        tc_commit(bar_kempty);
+        if (leader) tc_commit(bar_kempty);
       }
       for (int j = 0; j < n && ok; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(bar_vfull + 8 * s, ph, KID, 22)) break;
+        if (!wait_all(bar_vfull + 8 * s, ph, 22)) break;
         const uint32_t va = smem_u32(sV + s * TILE_BYTES);
         for (int i = 0; i < 2; ++i) {
-          if (!mbar_wait(bar_pfull + 8 * i, j & 1, KID, 23)) { ok = false; break; }
+          if (!wait_all(bar_pfull + 8 * i, j & 1, 23)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < BKV / 16; ++k)
-            tc_mma_ts(tmem_base + 256 + i * 128, tmem_base + i * 128 + k * 8,
-                      make_smem_desc_sw128(va + k * 2048, HALF_BYTES, 1024), idesc_pv,
-                      (j | k) ? 1u : 0u);
-          if (j + 1 == n) tc_commit(bar_odone + 8 * i);
-          if (i == 1) tc_commit(bar_vempty + 8 * s);
+          for (int k = 0; k < BKV / 16; ++k) {
+            const uint64_t bd = make_smem_desc_sw128(va + k * 2048, HALF_BYTES, 1024);
+            if (leader)
+              tc_mma_ts(tmem_base + 256 + i * 128, tmem_base + i * 128 + k * 8, bd, idesc_pv, (j | k) ? 1u : 0u);
+          }
+          if (leader) {
+            if (j + 1 == n) tc_commit(bar_odone + 8 * i);
+            if (i == 1) tc_commit(bar_vempty + 8 * s);
+          }
           if (j + 1 < n) {
             const int s1 = (j + 1) & 1;
             if (i == 0) {
-              if (!mbar_wait(bar_kfull + 8 * s1, ((j + 1) >> 1) & 1, KID, 24)) { ok = false; break; }
+              if (!wait_all(bar_kfull + 8 * s1, ((j + 1) >> 1) & 1, 24)) { ok = false; break; }
               tc_fence_after();
             }
             issue_qk(i, s1);
-            if (i == 1) tc_commit(bar_kempty + 8 * s1);
+            if (i == 1 && leader) tc_commit(bar_kempty + 8 * s1);
           }
         }
       }
+      __syncwarp();
     }
   } else {
     // ------------------------------ softmax groups -----------------------------

@@ -162,7 +162,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+    // whole warp with identical values; one elected lane issues, so that the descriptors stay in
+    // uniform registers (a divergent lane-0 branch makes every MMA cost ~130 cycles to issue)
+    {
+      const bool leader = elect_one();
       const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn_major, p.b_mn_major);
       int stage = 0;
       uint32_t phase = 0;
@@ -171,11 +174,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
         const int buf = it & 1;
         const uint32_t tphase = (it >> 1) & 1;
-        if (!mbar_wait(bar_tempty + 8 * buf, tphase ^ 1, GEMM_KERNEL_ID, 20)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * buf, tphase ^ 1, GEMM_KERNEL_ID, 20))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, GEMM_KERNEL_ID, 21)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * stage, phase, GEMM_KERNEL_ID, 21))) {
             ok = false;
             break;
           }
@@ -192,16 +195,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint64_t bd = p.b_mn_major
                                     ? make_smem_desc_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024)
                                     : make_smem_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
-            tc_mma_ss(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+            if (leader) tc_mma_ss(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
           }
-          tc_commit(bar_empty + 8 * stage);
+          if (leader) tc_commit(bar_empty + 8 * stage);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) tc_commit(bar_tfull + 8 * buf);
+        if (ok && leader) tc_commit(bar_tfull + 8 * buf);
       }
+      __syncwarp();
     }
   } else {
     // ------------------------------ epilogue warps ----------------------------
