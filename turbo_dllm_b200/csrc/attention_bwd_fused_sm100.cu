@@ -1,23 +1,28 @@
 // Block-diffusion attention backward in one pass (sm_100a, head_dim 128): dK, dV and dQ.
 //
 // One CTA owns one 128-row key tile of one KV head and walks every (query head of the
-// group, visible query tile) pair. Everything is computed transposed (keys on the TMEM
-// lanes), in 64-query halves that two warp groups handle in alternation:
+// group, visible query tile) pair in units of 64 queries. Everything is computed transposed
+// (keys on the TMEM lanes):
 //   Sᵀ  = K·Qᵀ   (128 keys x 64 queries)      dPᵀ = V·dOᵀ
 //   Pᵀ  = exp(Sᵀ·scale − lse[q])              dSᵀ = Pᵀ∘(dPᵀ − delta[q])·scale
 //   dV += Pᵀ·dO        dK += dSᵀ·Q            dQᵀ = Kᵀ·dSᵀ   (128 d x 64 queries)
 // Five tensor-core products per tile pair: the score and dP tiles are computed once and
 // feed all three gradients (separate dQ and dK/dV kernels need seven). dK/dV accumulate in
-// TMEM over the whole walk (the GQA sum over query heads included) and are stored once;
-// dQᵀ of one pair is a partial sum over this key tile only, so it is read back from TMEM and
-// added to an fp32 accumulator in global memory with warp-coalesced reductions (lanes = d).
-// A small kernel afterwards casts the accumulator to bf16.
+// TMEM over the whole walk (the GQA sum over query heads included) and are stored once.
+// dQᵀ of one unit is a partial sum over this key tile only: it is read back from TMEM, staged
+// in shared memory as [query][d] fp32 and added to an fp32 accumulator in global memory by
+// TMA reduce-add copies (16 query rows of 512 bytes per copy). A small kernel afterwards
+// casts the accumulator to bf16.
 //
-// TMEM, per half b at column 128·b: [0,64) Sᵀ fp32, rewritten in place as bf16 (per 32-query group:
-// Pᵀ in 16 columns, dSᵀ in the next 16; A operands of the dV and dK products); [64,128) dPᵀ fp32, reused as the
-// dQᵀ accumulator once its values are in registers. dV at 256, dK at 384. dSᵀ also goes to
-// shared memory as bf16 (one 128-byte swizzled row of 64 queries per key): the B operand of
-// the dQᵀ product, whose A operand is the K tile read MN-major (same bytes as the Sᵀ product).
+// Warps: 0-15 do the element-wise work as four groups of four (unit parity b = warp/8, 32 of the
+// unit's 64 queries each), warp 16 issues TMA loads, warp 17 issues the MMAs. Units alternate
+// between two TMEM slots, so the exponentials of one unit overlap the products of the other.
+//
+// TMEM, per slot b at column 128·b: [0,64) Sᵀ fp32, rewritten in place as bf16 (per 32-query group:
+// Pᵀ in 16 columns, dSᵀ in the next 16; A operands of the dV and dK products); [64,128) dPᵀ fp32,
+// reused as the dQᵀ accumulator once its values are in registers. dV at 256, dK at 384. dSᵀ also
+// goes to shared memory as bf16 (one 128-byte swizzled row of 64 queries per key): the B operand
+// of the dQᵀ product, whose A operand is the K tile read MN-major (same bytes as the Sᵀ product).
 //
 // Reference counterpart: the masked FlashAttention backward
 // (third_party/flash-attention/hopper/mainloop_bwd_sm90_tma_gmma_ws.hpp, FA4
@@ -31,12 +36,23 @@ namespace attn_fused {
 
 constexpr int KID = 5;
 constexpr int HD = 128;
-constexpr int TILE_BYTES = 128 * HD * 2;  // 32 KiB
-constexpr int HALF_BYTES = TILE_BYTES / 2;
-constexpr int THREADS = 576;   // 16 exponentiation warps (4 groups), TMA warp 16, MMA warp 17
-constexpr int ROWSTAT_BYTES = 2 * 2 * 128 * 4;  // 2 stages x (lse2[128], delta_s[128])
+constexpr int KV_TILE_BYTES = 128 * HD * 2;   // 32 KiB: 128 keys, two 64-column halves
+constexpr int KV_HALF_BYTES = KV_TILE_BYTES / 2;
+constexpr int QS_BYTES = 64 * HD * 2;         // 16 KiB: 64 queries of Q (or dO), two 64-column halves
+constexpr int QS_HALF_BYTES = QS_BYTES / 2;
+constexpr int STAGES = 3;
+constexpr int DS_BYTES = 128 * 64 * 2;        // 16 KiB: dSᵀ of one unit, [128 keys][64 queries] bf16
+constexpr int RED_BYTES = 16 * HD * 4;        // 8 KiB per group: 16 query rows of dQ, fp32
+constexpr int THREADS = 576;
+constexpr int OFF_Q = 2 * KV_TILE_BYTES;
+constexpr int OFF_DO = OFF_Q + STAGES * QS_BYTES;
+constexpr int OFF_DS = OFF_DO + STAGES * QS_BYTES;
+constexpr int OFF_RED = OFF_DS + 2 * DS_BYTES;
+constexpr int OFF_BARS = OFF_RED + 4 * RED_BYTES;
+constexpr int OFF_STAT = OFF_BARS + 512;      // [stage][lse2 64 | delta_s 64] fp32
 // no alignment slack: the kernel checks that its dynamic shared memory starts 1 KiB aligned
-constexpr int SMEM_BYTES = 6 * TILE_BYTES + 2 * HALF_BYTES + 512 + ROWSTAT_BYTES;
+constexpr int SMEM_BYTES = OFF_STAT + STAGES * 128 * 4;
+static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
 
 struct Params {
   int nq_pad, Hq, Hkv;
@@ -49,7 +65,6 @@ struct Params {
   const int* order;     // key tiles, heaviest first
   const float* lse2;   // [Hq, nq_pad] lse·log2e (+inf = row without keys)
   const float* delta;  // [Hq, nq_pad] scale · rowsum(dO∘O)
-  float* dq_acc;       // [nq_pad, Hq, 128] fp32, zeroed by the caller
   float scale_log2, scale;
 };
 
@@ -70,33 +85,46 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
 __device__ __forceinline__ bool key_visible(int code, int lo, int hi, int grp) {
   return code >= 0 ? (code >= lo && code < hi) : (code == grp);
 }
+// barrier among `nthreads` threads that also ANDs a predicate over them
+__device__ __forceinline__ bool named_bar_all(int id, int nthreads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %3, 0;\n\t"
+      "bar.red.and.pred q, %1, %2, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
+}
 
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-                    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                    const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
-                    const Params p) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = smem_raw;
-  if (smem_u32(smem_raw) & 1023u) {   // swizzled tiles need 1 KiB alignment; nothing has been set up yet
+                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                      const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
+                      const __grid_constant__ CUtensorMap tm_dqacc, const Params p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {   // swizzled tiles need 1 KiB alignment; nothing has been set up yet
     if (threadIdx.x == 0) set_error(ERR_BAD_INDEX, KID, 1);
     return;
   }
   uint8_t* sK = smem;
-  uint8_t* sV = sK + TILE_BYTES;
-  uint8_t* sQ = sV + TILE_BYTES;        // 2 stages
-  uint8_t* sdO = sQ + 2 * TILE_BYTES;   // 2 stages
-  uint8_t* sdS = sdO + 2 * TILE_BYTES;  // [half][128 keys][64 queries] bf16
-  uint64_t* bars = (uint64_t*)(sdS + 2 * HALF_BYTES);
+  uint8_t* sV = sK + KV_TILE_BYTES;
+  uint8_t* sQ = smem + OFF_Q;     // [stage]
+  uint8_t* sdO = smem + OFF_DO;   // [stage]
+  uint8_t* sdS = smem + OFF_DS;   // [slot]
+  uint8_t* sRed = smem + OFF_RED; // [group]
+  uint64_t* bars = (uint64_t*)(smem + OFF_BARS);
+  float* sStat = (float*)(smem + OFF_STAT);
   const uint32_t b0 = smem_u32(bars);
   const uint32_t bar_kv = b0;
-  const uint32_t bar_qfull = b0 + 8, bar_qempty = b0 + 24;
-  const uint32_t bar_sfull = b0 + 40, bar_pfull = b0 + 56;
-  const uint32_t bar_done = b0 + 72;
-  const uint32_t bar_epi = b0 + 80;  // [2]
-  const uint32_t bar_dqfull = b0 + 96, bar_dqread = b0 + 112;  // [2] each
-  uint32_t* tmem_slot = (uint32_t*)(bars + 16);
-  float* sStat = (float*)((uint8_t*)bars + 512);  // [stage][lse2 128 | delta_s 128]
+  const uint32_t bar_qfull = b0 + 8, bar_qempty = b0 + 32;            // [3] each
+  const uint32_t bar_sfull = b0 + 56, bar_pfull = b0 + 72;            // [2] each
+  const uint32_t bar_dqfull = b0 + 88, bar_dqread = b0 + 104;         // [2] each
+  const uint32_t bar_done = b0 + 120;
+  const uint32_t bar_epi = b0 + 128;                                  // [2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 20);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -107,18 +135,20 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int n = p.tile_ptr[kt + 1] - list_begin;
   const int* list = p.tile_idx + list_begin;
   const int items = G * n;   // (query head, query tile) pairs
-  const int U = 2 * items;   // 64-query halves
+  const int U = 2 * items;   // 64-query units
 
   if (threadIdx.x == 0) {
     mbar_init(bar_kv, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_qfull + 8 * s, 1);
       mbar_init(bar_qempty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(bar_sfull + 8 * s, 1);
       mbar_init(bar_pfull + 8 * s, 256);
-      mbar_init(bar_epi + 8 * s, 256);
       mbar_init(bar_dqfull + 8 * s, 1);
       mbar_init(bar_dqread + 8 * s, 256);
+      mbar_init(bar_epi + 8 * s, 256);
     }
     mbar_init(bar_done, 1);
     fence_mbar_init();
@@ -131,34 +161,40 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // columns: ST_b at b*128, dPT_b / dQT_b at b*128+64 (b = half), dV at 256, dK at 384
+  // columns: ST_b at b*128, dPT_b / dQT_b at b*128+64 (b = unit parity), dV at 256, dK at 384
 
   if (warp == 16) {
     if (lane == 0 && items > 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_do);
-      mbar_expect_tx(bar_kv, 2 * TILE_BYTES);
+      mbar_expect_tx(bar_kv, 2 * KV_TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        tma_load_2d(smem_u32(sK + c * HALF_BYTES), &tm_k, bar_kv, kvh * HD + c * 64, kt * 128);
-        tma_load_2d(smem_u32(sV + c * HALF_BYTES), &tm_v, bar_kv, kvh * HD + c * 64, kt * 128);
+        tma_load_2d(smem_u32(sK + c * KV_HALF_BYTES), &tm_k, bar_kv, kvh * HD + c * 64, kt * 128);
+        tma_load_2d(smem_u32(sV + c * KV_HALF_BYTES), &tm_v, bar_kv, kvh * HD + c * 64, kt * 128);
       }
-      for (int it = 0; it < items; ++it) {
-        const int s = it & 1;
+      int st = 0;
+      uint32_t ph = 0;
+      for (int u = 0; u < U; ++u) {
+        const int it = u >> 1, b = u & 1;
         const int h = kvh * G + it / n;
-        const int qt = list[it % n] >> 1;
-        if (!mbar_wait(bar_qempty + 8 * s, ((it >> 1) & 1) ^ 1, KID, 10)) break;
-        mbar_expect_tx(bar_qfull + 8 * s, 2 * TILE_BYTES + 1024);
-        bulk_load_1d(smem_u32(sStat + s * 256), p.lse2 + (size_t)h * p.nq_pad + qt * 128, 512,
-                     bar_qfull + 8 * s);
-        bulk_load_1d(smem_u32(sStat + s * 256 + 128), p.delta + (size_t)h * p.nq_pad + qt * 128, 512,
-                     bar_qfull + 8 * s);
+        const int qrow = (list[it % n] >> 1) * 128 + b * 64;
+        if (!mbar_wait(bar_qempty + 8 * st, ph ^ 1, KID, 10)) break;
+        mbar_expect_tx(bar_qfull + 8 * st, 2 * QS_BYTES + 512);
+        bulk_load_1d(smem_u32(sStat + st * 128), p.lse2 + (size_t)h * p.nq_pad + qrow, 256,
+                     bar_qfull + 8 * st);
+        bulk_load_1d(smem_u32(sStat + st * 128 + 64), p.delta + (size_t)h * p.nq_pad + qrow, 256,
+                     bar_qfull + 8 * st);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          tma_load_2d(smem_u32(sQ + s * TILE_BYTES + c * HALF_BYTES), &tm_q, bar_qfull + 8 * s,
-                      h * HD + c * 64, qt * 128);
-          tma_load_2d(smem_u32(sdO + s * TILE_BYTES + c * HALF_BYTES), &tm_do, bar_qfull + 8 * s,
-                      h * HD + c * 64, qt * 128);
+          tma_load_2d(smem_u32(sQ + st * QS_BYTES + c * QS_HALF_BYTES), &tm_q, bar_qfull + 8 * st,
+                      h * HD + c * 64, qrow);
+          tma_load_2d(smem_u32(sdO + st * QS_BYTES + c * QS_HALF_BYTES), &tm_do, bar_qfull + 8 * st,
+                      h * HD + c * 64, qrow);
+        }
+        if (++st == STAGES) {
+          st = 0;
+          ph ^= 1;
         }
       }
     }
@@ -175,28 +211,24 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       auto wait_all = [&](uint32_t bar, uint32_t parity, int detail) {
         return __all_sync(0xffffffffu, mbar_wait(bar, parity, KID, detail));
       };
-      // half-tile u: item u>>1, query rows 64*(u&1).. of that item's tile
-      auto issue_s = [&](int u) {
-        const int s = (u >> 1) & 1, b = u & 1;
-        const uint32_t qa = smem_u32(sQ + s * TILE_BYTES) + b * 64 * 128;
+      // unit u lives in stage u % 3 and TMEM slot u & 1
+      auto issue_s = [&](int b, int st) {
+        const uint32_t qa = smem_u32(sQ + st * QS_BYTES);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          const uint64_t ad = make_smem_desc_sw128(ka + off, 16, 1024);
-          const uint64_t bd = make_smem_desc_sw128(qa + off, 16, 1024);
+          const uint64_t ad = make_smem_desc_sw128(ka + (k >> 2) * KV_HALF_BYTES + (k & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(qa + (k >> 2) * QS_HALF_BYTES + (k & 3) * 32, 16, 1024);
           if (leader) tc_mma_ss(tmem_base + b * 128, ad, bd, idesc_st, k ? 1u : 0u);
         }
       };
-      // dPᵀ overwrites the columns that held the previous dQᵀ of this half: issue only after
-      // the half's warp groups have read that dQᵀ back. Completes the pair (Sᵀ, dPᵀ) of unit u.
-      auto issue_dp = [&](int u) {
-        const int s = (u >> 1) & 1, b = u & 1;
-        const uint32_t da = smem_u32(sdO + s * TILE_BYTES) + b * 64 * 128;
+      // dPᵀ overwrites the columns that held the previous dQᵀ of this slot: issue only after the
+      // slot's warp groups have read that dQᵀ back. Completes the pair (Sᵀ, dPᵀ) of a unit.
+      auto issue_dp = [&](int b, int st) {
+        const uint32_t da = smem_u32(sdO + st * QS_BYTES);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          const uint64_t ad = make_smem_desc_sw128(va + off, 16, 1024);
-          const uint64_t bd = make_smem_desc_sw128(da + off, 16, 1024);
+          const uint64_t ad = make_smem_desc_sw128(va + (k >> 2) * KV_HALF_BYTES + (k & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(da + (k >> 2) * QS_HALF_BYTES + (k & 3) * 32, 16, 1024);
           if (leader) tc_mma_ss(tmem_base + b * 128 + 64, ad, bd, idesc_st, k ? 1u : 0u);
         }
         if (leader) tc_commit(bar_sfull + 8 * b);
@@ -204,155 +236,193 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       bool ok = wait_all(bar_kv, 0, 20) && wait_all(bar_qfull, 0, 21);
       if (ok) {
         tc_fence_after();
-        issue_s(0);
-        issue_dp(0);
-        issue_s(1);
-        issue_dp(1);
+        issue_s(0, 0);
+        issue_dp(0, 0);
+        ok = wait_all(bar_qfull + 8, 0, 21);   // U >= 2 always
       }
+      if (ok) {
+        tc_fence_after();
+        issue_s(1, 1);
+        issue_dp(1, 1);
+      }
+      int st = 0;            // stage of unit u
+      int st2 = 2;           // stage of unit u + 2
+      uint32_t ph2 = 0;      // phase of that stage's "full" barrier for unit u + 2
       for (int u = 0; u < U && ok; ++u) {
-        const int s = (u >> 1) & 1, b = u & 1;
+        const int b = u & 1;
         if (!wait_all(bar_pfull + 8 * b, (u >> 1) & 1, 22)) break;
         tc_fence_after();
-        const uint32_t qa = smem_u32(sQ + s * TILE_BYTES) + b * 64 * 128;
-        const uint32_t da = smem_u32(sdO + s * TILE_BYTES) + b * 64 * 128;
+        const uint32_t qa = smem_u32(sQ + st * QS_BYTES);
+        const uint32_t da = smem_u32(sdO + st * QS_BYTES);
         // dQᵀ first: its read-back by the warp groups then overlaps the dV and dK products, and
-        // the next dPᵀ of this half (which reuses the columns) can follow in the same round
+        // the next dPᵀ of this slot (which reuses the columns) can follow in the same round
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint64_t ad = make_smem_desc_sw128(ka + k * 2048, HALF_BYTES, 1024);
-          const uint64_t bd = make_smem_desc_sw128(sa + b * HALF_BYTES + k * 2048, HALF_BYTES, 1024);
+          const uint64_t ad = make_smem_desc_sw128(ka + k * 2048, KV_HALF_BYTES, 1024);
+          const uint64_t bd = make_smem_desc_sw128(sa + b * DS_BYTES + k * 2048, DS_BYTES, 1024);
           if (leader) tc_mma_ss(tmem_base + b * 128 + 64, ad, bd, idesc_dq, k ? 1u : 0u);
         }
         if (leader) tc_commit(bar_dqfull + 8 * b);
-        // A operands in TMEM: queries 16k..16k+15 of the half sit in 8 columns; the two 32-query
-        // groups of a half each own 32 columns (Pᵀ in the first 16, dSᵀ in the last 16)
+        // A operands in TMEM: queries 16k..16k+15 of the unit sit in 8 columns; the two 32-query
+        // groups of a unit each own 32 columns (Pᵀ in the first 16, dSᵀ in the last 16)
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint64_t bd = make_smem_desc_sw128(da + k * 2048, HALF_BYTES, 1024);
+          const uint64_t bd = make_smem_desc_sw128(da + k * 2048, QS_HALF_BYTES, 1024);
           if (leader)
             tc_mma_ts(tmem_base + 256, tmem_base + b * 128 + (k >> 1) * 32 + (k & 1) * 8, bd, idesc_acc,
                       (u | k) ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint64_t bd = make_smem_desc_sw128(qa + k * 2048, HALF_BYTES, 1024);
+          const uint64_t bd = make_smem_desc_sw128(qa + k * 2048, QS_HALF_BYTES, 1024);
           if (leader)
             tc_mma_ts(tmem_base + 384, tmem_base + b * 128 + 16 + (k >> 1) * 32 + (k & 1) * 8, bd, idesc_acc,
                       (u | k) ? 1u : 0u);
         }
         if (leader) {
-          if (b == 1) tc_commit(bar_qempty + 8 * s);
+          tc_commit(bar_qempty + 8 * st);
           if (u + 1 == U) tc_commit(bar_done);
         }
         if (u + 2 < U) {
-          if (b == 0) {
-            const int it1 = (u + 2) >> 1;
-            if (!wait_all(bar_qfull + 8 * (it1 & 1), (it1 >> 1) & 1, 23)) break;
-            tc_fence_after();
-          }
-          issue_s(u + 2);
+          if (!wait_all(bar_qfull + 8 * st2, ph2, 23)) break;
+          tc_fence_after();
+          issue_s(b, st2);
           if (!wait_all(bar_dqread + 8 * b, (u >> 1) & 1, 24)) break;
           tc_fence_after();
-          issue_dp(u + 2);
+          issue_dp(b, st2);
+        }
+        if (++st == STAGES) st = 0;
+        if (++st2 == STAGES) {
+          st2 = 0;
+          ph2 ^= 1;
         }
       }
       __syncwarp();
     }
   } else {
-    // four groups of four warps: half b of the query tile, and within it 32 of the 64 queries
+    // four groups of four warps: unit parity b, and within a unit 32 of its 64 queries
     const int b = warp >> 3;
     const int sub = (warp >> 2) & 1;
+    const int grp = warp >> 2;
     const int qd = warp & 3;
-    const int row = qd * 32 + lane;   // key row inside the tile
+    const int row = qd * 32 + lane;   // key row inside the tile (TMEM lane); d index for dQᵀ
     const int kcode = p.k_code[kt * 128 + row];
     const uint32_t t_s = tmem_base + ((uint32_t)(qd * 32) << 16) + b * 128;
-    uint32_t rs[32], rp[32];
-    bool ok = true;
+    float* red = (float*)(sRed + grp * RED_BYTES);
+    const bool issuer = (qd == 0 && lane == 0);   // issues and tracks this group's reduce-add copies
+    int st = b;   // stage of unit 2*it + b
     for (int it = 0; it < items; ++it) {
       const int ent = list[it % n];
       const int qrow0 = (ent >> 1) * 128 + b * 64 + sub * 32;
-      const float* sl = sStat + (it & 1) * 256 + b * 64 + sub * 32;   // lse2 of this group's 32 queries
-      const float* sd = sl + 128;                                     // delta_s
-      if (!mbar_wait(bar_sfull + 8 * b, it & 1, KID, 30)) { ok = false; break; }
-      tc_fence_after();
-      tmem_ld32(t_s + sub * 32, rs);
-      tmem_ld32(t_s + 64 + sub * 32, rp);
-      tmem_ld_wait();
-      uint32_t pk[16], dk[16];
-      if (ent & 1) {
+      const float* sl = sStat + st * 128 + sub * 32;   // lse2 of this group's 32 queries
+      const float* sd = sl + 64;                       // delta_s
+      bool good = __all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * b, it & 1, KID, 30));
+      if (good) {
+        tc_fence_after();
+        // two chunks of 16 queries: keeps the live registers under the 96 this block size allows
+        // (spilled values come back through L2, since nearly all of L1 is shared memory here)
+        uint32_t pk[16], dk[16];
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(sl + e);
-          const float4 d4 = *reinterpret_cast<const float4*>(sd + e);
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
-          const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pv[4], ds[4];
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rs[16], rp[16];
+          tmem_ld16(t_s + sub * 32 + c * 16, rs);
+          tmem_ld16(t_s + 64 + sub * 32 + c * 16, rp);
+          tmem_ld_wait();
+          if (ent & 1) {
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const int g = qrow0 + e + t;
-            float pr = fast_exp2(fmaf(__uint_as_float(rs[e + t]), p.scale_log2, -lv[t]));
-            if (!key_visible(kcode, __ldg(p.q_lo + g), __ldg(p.q_hi + g), __ldg(p.q_grp + g))) pr = 0.f;
-            pv[t] = pr;
-            ds[t] = pr * fmaf(__uint_as_float(rp[e + t]), p.scale, -dv[t]);
+            for (int e = 0; e < 16; e += 4) {
+              const float4 l4 = *reinterpret_cast<const float4*>(sl + c * 16 + e);
+              const float4 d4 = *reinterpret_cast<const float4*>(sd + c * 16 + e);
+              const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+              const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
+              float pv[4], ds[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                const int g = qrow0 + c * 16 + e + t;
+                float pr = fast_exp2(fmaf(__uint_as_float(rs[e + t]), p.scale_log2, -lv[t]));
+                if (!key_visible(kcode, __ldg(p.q_lo + g), __ldg(p.q_hi + g), __ldg(p.q_grp + g))) pr = 0.f;
+                pv[t] = pr;
+                ds[t] = pr * fmaf(__uint_as_float(rp[e + t]), p.scale, -dv[t]);
+              }
+              pk[c * 8 + (e >> 1)] = pack_bf16x2(pv[0], pv[1]);
+              pk[c * 8 + (e >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
+              dk[c * 8 + (e >> 1)] = pack_bf16x2(ds[0], ds[1]);
+              dk[c * 8 + (e >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; e += 4) {
+              const float4 l4 = *reinterpret_cast<const float4*>(sl + c * 16 + e);
+              const float4 d4 = *reinterpret_cast<const float4*>(sd + c * 16 + e);
+              const float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -l4.x));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, -l4.y));
+              const float p2 = fast_exp2(fmaf(__uint_as_float(rs[e + 2]), p.scale_log2, -l4.z));
+              const float p3 = fast_exp2(fmaf(__uint_as_float(rs[e + 3]), p.scale_log2, -l4.w));
+              pk[c * 8 + (e >> 1)] = pack_bf16x2(p0, p1);
+              pk[c * 8 + (e >> 1) + 1] = pack_bf16x2(p2, p3);
+              dk[c * 8 + (e >> 1)] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[e]), p.scale, -d4.x),
+                                                 p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, -d4.y));
+              dk[c * 8 + (e >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(rp[e + 2]), p.scale, -d4.z),
+                                                     p3 * fmaf(__uint_as_float(rp[e + 3]), p.scale, -d4.w));
+            }
           }
-          pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
-          pk[(e >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
-          dk[e >> 1] = pack_bf16x2(ds[0], ds[1]);
-          dk[(e >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
         }
-      } else {
+        // in place over the 32 Sᵀ columns this group has just read (the other group of the unit may
+        // still be reading its own): Pᵀ in the first 16, dSᵀ in the last 16
+        tmem_st16(t_s + sub * 32, pk);
+        tmem_st16(t_s + sub * 32 + 16, dk);
+        {
+          uint8_t* srow = sdS + b * DS_BYTES;   // this key's 64 queries: one swizzled 128-byte row
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(sl + e);
-          const float4 d4 = *reinterpret_cast<const float4*>(sd + e);
-          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -l4.x));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, -l4.y));
-          const float p2 = fast_exp2(fmaf(__uint_as_float(rs[e + 2]), p.scale_log2, -l4.z));
-          const float p3 = fast_exp2(fmaf(__uint_as_float(rs[e + 3]), p.scale_log2, -l4.w));
-          pk[e >> 1] = pack_bf16x2(p0, p1);
-          pk[(e >> 1) + 1] = pack_bf16x2(p2, p3);
-          dk[e >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[e]), p.scale, -d4.x),
-                                   p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, -d4.y));
-          dk[(e >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(rp[e + 2]), p.scale, -d4.z),
-                                         p3 * fmaf(__uint_as_float(rp[e + 3]), p.scale, -d4.w));
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(srow + sw128_offset(row, sub * 4 + j)) =
+                make_uint4(dk[4 * j], dk[4 * j + 1], dk[4 * j + 2], dk[4 * j + 3]);
         }
+        tmem_st_wait();
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(bar_pfull + 8 * b);
+        // dQᵀ of this unit: lanes = d, columns = the unit's 64 queries
+        good = __all_sync(0xffffffffu, mbar_wait(bar_dqfull + 8 * b, it & 1, KID, 33));
       }
-      // in place over the 32 Sᵀ columns this group has just read (the other group of the half may
-      // still be reading its own): Pᵀ in the first 16, dSᵀ in the last 16
-      tmem_st16(t_s + sub * 32, pk);
-      tmem_st16(t_s + sub * 32 + 16, dk);
-      {
-        uint8_t* srow = sdS + b * HALF_BYTES;   // this key's 64 queries: one swizzled 128-byte row
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(srow + sw128_offset(row, sub * 4 + j)) =
-              make_uint4(dk[4 * j], dk[4 * j + 1], dk[4 * j + 2], dk[4 * j + 3]);
-      }
-      tmem_st_wait();
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(bar_pfull + 8 * b);
-      // dQᵀ of this (half, key tile): lanes = d, columns = the half's 64 queries
-      if (!mbar_wait(bar_dqfull + 8 * b, it & 1, KID, 33)) { ok = false; break; }
+      // the group's staging rows are free once its previous copy has read them; the vote keeps the
+      // four warps together (a warp whose wait ran out takes the others out with it)
+      if (issuer) tma_store_wait_read<0>();
+      if (!named_bar_all(1 + grp, 128, good)) break;
       tc_fence_after();
-      tmem_ld32(t_s + 64 + sub * 32, rs);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(bar_dqread + 8 * b);
-      {
-        const int h = kvh * G + it / n;
-        float* dst = p.dq_acc + ((size_t)qrow0 * p.Hq + h) * HD + row;
-        const size_t step = (size_t)p.Hq * HD;
+      const int h = kvh * G + it / n;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) atomicAdd(dst + j * step, __uint_as_float(rs[j]));
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rq[16];
+        tmem_ld16(t_s + 64 + sub * 32 + c * 16, rq);
+        tmem_ld_wait();
+        if (c == 1) {
+          tc_fence_before();
+          mbar_arrive(bar_dqread + 8 * b);
+          if (issuer) tma_store_wait_read<0>();
+          named_bar_sync(1 + grp, 128);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) red[j * HD + row] = __uint_as_float(rq[j]);
+        fence_proxy_async_smem();
+        named_bar_sync(1 + grp, 128);
+        if (issuer) {
+          tma_reduce_add_2d(&tm_dqacc, smem_u32(red), h * HD, qrow0 + c * 16);
+          tma_store_commit();
+        }
       }
+      st += 2;
+      if (st >= STAGES) st -= STAGES;
     }
-    // epilogue: half 0's groups store dV, half 1's store dK; each group converts 64 of the 128 columns
+    if (issuer) tma_store_wait_all();
+    // epilogue: the groups of slot 0 store dV, those of slot 1 store dK; each converts 64 of the 128 columns
+    bool ok = !error_is_set();
     if (ok && items > 0) ok = mbar_wait(bar_done, 0, KID, 31);
     if (ok) {
       tc_fence_after();
       const uint32_t t_acc = tmem_base + ((uint32_t)(qd * 32) << 16) + 256 + b * 128;
-      uint8_t* st = sQ + b * TILE_BYTES;
+      uint8_t* stg = b ? sdO : sQ;   // 32 KiB each; every load and product has finished by now
+      uint32_t rs[32];
 #pragma unroll 1
       for (int c = 2 * sub; c < 2 * sub + 2; ++c) {
         if (items > 0) {
@@ -362,7 +432,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
           for (int e = 0; e < 32; ++e) rs[e] = 0u;
         }
-        uint8_t* half = st + (c >> 1) * HALF_BYTES;
+        uint8_t* half = stg + (c >> 1) * KV_HALF_BYTES;
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           uint32_t a[4];
@@ -380,7 +450,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           const CUtensorMap* tm = b ? &tm_dk : &tm_dv;
 #pragma unroll
           for (int c = 0; c < 2; ++c)
-            tma_store_2d(tm, smem_u32(st + c * HALF_BYTES), kvh * HD + c * 64, kt * 128);
+            tma_store_2d(tm, smem_u32(stg + c * KV_HALF_BYTES), kvh * HD + c * 64, kt * 128);
           tma_store_commit();
           tma_store_wait_all();
         }

@@ -131,8 +131,8 @@ extern "C" int tdllm_attn_bwd_fused(const void* q, const void* k, const void* v,
       tdllm_host::set_last_error("attn_bwd_fused: operand %d needs 16-byte aligned base and row stride", i);
       return 1;
     }
-  if ((uintptr_t)dq_acc % 16) {
-    tdllm_host::set_last_error("attn_bwd_fused: dq accumulator must be 16-byte aligned");
+  if ((uintptr_t)dq_acc % 128) {
+    tdllm_host::set_last_error("attn_bwd_fused: dq accumulator must be 128-byte aligned");
     return 1;
   }
   static bool attr_set = false;
@@ -154,9 +154,18 @@ extern "C" int tdllm_attn_bwd_fused(const void* q, const void* k, const void* v,
         (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, lse, delta, delta + (size_t)Hq * nq_pad, scale,
         nq, nq_pad, Hq, ldo, lddo);
   }
-  CUtensorMap tq, tdo, tk, tv, tdk, tdv;
-  if (tdllm_host::encode_rows_tmap(&tq, q, qc, nq, ldq, 128) ||
-      tdllm_host::encode_rows_tmap(&tdo, dout, qc, nq, lddo, 128) ||
+  CUtensorMap tq, tdo, tk, tv, tdk, tdv, tacc;
+  {
+    // fp32 accumulator as [nq_pad rows][Hq*128]; one reduce-add copy moves 16 rows of one head
+    const uint64_t dims[2] = {(uint64_t)qc, (uint64_t)nq_pad};
+    const uint64_t strides[1] = {(uint64_t)qc * sizeof(float)};
+    const uint32_t box[2] = {128, 16};
+    if (tdllm_host::encode_tmap(&tacc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dq_acc, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_NONE))
+      return 3;
+  }
+  if (tdllm_host::encode_rows_tmap(&tq, q, qc, nq, ldq, 64) ||
+      tdllm_host::encode_rows_tmap(&tdo, dout, qc, nq, lddo, 64) ||
       tdllm_host::encode_rows_tmap(&tk, k, kc, nk, ldk, 128) ||
       tdllm_host::encode_rows_tmap(&tv, v, kc, nk, ldv, 128) ||
       tdllm_host::encode_rows_tmap(&tdk, dk, kc, nk, lddk, 128) ||
@@ -166,10 +175,10 @@ extern "C" int tdllm_attn_bwd_fused(const void* q, const void* k, const void* v,
   p.nq_pad = nq_pad; p.Hq = Hq; p.Hkv = Hkv;
   p.q_lo = q_lo; p.q_hi = q_hi; p.q_grp = q_grp; p.k_code = k_code;
   p.tile_ptr = b_ptr; p.tile_idx = b_idx; p.order = b_order;
-  p.lse2 = delta + (size_t)Hq * nq_pad; p.delta = delta; p.dq_acc = dq_acc;
+  p.lse2 = delta + (size_t)Hq * nq_pad; p.delta = delta;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   attn_fused::attn_bwd_fused_kernel<<<n_ktiles * Hkv, attn_fused::THREADS, attn_fused::SMEM_BYTES, s>>>(
-      tq, tdo, tk, tv, tdk, tdv, p);
+      tq, tdo, tk, tv, tdk, tdv, tacc, p);
   {
     const long long n4 = (long long)nq * (qc / 4);
     dq_cast_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, s>>>(dq_acc, (__nv_bfloat16*)dq, nq, (int)qc, lddq);

@@ -167,6 +167,17 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src,
       "r"(src), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// shared -> global with element-wise add at the destination (fp32 here; the tensor map gives the type)
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, uint32_t src, int x, int y) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(m),
+      "r"(src), "r"(x), "r"(y)
+      : "memory");
+}
+// barrier among `nthreads` threads of the CTA (a multiple of 32) that all name the same id (1..15)
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
