@@ -25,17 +25,26 @@ constexpr int GEMM_KERNEL_ID = 1;
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int EPI_WARPS = 4;
 constexpr int EPI_BUF_BYTES = 32 * 128;  // one warp: 32 rows x 128 bytes
 constexpr int GEMM_THREADS = 32 * (2 + EPI_WARPS);
-constexpr int SMEM_TILES = STAGES * STAGE_BYTES;
 constexpr int SMEM_EPI = EPI_WARPS * 2 * EPI_BUF_BYTES;
-constexpr int GEMM_SMEM_BYTES = SMEM_TILES + SMEM_EPI + 256 + 1024;  // + barriers + align slack
+
+// PAIR = 1: one CTA per 128 x 256 tile. PAIR = 2: a cluster of two CTAs per 256 x 256 tile
+// (tcgen05 cta_group::2): each CTA loads its own 128 rows of A and half of the B tile, so
+// every MMA reads 8 KiB of shared memory per SM instead of 12 KiB; the single-CTA form is bound by
+// that read (171 cycles per 128x256x16 MMA measured, against 128 of tensor work).
+template <int PAIR>
+struct Cfg {
+  static constexpr int B_ROWS = BN / PAIR;
+  static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;        // 32 or 16 KiB
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = PAIR == 2 ? 6 : 4;
+  static constexpr int SMEM_TILES = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = SMEM_TILES + SMEM_EPI + 256 + 1024;  // + barriers + align slack
+};
 
 enum EpilogueMode : int {
   EPI_STORE = 0,     // D = acc (bf16 or fp32), optional D += acc
@@ -79,11 +88,17 @@ __device__ __forceinline__ float apply_softcap(float x, float cap) {
   return cap > 0.f ? cap * tanhf(x / cap) : x;
 }
 
+template <int PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
+  constexpr int STAGES = Cfg<PAIR>::STAGES;
+  constexpr int STAGE_BYTES = Cfg<PAIR>::STAGE_BYTES;
+  constexpr int SMEM_TILES = Cfg<PAIR>::SMEM_TILES;
+  constexpr int B_ROWS = Cfg<PAIR>::B_ROWS;
   extern __shared__ uint8_t smem_raw[];
+  // the two CTAs of a pair must use identical offsets: the window bases are equally aligned
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* epi_smem = smem + SMEM_TILES;
   uint64_t* bars = (uint64_t*)(epi_smem + SMEM_EPI);
@@ -96,7 +111,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.m_tiles * p.n_tiles;
+  // a pair walks 256-row tiles together; CTA `rank` owns the rank-th 128 rows of each
+  const int rank = PAIR == 2 ? (int)cluster_ctarank() : 0;
+  const int m_groups = (p.m_tiles + PAIR - 1) / PAIR;
+  const int num_tiles = m_groups * p.n_tiles;
+  const int walker = blockIdx.x / PAIR, walkers = gridDim.x / PAIR;
   const int k_blocks = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -106,16 +125,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull + 8 * b, 1);
-      mbar_init(bar_tempty + 8 * b, EPI_WARPS);
+      mbar_init(bar_tempty + 8 * b, EPI_WARPS * PAIR);
     }
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), 512);
-    tmem_relinquish();
+    if (PAIR == 2) {
+      tmem_alloc_pair(smem_u32(tmem_slot), 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR == 2) cluster_sync_all();   // the peer's barriers exist before anything is sent to them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -127,31 +152,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = walker; t < num_tiles && ok; t += walkers) {
         int tm, tn;
-        tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+        tile_coords(t, m_groups, p.n_tiles, tm, tn);
+        tm = tm * PAIR + rank;
+        const int b_row0 = tn * BN + rank * B_ROWS;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, GEMM_KERNEL_ID, 10)) {
             ok = false;
             break;
           }
-          const uint32_t full = bar_full + 8 * stage;
-          mbar_expect_tx(full, STAGE_BYTES);
+          // pair: both CTAs' bytes are credited to CTA 0's barrier, which expects the sum
+          const uint32_t full = PAIR == 2 ? ((bar_full + 8 * stage) & PEER_BIT_MASK) : (bar_full + 8 * stage);
+          if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES * PAIR);
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sb = sa + A_STAGE_BYTES;
+          auto load = [&](uint32_t dst, const CUtensorMap* m, int x, int y) {
+            if (PAIR == 2) tma_load_2d_pair(dst, m, full, x, y);
+            else tma_load_2d(dst, m, full, x, y);
+          };
           if (!p.a_mn_major) {
-            tma_load_2d(sa, &tmap_a, full, kb * BK, tm * BM);
+            load(sa, &tmap_a, kb * BK, tm * BM);
           } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c)
-              tma_load_2d(sa + c * (BK * 128), &tmap_a, full, tm * BM + c * 64, kb * BK);
+            for (int c = 0; c < BM / 64; ++c) load(sa + c * (BK * 128), &tmap_a, tm * BM + c * 64, kb * BK);
           }
           if (!p.b_mn_major) {
-            tma_load_2d(sb, &tmap_b, full, kb * BK, tn * BN);
+            load(sb, &tmap_b, kb * BK, b_row0);
           } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sb + c * (BK * 128), &tmap_b, full, tn * BN + c * 64, kb * BK);
+            for (int c = 0; c < B_ROWS / 64; ++c) load(sb + c * (BK * 128), &tmap_b, b_row0 + c * 64, kb * BK);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -164,14 +194,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------ MMA issuer --------------------------------
     // whole warp with identical values; one elected lane issues, so that the descriptors stay in
     // uniform registers (a divergent lane-0 branch makes every MMA cost ~130 cycles to issue)
-    {
+    if (rank == 0) {   // in a pair, CTA 0 issues for both
       const bool leader = elect_one();
-      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn_major, p.b_mn_major);
+      const uint32_t idesc = make_idesc_bf16(BM * PAIR, BN, p.a_mn_major, p.b_mn_major);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = walker; t < num_tiles && ok; t += walkers, ++it) {
         const int buf = it & 1;
         const uint32_t tphase = (it >> 1) & 1;
         if (!__all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * buf, tphase ^ 1, GEMM_KERNEL_ID, 20))) break;
@@ -195,15 +225,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint64_t bd = p.b_mn_major
                                     ? make_smem_desc_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024)
                                     : make_smem_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
-            if (leader) tc_mma_ss(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+            if (leader) {
+              if (PAIR == 2) tc_mma_ss_pair(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+              else tc_mma_ss(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+            }
           }
-          if (leader) tc_commit(bar_empty + 8 * stage);
+          if (leader) {
+            if (PAIR == 2) tc_commit_pair(bar_empty + 8 * stage, 3);
+            else tc_commit(bar_empty + 8 * stage);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok && leader) tc_commit(bar_tfull + 8 * buf);
+        if (ok && leader) {
+          if (PAIR == 2) tc_commit_pair(bar_tfull + 8 * buf, 3);
+          else tc_commit(bar_tfull + 8 * buf);
+        }
       }
       __syncwarp();
     }
@@ -214,9 +253,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint8_t* my_stage = epi_smem + (warp - 2) * 2 * EPI_BUF_BYTES;
     int sbuf = 0;
     int it = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+    for (int t = walker; t < num_tiles; t += walkers, ++it) {
       int tm, tn;
-      tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+      tile_coords(t, m_groups, p.n_tiles, tm, tn);
+      tm = tm * PAIR + rank;
       const int buf = it & 1;
       const uint32_t tphase = (it >> 1) & 1;
       if (!mbar_wait(bar_tfull + 8 * buf, tphase, GEMM_KERNEL_ID, 30)) break;
@@ -392,24 +432,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // accumulator buffer is free again
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+      if (lane == 0) {
+        if (PAIR == 2) mbar_arrive_cluster((bar_tempty + 8 * buf) & PEER_BIT_MASK);   // CTA 0 counts both
+        else mbar_arrive(bar_tempty + 8 * buf);
+      }
     }
     if (lane == 0) tma_store_wait_all();
   }
 
   // common exit: every role arrives here, also after a failed wait
   tc_fence_before();
-  __syncthreads();
+  if (PAIR == 2) cluster_sync_all();   // neither CTA leaves while the other may still read or signal it
+  else __syncthreads();
   if (error_is_set()) {
     // loads that were issued before an abort may still be landing in shared memory
     const unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
-    __syncthreads();
+    if (PAIR == 2) cluster_sync_all();
+    else __syncthreads();
   }
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if (PAIR == 2) tmem_dealloc_pair(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -440,16 +486,33 @@ extern "C" int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int
     return 1;
   }
   static bool attr_set = false;
+  static int max_pairs = 0;   // clusters of two that fit on the device at once (0 = pairs unavailable)
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         GEMM_SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg<1>::SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               Cfg<2>::SMEM_BYTES);
     if (e != cudaSuccess) {
       tdllm_host::set_last_error("gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       return 2;
     }
+    const char* env = getenv("TDLLM_GEMM_PAIR");
+    if (!(env && env[0] == '0')) {
+      cudaLaunchConfig_t cfg = {};
+      cudaLaunchAttribute at;
+      at.id = cudaLaunchAttributeClusterDimension;
+      at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+      cfg.gridDim = dim3(2 * 74); cfg.blockDim = dim3(GEMM_THREADS);
+      cfg.dynamicSmemBytes = Cfg<2>::SMEM_BYTES; cfg.attrs = &at; cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_kernel<2>, &cfg) == cudaSuccess && n > 0) max_pairs = n;
+      else (void)cudaGetLastError();
+    }
     attr_set = true;
   }
+  // pairs pay off when there are at least two 128-row tiles to share a B tile
+  const bool pair = max_pairs > 0 && M > BM;
   CUtensorMap ta, tb, td;
   {
     uint64_t dims[2], strides[1];
@@ -463,7 +526,7 @@ extern "C" int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int
     if (tdllm_host::encode_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, dims, strides, box,
                                 CU_TENSOR_MAP_SWIZZLE_128B)) return 3;
     if (!b_mn_major) {
-      dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = BK; box[1] = BN;
+      dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = BK; box[1] = pair ? BN / 2 : BN;
     } else {
       dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 64; box[1] = BK;
     }
@@ -500,11 +563,27 @@ extern "C" int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int
   }
   p.labels = labels; p.lse = lse; p.rowscale = rowscale; p.stats = stats;
   p.exclude_index = exclude_index; p.softcap = softcap;
-  const int tiles = p.m_tiles * p.n_tiles;
-  int ctas = max_ctas > 0 ? max_ctas : tdllm_num_sms();
-  if (ctas > tiles) ctas = tiles;
-  gemm_bf16_kernel<<<ctas, GEMM_THREADS, GEMM_SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, td, p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e;
+  if (pair) {
+    const int tiles = ((p.m_tiles + 1) / 2) * p.n_tiles;
+    int pairs = max_ctas > 0 ? (max_ctas / 2 > 0 ? max_ctas / 2 : 1) : max_pairs;
+    if (pairs > max_pairs) pairs = max_pairs;
+    if (pairs > tiles) pairs = tiles;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+    cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg<2>::SMEM_BYTES; cfg.stream = (cudaStream_t)stream;
+    cfg.attrs = &at; cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<2>, ta, tb, td, p);
+  } else {
+    const int tiles = p.m_tiles * p.n_tiles;
+    int ctas = max_ctas > 0 ? max_ctas : tdllm_num_sms();
+    if (ctas > tiles) ctas = tiles;
+    gemm_bf16_kernel<1><<<ctas, GEMM_THREADS, Cfg<1>::SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, td, p);
+    e = cudaGetLastError();
+  }
   if (e != cudaSuccess) {
     tdllm_host::set_last_error("gemm launch: %s", cudaGetErrorString(e));
     return 4;

@@ -53,10 +53,18 @@ int encode_tmap(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* 
   auto fn = get_encode();
   if (!fn) return 1;
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-  CUresult r = fn(out, dt, (cuuint32_t)rank, const_cast<void*>(base), (const cuuint64_t*)dims,
-                  (const cuuint64_t*)strides_bytes, (const cuuint32_t*)box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  auto encode = [&]() {
+    return fn(out, dt, (cuuint32_t)rank, const_cast<void*>(base), (const cuuint64_t*)dims,
+              (const cuuint64_t*)strides_bytes, (const cuuint32_t*)box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode();
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // a thread that has made no runtime call yet (an autograd worker) has no current context for
+    // this driver entry point; a runtime no-op binds the device's primary context to the thread
+    (void)cudaFree(nullptr);
+    r = encode();
+  }
   if (r != CUDA_SUCCESS) {
     set_last_error("cuTensorMapEncodeTiled failed: code %d (rank %d dims %llu,%llu stride %llu box %u,%u)",
                    (int)r, rank, (unsigned long long)dims[0], (unsigned long long)dims[1],
