@@ -103,10 +103,12 @@ class _LayerCheckpoint(torch.autograd.Function):
         for key in (idx - 1, (idx - 1, "attn_out"), (idx - 1, "attn_lse")):
             store.prefetch(key)
         h = h.detach().requires_grad_(True)
+        from ..ops.gemm import skip_last_output
+
         store.replaying = True
         try:
-            with torch.enable_grad():
-                out = ctx.layer(h, *ctx.args)
+            with torch.enable_grad(), skip_last_output():
+                out = ctx.layer(h, *ctx.args)   # its value is not needed: only the graph behind it
         finally:
             store.replaying = False
         torch.autograd.backward(out, dout)

@@ -146,7 +146,7 @@ class DecoderLayer(nn.Module):
         h = row_parallel_linear_residual(a, self.w_o, h, tp)
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
         act = linear_swiglu(copy_to_tensor_parallel(y2, tpg), self.w_gate_up)
-        return row_parallel_linear_residual(act, self.w_down, h, tp)
+        return row_parallel_linear_residual(act, self.w_down, h, tp, last=True)
 
     def _forward_lora(self, h, positions, inv_freq, attend):
         """Same layer with low-rank updates on the adapted projections (single tensor-parallel rank)."""

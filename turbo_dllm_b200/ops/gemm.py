@@ -104,13 +104,31 @@ def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return _Linear.apply(x, w)
 
 
+class _Replay:
+    """Set while a checkpointed layer is re-run for its backward pass: the value of the layer's last
+    product is then never read (the gradient of the layer output comes from outside), so the op only
+    records what its backward needs and skips the GEMM."""
+    skip_last_output = False
+
+
+class skip_last_output:
+    def __enter__(self):
+        self.prev = _Replay.skip_last_output
+        _Replay.skip_last_output = True
+
+    def __exit__(self, *exc):
+        _Replay.skip_last_output = self.prev
+
+
 class _LinearResidual(torch.autograd.Function):
     """h = res + x Wᵀ with the add done in the GEMM epilogue (no separate pass over the stream)."""
 
     @staticmethod
-    def forward(ctx, x, w, res):
+    def forward(ctx, x, w, res, value_unused=False):
         ctx.save_for_backward(x, w)
         ctx.wref = w
+        if value_unused:
+            return torch.empty_like(res)
         return gemm(x, w, residual=_as2d(res)).view(res.shape)
 
     @staticmethod
@@ -127,7 +145,7 @@ class _LinearResidual(torch.autograd.Function):
                 mark_grad_written(ctx.wref)
             else:
                 dw = gemm(dy2, _as2d(x), a_mn_major=True, b_mn_major=True, out_dtype=w.dtype)
-        return dx, dw, (dy if ctx.needs_input_grad[2] else None)
+        return dx, dw, (dy if ctx.needs_input_grad[2] else None), None
 
 
 def linear_residual(x: torch.Tensor, w: torch.Tensor, res: torch.Tensor) -> torch.Tensor:
@@ -140,11 +158,13 @@ class _RowParallelResidual(torch.autograd.Function):
     full gradient of the (replicated) residual stream."""
 
     @staticmethod
-    def forward(ctx, x, w, res, group, rank):
+    def forward(ctx, x, w, res, group, rank, value_unused=False):
         import torch.distributed as dist
 
         ctx.save_for_backward(x, w)
         ctx.wref = w
+        if value_unused:
+            return torch.empty_like(res)
         out = gemm(x, w, residual=_as2d(res) if rank == 0 else None)
         dist.all_reduce(out, group=group)
         return out.view(res.shape)
@@ -162,14 +182,16 @@ class _RowParallelResidual(torch.autograd.Function):
                 mark_grad_written(ctx.wref)
             else:
                 dw = gemm(dy2, _as2d(x), a_mn_major=True, b_mn_major=True, out_dtype=w.dtype)
-        return dx, dw, (dy if ctx.needs_input_grad[2] else None), None, None
+        return dx, dw, (dy if ctx.needs_input_grad[2] else None), None, None, None
 
 
-def row_parallel_linear_residual(x, w_shard, res, tp) -> torch.Tensor:
-    """`tp`: parallel.tensor_parallel.TPContext (or None / size 1 for no tensor parallelism)."""
+def row_parallel_linear_residual(x, w_shard, res, tp, last: bool = False) -> torch.Tensor:
+    """`tp`: parallel.tensor_parallel.TPContext (or None / size 1 for no tensor parallelism).
+    `last`: this product is the layer's output (skipped when a checkpointed layer is replayed)."""
+    unused = last and _Replay.skip_last_output and torch.is_grad_enabled()
     if tp is None or tp.size == 1:
-        return _LinearResidual.apply(x, w_shard, res)
-    return _RowParallelResidual.apply(x, w_shard, res, tp.group, tp.rank)
+        return _LinearResidual.apply(x, w_shard, res, unused)
+    return _RowParallelResidual.apply(x, w_shard, res, tp.group, tp.rank, unused)
 
 
 class _LinearSwiGLU(torch.autograd.Function):

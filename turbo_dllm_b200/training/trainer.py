@@ -149,7 +149,9 @@ def run_training(spec: RunSpec) -> dict:
             timed = step - start_step > spec.profiler.warmup_steps
             if timed:
                 timed_ms.append(ms)
-            counters.add(input_tokens=tokens_per_step, supervised_tokens=float(res.denominator), active_tokens=rows)
+            # drafter distillation normalises per micro-batch (denominator 1): its supervised count is the rows
+            supervised = rows if session.task is not None else float(res.denominator)
+            counters.add(input_tokens=tokens_per_step, supervised_tokens=supervised, active_tokens=rows)
             if rank == 0:
                 ev = ({"event": "step", "step": step, "completed_steps": step, "target_total_steps": total_steps,
                       "timed": timed, "loss": last_loss, "lr": session.scheduler.lr_at(session.scheduler.step_count),
