@@ -1,0 +1,133 @@
+"""Times the peer-memory kernels against their NVLink roofline, one process per GPU.
+
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
+        -m turbo_dllm_b200.benchmarks.comm_bench --params 2000000000 --kv-rows 16384
+
+Rank 0 prints one JSON line per kernel. Device time is taken with CUDA events around the launch,
+after warm-up, and reduced with MAX over ranks. Roofline: the bytes that must cross NVLink per GPU
+and direction, divided by the measured peer-copy bandwidth of this pool (770 GB/s per direction).
+
+* fused ZeRO step (`csrc/comm.cu::tdllm_zero_fused_step`): every rank pulls its shard of the bf16
+  gradients from the W-1 peers ((W-1)/W · 2P bytes in) and pushes its updated bf16 parameter shard
+  to them ((W-1)/W · 2P bytes out); the AdamW update of the shard (16 bytes per owned parameter of
+  HBM traffic) runs between the two.
+* clean K|V gather (`tdllm_kv_gather`): every rank pulls the other ranks' rows once.
+* its NCCL twins (`reduce_scatter` + `all_gather`, `all_gather`) on the same sizes.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+PEER_GBS = 770.0
+
+
+def _time(fn, iters: int, warmup: int) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ts = []
+    for _ in range(iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    t = torch.tensor([ts[len(ts) // 2]], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def main(argv=None):
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.models.dense import FlatParams
+    from turbo_dllm_b200.optim.flat_adamw import FlatAdamW
+    from turbo_dllm_b200.parallel.context_attention import PeerKVExchange
+    from turbo_dllm_b200.parallel.fused_zero import FusedZeroSync
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--params", type=int, default=2_000_000_000, help="bf16 parameters in the flat buffer")
+    ap.add_argument("--kv-rows", type=int, default=16384, help="clean rows owned by every rank")
+    ap.add_argument("--kv-row-elems", type=int, default=2048, help="K|V elements per row (2 * kv heads * head dim)")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args(argv)
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    group = dist.group.WORLD
+    out = []
+
+    # ---- fused ZeRO step vs reduce_scatter + AdamW + all_gather
+    n = (args.params // (world * 1024)) * world * 1024
+    flat = FlatParams([("w", (n,), True)], torch.bfloat16, dev)
+    flat.data.normal_(0, 0.02)
+    sync = FusedZeroSync.create(flat, group)
+    opt = FlatAdamW(flat, lr=1e-4, group=group, fused_sync=sync)
+    flat.grad.normal_(0, 1e-3)
+
+    def fused():
+        opt.step(lr=1e-4, weight_decay=0.0, max_grad_norm=1.0)
+
+    ms = _time(fused, args.iters, args.warmup)
+    cross = (world - 1) / world * 2 * n      # bytes per direction per GPU, each phase
+    out.append({"kernel": "zero_fused_step (pull-reduce + clip + AdamW + push)", "world": world, "params": n,
+                "ms": round(ms, 3), "nvlink_bytes_in": cross, "nvlink_bytes_out": cross,
+                "roofline_ms": round(2 * cross / (PEER_GBS * 1e9) * 1e3, 3),
+                "fraction_of_roofline": round(2 * cross / (PEER_GBS * 1e9) * 1e3 / ms, 3),
+                "note": "roofline = gradient pull then parameter push, each (W-1)/W*2P bytes at 770 GB/s per direction"})
+    native.raise_on_device_error()
+    sync_opt = opt
+    # NCCL twin on separate buffers of the same size
+    g = torch.randn(n, device=dev, dtype=torch.bfloat16) * 1e-3
+    shard = torch.empty(n // world, device=dev, dtype=torch.bfloat16)
+    full = torch.empty(n, device=dev, dtype=torch.bfloat16)
+
+    def nccl():
+        dist.reduce_scatter_tensor(shard, g, group=group)
+        dist.all_gather_into_tensor(full, shard, group=group)
+
+    ms2 = _time(nccl, args.iters, args.warmup)
+    out.append({"kernel": "nccl reduce_scatter + all_gather (no optimizer math)", "world": world, "params": n,
+                "ms": round(ms2, 3), "fraction_of_roofline": round(2 * cross / (PEER_GBS * 1e9) * 1e3 / ms2, 3)})
+    del g, shard, full
+    sync.close()
+    del sync_opt, opt, flat
+    torch.cuda.empty_cache()
+
+    # ---- clean K|V gather vs all_gather
+    counts = [args.kv_rows] * world
+    ex = PeerKVExchange(group, dev, counts, args.kv_row_elems)
+    x = torch.randn(args.kv_rows, args.kv_row_elems, device=dev).bfloat16()
+    ms3 = _time(lambda: ex.gather(x), args.iters, args.warmup)
+    pulled = (world - 1) * args.kv_rows * args.kv_row_elems * 2
+    out.append({"kernel": "kv_gather (peer pull into local memory, includes the staging copy)", "world": world,
+                "rows_per_rank": args.kv_rows, "ms": round(ms3, 3), "nvlink_bytes_in": pulled,
+                "roofline_ms": round(pulled / (PEER_GBS * 1e9) * 1e3, 3),
+                "fraction_of_roofline": round(pulled / (PEER_GBS * 1e9) * 1e3 / ms3, 3)})
+    native.raise_on_device_error()
+    full = torch.empty(world * args.kv_rows, args.kv_row_elems, device=dev, dtype=torch.bfloat16)
+    ms4 = _time(lambda: dist.all_gather_into_tensor(full, x, group=group), args.iters, args.warmup)
+    out.append({"kernel": "nccl all_gather of the same rows", "world": world, "ms": round(ms4, 3),
+                "fraction_of_roofline": round(pulled / (PEER_GBS * 1e9) * 1e3 / ms4, 3)})
+    ex.close()
+    if rank == 0:
+        for rec in out:
+            print(json.dumps(rec), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

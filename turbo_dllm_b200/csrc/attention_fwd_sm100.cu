@@ -238,29 +238,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t t_o = tmem_base + ((uint32_t)(qd * 32) << 16) + 256 + i * 128;
     float m_used = -INFINITY;  // max the stored probabilities are relative to (raw score units)
     float l = 0.f;
+    uint32_t r[128];
     bool ok = true;
     for (int j = 0; j < n; ++j) {
       const int ent = list[j];
       const int* kc = p.k_code + (ent >> 1) * BKV;
       if (!mbar_wait(bar_sfull + 8 * i, j & 1, KID, 30)) { ok = false; break; }
       tc_fence_after();
-      // two passes over the score row in TMEM, 32 columns at a time (row maximum, then probabilities):
-      // a register-resident 128-value row spills at this block size, and spills come back through L2
+      // the whole score row lives in registers: one TMEM round trip per tile
+      tmem_ld32(t_s, r);
+      tmem_ld32(t_s + 32, r + 32);
+      tmem_ld32(t_s + 64, r + 64);
+      tmem_ld32(t_s + 96, r + 96);
+      tmem_ld_wait();
+      if (ent & 1) {
+#pragma unroll
+        for (int e = 0; e < 128; ++e)
+          if (!key_visible(__ldg(kc + e), lo, hi, grp)) r[e] = 0xff800000u;  // -inf
+      }
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_s + c * 32, r);
-        tmem_ld_wait();
-        if (ent & 1) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (key_visible(__ldg(kc + c * 32 + e), lo, hi, grp)) mx = fmaxf(mx, __uint_as_float(r[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
-        }
-      }
+      for (int e = 0; e < 128; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
       // lazy rescale: keep the old reference max unless the new one is 2^8 larger
       float alpha = 1.f;
       if (mx > -INFINITY && (m_used == -INFINITY || (mx - m_used) * p.scale_log2 > 8.f)) {
@@ -279,32 +277,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_st32(t_o + c * 32, ro);
         }
       }
-      // probabilities -> bf16 P in TMEM over the S columns (chunk c lands on columns every earlier
-      // chunk has already been read from); masked scores -> exactly 0
+      // probabilities -> bf16 P in TMEM over the S columns; masked scores are -inf -> exactly 0
       const float mref = (m_used == -INFINITY) ? 0.f : m_used * p.scale_log2;
+      // 32 scores at a time, stored as soon as they are packed: keeps the packed values out of the
+      // register budget (the score row itself already takes 128 registers)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32], pk[16];
-        tmem_ld32(t_s + c * 32, r);
-        tmem_ld_wait();
-        if (ent & 1) {
+        uint32_t pk[16];
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, -mref));
-            float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, -mref));
-            if (!key_visible(__ldg(kc + c * 32 + e), lo, hi, grp)) p0 = 0.f;
-            if (!key_visible(__ldg(kc + c * 32 + e + 1), lo, hi, grp)) p1 = 0.f;
-            l += p0 + p1;
-            pk[e >> 1] = pack_bf16x2(p0, p1);
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, -mref));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, -mref));
-            l += p0 + p1;
-            pk[e >> 1] = pack_bf16x2(p0, p1);
-          }
+        for (int e = 0; e < 32; e += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(r[c * 32 + e]), p.scale_log2, -mref));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(r[c * 32 + e + 1]), p.scale_log2, -mref));
+          l += p0 + p1;
+          pk[e >> 1] = pack_bf16x2(p0, p1);
         }
         tmem_st16(t_s + c * 16, pk);
       }
@@ -318,7 +303,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       uint8_t* st = sQ + i * TILE_BYTES;
-      uint32_t r[32];
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         if (n > 0) {
