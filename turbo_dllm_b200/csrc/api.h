@@ -83,15 +83,17 @@ int tdllm_attn_bwd(const void* q, const void* k, const void* v, const void* o, c
                    const int* b_idx, const int* b_order, int n_qtiles, int n_ktiles, float scale,
                    void* stream);
 
-// One-pass backward (five tensor-core products per tile pair instead of seven): dQ is summed over
-// key tiles in `dq_acc`, fp32 scratch [n_qtiles*128, Hq, 128] that this call zeroes, then cast.
+// One-pass backward (five tensor-core products per tile pair instead of seven). dQ, dK and dV are
+// summed in `acc`, fp32 scratch of n_qtiles*128*Hq*128 + 2*n_ktiles*128*Hkv*128 floats that this call
+// zeroes, then cast. Work item c*n_ktiles + kt = the query tiles of chunk c that see key tile kt
+// (w_ptr: one entry per item plus one; w_order: the n_work non-empty items, chunk by chunk).
 int tdllm_attn_bwd_fused(const void* q, const void* k, const void* v, const void* o, const void* dout,
-                         void* dq, void* dk, void* dv, const float* lse, float* delta, float* dq_acc,
+                         void* dq, void* dk, void* dv, const float* lse, float* delta, float* acc,
                          int nq, int nk, int Hq, int Hkv, long long ldq, long long ldk, long long ldv,
                          long long ldo, long long lddo, long long lddq, long long lddk,
                          long long lddv, const int* q_lo, const int* q_hi, const int* q_grp,
-                         const int* k_code, const int* b_ptr, const int* b_idx, const int* b_order,
-                         int n_qtiles, int n_ktiles, float scale, void* stream);
+                         const int* k_code, const int* w_ptr, const int* w_idx, const int* w_order,
+                         int n_work, int n_qtiles, int n_ktiles, float scale, void* stream);
 
 // Issue-rate probe of tcgen05.mma (128 x n x 16, bf16): out[0] = cycles in the issue loop of one
 // thread, out[1] = cycles until the last MMA completed.

@@ -14,6 +14,12 @@
 // TMA reduce-add copies (16 query rows of 512 bytes per copy). A small kernel afterwards
 // casts the accumulator to bf16.
 //
+// The walk of a key tile is cut into chunks of consecutive query tiles and the grid runs chunk by
+// chunk (all key tiles of chunk 0, then chunk 1, ...): the rows of the dQ accumulator that a chunk
+// touches then stay in L2 while every key tile adds to them, instead of going to DRAM and back once
+// per wave of CTAs. The price: dK/dV of a CTA are partial sums too, added to fp32 accumulators by the
+// same kind of copy when the CTA ends (128 KiB per CTA against 32 KiB per 64-query unit for dQ).
+//
 // Warps: 0-15 do the element-wise work as four groups of four (unit parity b = warp/8, 32 of the
 // unit's 64 queries each), warp 16 issues TMA loads, warp 17 issues the MMAs. Units alternate
 // between two TMEM slots, so the exponentials of one unit overlap the products of the other.
@@ -53,6 +59,7 @@ constexpr int OFF_STAT = OFF_BARS + 512;      // [stage][lse2 64 | delta_s 64] f
 // no alignment slack: the kernel checks that its dynamic shared memory starts 1 KiB aligned
 constexpr int SMEM_BYTES = OFF_STAT + STAGES * 128 * 4;
 static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
+static_assert(OFF_Q + 2 * 65536 <= OFF_RED, "dK/dV staging must not reach the dQ staging rows");
 
 struct Params {
   int nq_pad, Hq, Hkv;
@@ -60,9 +67,10 @@ struct Params {
   const int* q_hi;
   const int* q_grp;
   const int* k_code;
-  const int* tile_ptr;  // per key tile: query tiles that see it
+  int nkt;              // key tiles
+  const int* tile_ptr;  // per work item (chunk * nkt + key tile): the chunk's query tiles that see the key tile
   const int* tile_idx;  // q_tile * 2 + needs_mask
-  const int* order;     // key tiles, heaviest first
+  const int* order;     // non-empty work items: chunk by chunk, heaviest first inside a chunk
   const float* lse2;   // [Hq, nq_pad] lse·log2e (+inf = row without keys)
   const float* delta;  // [Hq, nq_pad] scale · rowsum(dO∘O)
   float scale_log2, scale;
@@ -102,7 +110,7 @@ __device__ __forceinline__ bool named_bar_all(int id, int nthreads, bool pred) {
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                      const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
+                      const __grid_constant__ CUtensorMap tm_dkacc, const __grid_constant__ CUtensorMap tm_dvacc,
                       const __grid_constant__ CUtensorMap tm_dqacc, const Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   if (smem_u32(smem) & 1023u) {   // swizzled tiles need 1 KiB alignment; nothing has been set up yet
@@ -130,9 +138,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int lane = threadIdx.x & 31;
   const int G = p.Hq / p.Hkv;
   const int kvh = blockIdx.x % p.Hkv;
-  const int kt = p.order[blockIdx.x / p.Hkv];
-  const int list_begin = p.tile_ptr[kt];
-  const int n = p.tile_ptr[kt + 1] - list_begin;
+  const int work = p.order[blockIdx.x / p.Hkv];
+  const int kt = work % p.nkt;
+  const int list_begin = p.tile_ptr[work];
+  const int n = p.tile_ptr[work + 1] - list_begin;
   const int* list = p.tile_idx + list_begin;
   const int items = G * n;   // (query head, query tile) pairs
   const int U = 2 * items;   // 64-query units
@@ -415,42 +424,34 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       if (st >= STAGES) st -= STAGES;
     }
     if (issuer) tma_store_wait_all();
-    // epilogue: the groups of slot 0 store dV, those of slot 1 store dK; each converts 64 of the 128 columns
+    // epilogue: the groups of slot 0 add dV, those of slot 1 add dK to the fp32 accumulators: fp32 tile
+    // staged as four [128 keys][32 columns] swizzled blocks (64 KiB per tensor, over the Q / dO / dSᵀ
+    // buffers, which nothing reads any more once the last product has completed)
     bool ok = !error_is_set();
     if (ok && items > 0) ok = mbar_wait(bar_done, 0, KID, 31);
-    if (ok) {
+    if (ok && items > 0) {
       tc_fence_after();
       const uint32_t t_acc = tmem_base + ((uint32_t)(qd * 32) << 16) + 256 + b * 128;
-      uint8_t* stg = b ? sdO : sQ;   // 32 KiB each; every load and product has finished by now
+      uint8_t* stg = smem + OFF_Q + b * 65536;
       uint32_t rs[32];
 #pragma unroll 1
       for (int c = 2 * sub; c < 2 * sub + 2; ++c) {
-        if (items > 0) {
-          tmem_ld32(t_acc + c * 32, rs);
-          tmem_ld_wait();
-        } else {
+        tmem_ld32(t_acc + c * 32, rs);
+        tmem_ld_wait();
+        uint8_t* blk = stg + c * 16384;
 #pragma unroll
-          for (int e = 0; e < 32; ++e) rs[e] = 0u;
-        }
-        uint8_t* half = stg + (c >> 1) * KV_HALF_BYTES;
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint32_t a[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            a[e] = pack_bf16x2(__uint_as_float(rs[8 * v + 2 * e]), __uint_as_float(rs[8 * v + 2 * e + 1]));
-          *reinterpret_cast<uint4*>(half + sw128_offset(row, (c & 1) * 4 + v)) =
-              make_uint4(a[0], a[1], a[2], a[3]);
-        }
+        for (int v = 0; v < 8; ++v)
+          *reinterpret_cast<uint4*>(blk + sw128_offset(row, v)) =
+              make_uint4(rs[4 * v], rs[4 * v + 1], rs[4 * v + 2], rs[4 * v + 3]);
       }
       fence_proxy_async_smem();
       mbar_arrive(bar_epi + 8 * b);
       if (row == 0 && sub == 0) {
         if (mbar_wait(bar_epi + 8 * b, 0, KID, 32)) {
-          const CUtensorMap* tm = b ? &tm_dk : &tm_dv;
+          const CUtensorMap* tm = b ? &tm_dkacc : &tm_dvacc;
 #pragma unroll
-          for (int c = 0; c < 2; ++c)
-            tma_store_2d(tm, smem_u32(stg + c * KV_HALF_BYTES), kvh * HD + c * 64, kt * 128);
+          for (int c = 0; c < 4; ++c)
+            tma_reduce_add_2d(tm, smem_u32(stg + c * 16384), kvh * HD + c * 32, kt * 128);
           tma_store_commit();
           tma_store_wait_all();
         }

@@ -94,31 +94,34 @@ extern "C" int tdllm_attn_bwd(const void* q, const void* k, const void* v, const
 }
 
 namespace tdllm {
-__global__ void dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, int nq,
-                               int cols, long long lddq) {
+// fp32 [rows, cols] accumulator -> bf16 rows of a (possibly wider) destination
+__global__ void acc_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ out, int rows,
+                                int cols, long long ld_out) {
   const long long per_row = cols / 4;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (long long)nq * per_row) return;
+  if (i >= (long long)rows * per_row) return;
   const long long r = i / per_row, c = (i % per_row) * 4;
   const float4 v = *reinterpret_cast<const float4*>(acc + r * cols + c);
   uint2 o;
   o.x = pack_bf16x2(v.x, v.y);
   o.y = pack_bf16x2(v.z, v.w);
-  *reinterpret_cast<uint2*>(dq + r * lddq + c) = o;
+  *reinterpret_cast<uint2*>(out + r * ld_out + c) = o;
 }
 }  // namespace tdllm
 
-// One-pass variant: same operands plus `dq_acc`, fp32 scratch [n_qtiles*128, Hq, 128] (zeroed
-// here). The forward-side tile lists (f_*) are not needed.
+// One-pass variant. `acc`: fp32 scratch of n_qtiles*128*Hq*128 + 2*n_ktiles*128*Hkv*128 floats (dQ, dK, dV
+// accumulators, zeroed here). Work items (`w_*`): for chunk c of query tiles and key tile kt, item
+// c*n_ktiles + kt lists the chunk's query tiles that see the key tile (w_ptr has one entry per item
+// plus one); `w_order` names the non-empty items, chunk by chunk.
 extern "C" int tdllm_attn_bwd_fused(const void* q, const void* k, const void* v, const void* o,
                                     const void* dout, void* dq, void* dk, void* dv, const float* lse,
-                                    float* delta, float* dq_acc, int nq, int nk, int Hq, int Hkv,
+                                    float* delta, float* acc, int nq, int nk, int Hq, int Hkv,
                                     long long ldq, long long ldk, long long ldv, long long ldo,
                                     long long lddo, long long lddq, long long lddk, long long lddv,
                                     const int* q_lo, const int* q_hi, const int* q_grp,
-                                    const int* k_code, const int* b_ptr, const int* b_idx,
-                                    const int* b_order, int n_qtiles, int n_ktiles, float scale,
-                                    void* stream) {
+                                    const int* k_code, const int* w_ptr, const int* w_idx,
+                                    const int* w_order, int n_work, int n_qtiles, int n_ktiles,
+                                    float scale, void* stream) {
   if (nq <= 0 || nk <= 0) return 0;
   if (Hq % Hkv) {
     tdllm_host::set_last_error("attn_bwd_fused: %d query heads do not divide over %d KV heads", Hq, Hkv);
@@ -131,8 +134,8 @@ extern "C" int tdllm_attn_bwd_fused(const void* q, const void* k, const void* v,
       tdllm_host::set_last_error("attn_bwd_fused: operand %d needs 16-byte aligned base and row stride", i);
       return 1;
     }
-  if ((uintptr_t)dq_acc % 128) {
-    tdllm_host::set_last_error("attn_bwd_fused: dq accumulator must be 128-byte aligned");
+  if ((uintptr_t)acc % 128) {
+    tdllm_host::set_last_error("attn_bwd_fused: accumulator scratch must be 128-byte aligned");
     return 1;
   }
   static bool attr_set = false;
@@ -145,9 +148,12 @@ extern "C" int tdllm_attn_bwd_fused(const void* q, const void* k, const void* v,
     attr_set = true;
   }
   cudaStream_t s = (cudaStream_t)stream;
-  const int nq_pad = n_qtiles * 128;
+  const int nq_pad = n_qtiles * 128, nk_pad = n_ktiles * 128;
   const long long qc = (long long)Hq * 128, kc = (long long)Hkv * 128;
-  cudaMemsetAsync(dq_acc, 0, (size_t)nq_pad * qc * sizeof(float), s);
+  float* dq_acc = acc;
+  float* dk_acc = dq_acc + (size_t)nq_pad * qc;
+  float* dv_acc = dk_acc + (size_t)nk_pad * kc;
+  cudaMemsetAsync(acc, 0, ((size_t)nq_pad * qc + 2 * (size_t)nk_pad * kc) * sizeof(float), s);
   {
     const long long items = (long long)nq_pad * Hq;
     attn_dq::attn_delta_kernel<<<(unsigned)((items + 7) / 8), 256, 0, s>>>(
@@ -156,32 +162,44 @@ extern "C" int tdllm_attn_bwd_fused(const void* q, const void* k, const void* v,
   }
   CUtensorMap tq, tdo, tk, tv, tdk, tdv, tacc;
   {
-    // fp32 accumulator as [nq_pad rows][Hq*128]; one reduce-add copy moves 16 rows of one head
-    const uint64_t dims[2] = {(uint64_t)qc, (uint64_t)nq_pad};
-    const uint64_t strides[1] = {(uint64_t)qc * sizeof(float)};
-    const uint32_t box[2] = {128, 16};
+    // fp32 accumulators as [rows][heads*128]; one reduce-add copy moves 16 query rows (dQ) or a
+    // swizzled block of 128 key rows x 32 columns (dK, dV) of one head
+    uint64_t dims[2] = {(uint64_t)qc, (uint64_t)nq_pad};
+    uint64_t strides[1] = {(uint64_t)qc * sizeof(float)};
+    uint32_t box[2] = {128, 16};
     if (tdllm_host::encode_tmap(&tacc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dq_acc, dims, strides, box,
                                 CU_TENSOR_MAP_SWIZZLE_NONE))
+      return 3;
+    dims[0] = (uint64_t)kc; dims[1] = (uint64_t)nk_pad;
+    strides[0] = (uint64_t)kc * sizeof(float);
+    box[0] = 32; box[1] = 128;
+    if (tdllm_host::encode_tmap(&tdk, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dk_acc, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B) ||
+        tdllm_host::encode_tmap(&tdv, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dv_acc, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B))
       return 3;
   }
   if (tdllm_host::encode_rows_tmap(&tq, q, qc, nq, ldq, 64) ||
       tdllm_host::encode_rows_tmap(&tdo, dout, qc, nq, lddo, 64) ||
       tdllm_host::encode_rows_tmap(&tk, k, kc, nk, ldk, 128) ||
-      tdllm_host::encode_rows_tmap(&tv, v, kc, nk, ldv, 128) ||
-      tdllm_host::encode_rows_tmap(&tdk, dk, kc, nk, lddk, 128) ||
-      tdllm_host::encode_rows_tmap(&tdv, dv, kc, nk, lddv, 128))
+      tdllm_host::encode_rows_tmap(&tv, v, kc, nk, ldv, 128))
     return 3;
-  attn_fused::Params p;
-  p.nq_pad = nq_pad; p.Hq = Hq; p.Hkv = Hkv;
-  p.q_lo = q_lo; p.q_hi = q_hi; p.q_grp = q_grp; p.k_code = k_code;
-  p.tile_ptr = b_ptr; p.tile_idx = b_idx; p.order = b_order;
-  p.lse2 = delta + (size_t)Hq * nq_pad; p.delta = delta;
-  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
-  attn_fused::attn_bwd_fused_kernel<<<n_ktiles * Hkv, attn_fused::THREADS, attn_fused::SMEM_BYTES, s>>>(
-      tq, tdo, tk, tv, tdk, tdv, tacc, p);
+  if (n_work > 0) {
+    attn_fused::Params p;
+    p.nq_pad = nq_pad; p.Hq = Hq; p.Hkv = Hkv; p.nkt = n_ktiles;
+    p.q_lo = q_lo; p.q_hi = q_hi; p.q_grp = q_grp; p.k_code = k_code;
+    p.tile_ptr = w_ptr; p.tile_idx = w_idx; p.order = w_order;
+    p.lse2 = delta + (size_t)Hq * nq_pad; p.delta = delta;
+    p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+    attn_fused::attn_bwd_fused_kernel<<<n_work * Hkv, attn_fused::THREADS, attn_fused::SMEM_BYTES, s>>>(
+        tq, tdo, tk, tv, tdk, tdv, tacc, p);
+  }
   {
     const long long n4 = (long long)nq * (qc / 4);
-    dq_cast_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, s>>>(dq_acc, (__nv_bfloat16*)dq, nq, (int)qc, lddq);
+    acc_cast_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, s>>>(dq_acc, (__nv_bfloat16*)dq, nq, (int)qc, lddq);
+    const long long k4 = (long long)nk * (kc / 4);
+    acc_cast_kernel<<<(unsigned)((k4 + 255) / 256), 256, 0, s>>>(dk_acc, (__nv_bfloat16*)dk, nk, (int)kc, lddk);
+    acc_cast_kernel<<<(unsigned)((k4 + 255) / 256), 256, 0, s>>>(dv_acc, (__nv_bfloat16*)dv, nk, (int)kc, lddv);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

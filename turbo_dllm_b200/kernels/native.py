@@ -158,7 +158,7 @@ def lib() -> ctypes.CDLL:
 
 LAUNCHES = {"kernels": 0}
 # device kernels launched by one successful call of each entry point
-_KERNELS_PER_CALL = {"rmsnorm_bwd": 2, "qk_norm_rope_bwd": 4, "attn_bwd": 3, "attn_bwd_fused": 3}
+_KERNELS_PER_CALL = {"rmsnorm_bwd": 2, "qk_norm_rope_bwd": 4, "attn_bwd": 3, "attn_bwd_fused": 5}
 
 
 def check(rc: int, what: str) -> None:

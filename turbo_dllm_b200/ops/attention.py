@@ -127,7 +127,45 @@ class MaskLayout:
                      k_code=k_code, f_ptr=f_ptr, f_idx=f_idx, f_order=f_order, b_ptr=b_ptr, b_idx=b_idx,
                      b_order=b_order, visited_tiles=int(visible.sum()))
         self._cache["lists"] = lists
+        self._cache["visible"] = (visible, full)
         return lists
+
+    def backward_work(self, chunk_tiles: int) -> dict:
+        """Work items of the one-pass backward: for chunk c of `chunk_tiles` consecutive query tiles and
+        key tile kt, item c·nkt + kt lists the chunk's query tiles that see the key tile (entry = q_tile·2 +
+        needs_mask). `w_order` holds the non-empty items chunk by chunk, heaviest first inside a chunk, so
+        that every key tile adds to one chunk's dQ rows while those rows are still in L2."""
+        key = ("work", int(chunk_tiles))
+        if key in self._cache:
+            return self._cache[key]
+        L = self.tile_lists()
+        visible, full = self._cache["visible"]
+        dev = visible.device
+        nqt, nkt = L["nqt"], L["nkt"]
+        S = max(1, min(int(chunk_tiles), nqt)) if chunk_tiles > 0 else nqt
+        nch = (nqt + S - 1) // S
+        i32 = torch.int32
+        vis = torch.zeros(nch * S, nkt, dtype=torch.bool, device=dev)
+        vis[:nqt] = visible
+        vis = vis.view(nch, S, nkt).permute(0, 2, 1).contiguous()          # [chunk, kt, s]
+        idx = vis.nonzero()                                                 # sorted by (chunk, kt, s)
+        qt = idx[:, 0] * S + idx[:, 2]
+        ent = (qt * 2 + (~full[qt, idx[:, 1]]).long()).to(i32)
+        counts = vis.sum(2).reshape(-1)                                     # [chunk * nkt]
+        w_ptr = torch.zeros(nch * nkt + 1, dtype=i32, device=dev)
+        w_ptr[1:] = counts.cumsum(0).to(i32)
+        items = counts.nonzero().squeeze(1)
+        chunk_of = items // nkt
+        sort_key = chunk_of * (S + 1) + (S - counts[items])                 # chunk ascending, count descending
+        w_order = items[torch.argsort(sort_key, stable=True)].to(i32)
+        if ent.numel() == 0:
+            ent = torch.zeros(1, dtype=i32, device=dev)
+        if w_order.numel() == 0:
+            w_order = torch.zeros(1, dtype=i32, device=dev)
+        out = dict(w_ptr=w_ptr.contiguous(), w_idx=ent.contiguous(), w_order=w_order.contiguous(),
+                   n_work=int(items.numel()), chunk_tiles=S)
+        self._cache[key] = out
+        return out
 
 
 def attention_reference(q, k, v, layout: MaskLayout, scale: float | None = None):
@@ -224,9 +262,16 @@ native.register_signatures({
                        + [native.c_void_p] * 10 + [native.c_int, native.c_int, native.c_float,
                                                    native.c_void_p]),
     "tdllm_attn_bwd_fused": (native.c_int, [native.c_void_p] * 11 + [native.c_int] * 4 + [native.c_ll] * 8
-                             + [native.c_void_p] * 7 + [native.c_int, native.c_int, native.c_float,
+                             + [native.c_void_p] * 7 + [native.c_int, native.c_int, native.c_int, native.c_float,
                                                         native.c_void_p]),
 })
+
+
+def backward_chunk_tiles() -> int:
+    """Query tiles per chunk of the one-pass backward (TDLLM_ATTN_BWD_CHUNK; 0 = one chunk). Tiles of
+    128 rows touch 2 MiB of the dQ accumulator each at 32 heads; 64 per chunk measured best at 32k and 128k
+    rows (the accumulator rows of a chunk mostly stay in the 126 MB L2 while all key tiles add to them)."""
+    return int(os.environ.get("TDLLM_ATTN_BWD_CHUNK", "64"))
 
 
 def backward_mode() -> str:
@@ -267,13 +312,15 @@ def attention_backward_native(q, k, v, out, dout, lse, layout: MaskLayout, scale
         lse = padded
     delta = torch.empty(2, Hq, L["nq_pad"], dtype=torch.float32, device=dev)
     if backward_mode() == "fused":
-        acc = scratch(dev, L["nq_pad"] * Hq * D, key="attn_dq_acc")
+        W = layout.backward_work(backward_chunk_tiles())
+        acc = scratch(dev, L["nq_pad"] * Hq * D + 2 * L["nk_pad"] * Hkv * D, key="attn_bwd_acc")
         rc = native.lib().tdllm_attn_bwd_fused(
             ptr(q), ptr(k), ptr(v), ptr(out), ptr(dout), ptr(dq), ptr(dk), ptr(dv), ptr(lse), ptr(delta), ptr(acc),
             nq, nk, Hq, Hkv, _rows_view(q), _rows_view(k), _rows_view(v), _rows_view(out),
             dout.stride(0), dq.stride(0), dk.stride(0), dv.stride(0),
             ptr(L["q_lo"]), ptr(L["q_hi"]), ptr(L["q_grp"]), ptr(L["k_code"]),
-            ptr(L["b_ptr"]), ptr(L["b_idx"]), ptr(L["b_order"]), L["nqt"], L["nkt"], float(scale), stream())
+            ptr(W["w_ptr"]), ptr(W["w_idx"]), ptr(W["w_order"]), W["n_work"], L["nqt"], L["nkt"], float(scale),
+            stream())
         native.check(rc, "attn_bwd_fused")
         return dq, dk, dv
     rc = native.lib().tdllm_attn_bwd(
