@@ -87,8 +87,11 @@ def run_ours(args):
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         loss, d2h = None, 0
+        marks = [start]
         for _ in range(steps):
             r = session.step()
+            marks.append(torch.cuda.Event(enable_timing=True))
+            marks[-1].record()
             if read_loss:
                 loss = float(r.loss_sum) / r.denominator * world   # device -> host every step (rank-local part)
                 d2h = r.loss_sum.element_size()
@@ -102,6 +105,7 @@ def run_ours(args):
             if world > 1:
                 dist.all_reduce(t)
             loss = float(t) / r.denominator
+        timed.each = [round(a.elapsed_time(b), 1) for a, b in zip(marks[:-1], marks[1:])]
         return float(ms) / steps, loss, native.LAUNCHES["kernels"], r, d2h
 
     session = TrainingSession(spec, device=f"cuda:{local_rank}")
@@ -112,6 +116,7 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     ms, loss, launches, last, _ = timed(session, args.steps, read_loss=False)
+    each_ms = timed.each
     clocks = sampler.stop() if rank == 0 else None
     native.raise_on_device_error()
     tokens_per_step = args.batch_per_gpu * args.seq_len * world
@@ -156,6 +161,7 @@ def run_ours(args):
             "model_tflop_per_step": fl.total / 1e12,
             "mfu_pct_of_nominal_2250": model_flops_utilization_pct(fl.total, ms / 1e3, world, 2250.0),
             "gpu_launches": launches, "loss": loss, "clocks": clocks, "e2e": e2e,
+            "ms_each_step_rank0": each_ms,
         }
         if peaks.get("bf16_tflops_sustained"):
             out["mfu_pct_of_measured_sustained"] = model_flops_utilization_pct(

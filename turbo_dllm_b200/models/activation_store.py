@@ -32,12 +32,17 @@ class ActivationStore:
         self.recording = False      # True while a checkpointed layer runs its no-grad forward
         self.replaying = False      # True while a checkpointed layer is recomputed for backward
         self.keep_attention = True  # stash (out, lse) of the attention op across the boundary
+        # attention outputs of layers >= this index stay on the device even when the others are offloaded
+        # (the backward pass needs the last layers first, while earlier ones are still being fetched)
+        self.attention_resident_from = 1 << 30
 
     def has(self, idx) -> bool:
         return idx in self.kept or idx in self.ready
 
     def _to_host(self, idx) -> bool:
-        return self.offload_attention if isinstance(idx, tuple) else self.offload
+        if isinstance(idx, tuple):
+            return self.offload_attention and idx[0] < self.attention_resident_from
+        return self.offload
 
     def stash(self, idx, x: torch.Tensor) -> None:
         if not self._to_host(idx):

@@ -92,9 +92,10 @@ class TrainingSession:
                                    dropout=spec.adapter.dropout, targets=spec.adapter.targets or ("attention", "mlp"),
                                    seed=seed)
         keep = os.environ.get("TDLLM_KEEP_ATTENTION")
-        _, off_attn, keep_attn = self._memory_plan()
+        _, off_attn, keep_attn, resident = self._memory_plan()
         self.model.store.keep_attention = (keep == "1") if keep is not None else keep_attn
         self.model.store.offload_attention = off_attn and self.device.type == "cuda"
+        self.model.store.attention_resident_from = self.cfg.num_layers - resident
         if self.model.store.offload_attention and self.model.store.stream is None:
             self.model.store.stream = torch.cuda.Stream(device=self.device)
         dp_rank = runtime.sample_parallel_rank if runtime is not None else self.rank
@@ -190,29 +191,36 @@ class TrainingSession:
         self.scheduler = RunSpecLRScheduler.from_run_spec(spec)
         self.steps_done = 0
 
-    def _memory_plan(self) -> tuple[bool, bool, bool]:
-        """(offload layer inputs, offload attention out/lse, keep attention out/lse at all).
+    def _memory_plan(self) -> tuple[bool, bool, bool, int]:
+        """(offload layer inputs, offload attention out/lse, keep attention out/lse at all, number of
+        last layers whose attention outputs stay on the device although the others are offloaded).
 
         Keeping the attention output of every layer saves the forward kernel in the recomputation.
         Everything stays in HBM when it fits next to parameters, gradients, optimizer shard and one
-        layer's working set; otherwise the attention outputs go to pinned host memory first, and the
-        layer inputs follow only if that is still not enough (the copies hide behind the GEMMs)."""
+        layer's working set; otherwise the attention outputs go to pinned host memory first (all but as
+        many of the last layers as still fit), and the layer inputs follow only if that is still not
+        enough. The copies hide behind the GEMMs as long as the host link keeps up, so less is better."""
         env = os.environ.get("TDLLM_ACTIVATION_OFFLOAD")
         if env is not None:
-            return env == "1", env == "1", True
+            return env == "1", env == "1", True, 0
         if self.device.type != "cuda" or not self.spec.training.activation_checkpointing:
-            return False, False, self.device.type == "cuda"
+            return False, False, self.device.type == "cuda", 0
         cfg, s = self.cfg, self.spec
         rows = 3 * s.model.seq_len * s.training.batch_size  # upper bound: two noisy views + clean
-        ckpt = rows * cfg.hidden_size * 2 * cfg.num_layers
+        per_layer = rows * cfg.hidden_size * 2
+        ckpt = per_layer * cfg.num_layers
         work = rows * 2 * (6 * cfg.hidden_size + 2 * cfg.qkv_dim + 5 * max(cfg.intermediate_size, 1))
         static = cfg.num_params() * (2 + 2 + 12 / max(self.world, 1))
         budget = 0.85 * torch.cuda.get_device_properties(self.device).total_memory
         if static + 2 * ckpt + work < budget:
-            return False, False, True
+            return False, False, True, 0
         if static + ckpt + work < budget:
-            return False, True, True
-        return True, True, True
+            resident = int((budget - static - ckpt - work) // (per_layer * 1.02))
+            return False, True, True, max(0, min(resident, cfg.num_layers))
+        # both streams go to the host. Keeping some attention outputs resident was measured slower here:
+        # with 156 of 178 GiB allocated the caching allocator runs out of reusable blocks mid-step
+        # (growable segments were slower still), so the whole budget is left to the working set.
+        return True, True, True, 0
 
     def _want_activation_offload(self) -> bool:
         return self._memory_plan()[0]
