@@ -182,3 +182,42 @@ def test_tp2_on_gpus_matches_single_gpu():
         assert losses == pytest.approx(ref[0], rel=3e-2)
         assert norm == pytest.approx(ref[1], rel=5e-2)
         assert (torch.from_numpy(fnorm) - torch.from_numpy(ref[2])).abs().max().item() < 2e-2
+
+
+def _fused_allreduce_gemm(rank, world):
+    """Every rank holds a K-slice of x and w; the GEMM's epilogue must deliver the full sum everywhere."""
+    import os
+
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.parallel.fused_allreduce import FusedAllReduceGemm
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    ws = FusedAllReduceGemm(dist.group.WORLD, dev, max_rows=1000, n_cols=520)
+    errs = []
+    # several calls in a row (both workspaces, growing epochs), row counts that leave ragged and empty tiles
+    for call, (M, K) in enumerate([(1000, 136), (384, 64), (1000, 320), (130, 72), (777, 136)]):
+        g = torch.Generator(device="cpu").manual_seed(100 * call + 1)
+        x_full = torch.randn(M, K * world, generator=g).bfloat16()
+        w_full = (torch.randn(520, K * world, generator=g) * 0.1).bfloat16()
+        res = torch.randn(M, 520, generator=g).bfloat16()
+        x = x_full[:, rank * K:(rank + 1) * K].contiguous().to(dev)
+        w = w_full[:, rank * K:(rank + 1) * K].contiguous().to(dev)
+        out = ws.matmul(x, w, residual=res.to(dev) if call % 2 == 0 else None)
+        torch.cuda.synchronize()
+        native.raise_on_device_error()
+        ref = x_full.float() @ w_full.float().t() + (res.float() if call % 2 == 0 else 0)
+        errs.append(((out.float().cpu() - ref).abs().max() / ref.abs().max()).item())
+    dist.barrier()
+    ws.close()
+    return errs
+
+
+@pytest.mark.distributed
+def test_gemm_with_allreduce_epilogue_over_peer_memory():
+    _need(2)
+    for errs in run_ranks(_fused_allreduce_gemm, 2, backend="nccl", deadline_s=300):
+        assert max(errs) < 2e-2, errs

@@ -28,6 +28,16 @@ int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, 
                     int max_ctas, const void* c_src, long long ldc, void* stream);
 int tdllm_gemm_n_tiles(int N);
 
+// Row-parallel product with the all-reduce done in the epilogue over peer memory: D = sum_r A_r * B_r (+ C).
+// ws[d] / flags[d]: rank d's workspace ([world][ws_rows][N] bf16) and flags ([world][tdllm_gemm_flag_count(M,N)]
+// int32, zeroed once) as mapped here. `epoch` grows per call on one workspace; alternate two workspaces.
+int tdllm_gemm_allreduce_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
+                              long long ldb, long long ldd, int a_mn_major, int b_mn_major,
+                              const void* c_src, long long ldc, int world, int rank, int epoch,
+                              long long ws_rows, void* const* ws, void* const* flags, int max_ctas,
+                              void* stream);
+int tdllm_gemm_flag_count(int M, int N);
+
 // ---- normalisation / rotary / activation ---------------------------------
 int tdllm_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out,
                       float* rstd, int rows, int H, float eps, void* stream);

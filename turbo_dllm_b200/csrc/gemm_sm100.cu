@@ -10,7 +10,12 @@
 //
 // Epilogues: plain store (bf16 or fp32, optional accumulate into the destination),
 // SwiGLU on interleaved gate/up columns, cross-entropy row statistics (no logits
-// written), and cross-entropy gradient of the logits (written as bf16).
+// written), cross-entropy gradient of the logits (written as bf16), and an all-reduce over
+// peer memory for products whose K dimension is split over ranks (row-parallel linears):
+// every epilogue warp writes its bf16 partial tile into the workspace of every rank (plain
+// peer stores), publishes a per-(tile, warp) flag, and one tile later sums the partials that
+// have arrived in its own workspace (+ residual) into the destination. The transfer of a tile
+// overlaps the tensor-core work on the next ones; no collective call is involved.
 //
 // This replaces the library GEMMs the reference calls (cublasGemmEx in
 // dllm_parallel/core/csrc/fused_linear_ce/fused_linear_ce_cuda.cu:618-791 and the
@@ -51,7 +56,9 @@ enum EpilogueMode : int {
   EPI_SWIGLU = 1,    // D[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1], bf16, N_out = N/2
   EPI_CE_STATS = 2,  // per (row, n-tile): max, sum exp, target logit -> fp32 scratch
   EPI_CE_GRAD = 3,   // D = (exp(acc - lse[row]) - onehot(label[row])) * rowscale[row], bf16
+  EPI_ALLREDUCE = 4, // D = sum over ranks of acc (+ C), bf16, partial tiles exchanged through peer memory
 };
+constexpr int AR_MAX_RANKS = 8;
 
 struct GemmParams {
   int M, N, K;
@@ -71,6 +78,14 @@ struct GemmParams {
   float* stats;           // [M, n_tiles, 3]
   int exclude_index;      // column removed from the softmax (-1 = none)
   float softcap;          // 0 = off
+  // all-reduce epilogue: workspace of rank d (as mapped here) holds [ranks][ar_rows][N] bf16 partials,
+  // flags of rank d hold [ranks][tiles * 4] epochs (one per source rank, 128-row tile and 32-row warp slice)
+  int ar_world, ar_rank, ar_epoch;
+  long long ar_rows;
+  void* ar_ws[AR_MAX_RANKS];
+  int* ar_flags[AR_MAX_RANKS];
+  void* ar_out;       // destination (this rank's memory), row stride ar_ldd elements
+  long long ar_ldd;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& m, int& n) {
@@ -86,6 +101,61 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
 
 __device__ __forceinline__ float apply_softcap(float x, float cap) {
   return cap > 0.f ? cap * tanhf(x / cap) : x;
+}
+
+// Second half of the all-reduce epilogue for the 32 x 256 slice (tile tm/tn, warp slice q): wait (bounded)
+// until every rank's partial of this slice has landed in this rank's workspace, then D = sum (+ C).
+// Lane l owns 16-byte pieces l, l+32, ... of each 512-byte row slice: all accesses are coalesced.
+__device__ __forceinline__ bool ar_reduce(const GemmParams& p, int tm, int tn, int q, int lane) {
+  const int fidx = (tm * p.n_tiles + tn) * 4 + q;
+  const size_t per_rank_flags = (size_t)p.m_tiles * p.n_tiles * 4;
+  bool ok = true;
+  if (lane < p.ar_world)
+    ok = flag_wait_geq(p.ar_flags[p.ar_rank] + lane * per_rank_flags + fidx, p.ar_epoch, GEMM_KERNEL_ID, 40 + lane);
+  if (!__all_sync(0xffffffffu, ok)) return false;
+  const __nv_bfloat16* ws = (const __nv_bfloat16*)p.ar_ws[p.ar_rank];
+  const size_t slot_stride = (size_t)p.ar_rows * p.N;
+  const int col = tn * BN + lane * 8;
+  if (col >= p.N) return true;
+#pragma unroll 1
+  for (int rr = 0; rr < 32; ++rr) {
+    const int grow = tm * BM + q * 32 + rr;
+    if (grow >= p.M) break;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int s = 0; s < p.ar_world; ++s) {
+      uint4 v;
+      // written by a peer through NVLink: bypass L1, which may hold lines of an earlier call
+      asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                   : "l"(ws + s * slot_stride + (size_t)grow * p.N + col));
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+    if (p.accumulate) {
+      const uint4 v = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.c_ptr + (size_t)grow * p.ldc + col);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>((__nv_bfloat16*)p.ar_out + (size_t)grow * p.ar_ldd + col) = o;
+  }
+  return true;
 }
 
 template <int PAIR>
@@ -253,6 +323,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint8_t* my_stage = epi_smem + (warp - 2) * 2 * EPI_BUF_BYTES;
     int sbuf = 0;
     int it = 0;
+    int ar_prev_tm = -1, ar_prev_tn = 0;   // all-reduce epilogue: tile whose sum is still owed
     for (int t = walker; t < num_tiles; t += walkers, ++it) {
       int tm, tn;
       tile_coords(t, m_groups, p.n_tiles, tm, tn);
@@ -298,6 +369,60 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           o[1] = sum;
           o[2] = (label >= n0 && label < n0 + BN) ? tgt : 0.f;
         }
+      } else if (p.mode == EPI_ALLREDUCE) {
+        // 1. this warp's 32 x 256 partial, as bf16, into every rank's workspace (slot of this rank)
+        const bool live = tm < p.m_tiles;   // a pair's second CTA may sit past the last row tile
+        const size_t slot = (size_t)p.ar_rank * p.ar_rows * p.N;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint8_t* st = my_stage + sbuf * EPI_BUF_BYTES;
+          __syncwarp();
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            tmem_ld32(taddr + c * 64 + h * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t a0 = pack_bf16x2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]));
+              const uint32_t a1 = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+              const uint32_t a2 = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+              const uint32_t a3 = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+              *reinterpret_cast<uint4*>(st + sw128_offset(lane, h * 4 + i)) = make_uint4(a0, a1, a2, a3);
+            }
+          }
+          __syncwarp();
+          // 32 rows x 128 bytes: lane l moves the 16-byte pieces l, l+32, ... (8 consecutive lanes = one row)
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int piece = k * 32 + lane;
+            const int rr = piece >> 3, ch = piece & 7;
+            const int grow = tm * BM + q * 32 + rr;
+            const int col = n0 + c * 64 + ch * 8;
+            if (grow < p.M && col < p.N) {
+              const uint4 v = *reinterpret_cast<const uint4*>(st + sw128_offset(rr, ch));
+              const size_t off = slot + (size_t)grow * p.N + col;
+              for (int d = 0; d < p.ar_world; ++d)
+                *reinterpret_cast<uint4*>((__nv_bfloat16*)p.ar_ws[d] + off) = v;
+            }
+          }
+          sbuf ^= 1;
+        }
+        // accumulator buffer is free again (the partial is out of TMEM); publish the slice everywhere
+        tc_fence_before();
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          if (PAIR == 2) mbar_arrive_cluster((bar_tempty + 8 * buf) & PEER_BIT_MASK);
+          else mbar_arrive(bar_tempty + 8 * buf);
+          const int fidx = (tm * p.n_tiles + tn) * 4 + q;
+          for (int d = 0; d < p.ar_world && live; ++d)
+            flag_store_release(p.ar_flags[d] + (size_t)p.ar_rank * p.m_tiles * p.n_tiles * 4 + fidx, p.ar_epoch);
+        }
+        // 2. one tile behind: sum what has arrived here for the previous tile of this CTA
+        if (ar_prev_tm >= 0 && !ar_reduce(p, ar_prev_tm, ar_prev_tn, q, lane)) break;
+        ar_prev_tm = live ? tm : -1;
+        ar_prev_tn = tn;
+        continue;
       } else if (p.mode == EPI_SWIGLU) {
 #pragma unroll 1
         for (int c = 0; c < BN / 128; ++c) {
@@ -437,6 +562,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         else mbar_arrive(bar_tempty + 8 * buf);
       }
     }
+    if (p.mode == EPI_ALLREDUCE && ar_prev_tm >= 0) ar_reduce(p, ar_prev_tm, ar_prev_tn, q, lane);
     if (lane == 0) tma_store_wait_all();
   }
 
@@ -466,13 +592,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // ---------------------------------------------------------------------------
 using namespace tdllm;
 
-extern "C" int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K,
-                               long long lda, long long ldb, long long ldd, int a_mn_major,
-                               int b_mn_major, int out_fp32, int accumulate, int mode,
-                               const int* labels, const float* lse, const float* rowscale,
-                               float* stats, int exclude_index, float softcap, int max_ctas,
-                               const void* c_src, long long ldc, void* stream) {
+struct ArConfig {
+  int world, rank, epoch;
+  long long rows;
+  void* const* ws;
+  void* const* flags;
+};
+
+static int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
+                     long long ldb, long long ldd, int a_mn_major, int b_mn_major, int out_fp32,
+                     int accumulate, int mode, const int* labels, const float* lse,
+                     const float* rowscale, float* stats, int exclude_index, float softcap,
+                     int max_ctas, const void* c_src, long long ldc, const ArConfig* ar, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (mode == EPI_ALLREDUCE) {
+    if (!ar || ar->world < 2 || ar->world > AR_MAX_RANKS || ar->rank < 0 || ar->rank >= ar->world ||
+        out_fp32 || (N % 8) || ar->rows < M) {
+      tdllm_host::set_last_error("gemm: all-reduce epilogue needs 2..%d ranks, bf16 output, N %% 8 == 0 and a "
+                                 "workspace of at least M rows", AR_MAX_RANKS);
+      return 1;
+    }
+  }
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A % 16) || ((uintptr_t)B % 16)) {
     tdllm_host::set_last_error("gemm: operands need 16-byte aligned base and row stride");
     return 1;
@@ -563,6 +703,12 @@ extern "C" int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int
   }
   p.labels = labels; p.lse = lse; p.rowscale = rowscale; p.stats = stats;
   p.exclude_index = exclude_index; p.softcap = softcap;
+  p.ar_world = 0; p.ar_rank = 0; p.ar_epoch = 0; p.ar_rows = 0; p.ar_out = D; p.ar_ldd = ldd;
+  for (int i = 0; i < AR_MAX_RANKS; ++i) { p.ar_ws[i] = nullptr; p.ar_flags[i] = nullptr; }
+  if (mode == EPI_ALLREDUCE) {
+    p.ar_world = ar->world; p.ar_rank = ar->rank; p.ar_epoch = ar->epoch; p.ar_rows = ar->rows;
+    for (int i = 0; i < ar->world; ++i) { p.ar_ws[i] = ar->ws[i]; p.ar_flags[i] = (int*)ar->flags[i]; }
+  }
   cudaError_t e;
   if (pair) {
     const int tiles = ((p.m_tiles + 1) / 2) * p.n_tiles;
@@ -590,5 +736,36 @@ extern "C" int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int
   }
   return 0;
 }
+
+extern "C" int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K,
+                               long long lda, long long ldb, long long ldd, int a_mn_major,
+                               int b_mn_major, int out_fp32, int accumulate, int mode,
+                               const int* labels, const float* lse, const float* rowscale,
+                               float* stats, int exclude_index, float softcap, int max_ctas,
+                               const void* c_src, long long ldc, void* stream) {
+  if (mode == EPI_ALLREDUCE) {
+    tdllm_host::set_last_error("gemm: the all-reduce epilogue is reached through tdllm_gemm_allreduce_bf16");
+    return 1;
+  }
+  return gemm_impl(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, out_fp32, accumulate, mode,
+                   labels, lse, rowscale, stats, exclude_index, softcap, max_ctas, c_src, ldc, nullptr, stream);
+}
+
+// D = sum over the `world` ranks of (A_r * B_r) (+ C): every rank calls this with its K-slice of A and B.
+// ws[d] / flags[d]: rank d's workspace ([world][ws_rows][N] bf16) and flag array ([world][m_tiles*n_tiles*4]
+// int32, zero at allocation) as mapped into this process; `epoch` must grow from call to call on one
+// workspace, and two workspaces must alternate between consecutive calls (a rank may start the next call
+// while a peer still sums the previous one).
+extern "C" int tdllm_gemm_allreduce_bf16(const void* A, const void* B, void* D, int M, int N, int K,
+                                         long long lda, long long ldb, long long ldd, int a_mn_major,
+                                         int b_mn_major, const void* c_src, long long ldc, int world,
+                                         int rank, int epoch, long long ws_rows, void* const* ws,
+                                         void* const* flags, int max_ctas, void* stream) {
+  ArConfig ar{world, rank, epoch, ws_rows, ws, flags};
+  return gemm_impl(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, 0, c_src != nullptr, EPI_ALLREDUCE,
+                   nullptr, nullptr, nullptr, nullptr, -1, 0.f, max_ctas, c_src, ldc, &ar, stream);
+}
+
+extern "C" int tdllm_gemm_flag_count(int M, int N) { return ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * 4; }
 
 extern "C" int tdllm_gemm_n_tiles(int N) { return (N + BN - 1) / BN; }

@@ -158,13 +158,17 @@ class _RowParallelResidual(torch.autograd.Function):
     full gradient of the (replicated) residual stream."""
 
     @staticmethod
-    def forward(ctx, x, w, res, group, rank, value_unused=False):
+    def forward(ctx, x, w, res, group, rank, value_unused=False, tp=None):
         import torch.distributed as dist
 
         ctx.save_for_backward(x, w)
         ctx.wref = w
         if value_unused:
             return torch.empty_like(res)
+        x2, r2 = _as2d(x), _as2d(res)
+        fused = tp.fused_allreduce(r2.shape[0], r2.shape[1], x.device) if (tp is not None and use_native(x, w)) else None
+        if fused is not None:   # all-reduce inside the GEMM epilogue over peer memory
+            return fused.matmul(x2 if x2.is_contiguous() else x2.contiguous(), w, residual=r2).view(res.shape)
         out = gemm(x, w, residual=_as2d(res) if rank == 0 else None)
         dist.all_reduce(out, group=group)
         return out.view(res.shape)
@@ -182,7 +186,7 @@ class _RowParallelResidual(torch.autograd.Function):
                 mark_grad_written(ctx.wref)
             else:
                 dw = gemm(dy2, _as2d(x), a_mn_major=True, b_mn_major=True, out_dtype=w.dtype)
-        return dx, dw, (dy if ctx.needs_input_grad[2] else None), None, None, None
+        return dx, dw, (dy if ctx.needs_input_grad[2] else None), None, None, None, None
 
 
 def row_parallel_linear_residual(x, w_shard, res, tp, last: bool = False) -> torch.Tensor:
@@ -191,7 +195,7 @@ def row_parallel_linear_residual(x, w_shard, res, tp, last: bool = False) -> tor
     unused = last and _Replay.skip_last_output and torch.is_grad_enabled()
     if tp is None or tp.size == 1:
         return _LinearResidual.apply(x, w_shard, res, unused)
-    return _RowParallelResidual.apply(x, w_shard, res, tp.group, tp.rank, unused)
+    return _RowParallelResidual.apply(x, w_shard, res, tp.group, tp.rank, unused, tp)
 
 
 class _LinearSwiGLU(torch.autograd.Function):

@@ -130,6 +130,29 @@ class TPContext:
         self.size = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
         self.sequence_parallel = bool(sequence_parallel) and self.size > 1
+        self._fused_ar: dict = {}
+        # TDLLM_TP_FUSED_ALLREDUCE=0 keeps the row-parallel projections on GEMM + NCCL all-reduce
+        import os
+
+        self.fused_allreduce_enabled = os.environ.get("TDLLM_TP_FUSED_ALLREDUCE", "1") != "0"
+
+    def fused_allreduce(self, rows: int, cols: int, device):
+        """Workspace of the GEMM whose epilogue all-reduces over peer memory, or None when the group
+        cannot use it (CPU, no peer access, more than 8 ranks). Grown when a call brings more rows."""
+        if not self.fused_allreduce_enabled or self.size < 2 or torch.device(device).type != "cuda":
+            return None
+        ws = self._fused_ar.get(cols)
+        if ws is not None and ws is not False and ws.max_rows >= rows:
+            return ws
+        if ws is False:
+            return None
+        from .fused_allreduce import maybe_create
+
+        if ws is not None:
+            ws.close()
+        ws = maybe_create(self.group, torch.device(device), rows, cols)
+        self._fused_ar[cols] = ws if ws is not None else False
+        return ws
 
     def shard(self, full: torch.Tensor, dim: int) -> torch.Tensor:
         n = full.shape[dim] // self.size
