@@ -155,6 +155,7 @@ def _tp(rank, world, tp, steps):
     from turbo_dllm_b200.training.session import TrainingSession
 
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["TDLLM_TP_FUSED_ALLREDUCE_MIN_K"] = "0"   # the tiny model's projections take the fused path too
     torch.cuda.set_device(rank)
     spec = RunSpec.from_mapping({
         "model": {"id": "synthetic:tiny-hd128", "seq_len": 512, "dtype": "bf16"},

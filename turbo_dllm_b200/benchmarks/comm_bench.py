@@ -13,6 +13,8 @@ and direction, divided by the measured peer-copy bandwidth of this pool (770 GB/
   HBM traffic) runs between the two.
 * clean K|V gather (`tdllm_kv_gather`): every rank pulls the other ranks' rows once.
 * its NCCL twins (`reduce_scatter` + `all_gather`, `all_gather`) on the same sizes.
+* row-parallel GEMM with the all-reduce in its epilogue (`tdllm_gemm_allreduce_bf16`) against the same GEMM
+  followed by an NCCL all-reduce; its roofline is the slower of FLOPs ÷ measured GEMM peak and pushed bytes ÷ 770 GB/s.
 """
 from __future__ import annotations
 
@@ -57,6 +59,9 @@ def main(argv=None):
     ap.add_argument("--params", type=int, default=2_000_000_000, help="bf16 parameters in the flat buffer")
     ap.add_argument("--kv-rows", type=int, default=16384, help="clean rows owned by every rank")
     ap.add_argument("--kv-row-elems", type=int, default=2048, help="K|V elements per row (2 * kv heads * head dim)")
+    ap.add_argument("--tp-rows", type=int, default=32768, help="rows of the row-parallel products")
+    ap.add_argument("--tp-hidden", type=int, default=4096)
+    ap.add_argument("--tp-k", type=int, nargs="+", default=[4096, 12288], help="full K of the products (split over ranks)")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)
@@ -122,6 +127,40 @@ def main(argv=None):
     out.append({"kernel": "nccl all_gather of the same rows", "world": world, "ms": round(ms4, 3),
                 "fraction_of_roofline": round(pulled / (PEER_GBS * 1e9) * 1e3 / ms4, 3)})
     ex.close()
+    del full, x
+    torch.cuda.empty_cache()
+
+    # ---- row-parallel GEMM with the all-reduce in its epilogue vs GEMM + NCCL all-reduce
+    from turbo_dllm_b200.ops.gemm import gemm
+    from turbo_dllm_b200.parallel.fused_allreduce import FusedAllReduceGemm
+
+    peaks_tflops = 1604.6   # measured cuBLAS bf16 burst rate of this pool
+    M, N = args.tp_rows, args.tp_hidden
+    ws = FusedAllReduceGemm(group, dev, M, N)
+    for k_full in args.tp_k:
+        K = k_full // world
+        a = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+        w = (torch.randn(N, K, device=dev) * 0.05).bfloat16()
+        res = torch.randn(M, N, device=dev).bfloat16()
+        o1 = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        ms_f = _time(lambda: ws.matmul(a, w, residual=res, out=o1), args.iters, args.warmup)
+        native.raise_on_device_error()
+
+        def twin():
+            o = gemm(a, w, residual=res if rank == 0 else None)
+            dist.all_reduce(o, group=group)
+            return o
+
+        ms_n = _time(twin, args.iters, args.warmup)
+        flops = 2.0 * M * N * K
+        link = (world - 1) * M * N * 2
+        roof = max(flops / (peaks_tflops * 1e12), link / (PEER_GBS * 1e9)) * 1e3
+        out.append({"kernel": "gemm_allreduce (tcgen05 tiles + peer stores in one kernel)", "world": world,
+                    "shape": f"{M}x{N}x{K} per rank", "ms": round(ms_f, 3), "gemm_plus_nccl_allreduce_ms": round(ms_n, 3),
+                    "tflops_per_gpu": round(flops / ms_f / 1e9, 1), "nvlink_bytes_out": link,
+                    "roofline_ms": round(roof, 3), "fraction_of_roofline": round(roof / ms_f, 3),
+                    "bound": "compute" if flops / (peaks_tflops * 1e12) > link / (PEER_GBS * 1e9) else "nvlink"})
+    ws.close()
     if rank == 0:
         for rec in out:
             print(json.dumps(rec), flush=True)

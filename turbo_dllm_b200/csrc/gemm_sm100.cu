@@ -12,10 +12,11 @@
 // SwiGLU on interleaved gate/up columns, cross-entropy row statistics (no logits
 // written), cross-entropy gradient of the logits (written as bf16), and an all-reduce over
 // peer memory for products whose K dimension is split over ranks (row-parallel linears):
-// every epilogue warp writes its bf16 partial tile into the workspace of every rank (plain
-// peer stores), publishes a per-(tile, warp) flag, and one tile later sums the partials that
-// have arrived in its own workspace (+ residual) into the destination. The transfer of a tile
-// overlaps the tensor-core work on the next ones; no collective call is involved.
+// every epilogue warp writes its bf16 partial slice into the workspace of every other rank (plain
+// peer stores), publishes a per-(tile, warp) flag, waits for the peers' flags of the same slice and
+// adds their partials (+ residual) to its own fp32 accumulator, which never leaves TMEM. Ranks
+// walk the tiles in the same order, so the exchange of one tile overlaps the tensor-core work on
+// the next (two accumulator buffers); no collective call is involved.
 //
 // This replaces the library GEMMs the reference calls (cublasGemmEx in
 // dllm_parallel/core/csrc/fused_linear_ce/fused_linear_ce_cuda.cu:618-791 and the
@@ -101,61 +102,6 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
 
 __device__ __forceinline__ float apply_softcap(float x, float cap) {
   return cap > 0.f ? cap * tanhf(x / cap) : x;
-}
-
-// Second half of the all-reduce epilogue for the 32 x 256 slice (tile tm/tn, warp slice q): wait (bounded)
-// until every rank's partial of this slice has landed in this rank's workspace, then D = sum (+ C).
-// Lane l owns 16-byte pieces l, l+32, ... of each 512-byte row slice: all accesses are coalesced.
-__device__ __forceinline__ bool ar_reduce(const GemmParams& p, int tm, int tn, int q, int lane) {
-  const int fidx = (tm * p.n_tiles + tn) * 4 + q;
-  const size_t per_rank_flags = (size_t)p.m_tiles * p.n_tiles * 4;
-  bool ok = true;
-  if (lane < p.ar_world)
-    ok = flag_wait_geq(p.ar_flags[p.ar_rank] + lane * per_rank_flags + fidx, p.ar_epoch, GEMM_KERNEL_ID, 40 + lane);
-  if (!__all_sync(0xffffffffu, ok)) return false;
-  const __nv_bfloat16* ws = (const __nv_bfloat16*)p.ar_ws[p.ar_rank];
-  const size_t slot_stride = (size_t)p.ar_rows * p.N;
-  const int col = tn * BN + lane * 8;
-  if (col >= p.N) return true;
-#pragma unroll 1
-  for (int rr = 0; rr < 32; ++rr) {
-    const int grow = tm * BM + q * 32 + rr;
-    if (grow >= p.M) break;
-    float acc[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-    for (int s = 0; s < p.ar_world; ++s) {
-      uint4 v;
-      // written by a peer through NVLink: bypass L1, which may hold lines of an earlier call
-      asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                   : "l"(ws + s * slot_stride + (size_t)grow * p.N + col));
-      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __bfloat1622float2(h2[e]);
-        acc[2 * e] += f.x;
-        acc[2 * e + 1] += f.y;
-      }
-    }
-    if (p.accumulate) {
-      const uint4 v = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.c_ptr + (size_t)grow * p.ldc + col);
-      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __bfloat1622float2(h2[e]);
-        acc[2 * e] += f.x;
-        acc[2 * e + 1] += f.y;
-      }
-    }
-    uint4 o;
-    o.x = pack_bf16x2(acc[0], acc[1]);
-    o.y = pack_bf16x2(acc[2], acc[3]);
-    o.z = pack_bf16x2(acc[4], acc[5]);
-    o.w = pack_bf16x2(acc[6], acc[7]);
-    *reinterpret_cast<uint4*>((__nv_bfloat16*)p.ar_out + (size_t)grow * p.ar_ldd + col) = o;
-  }
-  return true;
 }
 
 template <int PAIR>
@@ -323,7 +269,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint8_t* my_stage = epi_smem + (warp - 2) * 2 * EPI_BUF_BYTES;
     int sbuf = 0;
     int it = 0;
-    int ar_prev_tm = -1, ar_prev_tn = 0;   // all-reduce epilogue: tile whose sum is still owed
     for (int t = walker; t < num_tiles; t += walkers, ++it) {
       int tm, tn;
       tile_coords(t, m_groups, p.n_tiles, tm, tn);
@@ -337,6 +282,62 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int n0 = tn * BN;
       uint32_t r[32];
 
+      if (p.mode == EPI_ALLREDUCE) {
+        // 1. this warp's 32 x 256 partial, as bf16, into the workspace of every OTHER rank (slot of
+        //    this rank); the fp32 accumulator stays in TMEM for step 2
+        const bool live = tm < p.m_tiles;   // a pair's second CTA may sit past the last row tile
+        const size_t slot = (size_t)p.ar_rank * p.ar_rows * p.N;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64 && live; ++c) {
+          uint8_t* st = my_stage + sbuf * EPI_BUF_BYTES;
+          if (lane == 0) tma_store_wait_read<1>();   // an earlier tile's TMA store may still read this buffer
+          __syncwarp();
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            tmem_ld32(taddr + c * 64 + h * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t a0 = pack_bf16x2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]));
+              const uint32_t a1 = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+              const uint32_t a2 = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+              const uint32_t a3 = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+              *reinterpret_cast<uint4*>(st + sw128_offset(lane, h * 4 + i)) = make_uint4(a0, a1, a2, a3);
+            }
+          }
+          __syncwarp();
+          // 32 rows x 128 bytes: lane l moves the 16-byte pieces l, l+32, ... (8 consecutive lanes = one row)
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int piece = k * 32 + lane;
+            const int rr = piece >> 3, ch = piece & 7;
+            const int grow = tm * BM + q * 32 + rr;
+            const int col = n0 + c * 64 + ch * 8;
+            if (grow < p.M && col < p.N) {
+              const uint4 v = *reinterpret_cast<const uint4*>(st + sw128_offset(rr, ch));
+              const size_t off = slot + (size_t)grow * p.N + col;
+              for (int d = 0; d < p.ar_world; ++d)
+                if (d != p.ar_rank) *reinterpret_cast<uint4*>((__nv_bfloat16*)p.ar_ws[d] + off) = v;
+            }
+          }
+          __syncwarp();
+          sbuf ^= 1;
+        }
+        // publish the slice to the peers, then wait (bounded) for theirs: ranks run the same tile
+        // order, so after the first tile this wait is short
+        __threadfence_system();
+        __syncwarp();
+        const int fidx = (tm * p.n_tiles + tn) * 4 + q;
+        const size_t per_rank_flags = (size_t)p.m_tiles * p.n_tiles * 4;
+        bool ok_ar = true;
+        if (live && lane < p.ar_world && lane != p.ar_rank) {
+          flag_store_release(p.ar_flags[lane] + (size_t)p.ar_rank * per_rank_flags + fidx, p.ar_epoch);
+          ok_ar = flag_wait_geq(p.ar_flags[p.ar_rank] + (size_t)lane * per_rank_flags + fidx, p.ar_epoch,
+                                GEMM_KERNEL_ID, 40 + lane);
+        }
+        if (!__all_sync(0xffffffffu, ok_ar)) break;
+        // 2. falls into the bf16 store path below, which adds the peers' partials (and C) to the accumulator
+      }
       if (p.mode == EPI_CE_STATS) {
         float mx = -INFINITY, sum = 0.f, tgt = 0.f;
         const int label = (gm < p.M) ? p.labels[gm] : -1;
@@ -369,60 +370,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           o[1] = sum;
           o[2] = (label >= n0 && label < n0 + BN) ? tgt : 0.f;
         }
-      } else if (p.mode == EPI_ALLREDUCE) {
-        // 1. this warp's 32 x 256 partial, as bf16, into every rank's workspace (slot of this rank)
-        const bool live = tm < p.m_tiles;   // a pair's second CTA may sit past the last row tile
-        const size_t slot = (size_t)p.ar_rank * p.ar_rows * p.N;
-#pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          uint8_t* st = my_stage + sbuf * EPI_BUF_BYTES;
-          __syncwarp();
-#pragma unroll 1
-          for (int h = 0; h < 2; ++h) {
-            tmem_ld32(taddr + c * 64 + h * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const uint32_t a0 = pack_bf16x2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]));
-              const uint32_t a1 = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-              const uint32_t a2 = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-              const uint32_t a3 = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-              *reinterpret_cast<uint4*>(st + sw128_offset(lane, h * 4 + i)) = make_uint4(a0, a1, a2, a3);
-            }
-          }
-          __syncwarp();
-          // 32 rows x 128 bytes: lane l moves the 16-byte pieces l, l+32, ... (8 consecutive lanes = one row)
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int piece = k * 32 + lane;
-            const int rr = piece >> 3, ch = piece & 7;
-            const int grow = tm * BM + q * 32 + rr;
-            const int col = n0 + c * 64 + ch * 8;
-            if (grow < p.M && col < p.N) {
-              const uint4 v = *reinterpret_cast<const uint4*>(st + sw128_offset(rr, ch));
-              const size_t off = slot + (size_t)grow * p.N + col;
-              for (int d = 0; d < p.ar_world; ++d)
-                *reinterpret_cast<uint4*>((__nv_bfloat16*)p.ar_ws[d] + off) = v;
-            }
-          }
-          sbuf ^= 1;
-        }
-        // accumulator buffer is free again (the partial is out of TMEM); publish the slice everywhere
-        tc_fence_before();
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) {
-          if (PAIR == 2) mbar_arrive_cluster((bar_tempty + 8 * buf) & PEER_BIT_MASK);
-          else mbar_arrive(bar_tempty + 8 * buf);
-          const int fidx = (tm * p.n_tiles + tn) * 4 + q;
-          for (int d = 0; d < p.ar_world && live; ++d)
-            flag_store_release(p.ar_flags[d] + (size_t)p.ar_rank * p.m_tiles * p.n_tiles * 4 + fidx, p.ar_epoch);
-        }
-        // 2. one tile behind: sum what has arrived here for the previous tile of this CTA
-        if (ar_prev_tm >= 0 && !ar_reduce(p, ar_prev_tm, ar_prev_tn, q, lane)) break;
-        ar_prev_tm = live ? tm : -1;
-        ar_prev_tn = tn;
-        continue;
       } else if (p.mode == EPI_SWIGLU) {
 #pragma unroll 1
         for (int c = 0; c < BN / 128; ++c) {
@@ -520,6 +467,44 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (col == label) g -= 1.f;
                 r[j] = __float_as_uint(g * row_scale * dcap);
               }
+            } else if (p.mode == EPI_ALLREDUCE && gm < p.M) {
+              // partial sums of the other ranks, landed in this rank's workspace (read past L1: a peer
+              // wrote them), plus the optional C operand
+              const __nv_bfloat16* ws = (const __nv_bfloat16*)p.ar_ws[p.ar_rank];
+              // sources two at a time, all eight 16-byte loads in flight before the first add
+              for (int s0 = 0; s0 <= p.ar_world; s0 += 2) {
+                uint4 v[2][4];
+                bool use[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                  const int s = s0 + u;
+                  use[u] = s <= p.ar_world && s != p.ar_rank && !(s == p.ar_world && !p.accumulate);
+                  const __nv_bfloat16* dp = (s >= p.ar_world)
+                                                ? (const __nv_bfloat16*)p.c_ptr + (size_t)gm * p.ldc + cbase
+                                                : ws + ((size_t)s * p.ar_rows + gm) * p.N + cbase;
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    v[u][j] = make_uint4(0, 0, 0, 0);
+                    if (use[u] && cbase + j * 8 < p.N)
+                      asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                   : "=r"(v[u][j].x), "=r"(v[u][j].y), "=r"(v[u][j].z), "=r"(v[u][j].w)
+                                   : "l"(dp + j * 8));
+                  }
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v[u][j]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      const float2 f = __bfloat1622float2(h2[e]);   // zeros where nothing was loaded
+                      r[j * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[j * 8 + 2 * e]) + f.x);
+                      r[j * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[j * 8 + 2 * e + 1]) + f.y);
+                    }
+                  }
+                }
+              }
             } else if (p.accumulate && gm < p.M) {
               const __nv_bfloat16* dp = (const __nv_bfloat16*)p.c_ptr + (size_t)gm * p.ldc + cbase;
 #pragma unroll
@@ -562,7 +547,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         else mbar_arrive(bar_tempty + 8 * buf);
       }
     }
-    if (p.mode == EPI_ALLREDUCE && ar_prev_tm >= 0) ar_reduce(p, ar_prev_tm, ar_prev_tn, q, lane);
     if (lane == 0) tma_store_wait_all();
   }
 

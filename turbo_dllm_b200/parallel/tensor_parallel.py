@@ -135,6 +135,7 @@ class TPContext:
         import os
 
         self.fused_allreduce_enabled = os.environ.get("TDLLM_TP_FUSED_ALLREDUCE", "1") != "0"
+        self.fused_allreduce_min_k = int(os.environ.get("TDLLM_TP_FUSED_ALLREDUCE_MIN_K", "4096"))
 
     def fused_allreduce(self, rows: int, cols: int, device):
         """Workspace of the GEMM whose epilogue all-reduces over peer memory, or None when the group
