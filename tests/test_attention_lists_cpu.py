@@ -1,0 +1,67 @@
+"""Host-side structures of the attention kernels and of activation checkpointing, checked on CPU."""
+import pytest
+import torch
+
+
+@pytest.mark.parametrize("chunk", [0, 1, 4, 5, 32, 1000])
+@pytest.mark.parametrize("views", [1, 2])
+def test_backward_work_items_cover_every_visible_tile_pair_once(chunk, views):
+    from turbo_dllm_b200.ops.attention import single_sequence_layout
+
+    lay = single_sequence_layout(1536, 32, "cpu", views)
+    L = lay.tile_lists()
+    W = lay.backward_work(chunk)
+    nkt, nqt = L["nkt"], L["nqt"]
+    visible, full = lay._cache["visible"]
+    seen = torch.zeros(nqt, nkt, dtype=torch.int32)
+    order = W["w_order"][: W["n_work"]].tolist()
+    assert len(set(order)) == len(order)
+    for w in order:
+        kt, c = w % nkt, w // nkt
+        ents = W["w_idx"][W["w_ptr"][w]:W["w_ptr"][w + 1]].tolist()
+        assert ents, "empty work items must not be scheduled"
+        for e in ents:
+            qt = e >> 1
+            assert qt // W["chunk_tiles"] == c
+            assert bool(e & 1) == (not bool(full[qt, kt])), "mask flag must mark the tiles that are not fully visible"
+            seen[qt, kt] += 1
+    assert (seen == visible.int()).all()
+    chunks = [w // nkt for w in order]
+    assert chunks == sorted(chunks), "the grid must run chunk by chunk"
+    # heaviest first inside a chunk
+    sizes = [int(W["w_ptr"][w + 1] - W["w_ptr"][w]) for w in order]
+    for c in set(chunks):
+        s = [sz for sz, cc in zip(sizes, chunks) if cc == c]
+        assert s == sorted(s, reverse=True)
+
+
+def _grads(checkpoint: bool):
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-qwen3", "seq_len": 128, "dtype": "fp32"},
+        "objective": {"name": "fast_dllm_v2", "block_size": 16},
+        "training": {"batch_size": 2, "steps": 1, "activation_checkpointing": checkpoint, "skip_optimizer_step": True},
+        "optimizer": {"lr": 1e-3}}).validate()
+    s = TrainingSession(spec, device="cpu")
+    r = s.step()
+    return float(r.loss_sum) / r.denominator, s.model.flat.grad.clone()
+
+
+def test_replay_without_the_layer_output_gives_the_same_gradients():
+    """The checkpoint replay skips the layer's last product (its value is never read); gradients must
+    equal those of the run that keeps every activation."""
+    la, ga = _grads(False)
+    lb, gb = _grads(True)
+    assert la == pytest.approx(lb, rel=1e-6)
+    assert torch.allclose(ga, gb, rtol=1e-5, atol=1e-7)
+
+
+def test_skip_flag_only_applies_inside_the_replay():
+    from turbo_dllm_b200.ops import gemm as G
+
+    assert G._Replay.skip_last_output is False
+    with G.skip_last_output():
+        assert G._Replay.skip_last_output is True
+    assert G._Replay.skip_last_output is False
