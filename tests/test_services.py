@@ -163,3 +163,17 @@ def test_launch_command_and_environment(tmp_path):
 
     with pytest.raises(RunSpecError, match="not idle"):
         require_idle_assigned_gpus(1, command_runner=lambda cmd: R())
+
+
+def test_execution_facade_and_launch_wrappers():
+    import os
+
+    from turbo_dllm_b200.training.execution import Execution, execution_for
+
+    assert execution_for(None, 4, 2).data_parallel_rank == 2
+    assert execution_for(None, 4, 2).active_block_mode == "all_blocks"
+    assert Execution(block_parallel_size=4).active_block_mode == "dual_end"
+    here = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "turbo_dllm_b200", "cli")
+    for name in ("torchrun.sh", "slurm.sh"):
+        text = open(os.path.join(here, name)).read()
+        assert "turbo_dllm_b200.cli.main launch" in text and os.access(os.path.join(here, name), os.X_OK)
