@@ -83,8 +83,16 @@ def gate_bounded_device_waits() -> GateResult:
 
 
 def gate_no_cluster_broadcast_loads() -> GateResult:
+    """No bulk / tensor LOAD (`cp.async.bulk…`) may carry the cluster-broadcast qualifier. The qualifier on
+    `tcgen05.commit` (an mbarrier arrival in both CTAs of a pair, no memory is loaded) is allowed."""
     needle = "multi" + "cast"
-    bad = [p.name for p in _cu_files() if needle in p.read_text()]
+    bad = []
+    for p in _cu_files():
+        for n, line in enumerate(p.read_text().splitlines(), 1):
+            if needle in line and "cp.async.bulk" in line:
+                bad.append(f"{p.name}:{n}")
+            elif needle in line and "tcgen05.commit" not in line:
+                bad.append(f"{p.name}:{n} (outside a tcgen05.commit)")
     return GateResult("no_cluster_broadcast_loads", not bad, f"offenders: {bad}")
 
 
