@@ -65,3 +65,27 @@ def test_skip_flag_only_applies_inside_the_replay():
     with G.skip_last_output():
         assert G._Replay.skip_last_output is True
     assert G._Replay.skip_last_output is False
+
+
+def test_grouped_row_layout_tables():
+    from turbo_dllm_b200.ops.grouped import PAD, build_grouped_rows
+
+    counts = torch.tensor([300, 0, 17, 512, 1])
+    rows = int(counts.sum())
+    g = build_grouped_rows(counts, rows)
+    assert g.capacity % PAD == 0 and g.capacity >= rows
+    begin = g.row_begin.tolist()
+    assert all(b % PAD == 0 for b in begin) and begin == sorted(begin)
+    # every sorted row lands inside its expert's padded segment, in order, without collisions
+    dest = g.dest.tolist()
+    assert len(set(dest)) == rows
+    off = 0
+    for e, n in enumerate(counts.tolist()):
+        assert dest[off:off + n] == list(range(begin[e], begin[e] + n))
+        off += n
+    # tile -> expert table agrees with the segments (tiles of empty experts do not exist)
+    for t, e in enumerate(g.mt_group.tolist()):
+        row = t * 128
+        owners = [k for k in range(len(begin)) if begin[k] <= row < begin[k] + (int(counts[k]) + PAD - 1) // PAD * PAD]
+        assert not owners or owners[0] == e
+    assert g.row_blocks_end.tolist() == [(b + (int(n) + 63) // 64 * 64) // 64 for b, n in zip(begin, counts.tolist())]

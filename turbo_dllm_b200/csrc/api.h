@@ -38,6 +38,14 @@ int tdllm_gemm_allreduce_bf16(const void* A, const void* B, void* D, int M, int 
                               void* stream);
 int tdllm_gemm_flag_count(int M, int N);
 
+// Grouped product (experts): per 128-row tile of M a slice of B (row coordinate shifted by mt_group[tm] *
+// b_group_rows) and/or a range of 64-element K blocks; tables on the device, null = not used.
+int tdllm_gemm_grouped_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
+                            long long ldb, long long ldd, int a_mn_major, int b_mn_major, int accumulate,
+                            int mode, const int* mt_group, long long b_group_rows, long long b_rows_total,
+                            long long a_group_rows, long long a_m_total, const int* mt_kbegin,
+                            const int* mt_kend, int max_ctas, void* stream);
+
 // ---- normalisation / rotary / activation ---------------------------------
 int tdllm_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out,
                       float* rstd, int rows, int H, float eps, void* stream);

@@ -87,6 +87,14 @@ struct GemmParams {
   int* ar_flags[AR_MAX_RANKS];
   void* ar_out;       // destination (this rank's memory), row stride ar_ldd elements
   long long ar_ldd;
+  // grouped products (experts): per 128-row tile of M, the group whose slice of B is used (B's row
+  // coordinate is shifted by group * b_group_rows) and/or the range of K blocks to run over (ragged K:
+  // each group of output rows sums over its own rows of the operands). Null = plain GEMM.
+  const int* mt_group;
+  long long b_group_rows;
+  long long a_group_rows;   // A's M coordinate is shifted back by group * a_group_rows (per-group outputs)
+  const int* mt_kbegin;
+  const int* mt_kend;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& m, int& n) {
@@ -173,7 +181,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tile_coords(t, m_groups, p.n_tiles, tm, tn);
         tm = tm * PAIR + rank;
         const int b_row0 = tn * BN + rank * B_ROWS;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int tml = min(tm, p.m_tiles - 1);   // a pair's second CTA may sit past the last row tile
+        const int b_shift = p.mt_group ? (int)(p.mt_group[tml] * p.b_group_rows) : 0;
+        const int a_m0 = tm * BM - (p.mt_group ? (int)(p.mt_group[tml] * p.a_group_rows) : 0);
+        const int kb0 = p.mt_kbegin ? p.mt_kbegin[tml] : 0;
+        const int kb1 = p.mt_kend ? p.mt_kend[tml] : k_blocks;
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, GEMM_KERNEL_ID, 10)) {
             ok = false;
             break;
@@ -188,16 +201,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             else tma_load_2d(dst, m, full, x, y);
           };
           if (!p.a_mn_major) {
-            load(sa, &tmap_a, kb * BK, tm * BM);
+            load(sa, &tmap_a, kb * BK, a_m0);
           } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) load(sa + c * (BK * 128), &tmap_a, tm * BM + c * 64, kb * BK);
+            for (int c = 0; c < BM / 64; ++c) load(sa + c * (BK * 128), &tmap_a, a_m0 + c * 64, kb * BK);
           }
           if (!p.b_mn_major) {
-            load(sb, &tmap_b, kb * BK, b_row0);
+            load(sb, &tmap_b, kb * BK, b_row0 + b_shift);
           } else {
 #pragma unroll
-            for (int c = 0; c < B_ROWS / 64; ++c) load(sb + c * (BK * 128), &tmap_b, b_row0 + c * 64, kb * BK);
+            for (int c = 0; c < B_ROWS / 64; ++c)
+              load(sb + c * (BK * 128), &tmap_b, b_row0 + c * 64, kb * BK + b_shift);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -223,7 +237,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!__all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * buf, tphase ^ 1, GEMM_KERNEL_ID, 20))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        int kb0 = 0, kb1 = k_blocks;
+        if (p.mt_kbegin) {
+          int tm_, tn_;
+          tile_coords(t, m_groups, p.n_tiles, tm_, tn_);
+          const int tml = min(tm_ * PAIR, p.m_tiles - 1);
+          kb0 = p.mt_kbegin[tml];
+          kb1 = p.mt_kend[tml];
+        }
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * stage, phase, GEMM_KERNEL_ID, 21))) {
             ok = false;
             break;
@@ -242,8 +264,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                     ? make_smem_desc_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024)
                                     : make_smem_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
             if (leader) {
-              if (PAIR == 2) tc_mma_ss_pair(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
-              else tc_mma_ss(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+              if (PAIR == 2) tc_mma_ss_pair(d_tmem, ad, bd, idesc, ((kb - kb0) | k) ? 1u : 0u);
+              else tc_mma_ss(d_tmem, ad, bd, idesc, ((kb - kb0) | k) ? 1u : 0u);
             }
           }
           if (leader) {
@@ -281,6 +303,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int gm = tm * BM + row;
       const int n0 = tn * BN;
       uint32_t r[32];
+      // a group without rows runs no MMA: its accumulator is undefined and counts as zero
+      const bool empty_k = p.mt_kbegin && p.mt_kbegin[min(tm, p.m_tiles - 1)] >= p.mt_kend[min(tm, p.m_tiles - 1)];
 
       if (p.mode == EPI_ALLREDUCE) {
         // 1. this warp's 32 x 256 partial, as bf16, into the workspace of every OTHER rank (slot of
@@ -380,6 +404,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int h = 0; h < 4; ++h) {
             tmem_ld32(taddr + c * 128 + h * 32, r);
             tmem_ld_wait();
+            if (empty_k) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
             uint32_t o[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -406,6 +434,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint8_t* st = my_stage + sbuf * EPI_BUF_BYTES;
           tmem_ld32(taddr + c * 32, r);
           tmem_ld_wait();
+            if (empty_k) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
           if (p.accumulate && gm < p.M) {
             const float* dp = (const float*)p.c_ptr + (size_t)gm * p.ldc + n0 + c * 32;
 #pragma unroll
@@ -452,6 +484,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int cbase = n0 + c * 64 + h * 32;
             tmem_ld32(taddr + c * 64 + h * 32, r);
             tmem_ld_wait();
+            if (empty_k) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
             if (p.mode == EPI_CE_GRAD) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
@@ -576,6 +612,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // ---------------------------------------------------------------------------
 using namespace tdllm;
 
+static thread_local long long g_b_rows_override = 0;   // rows of the whole (all groups) B operand
+static thread_local long long g_a_m_override = 0;      // extent of A along M when outputs are stacked per group
+
+struct GroupConfig {
+  const int* mt_group;
+  long long b_group_rows;
+  long long a_group_rows;
+  long long a_m_total;   // extent of A along M (0 = M)
+  const int* mt_kbegin;
+  const int* mt_kend;
+};
+
 struct ArConfig {
   int world, rank, epoch;
   long long rows;
@@ -587,7 +635,8 @@ static int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K,
                      long long ldb, long long ldd, int a_mn_major, int b_mn_major, int out_fp32,
                      int accumulate, int mode, const int* labels, const float* lse,
                      const float* rowscale, float* stats, int exclude_index, float softcap,
-                     int max_ctas, const void* c_src, long long ldc, const ArConfig* ar, void* stream) {
+                     int max_ctas, const void* c_src, long long ldc, const ArConfig* ar, const GroupConfig* grp,
+                     void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (mode == EPI_ALLREDUCE) {
     if (!ar || ar->world < 2 || ar->world > AR_MAX_RANKS || ar->rank < 0 || ar->rank >= ar->world ||
@@ -641,18 +690,21 @@ static int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K,
   {
     uint64_t dims[2], strides[1];
     uint32_t box[2];
+    const uint64_t a_m = (uint64_t)(g_a_m_override ? g_a_m_override : M);
     if (!a_mn_major) {
-      dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = BK; box[1] = BM;
+      dims[0] = (uint64_t)K; dims[1] = a_m; box[0] = BK; box[1] = BM;
     } else {
-      dims[0] = (uint64_t)M; dims[1] = (uint64_t)K; box[0] = 64; box[1] = BK;
+      dims[0] = a_m; dims[1] = (uint64_t)K; box[0] = 64; box[1] = BK;
     }
     strides[0] = (uint64_t)lda * 2;
     if (tdllm_host::encode_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, dims, strides, box,
                                 CU_TENSOR_MAP_SWIZZLE_128B)) return 3;
     if (!b_mn_major) {
-      dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = BK; box[1] = pair ? BN / 2 : BN;
+      dims[0] = (uint64_t)K; dims[1] = (uint64_t)(g_b_rows_override ? g_b_rows_override : N);
+      box[0] = BK; box[1] = pair ? BN / 2 : BN;
     } else {
-      dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 64; box[1] = BK;
+      dims[0] = (uint64_t)N; dims[1] = (uint64_t)(g_b_rows_override ? g_b_rows_override : K);
+      box[0] = 64; box[1] = BK;
     }
     strides[0] = (uint64_t)ldb * 2;
     if (tdllm_host::encode_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, dims, strides, box,
@@ -687,6 +739,9 @@ static int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K,
   }
   p.labels = labels; p.lse = lse; p.rowscale = rowscale; p.stats = stats;
   p.exclude_index = exclude_index; p.softcap = softcap;
+  p.mt_group = grp ? grp->mt_group : nullptr; p.b_group_rows = grp ? grp->b_group_rows : 0;
+  p.a_group_rows = grp ? grp->a_group_rows : 0;
+  p.mt_kbegin = grp ? grp->mt_kbegin : nullptr; p.mt_kend = grp ? grp->mt_kend : nullptr;
   p.ar_world = 0; p.ar_rank = 0; p.ar_epoch = 0; p.ar_rows = 0; p.ar_out = D; p.ar_ldd = ldd;
   for (int i = 0; i < AR_MAX_RANKS; ++i) { p.ar_ws[i] = nullptr; p.ar_flags[i] = nullptr; }
   if (mode == EPI_ALLREDUCE) {
@@ -732,7 +787,7 @@ extern "C" int tdllm_gemm_bf16(const void* A, const void* B, void* D, int M, int
     return 1;
   }
   return gemm_impl(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, out_fp32, accumulate, mode,
-                   labels, lse, rowscale, stats, exclude_index, softcap, max_ctas, c_src, ldc, nullptr, stream);
+                   labels, lse, rowscale, stats, exclude_index, softcap, max_ctas, c_src, ldc, nullptr, nullptr, stream);
 }
 
 // D = sum over the `world` ranks of (A_r * B_r) (+ C): every rank calls this with its K-slice of A and B.
@@ -747,7 +802,33 @@ extern "C" int tdllm_gemm_allreduce_bf16(const void* A, const void* B, void* D, 
                                          void* const* flags, int max_ctas, void* stream) {
   ArConfig ar{world, rank, epoch, ws_rows, ws, flags};
   return gemm_impl(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, 0, c_src != nullptr, EPI_ALLREDUCE,
-                   nullptr, nullptr, nullptr, nullptr, -1, 0.f, max_ctas, c_src, ldc, &ar, stream);
+                   nullptr, nullptr, nullptr, nullptr, -1, 0.f, max_ctas, c_src, ldc, &ar, nullptr, stream);
+}
+
+// Grouped product over row tiles (experts): tile tm of M uses the slice `mt_group[tm]` of B (B's row coordinate
+// shifted by mt_group[tm] * b_group_rows, A's M coordinate shifted back by mt_group[tm] * a_group_rows with
+// A spanning a_m_total along M; pass null / 0 for none) and runs over K blocks [mt_kbegin[tm], mt_kend[tm])
+// (64-element blocks; null = all of K). The tables live on the device, one entry per 128-row tile of M; both
+// tiles of a 256-row pair must agree. `b_rows_total`: rows of the whole B operand (all groups).
+// mode: EPI_STORE or EPI_SWIGLU.
+extern "C" int tdllm_gemm_grouped_bf16(const void* A, const void* B, void* D, int M, int N, int K,
+                                       long long lda, long long ldb, long long ldd, int a_mn_major,
+                                       int b_mn_major, int accumulate, int mode, const int* mt_group,
+                                       long long b_group_rows, long long b_rows_total, long long a_group_rows,
+                                       long long a_m_total, const int* mt_kbegin, const int* mt_kend,
+                                       int max_ctas, void* stream) {
+  if (mode != EPI_STORE && mode != EPI_SWIGLU) {
+    tdllm_host::set_last_error("gemm_grouped: only the store and SwiGLU epilogues are grouped");
+    return 1;
+  }
+  GroupConfig g{mt_group, b_group_rows, a_group_rows, a_m_total, mt_kbegin, mt_kend};
+  g_b_rows_override = b_rows_total;
+  g_a_m_override = a_m_total;
+  const int rc = gemm_impl(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, 0, accumulate, mode, nullptr,
+                           nullptr, nullptr, nullptr, -1, 0.f, max_ctas, nullptr, 0, nullptr, &g, stream);
+  g_b_rows_override = 0;
+  g_a_m_override = 0;
+  return rc;
 }
 
 extern "C" int tdllm_gemm_flag_count(int M, int N) { return ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * 4; }

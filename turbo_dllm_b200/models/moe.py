@@ -83,11 +83,20 @@ class ExpertBank(nn.Module):
         self.e_local = self.w_gu.shape[0]
         self.last_counts = None
 
-    def _local_experts(self, x_sorted: torch.Tensor, counts: list[int]) -> torch.Tensor:
-        """x_sorted: rows grouped by local expert (counts per expert). Per-expert slabs run through the
-        shared GEMM; weight gradients land in the experts' slices of the flat gradient buffer."""
+    def _local_experts(self, x_sorted: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+        """x_sorted: rows grouped by local expert (`counts` per expert, on the device). On the GPU all
+        experts run as one grouped GEMM per projection over a padded row layout; otherwise (CPU, or
+        expert shapes off the tile grid) per-expert slabs run through the shared GEMM. Weight
+        gradients land in the experts' slices of the flat gradient buffer either way."""
+        from ..ops.grouped import build_grouped_rows, grouped_linear, grouped_supported
+
+        if x_sorted.shape[0] > 0 and grouped_supported(x_sorted, self.w_gu) and grouped_supported(x_sorted, self.w_down):
+            g = build_grouped_rows(counts, x_sorted.shape[0])
+            x_pad = x_sorted.new_zeros(g.capacity, x_sorted.shape[1]).index_copy(0, g.dest, x_sorted)
+            act = swiglu(grouped_linear(x_pad, self.w_gu, g))
+            return grouped_linear(act, self.w_down, g).index_select(0, g.dest)
         outs, off = [], 0
-        for e, n in enumerate(counts):
+        for e, n in enumerate(counts.tolist()):
             if n == 0:
                 continue
             xe = x_sorted[off:off + n]
@@ -120,11 +129,11 @@ class ExpertBank(nn.Module):
             eid = torch.repeat_interleave(torch.arange(self.e_local, device=x.device).repeat(self.ep),
                                           torch.tensor(src_counts, device=x.device))
             eorder = torch.argsort(eid, stable=True)
-            y_sorted = self._local_experts(recv.index_select(0, eorder), mine.sum(0).tolist())
+            y_sorted = self._local_experts(recv.index_select(0, eorder), mine.sum(0))
             y_recv = torch.empty_like(y_sorted).index_copy_(0, eorder, y_sorted) if y_sorted.numel() else y_sorted
             y_perm = _AllToAllRows.apply(y_recv, recv_l, send_l, self.ep_group)
         else:
-            y_perm = self._local_experts(x_perm, counts_g.tolist())
+            y_perm = self._local_experts(x_perm, counts_g)
         self.last_counts = counts_g
         wk = w.reshape(-1).index_select(0, order).to(y_perm.dtype)
         out = torch.zeros_like(x)
