@@ -122,12 +122,13 @@ class ExpertBank(nn.Module):
             all_counts = torch.empty(self.ep, cfg.num_experts, dtype=counts_g.dtype, device=x.device)
             dist.all_gather_into_tensor(all_counts.view(-1), counts_g, group=self.ep_group)
             mine = all_counts[:, self.ep_rank * self.e_local:(self.ep_rank + 1) * self.e_local]   # [src, e_local]
-            send_l, recv_l = send.tolist(), mine.sum(1).tolist()
+            # one host read for both all-to-all size lists (NCCL wants them on the host)
+            sizes = torch.cat([send, mine.sum(1)]).tolist()
+            send_l, recv_l = sizes[: self.ep], sizes[self.ep:]
             recv = _AllToAllRows.apply(x_perm, send_l, recv_l, self.ep_group)
             # received rows are ordered (source rank, local expert): regroup by local expert
-            src_counts = mine.reshape(-1).tolist()
             eid = torch.repeat_interleave(torch.arange(self.e_local, device=x.device).repeat(self.ep),
-                                          torch.tensor(src_counts, device=x.device))
+                                          mine.reshape(-1), output_size=recv.shape[0])
             eorder = torch.argsort(eid, stable=True)
             y_sorted = self._local_experts(recv.index_select(0, eorder), mine.sum(0))
             y_recv = torch.empty_like(y_sorted).index_copy_(0, eorder, y_sorted) if y_sorted.numel() else y_sorted
