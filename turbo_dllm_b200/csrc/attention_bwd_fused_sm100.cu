@@ -188,7 +188,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const int it = u >> 1, b = u & 1;
         const int h = kvh * G + it / n;
         const int qrow = (list[it % n] >> 1) * 128 + b * 64;
-        if (!mbar_wait(bar_qempty + 8 * st, ph ^ 1, KID, 10)) break;
+        if (!mbar_wait_spin(bar_qempty + 8 * st, ph ^ 1, KID, 10)) break;
         mbar_expect_tx(bar_qfull + 8 * st, 2 * QS_BYTES + 512);
         bulk_load_1d(smem_u32(sStat + st * 128), p.lse2 + (size_t)h * p.nq_pad + qrow, 256,
                      bar_qfull + 8 * st);
@@ -218,7 +218,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const uint32_t idesc_dq = make_idesc_bf16(HD, 64, 1, 1);     // [128 d] x [64 q], K = keys
       const uint32_t ka = smem_u32(sK), va = smem_u32(sV), sa = smem_u32(sdS);
       auto wait_all = [&](uint32_t bar, uint32_t parity, int detail) {
-        return __all_sync(0xffffffffu, mbar_wait(bar, parity, KID, detail));
+        return __all_sync(0xffffffffu, mbar_wait_spin(bar, parity, KID, detail));
       };
       // unit u lives in stage u % 3 and TMEM slot u & 1
       auto issue_s = [&](int b, int st) {
@@ -325,7 +325,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const int qrow0 = (ent >> 1) * 128 + b * 64 + sub * 32;
       const float* sl = sStat + st * 128 + sub * 32;   // lse2 of this group's 32 queries
       const float* sd = sl + 64;                       // delta_s
-      bool good = __all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * b, it & 1, KID, 30));
+      bool good = __all_sync(0xffffffffu, mbar_wait_spin(bar_sfull + 8 * b, it & 1, KID, 30));
       if (good) {
         tc_fence_after();
         // two chunks of 16 queries: keeps the live registers under the 96 this block size allows
@@ -392,7 +392,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         tc_fence_before();
         mbar_arrive(bar_pfull + 8 * b);
         // dQᵀ of this unit: lanes = d, columns = the unit's 64 queries
-        good = __all_sync(0xffffffffu, mbar_wait(bar_dqfull + 8 * b, it & 1, KID, 33));
+        good = __all_sync(0xffffffffu, mbar_wait_spin(bar_dqfull + 8 * b, it & 1, KID, 33));
       }
       // the group's staging rows are free once its previous copy has read them; the vote keeps the
       // four warps together (a warp whose wait ran out takes the others out with it)
@@ -428,7 +428,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     // staged as four [128 keys][32 columns] swizzled blocks (64 KiB per tensor, over the Q / dO / dSᵀ
     // buffers, which nothing reads any more once the last product has completed)
     bool ok = !error_is_set();
-    if (ok && items > 0) ok = mbar_wait(bar_done, 0, KID, 31);
+    if (ok && items > 0) ok = mbar_wait_spin(bar_done, 0, KID, 31);
     if (ok && items > 0) {
       tc_fence_after();
       const uint32_t t_acc = tmem_base + ((uint32_t)(qd * 32) << 16) + 256 + b * 128;
@@ -447,7 +447,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       fence_proxy_async_smem();
       mbar_arrive(bar_epi + 8 * b);
       if (row == 0 && sub == 0) {
-        if (mbar_wait(bar_epi + 8 * b, 0, KID, 32)) {
+        if (mbar_wait_spin(bar_epi + 8 * b, 0, KID, 32)) {
           const CUtensorMap* tm = b ? &tm_dkacc : &tm_dvacc;
 #pragma unroll
           for (int c = 0; c < 4; ++c)

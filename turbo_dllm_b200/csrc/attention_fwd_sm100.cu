@@ -152,13 +152,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int kt = list[j] >> 1;
-        if (!mbar_wait(bar_kempty + 8 * s, ph ^ 1, KID, 10)) break;
+        if (!mbar_wait_spin(bar_kempty + 8 * s, ph ^ 1, KID, 10)) break;
         mbar_expect_tx(bar_kfull + 8 * s, TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < 2; ++c)
           tma_load_2d(smem_u32(sK + s * TILE_BYTES + c * HALF_BYTES), &tm_k, bar_kfull + 8 * s,
                       kvh * HD + c * 64, kt * BKV);
-        if (!mbar_wait(bar_vempty + 8 * s, ph ^ 1, KID, 11)) break;
+        if (!mbar_wait_spin(bar_vempty + 8 * s, ph ^ 1, KID, 11)) break;
         mbar_expect_tx(bar_vfull + 8 * s, TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < 2; ++c)
@@ -175,7 +175,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t idesc_qk = make_idesc_bf16(BQ, BKV, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(BQ, HD, 0, 1);
       auto wait_all = [&](uint32_t bar, uint32_t parity, int detail) {
-        return __all_sync(0xffffffffu, mbar_wait(bar, parity, KID, detail));
+        return __all_sync(0xffffffffu, mbar_wait_spin(bar, parity, KID, detail));
       };
       auto issue_qk = [&](int i, int s) {
         const uint32_t qa = smem_u32(sQ + i * TILE_BYTES);
@@ -243,7 +243,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int j = 0; j < n; ++j) {
       const int ent = list[j];
       const int* kc = p.k_code + (ent >> 1) * BKV;
-      if (!mbar_wait(bar_sfull + 8 * i, j & 1, KID, 30)) { ok = false; break; }
+      if (!mbar_wait_spin(bar_sfull + 8 * i, j & 1, KID, 30)) { ok = false; break; }
       tc_fence_after();
       // the whole score row lives in registers: one TMEM round trip per tile
       tmem_ld32(t_s, r);
@@ -298,7 +298,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_arrive(bar_pfull + 8 * i);
     }
     // epilogue: O / l -> bf16 -> shared staging (the Q tile of this head) -> TMA store
-    if (ok && n > 0) ok = mbar_wait(bar_odone + 8 * i, 0, KID, 31);
+    if (ok && n > 0) ok = mbar_wait_spin(bar_odone + 8 * i, 0, KID, 31);
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -329,7 +329,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       fence_proxy_async_smem();
       mbar_arrive(bar_epi + 8 * i);
       if (row == 0) {
-        if (mbar_wait(bar_epi + 8 * i, 0, KID, 32)) {
+        if (mbar_wait_spin(bar_epi + 8 * i, 0, KID, 32)) {
 #pragma unroll
           for (int c = 0; c < 2; ++c)
             tma_store_2d(&tm_o, smem_u32(st + c * HALF_BYTES), (h0 + i) * HD + c * 64, qt * BQ);

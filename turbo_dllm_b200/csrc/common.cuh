@@ -83,6 +83,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// One try without a time hint: returns as soon as the hardware's default wait ends. Lower wake-up latency,
+// more issue slots burnt while waiting.
+__device__ __forceinline__ bool mbar_try_wait_spin(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait. Returns false when the budget ran out or another block already
 // recorded an error; the caller must then stop issuing work and fall through to
 // the kernel's common exit.
@@ -98,6 +112,27 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int ker
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
+    if (error_is_set()) return false;
+    if (globaltimer_ns() - t0 > budget) {
+      set_error(ERR_WAIT_TIMEOUT, kernel_id, detail);
+      return false;
+    }
+  }
+}
+
+// Same contract, polling without the time hint (for waits on the critical path of a short loop).
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, int kernel_id,
+                                          int detail) {
+#pragma unroll 1
+  for (int i = 0; i < 32; ++i)
+    if (mbar_try_wait_spin(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  const unsigned long long budget = g_tdllm_timeout_ns;
+#pragma unroll 1
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait_spin(bar, parity)) return true;
     if (error_is_set()) return false;
     if (globaltimer_ns() - t0 > budget) {
       set_error(ERR_WAIT_TIMEOUT, kernel_id, detail);
