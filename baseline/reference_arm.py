@@ -126,7 +126,7 @@ def run(args) -> dict:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if not os.path.isdir(os.path.join(REF, "dllm_parallel")):
-        return {**base, "unavailable": "baseline/_ref is empty: install with pip --no-index --no-deps --target baseline/_ref /root/reference"}
+        return {**base, "unavailable": "baseline/_ref is empty: install the reference package there with pip --no-index --no-deps --target baseline/_ref <reference source tree>"}
     shape = SHAPES.get(args.model)
     if shape is None:
         return {**base, "unavailable": f"no Hugging Face shape for {args.model}"}

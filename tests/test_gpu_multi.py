@@ -222,3 +222,41 @@ def test_gemm_with_allreduce_epilogue_over_peer_memory():
     _need(2)
     for errs in run_ranks(_fused_allreduce_gemm, 2, backend="nccl", deadline_s=300):
         assert max(errs) < 2e-2, errs
+
+
+def _ce_exchange(rank, world):
+    import os
+
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.parallel.fused_allreduce import CrossEntropyExchange
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    ex = CrossEntropyExchange(dist.group.WORLD, dev, max_rows=5000)
+    errs = []
+    for call, (rows, nt) in enumerate([(5000, 7), (33, 1), (4097, 40), (1, 3)]):
+        g = torch.Generator(device="cpu").manual_seed(7 * call + 3)
+        stats = torch.randn(world, rows, nt, 3, generator=g)
+        stats[..., 1] = stats[..., 1].abs() + 0.1          # sum exp > 0
+        stats[:, 0, :, 0] = float("-inf")                  # a row whose shard tiles are all masked on every rank...
+        stats[0, 0, 0, 0] = 0.5                            # ...but one tile of rank 0
+        lse, tgt = ex.finish(stats[rank].contiguous().to(dev))
+        torch.cuda.synchronize()
+        native.raise_on_device_error()
+        mx = stats[..., 0]
+        ref_lse = torch.logsumexp((mx + torch.log(stats[..., 1])).permute(1, 0, 2).reshape(rows, -1), dim=1)
+        ref_tgt = stats[..., 2].sum(dim=(0, 2))
+        errs.append(max((lse.cpu() - ref_lse).abs().max().item(), (tgt.cpu() - ref_tgt).abs().max().item()))
+    dist.barrier()
+    ex.close()
+    return errs
+
+
+@pytest.mark.distributed
+def test_cross_entropy_statistics_exchange_over_peer_memory():
+    _need(2)
+    for errs in run_ranks(_ce_exchange, 2, backend="nccl", deadline_s=300):
+        assert max(errs) < 1e-3, errs

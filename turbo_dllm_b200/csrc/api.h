@@ -38,6 +38,13 @@ int tdllm_gemm_allreduce_bf16(const void* A, const void* B, void* D, int M, int 
                               void* stream);
 int tdllm_gemm_flag_count(int M, int N);
 
+// Cross-rank finish of vocab-parallel CE statistics over peer memory: lse = logsumexp over ranks of the
+// shard lse, target = sum of the shard target logits. ws[d]: [world][rows_cap][2] fp32, flags[d]:
+// [world][tdllm_ce_exchange_blocks(rows_cap)] int32 (zeroed once); growing epoch, two alternating workspaces.
+int tdllm_ce_exchange(const float* stats, int M, int n_tiles, void* const* ws, void* const* flags, int rank,
+                      int world, int epoch, long long rows_cap, float* lse_out, float* tgt_out, void* stream);
+int tdllm_ce_exchange_blocks(long long rows_cap);
+
 // Grouped product (experts): per 128-row tile of M a slice of B (row coordinate shifted by mt_group[tm] *
 // b_group_rows) and/or a range of 64-element K blocks; tables on the device, null = not used.
 int tdllm_gemm_grouped_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda,

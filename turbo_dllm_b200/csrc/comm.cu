@@ -201,6 +201,77 @@ __global__ void kv_scatter_reduce_kernel(PeerPtrs partial, RowPlan plan, int ran
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// Vocab-parallel cross-entropy: cross-rank finish of the row statistics.
+// Every rank holds, per row, the statistics of its vocabulary shard as written by the GEMM's
+// statistics epilogue ([M, n_tiles, 3]: max, sum exp, target logit). One warp per row folds the
+// tiles into (lse_shard, target_shard), writes the pair into the workspace of every rank
+// ([ranks][rows_cap][2] fp32, slot of this rank), the block publishes an epoch flag per
+// (rank, block) and waits (bounded) for the peers' flags of the same block, then the warps
+// combine: lse = logsumexp over ranks, target = sum over ranks. No collective call.
+// ---------------------------------------------------------------------------
+constexpr int KID_CE_EXCHANGE = 13;
+
+__global__ void __launch_bounds__(256)
+ce_exchange_kernel(const float* __restrict__ stats, int M, int n_tiles, PeerPtrs ws, PeerPtrs flags,
+                   int rank, int world, int epoch, long long rows_cap, float* __restrict__ lse_out,
+                   float* __restrict__ tgt_out) {
+  // the grid is small enough to be resident at once (no block waits for one that cannot start);
+  // a warp walks rows blockIdx*8 + warp, + 8*gridDim, ... in both phases
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int stride = gridDim.x * 8;
+  for (int row = blockIdx.x * 8 + wib; row < M; row += stride) {
+    const float* s = stats + (size_t)row * n_tiles * 3;
+    float mx = -INFINITY;
+    for (int t = lane; t < n_tiles; t += 32) mx = fmaxf(mx, s[t * 3]);
+    mx = warp_max(mx);
+    float sum = 0.f, tgt = 0.f;
+    for (int t = lane; t < n_tiles; t += 32) {
+      const float tm = s[t * 3];
+      if (tm > -INFINITY) sum += s[t * 3 + 1] * __expf(tm - mx);
+      tgt += s[t * 3 + 2];
+    }
+    sum = warp_sum(sum);
+    tgt = warp_sum(tgt);
+    const float lse = (mx > -INFINITY) ? mx + logf(sum) : -INFINITY;
+    if (lane < world) {
+      float2* dst = (float2*)ws.p[lane] + (size_t)rank * rows_cap + row;
+      *dst = make_float2(lse, tgt);
+    }
+  }
+  __threadfence_system();
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const size_t per_rank = gridDim.x;
+    flag_store_release((int*)flags.p[threadIdx.x] + (size_t)rank * per_rank + blockIdx.x, epoch);
+    if (!flag_wait_geq((const int*)flags.p[rank] + (size_t)threadIdx.x * per_rank + blockIdx.x, epoch,
+                       KID_CE_EXCHANGE, (int)threadIdx.x))
+      ok_s = 0;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  // combine the shards (read past L1: peers wrote these lines)
+  for (int row = blockIdx.x * 8 + wib; row < M; row += stride) {
+    float my_l = -INFINITY, my_t = 0.f;
+    if (lane < world) {
+      const float* src = (const float*)ws.p[rank] + ((size_t)lane * rows_cap + row) * 2;
+      asm volatile("ld.global.cg.v2.f32 {%0,%1}, [%2];" : "=f"(my_l), "=f"(my_t) : "l"(src));
+    }
+    const float m = warp_max(my_l);
+    const float e = (my_l > -INFINITY) ? __expf(my_l - m) : 0.f;
+    const float se = warp_sum(e);
+    const float tg = warp_sum(my_t);
+    if (lane == 0) {
+      lse_out[row] = (m > -INFINITY) ? m + logf(se) : -INFINITY;
+      tgt_out[row] = tg;
+    }
+  }
+}
+
 }  // namespace comm
 }  // namespace tdllm
 
@@ -358,4 +429,39 @@ extern "C" int tdllm_kv_scatter_reduce(void* const* partial_ptrs, void* const* f
   comm::barrier_kernel<<<1, 32, 0, s>>>(f, rank, world, epoch + 1);
   TD_CUDA(cudaGetLastError(), "kv_scatter_reduce launch");
   return 0;
+}
+
+// Cross-rank finish of vocab-parallel cross-entropy statistics over peer memory (see ce_exchange_kernel).
+// ws[d]: rank d's workspace, [world][rows_cap][2] fp32; flags[d]: [world][tdllm_ce_exchange_blocks(rows_cap)] int32,
+// zeroed once.
+// `epoch` grows per call on one workspace; alternate two workspaces between consecutive calls.
+extern "C" int tdllm_ce_exchange(const float* stats, int M, int n_tiles, void* const* ws, void* const* flags,
+                                 int rank, int world, int epoch, long long rows_cap, float* lse_out,
+                                 float* tgt_out, void* stream) {
+  if (M <= 0) return 0;
+  if (world < 1 || world > 32 || world > comm::MAX_RANKS || M > rows_cap) {
+    tdllm_host::set_last_error("ce_exchange: 1..%d ranks and M <= rows_cap", comm::MAX_RANKS);
+    return 1;
+  }
+  comm::PeerPtrs w, f;
+  for (int i = 0; i < world; ++i) { w.p[i] = ws[i]; f.p[i] = flags[i]; }
+  // the flag stride is the grid size: fixed by the capacity (and the device), not by M, so that every rank
+  // and every call agrees on the layout; at most four blocks per SM, all resident at once
+  int blocks = (int)((rows_cap + 7) / 8);
+  const int cap = 4 * tdllm_num_sms();
+  if (blocks > cap) blocks = cap;
+  comm::ce_exchange_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(stats, M, n_tiles, w, f, rank, world, epoch,
+                                                                    rows_cap, lse_out, tgt_out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    tdllm_host::set_last_error("ce_exchange launch: %s", cudaGetErrorString(e));
+    return 4;
+  }
+  return 0;
+}
+
+extern "C" int tdllm_ce_exchange_blocks(long long rows_cap) {
+  long long blocks = (rows_cap + 7) / 8;
+  const long long cap = 4LL * tdllm_num_sms();
+  return (int)(blocks > cap ? cap : blocks);
 }

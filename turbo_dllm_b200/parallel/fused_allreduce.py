@@ -30,6 +30,10 @@ native.register_signatures({
                                   + [native.c_int] * 2 + [native.c_void_p, native.c_ll] + [native.c_int] * 3
                                   + [native.c_ll, native.c_void_p, native.c_void_p, native.c_int, native.c_void_p]),
     "tdllm_gemm_flag_count": (native.c_int, [native.c_int, native.c_int]),
+    "tdllm_ce_exchange": (native.c_int, [native.c_void_p, native.c_int, native.c_int, native.c_void_p,
+                                         native.c_void_p, native.c_int, native.c_int, native.c_int, native.c_ll,
+                                         native.c_void_p, native.c_void_p, native.c_void_p]),
+    "tdllm_ce_exchange_blocks": (native.c_int, [native.c_ll]),
 })
 
 MAX_RANKS = 8
@@ -96,3 +100,52 @@ def maybe_create(group, device, max_rows: int, n_cols: int) -> FusedAllReduceGem
 
 
 maybe_create.last_reason = ""
+
+
+class CrossEntropyExchange:
+    """Cross-rank finish of vocab-parallel cross-entropy over peer memory: every rank contributes the
+    (log-sum-exp, target logit) of its vocabulary shard per row and receives the global pair
+    (csrc/comm.cu::ce_exchange_kernel). Replaces an all-gather and an all-reduce of per-row scalars.
+    Two workspaces alternate and flags carry a growing epoch, as for the all-reduce GEMM.
+
+    Counterpart: the in-kernel max / sum / target exchange of the reference's vocab-parallel fused
+    linear-CE (dllm_parallel/core/csrc/fused_linear_ce/fused_linear_ce_cuda.cu:618-1268,
+    dllm_parallel/core/parallel/cross_entropy.py:198-276)."""
+
+    def __init__(self, group, device: torch.device, max_rows: int):
+        self.group, self.device = group, device
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if not 2 <= self.world <= 16:
+            raise RuntimeError(f"cross-entropy exchange supports 2..16 ranks, got {self.world}")
+        if not peer_access_available(group):
+            raise RuntimeError("GPUs of this group cannot address one another (no peer access)")
+        self.max_rows = int(max_rows)
+        blocks = native.lib().tdllm_ce_exchange_blocks(self.max_rows)
+        self.ws = [SymmetricBuffer(self.world * self.max_rows * 8, group, device) for _ in range(2)]
+        self.flags = [SymmetricBuffer(self.world * blocks * 4, group, device) for _ in range(2)]
+        for f in self.flags:
+            f.as_tensor(torch.int32).zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+        self.epoch = [0, 0]
+        self.flip = 0
+
+    def finish(self, stats: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """stats [rows, n_tiles, 3] fp32 of this rank's shard -> (lse [rows], target logit [rows]), global."""
+        rows, nt, _ = stats.shape
+        if rows > self.max_rows:
+            raise ValueError(f"{rows} rows exceed this workspace ({self.max_rows})")
+        lse = torch.empty(rows, dtype=torch.float32, device=stats.device)
+        tgt = torch.empty(rows, dtype=torch.float32, device=stats.device)
+        b = self.flip
+        self.flip ^= 1
+        self.epoch[b] += 1
+        rc = native.lib().tdllm_ce_exchange(ptr(stats), rows, nt, self.ws[b].ptr_array, self.flags[b].ptr_array,
+                                            self.rank, self.world, self.epoch[b], self.max_rows, ptr(lse), ptr(tgt),
+                                            stream())
+        native.check(rc, "ce_exchange")
+        return lse, tgt
+
+    def close(self) -> None:
+        for b in (*self.ws, *self.flags):
+            b.close()

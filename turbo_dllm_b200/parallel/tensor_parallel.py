@@ -155,6 +155,27 @@ class TPContext:
         self._fused_ar[cols] = ws if ws is not None else False
         return ws
 
+    def ce_exchange(self, rows: int, device):
+        """Peer-memory workspace for the cross-rank finish of vocab-parallel cross-entropy, or None."""
+        if not self.fused_allreduce_enabled or self.size < 2 or torch.device(device).type != "cuda":
+            return None
+        ws = self._fused_ar.get("ce")
+        if ws is False:
+            return None
+        if ws is not None and ws.max_rows >= rows:
+            return ws
+        from ..kernels import native
+        from .fused_allreduce import CrossEntropyExchange
+
+        if ws is not None:
+            ws.close()
+        try:
+            ws = CrossEntropyExchange(self.group, torch.device(device), max(rows, 1024))
+        except (RuntimeError, native.NativeKernelError):
+            ws = None
+        self._fused_ar["ce"] = ws if ws is not None else False
+        return ws
+
     def shard(self, full: torch.Tensor, dim: int) -> torch.Tensor:
         n = full.shape[dim] // self.size
         return full.narrow(dim, self.rank * n, n)
@@ -206,7 +227,7 @@ class _VocabParallelLinearCE(torch.autograd.Function):
     """Native path: h [rows,H] bf16 (replicated), w_shard [V/tp, H]."""
 
     @staticmethod
-    def forward(ctx, h, w, labels, weights, v0, exclude_index, group, chunk_rows):
+    def forward(ctx, h, w, labels, weights, v0, exclude_index, group, chunk_rows, tp=None):
         from ..kernels import native
         from ..ops._util import ptr, stream
 
@@ -222,15 +243,19 @@ class _VocabParallelLinearCE(torch.autograd.Function):
         native.check(lib.tdllm_gemm_bf16(ptr(h), ptr(w), None, rows, Vl, H, h.stride(0), w.stride(0), 0, 0, 0, 0, 0,
                                          EPI_CE_STATS, ptr(local_labels), None, None, ptr(stats), int(ex), 0.0, 0,
                                          None, 0, stream()), "vocab-parallel ce stats")
-        s = stats.view(rows, nt, 3)
-        mx = s[:, :, 0].amax(1)
-        lse_local = mx + torch.log((s[:, :, 1] * torch.exp(s[:, :, 0] - mx[:, None])).sum(1))
-        tgt = s[:, :, 2].sum(1)
-        world = dist.get_world_size(group)
-        all_lse = torch.empty(world, rows, dtype=torch.float32, device=dev)
-        dist.all_gather_into_tensor(all_lse.view(-1), lse_local.contiguous(), group=group)
-        lse = torch.logsumexp(all_lse, dim=0)
-        dist.all_reduce(tgt, group=group)
+        exchange = tp.ce_exchange(rows, dev) if tp is not None else None
+        if exchange is not None:   # shard statistics meet in peer memory: no collective call
+            lse, tgt = exchange.finish(stats)
+        else:
+            s = stats.view(rows, nt, 3)
+            mx = s[:, :, 0].amax(1)
+            lse_local = mx + torch.log((s[:, :, 1] * torch.exp(s[:, :, 0] - mx[:, None])).sum(1))
+            tgt = s[:, :, 2].sum(1)
+            world = dist.get_world_size(group)
+            all_lse = torch.empty(world, rows, dtype=torch.float32, device=dev)
+            dist.all_gather_into_tensor(all_lse.view(-1), lse_local.contiguous(), group=group)
+            lse = torch.logsumexp(all_lse, dim=0)
+            dist.all_reduce(tgt, group=group)
         valid = labels >= 0
         per_row = torch.where(valid, lse - tgt, torch.zeros_like(lse))
         wts = torch.ones_like(per_row) if weights is None else weights.float()
@@ -275,7 +300,7 @@ class _VocabParallelLinearCE(torch.autograd.Function):
             mark_grad_written(ctx.wref)
         else:
             dw = dw.to(w.dtype)
-        return dh, dw, None, None, None, None, None, None
+        return dh, dw, None, None, None, None, None, None, None
 
 
 def vocab_parallel_linear_cross_entropy(h, w_shard, labels, weights, tp: TPContext, vocab: int,
@@ -286,7 +311,7 @@ def vocab_parallel_linear_cross_entropy(h, w_shard, labels, weights, tp: TPConte
     v0, v1 = tp.vocab_range(vocab)
     if use_native(h, w_shard):
         return _VocabParallelLinearCE.apply(h.contiguous(), w_shard, labels, weights, v0, exclude_index, tp.group,
-                                            chunk_rows)
+                                            chunk_rows, tp)
     # reference path (CPU / fp32): gather the shards' logits statistics with autograd-aware ops
     hc = copy_to_tensor_parallel(h, tp.group)
     z = hc.float() @ w_shard.float().t()
