@@ -139,13 +139,13 @@ class DecoderLayer(nn.Module):
         if getattr(self, "lora", None) is not None:
             return self._forward_lora(h, positions, inv_freq, attend)
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
-        qkv = linear(copy_to_tensor_parallel(y, tpg), self.w_qkv)
+        qkv = linear(y, self.w_qkv, tp) if tpg is not None else linear(y, self.w_qkv)
         qkv = qk_norm_rope(qkv, positions, inv_freq, self.q_norm, self.k_norm, cfg.num_attention_heads,
                            cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
         a = attend(qkv, self.idx)          # [rows, Hq_local·D]
         h = row_parallel_linear_residual(a, self.w_o, h, tp)
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
-        act = linear_swiglu(copy_to_tensor_parallel(y2, tpg), self.w_gate_up)
+        act = linear_swiglu(y2, self.w_gate_up, tp) if tpg is not None else linear_swiglu(y2, self.w_gate_up)
         return row_parallel_linear_residual(act, self.w_down, h, tp, last=True)
 
     def _forward_lora(self, h, positions, inv_freq, attend):

@@ -71,14 +71,31 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     return out
 
 
+def _dgrad_over_tensor_parallel(dy2: torch.Tensor, w: torch.Tensor, tp) -> torch.Tensor:
+    """dx = Σ_ranks dy_r · W_r for a weight split along its output rows (column-parallel linear): the
+    all-reduce runs in the GEMM epilogue over peer memory when the product is large enough for that to
+    pay, otherwise as an NCCL all-reduce after the GEMM."""
+    import torch.distributed as dist
+
+    fused = (tp.fused_allreduce(dy2.shape[0], w.shape[1], dy2.device)
+             if (use_native(dy2, w) and w.shape[0] >= tp.fused_allreduce_min_k) else None)
+    if fused is not None:
+        return fused.matmul(dy2, w, b_mn_major=True)
+    dx = gemm(dy2, w, b_mn_major=True)
+    dist.all_reduce(dx, group=tp.group)
+    return dx
+
+
 class _Linear(torch.autograd.Function):
     """y = x Wᵀ with W [out, in]. The weight gradient goes straight into the parameter's
-    slice of the flat gradient buffer when it has one (no .grad tensor, no extra add)."""
+    slice of the flat gradient buffer when it has one (no .grad tensor, no extra add). With `tp`
+    (column-parallel: W holds this rank's output rows, x is replicated) the input gradient is summed
+    over the tensor-parallel group."""
 
     @staticmethod
-    def forward(ctx, x, w):
+    def forward(ctx, x, w, tp=None):
         ctx.save_for_backward(x, w)
-        ctx.wref = w
+        ctx.wref, ctx.tp = w, tp
         y = gemm(x, w)
         return y.view(*x.shape[:-1], w.shape[0])
 
@@ -89,7 +106,8 @@ class _Linear(torch.autograd.Function):
         x2 = _as2d(x)
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, w, b_mn_major=True).view_as(x)
+            dx = (_dgrad_over_tensor_parallel(dy2, w, ctx.tp) if ctx.tp is not None
+                  else gemm(dy2, w, b_mn_major=True)).view_as(x)
         if ctx.needs_input_grad[1]:
             sink, acc = grad_sink(ctx.wref)
             if sink is not None:
@@ -97,11 +115,12 @@ class _Linear(torch.autograd.Function):
                 mark_grad_written(ctx.wref)
             else:
                 dw = gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out_dtype=w.dtype)
-        return dx, dw
+        return dx, dw, None
 
 
-def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    return _Linear.apply(x, w)
+def linear(x: torch.Tensor, w: torch.Tensor, tp=None) -> torch.Tensor:
+    """`tp`: a TPContext of size > 1 makes this a column-parallel linear (see _Linear)."""
+    return _Linear.apply(x, w, tp if (tp is not None and tp.size > 1) else None)
 
 
 class _Replay:
@@ -208,13 +227,13 @@ class _LinearSwiGLU(torch.autograd.Function):
     pre-activation never reaches HBM; with grad it is kept for the backward pass."""
 
     @staticmethod
-    def forward(ctx, x, w_gu):
+    def forward(ctx, x, w_gu, tp=None):
         from .activation import swiglu_forward
 
         gu = gemm(x, w_gu)
         act = swiglu_forward(gu)
         ctx.save_for_backward(x, w_gu, gu)
-        ctx.wref = w_gu
+        ctx.wref, ctx.tp = w_gu, tp
         return act.view(*x.shape[:-1], w_gu.shape[0] // 2)
 
     @staticmethod
@@ -225,7 +244,8 @@ class _LinearSwiGLU(torch.autograd.Function):
         dgu = swiglu_backward(_as2d(dact.contiguous()), gu)
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dgu, w, b_mn_major=True).view_as(x)
+            dx = (_dgrad_over_tensor_parallel(dgu, w, ctx.tp) if ctx.tp is not None
+                  else gemm(dgu, w, b_mn_major=True)).view_as(x)
         if ctx.needs_input_grad[1]:
             sink, acc = grad_sink(ctx.wref)
             if sink is not None:
@@ -233,11 +253,12 @@ class _LinearSwiGLU(torch.autograd.Function):
                 mark_grad_written(ctx.wref)
             else:
                 dw = gemm(dgu, _as2d(x), a_mn_major=True, b_mn_major=True, out_dtype=w.dtype)
-        return dx, dw
+        return dx, dw, None
 
 
-def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor) -> torch.Tensor:
+def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, tp=None) -> torch.Tensor:
+    """`tp`: a TPContext of size > 1 makes this a column-parallel projection (input gradient summed over it)."""
     if not (torch.is_grad_enabled() and (x.requires_grad or w_gu.requires_grad)):
         y = gemm(x, w_gu, swiglu=True)
         return y.view(*x.shape[:-1], w_gu.shape[0] // 2)
-    return _LinearSwiGLU.apply(x, w_gu)
+    return _LinearSwiGLU.apply(x, w_gu, tp if (tp is not None and tp.size > 1) else None)

@@ -63,11 +63,12 @@ class FusedAllReduceGemm:
         self.flip = 0
 
     def matmul(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None,
-               out: torch.Tensor | None = None) -> torch.Tensor:
-        """x [M, K_local] · w[N, K_local]ᵀ summed over the group (+ residual [M, N]) -> [M, N] bf16."""
+               out: torch.Tensor | None = None, b_mn_major: bool = False) -> torch.Tensor:
+        """x [M, K_local] · w[N, K_local]ᵀ (or · w[K_local, N] with `b_mn_major`) summed over the group
+        (+ residual [M, N]) -> [M, N] bf16."""
         M, K = x.shape
-        N = w.shape[0]
-        if N != self.n_cols or M > self.max_rows or w.shape[1] != K:
+        N = w.shape[1] if b_mn_major else w.shape[0]
+        if N != self.n_cols or M > self.max_rows or (w.shape[0] if b_mn_major else w.shape[1]) != K:
             raise ValueError(f"shape [{M},{K}]x[{N},{w.shape[1]}] outside this workspace ({self.max_rows} rows, "
                              f"{self.n_cols} columns)")
         if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or w.stride(1) != 1:
@@ -78,7 +79,7 @@ class FusedAllReduceGemm:
         self.flip ^= 1
         self.epoch[b] += 1
         rc = native.lib().tdllm_gemm_allreduce_bf16(
-            ptr(x), ptr(w), ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0), 0, 0,
+            ptr(x), ptr(w), ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0), 0, int(b_mn_major),
             ptr(residual) if residual is not None else None, residual.stride(0) if residual is not None else 0,
             self.world, self.rank, self.epoch[b], self.max_rows, self.ws[b].ptr_array, self.flags[b].ptr_array,
             0, stream())
