@@ -88,3 +88,70 @@ def test_dflash_anchor_blocks_and_document_boundaries():
     s, t = torch.randn(24, 50), torch.randn(24, 50)
     loss, per = reference_dflash_loss(s, t, sup.view(2, -1)[0], b.position_weights[0])
     assert loss >= 0 and per.shape == (24,)
+
+
+def test_diffusiongemma_native_replaces_tokens_and_scores_every_position():
+    from turbo_dllm_b200.objectives.runtime import LABEL_IGNORE_INDEX, DiffusionGemmaNativeRuntime
+
+    rt = DiffusionGemmaNativeRuntime(vocab_size=500, self_conditioning_probability=0.5, block_size=16,
+                                     mask_token_id=499, max_seq_len=128, seed=11)
+    x0 = torch.randint(0, 400, (6, 128))
+    sup = torch.zeros_like(x0, dtype=torch.bool)
+    sup[:, 32:] = True
+    cb = rt.corrupt(x0, supervision_mask=sup)
+    noisy, labels = cb.noisy_input_ids[:, 0], cb.labels[:, 0]
+    assert cb.views == 1 and (cb.loss_weights == 1).all()
+    # labels: the clean token on every scored position, nothing elsewhere
+    assert (labels[:, 32:] == x0[:, 32:]).all() and (labels[:, :32] == LABEL_IGNORE_INDEX).all()
+    # corruption only inside the scored region, by replacement (never the mask id by construction of this data)
+    assert (noisy[:, :32] == x0[:, :32]).all()
+    changed = (noisy != x0)
+    assert changed.any() and int(changed.sum()) <= int(cb.replaced_tokens)
+    assert cb.loss_denominator == float(sup.sum()) and int(cb.active_tokens) == int(sup.sum())
+    assert cb.self_conditioning_mask.shape == (6,) and cb.self_conditioning_mask.dtype == torch.bool
+    # deterministic and resumable through the batch counter alone
+    rt2 = DiffusionGemmaNativeRuntime(vocab_size=500, self_conditioning_probability=0.5, block_size=16,
+                                      mask_token_id=499, max_seq_len=128, seed=11)
+    cb2 = rt2.corrupt(x0, supervision_mask=sup)
+    assert (cb2.noisy_input_ids == cb.noisy_input_ids).all()
+    rt2.load_state_dict(rt.state_dict())
+    a, b = rt.corrupt(x0), rt2.corrupt(x0)
+    assert (a.noisy_input_ids == b.noisy_input_ids).all() and (a.self_conditioning_mask == b.self_conditioning_mask).all()
+
+
+def test_streaming_soft_embedding_matches_dense_softmax():
+    from turbo_dllm_b200.ops.soft_embedding import streaming_soft_embedding
+
+    torch.manual_seed(0)
+    h, w = torch.randn(37, 48), torch.randn(301, 48) * 0.3
+    ref = torch.softmax(h @ w.t(), 1) @ w
+    out = streaming_soft_embedding(h, w, row_chunk_size=10, vocab_chunk_size=64)
+    assert torch.allclose(out, ref, atol=1e-5) and not out.requires_grad
+    cap = 5.0
+    ref2 = torch.softmax(cap * torch.tanh(h @ w.t() / cap), 1) @ w * 2
+    out2 = streaming_soft_embedding(h.view(1, 37, 48), w, row_chunk_size=100, vocab_chunk_size=1000,
+                                    logit_softcap=cap, embedding_scale=2.0)
+    assert out2.shape == (1, 37, 48) and torch.allclose(out2[0], ref2, atol=1e-5)
+
+
+def test_native_sft_session_step_with_self_conditioning():
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    def run(p):
+        spec = RunSpec.from_mapping({
+            "model": {"id": "synthetic:tiny-moe", "seq_len": 128, "dtype": "fp32"},
+            "objective": {"name": "diffusiongemma_native_sft", "block_size": 16, "loss_weighting": "unit",
+                          "self_conditioning_probability": p, "self_conditioning_row_chunk_size": 64,
+                          "self_conditioning_vocab_chunk_size": 100},
+            "training": {"batch_size": 2, "steps": 1, "skip_optimizer_step": True},
+            "optimizer": {"lr": 1e-3}}).validate()
+        s = TrainingSession(spec, device="cpu")
+        r = s.step()
+        return float(r.loss_sum) / r.denominator, s.model.flat.grad.clone()
+
+    l0, g0 = run(0.0)
+    l1, g1 = run(1.0)
+    assert l0 == l0 and l1 == l1 and l0 > 0 and l1 > 0
+    assert abs(l0 - l1) > 1e-6, "feeding the first pass back must change the prediction"
+    assert g1.abs().sum() > 0 and not torch.allclose(g0, g1)

@@ -145,8 +145,15 @@ class RunSpec:
                     need(m.seq_len // o.block_size >= bp,
                          f"block_parallel_size ({bp}) exceeds the number of blocks "
                          f"({m.seq_len // o.block_size})")
-        elif o.name in ("standard_block_diffusion", "fast_dllm_v2"):
+        elif o.name in ("standard_block_diffusion", "fast_dllm_v2", "diffusiongemma_native_sft"):
             problems.append(f"objective.block_size is required for {o.name}")
+        if o.name == "diffusiongemma_native_sft":
+            need(o.noise_schedule == "loglinear", "diffusiongemma_native_sft requires objective.noise_schedule=loglinear")
+            need(o.loss_weighting == "unit", "diffusiongemma_native_sft requires objective.loss_weighting=unit")
+            need(0.0 <= o.self_conditioning_probability <= 1.0,
+                 "objective.self_conditioning_probability must be in [0, 1]")
+            need(o.self_conditioning_row_chunk_size > 0 and o.self_conditioning_vocab_chunk_size > 0,
+                 "objective.self_conditioning_row_chunk_size / vocab_chunk_size must be positive")
         need(0.0 < o.sampling_epsilon_min <= o.sampling_epsilon_max <= 1.0,
              "objective.sampling_epsilon_min/max must satisfy 0 < min <= max <= 1")
         need(0.0 <= o.noise_schedule_epsilon < 1.0, "objective.noise_schedule_epsilon must be in [0, 1)")

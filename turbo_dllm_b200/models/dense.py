@@ -243,12 +243,17 @@ class BlockDiffusionTransformer(nn.Module):
                 shard = full
             p.copy_((shard * std).to(p.dtype))
 
-    def forward(self, tokens: torch.Tensor, positions: torch.Tensor, attend: Callable) -> torch.Tensor:
-        """tokens, positions: [rows]; returns final-norm hidden states [rows, H]."""
+    def forward(self, tokens: torch.Tensor, positions: torch.Tensor, attend: Callable,
+                soft_embeddings: torch.Tensor | None = None, soft_rows: torch.Tensor | None = None) -> torch.Tensor:
+        """tokens, positions: [rows]; returns final-norm hidden states [rows, H].
+        `soft_embeddings` [n, H] (detached predictions of an earlier pass) are added to the input
+        embeddings of the rows `soft_rows` [n] (self-conditioning)."""
         if self.tp is not None:
             h = vocab_parallel_embedding(tokens, self.embed, self.tp, self.cfg.vocab_size)
         else:
             h = embedding(tokens, self.embed)
+        if soft_embeddings is not None and soft_rows is not None and soft_rows.numel() > 0:
+            h = h.index_add(0, soft_rows, soft_embeddings.to(h.dtype))
         positions = positions.to(torch.int32)
         if torch.is_grad_enabled() and not h.requires_grad:
             h = h.detach().requires_grad_(True)   # frozen embedding (adapters): keep the checkpoint chain alive

@@ -8,6 +8,8 @@ standard_block_diffusion: one diffusion time t per (sample, block), antithetic-s
 default (one uniform draw, strata rotated by it), scaled to [eps_min, eps_max]; a token is
 masked iff rand <= t; labels are the clean token on masked positions and -100 elsewhere; the
 per-block loss weight is 1/t (or 1).
+diffusiongemma_native_sft: same block times, uniform random-token replacement, labels on every scored
+position, unit weights, a per-sample self-conditioning draw (see DiffusionGemmaNativeRuntime).
 fast_dllm_v2: t ~ U(0,1) per (sample, block), move chance (1-eps)·t + eps, two complementary
 views (mask, ~mask) share the clean copy, labels are shifted left by one, weights are 1 and the
 denominator is batch·(L-1).
@@ -208,6 +210,74 @@ class FastDLLMv2Runtime(_ObjectiveRuntime):
                               active, valid, float(valid))
 
 
+class DiffusionGemmaNativeRuntime(StandardBlockDiffusionRuntime):
+    """diffusiongemma_native_sft: uniform-replacement corruption with unit loss weights.
+
+    Per (sample, block) a time t in [eps_min, eps_max] (antithetic-stratified by default); a scored
+    token is REPLACED by a uniformly random vocabulary token with probability t (no mask token); the
+    label is the clean token on EVERY scored position (replaced or not), all weights are 1 and the
+    denominator is the scored-token count. With probability `self_conditioning_probability` a sample
+    is marked for self-conditioning (`CorruptedBatch.self_conditioning_mask`): the training step then
+    runs a detached first pass and feeds its soft predictions back (`ops/soft_embedding.py`).
+    The Bernoulli draws use the counter-based generator shared with the other objectives; the random
+    replacement tokens and the self-conditioning draw come from a torch generator re-seeded from
+    (seed, batch counter), so the resumable state is still just the counter.
+
+    Semantics follow dllm_parallel/core/objectives/diffusiongemma.py:66-460 (all-block corruption over
+    the scored region; its separate encoder next-token term is not part of this runtime).
+    """
+    name = "diffusiongemma_native_sft"
+    views = 1
+    exclude_mask_token = False
+
+    def __init__(self, *, vocab_size: int, self_conditioning_probability: float = 0.5, **kw):
+        kw.setdefault("loss_weighting", "unit")
+        super().__init__(**kw)
+        if vocab_size <= 1:
+            raise ValueError("vocab_size must be greater than one")
+        if not 0.0 <= self_conditioning_probability <= 1.0:
+            raise ValueError("self_conditioning_probability must be in [0, 1]")
+        if self.loss_weighting != "unit":
+            raise ValueError("diffusiongemma_native_sft requires loss_weighting=unit")
+        self.vocab_size = int(vocab_size)
+        self.self_conditioning_probability = float(self_conditioning_probability)
+
+    def corrupt(self, x0, *, supervision_mask=None, supervision_count=None) -> CorruptedBatch:
+        b, l, nblk = self._check(x0)
+        x0 = x0.to(self.device)
+        if supervision_mask is None:
+            if supervision_count is not None:
+                raise ValueError("supervision_count requires an explicit supervision_mask")
+            eligible, valid = None, b * l
+        else:
+            if supervision_mask.shape != x0.shape:
+                raise ValueError("supervision_mask must match input_ids")
+            eligible = supervision_mask.to(self.device, torch.bool)
+            valid = int(eligible.sum()) if supervision_count is None else int(supervision_count)
+        if valid <= 0:
+            raise ValueError("each training batch must contain supervised tokens")
+        t = self.sample_times(b, nblk)
+        noise = (-torch.log1p(-t.clamp(max=1.0 - 1e-7))).clamp(max=-math.log(self.noise_schedule_epsilon))
+        # which scored tokens move: the shared counter-based Bernoulli draw (positions that got the mask id)
+        _, moved_labels = self._tokens(x0, t, eligible, shift=False)
+        moved = moved_labels[:, 0] != LABEL_IGNORE_INDEX
+        g = torch.Generator(device=self.device)
+        g.manual_seed((self.seed * 1_000_003 + 2 * self.batches_corrupted + 1) % (2 ** 63 - 1))
+        random_tokens = torch.randint(0, self.vocab_size, x0.shape, dtype=x0.dtype, device=self.device, generator=g)
+        noisy = torch.where(moved, random_tokens, x0)
+        scored = torch.ones_like(x0, dtype=torch.bool) if eligible is None else eligible
+        labels = torch.where(scored, x0, torch.full_like(x0, LABEL_IGNORE_INDEX))
+        sc_mask = torch.rand(b, device=self.device, generator=g) < self.self_conditioning_probability
+        active = scored.sum(dtype=torch.int64)
+        self.batches_corrupted += 1
+        self.valid_tokens_seen += valid
+        out = CorruptedBatch(x0, noisy[:, None], labels[:, None], t, noise, torch.ones(b, 1, nblk, device=self.device),
+                             active, valid, float(valid))
+        out.self_conditioning_mask = sc_mask
+        out.replaced_tokens = moved.sum(dtype=torch.int64)
+        return out
+
+
 def fused_corrupt(x0: torch.Tensor, t: torch.Tensor, eligible, *, block_size: int, views: int, shift: bool,
                   mask_id: int, seed: int, offset: int):
     """Noisy ids and labels [B, V, L] from per-block move chances `t` with the counter-based
@@ -231,7 +301,7 @@ def fused_corrupt(x0: torch.Tensor, t: torch.Tensor, eligible, *, block_size: in
     return corrupt_reference(x0, t, eligible, block_size, views, shift, mask_id, seed, offset)
 
 
-def build_objective_runtime(spec, *, mask_token_id: int, seed: int, device="cpu"):
+def build_objective_runtime(spec, *, mask_token_id: int, seed: int, device="cpu", vocab_size: int | None = None):
     """spec: RunSpec. Returns the corruption runtime of `objective.name`."""
     o = spec.objective
     common = dict(block_size=o.block_size, mask_token_id=mask_token_id, max_seq_len=spec.model.seq_len,
@@ -243,4 +313,12 @@ def build_objective_runtime(spec, *, mask_token_id: int, seed: int, device="cpu"
             antithetic_sampling=o.antithetic_sampling, **common)
     if o.name == "fast_dllm_v2":
         return FastDLLMv2Runtime(noise_schedule_epsilon=o.noise_schedule_epsilon, **common)
+    if o.name == "diffusiongemma_native_sft":
+        if vocab_size is None:
+            raise ValueError("diffusiongemma_native_sft needs the model's vocabulary size")
+        return DiffusionGemmaNativeRuntime(
+            vocab_size=vocab_size, self_conditioning_probability=o.self_conditioning_probability,
+            loss_weighting=o.loss_weighting, noise_schedule_epsilon=o.noise_schedule_epsilon,
+            sampling_epsilon_min=o.sampling_epsilon_min, sampling_epsilon_max=o.sampling_epsilon_max,
+            antithetic_sampling=o.antithetic_sampling, **common)
     raise ValueError(f"no corruption runtime for objective {o.name!r}")

@@ -20,7 +20,7 @@ def evaluate_masked_token_accuracy(session, batches: int, seed: int = 314159) ->
         return {}
     spec = session.spec
     objective = build_objective_runtime(spec, mask_token_id=session.cfg.mask_token_id, seed=seed,
-                                        device=session.device)
+                                        vocab_size=session.cfg.vocab_size, device=session.device)
     saved = session.objective
     session.objective = objective
     correct = torch.zeros((), dtype=torch.float64, device=session.device)

@@ -101,7 +101,8 @@ class TrainingSession:
         dp_rank = runtime.sample_parallel_rank if runtime is not None else self.rank
         self.dp_size = runtime.data_parallel_size * ep if runtime is not None else self.world
         self.objective = build_objective_runtime(spec, mask_token_id=self.cfg.mask_token_id,
-                                                 seed=seed + 7919 * (dp_rank + 1), device=self.device)
+                                                 seed=seed + 7919 * (dp_rank + 1), device=self.device,
+                                                 vocab_size=self.cfg.vocab_size)
         data_kw = dict(batch_size=spec.training.batch_size, seq_len=spec.model.seq_len,
                        vocab_size=self.cfg.vocab_size, mask_token_id=self.cfg.mask_token_id,
                        seed=seed + 104729 * (dp_rank + 1), vocab_sample_size=spec.data.vocab_sample_size)
@@ -298,7 +299,8 @@ class TrainingSession:
         cb = self.objective.corrupt(batch.input_ids, supervision_mask=batch.supervision_mask,
                                     supervision_count=batch.supervision_count)
         tokens, labels, weights = self.assemble_rows(cb)
-        hidden = self.model(tokens, self.layout.positions, self.attend)
+        soft, soft_rows = self._self_conditioning_inputs(tokens, cb)
+        hidden = self.model(tokens, self.layout.positions, self.attend, soft, soft_rows)
         self.memory_report("after forward")
         h, l, w, _ = compact_supervised_rows(hidden, labels, weights)
         loss_sum, _ = self.model.loss(h, l, w, self.objective.exclude_mask_token)
@@ -306,6 +308,29 @@ class TrainingSession:
         (loss_sum / denominator).backward()
         self.memory_report("after backward")
         return loss_sum.detach(), l.shape[0], cb
+
+    def _self_conditioning_inputs(self, tokens: torch.Tensor, cb):
+        """Self-conditioning (diffusiongemma_native_sft): for the samples the objective marked, a detached
+        first pass predicts every noisy row and the expected embedding under that prediction
+        (`ops.soft_embedding`) is added to the row's input embedding in the real pass."""
+        chosen = getattr(cb, "self_conditioning_mask", None)
+        if chosen is None or getattr(self, "lora", None) is not None:
+            return None, None
+        from ..ops.soft_embedding import streaming_soft_embedding
+
+        lay = self.layout
+        rows = chosen.to(self.device)[lay.noisy_seq].nonzero(as_tuple=True)[0]   # noisy rows come first in the packing
+        if rows.numel() == 0:
+            return None, None
+        with torch.no_grad():
+            hidden0 = self.model(tokens, lay.positions, self.attend)
+            o = self.spec.objective
+            tp = getattr(self.model, "tp", None)
+            soft = streaming_soft_embedding(hidden0.index_select(0, rows), self.model.lm_head,
+                                            row_chunk_size=o.self_conditioning_row_chunk_size,
+                                            vocab_chunk_size=o.self_conditioning_vocab_chunk_size,
+                                            tp_group=tp.group if tp is not None and tp.size > 1 else None)
+        return soft, rows
 
     def global_denominator(self, batches: list[DataBatch]) -> float:
         """Loss denominator of the whole optimizer step over all data-parallel ranks."""
