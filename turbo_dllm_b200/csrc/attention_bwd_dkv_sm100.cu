@@ -40,8 +40,8 @@ struct Params {
   const int* tile_ptr;  // per key tile: query tiles that see it
   const int* tile_idx;  // q_tile * 2 + needs_mask
   const int* order;     // key tiles, heaviest first
-  const float* lse2;   // [Hq, nq_pad] lse·log2e (+inf = row without keys)
-  const float* delta;  // [Hq, nq_pad] scale · rowsum(dO∘O)
+  const float* lse2;   // [Hq, nq_pad] −lse·log2e (−inf = row without keys)
+  const float* delta;  // [Hq, nq_pad] −scale · rowsum(dO∘O)
   float scale_log2, scale;
 };
 
@@ -249,10 +249,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
             const int g = qrow0 + e + t;
-            float pr = fast_exp2(fmaf(__uint_as_float(rs[e + t]), p.scale_log2, -lv[t]));
+            float pr = fast_exp2(fmaf(__uint_as_float(rs[e + t]), p.scale_log2, lv[t]));
             if (!key_visible(kcode, __ldg(p.q_lo + g), __ldg(p.q_hi + g), __ldg(p.q_grp + g))) pr = 0.f;
             pv[t] = pr;
-            ds[t] = pr * fmaf(__uint_as_float(rp[e + t]), p.scale, -dv[t]);
+            ds[t] = pr * fmaf(__uint_as_float(rp[e + t]), p.scale, dv[t]);
           }
           pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
           pk[(e >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
@@ -264,16 +264,16 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         for (int e = 0; e < 64; e += 4) {
           const float4 l4 = *reinterpret_cast<const float4*>(sl + e);
           const float4 d4 = *reinterpret_cast<const float4*>(sd + e);
-          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -l4.x));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, -l4.y));
-          const float p2 = fast_exp2(fmaf(__uint_as_float(rs[e + 2]), p.scale_log2, -l4.z));
-          const float p3 = fast_exp2(fmaf(__uint_as_float(rs[e + 3]), p.scale_log2, -l4.w));
+          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, l4.x));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, l4.y));
+          const float p2 = fast_exp2(fmaf(__uint_as_float(rs[e + 2]), p.scale_log2, l4.z));
+          const float p3 = fast_exp2(fmaf(__uint_as_float(rs[e + 3]), p.scale_log2, l4.w));
           pk[e >> 1] = pack_bf16x2(p0, p1);
           pk[(e >> 1) + 1] = pack_bf16x2(p2, p3);
-          dk[e >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[e]), p.scale, -d4.x),
-                                   p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, -d4.y));
-          dk[(e >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(rp[e + 2]), p.scale, -d4.z),
-                                         p3 * fmaf(__uint_as_float(rp[e + 3]), p.scale, -d4.w));
+          dk[e >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[e]), p.scale, d4.x),
+                                   p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, d4.y));
+          dk[(e >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(rp[e + 2]), p.scale, d4.z),
+                                         p3 * fmaf(__uint_as_float(rp[e + 3]), p.scale, d4.w));
         }
       }
       tmem_st16(t_s, pk);

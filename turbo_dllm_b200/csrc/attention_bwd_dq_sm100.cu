@@ -39,8 +39,8 @@ struct Params {
   const int* tile_ptr;
   const int* tile_idx;
   const int* order;
-  const float* lse2;   // [Hq, nq_pad] lse·log2e (+inf = row without keys)
-  const float* delta;  // [Hq, nq_pad] scale · rowsum(dO∘O)
+  const float* lse2;   // [Hq, nq_pad] −lse·log2e (−inf = row without keys)
+  const float* delta;  // [Hq, nq_pad] −scale · rowsum(dO∘O)
   float scale_log2, scale;
 };
 
@@ -249,20 +249,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (ent & 1) {
 #pragma unroll
         for (int e = 0; e < 64; e += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -lse2));
-          float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, -lse2));
+          float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, lse2));
+          float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, lse2));
           if (!key_visible(__ldg(kc + e), lo, hi, grp)) p0 = 0.f;
           if (!key_visible(__ldg(kc + e + 1), lo, hi, grp)) p1 = 0.f;
-          pk[e >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[e]), p.scale, -delta),
-                                   p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, -delta));
+          pk[e >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[e]), p.scale, delta),
+                                   p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, delta));
         }
       } else {
 #pragma unroll
         for (int e = 0; e < 64; e += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -lse2));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, -lse2));
-          pk[e >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[e]), p.scale, -delta),
-                                   p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, -delta));
+          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, lse2));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, lse2));
+          pk[e >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[e]), p.scale, delta),
+                                   p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, delta));
         }
       }
       tmem_st16(t_s, pk);
@@ -323,8 +323,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   }
 }
 
-// Per (row, head): delta_s = scale * sum_d dO·O and lse2 = lse·log2(e), with lse2 = +inf for rows
-// that saw no key (and for padding rows) so that exp2(x − lse2) is exactly 0 there.
+// Per (row, head), both NEGATED so that the consumers need one fused multiply-add each:
+// delta_s = −scale · sum_d dO·O and lse2 = −lse·log2(e), with lse2 = −inf for rows that saw no key
+// (and for padding rows) so that exp2(x + lse2) is exactly 0 there.
 // One warp per (row, head). Output layout: delta_s [Hq, nq_pad], lse2 [Hq, nq_pad].
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
                                   const __nv_bfloat16* __restrict__ dout,
@@ -351,8 +352,8 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
   if (lane == 0) {
     const size_t at = (size_t)h * nq_pad + row;
     const float l = lse[at];
-    delta[at] = s * scale;
-    lse2[at] = (row < nq && l > -INFINITY) ? l * 1.4426950408889634f : INFINITY;
+    delta[at] = -s * scale;
+    lse2[at] = (row < nq && l > -INFINITY) ? -l * 1.4426950408889634f : -INFINITY;
   }
 }
 

@@ -4,7 +4,7 @@
 // group, visible query tile) pair in units of 64 queries. Everything is computed transposed
 // (keys on the TMEM lanes):
 //   Sᵀ  = K·Qᵀ   (128 keys x 64 queries)      dPᵀ = V·dOᵀ
-//   Pᵀ  = exp(Sᵀ·scale − lse[q])              dSᵀ = Pᵀ∘(dPᵀ − delta[q])·scale
+//   Pᵀ  = exp(Sᵀ·scale − lse[q])              dSᵀ = Pᵀ∘(dPᵀ − delta[q])·scale   (packed fp32x2 arithmetic)
 //   dV += Pᵀ·dO        dK += dSᵀ·Q            dQᵀ = Kᵀ·dSᵀ   (128 d x 64 queries)
 // Five tensor-core products per tile pair: the score and dP tiles are computed once and
 // feed all three gradients (separate dQ and dK/dV kernels need seven). dK/dV accumulate in
@@ -71,8 +71,8 @@ struct Params {
   const int* tile_ptr;  // per work item (chunk * nkt + key tile): the chunk's query tiles that see the key tile
   const int* tile_idx;  // q_tile * 2 + needs_mask
   const int* order;     // non-empty work items: chunk by chunk, heaviest first inside a chunk
-  const float* lse2;   // [Hq, nq_pad] lse·log2e (+inf = row without keys)
-  const float* delta;  // [Hq, nq_pad] scale · rowsum(dO∘O)
+  const float* lse2;   // [Hq, nq_pad] −lse·log2e (−inf = row without keys)
+  const float* delta;  // [Hq, nq_pad] −scale · rowsum(dO∘O)
   float scale_log2, scale;
 };
 
@@ -348,10 +348,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
               for (int t = 0; t < 4; ++t) {
                 const int g = qrow0 + c * 16 + e + t;
-                float pr = fast_exp2(fmaf(__uint_as_float(rs[e + t]), p.scale_log2, -lv[t]));
+                float pr = fast_exp2(fmaf(__uint_as_float(rs[e + t]), p.scale_log2, lv[t]));
                 if (!key_visible(kcode, __ldg(p.q_lo + g), __ldg(p.q_hi + g), __ldg(p.q_grp + g))) pr = 0.f;
                 pv[t] = pr;
-                ds[t] = pr * fmaf(__uint_as_float(rp[e + t]), p.scale, -dv[t]);
+                ds[t] = pr * fmaf(__uint_as_float(rp[e + t]), p.scale, dv[t]);
               }
               pk[c * 8 + (e >> 1)] = pack_bf16x2(pv[0], pv[1]);
               pk[c * 8 + (e >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
@@ -359,20 +359,31 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
               dk[c * 8 + (e >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
             }
           } else {
+            // two queries per instruction: t = s·scale_log2 + (−lse2), u = dP·scale + (−delta_s), dS = p·u
+            const uint64_t sc_l2 = pair_f32(p.scale_log2, p.scale_log2), sc = pair_f32(p.scale, p.scale);
 #pragma unroll
             for (int e = 0; e < 16; e += 4) {
               const float4 l4 = *reinterpret_cast<const float4*>(sl + c * 16 + e);
               const float4 d4 = *reinterpret_cast<const float4*>(sd + c * 16 + e);
-              const float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -l4.x));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, -l4.y));
-              const float p2 = fast_exp2(fmaf(__uint_as_float(rs[e + 2]), p.scale_log2, -l4.z));
-              const float p3 = fast_exp2(fmaf(__uint_as_float(rs[e + 3]), p.scale_log2, -l4.w));
+              const uint64_t t01 = fma_f32x2(pair_f32(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), sc_l2,
+                                             pair_f32(l4.x, l4.y));
+              const uint64_t t23 = fma_f32x2(pair_f32(__uint_as_float(rs[e + 2]), __uint_as_float(rs[e + 3])), sc_l2,
+                                             pair_f32(l4.z, l4.w));
+              const uint64_t u01 = fma_f32x2(pair_f32(__uint_as_float(rp[e]), __uint_as_float(rp[e + 1])), sc,
+                                             pair_f32(d4.x, d4.y));
+              const uint64_t u23 = fma_f32x2(pair_f32(__uint_as_float(rp[e + 2]), __uint_as_float(rp[e + 3])), sc,
+                                             pair_f32(d4.z, d4.w));
+              float t0, t1, t2, t3;
+              unpair_f32(t01, t0, t1);
+              unpair_f32(t23, t2, t3);
+              const float p0 = fast_exp2(t0), p1 = fast_exp2(t1), p2 = fast_exp2(t2), p3 = fast_exp2(t3);
+              float s0, s1, s2, s3;
+              unpair_f32(mul_f32x2(pair_f32(p0, p1), u01), s0, s1);
+              unpair_f32(mul_f32x2(pair_f32(p2, p3), u23), s2, s3);
               pk[c * 8 + (e >> 1)] = pack_bf16x2(p0, p1);
               pk[c * 8 + (e >> 1) + 1] = pack_bf16x2(p2, p3);
-              dk[c * 8 + (e >> 1)] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[e]), p.scale, -d4.x),
-                                                 p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, -d4.y));
-              dk[c * 8 + (e >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(rp[e + 2]), p.scale, -d4.z),
-                                                     p3 * fmaf(__uint_as_float(rp[e + 3]), p.scale, -d4.w));
+              dk[c * 8 + (e >> 1)] = pack_bf16x2(s0, s1);
+              dk[c * 8 + (e >> 1) + 1] = pack_bf16x2(s2, s3);
             }
           }
         }
