@@ -78,7 +78,9 @@ def _first_error(text: str) -> str:
     return (lines[-1] if lines else "no output")[:300]
 
 
-def _run_reference(recipe: dict, timeout: float):
+def _run_reference(recipe: dict, timeout: float, single_process: bool = False):
+    """Runs the reference trainer on `recipe` in a child process. `single_process`: drop the launcher's
+    rendezvous variables so that the child is a one-GPU run on this rank's device (used by the probe)."""
     import yaml
 
     with tempfile.NamedTemporaryFile("w", suffix=".yaml", delete=False) as f:
@@ -87,6 +89,14 @@ def _run_reference(recipe: dict, timeout: float):
     env = dict(os.environ)
     env["PYTHONPATH"] = REF + os.pathsep + env.get("PYTHONPATH", "")
     env.setdefault("DLLM_RUN_DIR", tempfile.mkdtemp(prefix="dllm_ref_run_"))
+    if single_process:
+        local = env.get("LOCAL_RANK", "0")
+        for k in list(env):
+            if k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE", "GROUP_RANK", "GROUP_WORLD_SIZE",
+                     "MASTER_ADDR", "MASTER_PORT", "ROLE_RANK", "ROLE_WORLD_SIZE", "ROLE_NAME") or \
+                    k.startswith("TORCHELASTIC_"):
+                del env[k]
+        env["CUDA_VISIBLE_DEVICES"] = local
     try:
         proc = subprocess.run([sys.executable, "-c", _RUN_REF, REF, path], capture_output=True, text=True,
                               timeout=timeout, env=env)
@@ -149,7 +159,7 @@ def run(args) -> dict:
     if p.returncode != 0:
         return {**base, "unavailable": "cannot build a Hugging Face Qwen3 model dir: " + _first_error(p.stderr)}
     _, err = _run_reference(_recipe(probe_dir, probe_shape, 1024, args.block_size, 1, 1, 0,
-                                    probe_shape["vocab_size"] - 1), timeout=600)
+                                    probe_shape["vocab_size"] - 1), timeout=600, single_process=True)
     if err is not None:
         return {**base, "unavailable": "reference trainer refuses to run on this machine: " + err}
     # 2) the real measurement

@@ -174,7 +174,9 @@ def run_ours(args):
 def run_reference(args):
     from baseline.reference_arm import run as run_ref
 
-    print(json.dumps(run_ref(args)), flush=True)
+    out = run_ref(args)
+    if int(os.environ.get("RANK", "0")) == 0:   # one line per job, also when every rank found the same refusal
+        print(json.dumps(out), flush=True)
 
 
 if __name__ == "__main__":
