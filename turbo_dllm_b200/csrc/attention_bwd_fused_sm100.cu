@@ -93,20 +93,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
 __device__ __forceinline__ bool key_visible(int code, int lo, int hi, int grp) {
   return code >= 0 ? (code >= lo && code < hi) : (code == grp);
 }
-// barrier among `nthreads` threads that also ANDs a predicate over them
-__device__ __forceinline__ bool named_bar_all(int id, int nthreads, bool pred) {
-  uint32_t out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.u32 p, %3, 0;\n\t"
-      "bar.red.and.pred q, %1, %2, p;\n\t"
-      "selp.u32 %0, 1, 0, q;\n\t}"
-      : "=r"(out)
-      : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
-      : "memory");
-  return out != 0;
-}
-
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,

@@ -35,8 +35,8 @@ constexpr int HD = 128;
 constexpr int TILE_BYTES = 128 * HD * 2;  // 32 KiB: two 64-column halves of 128 rows x 128 B
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 320;
-constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 512 + 1024;
+constexpr int THREADS = 576;   // 16 softmax warps (2 heads x 2 column halves x 4 lane quarters), TMA warp 16, MMA warp 17
+constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 512 + 2048 + 1024;   // + barriers + row exchange
 
 struct FwdParams {
   int nq_pad;          // query rows padded to a multiple of 128
@@ -69,6 +69,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 __device__ __forceinline__ bool key_visible(int code, int lo, int hi, int grp) {
   return code >= 0 ? (code >= lo && code < hi) : (code == grp);
 }
@@ -94,6 +100,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t bar_odone = b0 + 104;       // [2] last P·V of head i complete
   const uint32_t bar_epi = b0 + 120;         // [2] output staged in shared memory
   uint32_t* tmem_slot = (uint32_t*)(bars + 17);
+  float* sX = (float*)((uint8_t*)bars + 512);   // [head][column half][128 rows]: row maxima, then row sums
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -119,13 +126,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar_vfull + 8 * s, 1);
       mbar_init(bar_vempty + 8 * s, 1);
       mbar_init(bar_sfull + 8 * s, 1);
-      mbar_init(bar_pfull + 8 * s, 128);
+      mbar_init(bar_pfull + 8 * s, 256);
       mbar_init(bar_odone + 8 * s, 1);
-      mbar_init(bar_epi + 8 * s, 128);
+      mbar_init(bar_epi + 8 * s, 256);
     }
     fence_mbar_init();
   }
-  if (warp == 9) {
+  if (warp == 17) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
@@ -135,7 +142,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i aliases S_i[0,64)
 
-  if (warp == 8) {
+  if (warp == 16) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0 && n > 0) {
       tma_prefetch_desc(&tm_q);
@@ -166,7 +173,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                       kvh * HD + c * 64, kt * BKV);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ------------------------------ MMA issuer --------------------------------
     // whole warp, identical values, one elected lane issues (descriptors stay in uniform registers;
     // issuing from a divergent lane-0 branch costs ~130 cycles per MMA on the issuing thread)
@@ -229,37 +236,47 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else {
     // ------------------------------ softmax groups -----------------------------
-    const int i = warp >> 2;        // which head of the pair
-    const int qd = warp & 3;        // TMEM lane quarter
+    // four warps per (head, column half): a thread owns one query row and 64 of the tile's 128 keys;
+    // the two threads of a row meet through shared memory for the row maximum (every tile) and the
+    // row sum (once, at the end)
+    const int i = warp >> 3;          // which head of the pair
+    const int sub = (warp >> 2) & 1;  // which 64 keys of a tile
+    const int qd = warp & 3;          // TMEM lane quarter
     const int row = qd * 32 + lane;
     const int grow = qt * BQ + row;
-    const int lo = p.q_lo[grow], hi = p.q_hi[grow], grp = p.q_grp[grow];
     const uint32_t t_s = tmem_base + ((uint32_t)(qd * 32) << 16) + i * 128;
     const uint32_t t_o = tmem_base + ((uint32_t)(qd * 32) << 16) + 256 + i * 128;
+    float* xmine = sX + (i * 2 + sub) * 128 + row;
+    const float* xother = sX + (i * 2 + (sub ^ 1)) * 128 + row;
     float m_used = -INFINITY;  // max the stored probabilities are relative to (raw score units)
-    float l = 0.f;
-    uint32_t r[128];
+    float l = 0.f;             // this thread's share of the row sum
+    uint32_t r[64];
     bool ok = true;
     for (int j = 0; j < n; ++j) {
       const int ent = list[j];
-      const int* kc = p.k_code + (ent >> 1) * BKV;
-      if (!mbar_wait_spin(bar_sfull + 8 * i, j & 1, KID, 30)) { ok = false; break; }
-      tc_fence_after();
-      // the whole score row lives in registers: one TMEM round trip per tile
-      tmem_ld32(t_s, r);
-      tmem_ld32(t_s + 32, r + 32);
-      tmem_ld32(t_s + 64, r + 64);
-      tmem_ld32(t_s + 96, r + 96);
-      tmem_ld_wait();
-      if (ent & 1) {
+      const int* kc = p.k_code + (ent >> 1) * BKV + sub * 64;
+      bool good = __all_sync(0xffffffffu, mbar_wait_spin(bar_sfull + 8 * i, j & 1, KID, 30));
+      if (good) {
+        tc_fence_after();
+        tmem_ld32(t_s + sub * 64, r);
+        tmem_ld32(t_s + sub * 64 + 32, r + 32);
+        tmem_ld_wait();
+        if (ent & 1) {
+          const int lo = __ldg(p.q_lo + grow), hi = __ldg(p.q_hi + grow), grp = __ldg(p.q_grp + grow);
 #pragma unroll
-        for (int e = 0; e < 128; ++e)
-          if (!key_visible(__ldg(kc + e), lo, hi, grp)) r[e] = 0xff800000u;  // -inf
+          for (int e = 0; e < 64; ++e)
+            if (!key_visible(__ldg(kc + e), lo, hi, grp)) r[e] = 0xff800000u;  // -inf
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 64; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
+        *xmine = mx;
       }
-      float mx = -INFINITY;
-#pragma unroll
-      for (int e = 0; e < 128; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
-      // lazy rescale: keep the old reference max unless the new one is 2^8 larger
+      // the barrier also orders the P stores below after the partner's loads of its score columns
+      if (!named_bar_all(1 + i, 256, good)) { ok = false; break; }
+      float mx = fmaxf(*xmine, *xother);
+      // lazy rescale: keep the old reference max unless the new one is 2^8 larger (both threads of a
+      // row take the same decision: same inputs)
       float alpha = 1.f;
       if (mx > -INFINITY && (m_used == -INFINITY || (mx - m_used) * p.scale_log2 > 8.f)) {
         alpha = (m_used == -INFINITY) ? 0.f : fast_exp2((m_used - mx) * p.scale_log2);
@@ -267,31 +284,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       l *= alpha;
       if (__any_sync(0xffffffffu, alpha != 1.f) && j > 0) {
-        uint32_t ro[32];
+        uint32_t ro[16];
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld32(t_o + c * 32, ro);
+        for (int c = 4 * sub; c < 4 * sub + 4; ++c) {   // this thread's half of the accumulator columns
+          tmem_ld16(t_o + c * 16, ro);
           tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) ro[e] = __float_as_uint(__uint_as_float(ro[e]) * alpha);
-          tmem_st32(t_o + c * 32, ro);
+          for (int e = 0; e < 16; ++e) ro[e] = __float_as_uint(__uint_as_float(ro[e]) * alpha);
+          tmem_st16(t_o + c * 16, ro);
         }
       }
       // probabilities -> bf16 P in TMEM over the S columns; masked scores are -inf -> exactly 0
       const float mref = (m_used == -INFINITY) ? 0.f : m_used * p.scale_log2;
-      // 32 scores at a time, stored as soon as they are packed: keeps the packed values out of the
-      // register budget (the score row itself already takes 128 registers)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
+        uint32_t pk[8];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(r[c * 32 + e]), p.scale_log2, -mref));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(r[c * 32 + e + 1]), p.scale_log2, -mref));
+        for (int e = 0; e < 16; e += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(r[c * 16 + e]), p.scale_log2, -mref));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(r[c * 16 + e + 1]), p.scale_log2, -mref));
           l += p0 + p1;
           pk[e >> 1] = pack_bf16x2(p0, p1);
         }
-        tmem_st16(t_s + c * 16, pk);
+        tmem_st8(t_s + sub * 32 + c * 8, pk);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -299,18 +314,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     // epilogue: O / l -> bf16 -> shared staging (the Q tile of this head) -> TMA store
     if (ok && n > 0) ok = mbar_wait_spin(bar_odone + 8 * i, 0, KID, 31);
+    // row sum over both column halves (every thread takes part in the exchange, also after a failed wait)
+    *xmine = l;
+    ok = named_bar_all(1 + i, 256, ok);
     if (ok) {
+      l += *xother;
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       uint8_t* st = sQ + i * TILE_BYTES;
+      uint32_t ro[32];
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * sub; c < 2 * sub + 2; ++c) {
         if (n > 0) {
-          tmem_ld32(t_o + c * 32, r);
+          tmem_ld32(t_o + c * 32, ro);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = 0u;
+          for (int e = 0; e < 32; ++e) ro[e] = 0u;
         }
         uint8_t* half = st + (c >> 1) * HALF_BYTES;
 #pragma unroll
@@ -318,17 +338,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           uint32_t a[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            a[e] = pack_bf16x2(__uint_as_float(r[8 * v + 2 * e]) * inv,
-                               __uint_as_float(r[8 * v + 2 * e + 1]) * inv);
+            a[e] = pack_bf16x2(__uint_as_float(ro[8 * v + 2 * e]) * inv,
+                               __uint_as_float(ro[8 * v + 2 * e + 1]) * inv);
           *reinterpret_cast<uint4*>(half + sw128_offset(row, (c & 1) * 4 + v)) =
               make_uint4(a[0], a[1], a[2], a[3]);
         }
       }
-      p.lse[(size_t)(h0 + i) * p.nq_pad + grow] =
-          l > 0.f ? m_used * p.scale + __logf(l) : -INFINITY;
+      if (sub == 0)
+        p.lse[(size_t)(h0 + i) * p.nq_pad + grow] = l > 0.f ? m_used * p.scale + __logf(l) : -INFINITY;
       fence_proxy_async_smem();
       mbar_arrive(bar_epi + 8 * i);
-      if (row == 0) {
+      if (row == 0 && sub == 0) {
         if (mbar_wait_spin(bar_epi + 8 * i, 0, KID, 32)) {
 #pragma unroll
           for (int c = 0; c < 2; ++c)
@@ -347,7 +367,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 9) {
+  if (warp == 17) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
