@@ -70,6 +70,13 @@ SECTIONS: dict[str, tuple[F, ...]] = {
         F("num_experts", OPT_INT, None, ext=True),
         F("num_experts_per_token", OPT_INT, None, ext=True),
         F("moe_intermediate_size", OPT_INT, None, ext=True),
+        F("full_attention_interval", OPT_INT, None, ext=True,
+          help="hybrid decoders: every n-th layer is softmax attention, the others are linear attention"),
+        F("linear_num_key_heads", OPT_INT, None, ext=True),
+        F("linear_num_value_heads", OPT_INT, None, ext=True),
+        F("linear_key_head_dim", OPT_INT, None, ext=True),
+        F("linear_value_head_dim", OPT_INT, None, ext=True),
+        F("linear_conv_kernel", OPT_INT, None, ext=True),
         F("random_init", bool, False, ext=True, help="build from the shape fields, load no weights"),
     ),
     "objective": (

@@ -30,6 +30,14 @@ class ModelConfig:
     moe_intermediate_size: int = 0
     sliding_window: int | None = None
     family: str = "causal_lm"
+    # hybrid decoders (family qwen3_8): every `full_attention_interval`-th layer is gated softmax
+    # attention, the others are Gated DeltaNet linear-attention layers (0 = no linear layers)
+    full_attention_interval: int = 0
+    linear_num_key_heads: int = 0
+    linear_num_value_heads: int = 0
+    linear_key_head_dim: int = 0
+    linear_value_head_dim: int = 0
+    linear_conv_kernel: int = 4
 
     @property
     def q_dim(self) -> int:
@@ -47,9 +55,44 @@ class ModelConfig:
     def is_moe(self) -> bool:
         return self.num_experts > 0
 
+    @property
+    def is_hybrid(self) -> bool:
+        return self.full_attention_interval > 0
+
+    def layer_kind(self, i: int) -> str:
+        """"full_attention" or "linear_attention" for layer i (every interval-th layer is full)."""
+        if not self.is_hybrid or (i + 1) % self.full_attention_interval == 0:
+            return "full_attention"
+        return "linear_attention"
+
+    @property
+    def linear_key_dim(self) -> int:
+        return self.linear_num_key_heads * self.linear_key_head_dim
+
+    @property
+    def linear_value_dim(self) -> int:
+        return self.linear_num_value_heads * self.linear_value_head_dim
+
+    @property
+    def linear_conv_channels(self) -> int:
+        return 2 * self.linear_key_dim + self.linear_value_dim
+
+    @property
+    def linear_in_dim(self) -> int:
+        """Rows of the fused input projection of a linear-attention layer: q | k | v | z | b | a, padded to 64."""
+        n = self.linear_conv_channels + self.linear_value_dim + 2 * self.linear_num_value_heads
+        return (n + 63) // 64 * 64
+
     def layer_params(self) -> int:
         h = self.hidden_size
         attn = h * self.qkv_dim + self.q_dim * h + (2 * self.head_dim if self.qk_norm else 0)
+        if self.is_hybrid:
+            full = attn + h * self.q_dim   # output gate
+            lin = (h * self.linear_in_dim + self.linear_value_dim * h
+                   + self.linear_conv_channels * (self.linear_conv_kernel + 1)
+                   + 2 * self.linear_num_value_heads + self.linear_value_head_dim)
+            n_full = sum(self.layer_kind(i) == "full_attention" for i in range(self.num_layers))
+            attn = (n_full * full + (self.num_layers - n_full) * lin) // max(self.num_layers, 1)
         if self.is_moe:
             ffn = self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
         else:
@@ -109,7 +152,8 @@ def model_config_from_run_spec(spec) -> ModelConfig:
     over = {}
     for name in ("vocab_size", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
                  "intermediate_size", "rope_theta", "mask_token_id", "num_experts", "num_experts_per_token",
-                 "moe_intermediate_size"):
+                 "moe_intermediate_size", "full_attention_interval", "linear_num_key_heads",
+                 "linear_num_value_heads", "linear_key_head_dim", "linear_value_head_dim", "linear_conv_kernel"):
         v = getattr(m, name)
         if v is not None:
             over[name] = v
@@ -123,6 +167,17 @@ def model_config_from_run_spec(spec) -> ModelConfig:
         cfg = replace(cfg, mask_token_id=cfg.vocab_size - 1)
     return cfg
 
+PRESETS["synthetic:tiny-qwen3_8"] = ModelConfig(vocab_size=1024, hidden_size=128, num_layers=4, num_attention_heads=4,
+                                                num_key_value_heads=2, head_dim=32, intermediate_size=256,
+                                                mask_token_id=1023, family="qwen3_8", full_attention_interval=4,
+                                                linear_num_key_heads=2, linear_num_value_heads=4,
+                                                linear_key_head_dim=16, linear_value_head_dim=16)
+PRESETS["synthetic:tiny-qwen3_8-hd128"] = ModelConfig(vocab_size=2048, hidden_size=256, num_layers=2,
+                                                      num_attention_heads=2, num_key_value_heads=2, head_dim=128,
+                                                      intermediate_size=512, mask_token_id=2047, family="qwen3_8",
+                                                      full_attention_interval=2, linear_num_key_heads=2,
+                                                      linear_num_value_heads=4, linear_key_head_dim=64,
+                                                      linear_value_head_dim=64)
 PRESETS["synthetic:tiny-moe"] = ModelConfig(vocab_size=1024, hidden_size=128, num_layers=2, num_attention_heads=4,
                                             num_key_value_heads=2, head_dim=64, intermediate_size=0, num_experts=8,
                                             num_experts_per_token=2, moe_intermediate_size=96, mask_token_id=1023,

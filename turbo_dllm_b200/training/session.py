@@ -64,7 +64,17 @@ class TrainingSession:
             self._init_dflash(seed, runtime, host_staged_data)
             return
         ep = runtime.expert_parallel_size if runtime is not None else 1
-        if self.cfg.is_moe:
+        if self.cfg.is_hybrid:
+            from ..models.hybrid import HybridBlockDiffusionTransformer
+
+            if runtime is not None and (runtime.tensor_parallel_size > 1 or runtime.context_parallel_size > 1):
+                raise ValueError("the hybrid (qwen3_8) family runs on data-parallel and block-parallel ranks; "
+                                 "tensor and context parallelism of its linear-attention layers are not built")
+            self.model = HybridBlockDiffusionTransformer(
+                self.cfg, dtype=self.dtype, device=self.device,
+                activation_checkpointing=spec.training.activation_checkpointing,
+                activation_offload=self._want_activation_offload(), seed=seed)
+        elif self.cfg.is_moe:
             from ..models.moe import MoEBlockDiffusionTransformer
 
             self.model = MoEBlockDiffusionTransformer(
@@ -86,7 +96,7 @@ class TrainingSession:
         if spec.adapter.type == "lora":
             from ..adapters.lora import apply_lora
 
-            if self.cfg.is_moe or getattr(self.model, "tp", None) is not None:
+            if self.cfg.is_moe or self.cfg.is_hybrid or getattr(self.model, "tp", None) is not None:
                 raise ValueError("LoRA adapters support dense models on one tensor-parallel rank")
             self.lora = apply_lora(self.model, rank=spec.adapter.rank, alpha=spec.adapter.alpha,
                                    dropout=spec.adapter.dropout, targets=spec.adapter.targets or ("attention", "mlp"),
@@ -115,6 +125,10 @@ class TrainingSession:
             self.data = build_artifact_runtime(spec, device=self.device, dp_rank=dp_rank, dp_size=self.dp_size)
         self.layout = self._build_layout()
         self.attend = self._build_attention()
+        if self.cfg.is_hybrid:
+            from ..models.hybrid import BlockRows
+
+            self.attend.block_rows = BlockRows(self.layout, spec.model.seq_len)
         o = spec.optimizer
         okw = dict(lr=o.lr, betas=(o.adam_beta1, o.adam_beta2), eps=o.adam_eps, weight_decay=o.weight_decay)
         self.expert_optimizer = None
