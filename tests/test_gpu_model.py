@@ -5,24 +5,28 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _spec(dtype, objective="fast_dllm_v2"):
+def _spec(dtype, objective="fast_dllm_v2", model="synthetic:tiny-hd128"):
     from turbo_dllm_b200.config.run_spec import RunSpec
 
     return RunSpec.from_mapping({
-        "model": {"id": "synthetic:tiny-hd128", "seq_len": 256, "dtype": dtype},
+        "model": {"id": model, "seq_len": 256, "dtype": dtype},
         "objective": {"name": objective, "block_size": 32, "noise_schedule_epsilon": 0.1},
         "training": {"batch_size": 2, "steps": 2, "activation_checkpointing": True},
         "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
         "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate()
 
 
-@pytest.mark.parametrize("objective", ["fast_dllm_v2", "standard_block_diffusion"])
-def test_loss_and_grads_match_cpu_reference(objective):
+@pytest.mark.parametrize("objective,model", [("fast_dllm_v2", "synthetic:tiny-hd128"),
+                                             ("standard_block_diffusion", "synthetic:tiny-hd128"),
+                                             ("fast_dllm_v2", "synthetic:tiny-qwen3_8-hd128")])
+def test_loss_and_grads_match_cpu_reference(objective, model):
+    """The last case is the hybrid family: Gated DeltaNet layers (projections on the tcgen05 GEMM,
+    recurrence as batched products) and a gated softmax-attention layer."""
     from turbo_dllm_b200.kernels import native
     from turbo_dllm_b200.training.session import TrainingSession
 
-    gpu = TrainingSession(_spec("bf16", objective), device="cuda")
-    cpu = TrainingSession(_spec("fp32", objective), device="cpu")
+    gpu = TrainingSession(_spec("bf16", objective, model), device="cuda")
+    cpu = TrainingSession(_spec("fp32", objective, model), device="cpu")
     cpu.model.flat.data.copy_(gpu.model.flat.data.float().cpu())
     batch = gpu.data.next_batch()
     cb = gpu.objective.corrupt(batch.input_ids)

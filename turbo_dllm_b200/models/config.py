@@ -173,7 +173,7 @@ PRESETS["synthetic:tiny-qwen3_8"] = ModelConfig(vocab_size=1024, hidden_size=128
                                                 linear_num_key_heads=2, linear_num_value_heads=4,
                                                 linear_key_head_dim=16, linear_value_head_dim=16)
 PRESETS["synthetic:tiny-qwen3_8-hd128"] = ModelConfig(vocab_size=2048, hidden_size=256, num_layers=2,
-                                                      num_attention_heads=2, num_key_value_heads=2, head_dim=128,
+                                                      num_attention_heads=2, num_key_value_heads=1, head_dim=128,
                                                       intermediate_size=512, mask_token_id=2047, family="qwen3_8",
                                                       full_attention_interval=2, linear_num_key_heads=2,
                                                       linear_num_value_heads=4, linear_key_head_dim=64,
