@@ -1,0 +1,207 @@
+"""DFlash2 drafter: block-local dynamic convolution, D-PACE weights, cross-entropy with top-k
+candidates through the frozen head, candidate selector, and a training step (CPU, fp32)."""
+import math
+
+import pytest
+import torch
+
+from turbo_dllm_b200.ops.dflash2 import (dpace_weight, frozen_linear_ce_topk, grouped_dynamic_conv,
+                                          selector_schedule_factor, transform_logits)
+
+
+def test_grouped_dynamic_conv_against_a_direct_loop():
+    torch.manual_seed(0)
+    bs, H, taps, groups, nb = 4, 6, 3, 2, 3
+    x = torch.randn(nb * bs, H)
+    dyn = torch.randn(nb * bs, taps, groups) * 0.3
+    base = torch.randn(taps, H)
+    got = grouped_dynamic_conv(x, dyn, base, bs)
+    want = torch.zeros_like(x)
+    for r in range(nb * bs):
+        t = r % bs
+        for i in range(taps):
+            if t - i < 0:
+                continue        # nothing in front of the block start
+            for c in range(H):
+                want[r, c] += (base[i, c] + dyn[r, i, c // (H // groups)]) * x[r - i, c]
+    assert torch.allclose(got, want, atol=1e-5)
+    ident = torch.zeros(taps, H)
+    ident[0] = 1.0
+    assert torch.allclose(grouped_dynamic_conv(x, torch.zeros_like(dyn), ident, bs), x)
+    with pytest.raises(ValueError):
+        grouped_dynamic_conv(x[:-1], dyn[:-1], base, bs)
+
+
+def test_dpace_weights():
+    p = torch.tensor([[0.9, 0.5, 0.2, 0.7]])
+    m = torch.tensor([[1.0, 1.0, 0.0, 1.0]])
+    a = 0.5
+    smooth = [(1 - a) * 0.9 + a, (1 - a) * 0.5 + a, 1.0, (1 - a) * 0.7 + a]
+    prefix = [smooth[0], smooth[0] * smooth[1], smooth[0] * smooth[1], smooth[0] * smooth[1] * smooth[3]]
+    suffix = [prefix[0] + prefix[1] + prefix[3], prefix[1] + prefix[3], prefix[3], prefix[3]]
+    assert torch.allclose(dpace_weight(p, m, alpha=a, kind="dpace-cumulative-confidence-only"), torch.tensor([prefix]))
+    assert torch.allclose(dpace_weight(p, m, alpha=a, kind="dpace"), torch.tensor([suffix]))
+    cont = [s / q for s, q in zip(suffix, prefix)]
+    assert torch.allclose(dpace_weight(p, m, alpha=a, kind="dpace-continuation-value-only"), torch.tensor([cont]))
+    with pytest.raises(ValueError):
+        dpace_weight(p, m, alpha=a, kind="other")
+
+
+def test_selector_schedule():
+    f = lambda s: selector_schedule_factor(s, 100, 0.1, 0.2)
+    assert f(0) == 0.0 and f(9) == 0.0
+    assert f(10) == pytest.approx(1 / 20) and f(19) == pytest.approx(0.5) and f(29) == 1.0 and f(99) == 1.0
+    assert selector_schedule_factor(0, 100, 0.0, 0.0) == 1.0
+
+
+@pytest.mark.parametrize("softcap,mult", [(None, 1.0), (5.0, 0.5)])
+def test_frozen_linear_ce_topk_matches_dense_logits(softcap, mult):
+    torch.manual_seed(1)
+    n, H, V, k = 37, 16, 203, 4
+    h = torch.randn(n, H, requires_grad=True)
+    w = torch.randn(V, H)
+    labels = torch.randint(0, V, (n,))
+    wts = torch.rand(n)
+    ce_sum, ce, prob, topz, ids = frozen_linear_ce_topk(h, w, labels, top_k=k, vocab_block_size=64,
+                                                        output_multiplier=mult, logit_softcap=softcap,
+                                                        loss_weights=wts)
+    hr = h.detach().clone().requires_grad_(True)
+    z = transform_logits(hr @ w.t(), mult, softcap)
+    ce_ref = torch.nn.functional.cross_entropy(z, labels, reduction="none")
+    assert torch.allclose(ce, ce_ref.detach(), atol=1e-4)
+    assert torch.allclose(prob, torch.exp(-ce_ref.detach()), atol=1e-5)
+    zr, ir = z.topk(k, dim=-1)
+    assert torch.equal(ids, ir)
+    assert torch.allclose(topz, zr.detach(), atol=1e-4)
+    assert not ce.requires_grad and not prob.requires_grad and topz.requires_grad
+    g = torch.randn(n, k)
+    (ce_sum + (topz * g).sum()).backward()
+    ((ce_ref * wts).sum() + (zr * g).sum()).backward()
+    assert torch.allclose(h.grad, hr.grad, atol=1e-4, rtol=1e-3)
+
+
+def _models():
+    from turbo_dllm_b200.models.config import PRESETS
+    from turbo_dllm_b200.models.dflash import DFlashDraftModel
+    from turbo_dllm_b200.models.dflash2 import DFlash2DraftModel
+
+    cfg = PRESETS["synthetic:tiny-qwen3"]
+    kw = dict(target_hidden=32, num_target_layers=2, dtype=torch.float32, seed=3, init_std=0.05)
+    v1 = DFlashDraftModel(cfg, **kw)
+    v2 = DFlash2DraftModel(cfg, block_size=8, conv_kernel_size=3, conv_group_size=64, selector_rank=6,
+                           selector_top_k=4, verifier_vocab_size=cfg.vocab_size, **kw)
+    return cfg, v1, v2
+
+
+def _draft_inputs(cfg, bs=8, blocks=3, ctx=24):
+    from turbo_dllm_b200.ops.attention import MaskLayout
+
+    g = torch.Generator().manual_seed(4)
+    nd = bs * blocks
+    emb = torch.randn(nd, cfg.hidden_size, generator=g)
+    feats = torch.randn(ctx, 64, generator=g)
+    starts = torch.tensor([4, 10, 20])
+    pos_d = (starts[:, None] + torch.arange(bs)[None]).reshape(-1)
+    pos_c = torch.arange(ctx)
+    i32 = torch.int32
+    q_lo = torch.zeros(nd, dtype=i32)
+    q_hi = starts.repeat_interleave(bs).to(i32)
+    q_grp = -(torch.arange(blocks).repeat_interleave(bs) + 1).to(i32)
+    mask = MaskLayout(q_lo, q_hi, q_grp, torch.cat([q_grp, pos_c.to(i32)]))
+    return emb, feats, pos_d, pos_c, mask
+
+
+def test_fresh_dflash2_equals_dflash_and_convolutions_train():
+    cfg, v1, v2 = _models()
+    with torch.no_grad():
+        for name, p in v1.flat.params.items():
+            v2.flat.params[name].copy_(p)
+    emb, feats, pos_d, pos_c, mask = _draft_inputs(cfg)
+    with torch.no_grad():
+        a, b = v1(emb, feats, pos_d, pos_c, mask), v2(emb, feats, pos_d, pos_c, mask)
+    assert torch.allclose(a, b, atol=1e-5)
+    v2.flat.zero_grad()
+    out = v2(emb, feats, pos_d, pos_c, mask)
+    out.square().sum().backward()
+    v2.flat.collect_grads()
+    for leaf in ("attn_conv_base", "attn_conv_proj", "mlp_conv_base", "mlp_conv_proj"):
+        assert v2.flat.params[f"layers.0.{leaf}"].main_grad.abs().sum() > 0, leaf
+    # a non-zero correction changes the output, and only inside blocks: perturb the first block's input
+    with torch.no_grad():
+        v2.flat.params["layers.0.attn_conv_base"][0, 1] = 0.5
+        c = v2(emb, feats, pos_d, pos_c, mask)
+    assert not torch.allclose(b, c, atol=1e-4)
+
+
+def test_candidate_selector_lattice_and_greedy_path():
+    cfg, _, v2 = _models()
+    sel = v2.candidate_selector
+    with torch.no_grad():
+        sel.successor.normal_(0, 0.5)
+    b, L, k = 2, 5, sel.top_k
+    g = torch.Generator().manual_seed(6)
+    cand = torch.stack([torch.randperm(cfg.vocab_size, generator=g)[:k] for _ in range(b * L)]).view(b, L, k)
+    unary = torch.randn(b, L, k, generator=g)
+    hid = torch.randn(b, L, cfg.hidden_size, generator=g)
+    anchor = torch.randint(0, cfg.vocab_size, (b,), generator=g)
+    lat = sel.build_lattice(candidate_ids=cand, unary_logits=unary, hidden_states=hid, anchor_token_ids=anchor)
+    assert lat.shape == (b, L, k, k)
+    # row p of the lattice at position t = scores after predecessor candidate p of position t-1
+    t, p = 3, 2
+    s = sel.score_candidates(candidate_ids=cand[:, t], unary_logits=unary[:, t], hidden_states=hid[:, t],
+                             predecessor_ids=cand[:, t - 1, p])
+    assert torch.allclose(lat[:, t, p], s, atol=1e-5)
+    s0 = sel.score_candidates(candidate_ids=cand[:, 0], unary_logits=unary[:, 0], hidden_states=hid[:, 0],
+                              predecessor_ids=anchor)
+    assert torch.allclose(lat[:, 0, 0], s0, atol=1e-5)
+    path = sel.greedy_path(candidate_ids=cand, unary_logits=unary, hidden_states=hid, anchor_token_ids=anchor)
+    assert path.shape == (b, L)
+    assert torch.equal(path[:, 0], cand[:, 0].gather(1, s0.argmax(-1, keepdim=True))[:, 0])
+    assert all(int(path[i, j]) in cand[i, j].tolist() for i in range(b) for j in range(L))
+
+
+@pytest.mark.parametrize("loss,lk", [("dpace", None), ("dflash", "lambda"), ("dpace-continuation-value-only", "tv")])
+def test_dflash2_training_step(loss, lk):
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-qwen3", "seq_len": 128, "dtype": "fp32", "family": "dflash",
+                  "verifier_id": "synthetic:tiny-qwen3", "target_layer_ids": [0, 2], "max_layers": 2,
+                  "dflash2_conv_kernel_size": 3, "dflash2_conv_group_size": 64, "dflash2_selector_rank": 8,
+                  "dflash2_selector_top_k": 4},
+        "objective": {"name": "dflash_distillation", "block_size": 8, "max_anchors": 6, "decay_gamma": 4.0,
+                      "dflash_loss": loss, "lk_loss_type": lk, "selector_loss_alpha": 0.5,
+                      "dflash_vocab_block_size": 300},
+        "data": {"target_features": "online"}, "training": {"batch_size": 2, "steps": 4},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
+        "optimizer": {"lr": 2e-3, "gradient_clip_norm": 1.0}}).validate()
+    s = TrainingSession(spec, device="cpu")
+    from turbo_dllm_b200.models.dflash2 import DFlash2DraftModel
+
+    assert isinstance(s.model, DFlash2DraftModel)
+    before = s.model.flat.data.clone()
+    losses = []
+    for _ in range(3):
+        r = s.step()
+        losses.append(float(r.loss_sum))
+    assert all(math.isfinite(x) and x > 0 for x in losses)
+    moved = lambda n: (s.model.flat.params[n] - before[s.model.flat.offsets[n][0]:][: s.model.flat.params[n].numel()]
+                       .view_as(s.model.flat.params[n])).abs().sum() > 0
+    assert moved("selector_proj") and moved("layers.0.attn_conv_proj") and moved("layers.0.w_q")
+    m = s.task.last_objective_metrics
+    assert 0.0 <= float(m["selector_coverage"]) <= 1.0 and 0.0 < float(m["target_probability"]) < 1.0
+
+
+def test_dpace_loss_needs_the_dflash2_drafter():
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "family": "dflash",
+                  "verifier_id": "synthetic:tiny-qwen3", "target_layer_ids": [0]},
+        "objective": {"name": "dflash_distillation", "block_size": 8, "dflash_loss": "dpace"},
+        "data": {"target_features": "online"}, "training": {"batch_size": 1, "steps": 1},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}).validate()
+    with pytest.raises(ValueError):
+        TrainingSession(spec, device="cpu")

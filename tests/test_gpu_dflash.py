@@ -51,3 +51,38 @@ def test_dflash_training_step_matches_cpu_loss():
     assert lg == lg and lg > 0
     for _ in range(2):
         assert float(g.step().loss_sum) > 0
+
+
+def test_dflash2_training_step_on_gpu():
+    """DFlash2 drafter (dynamic convolutions, candidate selector, D-PACE weights) in bf16 on the device:
+    finite positive loss, gradients reach the selector and the convolution projections, steps keep running."""
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    def spec(dtype):
+        return RunSpec.from_mapping({
+            "model": {"id": "synthetic:tiny-hd128", "seq_len": 512, "dtype": dtype, "family": "dflash",
+                      "verifier_id": "synthetic:tiny-hd128", "target_layer_ids": [0, 1],
+                      "dflash2_conv_kernel_size": 4, "dflash2_conv_group_size": 64, "dflash2_selector_rank": 16,
+                      "dflash2_selector_top_k": 8},
+            "objective": {"name": "dflash_distillation", "block_size": 16, "max_anchors": 24, "decay_gamma": 4.0,
+                          "dflash_loss": "dpace", "dflash_vocab_block_size": 1024},
+            "data": {"target_features": "online"}, "training": {"batch_size": 2, "steps": 3},
+            "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
+            "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate()
+
+    g = TrainingSession(spec("bf16"), device="cuda")
+    batch = g.data.next_batch()
+    g.model.flat.zero_grad()
+    lg, ng, dg = g.task.forward_backward(batch)
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    assert float(lg) == float(lg) and float(lg) > 0 and ng > 0
+    g.model.flat.collect_grads()
+    assert float(g.model.flat.params["selector_proj"].main_grad.float().abs().sum()) > 0
+    assert float(g.model.flat.params["layers.0.attn_conv_proj"].main_grad.float().abs().sum()) > 0
+    for _ in range(2):
+        assert float(g.step().loss_sum) > 0
+    torch.cuda.synchronize()
+    native.raise_on_device_error()

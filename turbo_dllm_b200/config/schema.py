@@ -70,6 +70,10 @@ SECTIONS: dict[str, tuple[F, ...]] = {
         F("num_experts", OPT_INT, None, ext=True),
         F("num_experts_per_token", OPT_INT, None, ext=True),
         F("moe_intermediate_size", OPT_INT, None, ext=True),
+        F("dflash2_conv_kernel_size", OPT_INT, None),
+        F("dflash2_conv_group_size", OPT_INT, None),
+        F("dflash2_selector_rank", OPT_INT, None),
+        F("dflash2_selector_top_k", OPT_INT, None),
         F("full_attention_interval", OPT_INT, None, ext=True,
           help="hybrid decoders: every n-th layer is softmax attention, the others are linear attention"),
         F("linear_num_key_heads", OPT_INT, None, ext=True),
@@ -98,7 +102,8 @@ SECTIONS: dict[str, tuple[F, ...]] = {
         F("anchor_sampling", str, "uniform", choices=("uniform", "locality")),
         F("anchor_group_size", int, 0),
         F("sample_from_anchor", bool, False),
-        F("dflash_loss", str, "speculators_kl", choices=("speculators_kl", "paper_ce", "dpace")),
+        F("dflash_loss", str, "speculators_kl", choices=("speculators_kl", "paper_ce", "dflash", "dpace", "dpace-cumulative-confidence-only",
+                   "dpace-continuation-value-only")),
         F("decay_gamma", OPT_FLOAT, None),
         F("dpace_alpha", float, 0.5),
         F("lk_loss_type", OPT_STR, None),

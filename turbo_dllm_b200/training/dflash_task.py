@@ -1,8 +1,15 @@
 """DFlash drafter-distillation task: frozen target forward → anchors and drafting blocks →
 draft forward over [draft rows ; conditioned context] → soft-label KL through the frozen head.
 
+With `model.dflash2_*` set the drafter is the DFlash2 architecture (block-local dynamic convolutions,
+candidate selector) and the losses `dflash` / `dpace*` apply: hard-label cross-entropy through the
+frozen head with position weights that are either the sampled decay weights (`dflash`) or the D-PACE
+weights computed from the drafter's own label probabilities, optionally mixed with a total-variation
+term (`lk_loss_type`), plus the selector's cross-entropy over the head's top-k candidates.
+
 Counterparts: DFlashTrainingTask (dllm_parallel/core/models/backbones/dflash/training.py:29-197),
-`distributed_dflash_loss` (dllm_parallel/core/models/backbones/dflash/model.py:862-956).
+`distributed_dflash_loss` (dllm_parallel/core/models/backbones/dflash/model.py:862-956,
+dllm_parallel/core/models/backbones/dflash/dflash2.py:552-701).
 """
 from __future__ import annotations
 
@@ -29,8 +36,29 @@ class DFlashTask:
         if m.max_layers is not None and spec.data.target_features == "synthetic":
             pass
         self.target = FrozenTarget(target_cfg, tuple(m.target_layer_ids), dtype=dtype, device=device, seed=seed + 1)
-        self.model = DFlashDraftModel(cfg, target_hidden=target_cfg.hidden_size,
-                                      num_target_layers=len(m.target_layer_ids), dtype=dtype, device=device, seed=seed)
+        self.is_dflash2 = bool(m.dflash2_conv_kernel_size or m.dflash2_selector_rank)
+        if self.is_dflash2:
+            from ..models.dflash2 import DFlash2DraftModel
+
+            self.model = DFlash2DraftModel(
+                cfg, target_hidden=target_cfg.hidden_size, num_target_layers=len(m.target_layer_ids),
+                block_size=o.block_size or 16, conv_kernel_size=m.dflash2_conv_kernel_size or 1,
+                conv_group_size=m.dflash2_conv_group_size or cfg.hidden_size,
+                selector_rank=m.dflash2_selector_rank or 1, selector_top_k=m.dflash2_selector_top_k or 1,
+                verifier_vocab_size=target_cfg.vocab_size, dtype=dtype, device=device, seed=seed)
+        else:
+            self.model = DFlashDraftModel(cfg, target_hidden=target_cfg.hidden_size,
+                                          num_target_layers=len(m.target_layer_ids), dtype=dtype, device=device,
+                                          seed=seed)
+        from ..ops.dflash2 import DPACE_LOSSES
+
+        if o.dflash_loss in ("dflash",) + DPACE_LOSSES and not self.is_dflash2:
+            raise ValueError(f"objective.dflash_loss={o.dflash_loss} needs the DFlash2 drafter "
+                             "(model.dflash2_conv_kernel_size, model.dflash2_selector_rank, ...)")
+        if o.lk_loss_type not in (None, "alpha", "lambda", "tv"):
+            raise ValueError("objective.lk_loss_type must be unset, alpha, lambda or tv")
+        self.effective_selector_loss_alpha = float(o.selector_loss_alpha)
+        self.last_objective_metrics: dict = {}
         max_anchors = o.max_anchors or max(m.seq_len // (o.block_size or 16) // 2, 1)
         self.objective = DFlashObjectiveRuntime(
             block_size=o.block_size or 16, max_anchors=max_anchors, mask_token_id=target_cfg.mask_token_id,
@@ -38,6 +66,14 @@ class DFlashTask:
             anchor_group_size=o.anchor_group_size, sample_from_anchor=o.sample_from_anchor, decay_gamma=o.decay_gamma)
         self.loss_kind = o.dflash_loss
         self.synthetic = spec.data.target_features == "synthetic"
+
+    def set_optimizer_step(self, step: int, total_steps: int) -> None:
+        """Warm-up and ramp of the selector loss (fractions of the run's optimizer steps)."""
+        from ..ops.dflash2 import selector_schedule_factor
+
+        o = self.spec.objective
+        self.effective_selector_loss_alpha = float(o.selector_loss_alpha) * selector_schedule_factor(
+            int(step), int(total_steps), float(o.selector_warmup_ratio), float(o.selector_ramp_ratio))
 
     def target_features(self, input_ids: torch.Tensor) -> TargetFeatures:
         if self.synthetic:  # random features of the right shape: exercises the drafter without a target pass
@@ -72,6 +108,11 @@ class DFlashTask:
         wr = w.index_select(0, rows)
         if self.loss_kind == "speculators_kl":
             loss_sum, _ = frozen_linear_kl(h_s, h_t, self.target.lm_head, wr)
+        elif self.is_dflash2 and self.loss_kind != "paper_ce":
+            tgt_all = ids.reshape(-1).index_select(0, (ob.target_token_positions + seq_off).reshape(-1))
+            loss_sum, denom = self._dflash2_loss(h_s, rows, tgt_all, sup, ob.position_weights.reshape(-1))
+            (loss_sum / denom).backward()
+            return loss_sum.detach(), int(rows.numel()), denom
         else:  # paper_ce: hard labels = the data token at the target position
             tgt = (ob.target_token_positions + seq_off).reshape(-1).index_select(0, rows)
             labels = ids.reshape(-1).index_select(0, tgt)
@@ -79,3 +120,56 @@ class DFlashTask:
         denom = wr.sum().clamp_min(1.0) if denominator is None else denominator
         (loss_sum / denom).backward()
         return loss_sum.detach(), int(rows.numel()), denom
+
+    def _dflash2_loss(self, hidden, rows, targets_all, supervised, position_weights):
+        """hidden [n, H]: supervised draft rows `rows`; targets_all / supervised / position_weights:
+        per draft row in block order. Returns (loss numerator with gradient, detached denominator)."""
+        from ..ops.dflash2 import DPACE_LOSSES, dpace_weight, frozen_linear_ce_topk
+
+        o, model = self.spec.objective, self.model
+        bs = self.objective.block_size
+        sel = model.candidate_selector
+        selector_on = bool(model.selector_objective_enabled) and self.effective_selector_loss_alpha > 0.0
+        labels = targets_all.index_select(0, rows)
+        head = self.target.lm_head
+        kw = dict(top_k=sel.top_k if selector_on else 1, vocab_block_size=int(o.dflash_vocab_block_size),
+                  output_multiplier=model.output_multiplier, logit_softcap=model.final_logit_softcapping)
+        with torch.no_grad():      # label probabilities first: the position weights depend on them
+            _, _, prob, _, _ = frozen_linear_ce_topk(hidden.detach(), head, labels, **kw)
+        mask = supervised.reshape(-1, bs).float()
+        full_p = torch.zeros_like(mask).view(-1).index_copy_(0, rows, prob).view(-1, bs)
+        if self.loss_kind == "dflash":
+            weights = mask * position_weights.reshape(-1, bs).float()
+        else:
+            weights = mask * dpace_weight(full_p, mask, alpha=float(o.dpace_alpha), kind=self.loss_kind)
+        w_rows = weights.reshape(-1).index_select(0, rows)
+        # cross-entropy / total-variation mix. d(1 - p)/dh = p * d(ce)/dh, so the total-variation
+        # term is a cross-entropy whose row weights carry the detached probability.
+        ce_share = 1.0
+        if o.lk_loss_type == "tv":
+            ce_share = 0.0
+        elif o.lk_loss_type == "lambda":
+            acceptance = (full_p * mask).sum() / mask.sum().clamp_min(1.0)
+            ce_share = float(o.kl_scale) * float(torch.exp(-float(o.kl_decay) * acceptance))
+        eff = w_rows * (ce_share + (1.0 - ce_share) * prob)
+        grad_carrier, ce, _, unary, cand = frozen_linear_ce_topk(hidden, head, labels, loss_weights=eff, **kw)
+        value = (ce_share * ce + (1.0 - ce_share) * (1.0 - prob)) * w_rows
+        token_num = value.sum() + (grad_carrier - grad_carrier.detach())
+        selector_num = token_num.new_zeros(())
+        covered = torch.zeros_like(labels, dtype=torch.bool)
+        if selector_on:
+            blocks = targets_all.reshape(-1, bs)
+            predecessor = torch.cat([blocks[:, :1], blocks[:, :-1]], dim=-1).reshape(-1).index_select(0, rows)
+            stop = bool(o.selector_stop_gradient)
+            matches = cand.eq(labels[:, None])
+            covered = matches.any(-1)
+            scores = sel.score_candidates(candidate_ids=cand, unary_logits=unary.detach() if stop else unary,
+                                          hidden_states=hidden.detach() if stop else hidden,
+                                          predecessor_ids=predecessor)
+            sel_ce = torch.nn.functional.cross_entropy(scores.float(), matches.long().argmax(-1), reduction="none")
+            sel_w = w_rows * covered.float()
+            selector_num = (sel_ce * sel_w).sum()
+            self.last_objective_metrics["selector_loss"] = (selector_num.detach() / sel_w.sum().clamp_min(1.0))
+        self.last_objective_metrics.update(target_probability=prob.mean(), selector_coverage=covered.float().mean())
+        return token_num + self.effective_selector_loss_alpha * selector_num, w_rows.sum().clamp_min(
+            torch.finfo(torch.float32).tiny).detach()

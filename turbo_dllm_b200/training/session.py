@@ -374,6 +374,7 @@ class TrainingSession:
             # gradients are averaged over micro-batches and data-parallel ranks
             scale = float(len(batches) * self.dp_size)
             denom = 0.0
+            self.task.set_optimizer_step(self.steps_done, max(int(spec.training.steps or 1), 1))
             for b in batches:
                 ls, n, d = self.task.forward_backward(b)
                 total += ls.float() / d.float() / scale
