@@ -12,7 +12,7 @@ import torch.nn.functional as F
 
 from turbo_dllm_b200.models.config import PRESETS
 from turbo_dllm_b200.models.dense import LocalAttention
-from turbo_dllm_b200.models.hybrid import BlockRows, HybridBlockDiffusionTransformer
+from turbo_dllm_b200.models.hybrid import BlockRows, HybridBlockDiffusionTransformer, _HeadShard
 from turbo_dllm_b200.ops.gated_delta import (causal_conv_reference, expand_key_heads, gated_delta_reference,
                                               gated_rmsnorm, gdn_gate, l2_normalize)
 from turbo_dllm_b200.ops.rope import qk_norm_rope
@@ -42,7 +42,7 @@ def oracle_forward(model, tokens, positions, block_size):
         y = _rms(h, layer.input_norm, c.rms_norm_eps)
         if kind == "linear_attention":
             p = (y @ layer.w_in.float().t())[None]
-            qkv, z, b, a = layer._split(p)
+            qkv, z, b, a = layer._split(p, _HeadShard(layer))
             conv = causal_conv_reference(qkv, layer.conv_w, layer.conv_b)
             kd = c.linear_key_dim
             T = tokens.shape[0]
@@ -155,3 +155,73 @@ def test_training_session_steps_on_the_hybrid_family():
         losses.append(float(r.loss_sum) / r.denominator)
     assert all(math.isfinite(x) for x in losses)
     assert losses[-1] < losses[0]
+
+
+# ------------------------------------------------------------------ context sharding (gloo ranks)
+def _exchange_worker(rank, world):
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.parallel.head_sequence import head_to_sequence_parallel, sequence_to_head_parallel
+
+    counts = [3, 5]                      # rows held by rank 0 and rank 1
+    F = 4                                # features per head shard
+    g = torch.Generator().manual_seed(10)
+    full = [torch.randn(c, world * F, generator=g) for c in counts]      # every rank's rows, all heads
+    mine = full[rank].clone().requires_grad_(True)
+    parts = [mine[:, r * F:(r + 1) * F] for r in range(world)]
+    got = sequence_to_head_parallel(parts, counts, dist.group.WORLD)
+    want = torch.cat([f[:, rank * F:(rank + 1) * F] for f in full])
+    ok_fwd = torch.allclose(got, want)
+    back = head_to_sequence_parallel(got * 2.0, counts, rank, dist.group.WORLD)
+    ok_back = torch.allclose(back, 2.0 * full[rank])
+    w = torch.arange(back.numel(), dtype=torch.float32).view_as(back)
+    (back * w).sum().backward()
+    ok_grad = torch.allclose(mine.grad, 2.0 * w)
+    return [bool(ok_fwd), bool(ok_back), bool(ok_grad)]
+
+
+@pytest.mark.distributed
+def test_head_sequence_exchange_round_trip_and_gradient():
+    from tests._harness import run_ranks
+
+    for flags in run_ranks(_exchange_worker, 2, deadline_s=120):
+        assert all(flags), flags
+
+
+def _hybrid_run(rank, world, cp, bp, steps):
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    torch.set_num_threads(2)
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-qwen3_8", "family": "qwen3_8", "seq_len": 128, "dtype": "fp32"},
+        "objective": {"name": "fast_dllm_v2", "block_size": 16, "sampling_epsilon_min": 0.1},
+        "training": {"batch_size": 2, "steps": steps, "activation_checkpointing": True},
+        "topology": {"context_parallel_size": cp, "block_parallel_size": bp},
+        "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
+    rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
+    s = TrainingSession(spec, device="cpu", runtime=rt)
+    losses = []
+    for _ in range(steps):
+        r = s.step()
+        t = r.loss_sum.double().clone()
+        if world > 1:
+            dist.all_reduce(t)
+        losses.append(float(t) / r.denominator)
+    return losses, s.model.flat.data.clone()
+
+
+@pytest.mark.distributed
+def test_hybrid_context_sharded_run_matches_single_process():
+    """Two gloo ranks, clean rows and blocks sharded (CSBP degree 2): the linear-attention layers trade
+    row shards for head shards and back; losses and parameters must follow the single-process run."""
+    from tests._harness import run_ranks
+
+    ref_losses, ref_params = _hybrid_run(0, 1, 1, 1, 2)
+    outs = run_ranks(_hybrid_run, 2, args=(2, 2, 2), deadline_s=300)
+    for losses, params in outs:
+        assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
+        assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=3e-5)

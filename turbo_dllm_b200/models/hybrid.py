@@ -60,12 +60,14 @@ class BlockRows:
     """Where the noisy blocks and the clean sequences sit in the packed rows of a rank.
 
     Built once per layout. `block_seq` / `block_start` give, for every noisy block in row order, the
-    sequence of the micro-batch it belongs to and its first token position."""
+    sequence of the micro-batch it belongs to and its first token position. With `head_parallel`
+    (a `HeadParallelPlan`) the rank's clean rows may be a shard of the sequence."""
 
-    def __init__(self, layout, seq_len: int):
+    def __init__(self, layout, seq_len: int, head_parallel=None):
         bs = layout.block_size
         self.block_size, self.seq_len = bs, seq_len
         self.n_noisy, self.n_clean = layout.n_noisy, layout.n_clean
+        self.head_parallel = head_parallel
         if self.n_noisy % bs:
             raise ValueError("noisy rows must be whole blocks")
         pos = layout.noisy_pos.view(-1, bs)
@@ -73,6 +75,9 @@ class BlockRows:
             raise ValueError("noisy rows of a block must be consecutive positions")
         self.block_start = pos[:, 0].contiguous()
         self.block_seq = layout.noisy_seq.view(-1, bs)[:, 0].contiguous()
+        if head_parallel is not None:
+            self.batch = head_parallel.batch
+            return
         if self.n_clean % seq_len:
             raise ValueError("linear-attention layers need the whole clean sequence on the rank "
                              "(context sharding redistributes heads first)")
@@ -80,6 +85,74 @@ class BlockRows:
         want = torch.arange(seq_len, device=pos.device).repeat(self.batch)
         if not torch.equal(layout.clean_pos.to(want.dtype), want):
             raise ValueError("clean rows must be the sequences in position order")
+
+
+class _HeadShard:
+    """Sizes and parameter slices of the key/value heads [r * H / P, (r + 1) * H / P) of one layer."""
+
+    def __init__(self, layer: "GatedDeltaLayer", index: int = 0, parts: int = 1):
+        c = layer.cfg
+        if c.linear_num_key_heads % parts:
+            raise ValueError(f"{c.linear_num_key_heads} linear-attention key heads cannot be split over {parts} ranks")
+        self.hk, self.hv = c.linear_num_key_heads // parts, c.linear_num_value_heads // parts
+        self.dk, self.dv = c.linear_key_head_dim, c.linear_value_head_dim
+        kd, vd = self.hk * self.dk, self.hv * self.dv
+        self.kd, self.vd = kd, vd
+        if parts == 1:
+            self.conv_w, self.conv_b, self.A_log, self.dt_bias = layer.conv_w, layer.conv_b, layer.A_log, layer.dt_bias
+            self.columns = None
+            return
+        K, V, HV = c.linear_key_dim, c.linear_value_dim, c.linear_num_value_heads
+        dev = layer.conv_w.device
+        ar = lambda lo, n: torch.arange(lo, lo + n, device=dev)
+        conv_rows = torch.cat([ar(index * kd, kd), ar(K + index * kd, kd), ar(2 * K + index * vd, vd)])
+        self.conv_w, self.conv_b = layer.conv_w[conv_rows], layer.conv_b[conv_rows]
+        self.A_log = layer.A_log[index * self.hv:(index + 1) * self.hv]
+        self.dt_bias = layer.dt_bias[index * self.hv:(index + 1) * self.hv]
+        cc = c.linear_conv_channels
+        # columns of the fused input projection that belong to this shard: q | k | v | z | b | a
+        self.columns = torch.cat([conv_rows, ar(cc + index * vd, vd), ar(cc + V + index * self.hv, self.hv),
+                                  ar(cc + V + HV + index * self.hv, self.hv)])
+
+
+class HeadParallelPlan:
+    """Row bookkeeping for linear-attention layers over a context-sharded group.
+
+    Softmax attention can leave the clean rows sharded and move K/V; a recurrence cannot, it needs every
+    sequence whole. So inside a linear-attention layer the ranks of the group trade their row shards
+    for head shards with one all-to-all (`parallel/head_sequence.py`): afterwards every rank holds
+    all rows of the group (each rank's `[noisy ; clean]` rows, in rank order) for 1/P of the heads,
+    runs the recurrence there and trades back. This object knows, for that gathered row order, where
+    the noisy blocks are and how to put the clean rows into sequence order.
+
+    Reference: dllm_parallel/core/models/backbones/qwen3_8/context_parallel.py:89-143 (head <-> sequence
+    all-to-all), qwen3_8/model.py:1523-1636 (clean pass under context parallelism)."""
+
+    def __init__(self, *, group, index: int, noisy_blocks: list, clean_positions: list, batch: int, seq_len: int,
+                 block_size: int, device):
+        """noisy_blocks[r]: (block_seq [n_r], block_start [n_r]) of rank r's noisy blocks in row order;
+        clean_positions[r]: positions [c_r] of rank r's clean rows of ONE sequence (repeated per sequence)."""
+        self.group, self.index, self.parts = group, index, len(clean_positions)
+        self.row_counts = [int(nb[0].numel()) * block_size + int(cp.numel()) * batch
+                           for nb, cp in zip(noisy_blocks, clean_positions)]
+        noisy_rows, clean_rows, clean_key, off = [], [], [], 0
+        for (bseq, bstart), cpos in zip(noisy_blocks, clean_positions):
+            nn_ = int(bseq.numel()) * block_size
+            noisy_rows.append(torch.arange(off, off + nn_, device=device))
+            c = int(cpos.numel())
+            clean_rows.append(torch.arange(off + nn_, off + nn_ + c * batch, device=device))
+            seq = torch.arange(batch, device=device).repeat_interleave(c)
+            clean_key.append(seq * seq_len + cpos.to(device).repeat(batch))
+            off += nn_ + c * batch
+        self.total_rows = off
+        self.noisy_rows = torch.cat(noisy_rows)
+        clean_rows, clean_key = torch.cat(clean_rows), torch.cat(clean_key)
+        if clean_key.numel() != batch * seq_len or torch.unique(clean_key).numel() != batch * seq_len:
+            raise ValueError("the group's clean shards must cover every position of every sequence exactly once")
+        self.clean_rows = clean_rows[torch.argsort(clean_key)]      # gathered row of (sequence, position)
+        self.block_seq = torch.cat([nb[0].to(device) for nb in noisy_blocks])
+        self.block_start = torch.cat([nb[1].to(device) for nb in noisy_blocks])
+        self.batch, self.seq_len, self.block_size = batch, seq_len, block_size
 
 
 class GatedDeltaLayer(nn.Module):
@@ -92,57 +165,78 @@ class GatedDeltaLayer(nn.Module):
             setattr(self, n, g(n))
 
     # -- pieces ------------------------------------------------------------------------------
-    def _split(self, p: torch.Tensor):
-        c = self.cfg
-        cc, vd, hv = c.linear_conv_channels, c.linear_value_dim, c.linear_num_value_heads
-        return p[..., :cc], p[..., cc:cc + vd], p[..., cc + vd:cc + vd + hv], p[..., cc + vd + hv:cc + vd + 2 * hv]
+    @staticmethod
+    def _split(p: torch.Tensor, sh: _HeadShard):
+        cc = 2 * sh.kd + sh.vd
+        return p[..., :cc], p[..., cc:cc + sh.vd], p[..., cc + sh.vd:cc + sh.vd + sh.hv], \
+            p[..., cc + sh.vd + sh.hv:cc + sh.vd + 2 * sh.hv]
 
-    def _recurrence_inputs(self, conv: torch.Tensor, b: torch.Tensor, a: torch.Tensor):
+    def _recurrence_inputs(self, conv: torch.Tensor, b: torch.Tensor, a: torch.Tensor, sh: _HeadShard):
         """conv: [B, T, channels] after convolution and SiLU -> q, k, v, log decay, beta."""
-        c = self.cfg
         B, T = conv.shape[:2]
-        kd = c.linear_key_dim
-        q = l2_normalize(conv[..., :kd].reshape(B, T, c.linear_num_key_heads, c.linear_key_head_dim))
-        k = l2_normalize(conv[..., kd:2 * kd].reshape(B, T, c.linear_num_key_heads, c.linear_key_head_dim))
-        v = conv[..., 2 * kd:].reshape(B, T, c.linear_num_value_heads, c.linear_value_head_dim).float()
-        q, k = expand_key_heads(q, c.linear_num_value_heads), expand_key_heads(k, c.linear_num_value_heads)
-        return q, k, v, gdn_gate(a, self.A_log, self.dt_bias), torch.sigmoid(b.float())
+        q = l2_normalize(conv[..., :sh.kd].reshape(B, T, sh.hk, sh.dk))
+        k = l2_normalize(conv[..., sh.kd:2 * sh.kd].reshape(B, T, sh.hk, sh.dk))
+        v = conv[..., 2 * sh.kd:].reshape(B, T, sh.hv, sh.dv).float()
+        q, k = expand_key_heads(q, sh.hv), expand_key_heads(k, sh.hv)
+        return q, k, v, gdn_gate(a, sh.A_log, sh.dt_bias), torch.sigmoid(b.float())
 
-    def mix(self, y: torch.Tensor, rows: BlockRows) -> torch.Tensor:
-        """y: normed rows [rows, H] -> mixer features [rows, Hv * Dv] (input of the output projection)."""
+    def _mix_heads(self, p_noisy, p_clean, block_seq, block_start, sh: _HeadShard, bs: int):
+        """p_noisy: [blocks, bs, F], p_clean: [B, S, F] (features of the heads in `sh`).
+        Returns (noisy features [blocks * bs, hv * Dv], clean features [B * S, hv * Dv])."""
         c = self.cfg
-        bs, S, B, W = rows.block_size, rows.seq_len, rows.batch, c.linear_conv_kernel
+        B, S, W = p_clean.shape[0], p_clean.shape[1], c.linear_conv_kernel
         C = chunk_size_for(bs)
-        p = linear(y, self.w_in)
-        nn_ = rows.n_noisy
         # ---- clean rows: one causal pass per sequence, states in front of every chunk
-        qkv_c, z_c, b_c, a_c = self._split(p[nn_:].view(B, S, -1))
-        conv_c = causal_conv_reference(qkv_c, self.conv_w, self.conv_b)
-        q, k, v, g, beta = self._recurrence_inputs(conv_c, b_c, a_c)
+        qkv_c, z_c, b_c, a_c = self._split(p_clean, sh)
+        conv_c = causal_conv_reference(qkv_c, sh.conv_w, sh.conv_b)
+        q, k, v, g, beta = self._recurrence_inputs(conv_c, b_c, a_c, sh)
         o_c, _, states = gated_delta_chunked(q, k, v, g, beta, chunk=C, return_states=True)
-        out_c = gated_rmsnorm(o_c, z_c.reshape(B, S, c.linear_num_value_heads, -1), self.gdn_norm, c.rms_norm_eps)
-        outs = []
+        out_c = gated_rmsnorm(o_c, z_c.reshape(B, S, sh.hv, sh.dv), self.gdn_norm, c.rms_norm_eps)
         # ---- noisy blocks: short sequences from the clean state and the clean convolution history
-        nb = nn_ // bs
+        outs = []
+        nb = p_noisy.shape[0]
         if nb:
-            qkv_n, z_n, b_n, a_n = self._split(p[:nn_].view(nb, bs, -1))
+            qkv_n, z_n, b_n, a_n = self._split(p_noisy, sh)
             flat_clean = qkv_c.reshape(B * S, -1)
             flat_states = states.reshape(B * (S // C), *states.shape[2:])
-            hist_off = torch.arange(-(W - 1), 0, device=y.device)
+            hist_off = torch.arange(-(W - 1), 0, device=p_clean.device)
             for lo in range(0, nb, self.branch_group):
                 hi = min(lo + self.branch_group, nb)
-                start, seq = rows.block_start[lo:hi], rows.block_seq[lo:hi]
+                start, seq = block_start[lo:hi], block_seq[lo:hi]
                 tok = start[:, None] + hist_off[None, :]                       # [n, W-1]
                 hist = flat_clean.index_select(0, (seq[:, None] * S + tok.clamp_min(0)).reshape(-1))
                 hist = hist.view(hi - lo, W - 1, -1) * (tok >= 0)[..., None].to(hist.dtype)
-                conv_n = causal_conv_reference(qkv_n[lo:hi], self.conv_w, self.conv_b, history=hist)
-                q, k, v, g, beta = self._recurrence_inputs(conv_n, b_n[lo:hi], a_n[lo:hi])
+                conv_n = causal_conv_reference(qkv_n[lo:hi], sh.conv_w, sh.conv_b, history=hist)
+                q, k, v, g, beta = self._recurrence_inputs(conv_n, b_n[lo:hi], a_n[lo:hi], sh)
                 s0 = flat_states.index_select(0, seq * (S // C) + start // C)
                 o_n, _, _ = gated_delta_chunked(q, k, v, g, beta, initial_state=s0, chunk=C)
-                outs.append(gated_rmsnorm(o_n, z_n[lo:hi].reshape(hi - lo, bs, c.linear_num_value_heads, -1),
-                                          self.gdn_norm, c.rms_norm_eps).reshape((hi - lo) * bs, -1))
-        outs.append(out_c.reshape(B * S, -1))
-        return torch.cat(outs, dim=0).to(y.dtype)
+                outs.append(gated_rmsnorm(o_n, z_n[lo:hi].reshape(hi - lo, bs, sh.hv, sh.dv), self.gdn_norm,
+                                          c.rms_norm_eps).reshape((hi - lo) * bs, -1))
+        noisy = torch.cat(outs, dim=0) if outs else out_c.new_zeros(0, sh.vd)
+        return noisy, out_c.reshape(B * S, -1)
+
+    def mix(self, y: torch.Tensor, rows: BlockRows) -> torch.Tensor:
+        """y: normed rows [rows, H] -> mixer features [rows, Hv * Dv] (input of the output projection)."""
+        bs = rows.block_size
+        p = linear(y, self.w_in)
+        plan = rows.head_parallel
+        if plan is None:
+            sh = _HeadShard(self)
+            nn_ = rows.n_noisy
+            noisy, clean = self._mix_heads(p[:nn_].view(nn_ // bs, bs, -1), p[nn_:].view(rows.batch, rows.seq_len, -1),
+                                           rows.block_seq, rows.block_start, sh, bs)
+            return torch.cat([noisy, clean], dim=0).to(y.dtype)
+        from ..parallel.head_sequence import head_to_sequence_parallel, sequence_to_head_parallel
+
+        shards = [_HeadShard(self, r, plan.parts) for r in range(plan.parts)]
+        gathered = sequence_to_head_parallel([p[:, sh.columns] for sh in shards], plan.row_counts, plan.group)
+        sh = shards[plan.index]
+        p_noisy = gathered.index_select(0, plan.noisy_rows).view(-1, bs, gathered.shape[1])
+        p_clean = gathered.index_select(0, plan.clean_rows).view(plan.batch, plan.seq_len, -1)
+        noisy, clean = self._mix_heads(p_noisy, p_clean, plan.block_seq, plan.block_start, sh, bs)
+        out = noisy.new_zeros(plan.total_rows, sh.vd)
+        out = out.index_copy(0, plan.noisy_rows, noisy).index_copy(0, plan.clean_rows, clean)
+        return head_to_sequence_parallel(out.to(y.dtype), plan.row_counts, plan.index, plan.group)
 
     def forward(self, h, positions, inv_freq, attend):
         cfg = self.cfg

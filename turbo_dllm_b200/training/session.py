@@ -67,9 +67,9 @@ class TrainingSession:
         if self.cfg.is_hybrid:
             from ..models.hybrid import HybridBlockDiffusionTransformer
 
-            if runtime is not None and (runtime.tensor_parallel_size > 1 or runtime.context_parallel_size > 1):
-                raise ValueError("the hybrid (qwen3_8) family runs on data-parallel and block-parallel ranks; "
-                                 "tensor and context parallelism of its linear-attention layers are not built")
+            if runtime is not None and runtime.tensor_parallel_size > 1:
+                raise ValueError("the hybrid (qwen3_8) family runs on data-, context- and block-parallel ranks; "
+                                 "tensor parallelism of its linear-attention layers is not built")
             self.model = HybridBlockDiffusionTransformer(
                 self.cfg, dtype=self.dtype, device=self.device,
                 activation_checkpointing=spec.training.activation_checkpointing,
@@ -128,7 +128,8 @@ class TrainingSession:
         if self.cfg.is_hybrid:
             from ..models.hybrid import BlockRows
 
-            self.attend.block_rows = BlockRows(self.layout, spec.model.seq_len)
+            self.attend.block_rows = BlockRows(self.layout, spec.model.seq_len,
+                                               head_parallel=self._build_head_parallel_plan())
         o = spec.optimizer
         okw = dict(lr=o.lr, betas=(o.adam_beta1, o.adam_beta2), eps=o.adam_eps, weight_decay=o.weight_decay)
         self.expert_optimizer = None
@@ -255,6 +256,31 @@ class TrainingSession:
         return build_packed_layout(seq_len=s.model.seq_len, block_size=s.objective.block_size,
                                    batch=s.training.batch_size, views=self.objective.views,
                                    owned_blocks=owned, clean_pos=clean, device=self.device)
+
+    def _build_head_parallel_plan(self):
+        """Row bookkeeping of the head <-> sequence exchange that linear-attention layers use when the
+        clean rows are sharded over a context-parallel group (None otherwise)."""
+        rt, s = self.runtime, self.spec
+        if rt is None or rt.context_parallel_size <= 1:
+            return None
+        from ..models.hybrid import HeadParallelPlan
+
+        bs, batch = s.objective.block_size, s.training.batch_size
+        lay = runtime_clean_layout(s.kernel.cp_bp_clean_kv_layout, rt.block_parallel_size)
+        nblocks = s.model.seq_len // bs
+        noisy, clean = [], []
+        for phys in rt.groups.ranks["context_block_parallel"]:
+            a = rt.plan.rank_assignments[phys]
+            owned = sorted(a.owned_blocks) if rt.block_parallel_size > 1 else list(range(nblocks))
+            starts = torch.tensor(owned, device=self.device) * bs
+            reps = batch * self.objective.views
+            seq = torch.arange(batch, device=self.device).repeat_interleave(self.objective.views * len(owned))
+            noisy.append((seq, starts.repeat(reps)))
+            clean.append(clean_positions_for_rank(s.model.seq_len, rt.context_parallel_size, a.context_parallel_rank,
+                                                  lay, bs, self.device))
+        return HeadParallelPlan(group=rt.context_group, index=dist.get_rank(rt.context_group), noisy_blocks=noisy,
+                                clean_positions=clean, batch=batch, seq_len=s.model.seq_len, block_size=bs,
+                                device=self.device)
 
     def _build_attention(self):
         rt = self.runtime
