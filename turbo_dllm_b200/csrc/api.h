@@ -143,6 +143,20 @@ int tdllm_kv_gather(void* const* staging_ptrs, void* const* flag_ptrs, const lon
 int tdllm_kv_scatter_reduce(void* const* partial_ptrs, void* const* flag_ptrs, const long long* counts,
                             int rank, int world, int row_bytes, void* out, int epoch, void* stream);
 
+// ---- gated delta rule: chunk-to-chunk state scan ---------------------------------
+// All tensors fp32 and contiguous. ut/o/u: [BH, N, C, Dv]; w/qi/ko: [BH, N, C, Dk]; qk: [BH, N, C, C];
+// total: [BH, N]; s0 (may be null)/s_final: [BH, Dk, Dv]; states: [BH, N, Dk, Dv] (state in front of each chunk).
+// C <= 64, Dk <= 128 and a multiple of 8, Dv a multiple of 32.
+int tdllm_gdn_scan_fwd(const float* ut, const float* w, const float* qk, const float* qi, const float* ko,
+                       const float* total, const float* s0, float* o, float* u, float* states, float* s_final,
+                       int BH, int N, int C, int Dk, int Dv, void* stream);
+// d_states / d_sfinal may be null. d_w, d_qi, d_ko: [BH, N, Dv/32, C, Dk]; d_qk: [BH, N, Dv/32, C, C];
+// d_total: [BH, N, Dv/32]: partial sums per slice of 32 value columns, to be summed over that axis.
+int tdllm_gdn_scan_bwd(const float* w, const float* qk, const float* qi, const float* ko, const float* total,
+                       const float* states, const float* u, const float* d_o, const float* d_states,
+                       const float* d_sfinal, float* d_ut, float* d_w, float* d_qk, float* d_qi, float* d_ko,
+                       float* d_total, float* d_s0, int BH, int N, int C, int Dk, int Dv, void* stream);
+
 // ---- noising ---------------------------------------------------------------
 int tdllm_corrupt(const long long* x0, const float* t, const unsigned char* eligible, long long* xt,
                   long long* labels, int B, int L, int block_size, int views, int shift_labels,

@@ -37,7 +37,78 @@ import math
 import torch
 import torch.nn.functional as F
 
+from ..kernels import native
+
 MAX_CHUNK = 64
+
+native.register_signatures({
+    "tdllm_gdn_scan_fwd": (native.c_int, [native.c_void_p] * 11 + [native.c_int] * 5 + [native.c_void_p]),
+    "tdllm_gdn_scan_bwd": (native.c_int, [native.c_void_p] * 17 + [native.c_int] * 5 + [native.c_void_p]),
+})
+
+
+def _native_scan_ok(t: torch.Tensor, C: int, Dk: int, Dv: int) -> bool:
+    """The sm_100a scan kernel handles fp32 CUDA tensors with C <= 64, Dk <= 128 (multiple of 8) and Dv a
+    multiple of 32; `TDLLM_GDN_SCAN=torch` keeps the batched-product loop (the oracle of the kernel)."""
+    import os
+
+    if not t.is_cuda or os.environ.get("TDLLM_GDN_SCAN", "native") == "torch":
+        return False
+    return C <= 64 and Dk <= 128 and Dk % 8 == 0 and Dv % 32 == 0
+
+
+class _StateScan(torch.autograd.Function):
+    """The sequential part of the chunked rule as one kernel per direction
+    (`csrc/gated_delta_scan.cu`). Inputs are laid out [B, H, N, C, .]; returns
+    (o [B, H, N, C, Dv], final state [B, H, Dk, Dv], states in front of every chunk [B, H, N, Dk, Dv])."""
+
+    @staticmethod
+    def forward(ctx, u_tilde, w, qk, q_in, k_out, total, s0):
+        from ..kernels import native
+        from ._util import ptr, stream
+
+        u_tilde, w, qk, q_in, k_out, total = (t.contiguous() for t in (u_tilde, w, qk, q_in, k_out, total))
+        B, H, N, C, Dv = u_tilde.shape
+        Dk = w.shape[-1]
+        s0c = None if s0 is None else s0.contiguous()
+        o = torch.empty_like(u_tilde)
+        u = torch.empty_like(u_tilde)
+        states = torch.empty(B, H, N, Dk, Dv, dtype=torch.float32, device=w.device)
+        s_final = torch.empty(B, H, Dk, Dv, dtype=torch.float32, device=w.device)
+        rc = native.lib().tdllm_gdn_scan_fwd(ptr(u_tilde), ptr(w), ptr(qk), ptr(q_in), ptr(k_out), ptr(total), ptr(s0c),
+                                             ptr(o), ptr(u), ptr(states), ptr(s_final), B * H, N, C, Dk, Dv, stream())
+        native.check(rc, "gdn_scan_fwd")
+        ctx.save_for_backward(w, qk, q_in, k_out, total, states, u)
+        ctx.has_s0 = s0 is not None
+        ctx.set_materialize_grads(False)
+        return o, s_final, states
+
+    @staticmethod
+    def backward(ctx, d_o, d_sfinal, d_states):
+        from ..kernels import native
+        from ._util import ptr, stream
+
+        w, qk, q_in, k_out, total, states, u = ctx.saved_tensors
+        B, H, N, C, Dk = w.shape
+        Dv = u.shape[-1]
+        sl = Dv // 32
+        dev = w.device
+        d_o = torch.zeros_like(u) if d_o is None else d_o.contiguous().float()
+        d_sfinal = None if d_sfinal is None else d_sfinal.contiguous().float()
+        d_states = None if d_states is None else d_states.contiguous().float()
+        d_ut = torch.empty_like(u)
+        d_w = torch.empty(B, H, N, sl, C, Dk, dtype=torch.float32, device=dev)
+        d_qi, d_ko = torch.empty_like(d_w), torch.empty_like(d_w)
+        d_qk = torch.empty(B, H, N, sl, C, C, dtype=torch.float32, device=dev)
+        d_total = torch.empty(B, H, N, sl, dtype=torch.float32, device=dev)
+        d_s0 = torch.empty(B, H, Dk, Dv, dtype=torch.float32, device=dev)
+        rc = native.lib().tdllm_gdn_scan_bwd(ptr(w), ptr(qk), ptr(q_in), ptr(k_out), ptr(total), ptr(states), ptr(u),
+                                             ptr(d_o), ptr(d_states), ptr(d_sfinal), ptr(d_ut), ptr(d_w), ptr(d_qk),
+                                             ptr(d_qi), ptr(d_ko), ptr(d_total), ptr(d_s0), B * H, N, C, Dk, Dv,
+                                             stream())
+        native.check(rc, "gdn_scan_bwd")
+        return (d_ut, d_w.sum(3), d_qk.sum(3), d_qi.sum(3), d_ko.sum(3), d_total.sum(3),
+                d_s0 if ctx.has_s0 else None)
 
 
 def gdn_gate(a: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor) -> torch.Tensor:
@@ -141,6 +212,11 @@ def gated_delta_chunked(q, k, v, g, beta, *, scale: float | None = None, initial
     q, k, v = (t.reshape(B, N, chunk, H, t.shape[-1]) for t in (q, k, v))
     g, beta = (t.reshape(B, N, chunk, H) for t in (g, beta))
     u_tilde, w, qk, q_in, k_out, total = _chunk_terms(q, k, v, g, beta, scale)
+    if _native_scan_ok(u_tilde, chunk, Dk, Dv):
+        s0 = None if initial_state is None else initial_state.float()
+        o, S, st = _StateScan.apply(u_tilde, w, qk, q_in, k_out, total, s0)
+        o = o.permute(0, 2, 3, 1, 4).reshape(B, T, H, Dv)
+        return o, S, (st.permute(0, 2, 1, 3, 4) if return_states else None)
     S = q.new_zeros(B, H, Dk, Dv) if initial_state is None else initial_state.float()
     outs, states = [], []
     for n in range(N):
