@@ -205,3 +205,37 @@ def test_dpace_loss_needs_the_dflash2_drafter():
         "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}).validate()
     with pytest.raises(ValueError):
         TrainingSession(spec, device="cpu")
+
+
+def test_dflash2_export_round_trip(tmp_path):
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.models.export import (export_dflash_drafter, normalize_dflash2_config,
+                                               validate_dflash2_export)
+
+    cfg, _, v2 = _models()
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-qwen3", "family": "dflash", "verifier_id": "synthetic:tiny-qwen3",
+                  "target_layer_ids": [0, 2]},
+        "objective": {"name": "dflash_distillation", "block_size": 8}})
+    out = str(tmp_path / "export")
+    export_dflash_drafter(v2, spec, out)
+    assert validate_dflash2_export(out, expected_block_size=8) == []
+    import json
+    import os
+
+    conf = json.load(open(os.path.join(out, "config.json")))
+    assert conf["architectures"] == ["DFlash2DraftModel"] and conf["dflash_config"]["selector_top_k"] == 4
+    from safetensors import safe_open
+
+    with safe_open(os.path.join(out, "model.safetensors"), framework="pt") as f:
+        assert tuple(f.get_slice("layers.0.attn_conv_proj").get_shape()) == (2 * 3 * (cfg.hidden_size // 64),
+                                                                             cfg.hidden_size)
+        assert "embed" not in f.keys() and "lm_head" not in f.keys()
+    assert any("block_size" in p for p in validate_dflash2_export(out, expected_block_size=16))
+    bad = dict(conf, architectures=["DFlashDraftModel"])
+    with pytest.raises(ValueError):
+        normalize_dflash2_config(bad)
+    # a tampered tensor file is caught by the manifest hashes
+    with open(os.path.join(out, "model.safetensors"), "ab") as f:
+        f.write(b"x")
+    assert validate_dflash2_export(out) != []

@@ -91,6 +91,8 @@ def export_dflash_drafter(draft_model, spec, path: str) -> dict:
 
     os.makedirs(path, exist_ok=True)
     tensors = {name: p.detach().cpu().contiguous() for name, p in draft_model.flat.params.items()}
+    if hasattr(draft_model, "candidate_selector"):
+        return _export_dflash2_drafter(draft_model, spec, path, tensors)
     save_file(tensors, os.path.join(path, "model.safetensors"))
     cfg = draft_model.cfg
     json.dump({"architectures": ["DFlashDraftModel"], "model_type": "dflash", "hidden_size": cfg.hidden_size,
@@ -102,6 +104,111 @@ def export_dflash_drafter(draft_model, spec, path: str) -> dict:
                "verifier": spec.model.verifier_id, "gate_up_layout": "interleaved"},
               open(os.path.join(path, "dflash_config.json"), "w"), indent=1)
     return write_export_manifest(path, {"kind": "dflash_drafter"})
+
+
+def dflash2_serving_shapes(config: dict) -> dict[str, tuple[int, ...]]:
+    """Tensor inventory a DFlash2 export must hold, from its config (no verifier tensors: embeddings and
+    the output head are the target model's and are loaded by the serving stack)."""
+    m = config["dflash_config"]
+    h, L = config["hidden_size"], config["num_hidden_layers"]
+    q = config["num_attention_heads"] * config["head_dim"]
+    kv = config["num_key_value_heads"] * config["head_dim"]
+    taps, groups = m["conv_kernel_size"], h // m["conv_group_size"]
+    shapes = {"fc": (h, config["conditioning_dim"]), "hidden_norm": (h,), "final_norm": (h,),
+              "selector_predecessor": (config["vocab_size"], m["selector_rank"]),
+              "selector_successor": (config["vocab_size"], m["selector_rank"]),
+              "selector_proj": (m["selector_rank"], h)}
+    for i in range(L):
+        p = f"layers.{i}."
+        shapes.update({p + "input_norm": (h,), p + "post_norm": (h,), p + "w_q": (q, h), p + "w_kv": (2 * kv, h),
+                       p + "w_o": (h, q), p + "w_gate_up": (2 * config["intermediate_size"], h),
+                       p + "w_down": (h, config["intermediate_size"])})
+        if config.get("qk_norm", True):
+            shapes.update({p + "q_norm": (config["head_dim"],), p + "k_norm": (config["head_dim"],)})
+        for c in ("attn_conv", "mlp_conv"):
+            shapes.update({p + c + "_base": (2, taps, h), p + c + "_proj": (2 * taps * groups, h)})
+    return shapes
+
+
+def normalize_dflash2_config(config: dict, expected_block_size: int | None = None) -> dict:
+    """Checks the fields a DFlash2 serving loader needs and returns a standalone copy
+    (dllm_parallel/core/models/backbones/dflash/executor.py:465-514)."""
+    cfg = json.loads(json.dumps(config))
+    if cfg.get("architectures") != ["DFlash2DraftModel"]:
+        raise ValueError("a DFlash2 export needs architectures=['DFlash2DraftModel']")
+    m = cfg.get("dflash_config")
+    if not isinstance(m, dict):
+        raise ValueError("a DFlash2 export needs a dflash_config mapping")
+    block = cfg.get("block_size", m.get("block_size"))
+    if expected_block_size is not None and block != int(expected_block_size):
+        raise ValueError(f"exported block_size={block!r}, expected {int(expected_block_size)}")
+    for name in ("block_size", "conv_group_size", "conv_kernel_size", "selector_rank", "selector_top_k"):
+        v = block if name == "block_size" else m.get(name)
+        if isinstance(v, bool) or not isinstance(v, int) or v <= 0:
+            raise ValueError(f"DFlash2 requires positive integer {name}, got {v!r}")
+    mode = str(m.get("attention_mode", "gqa")).lower()
+    if mode not in ("gqa", "mha"):
+        raise ValueError(f"DFlash2 serving supports GQA/MHA only, got attention_mode={mode!r}")
+    m["attention_mode"] = mode
+    cfg.pop("auto_map", None)
+    return cfg
+
+
+@torch.no_grad()
+def _export_dflash2_drafter(draft_model, spec, path: str, tensors: dict) -> dict:
+    from safetensors.torch import save_file
+
+    cfg, sel = draft_model.cfg, draft_model.candidate_selector
+    layer0 = draft_model.layers[0].attention_conv
+    n_proj = 2 * layer0.taps * layer0.groups
+    for name in list(tensors):           # drop the GEMM padding rows of the tap projections
+        if name.endswith("_conv_proj"):
+            tensors[name] = tensors[name][:n_proj].contiguous()
+    save_file(tensors, os.path.join(path, "model.safetensors"))
+    config = {"architectures": ["DFlash2DraftModel"], "model_type": "dflash2", "hidden_size": cfg.hidden_size,
+              "num_hidden_layers": cfg.num_layers, "num_attention_heads": cfg.num_attention_heads,
+              "num_key_value_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "qk_norm": cfg.qk_norm,
+              "intermediate_size": cfg.intermediate_size, "vocab_size": int(sel.predecessor.shape[0]),
+              "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_norm_eps,
+              "block_size": draft_model.block_size, "target_layer_ids": list(spec.model.target_layer_ids),
+              "conditioning_dim": draft_model.conditioning_dim, "mask_token_id": cfg.mask_token_id,
+              "verifier": spec.model.verifier_id, "gate_up_layout": "interleaved",
+              "output_multiplier": draft_model.output_multiplier,
+              "final_logit_softcapping": draft_model.final_logit_softcapping,
+              "dflash_config": {"block_size": draft_model.block_size, "conv_kernel_size": layer0.taps,
+                                "conv_group_size": cfg.hidden_size // layer0.groups,
+                                "selector_rank": int(sel.predecessor.shape[1]), "selector_top_k": int(sel.top_k),
+                                "attention_mode": "gqa" if cfg.num_key_value_heads < cfg.num_attention_heads else "mha",
+                                "target_layer_ids": list(spec.model.target_layer_ids)}}
+    normalize_dflash2_config(config)
+    json.dump(config, open(os.path.join(path, "config.json"), "w"), indent=1)
+    json.dump(config, open(os.path.join(path, "dflash_config.json"), "w"), indent=1)
+    return write_export_manifest(path, {"kind": "dflash2_drafter", "tensor_count": len(tensors)})
+
+
+def validate_dflash2_export(path: str, expected_block_size: int | None = None) -> list[str]:
+    """Config, hashes and tensor inventory of a DFlash2 export
+    (dllm_parallel/core/models/backbones/dflash/executor.py:516-566)."""
+    problems = validate_dflash_export(path)
+    if problems:
+        return problems
+    try:
+        cfg = normalize_dflash2_config(json.load(open(os.path.join(path, "config.json"))), expected_block_size)
+    except (OSError, ValueError) as e:
+        return [str(e)]
+    from safetensors import safe_open
+
+    with safe_open(os.path.join(path, "model.safetensors"), framework="pt", device="cpu") as f:
+        got = {k: tuple(f.get_slice(k).get_shape()) for k in f.keys()}
+    want = dflash2_serving_shapes(cfg)
+    forbidden = {"embed", "lm_head", "embed_tokens.weight", "lm_head.weight"} & set(got)
+    if forbidden:
+        problems.append(f"export contains verifier-only tensors: {sorted(forbidden)}")
+    missing, extra = sorted(want.keys() - got.keys()), sorted(got.keys() - want.keys())
+    wrong = sorted(k for k in want.keys() & got.keys() if want[k] != got[k])
+    if missing or extra or wrong:
+        problems.append(f"tensor inventory mismatch: missing={missing[:3]} extra={extra[:3]} wrong_shapes={wrong[:3]}")
+    return problems
 
 
 def validate_dflash_export(path: str) -> list[str]:
