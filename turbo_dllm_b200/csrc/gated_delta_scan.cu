@@ -10,8 +10,8 @@
 //
 // One CTA owns one (batch, head) and a slice of 32 value columns; the slice of S lives in shared
 // memory for the whole scan, the chunk operands are staged in shared memory one chunk at a time.
-// Thread (g, j) = (tid / 32, tid % 32) works on column j: operand reads are warp broadcasts, state
-// reads are conflict-free. The products are C x Dk x 32 per step (C <= 64): the scan is bound by
+// Thread (g, j) = (tid / 32, tid % 32) works on column j: operand reads are warp broadcasts (float4), state
+// reads are conflict-free, and four output rows share each state load. The products are C x Dk x 32 per step (C <= 64): the scan is bound by
 // the chain of N dependent steps, not by arithmetic, so it runs on the fp32 pipes.
 //
 // Backward walks the chunks in reverse with dS in shared memory. Gradients that sum over the value
@@ -65,35 +65,85 @@ __global__ void __launch_bounds__(THREADS) gdn_scan_fwd_kernel(const FwdParams p
     for (int i = tid; i < C * Dk; i += THREADS) sA[i] = W[i];
     for (int i = tid; i < C * C; i += THREADS) sQK[i] = QK[i];
     __syncthreads();
-    // u = Ut - W S
-    for (int c = g; c < C; c += G) {
-      float acc = Ut[(size_t)c * Dv + col0 + j];
-      const float* wr = sA + c * Dk;
-      for (int k = 0; k < Dk; ++k) acc -= wr[k] * sS[k * DVT + j];
-      sU[c * DVT + j] = acc;
-      p.u[(chunk * C + c) * Dv + col0 + j] = acc;
+    // u = Ut - W S: four rows per pass share every load of the state column; operand rows are read as
+    // float4 broadcasts
+    for (int c0 = g; c0 < C; c0 += 4 * G) {
+      float acc[4];
+      const float4* wr[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int c = min(c0 + r * G, C - 1);
+        acc[r] = Ut[(size_t)c * Dv + col0 + j];
+        wr[r] = reinterpret_cast<const float4*>(sA + c * Dk);
+      }
+      for (int k4 = 0; k4 < Dk / 4; ++k4) {
+        const float s0v = sS[(4 * k4 + 0) * DVT + j], s1v = sS[(4 * k4 + 1) * DVT + j];
+        const float s2v = sS[(4 * k4 + 2) * DVT + j], s3v = sS[(4 * k4 + 3) * DVT + j];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const float4 a = wr[r][k4];
+          acc[r] -= a.x * s0v + a.y * s1v + a.z * s2v + a.w * s3v;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int c = c0 + r * G;
+        if (c < C) {
+          sU[c * DVT + j] = acc[r];
+          p.u[(chunk * C + c) * Dv + col0 + j] = acc[r];
+        }
+      }
     }
     __syncthreads();
     for (int i = tid; i < C * Dk; i += THREADS) sA[i] = Qi[i];
     __syncthreads();
     // o = Qi S + QK u
-    for (int c = g; c < C; c += G) {
-      float acc = 0.f;
-      const float* qr = sA + c * Dk;
-      for (int k = 0; k < Dk; ++k) acc += qr[k] * sS[k * DVT + j];
-      const float* ar = sQK + c * C;
-      for (int cc = 0; cc <= c; ++cc) acc += ar[cc] * sU[cc * DVT + j];
-      p.o[(chunk * C + c) * Dv + col0 + j] = acc;
+    for (int c0 = g; c0 < C; c0 += 4 * G) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const float4* qr[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) qr[r] = reinterpret_cast<const float4*>(sA + min(c0 + r * G, C - 1) * Dk);
+      for (int k4 = 0; k4 < Dk / 4; ++k4) {
+        const float s0v = sS[(4 * k4 + 0) * DVT + j], s1v = sS[(4 * k4 + 1) * DVT + j];
+        const float s2v = sS[(4 * k4 + 2) * DVT + j], s3v = sS[(4 * k4 + 3) * DVT + j];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const float4 a = qr[r][k4];
+          acc[r] += a.x * s0v + a.y * s1v + a.z * s2v + a.w * s3v;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int c = c0 + r * G;
+        if (c < C) {
+          float a = acc[r];
+          const float* ar = sQK + c * C;
+          for (int cc = 0; cc <= c; ++cc) a += ar[cc] * sU[cc * DVT + j];
+          p.o[(chunk * C + c) * Dv + col0 + j] = a;
+        }
+      }
     }
     __syncthreads();
     for (int i = tid; i < C * Dk; i += THREADS) sA[i] = Ko[i];
     __syncthreads();
     // S = t S + Ko^T u
     const float t = p.total[chunk];
-    for (int k = g; k < Dk; k += G) {
-      float acc = t * sS[k * DVT + j];
-      for (int c = 0; c < C; ++c) acc += sA[c * Dk + k] * sU[c * DVT + j];
-      sS[k * DVT + j] = acc;
+    for (int kq = g; kq < Dk / 4; kq += G) {   // four consecutive state rows per pass: one float4 of Ko per token
+      const int k = 4 * kq;
+      float a0 = t * sS[(k + 0) * DVT + j], a1 = t * sS[(k + 1) * DVT + j];
+      float a2 = t * sS[(k + 2) * DVT + j], a3 = t * sS[(k + 3) * DVT + j];
+      for (int c = 0; c < C; ++c) {
+        const float4 a = *reinterpret_cast<const float4*>(sA + c * Dk + k);
+        const float uv = sU[c * DVT + j];
+        a0 += a.x * uv;
+        a1 += a.y * uv;
+        a2 += a.z * uv;
+        a3 += a.w * uv;
+      }
+      sS[(k + 0) * DVT + j] = a0;
+      sS[(k + 1) * DVT + j] = a1;
+      sS[(k + 2) * DVT + j] = a2;
+      sS[(k + 3) * DVT + j] = a3;
     }
     __syncthreads();
   }
