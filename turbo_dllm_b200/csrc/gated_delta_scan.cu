@@ -203,13 +203,34 @@ __global__ void __launch_bounds__(THREADS) gdn_scan_bwd_kernel(const BwdParams p
       if (j == 0) sRed[g] = acc;
     }
     // du = QK^T dO + Ko dS'
-    for (int c = g; c < C; c += G) {
-      float acc = 0.f;
-      for (int cc = c; cc < C; ++cc) acc += sQK[cc * C + c] * sdO[cc * P + j];
-      const float* kr = sA + c * Dk;
-      for (int k = 0; k < Dk; ++k) acc += kr[k] * sdS[k * P + j];
-      sdU[c * P + j] = acc;
-      p.d_ut[(chunk * C + c) * Dv + col0 + j] = acc;
+    for (int c0 = g; c0 < C; c0 += 4 * G) {   // four rows per pass share each load of dS'
+      float acc[4];
+      const float4* kr[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int c = min(c0 + r * G, C - 1);
+        float a = 0.f;
+        for (int cc = c; cc < C; ++cc) a += sQK[cc * C + c] * sdO[cc * P + j];
+        acc[r] = a;
+        kr[r] = reinterpret_cast<const float4*>(sA + c * Dk);
+      }
+      for (int k4 = 0; k4 < Dk / 4; ++k4) {
+        const float d0 = sdS[(4 * k4 + 0) * P + j], d1 = sdS[(4 * k4 + 1) * P + j];
+        const float d2 = sdS[(4 * k4 + 2) * P + j], d3 = sdS[(4 * k4 + 3) * P + j];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const float4 a = kr[r][k4];
+          acc[r] += a.x * d0 + a.y * d1 + a.z * d2 + a.w * d3;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int c = c0 + r * G;
+        if (c < C) {
+          sdU[c * P + j] = acc[r];
+          p.d_ut[(chunk * C + c) * Dv + col0 + j] = acc[r];
+        }
+      }
     }
     __syncthreads();
     if (tid == 0) {
@@ -218,18 +239,28 @@ __global__ void __launch_bounds__(THREADS) gdn_scan_bwd_kernel(const BwdParams p
       p.d_total[part] = acc;
     }
     // partial sums over this slice's columns: thread -> one (c, k) / (c, c') entry at a time
-    for (int i = tid; i < C * Dk; i += THREADS) {
-      const int c = i / Dk, k = i % Dk;
-      float aw = 0.f, aq = 0.f, ak = 0.f;
+    const int KQ = Dk / 4;   // a thread takes entries (c, kk + r * KQ), r = 0..3: the three row operands are loaded once
+    for (int i = tid; i < C * KQ; i += THREADS) {
+      const int c = i / KQ, kk = i % KQ;
+      float aw[4] = {0.f, 0.f, 0.f, 0.f}, aq[4] = {0.f, 0.f, 0.f, 0.f}, ak[4] = {0.f, 0.f, 0.f, 0.f};
       for (int jj = 0; jj < DVT; ++jj) {
-        const float s = sS[k * P + jj];
-        aw -= sdU[c * P + jj] * s;
-        aq += sdO[c * P + jj] * s;
-        ak += sU[c * P + jj] * sdS[k * P + jj];
+        const float du = sdU[c * P + jj], dO = sdO[c * P + jj], uu = sU[c * P + jj];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int k = kk + r * KQ;
+          const float sv = sS[k * P + jj];
+          aw[r] -= du * sv;
+          aq[r] += dO * sv;
+          ak[r] += uu * sdS[k * P + jj];
+        }
       }
-      p.d_w[part * C * Dk + i] = aw;
-      p.d_qi[part * C * Dk + i] = aq;
-      p.d_ko[part * C * Dk + i] = ak;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const size_t at = part * C * Dk + (size_t)c * Dk + kk + r * KQ;
+        p.d_w[at] = aw[r];
+        p.d_qi[at] = aq[r];
+        p.d_ko[at] = ak[r];
+      }
     }
     for (int i = tid; i < C * C; i += THREADS) {
       const int c = i / C, cc = i % C;
@@ -244,19 +275,48 @@ __global__ void __launch_bounds__(THREADS) gdn_scan_bwd_kernel(const BwdParams p
     float keep[MAX_DK / G];
     for (int i = tid; i < C * Dk; i += THREADS) sA[i] = Qi[i];
     __syncthreads();
-    for (int k = g, r = 0; k < Dk; k += G, ++r) {
-      float acc = t * sdS[k * P + j];
-      for (int c = 0; c < C; ++c) acc += sA[c * Dk + k] * sdO[c * P + j];
-      keep[r] = acc;
+    for (int kq = g, r = 0; kq < Dk / 4; kq += G, ++r) {   // four consecutive state rows: one float4 of Qi per token
+      const int k = 4 * kq;
+      float a0 = t * sdS[(k + 0) * P + j], a1 = t * sdS[(k + 1) * P + j];
+      float a2 = t * sdS[(k + 2) * P + j], a3 = t * sdS[(k + 3) * P + j];
+      for (int c = 0; c < C; ++c) {
+        const float4 a = *reinterpret_cast<const float4*>(sA + c * Dk + k);
+        const float dv = sdO[c * P + j];
+        a0 += a.x * dv;
+        a1 += a.y * dv;
+        a2 += a.z * dv;
+        a3 += a.w * dv;
+      }
+      keep[4 * r + 0] = a0;
+      keep[4 * r + 1] = a1;
+      keep[4 * r + 2] = a2;
+      keep[4 * r + 3] = a3;
     }
     __syncthreads();
     for (int i = tid; i < C * Dk; i += THREADS) sA[i] = W[i];
     __syncthreads();
-    for (int k = g, r = 0; k < Dk; k += G, ++r) {
-      float acc = keep[r];
-      for (int c = 0; c < C; ++c) acc -= sA[c * Dk + k] * sdU[c * P + j];
-      if (p.d_states) acc += p.d_states[(chunk * Dk + k) * Dv + col0 + j];
-      sdS[k * P + j] = acc;
+    for (int kq = g, r = 0; kq < Dk / 4; kq += G, ++r) {
+      const int k = 4 * kq;
+      float a0 = keep[4 * r + 0], a1 = keep[4 * r + 1], a2 = keep[4 * r + 2], a3 = keep[4 * r + 3];
+      for (int c = 0; c < C; ++c) {
+        const float4 a = *reinterpret_cast<const float4*>(sA + c * Dk + k);
+        const float dv = sdU[c * P + j];
+        a0 -= a.x * dv;
+        a1 -= a.y * dv;
+        a2 -= a.z * dv;
+        a3 -= a.w * dv;
+      }
+      if (p.d_states) {
+        const float* ds = p.d_states + (chunk * Dk + k) * Dv + col0 + j;
+        a0 += ds[0];
+        a1 += ds[Dv];
+        a2 += ds[2 * (size_t)Dv];
+        a3 += ds[3 * (size_t)Dv];
+      }
+      sdS[(k + 0) * P + j] = a0;
+      sdS[(k + 1) * P + j] = a1;
+      sdS[(k + 2) * P + j] = a2;
+      sdS[(k + 3) * P + j] = a3;
     }
     __syncthreads();
   }
