@@ -225,3 +225,36 @@ def test_hybrid_context_sharded_run_matches_single_process():
     for losses, params in outs:
         assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
         assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=3e-5)
+
+
+def test_lora_on_the_hybrid_family_trains_adapters_only_and_merges():
+    from turbo_dllm_b200.adapters.lora import apply_lora, merge_lora
+
+    S, bs, B = 32, 8, 1
+    model = HybridBlockDiffusionTransformer(CFG, dtype=torch.float32, activation_checkpointing=True, seed=9,
+                                            init_std=0.05)
+    st = apply_lora(model, rank=4, alpha=8.0, targets=("attention", "mlp"), seed=1)
+    names = set(n.split(".", 2)[2].rsplit(".", 1)[0] for n in st.flat.params)
+    assert {"w_in", "w_out", "w_qkv", "w_o", "w_attn_gate", "w_gate_up", "w_down"} <= names
+    with torch.no_grad():       # non-zero B so that the adapters change the output
+        for n, p in st.flat.params.items():
+            if n.endswith("lora_B"):
+                p.normal_(0, 0.05)
+    clean = torch.randint(0, CFG.vocab_size - 1, (B, S), generator=torch.Generator().manual_seed(2))
+    noisy = clean[:, None].clone()
+    noisy[:, :, ::2] = CFG.mask_token_id
+    layout = build_packed_layout(seq_len=S, block_size=bs, batch=B, views=1)
+    st.flat.zero_grad()
+    out = _packed(model, clean, noisy, layout)
+    out.square().sum().backward()
+    st.flat.collect_grads()
+    assert st.flat.grad.abs().sum() > 0
+    assert all(p.grad is None and not p.requires_grad for p in model.flat.params.values())
+    with torch.no_grad():
+        with_adapters = _packed(model, clean, noisy, layout)
+        merge_lora(model)
+        for layer in model.layers:
+            layer.lora = None
+        model.lora = None
+        merged = _packed(model, clean, noisy, layout)
+    assert torch.allclose(with_adapters, merged, atol=2e-4, rtol=1e-3)

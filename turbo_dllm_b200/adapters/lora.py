@@ -19,7 +19,11 @@ import torch
 from ..models.dense import FlatParams
 from ..ops.gemm import linear
 
-ROLE_TARGETS = {"attention": ("w_qkv", "w_o"), "mlp": ("w_gate_up", "w_down"), "experts": ()}
+# `attention` also names the mixer projections of the hybrid family's layers (fused input projection and
+# output projection of a linear-attention layer, output gate of a gated softmax-attention layer);
+# a layer only gets adapters for the projections it has
+ROLE_TARGETS = {"attention": ("w_qkv", "w_o", "w_in", "w_out", "w_attn_gate"), "mlp": ("w_gate_up", "w_down"),
+                "experts": ()}
 
 
 class LoRAState:
@@ -90,7 +94,7 @@ def merge_lora(model) -> None:
     if st is None:
         return
     for i, layer in enumerate(model.layers):
-        for n in ("w_qkv", "w_o", "w_gate_up", "w_down"):
+        for n in (n for names in ROLE_TARGETS.values() for n in names):
             pair = st.pair(i, n)
             if pair is None:
                 continue

@@ -87,6 +87,26 @@ class BlockRows:
             raise ValueError("clean rows must be the sequences in position order")
 
 
+def _adapted_linear(layer, x, name):
+    """x W^T plus the layer's low-rank update of that projection, when adapters are attached."""
+    out = linear(x, getattr(layer, name))
+    st = getattr(layer, "lora", None)
+    pair = None if st is None else st.pair(layer.idx, name)
+    if pair is None:
+        return out
+    from ..adapters.lora import lora_delta
+
+    return out + lora_delta(x, pair[0], pair[1], st.scale, st.dropout)
+
+
+def _adapted_mlp(layer, h):
+    """SwiGLU MLP with residual, unfused so that adapters can sit on both projections."""
+    from ..ops.activation import swiglu as swiglu_op
+
+    y2, _ = rmsnorm(h, layer.post_norm, layer.cfg.rms_norm_eps)
+    return h + _adapted_linear(layer, swiglu_op(_adapted_linear(layer, y2, "w_gate_up")), "w_down")
+
+
 class _HeadShard:
     """Sizes and parameter slices of the key/value heads [r * H / P, (r + 1) * H / P) of one layer."""
 
@@ -218,7 +238,7 @@ class GatedDeltaLayer(nn.Module):
     def mix(self, y: torch.Tensor, rows: BlockRows) -> torch.Tensor:
         """y: normed rows [rows, H] -> mixer features [rows, Hv * Dv] (input of the output projection)."""
         bs = rows.block_size
-        p = linear(y, self.w_in)
+        p = _adapted_linear(self, y, "w_in")
         plan = rows.head_parallel
         if plan is None:
             sh = _HeadShard(self)
@@ -242,6 +262,8 @@ class GatedDeltaLayer(nn.Module):
         cfg = self.cfg
         rows = attend.block_rows
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
+        if getattr(self, "lora", None) is not None:
+            return _adapted_mlp(self, h + _adapted_linear(self, self.mix(y, rows), "w_out"))
         h = linear_residual(self.mix(y, rows), self.w_out, h)
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
         return row_parallel_linear_residual(linear_swiglu(y2, self.w_gate_up), self.w_down, h, None, last=True)
@@ -260,10 +282,12 @@ class GatedAttentionLayer(nn.Module):
     def forward(self, h, positions, inv_freq, attend):
         cfg = self.cfg
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
-        qkv = qk_norm_rope(linear(y, self.w_qkv), positions, inv_freq, self.q_norm, self.k_norm,
+        qkv = qk_norm_rope(_adapted_linear(self, y, "w_qkv"), positions, inv_freq, self.q_norm, self.k_norm,
                            cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
-        gate = torch.sigmoid(linear(y, self.w_attn_gate).float())
+        gate = torch.sigmoid(_adapted_linear(self, y, "w_attn_gate").float())
         a = (attend(qkv, self.idx).float() * gate).to(h.dtype)
+        if getattr(self, "lora", None) is not None:
+            return _adapted_mlp(self, h + _adapted_linear(self, a, "w_o"))
         h = linear_residual(a, self.w_o, h)
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
         return row_parallel_linear_residual(linear_swiglu(y2, self.w_gate_up), self.w_down, h, None, last=True)

@@ -96,7 +96,7 @@ class TrainingSession:
         if spec.adapter.type == "lora":
             from ..adapters.lora import apply_lora
 
-            if self.cfg.is_moe or self.cfg.is_hybrid or getattr(self.model, "tp", None) is not None:
+            if self.cfg.is_moe or getattr(self.model, "tp", None) is not None:
                 raise ValueError("LoRA adapters support dense models on one tensor-parallel rank")
             self.lora = apply_lora(self.model, rank=spec.adapter.rank, alpha=spec.adapter.alpha,
                                    dropout=spec.adapter.dropout, targets=spec.adapter.targets or ("attention", "mlp"),
