@@ -71,6 +71,18 @@ def transformer_step_flops(cfg: ModelConfig, *, rows: int, pairs: int, vocab_row
     else:
         ffn = 3 * h * cfg.intermediate_size
     per_row = h * cfg.qkv_dim + cfg.q_dim * h + ffn
+    if cfg.is_hybrid:
+        # linear-attention layers: fused input projection + output projection + MLP per row, and per row
+        # and value head the recurrence products (state read for u and o, state write, the intra-chunk
+        # C x C terms are small next to them): about 3 · Dk · Dv multiply-adds forward
+        n_full = sum(cfg.layer_kind(i) == "full_attention" for i in range(cfg.num_layers))
+        n_lin = cfg.num_layers - n_full
+        lin_row = h * cfg.linear_in_dim + cfg.linear_value_dim * h + ffn
+        full_row = per_row + h * cfg.q_dim                       # output gate
+        dense = 6.0 * rows * (n_full * full_row + n_lin * lin_row)
+        recurrence = 6.0 * rows * n_lin * cfg.linear_num_value_heads * 3 * cfg.linear_key_head_dim * cfg.linear_value_head_dim
+        attention = 12.0 * pairs * cfg.q_dim * n_full + recurrence
+        return StepFlops(dense, attention, 6.0 * vocab_rows * h * cfg.vocab_size)
     dense = 6.0 * rows * per_row * cfg.num_layers
     attention = 12.0 * pairs * cfg.q_dim * cfg.num_layers      # 4·pairs·D per head fwd, ×3 fwd+bwd
     head = 6.0 * vocab_rows * h * cfg.vocab_size
