@@ -258,3 +258,34 @@ def test_lora_on_the_hybrid_family_trains_adapters_only_and_merges():
         model.lora = None
         merged = _packed(model, clean, noisy, layout)
     assert torch.allclose(with_adapters, merged, atol=2e-4, rtol=1e-3)
+
+
+def test_hybrid_hugging_face_round_trip(tmp_path):
+    from turbo_dllm_b200.models.hf_loader import export_hf_checkpoint, load_hf_config, load_hf_weights
+
+    a = HybridBlockDiffusionTransformer(CFG, dtype=torch.float32, seed=11, init_std=0.05)
+    with torch.no_grad():
+        for n, p in a.flat.params.items():          # make every tensor distinctive, norms and biases included
+            if not p.decay:
+                p.add_(torch.randn_like(p) * 0.1)
+    path = export_hf_checkpoint(a, str(tmp_path / "hf"))
+    cfg = load_hf_config(path)
+    assert cfg.is_hybrid and cfg.linear_num_value_heads == CFG.linear_num_value_heads
+    assert [cfg.layer_kind(i) for i in range(cfg.num_layers)] == list(a.layer_kinds)
+    from safetensors import safe_open
+
+    with safe_open(path + "/model.safetensors", framework="pt") as f:
+        keys = set(f.keys())
+        q = f.get_tensor("model.layers.3.self_attn.q_proj.weight")
+    assert "model.layers.0.linear_attn.in_proj_qkv.weight" in keys and "model.layers.0.linear_attn.A_log" in keys
+    assert q.shape == (2 * CFG.q_dim, CFG.hidden_size)
+    # per head: query rows then gate rows
+    D = CFG.head_dim
+    assert torch.equal(q[:D], a.layers[3].w_qkv[:D]) and torch.equal(q[D:2 * D], a.layers[3].w_attn_gate[:D])
+    import dataclasses
+
+    b = HybridBlockDiffusionTransformer(dataclasses.replace(cfg, mask_token_id=CFG.mask_token_id),
+                                        dtype=torch.float32, seed=99, init_std=0.02)
+    load_hf_weights(b, path)
+    for n, p in a.flat.params.items():
+        assert torch.equal(p, b.flat.params[n]), n

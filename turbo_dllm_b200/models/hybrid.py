@@ -334,7 +334,10 @@ class HybridBlockDiffusionTransformer(BlockDiffusionTransformer):
         hv = self.cfg.linear_num_value_heads
         for name, p in self.flat.params.items():
             leaf = name.split(".")[-1]
-            if leaf == "conv_b":
+            if leaf == "w_in":         # rows past q | k | v | z | b | a only pad the GEMM's N; nothing reads them
+                c = self.cfg
+                p[c.linear_conv_channels + c.linear_value_dim + 2 * c.linear_num_value_heads:].zero_()
+            elif leaf == "conv_b":
                 p.zero_()
             elif leaf == "conv_w":       # starts close to "take the current token"
                 p.mul_(0.0)
