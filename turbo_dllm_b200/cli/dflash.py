@@ -55,7 +55,11 @@ def run_dflash(argv) -> int:
             print(json.dumps({"files": sorted(ex.export_dflash_drafter(s.model, spec, a.output)["files"])}))
             return 0
         if a.cmd == "validate-export":
-            problems = ex.validate_dflash_export(a.path)
+            import os
+
+            # a DFlash2 export carries config.json with its architecture; check its tensor inventory too
+            is_v2 = os.path.exists(os.path.join(a.path, "config.json"))
+            problems = ex.validate_dflash2_export(a.path) if is_v2 else ex.validate_dflash_export(a.path)
             print(json.dumps({"ok": not problems, "problems": problems}))
             return 0 if not problems else 1
         if a.cmd in ("serve-sglang", "serve-vllm"):
