@@ -99,7 +99,7 @@ def test_barrier_wait_runs_out_and_reports():
     assert float(torch.ones(4, device="cuda").sum()) == 4.0
 
 
-def _csbp(rank, world, transport, steps):
+def _csbp(rank, world, transport, steps, model="synthetic:tiny-hd128", objective="standard_block_diffusion"):
     import os
 
     import torch.distributed as dist
@@ -113,8 +113,8 @@ def _csbp(rank, world, transport, steps):
     torch.cuda.set_device(rank)
     cp = 2 if world > 1 else 1
     spec = RunSpec.from_mapping({
-        "model": {"id": "synthetic:tiny-hd128", "seq_len": 1024, "dtype": "bf16"},
-        "objective": {"name": "standard_block_diffusion", "block_size": 32, "sampling_epsilon_min": 0.1},
+        "model": {"id": model, "seq_len": 1024, "dtype": "bf16"},
+        "objective": {"name": objective, "block_size": 32, "sampling_epsilon_min": 0.1},
         "training": {"batch_size": 2, "steps": steps},
         "topology": {"context_parallel_size": cp, "block_parallel_size": cp},
         "kernel": {"cp_bp_clean_kv_transport": transport, "impl": "nccl_baseline"},
@@ -139,6 +139,19 @@ def test_csbp2_on_gpus_matches_single_gpu(transport):
     _need(2)
     ref = run_ranks(_csbp, 1, args=("collective", 3), backend=None, deadline_s=300)[0]
     outs = run_ranks(_csbp, 2, args=(transport, 3), backend="nccl", deadline_s=300)
+    for losses, params in outs:
+        assert losses == pytest.approx(ref[0], rel=3e-2)
+        assert (torch.from_numpy(params) - torch.from_numpy(ref[1])).abs().max().item() < 3e-2
+
+
+@pytest.mark.distributed
+def test_hybrid_csbp2_on_gpus_matches_single_gpu():
+    """Gated DeltaNet layers under context sharding: row shards traded for head shards over NCCL
+    (`parallel/head_sequence.py`), state-scan kernels on each rank's heads."""
+    _need(2)
+    args = ("collective", 2, "synthetic:tiny-qwen3_8-hd128", "fast_dllm_v2")
+    ref = run_ranks(_csbp, 1, args=args, backend=None, deadline_s=300)[0]
+    outs = run_ranks(_csbp, 2, args=args, backend="nccl", deadline_s=300)
     for losses, params in outs:
         assert losses == pytest.approx(ref[0], rel=3e-2)
         assert (torch.from_numpy(params) - torch.from_numpy(ref[1])).abs().max().item() < 3e-2
