@@ -155,3 +155,56 @@ def test_native_sft_session_step_with_self_conditioning():
     assert l0 == l0 and l1 == l1 and l0 > 0 and l1 > 0
     assert abs(l0 - l1) > 1e-6, "feeding the first pass back must change the prediction"
     assert g1.abs().sum() > 0 and not torch.allclose(g0, g1)
+
+
+def test_clean_causal_layout_hides_later_tokens_of_the_block():
+    import torch
+
+    from turbo_dllm_b200.parallel.layout import build_packed_layout
+
+    a = build_packed_layout(seq_len=16, block_size=4, batch=2, views=1)
+    b = build_packed_layout(seq_len=16, block_size=4, batch=2, views=1, clean_causal=True)
+    n = a.n_noisy
+    assert torch.equal(a.mask.q_hi[:n], b.mask.q_hi[:n])                # noisy rows unchanged
+    stride = 1 << 24
+    assert torch.equal(b.mask.q_hi[n:].long(), a.clean_seq * stride + a.clean_pos + 1)
+    assert torch.equal(a.mask.q_hi[n:].long(), a.clean_seq * stride + (a.clean_pos // 4 + 1) * 4)
+    assert b.clean_causal and not a.clean_causal
+
+
+def test_native_sft_encoder_next_token_term():
+    """With objective.encoder_loss_weight > 0 the clean stream is causal and adds Σ CE(h[p] -> x[p+1]) / pairs;
+    the clean hidden state at p must then not depend on the token at p + 1."""
+    import torch
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    def session(weight):
+        spec = RunSpec.from_mapping({
+            "model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "family": "diffusion_gemma",
+                      "num_layers": 2},
+            "objective": {"name": "diffusiongemma_native_sft", "block_size": 16, "loss_weighting": "unit",
+                          "self_conditioning_probability": 0.0, "encoder_loss_weight": weight},
+            "training": {"batch_size": 2, "steps": 1, "skip_optimizer_step": True},
+            "optimizer": {"lr": 1e-3}}).validate()
+        return TrainingSession(spec, device="cpu")
+
+    s0, s1 = session(0.0), session(1.0)
+    assert not s0.layout.clean_causal and s1.layout.clean_causal
+    r0, r1 = s0.step(), s1.step()
+    l0, l1 = float(r0.loss_sum) / r0.denominator, float(r1.loss_sum) / r1.denominator
+    enc = float(s1.last_encoder_loss)
+    assert s0.last_encoder_loss is None and enc > 0
+    assert l1 > l0 and abs(enc - 6.9) < 1.0          # ~ln(1024) at initialisation
+    # causality of the clean stream: change the last token of a block, earlier clean rows keep their states
+    lay = s1.layout
+    tokens = torch.randint(0, 1000, (lay.rows,), generator=torch.Generator().manual_seed(0))
+    with torch.no_grad():
+        h_a = s1.model(tokens, lay.positions, s1.attend)
+        t2 = tokens.clone()
+        row = lay.n_noisy + 15                         # sequence 0, position 15 (end of block 0)
+        t2[row] = (t2[row] + 1) % 1000
+        h_b = s1.model(t2, lay.positions, s1.attend)
+    assert torch.allclose(h_a[lay.n_noisy:row], h_b[lay.n_noisy:row], atol=1e-6)
+    assert not torch.allclose(h_a[row], h_b[row], atol=1e-4)

@@ -224,7 +224,8 @@ class DiffusionGemmaNativeRuntime(StandardBlockDiffusionRuntime):
     (seed, batch counter), so the resumable state is still just the counter.
 
     Semantics follow dllm_parallel/core/objectives/diffusiongemma.py:66-460 (all-block corruption over
-    the scored region; its separate encoder next-token term is not part of this runtime).
+    the scored region). The separate encoder next-token term is added by the training session
+    (`training/session.py::forward_backward`), which also makes the clean rows attend causally for it.
     """
     name = "diffusiongemma_native_sft"
     views = 1

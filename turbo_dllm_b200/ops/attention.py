@@ -216,13 +216,15 @@ def block_diffusion_layout(noisy_pos: torch.Tensor, noisy_group: torch.Tensor, c
                            block_size: int, *, noisy_seq: torch.Tensor | None = None,
                            clean_seq: torch.Tensor | None = None, seq_stride: int = 1 << 24,
                            window: int | None = None, key_clean_pos: torch.Tensor | None = None,
-                           key_clean_seq: torch.Tensor | None = None) -> MaskLayout:
+                           key_clean_seq: torch.Tensor | None = None, clean_causal: bool = False) -> MaskLayout:
     """Layout for packed rows `[noisy ; clean]` attending to keys `[noisy ; clean keys]`.
 
     noisy_pos/noisy_group: position and unique noisy-block id of each noisy row (the id must be
     distinct across sequences and views); clean_pos: position of each clean query row.
     `key_clean_*` default to the clean query rows (self-attention); a context-parallel rank passes
-    the gathered or peer-owned clean key positions instead. `window` limits clean visibility to
+    the gathered or peer-owned clean key positions instead. With `clean_causal` a clean row sees the clean
+    tokens up to and including itself instead of its whole block (the clean stream then is an ordinary
+    causal model whose hidden states may carry a next-token loss); noisy rows are unaffected. `window` limits clean visibility to
     the last `window` positions before the row's clean stop (sliding-window layers).
     Semantics: dllm_parallel/core/models/backbones/nemotron/model.py:3486-3520 and
     dllm_parallel/core/attention/context_parallel_attention.py:119-144.
@@ -236,7 +238,7 @@ def block_diffusion_layout(noisy_pos: torch.Tensor, noisy_group: torch.Tensor, c
     ks = (cs if key_clean_pos is None else
           (torch.zeros_like(kpos) if key_clean_seq is None else key_clean_seq.to(i64)))
     n_stop = (noisy_pos // block_size) * block_size
-    c_stop = (clean_pos // block_size + 1) * block_size
+    c_stop = clean_pos + 1 if clean_causal else (clean_pos // block_size + 1) * block_size
     stop = torch.cat([n_stop, c_stop])
     seq = torch.cat([ns, cs])
     start = torch.zeros_like(stop) if window is None else (stop - window).clamp_min(0)

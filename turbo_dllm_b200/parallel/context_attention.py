@@ -226,7 +226,7 @@ class ContextParallelAttention:
                     m = block_diffusion_layout(layout.noisy_pos, layout.noisy_group, layout.clean_pos,
                                                layout.block_size, noisy_seq=layout.noisy_seq,
                                                clean_seq=layout.clean_seq, key_clean_pos=kpos[r],
-                                               key_clean_seq=kseq[r])
+                                               key_clean_seq=kseq[r], clean_causal=layout.clean_causal)
                     if r > 0:   # only the first shard carries the noisy keys
                         m.k_code = m.k_code[layout.n_noisy:].contiguous()
                     self.shard_masks.append(m)
@@ -238,7 +238,7 @@ class ContextParallelAttention:
         self.mask = block_diffusion_layout(layout.noisy_pos, layout.noisy_group, layout.clean_pos,
                                            layout.block_size, noisy_seq=layout.noisy_seq,
                                            clean_seq=layout.clean_seq, key_clean_pos=torch.cat(kpos),
-                                           key_clean_seq=torch.cat(kseq))
+                                           key_clean_seq=torch.cat(kseq), clean_causal=layout.clean_causal)
 
     def shard_kv(self, qkv, r: int) -> torch.Tensor:
         """K|V rows attended in streaming step r: (noisy rows if r == 0) + owner r's clean rows."""

@@ -80,6 +80,7 @@ class PackedLayout:
     positions: torch.Tensor      # [rows] RoPE positions of [noisy ; clean]
     mask: MaskLayout             # attention mask over the rank's own rows (keys = own rows)
     block_size: int
+    clean_causal: bool = False   # clean rows attend causally (token by token) instead of block-causally
 
     @property
     def n_noisy(self) -> int:
@@ -96,7 +97,7 @@ class PackedLayout:
 
 def build_packed_layout(*, seq_len: int, block_size: int, batch: int, views: int = 1,
                         owned_blocks=None, clean_pos: torch.Tensor | None = None,
-                        window: int | None = None, device="cpu") -> PackedLayout:
+                        window: int | None = None, device="cpu", clean_causal: bool = False) -> PackedLayout:
     """Rows of one rank: for every sequence and view the noisy rows of `owned_blocks`, then for
     every sequence the clean rows `clean_pos` (default: all positions)."""
     nblocks = seq_len // block_size
@@ -115,6 +116,6 @@ def build_packed_layout(*, seq_len: int, block_size: int, batch: int, views: int
     clean_pos_all = cpos1.repeat(batch)
     clean_seq = seq_ids.repeat_interleave(cpos1.numel())
     mask = block_diffusion_layout(noisy_pos, noisy_group, clean_pos_all, block_size, noisy_seq=noisy_seq,
-                                  clean_seq=clean_seq, window=window)
+                                  clean_seq=clean_seq, window=window, clean_causal=clean_causal)
     return PackedLayout(noisy_pos, noisy_seq, noisy_view, noisy_group, clean_pos_all, clean_seq,
-                        torch.cat([noisy_pos, clean_pos_all]), mask, block_size)
+                        torch.cat([noisy_pos, clean_pos_all]), mask, block_size, clean_causal)

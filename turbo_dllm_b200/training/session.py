@@ -113,6 +113,11 @@ class TrainingSession:
         self.objective = build_objective_runtime(spec, mask_token_id=self.cfg.mask_token_id,
                                                  seed=seed + 7919 * (dp_rank + 1), device=self.device,
                                                  vocab_size=self.cfg.vocab_size)
+        # diffusiongemma_native_sft: the clean stream is causal and carries a next-token loss of its own
+        # (dllm_parallel/core/models/backbones/nemotron/model.py:1089-1096, :1966-2030)
+        self.encoder_loss_weight = (float(spec.objective.encoder_loss_weight)
+                                    if self.objective.name == "diffusiongemma_native_sft" else 0.0)
+        self.last_encoder_loss = None
         data_kw = dict(batch_size=spec.training.batch_size, seq_len=spec.model.seq_len,
                        vocab_size=self.cfg.vocab_size, mask_token_id=self.cfg.mask_token_id,
                        seed=seed + 104729 * (dp_rank + 1), vocab_sample_size=spec.data.vocab_sample_size)
@@ -255,7 +260,8 @@ class TrainingSession:
             clean = torch.arange(0, last * s.objective.block_size, device=self.device)
         return build_packed_layout(seq_len=s.model.seq_len, block_size=s.objective.block_size,
                                    batch=s.training.batch_size, views=self.objective.views,
-                                   owned_blocks=owned, clean_pos=clean, device=self.device)
+                                   owned_blocks=owned, clean_pos=clean, device=self.device,
+                                   clean_causal=getattr(self, "encoder_loss_weight", 0.0) > 0.0)
 
     def _build_head_parallel_plan(self):
         """Row bookkeeping of the head <-> sequence exchange that linear-attention layers use when the
@@ -339,11 +345,26 @@ class TrainingSession:
         cb = self.objective.corrupt(batch.input_ids, supervision_mask=batch.supervision_mask,
                                     supervision_count=batch.supervision_count)
         tokens, labels, weights = self.assemble_rows(cb)
+        n_noisy = self.layout.n_noisy
+        if self.encoder_loss_weight > 0.0:
+            # clean row (s, p) predicts the clean token at p + 1; the term has its own denominator (pairs of
+            # consecutive tokens over the whole step), folded into the row weights so that one division by
+            # the decoder's denominator normalises both terms
+            lay, x0 = self.layout, cb.clean_input_ids
+            nxt = (lay.clean_pos + 1).clamp_max(x0.shape[1] - 1)
+            enc_labels = torch.where(lay.clean_pos + 1 < x0.shape[1], x0[lay.clean_seq, nxt],
+                                     torch.full_like(nxt, -100))
+            labels = torch.cat([labels[:n_noisy], enc_labels.to(labels.dtype)])
+            enc_w = self.encoder_loss_weight * float(denominator) / self._encoder_denominator
+            weights = torch.cat([weights[:n_noisy], torch.full_like(weights[n_noisy:], enc_w)])
         soft, soft_rows = self._self_conditioning_inputs(tokens, cb)
         hidden = self.model(tokens, self.layout.positions, self.attend, soft, soft_rows)
         self.memory_report("after forward")
-        h, l, w, _ = compact_supervised_rows(hidden, labels, weights)
-        loss_sum, _ = self.model.loss(h, l, w, self.objective.exclude_mask_token)
+        h, l, w, kept = compact_supervised_rows(hidden, labels, weights)
+        loss_sum, per_row = self.model.loss(h, l, w, self.objective.exclude_mask_token)
+        if self.encoder_loss_weight > 0.0 and per_row is not None:
+            clean_rows = kept >= n_noisy
+            self.last_encoder_loss = (per_row.detach()[clean_rows].sum() / self._encoder_denominator)
         self.memory_report("after loss")
         (loss_sum / denominator).backward()
         self.memory_report("after backward")
@@ -409,6 +430,9 @@ class TrainingSession:
             self._grad_div = scale
         else:
             denom = self.global_denominator(batches)
+            if self.encoder_loss_weight > 0.0:
+                b0, l0 = batches[0].input_ids.shape
+                self._encoder_denominator = float(max(b0 * (l0 - 1) * len(batches) * self.dp_size, 1))
             for b in batches:
                 ls, n, _ = self.forward_backward(b, denom)
                 total += ls.float()
