@@ -8,9 +8,12 @@ pytestmark = pytest.mark.gpu
 def _spec(dtype, objective="fast_dllm_v2", model="synthetic:tiny-hd128"):
     from turbo_dllm_b200.config.run_spec import RunSpec
 
+    extra = {}
+    if objective == "diffusiongemma_native_sft":   # causal clean stream + encoder next-token term (weight 1)
+        extra = {"loss_weighting": "unit", "self_conditioning_probability": 0.0}
     return RunSpec.from_mapping({
         "model": {"id": model, "seq_len": 256, "dtype": dtype},
-        "objective": {"name": objective, "block_size": 32, "noise_schedule_epsilon": 0.1},
+        "objective": {"name": objective, "block_size": 32, "noise_schedule_epsilon": 0.1, **extra},
         "training": {"batch_size": 2, "steps": 2, "activation_checkpointing": True},
         "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
         "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate()
@@ -18,7 +21,8 @@ def _spec(dtype, objective="fast_dllm_v2", model="synthetic:tiny-hd128"):
 
 @pytest.mark.parametrize("objective,model", [("fast_dllm_v2", "synthetic:tiny-hd128"),
                                              ("standard_block_diffusion", "synthetic:tiny-hd128"),
-                                             ("fast_dllm_v2", "synthetic:tiny-qwen3_8-hd128")])
+                                             ("fast_dllm_v2", "synthetic:tiny-qwen3_8-hd128"),
+                                             ("diffusiongemma_native_sft", "synthetic:tiny-hd128")])
 def test_loss_and_grads_match_cpu_reference(objective, model):
     """The last case is the hybrid family: Gated DeltaNet layers (projections on the tcgen05 GEMM,
     recurrence as batched products) and a gated softmax-attention layer."""
