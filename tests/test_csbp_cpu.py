@@ -78,3 +78,35 @@ def test_harness_reports_failed_and_hung_ranks():
         run_ranks(_boom, 2, backend=None, deadline_s=20)
     with pytest.raises(AssertionError, match="did not finish"):
         run_ranks(_hang, 2, backend=None, deadline_s=3)
+
+
+def _modes(rank, world):
+    from turbo_dllm_b200.benchmarks.parallel_modes_bench import MODES, run_mode
+    from turbo_dllm_b200.config.run_spec import RunSpec
+
+    torch.set_num_threads(2)
+    spec = RunSpec.from_mapping(MAPPING)
+    return [run_mode(spec, m, device="cpu", steps=1, warmup=0) for m in MODES]
+
+
+@pytest.mark.distributed
+def test_parallel_modes_benchmark_agrees_between_layouts():
+    """Pure context parallelism, pure block parallelism with a replicated prefix and the fused layout
+    compute the same loss on the same data; the benchmark reports one record per mode."""
+    outs = run_ranks(_modes, 2, deadline_s=300)
+    recs = outs[0]
+    assert [r["mode"] for r in recs] == ["pure_cp", "pure_bp", "csbp"]
+    losses = [r["loss"] for r in recs]
+    assert losses[1] == pytest.approx(losses[0], rel=1e-4) and losses[2] == pytest.approx(losses[0], rel=1e-4)
+    assert all(r["ms_per_step"] > 0 and r["world"] == 2 for r in recs)
+
+
+@pytest.mark.distributed
+def test_pure_context_parallel_matches_single_process():
+    """CP 2 without block parallelism: both ranks compute every noisy block (the clean K/V are what is
+    sharded), so the loss terms exist twice and the step must still equal the single-process one."""
+    ref_losses, ref_params = _run(0, 1, 1, 1, 2, "standard_block_diffusion")
+    outs = run_ranks(_run, 2, args=(2, 1, 2, "standard_block_diffusion"), deadline_s=240)
+    for losses, params in outs:
+        assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
+        assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=2e-5)

@@ -397,8 +397,13 @@ class TrainingSession:
         """Loss denominator of the whole optimizer step over all data-parallel ranks."""
         b, l = batches[0].input_ids.shape
         per = (l - 1) if self.objective.name == "fast_dllm_v2" else l
+        # pure context parallelism (no block parallelism) keeps every noisy block on every rank of the context
+        # group: their loss terms are computed that many times and the summed gradients must be divided by it
+        rt = self.runtime
+        copies = (rt.context_parallel_size if rt is not None and rt.context_parallel_size > 1
+                  and rt.block_parallel_size == 1 else 1)
         if all(x.supervision_mask is None for x in batches):
-            return float(b * per * len(batches) * self.dp_size)
+            return float(b * per * len(batches) * self.dp_size * copies)
         cnt = torch.zeros(1, dtype=torch.float64, device=self.device)
         for x in batches:
             m = x.supervision_mask
@@ -407,7 +412,7 @@ class TrainingSession:
             dist.all_reduce(cnt)
             bpcp = (self.runtime.local_parallel_size * self.runtime.tensor_parallel_size) if self.runtime else 1
             cnt /= bpcp
-        return float(cnt)
+        return float(cnt) * copies
 
     def step(self) -> StepResult:
         spec = self.spec
