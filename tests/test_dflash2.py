@@ -239,3 +239,42 @@ def test_dflash2_export_round_trip(tmp_path):
     with open(os.path.join(out, "model.safetensors"), "ab") as f:
         f.write(b"x")
     assert validate_dflash2_export(out) != []
+
+
+def _dflash2_dp(rank, world):
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    torch.set_num_threads(2)
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "family": "dflash",
+                  "verifier_id": "synthetic:tiny-qwen3", "target_layer_ids": [0, 2], "max_layers": 2,
+                  "dflash2_conv_kernel_size": 2, "dflash2_conv_group_size": 64, "dflash2_selector_rank": 4,
+                  "dflash2_selector_top_k": 2},
+        "objective": {"name": "dflash_distillation", "block_size": 8, "max_anchors": 4, "dflash_loss": "dpace",
+                      "lk_loss_type": "lambda", "dflash_vocab_block_size": 512},
+        "data": {"target_features": "online"}, "training": {"batch_size": 1, "steps": 2},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
+        "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
+    s = TrainingSession(spec, device="cpu")
+    batch = s.data.next_batch()
+    s.model.flat.zero_grad()
+    _, _, denom = s.task.forward_backward(batch)
+    local = torch.tensor(float(denom))
+    both = [torch.zeros(()) for _ in range(world)]
+    dist.all_gather(both, local)
+    for _ in range(2):
+        s.step()
+    return [float(x) for x in both], s.model.flat.data.clone()
+
+
+@pytest.mark.distributed
+def test_dflash2_denominator_is_shared_by_the_data_parallel_ranks():
+    from tests._harness import run_ranks
+
+    outs = run_ranks(_dflash2_dp, 2, deadline_s=240)
+    (d0, p0), (d1, p1) = outs
+    assert d0[0] == pytest.approx(d0[1]) and d0 == pytest.approx(d1)      # same global count on both ranks
+    assert (p0 == p1).all()                                                # replicas stay in sync

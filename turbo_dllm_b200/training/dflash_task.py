@@ -145,11 +145,18 @@ class DFlashTask:
         w_rows = weights.reshape(-1).index_select(0, rows)
         # cross-entropy / total-variation mix. d(1 - p)/dh = p * d(ce)/dh, so the total-variation
         # term is a cross-entropy whose row weights carry the detached probability.
+        # sums over all data-parallel ranks: weighted supervised count, accepted probability mass, supervised count
+        stats = torch.stack([w_rows.sum(), (full_p * mask).sum(), mask.sum()]).detach().clone()
+        world = 1
+        if torch.distributed.is_available() and torch.distributed.is_initialized():
+            world = torch.distributed.get_world_size()
+            if world > 1:
+                torch.distributed.all_reduce(stats)
         ce_share = 1.0
         if o.lk_loss_type == "tv":
             ce_share = 0.0
         elif o.lk_loss_type == "lambda":
-            acceptance = (full_p * mask).sum() / mask.sum().clamp_min(1.0)
+            acceptance = stats[1] / stats[2].clamp_min(1.0)
             ce_share = float(o.kl_scale) * float(torch.exp(-float(o.kl_decay) * acceptance))
         eff = w_rows * (ce_share + (1.0 - ce_share) * prob)
         grad_carrier, ce, _, unary, cand = frozen_linear_ce_topk(hidden, head, labels, loss_weights=eff, **kw)
@@ -171,5 +178,7 @@ class DFlashTask:
             selector_num = (sel_ce * sel_w).sum()
             self.last_objective_metrics["selector_loss"] = (selector_num.detach() / sel_w.sum().clamp_min(1.0))
         self.last_objective_metrics.update(target_probability=prob.mean(), selector_coverage=covered.float().mean())
-        return token_num + self.effective_selector_loss_alpha * selector_num, w_rows.sum().clamp_min(
-            torch.finfo(torch.float32).tiny).detach()
+        # the session averages per-rank losses over the ranks: dividing by (global count / ranks) makes that
+        # average the global sum over the global count
+        denom = (stats[0] / world).clamp_min(torch.finfo(torch.float32).tiny)
+        return token_num + self.effective_selector_loss_alpha * selector_num, denom
