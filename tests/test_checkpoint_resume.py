@@ -95,3 +95,36 @@ def test_auto_resume_policy(tmp_path):
     save_training_checkpoint(str(d), s, step=1, rank=0, world_size=1)
     assert resolve_load_checkpoint(spec) == (str(d), "latest")
     assert [should_save(spec, st, 4, 0.0) for st in (1, 2, 3, 4)] == [False, True, False, True]
+
+
+@pytest.mark.checkpoint_resume
+@pytest.mark.parametrize("kind", ["hybrid", "dflash2"])
+def test_resume_of_the_hybrid_family_and_the_dflash2_drafter(tmp_path, kind):
+    """Same contract as above for the models with extra state: recurrence parameters and convolutions
+    (hybrid), selector codebooks and the selector loss schedule (DFlash2)."""
+    if kind == "hybrid":
+        mapping = {"model": {"id": "synthetic:tiny-qwen3_8", "family": "qwen3_8", "seq_len": 64, "dtype": "fp32"},
+                   "objective": {"name": "fast_dllm_v2", "block_size": 16}}
+    else:
+        mapping = {"model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "family": "dflash",
+                             "verifier_id": "synthetic:tiny-qwen3", "target_layer_ids": [0, 2], "max_layers": 2,
+                             "dflash2_conv_kernel_size": 2, "dflash2_conv_group_size": 64,
+                             "dflash2_selector_rank": 4, "dflash2_selector_top_k": 2},
+                   "objective": {"name": "dflash_distillation", "block_size": 8, "max_anchors": 4,
+                                 "dflash_loss": "dpace", "selector_ramp_ratio": 0.5, "dflash_vocab_block_size": 512},
+                   "data": {"target_features": "online"}}
+    spec = RunSpec.from_mapping({
+        **mapping, "training": {"batch_size": 1, "steps": 4},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
+        "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0},
+        "checkpointing": {"save_checkpoint_dir": str(tmp_path / "ck")}}).validate()
+    a = TrainingSession(spec, device="cpu")
+    full = [float(a.step().loss_sum) for _ in range(4)]
+    b = TrainingSession(spec, device="cpu")
+    first = [float(b.step().loss_sum) for _ in range(2)]
+    save_training_checkpoint(str(tmp_path / "ck"), b, step=2, rank=0, world_size=1)
+    c = TrainingSession(spec, device="cpu")
+    load_training_checkpoint(str(tmp_path / "ck"), "latest", c, rank=0, world_size=1)
+    rest = [float(c.step().loss_sum) for _ in range(2)]
+    assert first + rest == full
+    assert torch.equal(c.model.flat.data, a.model.flat.data)
