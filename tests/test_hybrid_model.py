@@ -289,3 +289,28 @@ def test_hybrid_hugging_face_round_trip(tmp_path):
     load_hf_weights(b, path)
     for n, p in a.flat.params.items():
         assert torch.equal(p, b.flat.params[n]), n
+
+
+def test_head_shards_partition_the_projection_and_plan_checks_coverage():
+    from turbo_dllm_b200.models.hybrid import HeadParallelPlan
+
+    model = HybridBlockDiffusionTransformer(CFG, dtype=torch.float32, seed=1)
+    layer = model.layers[0]
+    shards = [_HeadShard(layer, r, 2) for r in range(2)]
+    cols = torch.cat([s.columns for s in shards])
+    real = CFG.linear_conv_channels + CFG.linear_value_dim + 2 * CFG.linear_num_value_heads
+    assert cols.numel() == real and torch.equal(cols.sort().values, torch.arange(real))
+    assert shards[0].hk == CFG.linear_num_key_heads // 2 and shards[1].A_log.shape[0] == CFG.linear_num_value_heads // 2
+    with pytest.raises(ValueError):
+        _HeadShard(layer, 0, 4)          # two key heads cannot be split four ways
+    blocks = (torch.zeros(2, dtype=torch.long), torch.tensor([0, 8]))
+    ok = HeadParallelPlan(group=None, index=0, noisy_blocks=[blocks, blocks],
+                          clean_positions=[torch.arange(0, 8), torch.arange(8, 16)], batch=1, seq_len=16,
+                          block_size=8, device="cpu")
+    assert ok.total_rows == 2 * (16 + 8) and ok.row_counts == [24, 24]
+    # gathered row of (sequence 0, position p): rank 0 holds positions 0..7 after its 16 noisy rows
+    assert ok.clean_rows.tolist() == list(range(16, 24)) + list(range(40, 48))
+    with pytest.raises(ValueError):      # position 8..15 missing, 0..7 twice
+        HeadParallelPlan(group=None, index=0, noisy_blocks=[blocks, blocks],
+                         clean_positions=[torch.arange(0, 8), torch.arange(0, 8)], batch=1, seq_len=16,
+                         block_size=8, device="cpu")
