@@ -278,3 +278,22 @@ def test_dflash2_denominator_is_shared_by_the_data_parallel_ranks():
     (d0, p0), (d1, p1) = outs
     assert d0[0] == pytest.approx(d0[1]) and d0 == pytest.approx(d1)      # same global count on both ranks
     assert (p0 == p1).all()                                                # replicas stay in sync
+
+
+def test_topk_scan_and_gather_dot_in_small_chunks():
+    """Row and vocabulary chunking must not change the candidates, their order or the gradients."""
+    from turbo_dllm_b200.ops.dflash2 import _GatherDot, _topk_candidates
+
+    torch.manual_seed(8)
+    h, w = torch.randn(21, 12), torch.randn(97, 12)
+    ids = _topk_candidates(h, w, 5, 10, 1.0, None, row_chunk=4)
+    want = (h @ w.t()).topk(5, dim=-1).indices
+    assert torch.equal(ids, want)
+    capped = _topk_candidates(h, w, 3, 97, 2.0, 30.0, row_chunk=100)   # a cap far from saturation: no ties
+    assert torch.equal(capped, transform_logits(h @ w.t(), 2.0, 30.0).topk(3, dim=-1).indices)
+    a = h.clone().requires_grad_(True)
+    b = h.clone().requires_grad_(True)
+    g = torch.randn(21, 5)
+    (_GatherDot.apply(a, w, ids, 4) * g).sum().backward()
+    (torch.einsum("nh,nkh->nk", b, w[ids]) * g).sum().backward()
+    assert torch.allclose(a.grad, b.grad, atol=1e-5)
