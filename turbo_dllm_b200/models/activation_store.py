@@ -35,6 +35,11 @@ class ActivationStore:
         # attention outputs of layers >= this index stay on the device even when the others are offloaded
         # (the backward pass needs the last layers first, while earlier ones are still being fetched)
         self.attention_resident_from = 1 << 30
+        # how many layers ahead the backward pass fetches offloaded tensors (TDLLM_PREFETCH_DEPTH; each layer in
+        # flight holds its tensors in device memory until it is consumed)
+        import os
+
+        self.prefetch_depth = max(1, int(os.environ.get("TDLLM_PREFETCH_DEPTH", "1")))
 
     def has(self, idx) -> bool:
         return idx in self.kept or idx in self.ready
@@ -105,8 +110,9 @@ class _LayerCheckpoint(torch.autograd.Function):
     def backward(ctx, dout):
         store, idx = ctx.store, ctx.idx
         h = store.fetch(idx)
-        for key in (idx - 1, (idx - 1, "attn_out"), (idx - 1, "attn_lse")):
-            store.prefetch(key)
+        for d in range(1, store.prefetch_depth + 1):   # host -> device copies of the layers the backward pass needs next
+            for key in (idx - d, (idx - d, "attn_out"), (idx - d, "attn_lse")):
+                store.prefetch(key)
         h = h.detach().requires_grad_(True)
         from ..ops.gemm import skip_last_output
 
