@@ -111,7 +111,7 @@ def _csbp(rank, world, transport, steps, model="synthetic:tiny-hd128", objective
 
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
-    cp = 2 if world > 1 else 1
+    cp = world
     spec = RunSpec.from_mapping({
         "model": {"id": model, "seq_len": 1024, "dtype": "bf16"},
         "objective": {"name": objective, "block_size": 32, "sampling_epsilon_min": 0.1},
@@ -134,7 +134,7 @@ def _csbp(rank, world, transport, steps, model="synthetic:tiny-hd128", objective
 
 
 @pytest.mark.distributed
-@pytest.mark.parametrize("transport", ["collective", "peer_pull", "streaming"])
+@pytest.mark.parametrize("transport", ["collective", "peer_pull", "streaming", "fused"])
 def test_csbp2_on_gpus_matches_single_gpu(transport):
     _need(2)
     ref = run_ranks(_csbp, 1, args=("collective", 3), backend=None, deadline_s=300)[0]
@@ -142,6 +142,91 @@ def test_csbp2_on_gpus_matches_single_gpu(transport):
     for losses, params in outs:
         assert losses == pytest.approx(ref[0], rel=3e-2)
         assert (torch.from_numpy(params) - torch.from_numpy(ref[1])).abs().max().item() < 3e-2
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("world", [4, 8])
+def test_csbp_fused_transport_on_4_and_8_gpus_matches_single_gpu(world):
+    """The in-kernel pull / push at group sizes where a rank has several peers: segment tables, the
+    staggered peer order and ragged tile boundaries between the peers' rows."""
+    _need(world)
+    ref = run_ranks(_csbp, 1, args=("collective", 2), backend=None, deadline_s=300)[0]
+    outs = run_ranks(_csbp, world, args=("fused", 2), backend="nccl", deadline_s=300)
+    for losses, params in outs:
+        assert losses == pytest.approx(ref[0], rel=3e-2)
+        assert (torch.from_numpy(params) - torch.from_numpy(ref[1])).abs().max().item() < 3e-2
+
+
+def test_fused_pull_gives_up_when_a_peer_never_signals():
+    """Host-made failure on one GPU: the context-sharded forward is told about a peer whose "rows staged"
+    flag nothing ever sets. The pullers' bounded wait must run out, the error record must name the pull
+    side of the kernel, every other warp must leave its loop, and the context must stay usable."""
+    import ctypes
+
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.ops.attention import INT_MIN, MaskLayout, block_diffusion_layout
+    from turbo_dllm_b200.parallel import context_attention as ca  # noqa: F401
+    from turbo_dllm_b200.parallel import symm  # noqa: F401
+
+    V, I, LL, F = native.c_void_p, native.c_int, native.c_ll, native.c_float
+    native.register_signatures({
+        "tdllm_attn_fwd_csbp": (I, [V] * 6 + [I, I, LL, I, I] + [LL] * 4 + [V] * 7 + [I, F, V, V, V, I, I, I, V, V, I, V]),
+    })
+    lib = native.lib()
+    dev = torch.device("cuda")
+    Hq, Hkv, D, bs = 4, 2, 128, 32
+    pos = torch.arange(256, device=dev)
+    # this rank: noisy and clean rows of positions 128..255; the "peer" owns the clean rows 0..127, which every
+    # local query attends to
+    loc = block_diffusion_layout(pos[128:], pos[128:] // bs, pos[128:], bs)
+    rem = block_diffusion_layout(pos[128:], pos[128:] // bs, pos[128:], bs, key_clean_pos=pos[:128])
+    mask = MaskLayout(loc.q_lo, loc.q_hi, loc.q_grp, torch.cat([loc.k_code, rem.k_code[128:]]).contiguous())
+    L = mask.tile_lists()
+    qkv = torch.randn(256, (Hq + 2 * Hkv) * D, device=dev, dtype=torch.bfloat16)
+    staged = torch.zeros(128, 2 * Hkv * D, device=dev, dtype=torch.bfloat16)
+    kv_rem = torch.empty_like(staged)
+    out = torch.empty(256, Hq * D, device=dev, dtype=torch.bfloat16)
+    lse = torch.empty(Hq, L["nq_pad"], device=dev, dtype=torch.float32)
+    ready = torch.zeros(64, dtype=torch.int32, device=dev)
+    tiles = torch.zeros(4, dtype=torch.int32, device=dev)
+    two = lambda t: (ctypes.c_void_p * 2)(t.data_ptr(), t.data_ptr())
+    counts = (ctypes.c_longlong * 2)(128, 128)
+    lib.tdllm_clear_error()
+    native.check(lib.tdllm_set_wait_timeout_ns(2_000_000), "timeout")
+    try:
+        q, k, v = qkv[:, : Hq * D], qkv[:, Hq * D:(Hq + Hkv) * D], qkv[:, (Hq + Hkv) * D:]
+        native.check(lib.tdllm_attn_fwd_csbp(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), kv_rem.data_ptr(), out.data_ptr(), lse.data_ptr(), 256, 256,
+            128, Hq, Hkv, qkv.stride(0), qkv.stride(0), qkv.stride(0), out.stride(0), L["q_lo"].data_ptr(),
+            L["q_hi"].data_ptr(), L["q_grp"].data_ptr(), L["k_code"].data_ptr(), L["f_ptr"].data_ptr(),
+            L["f_idx"].data_ptr(), L["f_order"].data_ptr(), L["nqt"], 1.0 / D ** 0.5, two(staged), two(ready), counts,
+            0, 2, 1, tiles[3:].data_ptr(), tiles.data_ptr(), 1, None), "attn_fwd_csbp")
+        torch.cuda.synchronize()
+        err = native.device_error()
+        assert err["code"] == 1 and err["kernel"] == 6, err
+    finally:
+        lib.tdllm_clear_error()
+        lib.tdllm_set_wait_timeout_ns(2_000_000_000)
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0
+    # the same call with the flag set completes and equals attention over the concatenated keys
+    ready.fill_(1)
+    staged.copy_(torch.randn_like(staged))
+    tiles.zero_()
+    native.check(lib.tdllm_attn_fwd_csbp(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), kv_rem.data_ptr(), out.data_ptr(), lse.data_ptr(), 256, 256,
+        128, Hq, Hkv, qkv.stride(0), qkv.stride(0), qkv.stride(0), out.stride(0), L["q_lo"].data_ptr(),
+        L["q_hi"].data_ptr(), L["q_grp"].data_ptr(), L["k_code"].data_ptr(), L["f_ptr"].data_ptr(),
+        L["f_idx"].data_ptr(), L["f_order"].data_ptr(), L["nqt"], 1.0 / D ** 0.5, two(staged), two(ready), counts,
+        0, 2, 1, tiles[3:].data_ptr(), tiles.data_ptr(), 1, None), "attn_fwd_csbp")
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    assert torch.equal(kv_rem, staged)
+    from turbo_dllm_b200.ops.attention import attention_reference
+    kall = torch.cat([k.reshape(256, Hkv, D), staged[:, : Hkv * D].reshape(128, Hkv, D)])
+    vall = torch.cat([v.reshape(256, Hkv, D), staged[:, Hkv * D:].reshape(128, Hkv, D)])
+    ref, ref_lse = attention_reference(q.reshape(256, Hq, D), kall, vall, mask)
+    assert (out.view(256, Hq, D).float() - ref.float()).abs().max().item() < 2e-2
+    assert (lse[:, :256] - ref_lse).abs().max().item() < 2e-2
 
 
 @pytest.mark.distributed

@@ -97,6 +97,17 @@ int tdllm_attn_fwd(const void* q, const void* k, const void* v, void* o, float* 
                    const int* k_code, const int* tile_ptr, const int* tile_idx, const int* order,
                    int n_qtiles, float scale, void* stream);
 
+// Context-sharded forward: keys = this rank's rows, then the peers' clean K|V rows, pulled from the peers'
+// staged rows into kv_rem by two extra warps per CTA while the tiles of local keys run (see
+// attention_fwd_sm100.cu for the argument contract).
+int tdllm_attn_fwd_csbp(const void* q, const void* k_loc, const void* v_loc, void* kv_rem, void* o, float* lse,
+                        int nq, int nk_loc, long long n_rem, int Hq, int Hkv, long long ldq, long long ldk,
+                        long long ldv, long long ldo, const int* q_lo, const int* q_hi, const int* q_grp,
+                        const int* k_code, const int* tile_ptr, const int* tile_idx, const int* order,
+                        int n_qtiles, float scale, void* const* staging, void* const* ready,
+                        const long long* counts, int rank, int world, int ready_epoch, int* counter,
+                        int* tile_ready, int launch_no, void* stream);
+
 // dq/dk/dv may point into one packed [rows, (Hq+2Hkv)*128] buffer; delta is fp32 scratch
 // [2, Hq, n_qtiles*128]; f_* lists are per query tile, b_* lists per key tile.
 int tdllm_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
@@ -120,6 +131,19 @@ int tdllm_attn_bwd_fused(const void* q, const void* k, const void* v, const void
                          const int* k_code, const int* w_ptr, const int* w_idx, const int* w_order,
                          int n_work, int n_qtiles, int n_ktiles, float scale, void* stream);
 
+// Context-sharded one-pass backward: gradients of the peers' key rows are added to the owners' fp32
+// accumulators through peer memory from the kernel's epilogue (see attention_bwd_host.cu).
+int tdllm_attn_bwd_fused_csbp(const void* q, const void* k_loc, const void* v_loc, const void* kv_rem,
+                              const void* o, const void* dout, void* dq, void* dk, void* dv, const float* lse,
+                              float* delta, float* dq_acc, void* const* acc_dk, void* const* acc_dv,
+                              long long acc_rows, void* next_acc, long long next_bytes, int nq, int nk_loc,
+                              long long n_rem, int Hq, int Hkv, long long ldq, long long ldk, long long ldv,
+                              long long ldo, long long lddo, long long lddq, long long lddk, long long lddv,
+                              const int* q_lo, const int* q_hi, const int* q_grp, const int* k_code,
+                              const int* w_ptr, const int* w_idx, const int* w_order, int n_work, int n_qtiles,
+                              int n_ktiles, float scale, const long long* counts, const long long* dst_row0,
+                              void* const* flags, int rank, int world, int epoch, void* stream);
+
 // Issue-rate probe of tcgen05.mma (128 x n x 16, bf16): out[0] = cycles in the issue loop of one
 // thread, out[1] = cycles until the last MMA completed.
 int tdllm_mma_issue_probe(int n, int iters, int a_from_tmem, int accs, int uniform, int ctas,
@@ -132,6 +156,8 @@ int tdllm_ipc_get_handle(void* p, void* handle_out64);
 int tdllm_ipc_open(const void* handle64, void** out);
 int tdllm_ipc_close(void* p);
 int tdllm_symm_barrier(void* const* flag_ptrs, int rank, int world, int epoch, void* stream);
+// the arriving half of the barrier alone (consumers wait inside their own kernels)
+int tdllm_symm_signal(void* const* flag_ptrs, int rank, int world, int epoch, void* stream);
 int tdllm_zero_fused_step(void* const* grad_ptrs, void* const* param_ptrs, void* const* sumsq_ptrs,
                           void* const* flag_ptrs, float* master, float* m, float* v, int rank,
                           int world, long long start, long long n, long long decay_end, float lr,

@@ -30,6 +30,16 @@
 // goes to shared memory as bf16 (one 128-byte swizzled row of 64 queries per key): the B operand
 // of the dQᵀ product, whose A operand is the K tile read MN-major (same bytes as the Sᵀ product).
 //
+// Context-sharded form (template argument CSBP): key tiles [0, nlt) are this rank's own rows, key tiles from
+// nlt on are clean rows of the other ranks of the context-parallel group (their K|V were brought into
+// kv_rem by the forward kernel). The dK/dV partial sums of a remote key tile never touch this GPU's memory:
+// the epilogue adds them, fp32, straight into the owner's accumulator through peer memory (vector
+// red.add over NVLink, one 16-byte packet per four values), while later work items of the grid are still in
+// their products. The owner casts its accumulator once every rank has passed the barrier that follows the
+// kernel. Replaces the clean-gradient reduce-scatter of
+// dllm_parallel/core/attention/context_parallel_attention.py:760-885 and its overlap with the local
+// backward (:2292-2312).
+//
 // Reference counterpart: the masked FlashAttention backward
 // (third_party/flash-attention/hopper/mainloop_bwd_sm90_tma_gmma_ws.hpp, FA4
 // flash_bwd_sm100.py: five products, dQ by reduce-add) and the owner-major clean dK/dV
@@ -60,6 +70,18 @@ constexpr int OFF_STAT = OFF_BARS + 512;      // [stage][lse2 64 | delta_s 64] f
 constexpr int SMEM_BYTES = OFF_STAT + STAGES * 128 * 4;
 static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
 static_assert(OFF_Q + 2 * 65536 <= OFF_RED, "dK/dV staging must not reach the dQ staging rows");
+
+constexpr int MAX_PEERS = 16;
+// Where the gradients of remote key rows go: segment s = the rows of one peer, in the order of the forward
+// pull (rank+1, rank+2, ...).
+struct PushPlan {
+  float* dk[MAX_PEERS];               // segment s: the owner's dK accumulator [rows][Hkv*128] fp32 (peer memory)
+  float* dv[MAX_PEERS];
+  long long seg_begin[MAX_PEERS + 1]; // first remote row of segment s
+  long long dst_row0[MAX_PEERS];      // row of the owner's accumulator that takes the segment's first row
+  long long n_rows;                   // remote rows
+  int nseg, nlt;
+};
 
 struct Params {
   int nq_pad, Hq, Hkv;
@@ -93,11 +115,20 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
 __device__ __forceinline__ bool key_visible(int code, int lo, int hi, int grp) {
   return code >= 0 ? (code >= lo && code < hi) : (code == grp);
 }
+__device__ __forceinline__ void red_add_peer_f32x4(float* dst, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(a)),
+               "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+               : "memory");
+}
+
+template <bool CSBP>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const __grid_constant__ CUtensorMap tm_dkacc, const __grid_constant__ CUtensorMap tm_dvacc,
-                      const __grid_constant__ CUtensorMap tm_dqacc, const Params p) {
+                      const __grid_constant__ CUtensorMap tm_dqacc, const __grid_constant__ CUtensorMap tm_kr,
+                      const __grid_constant__ CUtensorMap tm_vr, const Params p,
+                      const __grid_constant__ PushPlan pp) {
   extern __shared__ __align__(1024) uint8_t smem[];
   if (smem_u32(smem) & 1023u) {   // swizzled tiles need 1 KiB alignment; nothing has been set up yet
     if (threadIdx.x == 0) set_error(ERR_BAD_INDEX, KID, 1);
@@ -163,10 +194,14 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_do);
       mbar_expect_tx(bar_kv, 2 * KV_TILE_BYTES);
+      const bool remote = CSBP && kt >= pp.nlt;
+      const CUtensorMap* mk = remote ? &tm_kr : &tm_k;
+      const CUtensorMap* mv = remote ? &tm_vr : &tm_v;
+      const int krow = (remote ? kt - pp.nlt : kt) * 128;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        tma_load_2d(smem_u32(sK + c * KV_HALF_BYTES), &tm_k, bar_kv, kvh * HD + c * 64, kt * 128);
-        tma_load_2d(smem_u32(sV + c * KV_HALF_BYTES), &tm_v, bar_kv, kvh * HD + c * 64, kt * 128);
+        tma_load_2d(smem_u32(sK + c * KV_HALF_BYTES), mk, bar_kv, kvh * HD + c * 64, krow);
+        tma_load_2d(smem_u32(sV + c * KV_HALF_BYTES), mv, bar_kv, kvh * HD + c * 64, krow);
       }
       int st = 0;
       uint32_t ph = 0;
@@ -426,7 +461,29 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     // buffers, which nothing reads any more once the last product has completed)
     bool ok = !error_is_set();
     if (ok && items > 0) ok = mbar_wait_spin(bar_done, 0, KID, 31);
-    if (ok && items > 0) {
+    if (CSBP && ok && items > 0 && kt >= pp.nlt) {
+      // a peer's key rows: this thread's row (TMEM lane) goes to the owner's accumulator, 64 of the 128
+      // columns per thread (the two groups of a slot split them), four values per packet
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + ((uint32_t)(qd * 32) << 16) + 256 + b * 128;
+      const long long rrow = (long long)(kt - pp.nlt) * 128 + row;
+      int s = 0;
+      while (s + 1 < pp.nseg && rrow >= pp.seg_begin[s + 1]) ++s;
+      const bool live = rrow < pp.n_rows;
+      float* base = b ? pp.dk[s] : pp.dv[s];
+      float* dst = base + (pp.dst_row0[s] + (rrow - pp.seg_begin[s])) * ((long long)p.Hkv * HD) + kvh * HD;
+      uint32_t rs[32];
+#pragma unroll 1
+      for (int c = 2 * sub; c < 2 * sub + 2; ++c) {
+        tmem_ld32(t_acc + c * 32, rs);
+        tmem_ld_wait();
+        if (live) {
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            red_add_peer_f32x4(dst + c * 32 + 4 * v, rs[4 * v], rs[4 * v + 1], rs[4 * v + 2], rs[4 * v + 3]);
+        }
+      }
+    } else if (ok && items > 0) {
       tc_fence_after();
       const uint32_t t_acc = tmem_base + ((uint32_t)(qd * 32) << 16) + 256 + b * 128;
       uint8_t* stg = smem + OFF_Q + b * 65536;

@@ -22,6 +22,17 @@
 // third_party/flash-attention/hopper/mask.h:165 (BDLM mask), dllm_parallel/core/attention/fa4.py:71-132
 // (mask_mod) and the predicate of dllm_parallel/core/attention/context_parallel_attention.py:119-144.
 // It returns (out, lse) so shard results can be merged across K/V owners.
+//
+// Context-sharded form (template argument CSBP): key tiles [0, nlt) are this rank's own rows and are read
+// in place; key tiles [nlt, nlt + nrt) are clean K|V rows owned by the peers of the context-parallel group.
+// Two extra warps per CTA ("pullers") fetch those rows from the peers' symmetric staging buffers with plain
+// 16-byte peer loads into a buffer in this GPU's memory, 16 rows per claim from a shared counter, and count
+// finished claims per key tile; the TMA warp waits (bounded) for a remote tile's count before it loads the
+// tile. Each remote row crosses NVLink once, the tiles of this rank run while the first remote rows arrive,
+// and the pull of later tiles overlaps the products of earlier ones. No TMA touches a peer's memory.
+// Counterpart: the asynchronous clean K/V all-gather overlapped with the local attention in
+// dllm_parallel/core/attention/context_parallel_attention.py:2315-2691 (:701-741 for the gather itself).
+#include <cstring>
 #include "common.cuh"
 #include "api.h"
 
@@ -36,6 +47,10 @@ constexpr int TILE_BYTES = 128 * HD * 2;  // 32 KiB: two 64-column halves of 128
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int KV_STAGES = 2;
 constexpr int THREADS = 576;   // 16 softmax warps (2 heads x 2 column halves x 4 lane quarters), TMA warp 16, MMA warp 17
+constexpr int THREADS_CSBP = 640;   // + puller warps 18 and 19
+constexpr int KID_PULL = 6;         // error-record id of the pull side of the context-sharded form
+constexpr int MAX_PEERS = 16;
+constexpr int PULL_ROWS = 16;       // rows per claim; a 128-row key tile is complete after 8 claims
 constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 512 + 2048 + 1024;   // + barriers + row exchange
 
 struct FwdParams {
@@ -51,6 +66,21 @@ struct FwdParams {
   float* lse;          // [Hq, nq_pad]
   float scale_log2;    // softmax scale * log2(e)
   float scale;         // softmax scale
+};
+
+// Pull plan of the context-sharded form. The remote rows form segments, one per peer, in the order this
+// rank visits its peers (rank+1, rank+2, ... so that no owner serves every puller at once).
+struct PullPlan {
+  const uint4* src[MAX_PEERS];        // segment s: the peer's staged rows (peer memory)
+  const int* ready[MAX_PEERS];        // segment s: word in THIS rank's flag array that the peer sets to `want`
+  long long seg_begin[MAX_PEERS + 1]; // first remote row of segment s (prefix sums of the peers' row counts)
+  uint4* dst;                         // [n_rows][row_vec16] in this GPU's memory
+  int* counter;                       // claim counter, zero at launch
+  int* tile_ready;                    // [nrt] finished claims per remote key tile, cumulative over launches
+  long long n_rows;
+  int nseg, want, row_vec16;
+  int nlt, nrt;                       // local and remote key tiles
+  int tile_target;                    // count a remote tile has reached when all its rows of this launch are in
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -79,10 +109,90 @@ __device__ __forceinline__ bool key_visible(int code, int lo, int hi, int grp) {
   return code >= 0 ? (code >= lo && code < hi) : (code == grp);
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+__device__ __forceinline__ uint4 ld_peer16(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+// bounded wait on a counter in this GPU's memory that other CTAs of the launch advance
+__device__ __forceinline__ bool count_wait_geq(const int* flag, int want, int kernel_id, int detail) {
+  const unsigned long long t0 = globaltimer_ns();
+  const unsigned long long budget = g_tdllm_timeout_ns;
+#pragma unroll 1
+  while (true) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= want) return true;
+    if (error_is_set()) return false;
+    if (globaltimer_ns() - t0 > budget) {
+      set_error(ERR_WAIT_TIMEOUT, kernel_id, detail);
+      return false;
+    }
+    __nanosleep(32);
+  }
+}
+
+// One puller warp: claims 16-row pieces of the remote rows until none is left.
+__device__ __forceinline__ void pull_remote_rows(const PullPlan& pl, int lane) {
+  const int n_claims = pl.nrt * (BKV / PULL_ROWS);
+  uint32_t seen = 0;   // segments whose owner has been seen ready
+#pragma unroll 1
+  while (true) {
+    int c = 0;
+    if (lane == 0) c = atomicAdd(pl.counter, 1);
+    c = __shfl_sync(0xffffffffu, c, 0);
+    if (c >= n_claims) break;
+    long long row = (long long)c * PULL_ROWS;
+    const long long row_end = min(row + PULL_ROWS, pl.n_rows);
+    bool ok = true;
+#pragma unroll 1
+    while (row < row_end) {
+      int s = 0;
+      while (s + 1 < pl.nseg && row >= pl.seg_begin[s + 1]) ++s;
+      const long long run_end = min(row_end, pl.seg_begin[s + 1]);
+      if (!((seen >> s) & 1u)) {
+        int good = 1;
+        if (lane == 0) good = flag_wait_geq(pl.ready[s], pl.want, KID_PULL, s) ? 1 : 0;
+        if (!__shfl_sync(0xffffffffu, good, 0)) { ok = false; break; }
+        seen |= 1u << s;
+      }
+      const uint4* src = pl.src[s] + (row - pl.seg_begin[s]) * pl.row_vec16;
+      uint4* dst = pl.dst + row * pl.row_vec16;
+      const long long n = (run_end - row) * pl.row_vec16;
+#pragma unroll 1
+      for (long long i = lane; i < n; i += 32 * 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (i + u * 32 < n) v[u] = ld_peer16(src + i + u * 32);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (i + u * 32 < n) dst[i + u * 32] = v[u];
+      }
+      row = run_end;
+    }
+    if (!ok) break;   // the error record is set: every waiter of the launch leaves its loop
+    // the rows are read by TMA (async proxy) in other CTAs: order them before the count
+    fence_proxy_async_global();
+    __threadfence();
+    __syncwarp();
+    if (lane == 0)
+      asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(pl.tile_ready + c / (BKV / PULL_ROWS)) : "memory");
+  }
+}
+
+template <bool CSBP>
+__global__ void __launch_bounds__(CSBP ? THREADS_CSBP : THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-                const FwdParams p) {
+                const __grid_constant__ CUtensorMap tm_kr, const __grid_constant__ CUtensorMap tm_vr,
+                const FwdParams p, const __grid_constant__ PullPlan pl) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;                                   // 2 heads x 32 KiB
@@ -148,6 +258,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
+      if (CSBP) {
+        tma_prefetch_desc(&tm_kr);
+        tma_prefetch_desc(&tm_vr);
+      }
       mbar_expect_tx(bar_q, 2 * TILE_BYTES);
 #pragma unroll
       for (int i = 0; i < 2; ++i)
@@ -158,18 +272,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int j = 0; j < n; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int kt = list[j] >> 1;
+        int kt = list[j] >> 1;
+        const CUtensorMap* mk = &tm_k;
+        const CUtensorMap* mv = &tm_v;
+        if (CSBP && kt >= pl.nlt) {
+          // a peer's rows: wait until the pullers have brought the whole tile into local memory
+          kt -= pl.nlt;
+          if (!count_wait_geq(pl.tile_ready + kt, pl.tile_target, KID_PULL, 100)) break;
+          fence_proxy_async_global();
+          mk = &tm_kr;
+          mv = &tm_vr;
+        }
         if (!mbar_wait_spin(bar_kempty + 8 * s, ph ^ 1, KID, 10)) break;
         mbar_expect_tx(bar_kfull + 8 * s, TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < 2; ++c)
-          tma_load_2d(smem_u32(sK + s * TILE_BYTES + c * HALF_BYTES), &tm_k, bar_kfull + 8 * s,
+          tma_load_2d(smem_u32(sK + s * TILE_BYTES + c * HALF_BYTES), mk, bar_kfull + 8 * s,
                       kvh * HD + c * 64, kt * BKV);
         if (!mbar_wait_spin(bar_vempty + 8 * s, ph ^ 1, KID, 11)) break;
         mbar_expect_tx(bar_vfull + 8 * s, TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < 2; ++c)
-          tma_load_2d(smem_u32(sV + s * TILE_BYTES + c * HALF_BYTES), &tm_v, bar_vfull + 8 * s,
+          tma_load_2d(smem_u32(sV + s * TILE_BYTES + c * HALF_BYTES), mv, bar_vfull + 8 * s,
                       kvh * HD + c * 64, kt * BKV);
       }
     }
@@ -234,6 +358,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       __syncwarp();
     }
+  } else if (CSBP && warp >= 18) {
+    // ------------------------------ pullers (context-sharded form) -------------
+    pull_remote_rows(pl, lane);
   } else {
     // ------------------------------ softmax groups -----------------------------
     // four warps per (head, column half): a thread owns one query row and 64 of the tile's 128 keys;
@@ -390,6 +517,19 @@ int encode_rows_tmap(CUtensorMap* out, const void* base, long long cols, long lo
 }
 }  // namespace tdllm_host
 
+static int attn_fwd_check(const char* who, int Hq, int Hkv, const long long* lds, const void* const* ptrs, int n) {
+  if (Hq % Hkv || (Hq / Hkv) % 2) {
+    tdllm_host::set_last_error("%s: query heads per KV head must be even (got %d/%d)", who, Hq, Hkv);
+    return 1;
+  }
+  for (int i = 0; i < n; ++i)
+    if ((lds[i] % 8) || ((uintptr_t)ptrs[i] % 16)) {
+      tdllm_host::set_last_error("%s: operand %d needs a 16-byte aligned base and row stride", who, i);
+      return 1;
+    }
+  return 0;
+}
+
 // q [nq, Hq*128] (row stride ldq), k/v [nk, Hkv*128], o [nq, Hq*128], lse [Hq, nq_pad].
 // Row metadata arrays are padded to nq_pad / nk_pad (multiples of 128) by the caller.
 extern "C" int tdllm_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
@@ -400,18 +540,12 @@ extern "C" int tdllm_attn_fwd(const void* q, const void* k, const void* v, void*
                               void* stream) {
   using namespace tdllm::attn;
   if (nq <= 0) return 0;
-  if (Hq % Hkv || (Hq / Hkv) % 2) {
-    tdllm_host::set_last_error("attn_fwd: query heads per KV head must be even (got %d/%d)", Hq, Hkv);
-    return 1;
-  }
-  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8) || ((uintptr_t)q % 16) ||
-      ((uintptr_t)k % 16) || ((uintptr_t)v % 16) || ((uintptr_t)o % 16)) {
-    tdllm_host::set_last_error("attn_fwd: operands need 16-byte aligned base and row stride");
-    return 1;
-  }
+  const long long lds[4] = {ldq, ldk, ldv, ldo};
+  const void* ptrs[4] = {q, k, v, o};
+  if (attn_fwd_check("attn_fwd", Hq, Hkv, lds, ptrs, 4)) return 1;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM_BYTES);
     if (e != cudaSuccess) {
       tdllm_host::set_last_error("attn_fwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -432,11 +566,107 @@ extern "C" int tdllm_attn_fwd(const void* q, const void* k, const void* v, void*
   p.lse = lse;
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
+  PullPlan pl;
+  memset(&pl, 0, sizeof(pl));
   const int grid = n_qtiles * Hkv * (Hq / Hkv / 2);
-  attn_fwd_kernel<<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(tq, tk, tv, to, p);
+  attn_fwd_kernel<false><<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(tq, tk, tv, to, tk, tv, p, pl);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     tdllm_host::set_last_error("attn_fwd launch: %s", cudaGetErrorString(e));
+    return 4;
+  }
+  return 0;
+}
+
+// Context-sharded forward. Keys are this rank's nk_loc rows (k_loc / v_loc, read in place) followed, from key
+// tile ceil(nk_loc / 128) on, by the clean K|V rows of the other ranks of the group: kv_rem
+// [n_rem, 2*Hkv*128] bf16 in this GPU's memory is filled inside the kernel from the peers' staged rows
+// (staging[r]: rank r's [counts[r], 2*Hkv*128] rows as mapped here; peers are visited in the order rank+1,
+// rank+2, ...). ready[r]: rank r's int32[world] flag array as mapped here; rank r stores `ready_epoch` into
+// slot r of every array once its rows are staged (tdllm_symm_signal). counter: one int32 of scratch, zeroed
+// here; tile_ready: int32 per remote key tile, zeroed once by the caller and never reset, with `launch_no`
+// the 1-based number of this call on those counters. k_code and the tile lists index the concatenated keys.
+extern "C" int tdllm_attn_fwd_csbp(const void* q, const void* k_loc, const void* v_loc, void* kv_rem, void* o,
+                                   float* lse, int nq, int nk_loc, long long n_rem, int Hq, int Hkv,
+                                   long long ldq, long long ldk, long long ldv, long long ldo, const int* q_lo,
+                                   const int* q_hi, const int* q_grp, const int* k_code, const int* tile_ptr,
+                                   const int* tile_idx, const int* order, int n_qtiles, float scale,
+                                   void* const* staging, void* const* ready, const long long* counts, int rank,
+                                   int world, int ready_epoch, int* counter, int* tile_ready, int launch_no,
+                                   void* stream) {
+  using namespace tdllm::attn;
+  if (nq <= 0) return 0;
+  const long long ldr = 2LL * Hkv * HD;
+  const long long lds[5] = {ldq, ldk, ldv, ldo, ldr};
+  const void* ptrs[5] = {q, k_loc, v_loc, o, kv_rem};
+  if (attn_fwd_check("attn_fwd_csbp", Hq, Hkv, lds, ptrs, 5)) return 1;
+  if (world < 2 || world > MAX_PEERS || rank < 0 || rank >= world) {
+    tdllm_host::set_last_error("attn_fwd_csbp: 2..%d ranks (got %d)", MAX_PEERS, world);
+    return 1;
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_BYTES);
+    if (e != cudaSuccess) {
+      tdllm_host::set_last_error("attn_fwd_csbp: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return 2;
+    }
+    attr_set = true;
+  }
+  PullPlan pl;
+  memset(&pl, 0, sizeof(pl));
+  long long total = 0;
+  pl.nseg = world - 1;
+  for (int s = 0; s < world - 1; ++s) {
+    const int peer = (rank + 1 + s) % world;
+    pl.src[s] = (const uint4*)staging[peer];
+    pl.ready[s] = (const int*)ready[rank] + peer;
+    pl.seg_begin[s] = total;
+    total += counts[peer];
+  }
+  for (int s = world - 1; s <= MAX_PEERS; ++s) pl.seg_begin[s] = total;
+  if (total != n_rem) {
+    tdllm_host::set_last_error("attn_fwd_csbp: peers hold %lld rows, caller expects %lld", total, n_rem);
+    return 1;
+  }
+  pl.dst = (uint4*)kv_rem;
+  pl.counter = counter;
+  pl.tile_ready = tile_ready;
+  pl.n_rows = n_rem;
+  pl.want = ready_epoch;
+  pl.row_vec16 = (int)(ldr * 2 / 16);
+  pl.nlt = (nk_loc + BKV - 1) / BKV;
+  pl.nrt = (int)((n_rem + BKV - 1) / BKV);
+  pl.tile_target = launch_no * (BKV / PULL_ROWS);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemsetAsync(counter, 0, sizeof(int), st) != cudaSuccess) {
+    tdllm_host::set_last_error("attn_fwd_csbp: clearing the claim counter failed");
+    return 5;
+  }
+  CUtensorMap tq, tk, tv, to, tkr, tvr;
+  if (tdllm_host::encode_rows_tmap(&tq, q, (long long)Hq * HD, nq, ldq, 128)) return 3;
+  if (tdllm_host::encode_rows_tmap(&tk, k_loc, (long long)Hkv * HD, nk_loc, ldk, 128)) return 3;
+  if (tdllm_host::encode_rows_tmap(&tv, v_loc, (long long)Hkv * HD, nk_loc, ldv, 128)) return 3;
+  if (tdllm_host::encode_rows_tmap(&to, o, (long long)Hq * HD, nq, ldo, 128)) return 3;
+  const long long rem_rows = n_rem > 0 ? n_rem : 1;
+  if (tdllm_host::encode_rows_tmap(&tkr, kv_rem, (long long)Hkv * HD, rem_rows, ldr, 128)) return 3;
+  if (tdllm_host::encode_rows_tmap(&tvr, (const __nv_bfloat16*)kv_rem + (long long)Hkv * HD, (long long)Hkv * HD,
+                                   rem_rows, ldr, 128))
+    return 3;
+  FwdParams p;
+  p.nq_pad = n_qtiles * BQ;
+  p.Hq = Hq; p.Hkv = Hkv;
+  p.q_lo = q_lo; p.q_hi = q_hi; p.q_grp = q_grp; p.k_code = k_code;
+  p.tile_ptr = tile_ptr; p.tile_idx = tile_idx; p.order = order;
+  p.lse = lse;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const int grid = n_qtiles * Hkv * (Hq / Hkv / 2);
+  attn_fwd_kernel<true><<<grid, THREADS_CSBP, SMEM_BYTES, st>>>(tq, tk, tv, to, tkr, tvr, p, pl);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    tdllm_host::set_last_error("attn_fwd_csbp launch: %s", cudaGetErrorString(e));
     return 4;
   }
   return 0;

@@ -42,6 +42,15 @@ __global__ void barrier_kernel(PeerPtrs flags, int rank, int world, int epoch) {
   flag_wait_geq((const int*)flags.p[rank] + r, epoch, KID_BARRIER, r);  // wait for peer r
 }
 
+// The arriving half of the barrier alone: tells every peer that this rank's earlier work on the stream (e.g.
+// rows it staged for the peers to pull) is done. The peers wait inside the kernel that consumes it.
+__global__ void signal_kernel(PeerPtrs flags, int rank, int world, int epoch) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  flag_store_release((int*)flags.p[r] + rank, epoch);
+}
+
 __device__ __forceinline__ void acc8(const uint4& v, float* f) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
@@ -327,6 +336,14 @@ extern "C" int tdllm_symm_barrier(void* const* flag_ptrs, int rank, int world, i
   if (fill_peers(f, flag_ptrs, world)) return 1;
   comm::barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, rank, world, epoch);
   TD_CUDA(cudaGetLastError(), "symm_barrier launch");
+  return 0;
+}
+
+extern "C" int tdllm_symm_signal(void* const* flag_ptrs, int rank, int world, int epoch, void* stream) {
+  comm::PeerPtrs f;
+  if (fill_peers(f, flag_ptrs, world)) return 1;
+  comm::signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, rank, world, epoch);
+  TD_CUDA(cudaGetLastError(), "symm_signal launch");
   return 0;
 }
 

@@ -7,6 +7,13 @@ K/V cross GPUs in the forward pass and only clean dK/dV in the backward pass:
   collective transport : all-gather clean K|V  → one attention call → reduce-scatter clean dK|dV
   streaming transport  : one attention call per owner shard, (out, lse) merged with the
                          online-softmax merge, gradients returned to each owner
+  peer_pull transport  : the gather / scatter-reduce as stand-alone peer-memory copy kernels
+  fused transport      : the transfer happens INSIDE the attention kernels. Forward: extra warps of every
+                         CTA pull the peers' staged clean K|V rows into local memory while the tiles of this
+                         rank's own keys run; a remote tile is loaded once its rows have arrived. Backward:
+                         the epilogue of a remote key tile adds its dK/dV partial sums to the owner's fp32
+                         accumulator through peer memory; one barrier, then every rank casts its own rows.
+                         No staging of the gathered rows, no concatenation, no reduce-scatter call.
 
 The all-gather and reduce-scatter are autograd functions over torch.distributed (NCCL on GPUs,
 gloo on CPU ranks); the peer-memory pull kernels replace them on NVSwitch machines.
@@ -135,6 +142,121 @@ class _PeerGatherRows(torch.autograd.Function):
         return ctx.exchange.scatter_reduce(g.contiguous()), None
 
 
+class FusedKVExchange:
+    """State of the fused transport for one context-parallel group: two staging buffers for this rank's clean
+    K|V rows (peers pull from them), two sets of fp32 dK/dV accumulators (peers add into them), ready flags,
+    a barrier, and the per-tile arrival counters of the forward kernel. The two-deep alternation is safe
+    because a rank can only be one attention call ahead of its slowest peer: finishing call n needs every
+    peer's rows of call n, which a peer stages only after its own call n-1 has finished on its stream."""
+
+    def __init__(self, group, device, counts: list[int], n_noisy: list[int], rows_local: int, kv_cols: int):
+        import ctypes
+
+        from ..kernels import native
+        from .symm import SymmetricBarrier, SymmetricBuffer
+
+        V, I, LL, F = native.c_void_p, native.c_int, native.c_ll, native.c_float
+        native.register_signatures({
+            "tdllm_symm_signal": (I, [V, I, I, I, V]),
+            "tdllm_attn_fwd_csbp": (I, [V] * 6 + [I, I, LL, I, I] + [LL] * 4 + [V] * 7 + [I, F, V, V, V, I, I, I, V, V, I,
+                                                                                         V]),
+            "tdllm_attn_bwd_fused_csbp": (I, [V] * 14 + [LL, V, LL, I, I, LL, I, I] + [LL] * 8 + [V] * 7
+                                          + [I, I, I, F, V, V, V, I, I, I, V]),
+        })
+        self.native, self.device, self.group = native, device, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.counts, self.kv_cols = counts, kv_cols
+        self.n_rem = sum(c for r, c in enumerate(counts) if r != self.rank)
+        self.nlt = (rows_local + 127) // 128
+        self.nrt = (self.n_rem + 127) // 128
+        self.acc_rows = max((n + c + 127) // 128 * 128 for n, c in zip(n_noisy, counts))
+        self.staging = [SymmetricBuffer(max(max(counts), 1) * kv_cols * 2, group, device) for _ in range(2)]
+        half = self.acc_rows * (kv_cols // 2) * 4
+        self.acc_bytes = 2 * half
+        self.acc = [SymmetricBuffer(self.acc_bytes, group, device) for _ in range(2)]   # zeroed at allocation
+        self.acc_dk = [(ctypes.c_void_p * self.world)(*b.ptrs) for b in self.acc]
+        self.acc_dv = [(ctypes.c_void_p * self.world)(*[p + half for p in b.ptrs]) for b in self.acc]
+        self.ready = SymmetricBuffer(256, group, device)
+        self.barrier = SymmetricBarrier(group, device)
+        self.counts_arr = (ctypes.c_longlong * self.world)(*counts)
+        self.row0_arr = (ctypes.c_longlong * self.world)(*n_noisy)
+        self.tile_ready = torch.zeros(max(self.nrt, 1) + 1, dtype=torch.int32, device=device)
+        self.counter = self.tile_ready[-1:]
+        self.fwd_calls = 0
+        self.bwd_calls = 0
+        dist.barrier(group=group)
+
+    def close(self) -> None:
+        for b in (*self.staging, *self.acc, self.ready, self.barrier.buf):
+            b.close()
+
+
+class _FusedContextAttention(torch.autograd.Function):
+    """Packed qkv of this rank's rows -> attention output, keys = own rows + the peers' clean rows."""
+
+    @staticmethod
+    def forward(ctx, qkv, cpa):
+        from ..ops._util import ptr, stream
+
+        ex, c = cpa.exchange, cpa.cfg
+        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        n_noisy, rows = cpa.layout.n_noisy, qkv.shape[0]
+        q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
+        L = cpa.mask.tile_lists()
+        ex.fwd_calls += 1
+        n = ex.fwd_calls
+        stage = ex.staging[n & 1]
+        stage.as_tensor(torch.bfloat16, (rows - n_noisy) * ex.kv_cols).view(rows - n_noisy, ex.kv_cols).copy_(
+            qkv[n_noisy:, Hq * D:])
+        lib = ex.native.lib()
+        ex.native.check(lib.tdllm_symm_signal(ex.ready.ptr_array, ex.rank, ex.world, n, stream()), "symm_signal")
+        kv_rem = torch.empty(max(ex.n_rem, 1), ex.kv_cols, dtype=qkv.dtype, device=qkv.device)
+        out = torch.empty(rows, Hq * D, dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty(Hq, L["nq_pad"], dtype=torch.float32, device=qkv.device)
+        ex.native.check(lib.tdllm_attn_fwd_csbp(
+            ptr(q), ptr(k), ptr(v), ptr(kv_rem), ptr(out), ptr(lse), rows, rows, ex.n_rem, Hq, Hkv,
+            qkv.stride(0), qkv.stride(0), qkv.stride(0), out.stride(0), ptr(L["q_lo"]), ptr(L["q_hi"]),
+            ptr(L["q_grp"]), ptr(L["k_code"]), ptr(L["f_ptr"]), ptr(L["f_idx"]), ptr(L["f_order"]), L["nqt"],
+            1.0 / D ** 0.5, stage.ptr_array, ex.ready.ptr_array, ex.counts_arr, ex.rank, ex.world, n,
+            ptr(ex.counter), ptr(ex.tile_ready), n, stream()), "attn_fwd_csbp")
+        ctx.save_for_backward(qkv, kv_rem, out, lse)
+        ctx.cpa = cpa
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops._util import ptr, scratch, stream
+        from ..ops.attention import backward_chunk_tiles
+
+        qkv, kv_rem, out, lse = ctx.saved_tensors
+        cpa = ctx.cpa
+        ex, c = cpa.exchange, cpa.cfg
+        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        rows = qkv.shape[0]
+        q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
+        L = cpa.mask.tile_lists()
+        W = cpa.mask.backward_work(backward_chunk_tiles())
+        dout = dout.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = split_packed_qkv(dqkv, Hq, Hkv, D)
+        delta = torch.empty(2, Hq, L["nq_pad"], dtype=torch.float32, device=qkv.device)
+        dq_acc = scratch(qkv.device, L["nq_pad"] * Hq * D, key="attn_bwd_acc")
+        ex.bwd_calls += 1
+        n = ex.bwd_calls
+        cur, nxt = n & 1, (n + 1) & 1
+        e = ex.barrier.reserve(1)
+        ex.native.check(ex.native.lib().tdllm_attn_bwd_fused_csbp(
+            ptr(q), ptr(k), ptr(v), ptr(kv_rem), ptr(out), ptr(dout), ptr(dq), ptr(dk), ptr(dv), ptr(lse),
+            ptr(delta), ptr(dq_acc), ex.acc_dk[cur], ex.acc_dv[cur], ex.acc_rows, ex.acc[nxt].local, ex.acc_bytes,
+            rows, rows, ex.n_rem, Hq, Hkv, qkv.stride(0), qkv.stride(0), qkv.stride(0), out.stride(0),
+            dout.stride(0), dqkv.stride(0), dqkv.stride(0), dqkv.stride(0), ptr(L["q_lo"]), ptr(L["q_hi"]),
+            ptr(L["q_grp"]), ptr(L["k_code"]), ptr(W["w_ptr"]), ptr(W["w_idx"]), ptr(W["w_order"]), W["n_work"],
+            L["nqt"], L["nkt"], 1.0 / D ** 0.5, ex.counts_arr, ex.row0_arr, ex.barrier.buf.ptr_array, ex.rank,
+            ex.world, e, stream()), "attn_bwd_fused_csbp")
+        return dqkv, None
+
+
 class _StreamingAttention(torch.autograd.Function):
     """Streaming transport: one owner shard of clean K|V is resident at a time. Forward: for every
     owner, broadcast its shard, run the attention kernel on it and fold (out, lse) into the
@@ -231,6 +353,12 @@ class ContextParallelAttention:
                         m.k_code = m.k_code[layout.n_noisy:].contiguous()
                     self.shard_masks.append(m)
         self.exchange = None
+        if self.transport == "fused":
+            if dev.type != "cuda" or cfg.head_dim != 128:
+                raise ValueError("kernel.cp_bp_clean_kv_transport=fused needs CUDA devices with peer access "
+                                 "and head_dim 128")
+            self._init_fused(cfg, layout, kpos, kseq, counts, dev)
+            return
         if self.transport == "peer_pull":
             if dev.type != "cuda":
                 raise ValueError("kernel.cp_bp_clean_kv_transport=peer_pull needs CUDA devices with peer access")
@@ -239,6 +367,28 @@ class ContextParallelAttention:
                                            layout.block_size, noisy_seq=layout.noisy_seq,
                                            clean_seq=layout.clean_seq, key_clean_pos=torch.cat(kpos),
                                            key_clean_seq=torch.cat(kseq), clean_causal=layout.clean_causal)
+
+    def _init_fused(self, cfg, layout, kpos, kseq, counts, dev) -> None:
+        """Key order of the fused transport: this rank's rows, padding up to a 128-row tile boundary, then
+        the peers' clean rows in pull order (rank+1, rank+2, ...)."""
+        from ..ops.attention import INT_MIN, MaskLayout
+
+        cp, me = self.cp, self.cp_rank
+        order = [(me + 1 + s) % cp for s in range(cp - 1)]
+        local = layout.mask                                   # keys = own rows
+        rem = block_diffusion_layout(layout.noisy_pos, layout.noisy_group, layout.clean_pos, layout.block_size,
+                                     noisy_seq=layout.noisy_seq, clean_seq=layout.clean_seq,
+                                     key_clean_pos=torch.cat([kpos[r] for r in order]),
+                                     key_clean_seq=torch.cat([kseq[r] for r in order]),
+                                     clean_causal=layout.clean_causal)
+        rem_code = rem.k_code[layout.n_noisy:]
+        pad = (-layout.rows) % 128
+        k_code = torch.cat([local.k_code, torch.full((pad,), INT_MIN, dtype=torch.int32, device=dev), rem_code])
+        self.mask = MaskLayout(local.q_lo, local.q_hi, local.q_grp, k_code.contiguous())
+        n_noisy = [torch.zeros(1, dtype=torch.long, device=dev) for _ in range(cp)]
+        dist.all_gather(n_noisy, torch.tensor([layout.n_noisy], dtype=torch.long, device=dev), group=self.group)
+        self.exchange = FusedKVExchange(self.group, dev, counts, [int(t) for t in n_noisy], layout.rows,
+                                        2 * cfg.num_key_value_heads * cfg.head_dim)
 
     def shard_kv(self, qkv, r: int) -> torch.Tensor:
         """K|V rows attended in streaming step r: (noisy rows if r == 0) + owner r's clean rows."""
@@ -262,6 +412,8 @@ class ContextParallelAttention:
     def __call__(self, qkv, layer_idx):
         if self.transport == "streaming":
             return _StreamingAttention.apply(qkv, self)
+        if self.transport == "fused":
+            return _FusedContextAttention.apply(qkv, self)
         c = self.cfg
         Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
         n_noisy = self.layout.n_noisy

@@ -24,7 +24,7 @@ class CPBPPolicy:
     def __post_init__(self):
         if self.clean_kv_layout not in ("zigzag", "contiguous"):
             raise ValueError(f"unknown clean_kv_layout {self.clean_kv_layout!r}")
-        if self.clean_kv_transport not in ("collective", "streaming", "peer_pull"):
+        if self.clean_kv_transport not in ("collective", "streaming", "peer_pull", "fused"):
             raise ValueError(f"unknown clean_kv_transport {self.clean_kv_transport!r}")
 
 

@@ -304,7 +304,9 @@ class TrainingSession:
         try:
             from ..parallel.fused_zero import FusedZeroSync
 
-            return FusedZeroSync.create(self.model.flat, group)
+            # the buffer the optimizer owns: the adapters when LoRA freezes the base model
+            lora = getattr(self, "lora", None)
+            return FusedZeroSync.create(lora.flat if lora is not None else self.model.flat, group)
         except Exception as e:  # no peer access, IPC refused, ...: keep the NCCL path, say why
             if self.spec.optimizer.backend == "zero_fused":
                 raise
@@ -470,13 +472,21 @@ class TrainingSession:
         extra = {}
         if self.expert_optimizer is not None:
             extra = {"expert_model": self.model.flat_experts.data, "expert_optimizer": self.expert_optimizer.state_dict()}
+        if getattr(self, "lora", None) is not None:
+            # the adapters are what training changes; every rank holds the whole (replicated) adapter buffer
+            extra["adapter"] = self.lora.flat.data
         return {**extra, "model": self.model.flat.data, "optimizer": self.optimizer.state_dict(),
                 "scheduler": self.scheduler.state_dict(), "objective": self.objective.state_dict(),
                 "data": self.data.state_dict(), "steps_done": self.steps_done}
 
     def load_state_dict(self, state: dict) -> None:
         self.model.flat.data.copy_(state["model"])
+        if getattr(self, "lora", None) is not None and "adapter" in state:
+            self.lora.flat.data.copy_(state["adapter"])
         self.optimizer.load_state_dict(state["optimizer"])
+        # the optimizer restored this rank's shard of its buffer from the fp32 master; the other shards come
+        # from their owners (a no-op on one rank)
+        self.optimizer._all_gather_params()
         if self.expert_optimizer is not None and "expert_model" in state:
             self.model.flat_experts.data.copy_(state["expert_model"])
             self.expert_optimizer.load_state_dict(state["expert_optimizer"])
