@@ -168,10 +168,6 @@ def test_fused_pull_gives_up_when_a_peer_never_signals():
     from turbo_dllm_b200.parallel import context_attention as ca  # noqa: F401
     from turbo_dllm_b200.parallel import symm  # noqa: F401
 
-    V, I, LL, F = native.c_void_p, native.c_int, native.c_ll, native.c_float
-    native.register_signatures({
-        "tdllm_attn_fwd_csbp": (I, [V] * 6 + [I, I, LL, I, I] + [LL] * 4 + [V] * 7 + [I, F, V, V, V, I, I, I, V, V, I, V]),
-    })
     lib = native.lib()
     dev = torch.device("cuda")
     Hq, Hkv, D, bs = 4, 2, 128, 32

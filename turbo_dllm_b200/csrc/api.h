@@ -144,11 +144,6 @@ int tdllm_attn_bwd_fused_csbp(const void* q, const void* k_loc, const void* v_lo
                               int n_ktiles, float scale, const long long* counts, const long long* dst_row0,
                               void* const* flags, int rank, int world, int epoch, void* stream);
 
-// Issue-rate probe of tcgen05.mma (128 x n x 16, bf16): out[0] = cycles in the issue loop of one
-// thread, out[1] = cycles until the last MMA completed.
-int tdllm_mma_issue_probe(int n, int iters, int a_from_tmem, int accs, int uniform, int ctas,
-                          long long* out, void* stream);
-
 // ---- peer memory and the fused ZeRO step -----------------------------------
 int tdllm_symm_alloc(long long bytes, void** out);
 int tdllm_symm_free(void* p);

@@ -142,8 +142,9 @@ __device__ __forceinline__ bool count_wait_geq(const int* flag, int want, int ke
 __device__ __forceinline__ void pull_remote_rows(const PullPlan& pl, int lane) {
   const int n_claims = pl.nrt * (BKV / PULL_ROWS);
   uint32_t seen = 0;   // segments whose owner has been seen ready
+  // every pass takes one claim off the shared counter: at most n_claims + 1 passes per warp
 #pragma unroll 1
-  while (true) {
+  for (int pass = 0; pass <= n_claims; ++pass) {
     int c = 0;
     if (lane == 0) c = atomicAdd(pl.counter, 1);
     c = __shfl_sync(0xffffffffu, c, 0);

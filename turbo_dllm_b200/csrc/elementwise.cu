@@ -159,13 +159,31 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
   }
 }
 
-// out[c] (+)= sum_r part[r, c]; out is bf16 or fp32
-__global__ void colsum_kernel(const float* __restrict__ part, int nparts, int H, void* out,
-                              int out_fp32, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
+// out[c] (+)= sum_r part[r, c]; out is bf16 or fp32. A block of 32 x 8 threads owns 32 columns: thread (x, y)
+// adds the partial rows y, y + 8, ... of column x (a warp reads 128 contiguous bytes per row), then the eight
+// row lanes meet in shared memory. The serial depth is nparts / 8 instead of nparts.
+constexpr int COLSUM_COLS = 32;
+constexpr int COLSUM_LANES = 8;
+__global__ void __launch_bounds__(COLSUM_COLS * COLSUM_LANES)
+colsum_kernel(const float* __restrict__ part, int nparts, int H, void* out, int out_fp32, int accumulate) {
+  __shared__ float sm[COLSUM_LANES][COLSUM_COLS];
+  const int x = threadIdx.x & (COLSUM_COLS - 1), y = threadIdx.x / COLSUM_COLS;
+  const int c = blockIdx.x * COLSUM_COLS + x;
+  float s0 = 0.f, s1 = 0.f;
+  if (c < H) {
+    int r = y;
+    for (; r + COLSUM_LANES < nparts; r += 2 * COLSUM_LANES) {
+      s0 += part[(size_t)r * H + c];
+      s1 += part[(size_t)(r + COLSUM_LANES) * H + c];
+    }
+    if (r < nparts) s0 += part[(size_t)r * H + c];
+  }
+  sm[y][x] = s0 + s1;
+  __syncthreads();
+  if (y != 0 || c >= H) return;
   float s = 0.f;
-  for (int r = 0; r < nparts; ++r) s += part[(size_t)r * H + c];
+#pragma unroll
+  for (int i = 0; i < COLSUM_LANES; ++i) s += sm[i][x];
   if (out_fp32) {
     float* o = (float*)out;
     o[c] = accumulate ? o[c] + s : s;
@@ -447,7 +465,7 @@ extern "C" int tdllm_rmsnorm_bwd(const void* dy, const void* h, const void* w, c
   else if (vpt == 2) ew::rmsnorm_bwd_kernel<2><<<parts, threads, 0, s>>>(a, b, c, rstd, d, o, scratch, rows, H);
   else ew::rmsnorm_bwd_kernel<4><<<parts, threads, 0, s>>>(a, b, c, rstd, d, o, scratch, rows, H);
   TD_CHECK_LAUNCH("rmsnorm_bwd");
-  ew::colsum_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, parts, H, dw, dw_fp32, dw_accumulate);
+  ew::colsum_kernel<<<(H + 31) / 32, 256, 0, s>>>(scratch, parts, H, dw, dw_fp32, dw_accumulate);
   TD_CHECK_LAUNCH("rmsnorm_bwd colsum");
   return 0;
 }
@@ -503,12 +521,12 @@ extern "C" int tdllm_qk_norm_rope_bwd(const void* dout, const void* in_raw, void
   if (part) {
     // partial rows are [q weights | k weights]; reduce both halves with stride 2*D
     const int parts = grid * 8;
-    ew::colsum_kernel<<<(2 * D + 255) / 256, 256, 0, s>>>(part, parts, 2 * D, scratch + (size_t)parts * 2 * D,
+    ew::colsum_kernel<<<(2 * D + 31) / 32, 256, 0, s>>>(part, parts, 2 * D, scratch + (size_t)parts * 2 * D,
                                                        1, 0);
     TD_CHECK_LAUNCH("qk colsum");
     const float* red = scratch + (size_t)parts * 2 * D;
-    ew::colsum_kernel<<<1, 256, 0, s>>>(red, 1, D, dqw, dw_fp32, dw_accumulate);
-    ew::colsum_kernel<<<1, 256, 0, s>>>(red + D, 1, D, dkw, dw_fp32, dw_accumulate);
+    ew::colsum_kernel<<<(D + 31) / 32, 256, 0, s>>>(red, 1, D, dqw, dw_fp32, dw_accumulate);
+    ew::colsum_kernel<<<(D + 31) / 32, 256, 0, s>>>(red + D, 1, D, dkw, dw_fp32, dw_accumulate);
     TD_CHECK_LAUNCH("qk colsum2");
   }
   return 0;
@@ -603,7 +621,7 @@ extern "C" int tdllm_rmsnorm_bwd_noalloc(const void* dy, const void* h, const vo
   else if (vpt == 2) ew::rmsnorm_bwd_kernel<2><<<parts, threads, 0, s>>>(a, b, c, rstd, d, o, scratch, rows, H);
   else ew::rmsnorm_bwd_kernel<4><<<parts, threads, 0, s>>>(a, b, c, rstd, d, o, scratch, rows, H);
   TD_CHECK_LAUNCH("rmsnorm_bwd_noalloc");
-  ew::colsum_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, parts, H, dw, dw_fp32, dw_accumulate);
+  ew::colsum_kernel<<<(H + 31) / 32, 256, 0, s>>>(scratch, parts, H, dw, dw_fp32, dw_accumulate);
   TD_CHECK_LAUNCH("rmsnorm_bwd_noalloc colsum");
   return 0;
 }

@@ -27,7 +27,9 @@ extern "C" {
 //  * H must be a multiple of 8 and at most TDLLM_NOALLOC_MAX_HIDDEN; larger sizes are rejected
 //    with a non-zero return code and a message in tdllm_last_error().
 //  * The first call on each device looks up the array's device address (once per device, with
-//    that device current). Make that first call before starting any stream capture.
+//    that device current). Make that first call before starting any stream capture, and make it from one
+//    thread: the per-device cache is filled without a lock (concurrent first calls would store the same
+//    value, which is harmless, but is not something this header promises).
 //  * The function calls no cudaMalloc / cudaFree and no allocating library routine.
 //  * Every call on a device shares the one array. Each call overwrites all partial sums it later
 //    reads, so nothing needs clearing between calls, but two calls that overlap on the GPU

@@ -22,6 +22,8 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from ..profiling import collectives as coll
+
 from ..ops.activation import swiglu
 from ..ops.gemm import linear, linear_residual
 from ..ops.norm import rmsnorm
@@ -58,13 +60,13 @@ class _AllToAllRows(torch.autograd.Function):
     def forward(ctx, x, send_counts, recv_counts, group):
         ctx.group, ctx.send, ctx.recv = group, send_counts, recv_counts
         out = x.new_empty(sum(recv_counts), x.shape[1])
-        dist.all_to_all_single(out, x.contiguous(), recv_counts, send_counts, group=group)
+        coll.all_to_all_single(out, x.contiguous(), recv_counts, send_counts, domain="expert", group=group)
         return out
 
     @staticmethod
     def backward(ctx, g):
         out = g.new_empty(sum(ctx.send), g.shape[1])
-        dist.all_to_all_single(out, g.contiguous(), ctx.send, ctx.recv, group=ctx.group)
+        coll.all_to_all_single(out, g.contiguous(), ctx.send, ctx.recv, domain="expert", group=ctx.group)
         return out, None, None, None
 
 
@@ -120,7 +122,7 @@ class ExpertBank(nn.Module):
         if self.ep > 1:
             send = counts_g.view(self.ep, self.e_local).sum(1)
             all_counts = torch.empty(self.ep, cfg.num_experts, dtype=counts_g.dtype, device=x.device)
-            dist.all_gather_into_tensor(all_counts.view(-1), counts_g, group=self.ep_group)
+            coll.all_gather_into_tensor(all_counts.view(-1), counts_g, "expert", group=self.ep_group)
             mine = all_counts[:, self.ep_rank * self.e_local:(self.ep_rank + 1) * self.e_local]   # [src, e_local]
             # one host read for both all-to-all size lists (NCCL wants them on the host)
             sizes = torch.cat([send, mine.sum(1)]).tolist()

@@ -16,6 +16,8 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from ..profiling import collectives as coll
+
 from ._util import use_native
 from .gemm import gemm
 
@@ -72,10 +74,10 @@ def streaming_soft_embedding(hidden: torch.Tensor, weight: torch.Tensor, *, row_
         m, den, num = _online_shard(rows, weight, vocab_chunk_size, logit_softcap)
         if sharded:
             m_all = m.clone()
-            dist.all_reduce(m_all, op=dist.ReduceOp.MAX, group=tp_group)
+            coll.all_reduce(m_all, "tensor", op=dist.ReduceOp.MAX, group=tp_group)
             scale = torch.exp(m - m_all)
             den, num = den * scale, num * scale[:, None]
-            dist.all_reduce(den, group=tp_group)
-            dist.all_reduce(num, group=tp_group)
+            coll.all_reduce(den, "tensor", group=tp_group)
+            coll.all_reduce(num, "tensor", group=tp_group)
         out[r0:r0 + row_chunk_size] = (num / den[:, None] * embedding_scale).to(out.dtype)
     return out.view_as(hidden).detach()

@@ -24,6 +24,7 @@ import torch.distributed as dist
 from ..kernels import native
 from ..models.dense import ALIGN, FlatParams
 from ..ops._util import ptr, stream
+from ..profiling.operator_trace import communication_scope
 
 
 def shard_bounds(numel: int, parts: int, index: int) -> tuple[int, int]:
@@ -71,9 +72,12 @@ class FlatAdamW:
         if g.is_cuda:
             padded = g if g.numel() == per * self.world else torch.nn.functional.pad(g, (0, per * self.world - g.numel()))
             out = torch.empty(per, dtype=g.dtype, device=g.device)
-            dist.reduce_scatter_tensor(out, padded, op=dist.ReduceOp.SUM, group=self.group)
+            with communication_scope("optimizer_data_parallel", "gradient_sync", "reduce_scatter",
+                                     padded.numel() * padded.element_size()):
+                dist.reduce_scatter_tensor(out, padded, op=dist.ReduceOp.SUM, group=self.group)
             return out[: self.stop - self.start]
-        dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.group)  # gloo has no reduce_scatter
+        with communication_scope("optimizer_data_parallel", "gradient_sync", "all_reduce", g.numel() * g.element_size()):
+            dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.group)  # gloo has no reduce_scatter
         return g[self.start:self.stop]
 
     def _all_gather_params(self) -> None:
@@ -84,7 +88,9 @@ class FlatAdamW:
         mine = torch.zeros(per, dtype=p.dtype, device=p.device)
         mine[: self.stop - self.start] = p[self.start:self.stop]
         full = torch.empty(per * self.world, dtype=p.dtype, device=p.device)
-        dist.all_gather_into_tensor(full, mine, group=self.group)
+        with communication_scope("optimizer_data_parallel", "optimizer", "all_gather", per * p.element_size(),
+                                 per * self.world * p.element_size()):
+            dist.all_gather_into_tensor(full, mine, group=self.group)
         p.copy_(full[: p.numel()])
 
     # ------------------------------------------------------------------ step
@@ -94,9 +100,11 @@ class FlatAdamW:
         """One optimizer step on gradients already present in flat.grad."""
         if self.fused_sync is not None and self.world > 1:
             self.step_count += 1
-            self.fused_sync.step(self, self.lr if lr is None else lr,
-                                 self.weight_decay if weight_decay is None else weight_decay, grad_scale,
-                                 max_grad_norm)
+            nbytes = (self.stop - self.start) * 2 * (self.world - 1)
+            with communication_scope("optimizer_data_parallel", "optimizer", "fused_zero_pull_push", nbytes, 2 * nbytes):
+                self.fused_sync.step(self, self.lr if lr is None else lr,
+                                     self.weight_decay if weight_decay is None else weight_decay, grad_scale,
+                                     max_grad_norm)
             return
         sumsq = self.reduce_gradients()
         self.apply_update(sumsq, lr=lr, weight_decay=weight_decay, grad_scale=grad_scale,
@@ -120,7 +128,8 @@ class FlatAdamW:
             repl = self._grad_sumsq(self._gshard[split:]).clone() if n > split else torch.zeros_like(sharded)
             sumsq = sharded + repl
         if self.world > 1:
-            dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=self.group)
+            with communication_scope("optimizer_data_parallel", "gradient_clip", "all_reduce", 4):
+                dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=self.group)
         return sumsq
 
     @torch.no_grad()

@@ -29,7 +29,23 @@ import torch.distributed as dist
 
 from ..models.config import ModelConfig
 from ..ops.attention import attention_reference, block_attention, block_diffusion_layout, split_packed_qkv
+from ..profiling.operator_trace import communication_scope
 from .layout import PackedLayout, clean_positions_for_rank, runtime_clean_layout
+
+
+def _register_fused_signatures() -> None:
+    from ..kernels import native
+
+    V, I, LL, F = native.c_void_p, native.c_int, native.c_ll, native.c_float
+    native.register_signatures({
+        "tdllm_symm_signal": (I, [V, I, I, I, V]),
+        "tdllm_attn_fwd_csbp": (I, [V] * 6 + [I, I, LL, I, I] + [LL] * 4 + [V] * 7 + [I, F, V, V, V, I, I, I, V, V, I, V]),
+        "tdllm_attn_bwd_fused_csbp": (I, [V] * 14 + [LL, V, LL, I, I, LL, I, I] + [LL] * 8 + [V] * 7
+                                      + [I, I, I, F, V, V, V, I, I, I, V]),
+    })
+
+
+_register_fused_signatures()
 
 
 class _AllGatherRows(torch.autograd.Function):
@@ -43,7 +59,9 @@ class _AllGatherRows(torch.autograd.Function):
         nmax = max(counts)
         pad = x if x.shape[0] == nmax else torch.cat([x, x.new_zeros(nmax - x.shape[0], x.shape[1])])
         out = x.new_empty(world * nmax, x.shape[1])
-        dist.all_gather_into_tensor(out, pad.contiguous(), group=group)
+        with communication_scope("context_parallel", "forward", "all_gather", pad.numel() * pad.element_size(),
+                                 out.numel() * out.element_size()):
+            dist.all_gather_into_tensor(out, pad.contiguous(), group=group)
         ctx.rank, ctx.nmax = rank, nmax
         if all(c == nmax for c in counts):
             return out
@@ -62,11 +80,13 @@ class _AllGatherRows(torch.autograd.Function):
                 full[r * nmax: r * nmax + c] = g[off: off + c]
                 off += c
         out = g.new_empty(nmax, g.shape[1])
-        if g.is_cuda:
-            dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.SUM, group=group)
-        else:  # gloo: all-reduce then slice
-            dist.all_reduce(full, op=dist.ReduceOp.SUM, group=group)
-            out = full[ctx.rank * nmax: (ctx.rank + 1) * nmax]
+        with communication_scope("context_parallel", "backward", "reduce_scatter", full.numel() * full.element_size(),
+                                 out.numel() * out.element_size()):
+            if g.is_cuda:
+                dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.SUM, group=group)
+            else:  # gloo: all-reduce then slice
+                dist.all_reduce(full, op=dist.ReduceOp.SUM, group=group)
+                out = full[ctx.rank * nmax: (ctx.rank + 1) * nmax]
         return out[: counts[ctx.rank]], None, None
 
 
@@ -114,9 +134,11 @@ class PeerKVExchange:
         buf.as_tensor(torch.bfloat16, n * self.row_elems).view(n, self.row_elems).copy_(x)
         out = torch.empty(self.total, self.row_elems, dtype=torch.bfloat16, device=self.device)
         e = self.barrier.reserve(1)
-        self.native.check(self.native.lib().tdllm_kv_gather(
-            buf.ptr_array, self.barrier.buf.ptr_array, self.counts_arr, self.rank, self.world, self.row_bytes,
-            ptr(out), e, stream()), "kv_gather")
+        with communication_scope("context_parallel", "forward", "peer_pull", (self.total - n) * self.row_bytes,
+                                 self.total * self.row_bytes):
+            self.native.check(self.native.lib().tdllm_kv_gather(
+                buf.ptr_array, self.barrier.buf.ptr_array, self.counts_arr, self.rank, self.world, self.row_bytes,
+                ptr(out), e, stream()), "kv_gather")
         return out
 
     def scatter_reduce(self, g: torch.Tensor) -> torch.Tensor:
@@ -125,9 +147,11 @@ class PeerKVExchange:
         self.partial.as_tensor(torch.bfloat16, self.total * self.row_elems).view(self.total, self.row_elems).copy_(g)
         out = torch.empty(self.counts[self.rank], self.row_elems, dtype=torch.bfloat16, device=self.device)
         e = self.barrier.reserve(2)
-        self.native.check(self.native.lib().tdllm_kv_scatter_reduce(
-            self.partial.ptr_array, self.barrier.buf.ptr_array, self.counts_arr, self.rank, self.world,
-            self.row_bytes, ptr(out), e, stream()), "kv_scatter_reduce")
+        with communication_scope("context_parallel", "backward", "peer_pull_reduce",
+                                 (self.world - 1) * self.counts[self.rank] * self.row_bytes):
+            self.native.check(self.native.lib().tdllm_kv_scatter_reduce(
+                self.partial.ptr_array, self.barrier.buf.ptr_array, self.counts_arr, self.rank, self.world,
+                self.row_bytes, ptr(out), e, stream()), "kv_scatter_reduce")
         return out
 
 
@@ -155,14 +179,6 @@ class FusedKVExchange:
         from ..kernels import native
         from .symm import SymmetricBarrier, SymmetricBuffer
 
-        V, I, LL, F = native.c_void_p, native.c_int, native.c_ll, native.c_float
-        native.register_signatures({
-            "tdllm_symm_signal": (I, [V, I, I, I, V]),
-            "tdllm_attn_fwd_csbp": (I, [V] * 6 + [I, I, LL, I, I] + [LL] * 4 + [V] * 7 + [I, F, V, V, V, I, I, I, V, V, I,
-                                                                                         V]),
-            "tdllm_attn_bwd_fused_csbp": (I, [V] * 14 + [LL, V, LL, I, I, LL, I, I] + [LL] * 8 + [V] * 7
-                                          + [I, I, I, F, V, V, V, I, I, I, V]),
-        })
         self.native, self.device, self.group = native, device, group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -214,12 +230,13 @@ class _FusedContextAttention(torch.autograd.Function):
         kv_rem = torch.empty(max(ex.n_rem, 1), ex.kv_cols, dtype=qkv.dtype, device=qkv.device)
         out = torch.empty(rows, Hq * D, dtype=qkv.dtype, device=qkv.device)
         lse = torch.empty(Hq, L["nq_pad"], dtype=torch.float32, device=qkv.device)
-        ex.native.check(lib.tdllm_attn_fwd_csbp(
-            ptr(q), ptr(k), ptr(v), ptr(kv_rem), ptr(out), ptr(lse), rows, rows, ex.n_rem, Hq, Hkv,
-            qkv.stride(0), qkv.stride(0), qkv.stride(0), out.stride(0), ptr(L["q_lo"]), ptr(L["q_hi"]),
-            ptr(L["q_grp"]), ptr(L["k_code"]), ptr(L["f_ptr"]), ptr(L["f_idx"]), ptr(L["f_order"]), L["nqt"],
-            1.0 / D ** 0.5, stage.ptr_array, ex.ready.ptr_array, ex.counts_arr, ex.rank, ex.world, n,
-            ptr(ex.counter), ptr(ex.tile_ready), n, stream()), "attn_fwd_csbp")
+        with communication_scope("context_parallel", "forward", "attention_with_peer_pull", ex.n_rem * ex.kv_cols * 2):
+            ex.native.check(lib.tdllm_attn_fwd_csbp(
+                ptr(q), ptr(k), ptr(v), ptr(kv_rem), ptr(out), ptr(lse), rows, rows, ex.n_rem, Hq, Hkv,
+                qkv.stride(0), qkv.stride(0), qkv.stride(0), out.stride(0), ptr(L["q_lo"]), ptr(L["q_hi"]),
+                ptr(L["q_grp"]), ptr(L["k_code"]), ptr(L["f_ptr"]), ptr(L["f_idx"]), ptr(L["f_order"]), L["nqt"],
+                1.0 / D ** 0.5, stage.ptr_array, ex.ready.ptr_array, ex.counts_arr, ex.rank, ex.world, n,
+                ptr(ex.counter), ptr(ex.tile_ready), n, stream()), "attn_fwd_csbp")
         ctx.save_for_backward(qkv, kv_rem, out, lse)
         ctx.cpa = cpa
         return out
@@ -246,14 +263,15 @@ class _FusedContextAttention(torch.autograd.Function):
         n = ex.bwd_calls
         cur, nxt = n & 1, (n + 1) & 1
         e = ex.barrier.reserve(1)
-        ex.native.check(ex.native.lib().tdllm_attn_bwd_fused_csbp(
-            ptr(q), ptr(k), ptr(v), ptr(kv_rem), ptr(out), ptr(dout), ptr(dq), ptr(dk), ptr(dv), ptr(lse),
-            ptr(delta), ptr(dq_acc), ex.acc_dk[cur], ex.acc_dv[cur], ex.acc_rows, ex.acc[nxt].local, ex.acc_bytes,
-            rows, rows, ex.n_rem, Hq, Hkv, qkv.stride(0), qkv.stride(0), qkv.stride(0), out.stride(0),
-            dout.stride(0), dqkv.stride(0), dqkv.stride(0), dqkv.stride(0), ptr(L["q_lo"]), ptr(L["q_hi"]),
-            ptr(L["q_grp"]), ptr(L["k_code"]), ptr(W["w_ptr"]), ptr(W["w_idx"]), ptr(W["w_order"]), W["n_work"],
-            L["nqt"], L["nkt"], 1.0 / D ** 0.5, ex.counts_arr, ex.row0_arr, ex.barrier.buf.ptr_array, ex.rank,
-            ex.world, e, stream()), "attn_bwd_fused_csbp")
+        with communication_scope("context_parallel", "backward", "attention_with_peer_add", ex.n_rem * ex.kv_cols * 4):
+            ex.native.check(ex.native.lib().tdllm_attn_bwd_fused_csbp(
+                ptr(q), ptr(k), ptr(v), ptr(kv_rem), ptr(out), ptr(dout), ptr(dq), ptr(dk), ptr(dv), ptr(lse),
+                ptr(delta), ptr(dq_acc), ex.acc_dk[cur], ex.acc_dv[cur], ex.acc_rows, ex.acc[nxt].local, ex.acc_bytes,
+                rows, rows, ex.n_rem, Hq, Hkv, qkv.stride(0), qkv.stride(0), qkv.stride(0), out.stride(0),
+                dout.stride(0), dqkv.stride(0), dqkv.stride(0), dqkv.stride(0), ptr(L["q_lo"]), ptr(L["q_hi"]),
+                ptr(L["q_grp"]), ptr(L["k_code"]), ptr(W["w_ptr"]), ptr(W["w_idx"]), ptr(W["w_order"]), W["n_work"],
+                L["nqt"], L["nkt"], 1.0 / D ** 0.5, ex.counts_arr, ex.row0_arr, ex.barrier.buf.ptr_array, ex.rank,
+                ex.world, e, stream()), "attn_bwd_fused_csbp")
         return dqkv, None
 
 
@@ -311,11 +329,32 @@ class _StreamingAttention(torch.autograd.Function):
                 dqkv[:n_noisy, Hq * D:] += dkv[:n_noisy]
                 off = n_noisy
             clean = dkv[off:].contiguous()
-            dist.reduce(clean, dst=cpa.group_ranks[r], op=dist.ReduceOp.SUM, group=cpa.group)
+            with communication_scope("context_parallel", "backward", "reduce", clean.numel() * clean.element_size()):
+                dist.reduce(clean, dst=cpa.group_ranks[r], op=dist.ReduceOp.SUM, group=cpa.group)
             if r == cpa.cp_rank:
                 dqkv[n_noisy:, Hq * D:] += clean
         dqkv[:, : Hq * D] = dq_acc.reshape(rows, Hq * D).to(dqkv.dtype)
         return dqkv, None
+
+
+def fused_key_layout(layout: PackedLayout, kpos: list, kseq: list, cp: int, me: int):
+    """Mask of the fused transport. Key order: this rank's rows, padding up to a 128-row tile boundary, then
+    the peers' clean rows in pull order (rank+1, rank+2, ...). kpos[r] / kseq[r]: positions and sequence
+    indices of rank r's clean rows."""
+    from ..ops.attention import INT_MIN, MaskLayout
+
+    dev = layout.positions.device
+    order = [(me + 1 + s) % cp for s in range(cp - 1)]
+    local = layout.mask                                   # keys = own rows
+    rem = block_diffusion_layout(layout.noisy_pos, layout.noisy_group, layout.clean_pos, layout.block_size,
+                                 noisy_seq=layout.noisy_seq, clean_seq=layout.clean_seq,
+                                 key_clean_pos=torch.cat([kpos[r] for r in order]),
+                                 key_clean_seq=torch.cat([kseq[r] for r in order]),
+                                 clean_causal=layout.clean_causal)
+    rem_code = rem.k_code[layout.n_noisy:]
+    pad = (-layout.rows) % 128
+    k_code = torch.cat([local.k_code, torch.full((pad,), INT_MIN, dtype=torch.int32, device=dev), rem_code])
+    return MaskLayout(local.q_lo, local.q_hi, local.q_grp, k_code.contiguous())
 
 
 class ContextParallelAttention:
@@ -369,23 +408,8 @@ class ContextParallelAttention:
                                            key_clean_seq=torch.cat(kseq), clean_causal=layout.clean_causal)
 
     def _init_fused(self, cfg, layout, kpos, kseq, counts, dev) -> None:
-        """Key order of the fused transport: this rank's rows, padding up to a 128-row tile boundary, then
-        the peers' clean rows in pull order (rank+1, rank+2, ...)."""
-        from ..ops.attention import INT_MIN, MaskLayout
-
-        cp, me = self.cp, self.cp_rank
-        order = [(me + 1 + s) % cp for s in range(cp - 1)]
-        local = layout.mask                                   # keys = own rows
-        rem = block_diffusion_layout(layout.noisy_pos, layout.noisy_group, layout.clean_pos, layout.block_size,
-                                     noisy_seq=layout.noisy_seq, clean_seq=layout.clean_seq,
-                                     key_clean_pos=torch.cat([kpos[r] for r in order]),
-                                     key_clean_seq=torch.cat([kseq[r] for r in order]),
-                                     clean_causal=layout.clean_causal)
-        rem_code = rem.k_code[layout.n_noisy:]
-        pad = (-layout.rows) % 128
-        k_code = torch.cat([local.k_code, torch.full((pad,), INT_MIN, dtype=torch.int32, device=dev), rem_code])
-        self.mask = MaskLayout(local.q_lo, local.q_hi, local.q_grp, k_code.contiguous())
-        n_noisy = [torch.zeros(1, dtype=torch.long, device=dev) for _ in range(cp)]
+        self.mask = fused_key_layout(layout, kpos, kseq, self.cp, self.cp_rank)
+        n_noisy = [torch.zeros(1, dtype=torch.long, device=dev) for _ in range(self.cp)]
         dist.all_gather(n_noisy, torch.tensor([layout.n_noisy], dtype=torch.long, device=dev), group=self.group)
         self.exchange = FusedKVExchange(self.group, dev, counts, [int(t) for t in n_noisy], layout.rows,
                                         2 * cfg.num_key_value_heads * cfg.head_dim)
@@ -399,7 +423,8 @@ class ContextParallelAttention:
             clean = qkv[n_noisy:, qd:].contiguous()
         else:
             clean = qkv.new_empty(self.counts[r], qkv.shape[1] - qd)
-        dist.broadcast(clean, src=self.group_ranks[r], group=self.group)
+        with communication_scope("context_parallel", "forward", "broadcast", clean.numel() * clean.element_size()):
+            dist.broadcast(clean, src=self.group_ranks[r], group=self.group)
         return torch.cat([qkv[:n_noisy, qd:], clean], dim=0) if r == 0 else clean
 
     def kv_views(self, kv):

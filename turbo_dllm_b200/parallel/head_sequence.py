@@ -15,11 +15,13 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from ..profiling import collectives as coll
+
 
 def _exchange(x: torch.Tensor, send_rows: list[int], recv_rows: list[int], group) -> torch.Tensor:
     out = x.new_empty(sum(recv_rows), x.shape[1])
-    dist.all_to_all_single(out, x.contiguous(), output_split_sizes=recv_rows, input_split_sizes=send_rows,
-                           group=group)
+    coll.all_to_all_single(out, x.contiguous(), output_split_sizes=recv_rows, input_split_sizes=send_rows,
+                           domain="context_parallel", group=group)
     return out
 
 

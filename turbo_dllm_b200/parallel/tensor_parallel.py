@@ -22,6 +22,8 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from ..profiling import collectives as coll
+
 from ..ops.gemm import EPI_CE_GRAD, EPI_CE_STATS, gemm
 from ..ops.linear_ce import linear_ce_reference
 
@@ -38,7 +40,7 @@ class _CopyToTP(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         g = g.contiguous()
-        dist.all_reduce(g, group=ctx.group)
+        coll.all_reduce(g, "tensor", group=ctx.group)
         return g, None
 
 
@@ -48,7 +50,7 @@ class _ReduceFromTP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
         x = x.contiguous()
-        dist.all_reduce(x, group=group)
+        coll.all_reduce(x, "tensor", group=group)
         return x
 
     @staticmethod
@@ -64,7 +66,7 @@ class _GatherRowsSP(torch.autograd.Function):
         ctx.group = group
         world = dist.get_world_size(group)
         out = x.new_empty(world * x.shape[0], *x.shape[1:])
-        dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+        coll.all_gather_into_tensor(out, x.contiguous(), "tensor", group=group)
         return out
 
     @staticmethod
@@ -72,10 +74,10 @@ class _GatherRowsSP(torch.autograd.Function):
         world = dist.get_world_size(ctx.group)
         out = g.new_empty(g.shape[0] // world, *g.shape[1:])
         if g.is_cuda:
-            dist.reduce_scatter_tensor(out, g.contiguous(), group=ctx.group)
+            coll.reduce_scatter_tensor(out, g.contiguous(), "tensor", group=ctx.group)
         else:
             full = g.contiguous().clone()
-            dist.all_reduce(full, group=ctx.group)
+            coll.all_reduce(full, "tensor", group=ctx.group)
             r = dist.get_rank(ctx.group)
             out = full[r * out.shape[0]:(r + 1) * out.shape[0]]
         return out, None
@@ -91,10 +93,10 @@ class _ScatterRowsSP(torch.autograd.Function):
         n = x.shape[0] // world
         if x.is_cuda:
             out = x.new_empty(n, *x.shape[1:])
-            dist.reduce_scatter_tensor(out, x.contiguous(), group=group)
+            coll.reduce_scatter_tensor(out, x.contiguous(), "tensor", group=group)
             return out
         full = x.contiguous().clone()
-        dist.all_reduce(full, group=group)
+        coll.all_reduce(full, "tensor", group=group)
         r = dist.get_rank(group)
         return full[r * n:(r + 1) * n].clone()
 
@@ -102,7 +104,7 @@ class _ScatterRowsSP(torch.autograd.Function):
     def backward(ctx, g):
         world = dist.get_world_size(ctx.group)
         out = g.new_empty(world * g.shape[0], *g.shape[1:])
-        dist.all_gather_into_tensor(out, g.contiguous(), group=ctx.group)
+        coll.all_gather_into_tensor(out, g.contiguous(), "tensor", group=ctx.group)
         return out, None
 
 
@@ -195,7 +197,7 @@ class _VocabParallelEmbedding(torch.autograd.Function):
         local = (tokens - v0).clamp(0, v1 - v0 - 1)
         out = weight.index_select(0, local)
         out = out * inside[:, None].to(out.dtype)
-        dist.all_reduce(out, group=group)
+        coll.all_reduce(out, "tensor", group=group)
         ctx.save_for_backward(local, inside)
         ctx.wref = weight
         return out
@@ -253,9 +255,9 @@ class _VocabParallelLinearCE(torch.autograd.Function):
             tgt = s[:, :, 2].sum(1)
             world = dist.get_world_size(group)
             all_lse = torch.empty(world, rows, dtype=torch.float32, device=dev)
-            dist.all_gather_into_tensor(all_lse.view(-1), lse_local.contiguous(), group=group)
+            coll.all_gather_into_tensor(all_lse.view(-1), lse_local.contiguous(), "tensor", group=group)
             lse = torch.logsumexp(all_lse, dim=0)
-            dist.all_reduce(tgt, group=group)
+            coll.all_reduce(tgt, "tensor", group=group)
         valid = labels >= 0
         per_row = torch.where(valid, lse - tgt, torch.zeros_like(lse))
         wts = torch.ones_like(per_row) if weights is None else weights.float()
@@ -295,7 +297,7 @@ class _VocabParallelLinearCE(torch.autograd.Function):
             else:
                 gemm(dlog[:n], h[r0:r1], a_mn_major=True, b_mn_major=True, out=dw, accumulate=not first)
             first = False
-        dist.all_reduce(dh, group=group)
+        coll.all_reduce(dh, "tensor", group=group)
         if sink is not None:
             mark_grad_written(ctx.wref)
         else:
@@ -320,7 +322,7 @@ def vocab_parallel_linear_cross_entropy(h, w_shard, labels, weights, tp: TPConte
         z[:, exclude_index - v0] = float("-inf")
     m_local = z.max(dim=1).values.detach()
     m = m_local.clone()
-    dist.all_reduce(m, op=dist.ReduceOp.MAX, group=tp.group)
+    coll.all_reduce(m, "tensor", op=dist.ReduceOp.MAX, group=tp.group)
     se = reduce_from_tensor_parallel(torch.exp(z - m[:, None]).sum(1), tp.group)
     inside = (labels >= v0) & (labels < v1)
     loc = (labels - v0).clamp(0, v1 - v0 - 1)

@@ -102,3 +102,50 @@ class SystemTrace:
             os.environ.pop(BACKEND_ENV, None)
             self.active = False
             self.enabled = False
+
+
+class PhaseTimer:
+    """Host-side milliseconds per step phase (`profiler.phase_timing`), reported as `phase_ms` in step events.
+    With `phase_timing_sync` the device is synchronised at both ends of every phase, so the figures are
+    device-inclusive (and the step slower); without it they show where the host spends its time while the
+    device runs behind. Each phase also opens the trace's `dllm.phase.*` range when a trace window is open.
+    Counterpart of the phase bookkeeping in dllm_parallel/training/block_diffusion_trainer.py:1292-1536."""
+
+    def __init__(self, device=None):
+        self.device = device
+        self.enabled = False
+        self.sync = False
+        self.ms: dict[str, float] = {}
+
+    def configure(self, enabled: bool, sync: bool = False) -> None:
+        self.enabled, self.sync = bool(enabled), bool(sync)
+
+    def _device_sync(self) -> None:
+        if self.sync and self.device is not None and getattr(self.device, "type", "cpu") == "cuda":
+            import torch
+
+            torch.cuda.synchronize(self.device)
+
+    @contextlib.contextmanager
+    def phase(self, name: str, trace: "SystemTrace | None" = None):
+        if name not in PHASES:
+            raise ValueError(f"unknown phase {name!r}")
+        ctx = trace.phase(name) if trace is not None else contextlib.nullcontext()
+        if not self.enabled:
+            with ctx:
+                yield
+            return
+        import time
+
+        self._device_sync()
+        t0 = time.perf_counter()
+        try:
+            with ctx:
+                yield
+        finally:
+            self._device_sync()
+            self.ms[name] = self.ms.get(name, 0.0) + (time.perf_counter() - t0) * 1e3
+
+    def take(self) -> dict[str, float]:
+        out, self.ms = {k: round(v, 3) for k, v in self.ms.items()}, {}
+        return out

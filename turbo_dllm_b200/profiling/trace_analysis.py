@@ -56,14 +56,28 @@ def _subtract(a, b) -> float:
     return both - _union_length(b)
 
 
-def summarize(kernels: list[tuple[str, float, float]], ranges: list[tuple[str, float, float]]) -> dict:
-    """kernels / ranges: (name, start_us, end_us)."""
+def _short_name(name: str) -> str:
+    """Kernel name without template arguments and parameter lists (one table row per kernel family)."""
+    n = re.sub(r"\(.*$", "", name)
+    n = re.sub(r"<.*$", "", n)
+    n = n.replace("void ", "").strip()
+    return n.split("::")[-1] if "::" in n and not n.startswith("at::") else n
+
+
+def summarize(kernels: list[tuple[str, float, float]], ranges: list[tuple[str, float, float]],
+              copies: list[tuple[str, float, float]] | None = None) -> dict:
+    """kernels / ranges / copies: (name, start_us, end_us). `copies` are device memcpy / memset activities."""
     by_class = defaultdict(lambda: {"count": 0, "time_us": 0.0})
+    by_name = defaultdict(lambda: {"count": 0, "time_us": 0.0, "class": ""})
     comm, compute = [], []
     for name, s, e in kernels:
         c = classify_kernel(name)
         by_class[c]["count"] += 1
         by_class[c]["time_us"] += e - s
+        rec = by_name[_short_name(name)]
+        rec["count"] += 1
+        rec["time_us"] += e - s
+        rec["class"] = c
         (comm if c in ("nccl", "peer_comm", "moe_transport") else compute).append((s, e))
     labels = defaultdict(lambda: {"count": 0, "time_us": 0.0, "input_bytes": 0, "logical_bytes": 0})
     operators = defaultdict(lambda: {"count": 0, "time_us": 0.0})
@@ -78,9 +92,32 @@ def summarize(kernels: list[tuple[str, float, float]], ranges: list[tuple[str, f
         elif name.startswith("dllm.operator.") or name.startswith("dllm.phase."):
             operators[name]["count"] += 1
             operators[name]["time_us"] += e - s
-    return {"kernel_classes": dict(by_class), "communication_labels": dict(labels), "operators": dict(operators),
+    copies = copies or []
+    copy_classes = defaultdict(lambda: {"count": 0, "time_us": 0.0})
+    for name, s, e in copies:
+        key = ("host_to_device" if re.search(r"HtoD|Host.*Device", name) else
+               "device_to_host" if re.search(r"DtoH|Device.*Host", name) else
+               "device_to_device" if re.search(r"DtoD|Device.*Device", name) else
+               "memset" if re.search(r"memset", name, re.I) else "other_copy")
+        copy_classes[key]["count"] += 1
+        copy_classes[key]["time_us"] += e - s
+    all_k = [(s, e) for _, s, e in kernels]
+    all_c = [(s, e) for _, s, e in copies]
+    span = 0.0
+    steps = [(s, e) for n, s, e in ranges if n.startswith("dllm.step.")]
+    if steps:
+        span = max(e for _, e in steps) - min(s for s, _ in steps)
+    elif all_k:
+        span = max(e for _, e in all_k) - min(s for s, _ in all_k)
+    busy = _union_length(all_k)
+    busy_or_copy = _union_length(all_k + all_c)
+    top = sorted(by_name.items(), key=lambda kv: -kv[1]["time_us"])
+    return {"kernel_classes": dict(by_class), "kernels_by_name": dict(top),
+            "copy_classes": dict(copy_classes), "communication_labels": dict(labels), "operators": dict(operators),
             "compute_time_us": _union_length(compute), "communication_time_us": _union_length(comm),
-            "exposed_communication_us": _subtract(comm, compute)}
+            "exposed_communication_us": _subtract(comm, compute),
+            "span_us": span, "kernel_busy_us": busy, "exposed_copy_us": _subtract(all_c, all_k),
+            "idle_us": max(span - busy_or_copy, 0.0) if span else 0.0}
 
 
 def analyze_kineto_trace(path: str) -> dict:
@@ -88,17 +125,19 @@ def analyze_kineto_trace(path: str) -> dict:
     with opener(path, "rt") as f:
         data = json.load(f)
     events = data["traceEvents"] if isinstance(data, dict) else data
-    kernels, ranges = [], []
+    kernels, ranges, copies = [], [], []
     for ev in events:
         if ev.get("ph") != "X":
             continue
         s, d = float(ev.get("ts", 0)), float(ev.get("dur", 0))
         cat = str(ev.get("cat", ""))
-        if cat in ("kernel", "gpu_memcpy", "gpu_memset"):
+        if cat == "kernel":
             kernels.append((ev.get("name", ""), s, s + d))
+        elif cat in ("gpu_memcpy", "gpu_memset"):
+            copies.append((ev.get("name", ""), s, s + d))
         elif cat in ("user_annotation", "gpu_user_annotation", "cpu_op") and str(ev.get("name", "")).startswith("dllm."):
             ranges.append((ev["name"], s, s + d))
-    return summarize(kernels, ranges)
+    return summarize(kernels, ranges, copies)
 
 
 def analyze_nsys_sqlite(path: str) -> dict:
@@ -124,3 +163,50 @@ def analyze_nsys_sqlite(path: str) -> dict:
 def write_summary(summary: dict, path: str) -> None:
     with open(path, "w") as f:
         json.dump(summary, f, indent=1, sort_keys=True)
+
+
+def format_table(summary: dict, top: int = 25) -> str:
+    """Markdown: device time per kernel family (share of the traced span), copies, exposed time and idle gaps."""
+    span = summary.get("span_us") or 1.0
+    lines = ["| kernel | class | launches | device ms | share of span |", "|---|---|---|---|---|"]
+    for name, rec in list(summary["kernels_by_name"].items())[:top]:
+        lines.append(f"| `{name}` | {rec['class']} | {rec['count']} | {rec['time_us'] / 1e3:.1f} | "
+                     f"{100 * rec['time_us'] / span:.1f} % |")
+    rest = list(summary["kernels_by_name"].items())[top:]
+    if rest:
+        t = sum(r["time_us"] for _, r in rest)
+        lines.append(f"| {len(rest)} other kernels | | {sum(r['count'] for _, r in rest)} | {t / 1e3:.1f} | "
+                     f"{100 * t / span:.1f} % |")
+    lines.append("")
+    lines.append("| quantity | ms | share of span |")
+    lines.append("|---|---|---|")
+    rows = [("traced span (dllm.step ranges)", span),
+            ("kernels busy (union over streams)", summary["kernel_busy_us"]),
+            ("copies not hidden behind kernels", summary["exposed_copy_us"]),
+            ("device idle inside the span (launch gaps, host waits)", summary["idle_us"]),
+            ("communication kernels not hidden behind compute", summary["exposed_communication_us"])]
+    for k, rec in summary["copy_classes"].items():
+        rows.append((f"copies: {k} ({rec['count']})", rec["time_us"]))
+    for k, v in rows:
+        lines.append(f"| {k} | {v / 1e3:.1f} | {100 * v / span:.1f} % |")
+    return "\n".join(lines)
+
+
+def main(argv=None) -> int:
+    import argparse
+
+    ap = argparse.ArgumentParser(prog="python -m turbo_dllm_b200.profiling.trace_analysis",
+                                 description="Summarise a Kineto chrome trace or an nsys sqlite export.")
+    ap.add_argument("trace")
+    ap.add_argument("--json", help="write the full summary here")
+    ap.add_argument("--top", type=int, default=25)
+    a = ap.parse_args(argv)
+    summary = analyze_nsys_sqlite(a.trace) if a.trace.endswith(".sqlite") else analyze_kineto_trace(a.trace)
+    if a.json:
+        write_summary(summary, a.json)
+    print(format_table(summary, a.top))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

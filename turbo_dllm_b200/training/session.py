@@ -60,6 +60,10 @@ class TrainingSession:
         self.cfg: ModelConfig = model_config_from_run_spec(spec)
         seed = spec.launch.seed
         self.task = None
+        from ..profiling.system_trace import PhaseTimer
+
+        self.trace = None                       # the trainer hands its SystemTrace over
+        self.phase_timer = PhaseTimer(self.device)
         if spec.objective.name == "dflash_distillation":
             self._init_dflash(seed, runtime, host_staged_data)
             return
@@ -359,16 +363,19 @@ class TrainingSession:
             labels = torch.cat([labels[:n_noisy], enc_labels.to(labels.dtype)])
             enc_w = self.encoder_loss_weight * float(denominator) / self._encoder_denominator
             weights = torch.cat([weights[:n_noisy], torch.full_like(weights[n_noisy:], enc_w)])
-        soft, soft_rows = self._self_conditioning_inputs(tokens, cb)
-        hidden = self.model(tokens, self.layout.positions, self.attend, soft, soft_rows)
+        with self._phase("forward"):
+            soft, soft_rows = self._self_conditioning_inputs(tokens, cb)
+            hidden = self.model(tokens, self.layout.positions, self.attend, soft, soft_rows)
         self.memory_report("after forward")
-        h, l, w, kept = compact_supervised_rows(hidden, labels, weights)
-        loss_sum, per_row = self.model.loss(h, l, w, self.objective.exclude_mask_token)
-        if self.encoder_loss_weight > 0.0 and per_row is not None:
-            clean_rows = kept >= n_noisy
-            self.last_encoder_loss = (per_row.detach()[clean_rows].sum() / self._encoder_denominator)
+        with self._phase("loss"):
+            h, l, w, kept = compact_supervised_rows(hidden, labels, weights)
+            loss_sum, per_row = self.model.loss(h, l, w, self.objective.exclude_mask_token)
+            if self.encoder_loss_weight > 0.0 and per_row is not None:
+                clean_rows = kept >= n_noisy
+                self.last_encoder_loss = (per_row.detach()[clean_rows].sum() / self._encoder_denominator)
         self.memory_report("after loss")
-        (loss_sum / denominator).backward()
+        with self._phase("backward"):
+            (loss_sum / denominator).backward()
         self.memory_report("after backward")
         return loss_sum.detach(), l.shape[0], cb
 
@@ -416,11 +423,16 @@ class TrainingSession:
             cnt /= bpcp
         return float(cnt) * copies
 
+    def _phase(self, name: str):
+        return self.phase_timer.phase(name, self.trace)
+
     def step(self) -> StepResult:
         spec = self.spec
-        for f in self.flats():
-            f.zero_grad()
-        batches = self.data.next_optimizer_step_batches(spec.training.gradient_accumulation_steps)
+        with self._phase("zero_grad"):
+            for f in self.flats():
+                f.zero_grad()
+        with self._phase("data"):
+            batches = self.data.next_optimizer_step_batches(spec.training.gradient_accumulation_steps)
         total = torch.zeros((), dtype=torch.float32, device=self.device)
         rows = 0
         if self.task is not None:
@@ -430,7 +442,8 @@ class TrainingSession:
             denom = 0.0
             self.task.set_optimizer_step(self.steps_done, max(int(spec.training.steps or 1), 1))
             for b in batches:
-                ls, n, d = self.task.forward_backward(b)
+                with self._phase("forward"):     # drafter tasks run forward, loss and backward as one call
+                    ls, n, d = self.task.forward_backward(b)
                 total += ls.float() / d.float() / scale
                 rows += n
             denom = 1.0
@@ -444,25 +457,30 @@ class TrainingSession:
                 ls, n, _ = self.forward_backward(b, denom)
                 total += ls.float()
                 rows += n
-        for f in self.flats():
-            f.collect_grads()
-        if getattr(self, "_grad_div", 1.0) != 1.0:
-            self.model.flat.grad.div_(self._grad_div)
+        with self._phase("gradient_sync"):
+            for f in self.flats():
+                f.collect_grads()
+            if getattr(self, "_grad_div", 1.0) != 1.0:
+                self.model.flat.grad.div_(self._grad_div)
         lr, wd = self.scheduler.step()
         clip = spec.optimizer.gradient_clip_norm
         if spec.training.skip_optimizer_step:
             pass
         elif self.expert_optimizer is None:
-            self.optimizer.step(lr=lr, weight_decay=wd, max_grad_norm=clip)
+            # reduce-scatter, global-norm clip, AdamW and parameter all-gather are one fused sequence
+            with self._phase("optimizer"):
+                self.optimizer.step(lr=lr, weight_decay=wd, max_grad_norm=clip)
         else:
             # one global norm over replicated and expert-sharded parameters
-            dense_sq = self.optimizer.reduce_gradients()
-            expert_sq = self.expert_optimizer.reduce_gradients()
-            if self.ep_group is not None:
-                dist.all_reduce(expert_sq, group=self.ep_group)
-            total_sq = dense_sq + expert_sq
-            self.optimizer.apply_update(total_sq, lr=lr, weight_decay=wd, max_grad_norm=clip)
-            self.expert_optimizer.apply_update(total_sq, lr=lr, weight_decay=wd, max_grad_norm=clip)
+            with self._phase("gradient_sync"):
+                dense_sq = self.optimizer.reduce_gradients()
+                expert_sq = self.expert_optimizer.reduce_gradients()
+                if self.ep_group is not None:
+                    dist.all_reduce(expert_sq, group=self.ep_group)
+                total_sq = dense_sq + expert_sq
+            with self._phase("optimizer"):
+                self.optimizer.apply_update(total_sq, lr=lr, weight_decay=wd, max_grad_norm=clip)
+                self.expert_optimizer.apply_update(total_sq, lr=lr, weight_decay=wd, max_grad_norm=clip)
         self.steps_done += 1
         return StepResult(total, denom, torch.tensor(rows), sum(int(b.input_ids.numel()) for b in batches),
                           sum(b.h2d_bytes for b in batches))

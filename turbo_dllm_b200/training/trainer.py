@@ -66,11 +66,18 @@ class AsyncLossReadback:
         self.host = torch.zeros(2, dtype=torch.float64, pin_memory=(device.type == "cuda"))
         self.event = torch.cuda.Event() if device.type == "cuda" else None
 
-    def enqueue(self, loss_sum: torch.Tensor, rows: int) -> None:
+    def enqueue(self, loss_sum: torch.Tensor, rows: int, replicas: int = 1) -> None:
+        """`replicas`: ranks that hold the SAME loss terms (tensor-parallel ranks all return the full loss of
+        their shared rows): their copies are divided out of the world sum."""
         self.buf[0] = loss_sum.double()
         self.buf[1] = float(rows)
+        if replicas > 1:
+            self.buf /= float(replicas)
         if self.world > 1:
-            dist.all_reduce(self.buf)
+            from ..profiling.operator_trace import communication_scope
+
+            with communication_scope("world", "loss", "all_reduce", self.buf.numel() * 8):
+                dist.all_reduce(self.buf)
         self.host.copy_(self.buf, non_blocking=True)
         if self.event is not None:
             self.event.record()
@@ -123,6 +130,10 @@ def run_training(spec: RunSpec) -> dict:
         run_ctx = collect_run_context(world)
         timed_ms: list[float] = []
         t_train0 = time.monotonic()
+        session.trace = trace
+        session.phase_timer.configure(spec.profiler.phase_timing, spec.profiler.phase_timing_sync)
+        control = ckpt_policy.StepControl(spec, spec.training.steps, rank=rank, world=world, group=gloo, device=device)
+        tp_replicas = runtime.tensor_parallel_size if runtime is not None else 1
         dp = session.dp_size
         tokens_per_step = spec.global_batch(dp) * spec.model.seq_len
         total_steps = spec.training.steps
@@ -133,7 +144,7 @@ def run_training(spec: RunSpec) -> dict:
             t0 = time.perf_counter()
             trace.begin_step(step)
             res = session.step()
-            readback.enqueue(res.loss_sum, int(res.supervised_rows))
+            readback.enqueue(res.loss_sum, int(res.supervised_rows), tp_replicas)
             if use_cuda:
                 torch.cuda.synchronize(device)
             ms = (time.perf_counter() - t0) * 1e3
@@ -163,19 +174,26 @@ def run_training(spec: RunSpec) -> dict:
                       "gradient_accumulation_steps": spec.training.gradient_accumulation_steps,
                       "optimizer_backend": "zero_fused" if session.optimizer.fused_sync else "flat_adamw",
                       "peak_mib": (torch.cuda.max_memory_allocated(device) / 2 ** 20) if use_cuda else None})
+                if spec.profiler.phase_timing:
+                    ev["phase_ms"] = session.phase_timer.take()
                 emit(ev)
                 wb.log_event(ev)
-            elapsed = time.monotonic() - t_train0
-            if ckpt_policy.should_save(spec, step, total_steps, elapsed):
+            elif spec.profiler.phase_timing:
+                session.phase_timer.take()
+            # rank 0's clock decides for everybody (a rank acting on its own clock would save or stop alone)
+            verdict = control.decide(step)
+            if verdict.save:
                 from ..checkpoint import save_training_checkpoint
 
                 tagname = save_training_checkpoint(spec.checkpointing.save_checkpoint_dir, session, step=step,
                                                    rank=rank, world_size=world, runtime=runtime, spec=spec,
-                                                   control_group=gloo)
+                                                   control_group=gloo, tag=verdict.tag)
                 if rank == 0:
                     emit({"event": "checkpoint", "step": step, "tag": tagname,
                           "dir": spec.checkpointing.save_checkpoint_dir})
-            if spec.training.max_duration_seconds and elapsed >= spec.training.max_duration_seconds:
+            if verdict.stop:
+                if rank == 0:
+                    emit({"event": "duration_limit", "step": step, "elapsed_seconds": control.elapsed()})
                 break
         mean_ms = sum(timed_ms) / len(timed_ms) if timed_ms else float("nan")
         if world > 1:
@@ -214,6 +232,9 @@ def run_training(spec: RunSpec) -> dict:
             emit(summary)
             wb.log_event(summary)
         wb.finish()
+        from ..checkpoint import wait_for_async_saves
+
+        wait_for_async_saves()
         session.close()
         return summary
     except Exception as e:
