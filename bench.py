@@ -35,24 +35,31 @@ def parse_args():
     ap.add_argument("--batch-per-gpu", type=int, default=1)
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncating makes the result invalid")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "fsdp", "fsdp_tp2"],
+                    help="dp: replicated bf16 parameters, optimizer state sharded over the ranks (default); fsdp: "
+                         "parameters, gradients and optimizer state sharded over the ranks; fsdp_tp2: tensor "
+                         "parallelism 2 inside parameter sharding over N/2 ranks (N=8: the FSDP 4 x TP 2 layout)")
     return ap.parse_args()
 
 
 def build_spec(args):
     from turbo_dllm_b200.config.run_spec import RunSpec
 
+    tp = 2 if args.parallelism == "fsdp_tp2" else 1
     mapping = {
         "model": {"id": args.model, "seq_len": args.seq_len, "dtype": "bf16", "family": "causal_lm"},
         "objective": {"name": "fast_dllm_v2", "block_size": args.block_size, "noise_schedule_epsilon": 0.1},
         "data": {"input_mode": "random"},
-        "training": {"batch_size": args.batch_per_gpu, "steps": args.steps + args.warmup,
+        # the global batch stays one sequence per GPU: a tensor-parallel pair takes two sequences per step
+        "training": {"batch_size": args.batch_per_gpu * tp, "steps": args.steps + args.warmup,
                      "activation_checkpointing": True},
-        "topology": {"context_parallel_size": 1, "block_parallel_size": 1, "tensor_parallel_size": 1},
-        "optimizer": {"backend": "auto", "lr": 1e-5, "gradient_clip_norm": 1.0},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1, "tensor_parallel_size": tp},
+        "optimizer": {"backend": "auto" if args.parallelism == "dp" else "fsdp", "lr": 1e-5,
+                      "gradient_clip_norm": 1.0},
     }
     if args.layers is not None:
         mapping["model"]["num_layers"] = args.layers
-    return RunSpec.from_mapping(mapping).validate()
+    return RunSpec.from_mapping(mapping).validate(world_size=args.gpus)
 
 
 def run_ours(args):
@@ -108,7 +115,12 @@ def run_ours(args):
         timed.each = [round(a.elapsed_time(b), 1) for a, b in zip(marks[:-1], marks[1:])]
         return float(ms) / steps, loss, native.LAUNCHES["kernels"], r, d2h
 
-    session = TrainingSession(spec, device=f"cuda:{local_rank}")
+    runtime = None
+    if spec.topology.tensor_parallel_size > 1:
+        from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+
+        runtime = build_parallel_runtime(spec, device=f"cuda:{local_rank}", rank=rank, world_size=world)
+    session = TrainingSession(spec, device=f"cuda:{local_rank}", runtime=runtime)
     cfg = session.cfg
     for _ in range(args.warmup):
         session.step()
@@ -130,7 +142,7 @@ def run_ours(args):
 
         gc.collect()
         torch.cuda.empty_cache()
-        session = TrainingSession(spec, device=f"cuda:{local_rank}", host_staged_data=True)
+        session = TrainingSession(spec, device=f"cuda:{local_rank}", runtime=runtime, host_staged_data=True)
         for _ in range(max(args.warmup, 3)):
             session.step()
         ms2, loss2, _, last2, d2h = timed(session, args.steps, read_loss=True)
@@ -153,7 +165,9 @@ def run_ours(args):
             "config": {"model": args.model, "layers": cfg.num_layers, "hidden": cfg.hidden_size,
                        "objective": "fast_dllm_v2", "block_size": args.block_size,
                        "global_batch": args.batch_per_gpu * world, "seq_len": args.seq_len,
-                       "parallelism": f"dp{world}" + ("_zero_sharded_optimizer" if world > 1 else ""),
+                       "parallelism": (f"dp{world}" + ("_zero_sharded_optimizer" if world > 1 else "")
+                                       if args.parallelism == "dp" else
+                                       f"fsdp{world}" if args.parallelism == "fsdp" else f"fsdp{world // 2}_tp2"),
                        "activation_checkpointing": True, "optimizer": "AdamW fp32 master, clip 1.0",
                        "l2": "inputs larger than L2 (16 GB of bf16 weights and >2 GB activations per layer stream "
                              "through HBM every step); no flush needed",

@@ -21,9 +21,10 @@ def _spec(backend):
         "objective": {"name": "fast_dllm_v2", "block_size": 32, "noise_schedule_epsilon": 0.1},
         "training": {"batch_size": 1, "steps": 3},
         "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
-        "kernel": {"impl": "nccl_baseline" if backend == "nccl" else "auto"},
+        "kernel": {"impl": "nccl_baseline" if backend in ("nccl", "fsdp_nccl") else "auto"},
         "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0,
-                      "backend": "zero_fused" if backend == "fused" else "auto"}}).validate()
+                      "backend": {"fused": "zero_fused", "fsdp": "fsdp", "fsdp_nccl": "fsdp"}.get(backend, "auto")}}
+    ).validate()
 
 
 def _train(rank, world, backend, steps):
@@ -38,6 +39,7 @@ def _train(rank, world, backend, steps):
     torch.cuda.set_device(rank)
     s = TrainingSession(_spec(backend), device=f"cuda:{rank}")
     assert (s.optimizer.fused_sync is not None) == (backend == "fused")
+    assert (s.sharded is not None) == backend.startswith("fsdp")
     losses = []
     for _ in range(steps):
         r = s.step()
@@ -46,7 +48,11 @@ def _train(rank, world, backend, steps):
         losses.append(float(t) / r.denominator)
     torch.cuda.synchronize()
     native.raise_on_device_error()
-    out = losses, s.model.flat.data.float().cpu(), s.optimizer.grad_norm()
+    params = s.sharded.gather_full() if s.sharded is not None else s.model.flat.data
+    out = losses, params.float().cpu(), s.optimizer.grad_norm()
+    if s.sharded is not None:
+        assert s.sharded.peer == (backend == "fsdp")
+        s.close()
     if backend == "fused":
         # closing hands the symmetric buffers back and leaves a session that still trains (NCCL path)
         used_before = torch.cuda.mem_get_info()[0]
@@ -70,6 +76,24 @@ def test_fused_zero_matches_nccl_twin():
         pa, pb = torch.from_numpy(pa), torch.from_numpy(pb)
         assert (pa - pb).abs().max().item() < 2e-2
     # replicas hold identical parameters after the push all-gather
+    assert (b[0][1] == b[1][1]).all()
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_parameter_sharding_over_peer_memory_matches_nccl_twin_and_replicated_path(world):
+    """optimizer.backend=fsdp with the peer-memory gather / reduce kernels against the same schedule over NCCL
+    collectives and against the replicated-parameter path."""
+    _need(world)
+    a = run_ranks(_train, world, args=("nccl", 3), backend="nccl", deadline_s=300)
+    b = run_ranks(_train, world, args=("fsdp", 3), backend="nccl", deadline_s=300)
+    c = run_ranks(_train, world, args=("fsdp_nccl", 3), backend="nccl", deadline_s=300)
+    for (la, pa, na), (lb, pb, nb), (lc, pc, nc) in zip(a, b, c):
+        assert lb == pytest.approx(la, rel=2e-2) and lb == pytest.approx(lc, rel=2e-2)
+        assert nb == pytest.approx(na, rel=2e-2)
+        pa, pb, pc = (torch.from_numpy(x) for x in (pa, pb, pc))
+        assert (pa - pb).abs().max().item() < 2e-2
+        assert (pc - pb).abs().max().item() < 2e-2
     assert (b[0][1] == b[1][1]).all()
 
 

@@ -182,6 +182,9 @@ def save_training_checkpoint(directory: str, session, *, step: int, rank: int, w
         "profiler_metadata": {}, "backbone_state": {"family": session.cfg.family},
         "rng_state": capture_rng_state(),
     }
+    if getattr(session, "sharded", None) is not None:
+        client_state["checkpoint_backend"] = "fsdp_sharded_rank_local"
+        client_state["model_state_scope"] = "sharded_flat_parameters"
     st = session.state_dict()
     payload = {"model": st["model"], "optimizer": st["optimizer"], "client_state": client_state}
     for key in ("expert_model", "expert_optimizer", "adapter"):
@@ -383,8 +386,9 @@ def publish_metadata(directory: str, tag: str, step: int, world_size: int, clien
             "dataloader_state": _jsonable(client_state["dataloader_state"]),
             "scheduler_state": client_state["scheduler_state"], "kernel_metadata": client_state["kernel_metadata"],
             "run_metadata": client_state["run_metadata"], "profiler_metadata": {},
-            "backbone_state": client_state["backbone_state"], "checkpoint_backend": BACKEND,
-            "model_state_scope": "replicated_flat_parameters",
+            "backbone_state": client_state["backbone_state"],
+            "checkpoint_backend": client_state.get("checkpoint_backend", BACKEND),
+            "model_state_scope": client_state.get("model_state_scope", "replicated_flat_parameters"),
             "rank_state_pattern": "rank_{rank:05d}_of_{world_size:05d}.pt",
             "created_at": time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())}
     _atomic_write_json(os.path.join(directory, "metadata.json"), meta)

@@ -162,6 +162,19 @@ class RunSpec:
         need(opt.lr > 0 and 0 <= opt.adam_beta1 < 1 and 0 <= opt.adam_beta2 < 1 and opt.adam_eps > 0,
              "optimizer.lr, adam_beta1/2 and adam_eps out of range")
         need(opt.gradient_clip_norm >= 0, "optimizer.gradient_clip_norm must be >= 0")
+        if opt.backend in ("fsdp", "fsdp2"):
+            # parameter sharding: per-layer gather / reduce hooks sit on the checkpointed layer boundary
+            need(tr.activation_checkpointing, "optimizer.backend=fsdp needs training.activation_checkpointing")
+            need(self.adapter.type == "none", "optimizer.backend=fsdp shards the base model: adapters use the "
+                                              "sharded-optimizer backends (auto, zero_fused, torch_*)")
+            need(o.name != "dflash_distillation" and m.family not in ("qwen3_8", "diffusion_gemma"),
+                 "optimizer.backend=fsdp is built for the dense decoder family (causal_lm, nemotron_labs_diffusion)")
+        if self.data.optimizer_step_unit == "trajectory":
+            need(self.data.input_mode == "dataset", "data.optimizer_step_unit=trajectory needs an indexed dataset "
+                                                    "with trajectory groups (data.input_mode=dataset)")
+        if self.data.trajectory_loss_reduction == "turn_mean":
+            need(self.data.optimizer_step_unit == "trajectory",
+                 "data.trajectory_loss_reduction=turn_mean applies to data.optimizer_step_unit=trajectory")
         if m.family not in ("auto", "hf"):
             from ..models.registry import objectives_for_family
 

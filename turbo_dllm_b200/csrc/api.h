@@ -77,6 +77,9 @@ int tdllm_sumsq_bf16(const void* g, long long n, float* out, void* stream);
 int tdllm_adamw(float* master, float* m, float* v, const void* grad, void* param, long long n,
                 float lr, float beta1, float beta2, float eps, float wd, int step,
                 float grad_scale, const float* sumsq, float max_norm, void* stream);
+int tdllm_adamw_f32grad(float* master, float* m, float* v, const float* grad, void* param, long long n,
+                        float lr, float beta1, float beta2, float eps, float wd, int step,
+                        float grad_scale, const float* sumsq, float max_norm, void* stream);
 int tdllm_ce_finalize(const float* stats, int M, int n_tiles, const int* labels,
                       const float* weights, float* lse_out, float* loss_rows, float* out2,
                       void* stream);
@@ -158,6 +161,13 @@ int tdllm_zero_fused_step(void* const* grad_ptrs, void* const* param_ptrs, void*
                           int world, long long start, long long n, long long decay_end, float lr,
                           float beta1, float beta2, float eps, float wd, int step, float grad_scale,
                           float max_norm, float* norm_out, int epoch, void* stream);
+
+// Parameter sharding: materialise a unit from the ranks' bf16 shards / reduce a unit's bf16 gradients into this
+// rank's fp32 shard (see comm.cu).
+int tdllm_fsdp_gather(void* const* shard_ptrs, long long shard_off, long long shard_len, long long unit_len,
+                      int rank, int world, void* out, void* stream);
+int tdllm_fsdp_reduce(void* const* grad_ptrs, long long my_off, long long n, int rank, int world, float* out,
+                      int accumulate, void* stream);
 
 int tdllm_kv_gather(void* const* staging_ptrs, void* const* flag_ptrs, const long long* counts, int rank,
                     int world, int row_bytes, void* out, int epoch, void* stream);

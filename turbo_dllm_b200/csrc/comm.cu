@@ -161,6 +161,48 @@ __global__ void zero_update_kernel(PeerPtrs params, PeerPtrs sumsq, const __nv_b
 
 
 // ---------------------------------------------------------------------------
+// Parameter sharding (FSDP): every rank keeps 1/W of each unit (a layer's matrices, the embedding, ...) of
+// the bf16 parameters in a symmetric shard buffer. A unit is materialised just before its layer runs by
+// pulling the W pieces (fsdp_gather_kernel: plain peer loads, every byte crosses NVLink once), and its
+// gradients leave the full-size bf16 gradient buffer as soon as the layer's backward is done:
+// fsdp_reduce_kernel pulls this rank's piece from every rank's buffer, sums in fp32 and writes (or adds to)
+// the rank's fp32 gradient shard, which the sharded AdamW consumes without another cast.
+// Counterparts: torch FSDP's per-module all-gather / reduce-scatter (dllm_parallel/core/optim/fsdp.py:56-114,
+// :145-264) and DeepSpeed's reduce-scatter buckets (dllm_parallel/core/optim/zero.py:93-211).
+// ---------------------------------------------------------------------------
+__global__ void fsdp_gather_kernel(PeerPtrs shards, long long shard_off8, long long shard_len8,
+                                   long long unit_len8, int rank, int world, uint4* __restrict__ out) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < unit_len8;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int k = (int)(i / shard_len8);
+    // the grid-stride walk spreads the blocks over all owners at any moment
+    const long long j = i - (long long)k * shard_len8;
+    out[i] = reinterpret_cast<const uint4*>(shards.p[k])[shard_off8 + j];
+  }
+}
+
+__global__ void fsdp_reduce_kernel(PeerPtrs grads, long long my_off8, long long n8, int rank, int world,
+                                   float* __restrict__ out, int accumulate) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * blockDim.x) {
+    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+    for (int k = 0; k < world; ++k) {
+      const int r = (rank + 1 + k) % world;
+      acc8(reinterpret_cast<const uint4*>(grads.p[r])[my_off8 + i], f);
+    }
+    float4* o = reinterpret_cast<float4*>(out + i * 8);
+    if (accumulate) {
+      const float4 a = o[0], b = o[1];
+      f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+      f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+    }
+    o[0] = make_float4(f[0], f[1], f[2], f[3]);
+    o[1] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Clean K/V exchange of context-sharded block parallelism over peer memory.
 //
 // gather: every rank owns `count[r]` rows of `row_bytes` bytes in its symmetric staging buffer;
@@ -388,6 +430,48 @@ extern "C" int tdllm_zero_fused_step(void* const* grad_ptrs, void* const* param_
   }
   comm::barrier_kernel<<<1, 32, 0, st>>>(f, rank, world, epoch + 2);
   TD_CUDA(cudaGetLastError(), "zero_fused_step launch");
+  return 0;
+}
+
+static unsigned copy_blocks(long long n16) {
+  long long blocks = (n16 + 255) / 256;
+  const long long cap = (long long)tdllm_num_sms() * 8;
+  return (unsigned)(blocks > cap ? cap : (blocks < 1 ? 1 : blocks));
+}
+
+// out[0, unit_len) = concatenation over ranks k of shard k's elements [shard_off, shard_off + shard_len)
+// (bf16 elements; all three are multiples of 8). No barrier inside: the caller orders the launch after the
+// barrier that follows the owners' last write of their shards.
+extern "C" int tdllm_fsdp_gather(void* const* shard_ptrs, long long shard_off, long long shard_len,
+                                 long long unit_len, int rank, int world, void* out, void* stream) {
+  comm::PeerPtrs sp;
+  if (fill_peers(sp, shard_ptrs, world)) return 1;
+  if ((shard_off | shard_len | unit_len) % 8 || shard_len <= 0 || unit_len > shard_len * world) {
+    tdllm_host::set_last_error("fsdp_gather: offsets and lengths must be multiples of 8 elements and the unit must fit its shards");
+    return 1;
+  }
+  if (unit_len <= 0) return 0;
+  comm::fsdp_gather_kernel<<<copy_blocks(unit_len / 8), 256, 0, (cudaStream_t)stream>>>(
+      sp, shard_off / 8, shard_len / 8, unit_len / 8, rank, world, (uint4*)out);
+  TD_CUDA(cudaGetLastError(), "fsdp_gather launch");
+  return 0;
+}
+
+// out[0, n) (+)= sum over ranks r of grad buffer r's elements [my_off, my_off + n) (bf16 in, fp32 out).
+// The caller places a barrier before (every rank's buffer is complete) and reuses a buffer only after the
+// next barrier.
+extern "C" int tdllm_fsdp_reduce(void* const* grad_ptrs, long long my_off, long long n, int rank, int world,
+                                 float* out, int accumulate, void* stream) {
+  comm::PeerPtrs gp;
+  if (fill_peers(gp, grad_ptrs, world)) return 1;
+  if ((my_off | n) % 8 || ((uintptr_t)out % 16)) {
+    tdllm_host::set_last_error("fsdp_reduce: offset and length must be multiples of 8 elements, the output 16-byte aligned");
+    return 1;
+  }
+  if (n <= 0) return 0;
+  comm::fsdp_reduce_kernel<<<copy_blocks(n / 8), 256, 0, (cudaStream_t)stream>>>(gp, my_off / 8, n / 8, rank, world,
+                                                                                 out, accumulate);
+  TD_CUDA(cudaGetLastError(), "fsdp_reduce launch");
   return 0;
 }
 

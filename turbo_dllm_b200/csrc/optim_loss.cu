@@ -47,8 +47,12 @@ __global__ void sumsq_bf16_kernel(const __nv_bfloat16* __restrict__ g, size_t n,
 // AdamW on a flat shard. grad_scale multiplies the gradient (loss scaling / averaging);
 // when sumsq and max_norm > 0 the gradient is also clipped to max_norm using
 // norm = sqrt(*sumsq) * grad_scale. step_size = lr / (1 - beta1^t); bias2 = 1 - beta2^t.
+__device__ __forceinline__ float grad_as_float(const __nv_bfloat16* g, size_t i) { return __bfloat162float(g[i]); }
+__device__ __forceinline__ float grad_as_float(const float* g, size_t i) { return g[i]; }
+
+template <typename G>
 __global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m,
-                             float* __restrict__ v, const __nv_bfloat16* __restrict__ grad,
+                             float* __restrict__ v, const G* __restrict__ grad,
                              __nv_bfloat16* __restrict__ param, size_t n, float lr, float beta1,
                              float beta2, float eps, float wd, float bias1, float bias2,
                              float grad_scale, const float* __restrict__ sumsq, float max_norm) {
@@ -61,7 +65,7 @@ __global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m,
   const float inv_sqrt_b2 = rsqrtf(bias2);
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (size_t)gridDim.x * blockDim.x) {
-    const float g = __bfloat162float(grad[i]) * gs;
+    const float g = grad_as_float(grad, i) * gs;
     float p = master[i];
     const float mi = beta1 * m[i] + (1.f - beta1) * g;
     const float vi = beta2 * v[i] + (1.f - beta2) * g * g;
@@ -282,10 +286,25 @@ extern "C" int tdllm_adamw(float* master, float* m, float* v, const void* grad, 
   if (n <= 0) return 0;
   const float bias1 = 1.f - powf(beta1, (float)step);
   const float bias2 = 1.f - powf(beta2, (float)step);
-  ol::adamw_kernel<<<grid_for((size_t)n, 256, 8), 256, 0, (cudaStream_t)stream>>>(
+  ol::adamw_kernel<__nv_bfloat16><<<grid_for((size_t)n, 256, 8), 256, 0, (cudaStream_t)stream>>>(
       master, m, v, (const __nv_bfloat16*)grad, (__nv_bfloat16*)param, (size_t)n, lr, beta1, beta2,
       eps, wd, bias1, bias2, grad_scale, sumsq, max_norm);
   TD_CHECK_LAUNCH("adamw");
+  return 0;
+}
+
+// Same update from an fp32 gradient (the shard that the fused gradient reduce-scatter leaves behind).
+extern "C" int tdllm_adamw_f32grad(float* master, float* m, float* v, const float* grad, void* param,
+                                   long long n, float lr, float beta1, float beta2, float eps, float wd,
+                                   int step, float grad_scale, const float* sumsq, float max_norm,
+                                   void* stream) {
+  if (n <= 0) return 0;
+  const float bias1 = 1.f - powf(beta1, (float)step);
+  const float bias2 = 1.f - powf(beta2, (float)step);
+  ol::adamw_kernel<float><<<grid_for((size_t)n, 256, 8), 256, 0, (cudaStream_t)stream>>>(
+      master, m, v, grad, (__nv_bfloat16*)param, (size_t)n, lr, beta1, beta2, eps, wd, bias1, bias2,
+      grad_scale, sumsq, max_norm);
+  TD_CHECK_LAUNCH("adamw_f32grad");
   return 0;
 }
 

@@ -116,6 +116,10 @@ class _LayerCheckpoint(torch.autograd.Function):
         h = h.detach().requires_grad_(True)
         from ..ops.gemm import skip_last_output
 
+        sharded = getattr(ctx.layer, "sharded", None)
+        if sharded is not None:      # parameter sharding: bring the layer's weights back, point its gradients
+            sharded.pre_layer(idx)
+            sharded.begin_layer_backward(idx)
         store.replaying = True
         try:
             with torch.enable_grad(), skip_last_output():
@@ -123,6 +127,8 @@ class _LayerCheckpoint(torch.autograd.Function):
         finally:
             store.replaying = False
         torch.autograd.backward(out, dout)
+        if sharded is not None:      # the layer's gradients are complete: reduce them into the ranks' shards
+            sharded.post_layer_backward(idx)
         return h.grad, None, None, None, None
 
 

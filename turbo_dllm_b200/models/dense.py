@@ -205,7 +205,18 @@ class BlockDiffusionTransformer(nn.Module):
         self.lm_head = self.flat.params.get("lm_head", self.embed)
         self.layers = nn.ModuleList(DecoderLayer(self.lcfg, i, self.flat, self.tp) for i in range(cfg.num_layers))
         self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device), persistent=False)
+        self.sharded = None      # parallel.fsdp.ShardedParameters when the parameters are sharded
         self.reset_parameters(seed, init_std)
+
+    def attach_parameter_sharding(self, sharded) -> None:
+        """From now on a layer's parameters exist at full size only while the layer runs: `sharded.pre_layer(i)`
+        materialises them, the checkpointed backward hands the gradients back (`activation_store`)."""
+        if not self.activation_checkpointing:
+            raise ValueError("parameter sharding needs training.activation_checkpointing (gradients leave a layer "
+                             "when its checkpointed backward ends)")
+        self.sharded = sharded
+        for layer in self.layers:
+            layer.sharded = sharded
 
     @torch.no_grad()
     def reset_parameters(self, seed: int, std: float) -> None:
@@ -258,6 +269,8 @@ class BlockDiffusionTransformer(nn.Module):
         if torch.is_grad_enabled() and not h.requires_grad:
             h = h.detach().requires_grad_(True)   # frozen embedding (adapters): keep the checkpoint chain alive
         for i, layer in enumerate(self.layers):
+            if self.sharded is not None:
+                self.sharded.pre_layer(i)
             if self.activation_checkpointing and torch.is_grad_enabled():
                 h = checkpointed_layer(layer, h, self.store, i, positions, self.inv_freq, attend)
             else:

@@ -62,6 +62,7 @@ class TrainingSession:
         self.task = None
         from ..profiling.system_trace import PhaseTimer
 
+        self.sharded = None
         self.trace = None                       # the trainer hands its SystemTrace over
         self.phase_timer = PhaseTimer(self.device)
         if spec.objective.name == "dflash_distillation":
@@ -97,6 +98,7 @@ class TrainingSession:
                 activation_offload=self._want_activation_offload(), seed=seed, tp=tp)
         self.memory_report("model built")
         self.lora = None
+        self.sharded = None      # parameter sharding (optimizer.backend: fsdp)
         if spec.adapter.type == "lora":
             from ..adapters.lora import apply_lora
 
@@ -152,10 +154,26 @@ class TrainingSession:
         else:
             group = runtime.optimizer_group if runtime is not None else (dist.group.WORLD if self.world > 1 else None)
             tp_group = runtime.tensor_group if (runtime is not None and runtime.tensor_parallel_size > 1) else None
-            self.optimizer = FlatAdamW(self.lora.flat if self.lora is not None else self.model.flat, group=group,
-                                       tp_group=tp_group,
-                                       fused_sync=None if tp_group is not None else self._build_fused_sync(group),
-                                       **okw)
+            if o.backend in ("fsdp", "fsdp2") and group is not None and dist.get_world_size(group) > 1:
+                from ..parallel.fsdp import ShardedAdamW, ShardedParameters
+
+                if self.lora is not None or self.cfg.is_hybrid:
+                    raise ValueError("optimizer.backend=fsdp shards the dense decoder's parameters; adapters and the "
+                                     "hybrid family use the sharded-optimizer backends")
+                peer = (self.device.type == "cuda" and spec.kernel.impl not in ("cpu_reference", "nccl_baseline"))
+                if peer:
+                    from ..parallel.symm import peer_access_available
+
+                    peer = peer_access_available(group)
+                self.sharded = ShardedParameters(self.model.flat, group, self.device, use_peer_kernels=peer,
+                                                 num_layers=self.cfg.num_layers)
+                self.model.attach_parameter_sharding(self.sharded)
+                self.optimizer = ShardedAdamW(self.sharded, tp_group=tp_group, **okw)
+            else:
+                self.optimizer = FlatAdamW(self.lora.flat if self.lora is not None else self.model.flat, group=group,
+                                           tp_group=tp_group,
+                                           fused_sync=None if tp_group is not None else self._build_fused_sync(group),
+                                           **okw)
         self.scheduler = RunSpecLRScheduler.from_run_spec(spec)
         self.steps_done = 0
         self.memory_report("session built")
@@ -179,6 +197,9 @@ class TrainingSession:
                 p.main_grad = grad[o:o + n].view(shape)
             sync.close()
             self.optimizer.fused_sync = None
+        if getattr(self, "sharded", None) is not None:
+            self.sharded.close()
+            self.sharded = None
         exchange = getattr(getattr(self, "attend", None), "exchange", None)
         if exchange is not None and hasattr(exchange, "close"):
             exchange.close()
@@ -235,7 +256,11 @@ class TrainingSession:
         per_layer = rows * cfg.hidden_size * 2
         ckpt = per_layer * cfg.num_layers
         work = rows * 2 * (6 * cfg.hidden_size + 2 * cfg.qkv_dim + 5 * max(cfg.intermediate_size, 1))
-        static = cfg.num_params() * (2 + 2 + 12 / max(self.world, 1))
+        if s.optimizer.backend in ("fsdp", "fsdp2") and self.world > 1:
+            # shards of parameters, fp32 gradients and AdamW state; two layers and the embeddings at full size
+            static = cfg.num_params() * 18 / self.world + 4 * 2 * cfg.layer_params() + 8 * cfg.vocab_size * cfg.hidden_size
+        else:
+            static = cfg.num_params() * (2 + 2 + 12 / max(self.world, 1))
         budget = 0.85 * torch.cuda.get_device_properties(self.device).total_memory
         if static + 2 * ckpt + work < budget:
             return False, False, True, 0
@@ -376,6 +401,8 @@ class TrainingSession:
         self.memory_report("after loss")
         with self._phase("backward"):
             (loss_sum / denominator).backward()
+            if self.sharded is not None:
+                self.sharded.end_micro_batch()
         self.memory_report("after backward")
         return loss_sum.detach(), l.shape[0], cb
 
@@ -431,6 +458,8 @@ class TrainingSession:
         with self._phase("zero_grad"):
             for f in self.flats():
                 f.zero_grad()
+            if self.sharded is not None:
+                self.sharded.zero_grad()
         with self._phase("data"):
             batches = self.data.next_optimizer_step_batches(spec.training.gradient_accumulation_steps)
         total = torch.zeros((), dtype=torch.float32, device=self.device)
@@ -458,8 +487,9 @@ class TrainingSession:
                 total += ls.float()
                 rows += n
         with self._phase("gradient_sync"):
-            for f in self.flats():
-                f.collect_grads()
+            if self.sharded is None:       # sharded parameters reduce their gradients layer by layer in the backward
+                for f in self.flats():
+                    f.collect_grads()
             if getattr(self, "_grad_div", 1.0) != 1.0:
                 self.model.flat.grad.div_(self._grad_div)
         lr, wd = self.scheduler.step()
@@ -493,12 +523,13 @@ class TrainingSession:
         if getattr(self, "lora", None) is not None:
             # the adapters are what training changes; every rank holds the whole (replicated) adapter buffer
             extra["adapter"] = self.lora.flat.data
-        return {**extra, "model": self.model.flat.data, "optimizer": self.optimizer.state_dict(),
+        model_state = self.sharded.param_shard if self.sharded is not None else self.model.flat.data
+        return {**extra, "model": model_state, "optimizer": self.optimizer.state_dict(),
                 "scheduler": self.scheduler.state_dict(), "objective": self.objective.state_dict(),
                 "data": self.data.state_dict(), "steps_done": self.steps_done}
 
     def load_state_dict(self, state: dict) -> None:
-        self.model.flat.data.copy_(state["model"])
+        (self.sharded.param_shard if self.sharded is not None else self.model.flat.data).copy_(state["model"])
         if getattr(self, "lora", None) is not None and "adapter" in state:
             self.lora.flat.data.copy_(state["adapter"])
         self.optimizer.load_state_dict(state["optimizer"])

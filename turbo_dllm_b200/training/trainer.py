@@ -172,7 +172,8 @@ def run_training(spec: RunSpec) -> dict:
                                "input_tokens_per_second_per_gpu": tokens_per_step / (ms / 1e3) / world},
                       "optimizer_step": not spec.training.skip_optimizer_step,
                       "gradient_accumulation_steps": spec.training.gradient_accumulation_steps,
-                      "optimizer_backend": "zero_fused" if session.optimizer.fused_sync else "flat_adamw",
+                      "optimizer_backend": ("fsdp_sharded" if getattr(session, "sharded", None) is not None else
+                                            "zero_fused" if session.optimizer.fused_sync else "flat_adamw"),
                       "peak_mib": (torch.cuda.max_memory_allocated(device) / 2 ** 20) if use_cuda else None})
                 if spec.profiler.phase_timing:
                     ev["phase_ms"] = session.phase_timer.take()
