@@ -15,7 +15,7 @@ MAPPING = {
 }
 
 
-def _run(rank, world, tp, steps):
+def _run(rank, world, tp, steps, sp=False):
     import torch.distributed as dist
 
     from turbo_dllm_b200.config.run_spec import RunSpec
@@ -25,6 +25,7 @@ def _run(rank, world, tp, steps):
     torch.set_num_threads(2)
     m = copy.deepcopy(MAPPING)
     m["topology"]["tensor_parallel_size"] = tp
+    m["topology"]["sequence_parallel"] = bool(sp)
     spec = RunSpec.from_mapping(m).validate(world_size=world)
     rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
     s = TrainingSession(spec, device="cpu", runtime=rt)
@@ -34,17 +35,37 @@ def _run(rank, world, tp, steps):
         losses.append(float(r.loss_sum) / r.denominator)
         norms.append(s.optimizer.grad_norm())
     names = {n: p.detach().clone() for n, p in s.model.flat.params.items()}
-    return losses, norms, names["final_norm"], names["layers.1.w_down"], names["layers.0.w_qkv"]
+    return (losses, norms, names["final_norm"], names["layers.1.w_down"], names["layers.0.w_qkv"],
+            names["layers.0.q_norm"], names["layers.1.input_norm"])
 
 
 @pytest.mark.distributed
 def test_tp2_matches_single_process():
     ref = _run(0, 1, 1, 3)
     outs = run_ranks(_run, 2, args=(2, 3), deadline_s=240)
-    for r, (losses, norms, fnorm, w_down, w_qkv) in enumerate(outs):
+    for r, (losses, norms, fnorm, w_down, w_qkv, q_norm, in_norm) in enumerate(outs):
         assert losses == pytest.approx(ref[0], rel=2e-4, abs=2e-4)
         assert norms == pytest.approx(ref[1], rel=2e-3)
         assert torch.allclose(torch.from_numpy(fnorm), ref[2], rtol=1e-3, atol=2e-5)
+        full = ref[3]
+        n = full.shape[1] // 2
+        assert torch.allclose(torch.from_numpy(w_down), full[:, r * n:(r + 1) * n], rtol=1e-3, atol=1e-4)
+        # replicated weights whose gradient a rank sees only partly (its heads) stay equal to the single-rank run
+        assert torch.allclose(torch.from_numpy(q_norm), ref[5], rtol=1e-3, atol=2e-5)
+
+
+@pytest.mark.distributed
+def test_tp2_with_sequence_parallel_rows_matches_single_process():
+    """Residual stream sharded by rows inside the tensor-parallel pair: gather → column GEMM, row GEMM →
+    reduce-scatter, layer-norm gradients summed over the pair."""
+    ref = _run(0, 1, 1, 3)
+    outs = run_ranks(_run, 2, args=(2, 3, True), deadline_s=240)
+    for r, (losses, norms, fnorm, w_down, w_qkv, q_norm, in_norm) in enumerate(outs):
+        assert losses == pytest.approx(ref[0], rel=2e-4, abs=2e-4)
+        assert norms == pytest.approx(ref[1], rel=2e-3)
+        assert torch.allclose(torch.from_numpy(fnorm), ref[2], rtol=1e-3, atol=2e-5)
+        assert torch.allclose(torch.from_numpy(q_norm), ref[5], rtol=1e-3, atol=2e-5)
+        assert torch.allclose(torch.from_numpy(in_norm), ref[6], rtol=1e-3, atol=2e-5)
         full = ref[3]
         n = full.shape[1] // 2
         assert torch.allclose(torch.from_numpy(w_down), full[:, r * n:(r + 1) * n], rtol=1e-3, atol=1e-4)

@@ -37,6 +37,16 @@ int tdllm_gemm_allreduce_bf16(const void* A, const void* B, void* D, int M, int 
                               long long ws_rows, void* const* ws, void* const* flags, int max_ctas,
                               void* stream);
 int tdllm_gemm_flag_count(int M, int N);
+// Sequence-parallel forms (see gemm_sm100.cu): GEMM -> reduce-scatter and all-gather -> GEMM in one kernel each.
+int tdllm_gemm_reduce_scatter_bf16(const void* A, const void* B, void* D_local, int M, int N, int K, long long lda,
+                                   long long ldb, long long ldd, int a_mn_major, int b_mn_major,
+                                   const void* c_local, long long ldc, int world, int rank, int epoch,
+                                   long long ws_rows, void* const* ws, void* const* flags, int max_ctas,
+                                   void* stream);
+int tdllm_gemm_allgather_bf16(void* const* bufs, const void* B, void* D, int M, int N, int K, long long ldb,
+                              long long ldd, int b_mn_major, int mode, int world, int rank, int epoch,
+                              void* const* ready, int* counter, int* tile_ready, int launch_no, int max_ctas,
+                              void* stream);
 
 // Cross-rank finish of vocab-parallel CE statistics over peer memory: lse = logsumexp over ranks of the
 // shard lse, target = sum of the shard target logits. ws[d]: [world][rows_cap][2] fp32, flags[d]:
@@ -173,6 +183,18 @@ int tdllm_kv_gather(void* const* staging_ptrs, void* const* flag_ptrs, const lon
                     int world, int row_bytes, void* out, int epoch, void* stream);
 int tdllm_kv_scatter_reduce(void* const* partial_ptrs, void* const* flag_ptrs, const long long* counts,
                             int rank, int world, int row_bytes, void* out, int epoch, void* stream);
+
+// ---- expert-parallel dispatch / combine over peer memory (moe_dispatch.cu) -------------
+int tdllm_ep_counts_exchange(const int* my_counts, void* const* tabs, void* const* flags, int rank, int world,
+                             int E, int epoch, void* stream);
+int tdllm_ep_dispatch(const void* x, const int* experts, const float* scale, const long long* base, int* counters,
+                      const int* pos_in, int* pos_out, void* const* slabs, long long rows, int k, int H,
+                      int e_local, long long cap_rows, int world, void* stream);
+int tdllm_ep_zero_pad_rows(void* slab, const long long* begin, const long long* count, int e_local, int H,
+                           void* stream);
+int tdllm_ep_combine(void* out, const float* weights, const int* experts, const int* pos, void* const* slabs,
+                     void* keep, long long rows, int k, int H, int e_local, int world, void* stream);
+int tdllm_ep_weight_grad(const void* dout, const void* y, float* dw, long long rows, int k, int H, void* stream);
 
 // ---- gated delta rule: chunk-to-chunk state scan ---------------------------------
 // All tensors fp32 and contiguous. ut/o/u: [BH, N, C, Dv]; w/qi/ko: [BH, N, C, Dk]; qk: [BH, N, C, C];

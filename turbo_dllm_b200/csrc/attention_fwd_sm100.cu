@@ -34,6 +34,7 @@
 // dllm_parallel/core/attention/context_parallel_attention.py:2315-2691 (:701-741 for the gather itself).
 #include <cstring>
 #include "common.cuh"
+#include "peer_pull.cuh"
 #include "api.h"
 
 namespace tdllm {
@@ -49,8 +50,9 @@ constexpr int KV_STAGES = 2;
 constexpr int THREADS = 576;   // 16 softmax warps (2 heads x 2 column halves x 4 lane quarters), TMA warp 16, MMA warp 17
 constexpr int THREADS_CSBP = 640;   // + puller warps 18 and 19
 constexpr int KID_PULL = 6;         // error-record id of the pull side of the context-sharded form
-constexpr int MAX_PEERS = 16;
-constexpr int PULL_ROWS = 16;       // rows per claim; a 128-row key tile is complete after 8 claims
+using peer::MAX_PEERS;
+using peer::PULL_ROWS;
+using peer::PullPlan;
 constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 512 + 2048 + 1024;   // + barriers + row exchange
 
 struct FwdParams {
@@ -66,21 +68,6 @@ struct FwdParams {
   float* lse;          // [Hq, nq_pad]
   float scale_log2;    // softmax scale * log2(e)
   float scale;         // softmax scale
-};
-
-// Pull plan of the context-sharded form. The remote rows form segments, one per peer, in the order this
-// rank visits its peers (rank+1, rank+2, ... so that no owner serves every puller at once).
-struct PullPlan {
-  const uint4* src[MAX_PEERS];        // segment s: the peer's staged rows (peer memory)
-  const int* ready[MAX_PEERS];        // segment s: word in THIS rank's flag array that the peer sets to `want`
-  long long seg_begin[MAX_PEERS + 1]; // first remote row of segment s (prefix sums of the peers' row counts)
-  uint4* dst;                         // [n_rows][row_vec16] in this GPU's memory
-  int* counter;                       // claim counter, zero at launch
-  int* tile_ready;                    // [nrt] finished claims per remote key tile, cumulative over launches
-  long long n_rows;
-  int nseg, want, row_vec16;
-  int nlt, nrt;                       // local and remote key tiles
-  int tile_target;                    // count a remote tile has reached when all its rows of this launch are in
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -107,85 +94,6 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
 
 __device__ __forceinline__ bool key_visible(int code, int lo, int hi, int grp) {
   return code >= 0 ? (code >= lo && code < hi) : (code == grp);
-}
-
-__device__ __forceinline__ uint4 ld_peer16(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ void fence_proxy_async_global() {
-  asm volatile("fence.proxy.async.global;" ::: "memory");
-}
-// bounded wait on a counter in this GPU's memory that other CTAs of the launch advance
-__device__ __forceinline__ bool count_wait_geq(const int* flag, int want, int kernel_id, int detail) {
-  const unsigned long long t0 = globaltimer_ns();
-  const unsigned long long budget = g_tdllm_timeout_ns;
-#pragma unroll 1
-  while (true) {
-    int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-    if (v >= want) return true;
-    if (error_is_set()) return false;
-    if (globaltimer_ns() - t0 > budget) {
-      set_error(ERR_WAIT_TIMEOUT, kernel_id, detail);
-      return false;
-    }
-    __nanosleep(32);
-  }
-}
-
-// One puller warp: claims 16-row pieces of the remote rows until none is left.
-__device__ __forceinline__ void pull_remote_rows(const PullPlan& pl, int lane) {
-  const int n_claims = pl.nrt * (BKV / PULL_ROWS);
-  uint32_t seen = 0;   // segments whose owner has been seen ready
-  // every pass takes one claim off the shared counter: at most n_claims + 1 passes per warp
-#pragma unroll 1
-  for (int pass = 0; pass <= n_claims; ++pass) {
-    int c = 0;
-    if (lane == 0) c = atomicAdd(pl.counter, 1);
-    c = __shfl_sync(0xffffffffu, c, 0);
-    if (c >= n_claims) break;
-    long long row = (long long)c * PULL_ROWS;
-    const long long row_end = min(row + PULL_ROWS, pl.n_rows);
-    bool ok = true;
-#pragma unroll 1
-    while (row < row_end) {
-      int s = 0;
-      while (s + 1 < pl.nseg && row >= pl.seg_begin[s + 1]) ++s;
-      const long long run_end = min(row_end, pl.seg_begin[s + 1]);
-      if (!((seen >> s) & 1u)) {
-        int good = 1;
-        if (lane == 0) good = flag_wait_geq(pl.ready[s], pl.want, KID_PULL, s) ? 1 : 0;
-        if (!__shfl_sync(0xffffffffu, good, 0)) { ok = false; break; }
-        seen |= 1u << s;
-      }
-      const uint4* src = pl.src[s] + (row - pl.seg_begin[s]) * pl.row_vec16;
-      uint4* dst = pl.dst + row * pl.row_vec16;
-      const long long n = (run_end - row) * pl.row_vec16;
-#pragma unroll 1
-      for (long long i = lane; i < n; i += 32 * 8) {
-        uint4 v[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (i + u * 32 < n) v[u] = ld_peer16(src + i + u * 32);
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (i + u * 32 < n) dst[i + u * 32] = v[u];
-      }
-      row = run_end;
-    }
-    if (!ok) break;   // the error record is set: every waiter of the launch leaves its loop
-    // the rows are read by TMA (async proxy) in other CTAs: order them before the count
-    fence_proxy_async_global();
-    __threadfence();
-    __syncwarp();
-    if (lane == 0)
-      asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(pl.tile_ready + c / (BKV / PULL_ROWS)) : "memory");
-  }
 }
 
 template <bool CSBP>
@@ -279,8 +187,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (CSBP && kt >= pl.nlt) {
           // a peer's rows: wait until the pullers have brought the whole tile into local memory
           kt -= pl.nlt;
-          if (!count_wait_geq(pl.tile_ready + kt, pl.tile_target, KID_PULL, 100)) break;
-          fence_proxy_async_global();
+          if (!peer::count_wait_geq(pl.tile_ready + kt, pl.tile_target, KID_PULL, 100)) break;
+          peer::fence_proxy_async_global();
           mk = &tm_kr;
           mv = &tm_vr;
         }
@@ -361,7 +269,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else if (CSBP && warp >= 18) {
     // ------------------------------ pullers (context-sharded form) -------------
-    pull_remote_rows(pl, lane);
+    peer::pull_remote_rows(pl, lane, KID_PULL);
   } else {
     // ------------------------------ softmax groups -----------------------------
     // four warps per (head, column half): a thread owns one query row and 64 of the tile's 128 keys;
@@ -624,6 +532,7 @@ extern "C" int tdllm_attn_fwd_csbp(const void* q, const void* k_loc, const void*
     pl.src[s] = (const uint4*)staging[peer];
     pl.ready[s] = (const int*)ready[rank] + peer;
     pl.seg_begin[s] = total;
+    pl.dst_begin[s] = total;
     total += counts[peer];
   }
   for (int s = world - 1; s <= MAX_PEERS; ++s) pl.seg_begin[s] = total;

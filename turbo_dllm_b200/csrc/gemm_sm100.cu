@@ -18,11 +18,25 @@
 // walk the tiles in the same order, so the exchange of one tile overlaps the tensor-core work on
 // the next (two accumulator buffers); no collective call is involved.
 //
+// Sequence parallelism inside a tensor-parallel group adds two fused forms (template argument AG, rs_rows):
+//   all-gather -> GEMM : A's rows are sharded over the ranks. Two extra warps per CTA pull the peers' rows into
+//     this GPU's copy of A (plain peer loads, 16-row pieces claimed from a shared counter, one arrival counter
+//     per 128-row tile) while the tiles of this rank's own rows run; the TMA warp waits (bounded) for a remote
+//     tile's counter before loading it. The tile walk starts at this rank's rows and follows the pull order.
+//   GEMM -> reduce-scatter : the all-reduce epilogue with an owner per row tile. A tile owned by a peer is pushed
+//     to that peer only and not stored here; a tile this rank owns waits for the peers' partials and is stored
+//     to the rank's [M / ranks, N] output. Rank r starts its walk at the rows of rank r+1 and reaches its own
+//     rows last, so the ranks push to different owners at any moment and an owner's waits are short.
+// Counterpart: Transformer Engine's userbuffers overlap (dllm_parallel/core/parallel/transformer_engine.py:84-139)
+// behind dllm_parallel/core/parallel/tensor_parallel/sequence_parallel.py:158-285.
+//
 // This replaces the library GEMMs the reference calls (cublasGemmEx in
 // dllm_parallel/core/csrc/fused_linear_ce/fused_linear_ce_cuda.cu:618-791 and the
 // torch / Transformer Engine linears of
 // dllm_parallel/core/models/backbones/nemotron/model.py:3727-4190).
+#include <cstring>
 #include "common.cuh"
+#include "peer_pull.cuh"
 #include "api.h"
 
 namespace tdllm {
@@ -36,6 +50,8 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int EPI_WARPS = 4;
 constexpr int EPI_BUF_BYTES = 32 * 128;  // one warp: 32 rows x 128 bytes
 constexpr int GEMM_THREADS = 32 * (2 + EPI_WARPS);
+constexpr int GEMM_THREADS_AG = GEMM_THREADS + 64;   // + two puller warps (all-gather fused into the product)
+constexpr int KID_GEMM_PULL = 7;
 constexpr int SMEM_EPI = EPI_WARPS * 2 * EPI_BUF_BYTES;
 
 // PAIR = 1: one CTA per 128 x 256 tile. PAIR = 2: a cluster of two CTAs per 256 x 256 tile
@@ -95,16 +111,22 @@ struct GemmParams {
   long long a_group_rows;   // A's M coordinate is shifted back by group * a_group_rows (per-group outputs)
   const int* mt_kbegin;
   const int* mt_kend;
+  // sequence-parallel forms
+  int m_rot;        // the tile walk starts at this group of PAIR row tiles and wraps around
+  int rs_rows;      // > 0: reduce-scatter epilogue, rank r owns rows [r * rs_rows, (r + 1) * rs_rows)
+  int ag_rows;      // > 0: all-gather form, rank r's rows of A are [r * ag_rows, (r + 1) * ag_rows)
+  int ag_rank;
 };
 
-__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& m, int& n) {
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& m, int& n, int m_rot = 0) {
   constexpr int G = 8;
   const int per_group = G * n_tiles;
   const int g = t / per_group;
   const int first_m = g * G;
   const int gsz = min(m_tiles - first_m, G);
   const int r = t - g * per_group;
-  m = first_m + r % gsz;
+  m = first_m + r % gsz + m_rot;
+  if (m >= m_tiles) m -= m_tiles;
   n = r / gsz;
 }
 
@@ -112,11 +134,12 @@ __device__ __forceinline__ float apply_softcap(float x, float cap) {
   return cap > 0.f ? cap * tanhf(x / cap) : x;
 }
 
-template <int PAIR>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <int PAIR, bool AG>
+__global__ void __launch_bounds__(AG ? GEMM_THREADS_AG : GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_d, const GemmParams p,
+                 const __grid_constant__ peer::PullPlan pl) {
   constexpr int STAGES = Cfg<PAIR>::STAGES;
   constexpr int STAGE_BYTES = Cfg<PAIR>::STAGE_BYTES;
   constexpr int SMEM_TILES = Cfg<PAIR>::SMEM_TILES;
@@ -178,7 +201,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int t = walker; t < num_tiles && ok; t += walkers) {
         int tm, tn;
-        tile_coords(t, m_groups, p.n_tiles, tm, tn);
+        tile_coords(t, m_groups, p.n_tiles, tm, tn, p.m_rot);
         tm = tm * PAIR + rank;
         const int b_row0 = tn * BN + rank * B_ROWS;
         const int tml = min(tm, p.m_tiles - 1);   // a pair's second CTA may sit past the last row tile
@@ -186,6 +209,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int a_m0 = tm * BM - (p.mt_group ? (int)(p.mt_group[tml] * p.a_group_rows) : 0);
         const int kb0 = p.mt_kbegin ? p.mt_kbegin[tml] : 0;
         const int kb1 = p.mt_kend ? p.mt_kend[tml] : k_blocks;
+        if (AG && tm < p.m_tiles && (tm * BM) / p.ag_rows != p.ag_rank) {
+          // rows of a peer: wait until the pullers have brought this 128-row tile into local memory
+          if (!peer::count_wait_geq(pl.tile_ready + tm, pl.tile_target, KID_GEMM_PULL, 100)) {
+            ok = false;
+            break;
+          }
+          peer::fence_proxy_async_global();
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, GEMM_KERNEL_ID, 10)) {
             ok = false;
@@ -240,7 +271,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int kb0 = 0, kb1 = k_blocks;
         if (p.mt_kbegin) {
           int tm_, tn_;
-          tile_coords(t, m_groups, p.n_tiles, tm_, tn_);
+          tile_coords(t, m_groups, p.n_tiles, tm_, tn_, p.m_rot);
           const int tml = min(tm_ * PAIR, p.m_tiles - 1);
           kb0 = p.mt_kbegin[tml];
           kb1 = p.mt_kend[tml];
@@ -284,6 +315,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       __syncwarp();
     }
+  } else if (AG && warp >= 2 + EPI_WARPS) {
+    // ------------------------------ pullers (all-gather form) -----------------
+    peer::pull_remote_rows(pl, lane, KID_GEMM_PULL);
   } else {
     // ------------------------------ epilogue warps ----------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
@@ -293,7 +327,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int it = 0;
     for (int t = walker; t < num_tiles; t += walkers, ++it) {
       int tm, tn;
-      tile_coords(t, m_groups, p.n_tiles, tm, tn);
+      tile_coords(t, m_groups, p.n_tiles, tm, tn, p.m_rot);
       tm = tm * PAIR + rank;
       const int buf = it & 1;
       const uint32_t tphase = (it >> 1) & 1;
@@ -303,6 +337,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int gm = tm * BM + row;
       const int n0 = tn * BN;
       uint32_t r[32];
+      // reduce-scatter form: the owner of this row tile, and the shift from global to the owner's local rows
+      const int owner = p.rs_rows > 0 ? min((tm * BM) / p.rs_rows, p.ar_world - 1) : p.ar_rank;
+      const int row_shift = p.rs_rows > 0 ? owner * p.rs_rows : 0;
+      bool skip_store = false;
       // a group without rows runs no MMA: its accumulator is undefined and counts as zero
       const bool empty_k = p.mt_kbegin && p.mt_kbegin[min(tm, p.m_tiles - 1)] >= p.mt_kend[min(tm, p.m_tiles - 1)];
 
@@ -311,8 +349,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         //    this rank); the fp32 accumulator stays in TMEM for step 2
         const bool live = tm < p.m_tiles;   // a pair's second CTA may sit past the last row tile
         const size_t slot = (size_t)p.ar_rank * p.ar_rows * p.N;
+        const bool push = p.rs_rows == 0 || owner != p.ar_rank;   // an owner keeps its own partial in TMEM
+        skip_store = p.rs_rows > 0 && owner != p.ar_rank;
 #pragma unroll 1
-        for (int c = 0; c < BN / 64 && live; ++c) {
+        for (int c = 0; c < BN / 64 && live && push; ++c) {
           uint8_t* st = my_stage + sbuf * EPI_BUF_BYTES;
           if (lane == 0) tma_store_wait_read<1>();   // an earlier tile's TMA store may still read this buffer
           __syncwarp();
@@ -339,9 +379,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int col = n0 + c * 64 + ch * 8;
             if (grow < p.M && col < p.N) {
               const uint4 v = *reinterpret_cast<const uint4*>(st + sw128_offset(rr, ch));
-              const size_t off = slot + (size_t)grow * p.N + col;
-              for (int d = 0; d < p.ar_world; ++d)
-                if (d != p.ar_rank) *reinterpret_cast<uint4*>((__nv_bfloat16*)p.ar_ws[d] + off) = v;
+              const size_t off = slot + (size_t)(grow - row_shift) * p.N + col;
+              if (p.rs_rows > 0) {
+                *reinterpret_cast<uint4*>((__nv_bfloat16*)p.ar_ws[owner] + off) = v;
+              } else {
+                for (int d = 0; d < p.ar_world; ++d)
+                  if (d != p.ar_rank) *reinterpret_cast<uint4*>((__nv_bfloat16*)p.ar_ws[d] + off) = v;
+              }
             }
           }
           __syncwarp();
@@ -355,14 +399,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const size_t per_rank_flags = (size_t)p.m_tiles * p.n_tiles * 4;
         bool ok_ar = true;
         if (live && lane < p.ar_world && lane != p.ar_rank) {
-          flag_store_release(p.ar_flags[lane] + (size_t)p.ar_rank * per_rank_flags + fidx, p.ar_epoch);
-          ok_ar = flag_wait_geq(p.ar_flags[p.ar_rank] + (size_t)lane * per_rank_flags + fidx, p.ar_epoch,
-                                GEMM_KERNEL_ID, 40 + lane);
+          if (p.rs_rows == 0) {
+            flag_store_release(p.ar_flags[lane] + (size_t)p.ar_rank * per_rank_flags + fidx, p.ar_epoch);
+            ok_ar = flag_wait_geq(p.ar_flags[p.ar_rank] + (size_t)lane * per_rank_flags + fidx, p.ar_epoch,
+                                  GEMM_KERNEL_ID, 40 + lane);
+          } else if (owner != p.ar_rank) {
+            if (lane == owner)
+              flag_store_release(p.ar_flags[owner] + (size_t)p.ar_rank * per_rank_flags + fidx, p.ar_epoch);
+          } else {
+            ok_ar = flag_wait_geq(p.ar_flags[p.ar_rank] + (size_t)lane * per_rank_flags + fidx, p.ar_epoch,
+                                  GEMM_KERNEL_ID, 40 + lane);
+          }
         }
         if (!__all_sync(0xffffffffu, ok_ar)) break;
         // 2. falls into the bf16 store path below, which adds the peers' partials (and C) to the accumulator
       }
-      if (p.mode == EPI_CE_STATS) {
+      if (skip_store) {
+        // reduce-scatter form, a peer owns this tile: the partial has been pushed, nothing is stored here
+      } else if (p.mode == EPI_CE_STATS) {
         float mx = -INFINITY, sum = 0.f, tgt = 0.f;
         const int label = (gm < p.M) ? p.labels[gm] : -1;
 #pragma unroll 1
@@ -516,8 +570,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const int s = s0 + u;
                   use[u] = s <= p.ar_world && s != p.ar_rank && !(s == p.ar_world && !p.accumulate);
                   const __nv_bfloat16* dp = (s >= p.ar_world)
-                                                ? (const __nv_bfloat16*)p.c_ptr + (size_t)gm * p.ldc + cbase
-                                                : ws + ((size_t)s * p.ar_rows + gm) * p.N + cbase;
+                                                ? (const __nv_bfloat16*)p.c_ptr + (size_t)(gm - row_shift) * p.ldc + cbase
+                                                : ws + ((size_t)s * p.ar_rows + (gm - row_shift)) * p.N + cbase;
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {
                     v[u][j] = make_uint4(0, 0, 0, 0);
@@ -569,7 +623,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&tmap_d, smem_u32(st), n0 + c * 64, tm * BM + q * 32);
+            tma_store_2d(&tmap_d, smem_u32(st), n0 + c * 64, tm * BM + q * 32 - row_shift);
             tma_store_commit();
           }
           sbuf ^= 1;
@@ -629,6 +683,19 @@ struct ArConfig {
   long long rows;
   void* const* ws;
   void* const* flags;
+  int rs_rows;   // > 0: reduce-scatter form, rows per rank
+};
+
+// all-gather form: A's rows are sharded over the ranks (`rows` each); bufs[r] = rank r's copy of the whole A
+// (symmetric memory, rank r's own rows already in place), ready[r] = rank r's int32[world] flag array
+struct AgConfig {
+  int world, rank, epoch;
+  long long rows;
+  void* const* bufs;
+  void* const* ready;
+  int* counter;
+  int* tile_ready;
+  int launch_no;
 };
 
 static int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
@@ -636,11 +703,21 @@ static int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K,
                      int accumulate, int mode, const int* labels, const float* lse,
                      const float* rowscale, float* stats, int exclude_index, float softcap,
                      int max_ctas, const void* c_src, long long ldc, const ArConfig* ar, const GroupConfig* grp,
-                     void* stream) {
+                     void* stream, const AgConfig* ag = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (ar && ar->rs_rows > 0 && (ar->rs_rows % (2 * BM) || (long long)ar->rs_rows * ar->world != M)) {
+    tdllm_host::set_last_error("gemm: reduce-scatter epilogue needs M = ranks * rows with rows a multiple of %d", 2 * BM);
+    return 1;
+  }
+  if (ag && (ag->world < 2 || ag->world > AR_MAX_RANKS || ag->rows % (2 * BM) || ag->rows * ag->world != M ||
+             a_mn_major || (lda != K) || grp)) {
+    tdllm_host::set_last_error("gemm: all-gather form needs 2..%d ranks, a dense K-major A of ranks * rows rows, rows a "
+                               "multiple of %d", AR_MAX_RANKS, 2 * BM);
+    return 1;
+  }
   if (mode == EPI_ALLREDUCE) {
     if (!ar || ar->world < 2 || ar->world > AR_MAX_RANKS || ar->rank < 0 || ar->rank >= ar->world ||
-        out_fp32 || (N % 8) || ar->rows < M) {
+        out_fp32 || (N % 8) || ar->rows < (ar->rs_rows > 0 ? ar->rs_rows : M)) {
       tdllm_host::set_last_error("gemm: all-reduce epilogue needs 2..%d ranks, bf16 output, N %% 8 == 0 and a "
                                  "workspace of at least M rows", AR_MAX_RANKS);
       return 1;
@@ -661,10 +738,16 @@ static int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K,
   static bool attr_set = false;
   static int max_pairs = 0;   // clusters of two that fit on the device at once (0 = pairs unavailable)
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg<1>::SMEM_BYTES);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      e = cudaFuncSetAttribute(gemm_bf16_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               Cfg<2>::SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_bf16_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               Cfg<1>::SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_bf16_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                Cfg<2>::SMEM_BYTES);
     if (e != cudaSuccess) {
       tdllm_host::set_last_error("gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -679,7 +762,7 @@ static int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K,
       cfg.gridDim = dim3(2 * 74); cfg.blockDim = dim3(GEMM_THREADS);
       cfg.dynamicSmemBytes = Cfg<2>::SMEM_BYTES; cfg.attrs = &at; cfg.numAttrs = 1;
       int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_kernel<2>, &cfg) == cudaSuccess && n > 0) max_pairs = n;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_kernel<2, false>, &cfg) == cudaSuccess && n > 0) max_pairs = n;
       else (void)cudaGetLastError();
     }
     attr_set = true;
@@ -718,7 +801,8 @@ static int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K,
         tdllm_host::set_last_error("gemm: destination needs 16-byte aligned base and row stride");
         return 1;
       }
-      dims[0] = (uint64_t)n_out; dims[1] = (uint64_t)M;
+      // reduce-scatter form: the destination holds the owner's rows only
+      dims[0] = (uint64_t)n_out; dims[1] = (uint64_t)((ar && ar->rs_rows > 0) ? ar->rs_rows : M);
       box[0] = out_fp32 ? 32 : 64; box[1] = 32;
       strides[0] = (uint64_t)ldd * esz;
       if (tdllm_host::encode_tmap(&td, out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
@@ -744,9 +828,44 @@ static int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K,
   p.mt_kbegin = grp ? grp->mt_kbegin : nullptr; p.mt_kend = grp ? grp->mt_kend : nullptr;
   p.ar_world = 0; p.ar_rank = 0; p.ar_epoch = 0; p.ar_rows = 0; p.ar_out = D; p.ar_ldd = ldd;
   for (int i = 0; i < AR_MAX_RANKS; ++i) { p.ar_ws[i] = nullptr; p.ar_flags[i] = nullptr; }
+  p.m_rot = 0; p.rs_rows = 0; p.ag_rows = 0; p.ag_rank = 0;
   if (mode == EPI_ALLREDUCE) {
     p.ar_world = ar->world; p.ar_rank = ar->rank; p.ar_epoch = ar->epoch; p.ar_rows = ar->rows;
     for (int i = 0; i < ar->world; ++i) { p.ar_ws[i] = ar->ws[i]; p.ar_flags[i] = (int*)ar->flags[i]; }
+    if (ar->rs_rows > 0) {
+      // start at the rows of the next rank, reach the own rows last (see the file header)
+      p.rs_rows = ar->rs_rows;
+      p.m_rot = (int)(((long long)((ar->rank + 1) % ar->world) * ar->rs_rows) / (BM * (pair ? 2 : 1)));
+    }
+  }
+  peer::PullPlan pl;
+  memset(&pl, 0, sizeof(pl));
+  if (ag) {
+    p.ag_rows = (int)ag->rows; p.ag_rank = ag->rank;
+    p.m_rot = (int)(((long long)ag->rank * ag->rows) / (BM * (pair ? 2 : 1)));   // own rows first
+    const long long row_bytes = (long long)K * 2;
+    long long total = 0;
+    pl.nseg = ag->world - 1;
+    for (int sgm = 0; sgm < ag->world - 1; ++sgm) {
+      const int peer_rank = (ag->rank + 1 + sgm) % ag->world;
+      pl.src[sgm] = (const uint4*)((const char*)ag->bufs[peer_rank] + (long long)peer_rank * ag->rows * row_bytes);
+      pl.ready[sgm] = (const int*)ag->ready[ag->rank] + peer_rank;
+      pl.seg_begin[sgm] = total;
+      pl.dst_begin[sgm] = (long long)peer_rank * ag->rows;
+      total += ag->rows;
+    }
+    for (int sgm = ag->world - 1; sgm <= peer::MAX_PEERS; ++sgm) pl.seg_begin[sgm] = total;
+    pl.dst = (uint4*)ag->bufs[ag->rank];
+    pl.counter = ag->counter;
+    pl.tile_ready = ag->tile_ready;
+    pl.n_rows = total;
+    pl.want = ag->epoch;
+    pl.row_vec16 = (int)(row_bytes / 16);
+    pl.tile_target = ag->launch_no * (peer::TILE_ROWS / peer::PULL_ROWS);
+    if (cudaMemsetAsync(ag->counter, 0, sizeof(int), (cudaStream_t)stream) != cudaSuccess) {
+      tdllm_host::set_last_error("gemm: clearing the claim counter failed");
+      return 5;
+    }
   }
   cudaError_t e;
   if (pair) {
@@ -758,15 +877,19 @@ static int gemm_impl(const void* A, const void* B, void* D, int M, int N, int K,
     cudaLaunchAttribute at;
     at.id = cudaLaunchAttributeClusterDimension;
     at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
-    cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(ag ? GEMM_THREADS_AG : GEMM_THREADS);
     cfg.dynamicSmemBytes = Cfg<2>::SMEM_BYTES; cfg.stream = (cudaStream_t)stream;
     cfg.attrs = &at; cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<2>, ta, tb, td, p);
+    if (ag) e = cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<2, true>, ta, tb, td, p, pl);
+    else e = cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<2, false>, ta, tb, td, p, pl);
   } else {
     const int tiles = p.m_tiles * p.n_tiles;
     int ctas = max_ctas > 0 ? max_ctas : tdllm_num_sms();
     if (ctas > tiles) ctas = tiles;
-    gemm_bf16_kernel<1><<<ctas, GEMM_THREADS, Cfg<1>::SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, td, p);
+    if (ag)
+      gemm_bf16_kernel<1, true><<<ctas, GEMM_THREADS_AG, Cfg<1>::SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, td, p, pl);
+    else
+      gemm_bf16_kernel<1, false><<<ctas, GEMM_THREADS, Cfg<1>::SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, td, p, pl);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) {
@@ -800,9 +923,51 @@ extern "C" int tdllm_gemm_allreduce_bf16(const void* A, const void* B, void* D, 
                                          int b_mn_major, const void* c_src, long long ldc, int world,
                                          int rank, int epoch, long long ws_rows, void* const* ws,
                                          void* const* flags, int max_ctas, void* stream) {
-  ArConfig ar{world, rank, epoch, ws_rows, ws, flags};
+  ArConfig ar{world, rank, epoch, ws_rows, ws, flags, 0};
   return gemm_impl(A, B, D, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, 0, c_src != nullptr, EPI_ALLREDUCE,
                    nullptr, nullptr, nullptr, nullptr, -1, 0.f, max_ctas, c_src, ldc, &ar, nullptr, stream);
+}
+
+// GEMM -> reduce-scatter over peer memory: D_local[M / world, N] = rows [rank * M / world, ...) of
+// sum over ranks of (A_r * B_r) (+ C_local, the same rows of a residual). Same workspace contract as
+// tdllm_gemm_allreduce_bf16, with ws_rows >= M / world (a workspace keeps only the owner's rows).
+extern "C" int tdllm_gemm_reduce_scatter_bf16(const void* A, const void* B, void* D_local, int M, int N, int K,
+                                              long long lda, long long ldb, long long ldd, int a_mn_major,
+                                              int b_mn_major, const void* c_local, long long ldc, int world,
+                                              int rank, int epoch, long long ws_rows, void* const* ws,
+                                              void* const* flags, int max_ctas, void* stream) {
+  if (world < 2 || M % world || ws_rows < M / world) {
+    tdllm_host::set_last_error("gemm_reduce_scatter: M must divide by the ranks and the workspace hold M / ranks rows");
+    return 1;
+  }
+  ArConfig ar{world, rank, epoch, ws_rows, ws, flags, M / world};
+  // the destination tensor map spans the owner's rows only: stores of other tiles never happen
+  return gemm_impl(A, B, D_local, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, 0, c_local != nullptr,
+                   EPI_ALLREDUCE, nullptr, nullptr, nullptr, nullptr, -1, 0.f, max_ctas, c_local, ldc, &ar, nullptr,
+                   stream);
+}
+
+// all-gather -> GEMM over peer memory: D[M, N] = A * B where A's rows are sharded over the ranks. bufs[r]: rank
+// r's [M, K] bf16 copy of A in symmetric memory as mapped here; this rank's own rows [rank * M / world, ...) are
+// already in bufs[rank]; the other rows are pulled inside the kernel once the owners have stored `epoch` into
+// slot `owner` of every rank's ready array (tdllm_symm_signal after they wrote their rows). counter: one int32,
+// zeroed here; tile_ready: one int32 per 128-row tile of A, zeroed once by the caller, `launch_no` = 1-based
+// number of this call on those counters. mode: EPI_STORE or EPI_SWIGLU.
+extern "C" int tdllm_gemm_allgather_bf16(void* const* bufs, const void* B, void* D, int M, int N, int K,
+                                         long long ldb, long long ldd, int b_mn_major, int mode, int world,
+                                         int rank, int epoch, void* const* ready, int* counter, int* tile_ready,
+                                         int launch_no, int max_ctas, void* stream) {
+  if (mode != EPI_STORE && mode != EPI_SWIGLU) {
+    tdllm_host::set_last_error("gemm_allgather: only the store and SwiGLU epilogues");
+    return 1;
+  }
+  if (world < 2 || M % world) {
+    tdllm_host::set_last_error("gemm_allgather: M must divide by the ranks");
+    return 1;
+  }
+  AgConfig ag{world, rank, epoch, M / world, bufs, ready, counter, tile_ready, launch_no};
+  return gemm_impl(bufs[rank], B, D, M, N, K, K, ldb, ldd, 0, b_mn_major, 0, 0, mode, nullptr, nullptr, nullptr,
+                   nullptr, -1, 0.f, max_ctas, nullptr, 0, nullptr, nullptr, stream, &ag);
 }
 
 // Grouped product over row tiles (experts): tile tm of M uses the slice `mt_group[tm]` of B (B's row coordinate

@@ -26,8 +26,9 @@ from ..ops.gemm import linear, linear_residual, linear_swiglu, row_parallel_line
 from ..ops.linear_ce import linear_cross_entropy
 from ..ops.norm import rmsnorm
 from ..ops.rope import qk_norm_rope, rope_inv_freq
-from ..parallel.tensor_parallel import (TPContext, copy_to_tensor_parallel, vocab_parallel_embedding,
-                                        vocab_parallel_linear_cross_entropy)
+from ..parallel.tensor_parallel import (TPContext, copy_to_tensor_parallel, gather_rows_replicated_grad,
+                                        sp_column_linear, sp_row_linear_residual, take_rows_sequence_parallel,
+                                        vocab_parallel_embedding, vocab_parallel_linear_cross_entropy)
 from .activation_store import ActivationStore, checkpointed_layer
 from .config import ModelConfig
 
@@ -130,6 +131,14 @@ class DecoderLayer(nn.Module):
         self.post_norm, self.w_gate_up, self.w_down = g("post_norm"), g("w_gate_up"), g("w_down")
         self.q_norm = g("q_norm") if cfg.qk_norm else None
         self.k_norm = g("k_norm") if cfg.qk_norm else None
+        if tp is not None and tp.size > 1:
+            # replicated weights whose gradient a rank computes from its own heads / rows only
+            for p in (self.q_norm, self.k_norm):
+                if p is not None:
+                    p.tp_partial = True
+            if tp.sequence_parallel:
+                self.input_norm.tp_partial = True
+                self.post_norm.tp_partial = True
 
     def forward(self, h, positions, inv_freq, attend: Callable):
         """h: residual stream [rows, H] -> residual stream. Both residual adds happen in the
@@ -138,6 +147,8 @@ class DecoderLayer(nn.Module):
         tpg = tp.group if tp is not None and tp.size > 1 else None
         if getattr(self, "lora", None) is not None:
             return self._forward_lora(h, positions, inv_freq, attend)
+        if tp is not None and tp.sequence_parallel:
+            return self._forward_sequence_parallel(h, positions, inv_freq, attend)
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
         qkv = linear(y, self.w_qkv, tp) if tpg is not None else linear(y, self.w_qkv)
         qkv = qk_norm_rope(qkv, positions, inv_freq, self.q_norm, self.k_norm, cfg.num_attention_heads,
@@ -147,6 +158,20 @@ class DecoderLayer(nn.Module):
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
         act = linear_swiglu(y2, self.w_gate_up, tp) if tpg is not None else linear_swiglu(y2, self.w_gate_up)
         return row_parallel_linear_residual(act, self.w_down, h, tp, last=True)
+
+    def _forward_sequence_parallel(self, h, positions, inv_freq, attend):
+        """h: this rank's rows of the residual stream. Norms run on local rows; the column-parallel projections
+        gather the rows on their way in, the row-parallel ones scatter the sum on their way out."""
+        cfg, tp = self.cfg, self.tp
+        y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
+        qkv = sp_column_linear(y, self.w_qkv, tp)
+        qkv = qk_norm_rope(qkv, positions, inv_freq, self.q_norm, self.k_norm, cfg.num_attention_heads,
+                           cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
+        a = attend(qkv, self.idx)
+        h = sp_row_linear_residual(a, self.w_o, h, tp)
+        y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
+        act = sp_column_linear(y2, self.w_gate_up, tp, swiglu=True)
+        return sp_row_linear_residual(act, self.w_down, h, tp, last=True)
 
     def _forward_lora(self, h, positions, inv_freq, attend):
         """Same layer with low-rank updates on the adapted projections (single tensor-parallel rank)."""
@@ -190,6 +215,9 @@ class BlockDiffusionTransformer(nn.Module):
         tps = self.tp.size if self.tp is not None else 1
         self.lcfg = local_config(cfg, tps)  # per-rank shapes
         self.activation_checkpointing = activation_checkpointing
+        if self.tp is not None:
+            # gathered inputs may stay in the rotating peer-memory buffers until a checkpointed layer's backward
+            self.tp.sp_saved_in_place = bool(activation_checkpointing)
         self.store = ActivationStore(torch.device(device), offload=activation_offload)
         h = cfg.hidden_size
         specs = [("embed", (cfg.vocab_size // tps, h), True), ("final_norm", (h,), False)]
@@ -266,6 +294,12 @@ class BlockDiffusionTransformer(nn.Module):
         if soft_embeddings is not None and soft_rows is not None and soft_rows.numel() > 0:
             h = h.index_add(0, soft_rows, soft_embeddings.to(h.dtype))
         positions = positions.to(torch.int32)
+        sp = self.tp is not None and self.tp.sequence_parallel
+        if sp:
+            if h.shape[0] % self.tp.size:
+                raise ValueError(f"sequence parallelism needs the {h.shape[0]} packed rows to divide by "
+                                 f"tensor_parallel_size {self.tp.size}")
+            h = take_rows_sequence_parallel(h, self.tp)
         if torch.is_grad_enabled() and not h.requires_grad:
             h = h.detach().requires_grad_(True)   # frozen embedding (adapters): keep the checkpoint chain alive
         for i, layer in enumerate(self.layers):
@@ -275,6 +309,8 @@ class BlockDiffusionTransformer(nn.Module):
                 h = checkpointed_layer(layer, h, self.store, i, positions, self.inv_freq, attend)
             else:
                 h = layer(h, positions, self.inv_freq, attend)
+        if sp:
+            h = gather_rows_replicated_grad(h, self.tp)
         y, _ = rmsnorm(h, self.final_norm, self.cfg.rms_norm_eps)
         return y
 

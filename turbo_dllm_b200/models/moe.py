@@ -84,6 +84,32 @@ class ExpertBank(nn.Module):
         self.ep_rank = dist.get_rank(ep_group) if ep_group is not None else 0
         self.e_local = self.w_gu.shape[0]
         self.last_counts = None
+        self.exchange_holder = None    # set by the model: one PeerExpertExchange shared by all layers
+
+    def _peer_exchange(self, x: torch.Tensor):
+        """The peer-memory dispatch / combine state, or None (CPU, no peer access, shapes off the tile grid,
+        TDLLM_EP_PEER=0): the caller then uses all-to-all collectives."""
+        import os
+
+        from ..ops.grouped import grouped_supported
+
+        holder = self.exchange_holder
+        if (holder is None or self.ep < 2 or not x.is_cuda or os.environ.get("TDLLM_EP_PEER", "1") == "0"
+                or not grouped_supported(x, self.w_gu) or not grouped_supported(x, self.w_down)):
+            return None
+        if holder.get("exchange") is None and not holder.get("failed"):
+            try:
+                from ..parallel.expert_exchange import PeerExpertExchange
+
+                holder["exchange"] = PeerExpertExchange(self.ep_group, x.device, rows=x.shape[0],
+                                                        top_k=self.cfg.num_experts_per_token, hidden=x.shape[1],
+                                                        num_experts=self.cfg.num_experts)
+            except Exception as e:   # no peer access, IPC refused: collectives carry the exchange
+                holder["failed"] = str(e)
+        ex = holder.get("exchange")
+        if ex is not None and x.shape[0] > ex.max_rows:
+            return None
+        return ex
 
     def _local_experts(self, x_sorted: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
         """x_sorted: rows grouped by local expert (`counts` per expert, on the device). On the GPU all
@@ -114,6 +140,19 @@ class ExpertBank(nn.Module):
         rows, H = x.shape
         k = cfg.num_experts_per_token
         w, idx = route_topk(linear(x, self.router), k)
+        ex = self._peer_exchange(x)
+        if ex is not None:
+            # rows go straight into the owners' slabs and come back weighted: no sort, no collective, no host read
+            from ..ops.grouped import grouped_linear
+            from ..parallel.expert_exchange import peer_combine, peer_dispatch
+
+            state: dict = {}
+            flat32 = idx.reshape(-1).to(torch.int32).contiguous()
+            x_pad = peer_dispatch(x.contiguous(), flat32, ex, state)
+            act = swiglu(grouped_linear(x_pad, self.w_gu, state["g"]))
+            y_pad = grouped_linear(act, self.w_down, state["g"])
+            self.last_counts = None
+            return peer_combine(y_pad, w, ex, state)
         flat_e = idx.reshape(-1)                                        # [rows*k]
         order = torch.argsort(flat_e, stable=True)
         token_of = torch.div(order, k, rounding_mode="floor")
@@ -249,6 +288,9 @@ class MoEBlockDiffusionTransformer(BlockDiffusionTransformer):
         self.embed, self.final_norm = self.flat.params["embed"], self.flat.params["final_norm"]
         self.lm_head = self.flat.params.get("lm_head", self.embed)
         self.layers = nn.ModuleList(MoEDecoderLayer(cfg, i, self.flat, ep_group) for i in range(cfg.num_layers))
+        self.expert_exchange = {}      # filled on the first routed batch on a GPU (parallel/expert_exchange.py)
+        for layer in self.layers:
+            layer.experts.exchange_holder = self.expert_exchange
         self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device), persistent=False)
         ep_rank = dist.get_rank(ep_group) if ep_group is not None else 0
         self.reset_parameters(seed, init_std)

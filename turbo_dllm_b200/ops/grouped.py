@@ -42,6 +42,15 @@ class GroupedRows:
     mt_group: torch.Tensor      # [capacity / 128] expert of every 128-row tile
     row_begin: torch.Tensor     # [E] first padded row of every expert
     row_blocks_end: torch.Tensor  # [E] end of the expert's rows in 64-row blocks (rounded up)
+    valid_tiles: torch.Tensor | None = None   # [capacity / 128] bool: tiles inside some expert's padded segment
+    # (None = all). Tiles outside run no tensor-core work: a slab of static capacity is mostly such tiles.
+
+    def k_range(self, k_blocks: int):
+        """Per-tile K-block ranges for the forward / input-gradient products (None = every tile runs all of K)."""
+        if self.valid_tiles is None:
+            return None, None
+        kend = (self.valid_tiles.to(torch.int32) * int(k_blocks)).contiguous()
+        return torch.zeros_like(kend), kend
 
 
 def build_grouped_rows(counts: torch.Tensor, sorted_rows: int) -> GroupedRows:
@@ -86,8 +95,9 @@ class _GroupedLinear(torch.autograd.Function):
     def forward(ctx, x_pad, w_all, g: GroupedRows):
         E, N, K = w_all.shape
         y = torch.empty(g.capacity, N, dtype=x_pad.dtype, device=x_pad.device)
+        kb, ke = g.k_range(K // 64)
         _launch(x_pad, w_all.view(E * N, K), y, g.capacity, N, K, 0, 0, 0, EPI_STORE, g.mt_group, N, E * N,
-                0, 0, None, None)
+                0, 0, kb, ke)
         ctx.save_for_backward(x_pad, w_all)
         ctx.g, ctx.wref = g, w_all
         return y
@@ -101,8 +111,9 @@ class _GroupedLinear(torch.autograd.Function):
         dx = None
         if ctx.needs_input_grad[0]:
             dx = torch.empty_like(x_pad)
+            kb, ke = g.k_range(N // 64)
             _launch(dy, w_all.view(E * N, K), dx, g.capacity, K, N, 0, 1, 0, EPI_STORE, g.mt_group, N, E * N,
-                    0, 0, None, None)
+                    0, 0, kb, ke)
         # dW[e] = dy_eᵀ x_e: output rows e*N.., A = dy read MN-major with its M coordinate taken modulo N
         tiles = torch.arange(E * N // 128, device=dy.device)
         grp = (tiles * 128 // N).to(torch.int32)

@@ -368,8 +368,9 @@ class ShardedAdamW:
         wd = self.weight_decay if weight_decay is None else weight_decay
         g = sp.grad_shard
         split = sp.decay_local
-        sharded_sq = torch.dot(g[:split], g[:split]).reshape(1)
-        repl_sq = torch.dot(g[split:], g[split:]).reshape(1)
+        # vector_norm reduces without a temporary and takes more than 2^31 elements (a dot product does not)
+        sharded_sq = torch.linalg.vector_norm(g[:split]).square().reshape(1)
+        repl_sq = torch.linalg.vector_norm(g[split:]).square().reshape(1)
         if self.tp_group is not None:
             # matrices are split over the tensor-parallel group, norm weights are replicated on it
             dist.all_reduce(sharded_sq, group=self.tp_group)

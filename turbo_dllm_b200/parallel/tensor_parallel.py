@@ -124,6 +124,10 @@ def scatter_sequence_parallel(x, group):
     return x if group is None else _ScatterRowsSP.apply(x, group)
 
 
+class FusedSequenceParallelUnavailable:
+    reason = ""
+
+
 class TPContext:
     """Group handle plus the shard arithmetic the model needs."""
 
@@ -156,6 +160,30 @@ class TPContext:
         ws = maybe_create(self.group, torch.device(device), rows, cols)
         self._fused_ar[cols] = ws if ws is not None else False
         return ws
+
+    def fused_sequence_parallel(self, rows: int, cols: int, device):
+        """Workspace of the fused all-gather→GEMM / GEMM→reduce-scatter kernels for activations of `rows` x
+        `cols`, or None when the group cannot use them (CPU, no peer access, row shards that are not whole
+        256-row tiles, TDLLM_TP_FUSED_SP=0): the caller then uses collectives around the GEMM."""
+        import os
+
+        if (self.size < 2 or torch.device(device).type != "cuda" or rows % (256 * self.size)
+                or os.environ.get("TDLLM_TP_FUSED_SP", "1") == "0"):
+            return None
+        key = ("sp", rows, cols)
+        ws = self._fused_ar.get(key)
+        if ws is False:
+            return None
+        if ws is None:
+            try:
+                from .fused_sequence_parallel import FusedSequenceParallel
+
+                ws = FusedSequenceParallel(self.group, torch.device(device), rows, cols)
+            except Exception as e:   # no peer access, no kernels: keep the collective path and say why once
+                FusedSequenceParallelUnavailable.reason = str(e)
+                ws = False
+            self._fused_ar[key] = ws
+        return ws or None
 
     def ce_exchange(self, rows: int, device):
         """Peer-memory workspace for the cross-rank finish of vocab-parallel cross-entropy, or None."""
@@ -333,3 +361,191 @@ def vocab_parallel_linear_cross_entropy(h, w_shard, labels, weights, tp: TPConte
     per_row = torch.where(valid, m + torch.log(se) - tgt, torch.zeros_like(m))
     wts = torch.ones_like(per_row) if weights is None else weights.float()
     return (per_row * wts).sum(), per_row.detach()
+
+
+# ------------------------------------------------------- sequence parallelism inside the tensor-parallel group
+# The residual stream is sharded along rows: rank r holds rows [r·n, (r+1)·n) of `rows = n·T`. A column-parallel
+# projection first gathers the rows (all-gather → GEMM; backward: input gradient → reduce-scatter), a row-parallel
+# projection ends in a reduce-scatter of its partial sums (GEMM → reduce-scatter; backward: all-gather → GEMMs).
+# On CUDA with peer access both run as ONE kernel each (csrc/gemm_sm100.cu: the gather is pulled into local memory
+# by extra warps of the GEMM while tiles of local rows run; the scatter is the reduce-scatter form of the
+# all-reduce epilogue); elsewhere they are collectives followed / preceded by the GEMM.
+# Counterparts: dllm_parallel/core/parallel/tensor_parallel/sequence_parallel.py:158-285 and the userbuffers
+# overlap of dllm_parallel/core/parallel/transformer_engine.py:84-139.
+
+def _gather_rows(x: torch.Tensor, tp: TPContext) -> torch.Tensor:
+    out = x.new_empty(tp.size * x.shape[0], *x.shape[1:])
+    coll.all_gather_into_tensor(out, x.contiguous(), "tensor", group=tp.group)
+    return out
+
+
+def _reduce_scatter_rows(x: torch.Tensor, tp: TPContext) -> torch.Tensor:
+    n = x.shape[0] // tp.size
+    if x.is_cuda:
+        out = x.new_empty(n, *x.shape[1:])
+        coll.reduce_scatter_tensor(out, x.contiguous(), "tensor", group=tp.group)
+        return out
+    full = x.contiguous().clone()
+    coll.all_reduce(full, "tensor", group=tp.group)
+    return full[tp.rank * n:(tp.rank + 1) * n].clone()
+
+
+class _TakeRowsSP(torch.autograd.Function):
+    """Full (replicated) rows -> this rank's rows; backward all-gathers the ranks' row gradients."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        n = x.shape[0] // tp.size
+        return x[tp.rank * n:(tp.rank + 1) * n].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        return _gather_rows(g, ctx.tp), None
+
+
+class _GatherRowsReplicatedGrad(torch.autograd.Function):
+    """This rank's rows -> all rows, for consumers that compute the SAME thing on every rank (final norm and
+    the vocabulary-parallel loss, whose hidden-state gradient is already summed): backward takes the slice."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _gather_rows(x, tp)
+
+    @staticmethod
+    def backward(ctx, g):
+        tp = ctx.tp
+        n = g.shape[0] // tp.size
+        return g[tp.rank * n:(tp.rank + 1) * n].contiguous(), None
+
+
+def take_rows_sequence_parallel(x, tp: TPContext):
+    return _TakeRowsSP.apply(x, tp)
+
+
+def gather_rows_replicated_grad(x, tp: TPContext):
+    return _GatherRowsReplicatedGrad.apply(x, tp)
+
+
+class _GatherLinearSP(torch.autograd.Function):
+    """y = gather_rows(x_local) · Wᵀ for a column-parallel W (optionally with SwiGLU on interleaved gate/up)."""
+
+    @staticmethod
+    def forward(ctx, x_local, w, tp, swiglu):
+        from ..ops._util import use_native
+        from ..ops.activation import swiglu_forward
+
+        fused = tp.fused_sequence_parallel(x_local.shape[0] * tp.size, x_local.shape[1], x_local.device) \
+            if use_native(x_local, w) else None
+        if fused is not None:
+            y, x_full = fused.gather_matmul(x_local, w)
+            if torch.is_grad_enabled() and not getattr(tp, "sp_saved_in_place", False):
+                x_full = x_full.clone()     # the rotating buffer is reused before an un-checkpointed backward
+        else:
+            x_full = _gather_rows(x_local, tp)
+            y = gemm(x_full, w)
+        ctx.tp, ctx.wref, ctx.swiglu = tp, w, swiglu
+        if swiglu:
+            act = swiglu_forward(y)
+            ctx.save_for_backward(x_full, w, y)
+            return act
+        ctx.save_for_backward(x_full, w)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops._util import grad_sink, mark_grad_written, use_native
+        from ..ops.activation import swiglu_backward
+
+        tp = ctx.tp
+        if ctx.swiglu:
+            x_full, w, gu = ctx.saved_tensors
+            dy = swiglu_backward(dy.contiguous(), gu)
+        else:
+            x_full, w = ctx.saved_tensors
+            dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            fused = tp.fused_sequence_parallel(dy.shape[0], w.shape[1], dy.device) if use_native(dy, w) else None
+            if fused is not None:
+                dx = fused.matmul_scatter(dy, w, b_mn_major=True)
+            else:
+                dx = _reduce_scatter_rows(gemm(dy, w, b_mn_major=True), tp)
+        if ctx.needs_input_grad[1]:
+            sink, acc = grad_sink(ctx.wref)
+            if sink is not None:
+                gemm(dy, x_full, a_mn_major=True, b_mn_major=True, out=sink, accumulate=acc)
+                mark_grad_written(ctx.wref)
+            else:
+                dw = gemm(dy, x_full, a_mn_major=True, b_mn_major=True, out_dtype=w.dtype)
+        return dx, dw, None, None
+
+
+class _LinearScatterResidualSP(torch.autograd.Function):
+    """h_local = res_local + reduce_scatter_rows(x · W_rᵀ) for a row-parallel W (split along its input)."""
+
+    @staticmethod
+    def forward(ctx, x, w, res_local, tp, value_unused):
+        from ..ops._util import use_native
+
+        ctx.save_for_backward(x, w)
+        ctx.tp, ctx.wref = tp, w
+        if value_unused:
+            return torch.empty_like(res_local)
+        fused = tp.fused_sequence_parallel(x.shape[0], w.shape[0], x.device) if use_native(x, w) else None
+        if fused is not None:
+            return fused.matmul_scatter(x if x.is_contiguous() else x.contiguous(), w, residual=res_local)
+        return res_local + _reduce_scatter_rows(gemm(x, w), tp)
+
+    @staticmethod
+    def backward(ctx, dy_local):
+        from ..ops._util import grad_sink, mark_grad_written, use_native
+
+        x, w = ctx.saved_tensors
+        tp = ctx.tp
+        dx = dw = None
+        dy_local = dy_local.contiguous()
+        fused = tp.fused_sequence_parallel(x.shape[0], w.shape[0], x.device) if use_native(x, w) else None
+        if fused is not None and ctx.needs_input_grad[0]:
+            dx, dy = fused.gather_matmul(dy_local, w, b_mn_major=True)
+        else:
+            dy = _gather_rows(dy_local, tp)
+            if ctx.needs_input_grad[0]:
+                dx = gemm(dy, w, b_mn_major=True)
+        if ctx.needs_input_grad[1]:
+            sink, acc = grad_sink(ctx.wref)
+            if sink is not None:
+                gemm(dy, x, a_mn_major=True, b_mn_major=True, out=sink, accumulate=acc)
+                mark_grad_written(ctx.wref)
+            else:
+                dw = gemm(dy, x, a_mn_major=True, b_mn_major=True, out_dtype=w.dtype)
+        return dx, dw, (dy_local if ctx.needs_input_grad[2] else None), None, None
+
+
+def sp_column_linear(x_local, w, tp: TPContext, swiglu: bool = False):
+    return _GatherLinearSP.apply(x_local, w, tp, swiglu)
+
+
+def sp_row_linear_residual(x, w_shard, res_local, tp: TPContext, last: bool = False):
+    from ..ops.gemm import _Replay
+
+    unused = last and _Replay.skip_last_output and torch.is_grad_enabled()
+    return _LinearScatterResidualSP.apply(x, w_shard, res_local, tp, unused)
+
+
+def sync_partial_gradients(params, tp: TPContext) -> None:
+    """Sums, over the tensor-parallel group, the gradients of replicated parameters that every rank computed
+    from ITS part of the work only (`param.tp_partial`): per-head q/k norm weights see this rank's heads, and
+    under sequence parallelism the layer norms see this rank's rows. One all-reduce over a packed copy.
+    Counterpart of the replicated-parameter sync of dllm_parallel/core/parallel/grad_sync.py:110-187."""
+    todo = [p for p in params if getattr(p, "tp_partial", False) and getattr(p, "main_grad", None) is not None]
+    if not todo or tp is None or tp.size == 1:
+        return
+    flat = torch.cat([p.main_grad.reshape(-1).float() for p in todo])
+    coll.all_reduce(flat, "tensor", group=tp.group)
+    off = 0
+    for p in todo:
+        n = p.main_grad.numel()
+        p.main_grad.copy_(flat[off:off + n].view_as(p.main_grad).to(p.main_grad.dtype))
+        off += n

@@ -200,6 +200,10 @@ class TrainingSession:
         if getattr(self, "sharded", None) is not None:
             self.sharded.close()
             self.sharded = None
+        ee = getattr(getattr(self, "model", None), "expert_exchange", None)
+        if ee and ee.get("exchange") is not None:
+            ee["exchange"].close()
+            ee["exchange"] = None
         exchange = getattr(getattr(self, "attend", None), "exchange", None)
         if exchange is not None and hasattr(exchange, "close"):
             exchange.close()
@@ -402,6 +406,7 @@ class TrainingSession:
         with self._phase("backward"):
             (loss_sum / denominator).backward()
             if self.sharded is not None:
+                self._sync_tensor_parallel_partial_gradients()     # per micro-batch: the buffers restart each time
                 self.sharded.end_micro_batch()
         self.memory_report("after backward")
         return loss_sum.detach(), l.shape[0], cb
@@ -450,6 +455,13 @@ class TrainingSession:
             cnt /= bpcp
         return float(cnt) * copies
 
+    def _sync_tensor_parallel_partial_gradients(self) -> None:
+        tp = getattr(self.model, "tp", None)
+        if tp is not None and tp.size > 1:
+            from ..parallel.tensor_parallel import sync_partial_gradients
+
+            sync_partial_gradients(self.model.flat.params.values(), tp)
+
     def _phase(self, name: str):
         return self.phase_timer.phase(name, self.trace)
 
@@ -490,6 +502,7 @@ class TrainingSession:
             if self.sharded is None:       # sharded parameters reduce their gradients layer by layer in the backward
                 for f in self.flats():
                     f.collect_grads()
+                self._sync_tensor_parallel_partial_gradients()     # once, on the sums over the micro-batches
             if getattr(self, "_grad_div", 1.0) != 1.0:
                 self.model.flat.grad.div_(self._grad_div)
         lr, wd = self.scheduler.step()
