@@ -41,6 +41,18 @@ def test_block_diffusion_full_sequence(L, bs, views, Hq, Hkv):
     _run(layout, n, n, Hq, Hkv)
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(2, 2), (3, 1), (6, 2)])
+def test_odd_number_of_query_heads_per_kv_head(Hq, Hkv, monkeypatch):
+    """Group sizes 1 and 3: the last CTA of a group runs its single head in both pipelines; the one-pass
+    backward takes any group size."""
+    from turbo_dllm_b200.ops.attention import single_sequence_layout
+
+    monkeypatch.setenv("TDLLM_ATTN_BWD", "fused")
+    layout = single_sequence_layout(384, 32, "cuda", 1)
+    _run(layout, 768, 768, Hq, Hkv)
+    _run_bwd(layout, 768, 768, Hq, Hkv)
+
+
 def test_ragged_rows_and_sparse_keys():
     """Row counts that are not multiples of 128, keys that are a strided subset (a CP shard),
     and query rows that see no key at all."""

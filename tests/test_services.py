@@ -177,3 +177,48 @@ def test_execution_facade_and_launch_wrappers():
     for name in ("torchrun.sh", "slurm.sh"):
         text = open(os.path.join(here, name)).read()
         assert "turbo_dllm_b200.cli.main launch" in text and os.access(os.path.join(here, name), os.X_OK)
+
+
+def test_family_executors_and_registration():
+    """Every family has an executor with capabilities, the session goes through it, and a new family plugs in by
+    registering one (no edit of the session)."""
+    import torch
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.models import contracts as c
+    from turbo_dllm_b200.models.registry import (FAMILY_OBJECTIVES, executor_for_family, register_executor,
+                                                 supported_families)
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    for fam in supported_families():
+        ex = executor_for_family(fam)
+        assert isinstance(ex, c.BackboneExecutor) and ex.family.name == fam
+        assert ex.family.objectives == FAMILY_OBJECTIVES[fam]
+    assert executor_for_family("causal_lm").capabilities.parameter_sharding
+    assert not executor_for_family("qwen3_8").capabilities.tensor_parallel
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "num_layers": 1},
+        "objective": {"name": "standard_block_diffusion", "block_size": 16},
+        "training": {"batch_size": 1, "steps": 1},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}).validate()
+    problems = executor_for_family("qwen3_8").validate_run_spec(spec.with_overrides(
+        {"topology": {"tensor_parallel_size": 2}, "objective": {"name": "fast_dllm_v2"}}))
+    assert any("tensor-parallel" in p for p in problems)
+
+    built = []
+
+    class Custom(c.DenseExecutor):
+        def build_model(self, ctx):
+            built.append(ctx.cfg.hidden_size)
+            return super().build_model(ctx)
+
+    old = executor_for_family("causal_lm")
+    try:
+        register_executor("causal_lm", Custom(old.family))
+        s = TrainingSession(spec, device="cpu")
+        assert built == [s.cfg.hidden_size] and isinstance(s.executor, Custom)
+        assert torch.isfinite(s.step().loss_sum)
+        assert s.executor.parallel_work_units(spec) == 4
+        assert s.executor.parameter_shard_units(s.model)[-1] == "norm_weights"
+    finally:
+        register_executor("causal_lm", old)

@@ -126,13 +126,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   // work decomposition
   const int G = p.Hq / p.Hkv;
-  const int pairs = G / 2;
+  const int pairs = (G + 1) / 2;   // an odd group's last CTA runs its single head in both pipelines
   int w = blockIdx.x;
   const int pr = w % pairs;
   w /= pairs;
   const int kvh = w % p.Hkv;
   const int qt = p.order[w / p.Hkv];
   const int h0 = kvh * G + 2 * pr;
+  const int h_last = kvh * G + G - 1;
   const int list_begin = p.tile_ptr[qt];
   const int n = p.tile_ptr[qt + 1] - list_begin;
   const int* list = p.tile_idx + list_begin;
@@ -177,7 +178,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int c = 0; c < 2; ++c)
           tma_load_2d(smem_u32(sQ + i * TILE_BYTES + c * HALF_BYTES), &tm_q, bar_q,
-                      (h0 + i) * HD + c * 64, qt * BQ);
+                      min(h0 + i, h_last) * HD + c * 64, qt * BQ);
       for (int j = 0; j < n; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -381,14 +382,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       if (sub == 0)
-        p.lse[(size_t)(h0 + i) * p.nq_pad + grow] = l > 0.f ? m_used * p.scale + __logf(l) : -INFINITY;
+        p.lse[(size_t)min(h0 + i, h_last) * p.nq_pad + grow] = l > 0.f ? m_used * p.scale + __logf(l) : -INFINITY;
       fence_proxy_async_smem();
       mbar_arrive(bar_epi + 8 * i);
       if (row == 0 && sub == 0) {
         if (mbar_wait_spin(bar_epi + 8 * i, 0, KID, 32)) {
 #pragma unroll
           for (int c = 0; c < 2; ++c)
-            tma_store_2d(&tm_o, smem_u32(st + c * HALF_BYTES), (h0 + i) * HD + c * 64, qt * BQ);
+            tma_store_2d(&tm_o, smem_u32(st + c * HALF_BYTES), min(h0 + i, h_last) * HD + c * 64, qt * BQ);
           tma_store_commit();
           tma_store_wait_all();
         }
@@ -427,8 +428,8 @@ int encode_rows_tmap(CUtensorMap* out, const void* base, long long cols, long lo
 }  // namespace tdllm_host
 
 static int attn_fwd_check(const char* who, int Hq, int Hkv, const long long* lds, const void* const* ptrs, int n) {
-  if (Hq % Hkv || (Hq / Hkv) % 2) {
-    tdllm_host::set_last_error("%s: query heads per KV head must be even (got %d/%d)", who, Hq, Hkv);
+  if (Hq % Hkv) {
+    tdllm_host::set_last_error("%s: %d query heads do not divide over %d KV heads", who, Hq, Hkv);
     return 1;
   }
   for (int i = 0; i < n; ++i)
@@ -477,7 +478,7 @@ extern "C" int tdllm_attn_fwd(const void* q, const void* k, const void* v, void*
   p.scale_log2 = scale * 1.4426950408889634f;
   PullPlan pl;
   memset(&pl, 0, sizeof(pl));
-  const int grid = n_qtiles * Hkv * (Hq / Hkv / 2);
+  const int grid = n_qtiles * Hkv * ((Hq / Hkv + 1) / 2);
   attn_fwd_kernel<false><<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(tq, tk, tv, to, tk, tv, p, pl);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -572,7 +573,7 @@ extern "C" int tdllm_attn_fwd_csbp(const void* q, const void* k_loc, const void*
   p.lse = lse;
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
-  const int grid = n_qtiles * Hkv * (Hq / Hkv / 2);
+  const int grid = n_qtiles * Hkv * ((Hq / Hkv + 1) / 2);
   attn_fwd_kernel<true><<<grid, THREADS_CSBP, SMEM_BYTES, st>>>(tq, tk, tv, to, tkr, tvr, p, pl);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

@@ -303,7 +303,7 @@ class BlockDiffusionTransformer(nn.Module):
         if torch.is_grad_enabled() and not h.requires_grad:
             h = h.detach().requires_grad_(True)   # frozen embedding (adapters): keep the checkpoint chain alive
         for i, layer in enumerate(self.layers):
-            if self.sharded is not None:
+            if getattr(self, "sharded", None) is not None:
                 self.sharded.pre_layer(i)
             if self.activation_checkpointing and torch.is_grad_enabled():
                 h = checkpointed_layer(layer, h, self.store, i, positions, self.inv_freq, attend)

@@ -17,6 +17,51 @@ FAMILY_OBJECTIVES: dict[str, tuple[str, ...]] = {
 }
 
 
+_DESCRIPTIONS = {
+    "causal_lm": "dense causal LMs (Qwen3 and alike) converted to block diffusion",
+    "dflash": "DFlash / DFlash2 speculative drafters distilled from a frozen verifier",
+    "diffusion_gemma": "DiffusionGemma-style decoders, dense or with routed experts",
+    "nemotron_labs_diffusion": "Nemotron-Labs-Diffusion block-diffusion decoders",
+    "qwen3_8": "hybrid Gated DeltaNet + gated softmax attention decoders",
+}
+_EXECUTORS: dict[str, object] = {}
+
+
+def register_executor(family: str, executor) -> None:
+    """Adds (or replaces) the executor of a family: the extension point for new model families."""
+    _EXECUTORS[family] = executor
+    if family not in FAMILY_OBJECTIVES:
+        FAMILY_OBJECTIVES[family] = tuple(executor.family.objectives)
+
+
+def executor_for_family(family: str):
+    """The `BackboneExecutor` that builds, validates and describes models of `family`."""
+    if family not in _EXECUTORS:
+        from . import contracts as c
+
+        if family not in FAMILY_OBJECTIVES:
+            raise ValueError(f"unknown model family {family!r}; known: {', '.join(FAMILY_OBJECTIVES)}")
+        spec = c.ModelFamilySpec(family, FAMILY_OBJECTIVES[family], _DESCRIPTIONS.get(family, ""))
+        cls = {"causal_lm": c.DenseExecutor, "nemotron_labs_diffusion": c.DenseExecutor,
+               "diffusion_gemma": c.MoEExecutor, "qwen3_8": c.HybridExecutor, "dflash": c.DFlashExecutor}[family]
+        _EXECUTORS[family] = cls(spec)
+    return _EXECUTORS[family]
+
+
+def family_of_config(cfg, spec) -> str:
+    """Family of a resolved model config: the spec's explicit family, else what the config and objective imply."""
+    fam = spec.model.family
+    if fam not in ("auto", "hf"):
+        return fam
+    if spec.objective.name == "dflash_distillation":
+        return "dflash"
+    if getattr(cfg, "is_hybrid", False):
+        return "qwen3_8"
+    if getattr(cfg, "is_moe", False):
+        return "diffusion_gemma"
+    return getattr(cfg, "family", None) or infer_family(spec.model.id, spec.objective.name)
+
+
 def supported_families() -> tuple[str, ...]:
     return FAMILIES
 

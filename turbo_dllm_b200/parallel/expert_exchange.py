@@ -117,8 +117,9 @@ class _PeerDispatch(torch.autograd.Function):
         ex.barrier.sync()          # every source's rows are in this rank's slab
         state.update(pos=pos, g=g, my_begin=my_begin, my_count=my_count, experts=experts_flat, rows=rows)
         ctx.ex, ctx.state = ex, state
-        # the slab is reused by the next routed batch: what autograd keeps must be a copy
-        return ex.x_slab.clone() if torch.is_grad_enabled() else ex.x_slab
+        # the slab is reused by the next routed batch: what autograd keeps must be a copy (and an autograd
+        # function must hand out a tensor of its own, never the persistent view)
+        return ex.x_slab.clone() if ctx.needs_input_grad[0] else ex.x_slab.detach()
 
     @staticmethod
     def backward(ctx, d_x_pad):
@@ -142,7 +143,7 @@ class _PeerCombine(torch.autograd.Function):
         ex.barrier.sync()          # every owner's expert outputs are in place
         out = torch.empty(rows, ex.H, dtype=torch.bfloat16, device=y_pad.device)
         keep = (torch.empty(rows * ex.k, ex.H, dtype=torch.bfloat16, device=y_pad.device)
-                if torch.is_grad_enabled() or weights.requires_grad else None)
+                if ctx.needs_input_grad[1] else None)
         w = weights.reshape(-1).float().contiguous()
         with communication_scope("expert", "forward", "combine", rows * ex.k * ex.H * 2):
             native.check(lib.tdllm_ep_combine(ptr(out), ptr(w), ptr(state["experts"]), ptr(state["pos"]),
@@ -174,7 +175,7 @@ class _PeerCombine(torch.autograd.Function):
                                                ex.dy_buf.ptr_array, rows, ex.k, ex.H, ex.el, ex.cap, ex.world, stream()),
                          "ep_dispatch")
         ex.barrier.sync()          # every source's output gradients are in this rank's slab
-        return ex.dy_slab, dw, None, None
+        return ex.dy_slab.detach(), dw, None, None
 
 
 def peer_dispatch(x, experts_flat, ex: PeerExpertExchange, state: dict):

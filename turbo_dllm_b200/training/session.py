@@ -69,33 +69,17 @@ class TrainingSession:
             self._init_dflash(seed, runtime, host_staged_data)
             return
         ep = runtime.expert_parallel_size if runtime is not None else 1
-        if self.cfg.is_hybrid:
-            from ..models.hybrid import HybridBlockDiffusionTransformer
+        # the family's executor builds the model: no family names are spelled out here
+        from ..models.contracts import BuildContext
+        from ..models.registry import executor_for_family, family_of_config
 
-            if runtime is not None and runtime.tensor_parallel_size > 1:
-                raise ValueError("the hybrid (qwen3_8) family runs on data-, context- and block-parallel ranks; "
-                                 "tensor parallelism of its linear-attention layers is not built")
-            self.model = HybridBlockDiffusionTransformer(
-                self.cfg, dtype=self.dtype, device=self.device,
-                activation_checkpointing=spec.training.activation_checkpointing,
-                activation_offload=self._want_activation_offload(), seed=seed)
-        elif self.cfg.is_moe:
-            from ..models.moe import MoEBlockDiffusionTransformer
-
-            self.model = MoEBlockDiffusionTransformer(
-                self.cfg, ep_group=runtime.group("expert") if ep > 1 else None, dtype=self.dtype, device=self.device,
-                activation_checkpointing=spec.training.activation_checkpointing,
-                activation_offload=self._want_activation_offload(), seed=seed)
-        else:
-            from ..parallel.tensor_parallel import TPContext
-
-            tp = None
-            if runtime is not None and runtime.tensor_parallel_size > 1:
-                tp = TPContext(runtime.tensor_group, spec.topology.sequence_parallel)
-            self.model = BlockDiffusionTransformer(
-                self.cfg, dtype=self.dtype, device=self.device,
-                activation_checkpointing=spec.training.activation_checkpointing,
-                activation_offload=self._want_activation_offload(), seed=seed, tp=tp)
+        self.executor = executor_for_family(family_of_config(self.cfg, spec))
+        problems = self.executor.validate_run_spec(spec)
+        if problems:
+            raise ValueError("run spec does not fit the model family:\n  - " + "\n  - ".join(problems))
+        self.model = self.executor.build_model(BuildContext(
+            spec=spec, cfg=self.cfg, device=self.device, dtype=self.dtype, runtime=runtime, seed=seed,
+            activation_offload=self._want_activation_offload()))
         self.memory_report("model built")
         self.lora = None
         self.sharded = None      # parameter sharding (optimizer.backend: fsdp)
@@ -124,16 +108,8 @@ class TrainingSession:
         self.encoder_loss_weight = (float(spec.objective.encoder_loss_weight)
                                     if self.objective.name == "diffusiongemma_native_sft" else 0.0)
         self.last_encoder_loss = None
-        data_kw = dict(batch_size=spec.training.batch_size, seq_len=spec.model.seq_len,
-                       vocab_size=self.cfg.vocab_size, mask_token_id=self.cfg.mask_token_id,
-                       seed=seed + 104729 * (dp_rank + 1), vocab_sample_size=spec.data.vocab_sample_size)
-        if spec.data.input_mode == "random":
-            self.data = (HostStagedRandomRuntime(device=self.device, **data_kw) if host_staged_data
-                         else RandomTokenDataRuntime(device=self.device, **data_kw))
-        else:
-            from ..data.artifact_runtimes import build_artifact_runtime
-
-            self.data = build_artifact_runtime(spec, device=self.device, dp_rank=dp_rank, dp_size=self.dp_size)
+        self.data = self.executor.build_data_runtime(spec, self.cfg, self.device, dp_rank, self.dp_size,
+                                                     host_staged=host_staged_data)
         self.layout = self._build_layout()
         self.attend = self._build_attention()
         if self.cfg.is_hybrid:
