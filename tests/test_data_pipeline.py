@@ -132,3 +132,72 @@ def test_cli_data_and_init(tmp_path, capsys):
     assert run(["data", "validate", str(root)]) == 0
     assert run(["data", "stats", str(root)]) == 0
     assert run(["data", "validate", str(tmp_path / "missing")]) == 2
+
+
+def _trajectory_artifact(root, lengths_by_group, vocab=900, seed=0):
+    from turbo_dllm_b200.data.artifacts import write_indexed_artifact
+
+    rng = np.random.default_rng(seed)
+    samples, sid = [], 0
+    for gid, lens in lengths_by_group.items():
+        for L in lens:
+            mask = np.zeros(L, dtype=np.uint8)
+            mask[L // 2:] = 1
+            samples.append({"tokens": rng.integers(0, vocab, L), "loss_mask": mask, "sample_id": sid, "group": gid})
+            sid += 1
+    write_indexed_artifact(root, samples, metadata={"block_size": 32, "tokenizer": {"vocab_size": vocab}},
+                           with_groups=True)
+
+
+def test_trajectory_step_units_and_turn_mean_reduction(tmp_path):
+    """One optimizer step = one trajectory (its turns as micro-batches, last turn weighted); `turn_mean` averages
+    the turns' token-mean losses instead of pooling tokens (dllm_parallel/core/data.py:966-1010, :739)."""
+    from turbo_dllm_b200.config.run_spec import RunSpec, RunSpecError
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    root = tmp_path / "traj"
+    _trajectory_artifact(root, {7: [64, 128, 64], 3: [128], 9: [64, 64]})
+    rt = IndexedSupervisedTokenDataRuntime(root, batch_size=1, block_size=32, max_seq_len=128, shuffle=False,
+                                           optimizer_step_unit="trajectory", terminal_turn_weight=3.0)
+    steps = [rt.next_optimizer_step_batches(1) for _ in range(3)]
+    assert [len(s) for s in steps] == [1, 3, 2]                       # groups 3, 7, 9 in id order
+    assert [b.turn_weight for b in steps[1]] == [1.0, 1.0, 3.0]
+    assert [b.input_ids.shape[1] for b in steps[1]] == [64, 128, 64]
+    state = rt.state_dict()
+    first_again = rt.next_optimizer_step_batches(1)                   # wraps into the next epoch
+    rt2 = IndexedSupervisedTokenDataRuntime(root, batch_size=1, block_size=32, max_seq_len=128, shuffle=False,
+                                            optimizer_step_unit="trajectory", terminal_turn_weight=3.0)
+    rt2.load_state_dict(state)
+    assert torch.equal(rt2.next_optimizer_step_batches(1)[0].input_ids, first_again[0].input_ids)
+    with pytest.raises(ArtifactError, match="hand out whole optimizer steps"):
+        rt.next_batch()
+    # a trajectory with a turn that does not fit is refused, never shortened
+    bad = tmp_path / "bad"
+    _trajectory_artifact(bad, {1: [64, 96 + 1]})
+    with pytest.raises(ArtifactError, match="ineligible"):
+        IndexedSupervisedTokenDataRuntime(bad, batch_size=1, block_size=32, max_seq_len=128,
+                                          optimizer_step_unit="trajectory")
+
+    def spec(reduction):
+        return RunSpec.from_mapping({
+            "model": {"id": "synthetic:tiny-qwen3", "seq_len": 128, "dtype": "fp32", "num_layers": 1},
+            "objective": {"name": "standard_block_diffusion", "block_size": 32, "sampling_epsilon_min": 0.1},
+            "data": {"input_mode": "dataset", "dataset_path": str(root), "shuffle": False,
+                     "optimizer_step_unit": "trajectory", "trajectory_loss_reduction": reduction,
+                     "trajectory_terminal_turn_weight": 3.0},
+            "training": {"batch_size": 1, "steps": 3},
+            "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
+            "optimizer": {"lr": 1e-3}}).validate()
+
+    a, b = TrainingSession(spec("token_mean"), device="cpu"), TrainingSession(spec("turn_mean"), device="cpu")
+    ra = [a.step() for _ in range(3)]
+    rb = [b.step() for _ in range(3)]
+    la = [float(r.loss_sum) / r.denominator for r in ra]
+    lb = [float(r.loss_sum) / r.denominator for r in rb]
+    assert all(x == x and x > 0 for x in la + lb)
+    assert la[0] == pytest.approx(lb[0], rel=1e-5)        # a single-turn trajectory: both reductions agree
+    assert abs(la[1] - lb[1]) > 1e-6                      # three turns of different lengths and weights: they differ
+    assert not torch.equal(a.model.flat.data, b.model.flat.data)
+    with pytest.raises(RunSpecError, match="turn_mean"):
+        RunSpec.from_mapping({"data": {"trajectory_loss_reduction": "turn_mean"},
+                              "model": {"id": "synthetic:tiny-qwen3", "dtype": "fp32"}}).validate()

@@ -222,3 +222,47 @@ def test_family_executors_and_registration():
         assert s.executor.parameter_shard_units(s.model)[-1] == "norm_weights"
     finally:
         register_executor("causal_lm", old)
+
+
+def test_portable_artifact_check_and_release_manifest(tmp_path):
+    import importlib.util
+    import json
+    import zipfile
+    from pathlib import Path
+
+    from turbo_dllm_b200.profiling.portable_artifacts import REQUIRED_SUFFIXES, check_artifact
+
+    def wheel(path, extra=()):
+        with zipfile.ZipFile(path, "w") as z:
+            for s in REQUIRED_SUFFIXES:
+                z.writestr(s, "# ok\n")
+            for name, data in extra:
+                z.writestr(name, data)
+
+    good = tmp_path / "turbo_dllm_b200-0.1-py3-none-any.whl"
+    wheel(good)
+    assert check_artifact(str(good), "portable").ok
+    bad = tmp_path / "bad.whl"
+    wheel(bad, [("turbo_dllm_b200/_C/libtdllm_kernels.so", b"\x7fELF"), ("turbo_dllm_b200/x.py", "p = '/root/secret'\n")])
+    rep = check_artifact(str(bad), "portable")
+    assert not rep.ok and any("native binary" in p for p in rep.problems) and any("forbidden" in p for p in rep.problems)
+    gpu = tmp_path / "gpu.whl"
+    wheel(gpu, [("turbo_dllm_b200/_C/libtdllm_kernels.so", b"\x7fELF"), ("turbo_dllm_b200/_C/native_kernels.json", "{}")])
+    assert check_artifact(str(gpu), "gpu").ok
+    assert not check_artifact(str(good), "gpu").ok              # the GPU wheel must carry the kernel library
+
+    spec = importlib.util.spec_from_file_location("release", Path(__file__).resolve().parent.parent / "packaging" / "release.py")
+    rel = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rel)
+    dist = tmp_path / "dist"
+    dist.mkdir()
+    wheel(dist / "turbo_dllm_b200-0.1-cp312-linux_x86_64.whl",
+          [("turbo_dllm_b200/_C/libtdllm_kernels.so", b"\x7fELF"), ("turbo_dllm_b200/_C/native_kernels.json", "{}")])
+    man = rel.build_manifest(str(dist))
+    assert man["bundle"] == "gpu-sm100a-cu129-cp312" and len(man["files"]) == 1
+    (dist / "release_manifest.json").write_text(json.dumps(man))
+    assert rel.verify(str(dist / "release_manifest.json")) == []
+    with open(dist / man["files"][0]["name"], "ab") as f:
+        f.write(b"tampered")
+    assert any("SHA-256" in p for p in rel.verify(str(dist / "release_manifest.json")))
+    assert {c["name"] for c in rel.sbom()["components"]} >= {"torch", "numpy"}

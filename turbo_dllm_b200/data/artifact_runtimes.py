@@ -9,6 +9,9 @@ pinned memory and copied on a transfer stream one batch ahead, shard by data-par
 * IndexedSupervisedTokenDataRuntime – samples of index.i64 with their loss masks; a batch holds
   samples of one length (length buckets), padded up to the block size by the preparation step;
   samples shorter than `minimum_sequence_length` or not aligned to the block size are skipped.
+  With `optimizer_step_unit="trajectory"` (artifacts with `groups.i64`) one optimizer step is one trajectory:
+  its turns, in order, one sample per micro-batch, every data-parallel rank taking its own trajectory; the
+  last turn carries `trajectory_terminal_turn_weight` for the `turn_mean` loss reduction.
 * BlendedPackedTokenDataRuntime – several packed artifacts mixed by weight with a seeded
   multinomial choice per batch.
 
@@ -106,7 +109,8 @@ class PackedTokenDataRuntime(DataRuntime):
 class IndexedSupervisedTokenDataRuntime(DataRuntime):
     def __init__(self, root: str | Path, *, batch_size: int, block_size: int, max_seq_len: int,
                  minimum_sequence_length: int | None = None, dp_rank: int = 0, dp_size: int = 1,
-                 shuffle: bool = True, seed: int = 0, device="cpu"):
+                 shuffle: bool = True, seed: int = 0, device="cpu", optimizer_step_unit: str = "microbatch",
+                 terminal_turn_weight: float = 1.0):
         self.root = Path(root)
         m = load_manifest(self.root)
         if m["format"] != INDEXED_FORMAT:
@@ -125,7 +129,64 @@ class IndexedSupervisedTokenDataRuntime(DataRuntime):
         self.shuffle, self.seed = shuffle, seed
         self.epoch, self.cursor = 0, 0
         self.stager = _Stager(device)
-        self._batches = self._epoch_batches(0)
+        self.step_unit, self.terminal_turn_weight = optimizer_step_unit, float(terminal_turn_weight)
+        self.groups = None
+        if optimizer_step_unit == "trajectory":
+            gpath = self.root / "groups.i64"
+            if not gpath.exists():
+                raise ArtifactError("data.optimizer_step_unit=trajectory needs an artifact with groups.i64 "
+                                    "(prepare it with records.group_column)")
+            self.groups = np.fromfile(gpath, dtype="<i8")
+            self._trajectories = self._epoch_trajectories(0)
+            self._batches = []
+        else:
+            self._batches = self._epoch_batches(0)
+
+    def _epoch_trajectories(self, epoch: int) -> list[np.ndarray]:
+        """Trajectories (samples of one group id, in file order), shuffled per epoch. A trajectory with a turn
+        that is not eligible (length off the block grid, too long) is an error: turns are never dropped silently
+        (dllm_parallel/core/data.py:966-1010)."""
+        eligible = np.zeros(len(self.index), dtype=bool)
+        eligible[self.eligible] = True
+        order = np.argsort(self.groups, kind="stable")
+        gids, starts = np.unique(self.groups[order], return_index=True)
+        trajs = np.split(order, starts[1:])
+        partial = [int(g) for g, t in zip(gids, trajs) if not eligible[t].all()]
+        if partial:
+            raise ArtifactError(f"trajectory steps cannot omit ineligible turns; {len(partial)} trajectories have "
+                                f"one (first group id {partial[0]})")
+        trajs = [np.sort(t) for t in trajs]
+        if self.shuffle and len(trajs) > 1:
+            perm = np.random.default_rng(self.seed + epoch).permutation(len(trajs))
+            trajs = [trajs[i] for i in perm]
+        if len(trajs) < self.dp_size:
+            raise ArtifactError(f"{len(trajs)} trajectories cannot feed {self.dp_size} data-parallel ranks")
+        return trajs
+
+    def _sample_batch(self, ids: np.ndarray, turn_weight: float | None = None) -> DataBatch:
+        toks = np.stack([self.tokens[o:o + n] for o, n in self.index[ids, :2]])
+        msk = np.stack([self.mask[o:o + n] for o, n in self.index[ids, :2]])
+        dev, nb = self.stager.to_device(toks)
+        dmask, nb2 = self.stager.to_device(msk, torch.bool)
+        return DataBatch(dev, supervision_mask=dmask, supervision_count=int(msk.sum()),
+                         sample_ids=torch.from_numpy(self.index[ids, 3].copy()), h2d_bytes=nb + nb2,
+                         turn_weight=turn_weight, supervision_count_shifted=int(msk[:, 1:].sum()))
+
+    def next_optimizer_step_batches(self, micro_batches: int) -> list[DataBatch]:
+        if self.step_unit != "trajectory":
+            return super().next_optimizer_step_batches(micro_batches)
+        per_global = self.dp_size
+        if (self.cursor + 1) * per_global > len(self._trajectories):
+            self.epoch += 1
+            self.cursor = 0
+            self._trajectories = self._epoch_trajectories(self.epoch)
+        traj = self._trajectories[self.cursor * per_global + self.dp_rank]
+        self.cursor += 1
+        out = []
+        for j, i in enumerate(traj):
+            w = self.terminal_turn_weight if j == len(traj) - 1 else 1.0
+            out.append(self._sample_batch(np.array([i]), turn_weight=w))
+        return out
 
     def _epoch_batches(self, epoch: int) -> list[np.ndarray]:
         """Global batches of same-length samples; every DP rank takes a `batch_size` slice."""
@@ -146,28 +207,30 @@ class IndexedSupervisedTokenDataRuntime(DataRuntime):
         return out
 
     def next_batch(self) -> DataBatch:
+        if self.step_unit == "trajectory":
+            raise ArtifactError("trajectory step units hand out whole optimizer steps (next_optimizer_step_batches)")
         if self.cursor >= len(self._batches):
             self.epoch += 1
             self.cursor = 0
             self._batches = self._epoch_batches(self.epoch)
         ids = self._batches[self.cursor][self.dp_rank * self.batch_size:(self.dp_rank + 1) * self.batch_size]
         self.cursor += 1
-        toks = np.stack([self.tokens[o:o + n] for o, n in self.index[ids, :2]])
-        msk = np.stack([self.mask[o:o + n] for o, n in self.index[ids, :2]])
-        dev, nb = self.stager.to_device(toks)
-        dmask, nb2 = self.stager.to_device(msk, torch.bool)
-        return DataBatch(dev, supervision_mask=dmask, supervision_count=int(msk.sum()),
-                         sample_ids=torch.from_numpy(self.index[ids, 3].copy()), h2d_bytes=nb + nb2)
+        return self._sample_batch(ids)
 
     def state_dict(self):
         return {"kind": "indexed", "epoch": self.epoch, "cursor": self.cursor, "fingerprint": self.fingerprint,
-                "seed": self.seed, "dp_size": self.dp_size}
+                "seed": self.seed, "dp_size": self.dp_size, "step_unit": self.step_unit}
 
     def load_state_dict(self, state):
         if state.get("fingerprint") != self.fingerprint:
             raise ArtifactError("checkpoint was written for a different dataset (fingerprint mismatch)")
+        if state.get("step_unit", "microbatch") != self.step_unit:
+            raise ArtifactError("data.optimizer_step_unit changed since the checkpoint")
         self.epoch, self.cursor = int(state["epoch"]), int(state["cursor"])
-        self._batches = self._epoch_batches(self.epoch)
+        if self.step_unit == "trajectory":
+            self._trajectories = self._epoch_trajectories(self.epoch)
+        else:
+            self._batches = self._epoch_batches(self.epoch)
 
 
 class BlendedPackedTokenDataRuntime(DataRuntime):
@@ -213,4 +276,6 @@ def build_artifact_runtime(spec, *, device, dp_rank: int, dp_size: int) -> DataR
         return PackedTokenDataRuntime(path, seq_len=spec.model.seq_len, seed=spec.launch.seed, **common)
     return IndexedSupervisedTokenDataRuntime(
         path, block_size=spec.objective.block_size or 1, max_seq_len=spec.model.seq_len,
-        minimum_sequence_length=spec.data.minimum_sequence_length, seed=spec.launch.seed, **common)
+        minimum_sequence_length=spec.data.minimum_sequence_length, seed=spec.launch.seed,
+        optimizer_step_unit=spec.data.optimizer_step_unit,
+        terminal_turn_weight=spec.data.trajectory_terminal_turn_weight, **common)

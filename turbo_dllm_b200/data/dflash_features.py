@@ -49,6 +49,60 @@ def capture_features(spec, output: str, batches: int) -> dict:
     return man
 
 
+class FeatureStoreDataRuntime:
+    """Data runtime over a feature store: a batch is one stored record (token ids plus the target's hidden
+    states), shards dealt out round-robin over the data-parallel ranks, the next record read ahead into pinned
+    memory while the current step runs. Counterpart of DFlashFeatureDataRuntime
+    (dllm_parallel/core/models/backbones/dflash/data.py:248-630)."""
+
+    def __init__(self, store: "FeatureStore", *, batch_size: int, device, dp_rank: int = 0, dp_size: int = 1):
+        from .runtimes import DataBatch  # noqa: F401
+
+        self.store, self.device = store, torch.device(device)
+        self.batch_size, self.dp_rank, self.dp_size = batch_size, dp_rank, dp_size
+        if len(store.manifest["shards"]) < dp_size:
+            raise ValueError(f"feature store has {len(store.manifest['shards'])} records, fewer than the {dp_size} "
+                             "data-parallel ranks")
+        self.step = 0
+        self._ahead = None
+
+    def _load(self, step: int) -> dict:
+        shards = self.store.manifest["shards"]
+        sh = shards[(step * self.dp_size + self.dp_rank) % len(shards)]
+        rec = torch.load(os.path.join(self.store.root, sh["name"]), map_location="cpu")
+        if rec["input_ids"].shape[0] != self.batch_size:
+            raise ValueError(f"feature records hold {rec['input_ids'].shape[0]} sequences, the run's batch size is "
+                             f"{self.batch_size}")
+        if self.device.type == "cuda":
+            rec = {k: v.pin_memory() for k, v in rec.items()}
+        return rec
+
+    def next_batch(self):
+        from .runtimes import DataBatch
+
+        rec = self._ahead if self._ahead is not None else self._load(self.step)
+        self.step += 1
+        nbytes = sum(v.numel() * v.element_size() for v in rec.values()) if self.device.type == "cuda" else 0
+        dev = {k: v.to(self.device, non_blocking=True) for k, v in rec.items()}
+        self._ahead = self._load(self.step)
+        b = DataBatch(dev["input_ids"], h2d_bytes=nbytes)
+        b.features = {"hidden": dev["hidden"], "final_hidden": dev["final_hidden"]}
+        return b
+
+    def next_optimizer_step_batches(self, micro_batches: int):
+        return [self.next_batch() for _ in range(micro_batches)]
+
+    def state_dict(self):
+        return {"kind": "dflash_features", "step": self.step, "dp_size": self.dp_size}
+
+    def load_state_dict(self, st):
+        self.step = int(st["step"])
+        self._ahead = None
+
+    def close(self):
+        self._ahead = None
+
+
 class FeatureStore:
     def __init__(self, root: str, verify: bool = False):
         self.root = root

@@ -26,6 +26,10 @@ class DataBatch:
     supervision_count: int | None = None
     sample_ids: torch.Tensor | None = None
     h2d_bytes: int = 0
+    # trajectory step units: weight of this turn inside its trajectory and its supervised-token counts
+    # (plain, and without position 0 for objectives with shifted labels)
+    turn_weight: float | None = None
+    supervision_count_shifted: int | None = None
 
 
 class DataRuntime(ABC):

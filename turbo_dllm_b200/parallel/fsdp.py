@@ -272,8 +272,10 @@ class ShardedParameters:
         self._reduce(u, self.grad_bufs[i % 2], self.grad_full[i % 2])
         self._reduced.add(u.name)
 
-    def end_micro_batch(self) -> None:
-        """After the backward pass of one micro-batch: resident units' gradients, layers without a backward."""
+    def end_micro_batch(self, before_reduce=None) -> None:
+        """After the backward pass of one micro-batch: resident units' gradients, layers without a backward.
+        `before_reduce()` runs once every resident gradient is complete in its buffer and before the buffers
+        are reduced (the tensor-parallel sum of partially computed norm-weight gradients goes there)."""
         for u in self.resident:
             for p in self.params_of[u.name]:
                 if p.grad is not None:
@@ -282,6 +284,9 @@ class ShardedParameters:
                     p.grad_acc = True
                 elif not p.grad_acc:
                     p.main_grad.zero_()
+        if before_reduce is not None:
+            before_reduce()
+        for u in self.resident:
             self._reduce(u, self.res_grad_buf[u.name], self.res_grad[u.name])
             for p in self.params_of[u.name]:
                 p.grad_acc = False

@@ -27,15 +27,44 @@ class DFlashTask:
     def __init__(self, spec, cfg: ModelConfig, *, dtype, device, seed: int, dp_rank: int):
         m, o = spec.model, spec.objective
         self.spec, self.cfg, self.device = spec, cfg, device
+        import os
+        from dataclasses import replace
+
+        self.offline = spec.data.target_features == "offline"
+        hf_dir = m.verifier_id if (m.verifier_id and os.path.isdir(m.verifier_id)) else None
         target_cfg = PRESETS.get(m.verifier_id or "")
+        if hf_dir is not None:
+            # a Hugging Face checkpoint directory on disk: its config gives the shapes, its tensors the weights
+            from ..models.hf_loader import load_hf_config
+
+            target_cfg = load_hf_config(hf_dir)
         if target_cfg is None:
-            raise ValueError(f"model.verifier_id {m.verifier_id!r} is not a built-in target preset "
-                             f"({', '.join(k for k in PRESETS)}); offline features need data.target_features=offline")
-        if spec.data.target_features == "offline":
-            raise NotImplementedError("offline target-feature stores are read by data.dflash_features")
-        if m.max_layers is not None and spec.data.target_features == "synthetic":
-            pass
-        self.target = FrozenTarget(target_cfg, tuple(m.target_layer_ids), dtype=dtype, device=device, seed=seed + 1)
+            raise ValueError(f"model.verifier_id {m.verifier_id!r} is neither a built-in target preset "
+                             f"({', '.join(k for k in PRESETS)}) nor a Hugging Face checkpoint directory")
+        layer_ids = tuple(m.target_layer_ids)
+        full_layers = target_cfg.num_layers
+        if self.offline:
+            # hidden states come from the feature store: only the verifier's embedding and head are needed
+            target_cfg = replace(target_cfg, num_layers=0)
+        self.target = FrozenTarget(target_cfg, () if self.offline else layer_ids, dtype=dtype, device=device,
+                                   seed=seed + 1)
+        self.target.layer_ids = layer_ids
+        if hf_dir is not None:
+            from ..models.hf_loader import load_hf_weights
+
+            load_hf_weights(self.target.model, hf_dir)
+        self.feature_store = None
+        if self.offline:
+            from ..data.dflash_features import FeatureStore
+
+            self.feature_store = FeatureStore(spec.data.target_feature_path, verify=True)
+            man = self.feature_store.manifest
+            if list(man.get("target_layer_ids", [])) != list(layer_ids) or int(man.get("seq_len", 0)) != m.seq_len:
+                raise ValueError(f"feature store {spec.data.target_feature_path} was captured for target layers "
+                                 f"{man.get('target_layer_ids')} at seq_len {man.get('seq_len')}; the run asks for "
+                                 f"{list(layer_ids)} at {m.seq_len}")
+            if any(i >= full_layers for i in layer_ids):
+                raise ValueError(f"target_layer_ids {layer_ids} outside the verifier's {full_layers} layers")
         self.is_dflash2 = bool(m.dflash2_conv_kernel_size or m.dflash2_selector_rank)
         if self.is_dflash2:
             from ..models.dflash2 import DFlash2DraftModel
@@ -75,7 +104,14 @@ class DFlashTask:
         self.effective_selector_loss_alpha = float(o.selector_loss_alpha) * selector_schedule_factor(
             int(step), int(total_steps), float(o.selector_warmup_ratio), float(o.selector_ramp_ratio))
 
-    def target_features(self, input_ids: torch.Tensor) -> TargetFeatures:
+    def target_features(self, input_ids: torch.Tensor, batch=None) -> TargetFeatures:
+        if self.offline:
+            feats = getattr(batch, "features", None)
+            if feats is None:
+                raise ValueError("data.target_features=offline needs batches of the feature-store data runtime")
+            dt = self.model.flat.data.dtype
+            return TargetFeatures(feats["hidden"].reshape(-1, feats["hidden"].shape[-1]).to(dt),
+                                  feats["final_hidden"].reshape(-1, feats["final_hidden"].shape[-1]).to(dt))
         if self.synthetic:  # random features of the right shape: exercises the drafter without a target pass
             b, l = input_ids.shape
             g = torch.Generator(device=self.device)
@@ -90,7 +126,7 @@ class DFlashTask:
         ids = batch.input_ids
         b, l = ids.shape
         ob = self.objective.prepare(ids, batch.supervision_mask)
-        feats = self.target_features(ids)
+        feats = self.target_features(ids, batch)
         bs = self.objective.block_size
         mask = dflash_mask_layout(ob, l, bs)
         draft_tok = ob.draft_input_ids.reshape(-1)

@@ -112,6 +112,7 @@ class TrainingSession:
                                                      host_staged=host_staged_data)
         self.layout = self._build_layout()
         self.attend = self._build_attention()
+        self._first_layout, self._first_attend = self.layout, self.attend
         if self.cfg.is_hybrid:
             from ..models.hybrid import BlockRows
 
@@ -203,11 +204,17 @@ class TrainingSession:
         self.task = DFlashTask(spec, self.cfg, dtype=self.dtype, device=self.device, seed=seed, dp_rank=dp_rank)
         self.model, self.objective = self.task.model, self.task.objective
         tcfg = self.task.target.cfg
-        data_kw = dict(batch_size=spec.training.batch_size, seq_len=spec.model.seq_len, vocab_size=tcfg.vocab_size,
-                       mask_token_id=tcfg.mask_token_id, seed=seed + 104729 * (dp_rank + 1),
-                       vocab_sample_size=spec.data.vocab_sample_size)
-        self.data = (HostStagedRandomRuntime(device=self.device, **data_kw) if host_staged_data
-                     else RandomTokenDataRuntime(device=self.device, **data_kw))
+        if self.task.feature_store is not None:
+            from ..data.dflash_features import FeatureStoreDataRuntime
+
+            self.data = FeatureStoreDataRuntime(self.task.feature_store, batch_size=spec.training.batch_size,
+                                                device=self.device, dp_rank=dp_rank, dp_size=self.dp_size)
+        else:
+            data_kw = dict(batch_size=spec.training.batch_size, seq_len=spec.model.seq_len,
+                           vocab_size=tcfg.vocab_size, mask_token_id=tcfg.mask_token_id,
+                           seed=seed + 104729 * (dp_rank + 1), vocab_sample_size=spec.data.vocab_sample_size)
+            self.data = (HostStagedRandomRuntime(device=self.device, **data_kw) if host_staged_data
+                         else RandomTokenDataRuntime(device=self.device, **data_kw))
         self.layout, self.attend = None, None
         self.expert_optimizer = None
         group = runtime.optimizer_group if runtime is not None else (dist.group.WORLD if self.world > 1 else None)
@@ -255,7 +262,27 @@ class TrainingSession:
     def _want_activation_offload(self) -> bool:
         return self._memory_plan()[0]
 
-    def _build_layout(self) -> PackedLayout:
+    def _select_layout(self, seq_len: int) -> None:
+        """Row layout and attention for micro-batches whose sequences are shorter than `model.seq_len` (indexed
+        datasets hand out same-length batches of any block-aligned length). Layouts are built once per length."""
+        if seq_len == getattr(self, "_layout_len", self.spec.model.seq_len):
+            return
+        cache = self.__dict__.setdefault("_layouts", {self.spec.model.seq_len: (self._first_layout, self._first_attend)})
+        if seq_len not in cache:
+            rt = self.runtime
+            if rt is not None and (rt.context_parallel_size > 1 or rt.block_parallel_size > 1):
+                raise ValueError("variable sequence lengths are built for data-parallel runs; context / block "
+                                 "parallelism plans its row layout for model.seq_len")
+            if seq_len % self.spec.objective.block_size or seq_len > self.spec.model.seq_len:
+                raise ValueError(f"a batch of length {seq_len} does not fit block size "
+                                 f"{self.spec.objective.block_size} / model.seq_len {self.spec.model.seq_len}")
+            lay = self._build_layout(seq_len)
+            cache[seq_len] = (lay, LocalAttention(getattr(self.model, "lcfg", self.cfg), lay.mask,
+                                                  store=self.model.store))
+        self.layout, self.attend = cache[seq_len]
+        self._layout_len = seq_len
+
+    def _build_layout(self, seq_len: int | None = None) -> PackedLayout:
         s, rt = self.spec, self.runtime
         owned, clean = None, None
         if rt is not None and rt.block_parallel_size > 1:
@@ -267,7 +294,7 @@ class TrainingSession:
         elif rt is not None and rt.block_parallel_size > 1 and s.topology.replicate_clean_prefix:
             last = max(owned)
             clean = torch.arange(0, last * s.objective.block_size, device=self.device)
-        return build_packed_layout(seq_len=s.model.seq_len, block_size=s.objective.block_size,
+        return build_packed_layout(seq_len=seq_len or s.model.seq_len, block_size=s.objective.block_size,
                                    batch=s.training.batch_size, views=self.objective.views,
                                    owned_blocks=owned, clean_pos=clean, device=self.device,
                                    clean_causal=getattr(self, "encoder_loss_weight", 0.0) > 0.0)
@@ -353,6 +380,8 @@ class TrainingSession:
 
     # ------------------------------------------------------------------ step
     def forward_backward(self, batch: DataBatch, denominator: float):
+        if not self.cfg.is_hybrid:
+            self._select_layout(int(batch.input_ids.shape[1]))
         cb = self.objective.corrupt(batch.input_ids, supervision_mask=batch.supervision_mask,
                                     supervision_count=batch.supervision_count)
         tokens, labels, weights = self.assemble_rows(cb)
@@ -382,8 +411,8 @@ class TrainingSession:
         with self._phase("backward"):
             (loss_sum / denominator).backward()
             if self.sharded is not None:
-                self._sync_tensor_parallel_partial_gradients()     # per micro-batch: the buffers restart each time
-                self.sharded.end_micro_batch()
+                # per micro-batch (the gradient buffers restart each time), once the gradients are in their buffers
+                self.sharded.end_micro_batch(before_reduce=self._sync_tensor_parallel_partial_gradients)
         self.memory_report("after backward")
         return loss_sum.detach(), l.shape[0], cb
 
@@ -466,13 +495,26 @@ class TrainingSession:
             denom = 1.0
             self._grad_div = scale
         else:
-            denom = self.global_denominator(batches)
+            turn_mean = (spec.data.trajectory_loss_reduction == "turn_mean"
+                         and all(b.turn_weight is not None for b in batches))
+            denom = 1.0 if turn_mean else self.global_denominator(batches)
             if self.encoder_loss_weight > 0.0:
                 b0, l0 = batches[0].input_ids.shape
                 self._encoder_denominator = float(max(b0 * (l0 - 1) * len(batches) * self.dp_size, 1))
+            wsum = sum(b.turn_weight for b in batches) if turn_mean else 0.0
+            shifted = self.objective.name == "fast_dllm_v2"
             for b in batches:
-                ls, n, _ = self.forward_backward(b, denom)
-                total += ls.float()
+                if turn_mean:
+                    # mean over the trajectory's turns (terminal turn weighted) of each turn's token-mean loss,
+                    # averaged over the data-parallel ranks' trajectories
+                    # (dllm_parallel/core/data.py:739, block_diffusion_trainer.py:385-415)
+                    cnt = b.supervision_count_shifted if shifted else b.supervision_count
+                    d = float(max(cnt, 1)) * wsum / b.turn_weight * self.dp_size
+                    ls, n, _ = self.forward_backward(b, d)
+                    total += ls.float() / d
+                else:
+                    ls, n, _ = self.forward_backward(b, denom)
+                    total += ls.float()
                 rows += n
         with self._phase("gradient_sync"):
             if self.sharded is None:       # sharded parameters reduce their gradients layer by layer in the backward
