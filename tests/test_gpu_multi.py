@@ -123,7 +123,8 @@ def test_barrier_wait_runs_out_and_reports():
     assert float(torch.ones(4, device="cuda").sum()) == 4.0
 
 
-def _csbp(rank, world, transport, steps, model="synthetic:tiny-hd128", objective="standard_block_diffusion"):
+def _csbp(rank, world, transport, steps, model="synthetic:tiny-hd128", objective="standard_block_diffusion",
+          block_axis=True):
     import os
 
     import torch.distributed as dist
@@ -140,7 +141,7 @@ def _csbp(rank, world, transport, steps, model="synthetic:tiny-hd128", objective
         "model": {"id": model, "seq_len": 1024, "dtype": "bf16"},
         "objective": {"name": objective, "block_size": 32, "sampling_epsilon_min": 0.1},
         "training": {"batch_size": 2, "steps": steps},
-        "topology": {"context_parallel_size": cp, "block_parallel_size": cp},
+        "topology": {"context_parallel_size": cp, "block_parallel_size": cp if block_axis else 1},
         "kernel": {"cp_bp_clean_kv_transport": transport, "impl": "nccl_baseline"},
         "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
     rt = build_parallel_runtime(spec, device=f"cuda:{rank}", rank=rank, world_size=world) if world > 1 else None
@@ -163,6 +164,20 @@ def test_csbp2_on_gpus_matches_single_gpu(transport):
     _need(2)
     ref = run_ranks(_csbp, 1, args=("collective", 3), backend=None, deadline_s=300)[0]
     outs = run_ranks(_csbp, 2, args=(transport, 3), backend="nccl", deadline_s=300)
+    for losses, params in outs:
+        assert losses == pytest.approx(ref[0], rel=3e-2)
+        assert (torch.from_numpy(params) - torch.from_numpy(ref[1])).abs().max().item() < 3e-2
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("transport,world", [("collective", 2), ("fused", 2), ("fused", 4), ("fused", 8)])
+def test_pure_context_parallel_token_split_on_gpus_matches_single_gpu(transport, world):
+    """Context parallelism without a block axis: every rank computes 32 / world offsets of every noisy block and
+    ALL K|V rows travel (gathered, or pulled by the attention kernel with dK/dV added into the owners' rows)."""
+    _need(world)
+    ref = run_ranks(_csbp, 1, args=("collective", 3), backend=None, deadline_s=300)[0]
+    outs = run_ranks(_csbp, world, args=(transport, 3, "synthetic:tiny-hd128", "standard_block_diffusion", False),
+                     backend="nccl", deadline_s=300)
     for losses, params in outs:
         assert losses == pytest.approx(ref[0], rel=3e-2)
         assert (torch.from_numpy(params) - torch.from_numpy(ref[1])).abs().max().item() < 3e-2

@@ -76,3 +76,30 @@ def test_clean_ownership_covers_each_token_once():
     assert balanced_bounds(10, 3, 0) == (0, 4) and balanced_bounds(10, 3, 2) == (7, 10)
     sh = clean_shards_for_rank(512, 2, 0, "dual_chunk", 32)
     assert [(s.start, s.stop) for s in sh] == [(0, 128), (384, 512)]
+
+
+def test_parallel_preflight_environment_policy():
+    import pytest
+
+    from turbo_dllm_b200.config.run_spec import RunSpec, RunSpecError
+    from turbo_dllm_b200.parallel.preflight import (infer_parallel_mesh_sizes, prepare_parallel_environment,
+                                                    uses_peer_memory_kernels, validate_supported_training_axes)
+
+    def spec(**topology):
+        return RunSpec.from_mapping({"model": {"id": "synthetic:tiny-hd128", "seq_len": 512, "dtype": "bf16"},
+                                     "objective": {"name": "fast_dllm_v2", "block_size": 32},
+                                     "topology": {"context_parallel_size": 1, "block_parallel_size": 1, **topology}})
+
+    s = spec(tensor_parallel_size=2, sequence_parallel=True)
+    assert uses_peer_memory_kernels(s, 2) and not uses_peer_memory_kernels(s, 1)
+    up = prepare_parallel_environment(s, {}, 2)
+    assert up["PYTORCH_CUDA_ALLOC_CONF"] == "expandable_segments:True" and up["TORCH_NCCL_ASYNC_ERROR_HANDLING"] == "1"
+    assert "PYTORCH_CUDA_ALLOC_CONF" not in prepare_parallel_environment(s, {"PYTORCH_CUDA_ALLOC_CONF": "expandable_segments:False"}, 2)
+    with pytest.raises(RunSpecError, match="CUDA_DEVICE_MAX_CONNECTIONS"):
+        prepare_parallel_environment(s, {"CUDA_DEVICE_MAX_CONNECTIONS": "1"}, 2)
+    base = s.with_overrides({"kernel": {"impl": "nccl_baseline"}})
+    assert prepare_parallel_environment(base, {"CUDA_DEVICE_MAX_CONNECTIONS": "1"}, 2) is not None
+    assert infer_parallel_mesh_sizes(8, spec(tensor_parallel_size=2)) == {
+        "data": 4, "pipeline": 1, "local": 1, "context": 1, "block": 1, "tensor": 2, "expert": 1}
+    with pytest.raises(RunSpecError, match="pipeline"):
+        validate_supported_training_axes(spec(pipeline_parallel_size=2))

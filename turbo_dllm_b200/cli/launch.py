@@ -93,6 +93,15 @@ def build_launch_environment(args, base_env=None) -> dict:
     return env
 
 
+def apply_parallel_environment(spec, env: dict, world_size: int | None = None) -> dict:
+    """Adds what the run spec's parallel features need (parallel/preflight.py) to the launch environment."""
+    from ..parallel.preflight import prepare_parallel_environment, validate_supported_training_axes
+
+    validate_supported_training_axes(spec)
+    env.update(prepare_parallel_environment(spec, env, world_size))
+    return env
+
+
 def validate_launch_world_size(spec, args) -> int:
     lo, hi = parse_nnodes(args.nnodes)
     for nodes in sorted({lo, hi}):
@@ -133,7 +142,7 @@ def run_launch(args) -> int:
         spec = load_run_spec(config_path)
         world = validate_launch_world_size(spec, args)
         cmd = build_launch_command(args, config_path, extra)
-        env = build_launch_environment(args)
+        env = apply_parallel_environment(spec, build_launch_environment(args), world)
         print(f"DLLM_RUN_DIR={env['DLLM_RUN_DIR']}")
         print(f"DLLM_CACHE_DIR={env['DLLM_CACHE_DIR']}")
         print("DLLM_COMMAND=" + " ".join(shlex.quote(c) for c in cmd), flush=True)

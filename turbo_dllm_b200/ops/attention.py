@@ -212,9 +212,12 @@ def attention_forward_native(q, k, v, layout: MaskLayout, scale: float):
     return out, lse
 
 
+SEQ_STRIDE = 1 << 24      # key/query codes are sequence * SEQ_STRIDE + position
+
+
 def block_diffusion_layout(noisy_pos: torch.Tensor, noisy_group: torch.Tensor, clean_pos: torch.Tensor,
                            block_size: int, *, noisy_seq: torch.Tensor | None = None,
-                           clean_seq: torch.Tensor | None = None, seq_stride: int = 1 << 24,
+                           clean_seq: torch.Tensor | None = None, seq_stride: int = SEQ_STRIDE,
                            window: int | None = None, key_clean_pos: torch.Tensor | None = None,
                            key_clean_seq: torch.Tensor | None = None, clean_causal: bool = False) -> MaskLayout:
     """Layout for packed rows `[noisy ; clean]` attending to keys `[noisy ; clean keys]`.

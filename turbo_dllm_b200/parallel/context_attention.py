@@ -217,7 +217,7 @@ class _FusedContextAttention(torch.autograd.Function):
 
         ex, c = cpa.exchange, cpa.cfg
         Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
-        n_noisy, rows = cpa.layout.n_noisy, qkv.shape[0]
+        n_noisy, rows = cpa.stage_row0, qkv.shape[0]     # rows from here on travel to the peers
         q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
         L = cpa.mask.tile_lists()
         ex.fwd_calls += 1
@@ -295,6 +295,8 @@ class _StreamingAttention(torch.autograd.Function):
         st = MergeState(rows, Hq, D, qkv.device)
         scale = 1.0 / D ** 0.5
         for r in range(cpa.cp):
+            if r > 0 and cpa.counts[r] == 0:
+                continue        # a member without clean rows (its shard is another rank's)
             kv = cpa.shard_kv(qkv, r)
             k, v = cpa.kv_views(kv)
             st.merge(*attention_forward_native(q, k, v, cpa.shard_masks[r], scale))
@@ -319,6 +321,8 @@ class _StreamingAttention(torch.autograd.Function):
         dout3 = dout.contiguous().view(rows, Hq, D)
         scale = 1.0 / D ** 0.5
         for r in range(cpa.cp):
+            if r > 0 and cpa.counts[r] == 0:
+                continue
             kv = cpa.shard_kv(qkv, r)
             k, v = cpa.kv_views(kv)
             dq, dk, dv = attention_backward_native(q, k, v, out, dout3, lse, cpa.shard_masks[r], scale)
@@ -337,15 +341,21 @@ class _StreamingAttention(torch.autograd.Function):
         return dqkv, None
 
 
-def fused_key_layout(layout: PackedLayout, kpos: list, kseq: list, cp: int, me: int):
+def fused_key_layout(layout: PackedLayout, kpos: list, kseq: list, cp: int, me: int, key_codes: list | None = None):
     """Mask of the fused transport. Key order: this rank's rows, padding up to a 128-row tile boundary, then
-    the peers' clean rows in pull order (rank+1, rank+2, ...). kpos[r] / kseq[r]: positions and sequence
-    indices of rank r's clean rows."""
+    the peers' exchanged rows in pull order (rank+1, rank+2, ...). kpos[r] / kseq[r]: positions and sequence
+    indices of rank r's clean rows; key_codes[r] (token-split context parallelism): the key codes of ALL of
+    rank r's rows, which then travel whole."""
     from ..ops.attention import INT_MIN, MaskLayout
 
     dev = layout.positions.device
     order = [(me + 1 + s) % cp for s in range(cp - 1)]
     local = layout.mask                                   # keys = own rows
+    if key_codes is not None:
+        pad = (-layout.rows) % 128
+        k_code = torch.cat([local.k_code, torch.full((pad,), INT_MIN, dtype=torch.int32, device=dev)]
+                           + [key_codes[r] for r in order])
+        return MaskLayout(local.q_lo, local.q_hi, local.q_grp, k_code.contiguous())
     rem = block_diffusion_layout(layout.noisy_pos, layout.noisy_group, layout.clean_pos, layout.block_size,
                                  noisy_seq=layout.noisy_seq, clean_seq=layout.clean_seq,
                                  key_clean_pos=torch.cat([kpos[r] for r in order]),
@@ -366,18 +376,45 @@ class ContextParallelAttention:
         batch = spec.training.batch_size
         lay = runtime_clean_layout(spec.kernel.cp_bp_clean_kv_layout, runtime.block_parallel_size)
         dev = layout.positions.device
-        # clean key coordinates in gather order: for each CP rank, for each sequence, its positions
+        # clean key coordinates in gather order: for each member of the exchange group that owns a clean shard,
+        # for each sequence, its positions. Without clean-replica sharing the members are the CP ranks of this
+        # chunk; with it they are all ranks of the context/block axis and only the first CP of them own rows.
+        members = runtime.context_members()
         kpos, kseq, counts = [], [], []
-        for r in range(cp):
-            pos = clean_positions_for_rank(seq_len, cp, r, lay, bs, dev)
+        for _, shard, owns in members:
+            pos = (clean_positions_for_rank(seq_len, cp, shard, lay, bs, dev) if owns
+                   else torch.zeros(0, dtype=torch.long, device=dev))
             kpos.append(pos.repeat(batch))
             kseq.append(torch.arange(batch, device=dev).repeat_interleave(pos.numel()))
             counts.append(pos.numel() * batch)
+        # Token-split context parallelism (no block axis): every rank computes a slice of the offsets of every
+        # noisy block, so noisy K/V rows are exchanged too: a member contributes ALL its rows, noisy then clean.
+        self.split = layout.noisy_offsets is not None
+        self.key_codes = None
+        self.stage_row0 = layout.n_noisy       # first local row that travels
+        if self.split:
+            from ..ops.attention import SEQ_STRIDE
+            from .layout import noisy_rows, pure_context_offsets
+
+            views = int(layout.noisy_view.max()) + 1 if layout.n_noisy else 1
+            self.key_codes = []
+            for i, (_, shard, _owns) in enumerate(members):
+                _, _, _, grp = noisy_rows(seq_len=seq_len, block_size=bs, batch=batch, views=views,
+                                          noisy_offsets=pure_context_offsets(bs, cp, shard), device=dev)
+                self.key_codes.append(torch.cat([-(grp + 1), kseq[i] * SEQ_STRIDE + kpos[i]]).to(torch.int32))
+                counts[i] += grp.numel()
+            self.stage_row0 = 0
         self.counts = counts
-        self.cp, self.cp_rank = cp, runtime.context_parallel_rank
-        self.group_ranks = runtime.groups.ranks["context_block_parallel"]
+        self.group_ranks = [m[0] for m in members]
+        # `cp` / `cp_rank` below: size of the exchange group and this rank's index in it
+        cp = len(members)
+        self.cp, self.cp_rank = cp, self.group_ranks.index(runtime.rank)
         self.transport = spec.kernel.cp_bp_clean_kv_transport
         self.shard_masks = None
+        if self.split and self.transport in ("streaming", "peer_pull"):
+            raise ValueError(f"kernel.cp_bp_clean_kv_transport={self.transport} exchanges clean rows only; context "
+                             "parallelism without block parallelism divides the tokens inside every block and needs "
+                             "'collective' or 'fused' (or kernel.pure_cp_token_split: false)")
         if self.transport == "streaming":
             if dev.type != "cuda":
                 self.transport = "collective"   # the streaming path drives the sm_100a kernels directly
@@ -402,15 +439,21 @@ class ContextParallelAttention:
             if dev.type != "cuda":
                 raise ValueError("kernel.cp_bp_clean_kv_transport=peer_pull needs CUDA devices with peer access")
             self.exchange = PeerKVExchange(self.group, dev, counts, 2 * cfg.num_key_value_heads * cfg.head_dim)
+        if self.split:
+            from ..ops.attention import MaskLayout
+
+            m = layout.mask
+            self.mask = MaskLayout(m.q_lo, m.q_hi, m.q_grp, torch.cat(self.key_codes).contiguous())
+            return
         self.mask = block_diffusion_layout(layout.noisy_pos, layout.noisy_group, layout.clean_pos,
                                            layout.block_size, noisy_seq=layout.noisy_seq,
                                            clean_seq=layout.clean_seq, key_clean_pos=torch.cat(kpos),
                                            key_clean_seq=torch.cat(kseq), clean_causal=layout.clean_causal)
 
     def _init_fused(self, cfg, layout, kpos, kseq, counts, dev) -> None:
-        self.mask = fused_key_layout(layout, kpos, kseq, self.cp, self.cp_rank)
+        self.mask = fused_key_layout(layout, kpos, kseq, self.cp, self.cp_rank, self.key_codes)
         n_noisy = [torch.zeros(1, dtype=torch.long, device=dev) for _ in range(self.cp)]
-        dist.all_gather(n_noisy, torch.tensor([layout.n_noisy], dtype=torch.long, device=dev), group=self.group)
+        dist.all_gather(n_noisy, torch.tensor([self.stage_row0], dtype=torch.long, device=dev), group=self.group)
         self.exchange = FusedKVExchange(self.group, dev, counts, [int(t) for t in n_noisy], layout.rows,
                                         2 * cfg.num_key_value_heads * cfg.head_dim)
 
@@ -444,6 +487,12 @@ class ContextParallelAttention:
         n_noisy = self.layout.n_noisy
         q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
         rows = qkv.shape[0]
+        if self.split:      # all K|V rows travel; the gathered rows include this rank's own
+            kv_all = _AllGatherRows.apply(qkv[:, Hq * D:].contiguous(), self.group, self.counts)
+            nk = kv_all.shape[0]
+            out = block_attention(q, kv_all[:, : Hkv * D].view(nk, Hkv, D), kv_all[:, Hkv * D:].view(nk, Hkv, D),
+                                  self.mask)
+            return out.reshape(rows, Hq * D)
         kv_clean = qkv[n_noisy:, Hq * D:]                       # [n_clean, 2·Hkv·D], K | V
         if self.exchange is not None:
             gathered = _PeerGatherRows.apply(kv_clean.contiguous(), self.exchange)

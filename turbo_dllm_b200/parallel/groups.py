@@ -18,7 +18,7 @@ import torch.distributed as dist
 
 from .topology import ParallelPlan, RankAssignment
 
-AXES = ("data_parallel", "dense_data_parallel", "context_block_parallel", "clean_replica",
+AXES = ("data_parallel", "dense_data_parallel", "context_block_parallel", "local_parallel", "clean_replica",
         "tensor", "pipeline", "expert", "model_input", "model_parallel", "optimizer_data_parallel",
         "dense_optimizer")
 
@@ -66,6 +66,7 @@ class ProcessGroupCollection:
         mine = plan.assignment(rank)
         field_of = {"data_parallel": "data_parallel_group", "dense_data_parallel": "dense_data_parallel_group",
                     "context_block_parallel": "context_block_parallel_group", "clean_replica": "clean_replica_group",
+                    "local_parallel": "local_parallel_group",
                     "tensor": "tensor_parallel_group", "pipeline": "pipeline_parallel_group",
                     "expert": "expert_parallel_group", "model_input": "model_input_group",
                     "model_parallel": "model_parallel_group"}

@@ -67,6 +67,22 @@ def clean_positions_for_rank(seq_len, cp_size, cp_rank, layout="dual_chunk", ali
     return torch.cat(parts) if parts else torch.zeros(0, dtype=torch.long, device=device)
 
 
+def pure_context_offsets(block_size: int, cp_size: int, cp_rank: int) -> list[int]:
+    """Token offsets inside every diffusion block that context-parallel rank `cp_rank` computes when context
+    parallelism runs without block parallelism: block_size / cp_size offsets per rank, taken from both ends of
+    the block (rank r: the r-th slice from the front and the r-th from the back) when that share is even, one
+    contiguous slice otherwise. Every offset belongs to exactly one rank.
+    Semantics of dllm_parallel/core/attention/layout.py:54-132."""
+    if block_size % cp_size:
+        raise ValueError(f"block_size {block_size} must divide by context_parallel_size {cp_size}")
+    per = block_size // cp_size
+    if per % 2:
+        return list(range(cp_rank * per, (cp_rank + 1) * per))
+    h = per // 2
+    return list(range(cp_rank * h, (cp_rank + 1) * h)) + list(range(block_size - (cp_rank + 1) * h,
+                                                                    block_size - cp_rank * h))
+
+
 @dataclass
 class PackedLayout:
     """Row bookkeeping of one rank for one micro-batch shape (static across steps)."""
@@ -81,6 +97,7 @@ class PackedLayout:
     mask: MaskLayout             # attention mask over the rank's own rows (keys = own rows)
     block_size: int
     clean_causal: bool = False   # clean rows attend causally (token by token) instead of block-causally
+    noisy_offsets: tuple | None = None   # offsets inside a block this rank computes (pure context parallelism)
 
     @property
     def n_noisy(self) -> int:
@@ -95,15 +112,15 @@ class PackedLayout:
         return self.n_noisy + self.n_clean
 
 
-def build_packed_layout(*, seq_len: int, block_size: int, batch: int, views: int = 1,
-                        owned_blocks=None, clean_pos: torch.Tensor | None = None,
-                        window: int | None = None, device="cpu", clean_causal: bool = False) -> PackedLayout:
-    """Rows of one rank: for every sequence and view the noisy rows of `owned_blocks`, then for
-    every sequence the clean rows `clean_pos` (default: all positions)."""
+def noisy_rows(*, seq_len: int, block_size: int, batch: int, views: int = 1, owned_blocks=None,
+               noisy_offsets=None, device="cpu"):
+    """(position, sequence, view, block id) of the noisy rows of a rank, in packed order: sequence-major, then
+    view, then block, then offset. The block id is the same on every rank that holds rows of the block."""
     nblocks = seq_len // block_size
     owned = list(range(nblocks)) if owned_blocks is None else sorted(owned_blocks)
     blk = torch.tensor(owned, dtype=torch.long, device=device)
-    in_blk = torch.arange(block_size, device=device)
+    in_blk = (torch.arange(block_size, device=device) if noisy_offsets is None
+              else torch.tensor(sorted(noisy_offsets), dtype=torch.long, device=device))
     pos1 = (blk[:, None] * block_size + in_blk[None, :]).reshape(-1)
     n1 = pos1.numel()
     seq_ids = torch.arange(batch, device=device)
@@ -112,10 +129,25 @@ def build_packed_layout(*, seq_len: int, block_size: int, batch: int, views: int
     noisy_seq = seq_ids.repeat_interleave(views * n1)
     noisy_view = view_ids.repeat_interleave(n1).repeat(batch)
     noisy_group = (noisy_seq * views + noisy_view) * nblocks + noisy_pos // block_size
+    return noisy_pos, noisy_seq, noisy_view, noisy_group
+
+
+def build_packed_layout(*, seq_len: int, block_size: int, batch: int, views: int = 1,
+                        owned_blocks=None, clean_pos: torch.Tensor | None = None,
+                        window: int | None = None, device="cpu", clean_causal: bool = False,
+                        noisy_offsets=None) -> PackedLayout:
+    """Rows of one rank: for every sequence and view the noisy rows of `owned_blocks` (all offsets of a block,
+    or only `noisy_offsets`: pure context parallelism splits the tokens inside every block), then for
+    every sequence the clean rows `clean_pos` (default: all positions)."""
+    noisy_pos, noisy_seq, noisy_view, noisy_group = noisy_rows(
+        seq_len=seq_len, block_size=block_size, batch=batch, views=views, owned_blocks=owned_blocks,
+        noisy_offsets=noisy_offsets, device=device)
+    seq_ids = torch.arange(batch, device=device)
     cpos1 = torch.arange(seq_len, device=device) if clean_pos is None else clean_pos.to(device)
     clean_pos_all = cpos1.repeat(batch)
     clean_seq = seq_ids.repeat_interleave(cpos1.numel())
     mask = block_diffusion_layout(noisy_pos, noisy_group, clean_pos_all, block_size, noisy_seq=noisy_seq,
                                   clean_seq=clean_seq, window=window, clean_causal=clean_causal)
     return PackedLayout(noisy_pos, noisy_seq, noisy_view, noisy_group, clean_pos_all, clean_seq,
-                        torch.cat([noisy_pos, clean_pos_all]), mask, block_size, clean_causal)
+                        torch.cat([noisy_pos, clean_pos_all]), mask, block_size, clean_causal,
+                        None if noisy_offsets is None else tuple(sorted(noisy_offsets)))

@@ -30,6 +30,8 @@ class ParallelRuntime:
     device: torch.device
     rank: int
     world_size: int
+    share_clean_replicas: bool = True
+    pure_cp_token_split: bool = True
 
     # sizes
     @property
@@ -91,8 +93,38 @@ class ParallelRuntime:
         return self.groups.group("optimizer_data_parallel")
 
     @property
+    def splits_block_tokens(self) -> bool:
+        """Context parallelism without block parallelism: the tokens INSIDE every noisy block are divided over the
+        ranks (two-ended), noisy K/V travel with the clean K/V, and no noisy row is computed twice."""
+        return self.pure_cp_token_split and self.context_parallel_size > 1 and self.block_parallel_size == 1
+
+    @property
+    def shares_clean_replicas(self) -> bool:
+        """Blocks are spread over more ranks than the clean tokens (BP > CP > 1). The ranks that would hold a
+        second copy of a clean shard hold no clean rows at all: every rank of the context/block axis pulls clean
+        K/V from the CP shard owners and returns clean dK/dV to them, so the clean stream is computed once per
+        shard. The reference computes it on the owner too and broadcasts tensors inside `clean_replica` groups
+        (dllm_parallel/core/parallel/runtime.py:558-687); on NVSwitch any rank reaches any owner directly."""
+        return (self.share_clean_replicas and self.context_parallel_size > 1
+                and self.block_parallel_size > self.context_parallel_size)
+
+    @property
+    def owns_clean_shard(self) -> bool:
+        return not self.shares_clean_replicas or self.assignment.local_parallel_rank < self.context_parallel_size
+
+    @property
     def context_group(self):
-        return self.groups.group("context_block_parallel")
+        return self.groups.group("local_parallel" if self.shares_clean_replicas else "context_block_parallel")
+
+    def context_members(self) -> list[tuple[int, int, bool]]:
+        """(rank, clean shard index, owns that shard) of every member of `context_group`, in group order."""
+        axis = "local_parallel" if self.shares_clean_replicas else "context_block_parallel"
+        out = []
+        for r in self.groups.ranks[axis]:
+            a = self.plan.assignment(r)
+            owns = not self.shares_clean_replicas or a.local_parallel_rank < self.context_parallel_size
+            out.append((r, a.context_parallel_rank, owns))
+        return out
 
     @property
     def tensor_group(self):
@@ -136,4 +168,7 @@ def build_parallel_runtime(spec, *, device, rank: int | None = None, world_size:
     policy = CPBPPolicy(clean_kv_layout=spec.kernel.cp_bp_clean_kv_layout,
                         clean_kv_transport=spec.kernel.cp_bp_clean_kv_transport)
     return ParallelRuntime(plan=plan, assignment=plan.assignment(rank), groups=groups, policy=policy,
-                           device=torch.device(device), rank=rank, world_size=world_size)
+                           device=torch.device(device), rank=rank, world_size=world_size,
+                           share_clean_replicas=bool(spec.kernel.cp_bp_share_clean_replicas),
+                           pure_cp_token_split=bool(spec.kernel.pure_cp_token_split)
+                           and (spec.objective.block_size or 0) % max(spec.topology.context_parallel_size, 1) == 0)

@@ -39,6 +39,9 @@ class RankAssignment:
     model_input_group: list[int]
     model_parallel_group: list[int]
     owned_blocks: tuple[int, ...] = ()
+    # all ranks of the context/block axis of one replica (the clean K/V of every shard owner is pulled by all of
+    # them when blocks are spread over more ranks than the clean tokens)
+    local_parallel_group: tuple[int, ...] = ()
 
     GROUP_FIELDS = ("data_parallel_group", "dense_data_parallel_group", "context_block_parallel_group",
                     "clean_replica_group", "tensor_parallel_group", "pipeline_parallel_group",
@@ -182,6 +185,7 @@ def build_parallel_plan(*, num_blocks: int, world_size: int, data_parallel_size:
             model_parallel_group=phys(logical(d, x, y, z, w) for x in range(pp) for y in range(local)
                                       for z in range(tp) for w in range(ep)),
             owned_blocks=schedule.blocks_by_worker[bp_rank] if bp > 1 else tuple(range(num_blocks)),
+            local_parallel_group=tuple(phys(logical(d, p, x, t, e) for x in range(local))),
         )
         assignments[a.rank] = a
     return ParallelPlan(

@@ -110,6 +110,8 @@ class TrainingSession:
         self.last_encoder_loss = None
         self.data = self.executor.build_data_runtime(spec, self.cfg, self.device, dp_rank, self.dp_size,
                                                      host_staged=host_staged_data)
+        if self.cfg.is_hybrid and runtime is not None:
+            runtime.share_clean_replicas = False    # linear-attention layers trade row shards inside a CP chunk
         self.layout = self._build_layout()
         self.attend = self._build_attention()
         self._first_layout, self._first_attend = self.layout, self.attend
@@ -291,12 +293,19 @@ class TrainingSession:
             lay = runtime_clean_layout(s.kernel.cp_bp_clean_kv_layout, rt.block_parallel_size)
             clean = clean_positions_for_rank(s.model.seq_len, rt.context_parallel_size, rt.context_parallel_rank,
                                              lay, s.objective.block_size, self.device)
+            if not rt.owns_clean_shard:     # another rank computes this shard's clean stream; its K/V are pulled
+                clean = clean[:0]
         elif rt is not None and rt.block_parallel_size > 1 and s.topology.replicate_clean_prefix:
             last = max(owned)
             clean = torch.arange(0, last * s.objective.block_size, device=self.device)
+        offsets = None
+        if rt is not None and rt.splits_block_tokens and not self.cfg.is_hybrid:
+            from ..parallel.layout import pure_context_offsets
+
+            offsets = pure_context_offsets(s.objective.block_size, rt.context_parallel_size, rt.context_parallel_rank)
         return build_packed_layout(seq_len=seq_len or s.model.seq_len, block_size=s.objective.block_size,
                                    batch=s.training.batch_size, views=self.objective.views,
-                                   owned_blocks=owned, clean_pos=clean, device=self.device,
+                                   owned_blocks=owned, clean_pos=clean, device=self.device, noisy_offsets=offsets,
                                    clean_causal=getattr(self, "encoder_loss_weight", 0.0) > 0.0)
 
     def _build_head_parallel_plan(self):
@@ -447,7 +456,7 @@ class TrainingSession:
         # group: their loss terms are computed that many times and the summed gradients must be divided by it
         rt = self.runtime
         copies = (rt.context_parallel_size if rt is not None and rt.context_parallel_size > 1
-                  and rt.block_parallel_size == 1 else 1)
+                  and rt.block_parallel_size == 1 and not (rt.splits_block_tokens and not self.cfg.is_hybrid) else 1)
         if all(x.supervision_mask is None for x in batches):
             return float(b * per * len(batches) * self.dp_size * copies)
         cnt = torch.zeros(1, dtype=torch.float64, device=self.device)
