@@ -14,7 +14,7 @@ MAPPING = {
 }
 
 
-def _run(rank, world, cp, bp, steps, objective, share=True, split=True):
+def _run(rank, world, cp, bp, steps, objective, share=True, split=True, window=None):
     import copy
 
     import torch.distributed as dist
@@ -27,6 +27,8 @@ def _run(rank, world, cp, bp, steps, objective, share=True, split=True):
     m = copy.deepcopy(MAPPING)
     m["topology"].update(context_parallel_size=cp, block_parallel_size=bp)
     m["objective"]["name"] = objective
+    if window:          # layer 0 slides, layer 1 attends to the full prefix
+        m["model"].update(sliding_window=window, sliding_window_pattern=2)
     m["kernel"] = {"cp_bp_share_clean_replicas": bool(share), "pure_cp_token_split": bool(split)}
     spec = RunSpec.from_mapping(m).validate(world_size=world)
     rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
@@ -130,6 +132,51 @@ def test_pure_context_parallel_matches_single_process(split):
         assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
         assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=2e-5)
         assert n_noisy == (n_noisy_full // 2 if split else n_noisy_full)
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("cp,bp", [(2, 2), (2, 1)])
+def test_sliding_window_layers_exchange_only_the_window(cp, bp):
+    """A model whose first layer has a 64-token window: under CP 2 x BP 2 that layer moves only the clean rows
+    inside some local row's window (one all-to-all), the other layer moves all of them; under token-split pure
+    CP only the mask narrows. The window changes the result, and every parallel form equals the single-process
+    run with the same window."""
+    ref_losses, ref_params, _ = _run(0, 1, 1, 1, 2, "standard_block_diffusion", True, True, 64)
+    full_losses, _, _ = _run(0, 1, 1, 1, 2, "standard_block_diffusion")
+    assert abs(ref_losses[-1] - full_losses[-1]) > 1e-4
+    outs = run_ranks(_run, cp * max(bp // cp, 1), args=(cp, bp, 2, "standard_block_diffusion", True, True, 64),
+                     deadline_s=300)
+    for losses, params, _ in outs:
+        assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
+        assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=2e-5)
+
+
+def test_windowed_exchange_plan_counts():
+    """Single-process check of the plan arithmetic: a rank that owns clean [0, 128) and noisy blocks at
+    [128, 256) with window 64 needs positions [64, 256) (own rows' windows); what it receives from the other
+    owner are exactly the needed positions in [128, 256)."""
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.parallel.context_attention import WindowedExchangePlan
+    from turbo_dllm_b200.parallel.layout import build_packed_layout
+
+    import os, socket
+    with socket.socket() as so:
+        so.bind(("127.0.0.1", 0))
+        port = so.getsockname()[1]
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=0, world_size=1)
+    try:
+        lay = build_packed_layout(seq_len=256, block_size=32, batch=2, owned_blocks=[4, 5, 6, 7],
+                                  clean_pos=torch.arange(0, 128), window=64)
+        kpos1 = [torch.arange(0, 128)]
+        plan = WindowedExchangePlan(lay, 64, 256, 2, kpos1, dist.group.WORLD, 0)
+        need = plan.needs[0]
+        # clean rows at [0,128): windows cover [0,128); noisy blocks 4..7 start at 128..224: windows [64, 224)
+        assert need[:224].all() and not need[224:].any()
+        assert plan.recv_counts == [128 * 2] and plan.send_counts == [128 * 2]
+    finally:
+        dist.destroy_process_group()
 
 
 def test_pure_context_offsets_partition_the_block():

@@ -81,6 +81,10 @@ SECTIONS: dict[str, tuple[F, ...]] = {
         F("linear_key_head_dim", OPT_INT, None, ext=True),
         F("linear_value_head_dim", OPT_INT, None, ext=True),
         F("linear_conv_kernel", OPT_INT, None, ext=True),
+        F("sliding_window", OPT_INT, None, ext=True,
+          help="window (clean positions) of the sliding-window layers"),
+        F("sliding_window_pattern", OPT_INT, None, ext=True,
+          help="every n-th layer attends to the full prefix, the others slide (0: every layer slides)"),
         F("random_init", bool, False, ext=True, help="build from the shape fields, load no weights"),
     ),
     "objective": (

@@ -28,7 +28,12 @@ class ModelConfig:
     num_experts: int = 0
     num_experts_per_token: int = 0
     moe_intermediate_size: int = 0
+    # sliding-window layers: a layer whose window is set lets a row see only the last `sliding_window` clean
+    # positions before its clean stop. Which layers slide: `layer_types` ("sliding_attention" / "full_attention"
+    # per layer) when given, else every layer except each `sliding_window_pattern`-th one (0: all layers slide).
     sliding_window: int | None = None
+    sliding_window_pattern: int = 0
+    layer_types: tuple | None = None
     family: str = "causal_lm"
     # hybrid decoders (family qwen3_8): every `full_attention_interval`-th layer is gated softmax
     # attention, the others are Gated DeltaNet linear-attention layers (0 = no linear layers)
@@ -58,6 +63,20 @@ class ModelConfig:
     @property
     def is_hybrid(self) -> bool:
         return self.full_attention_interval > 0
+
+    def layer_window(self, i: int) -> int | None:
+        """Window of layer i, or None when the layer attends to the whole clean prefix."""
+        if not self.sliding_window:
+            return None
+        if self.layer_types is not None:
+            return self.sliding_window if self.layer_types[i] == "sliding_attention" else None
+        if self.sliding_window_pattern > 0 and (i + 1) % self.sliding_window_pattern == 0:
+            return None
+        return self.sliding_window
+
+    @property
+    def has_sliding_layers(self) -> bool:
+        return any(self.layer_window(i) is not None for i in range(self.num_layers))
 
     def layer_kind(self, i: int) -> str:
         """"full_attention" or "linear_attention" for layer i (every interval-th layer is full)."""
@@ -153,7 +172,8 @@ def model_config_from_run_spec(spec) -> ModelConfig:
     for name in ("vocab_size", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
                  "intermediate_size", "rope_theta", "mask_token_id", "num_experts", "num_experts_per_token",
                  "moe_intermediate_size", "full_attention_interval", "linear_num_key_heads",
-                 "linear_num_value_heads", "linear_key_head_dim", "linear_value_head_dim", "linear_conv_kernel"):
+                 "linear_num_value_heads", "linear_key_head_dim", "linear_value_head_dim", "linear_conv_kernel",
+                 "sliding_window", "sliding_window_pattern"):
         v = getattr(m, name)
         if v is not None:
             over[name] = v

@@ -196,12 +196,15 @@ class DecoderLayer(nn.Module):
 class LocalAttention:
     """Keys are the rank's own rows (single rank, or pure data parallelism)."""
 
-    def __init__(self, cfg: ModelConfig, mask: MaskLayout, store=None):
-        self.cfg, self.mask, self.store = cfg, mask, store
+    def __init__(self, cfg: ModelConfig, mask: MaskLayout, store=None, window_mask: MaskLayout | None = None):
+        self.cfg, self.mask, self.store, self.window_mask = cfg, mask, store, window_mask
 
     def __call__(self, qkv, layer_idx):
         c = self.cfg
-        return packed_block_attention(qkv, c.num_attention_heads, c.num_key_value_heads, c.head_dim, self.mask,
+        mask = self.mask
+        if self.window_mask is not None and c.layer_window(layer_idx) is not None:
+            mask = self.window_mask         # sliding-window layer
+        return packed_block_attention(qkv, c.num_attention_heads, c.num_key_value_heads, c.head_dim, mask,
                                       store=self.store, key=layer_idx)
 
 

@@ -46,7 +46,13 @@ def load_hf_config(path: str, max_layers: int | None = None) -> ModelConfig:
                       linear_key_head_dim=int(c["linear_key_head_dim"]),
                       linear_value_head_dim=int(c["linear_value_head_dim"]),
                       linear_conv_kernel=int(c.get("linear_conv_kernel_dim", 4)))
-    return ModelConfig(**hybrid,
+    sliding = {}
+    if c.get("sliding_window") and c.get("use_sliding_window", True):
+        types = c.get("layer_types")
+        sliding = dict(sliding_window=int(c["sliding_window"]),
+                       sliding_window_pattern=int(c.get("sliding_window_pattern", 0) or 0),
+                       layer_types=tuple(types[:layers]) if types and not hybrid else None)
+    return ModelConfig(**hybrid, **sliding,
         vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], num_layers=layers, num_attention_heads=heads,
         num_key_value_heads=c.get("num_key_value_heads", heads), head_dim=c.get("head_dim", c["hidden_size"] // heads),
         intermediate_size=c["intermediate_size"], rope_theta=float(c.get("rope_theta", 1e6)),
@@ -67,7 +73,12 @@ def hf_config_dict(cfg: ModelConfig) -> dict:
                 "linear_num_key_heads": cfg.linear_num_key_heads, "linear_num_value_heads": cfg.linear_num_value_heads,
                 "linear_key_head_dim": cfg.linear_key_head_dim, "linear_value_head_dim": cfg.linear_value_head_dim,
                 "linear_conv_kernel_dim": cfg.linear_conv_kernel}
-    return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": cfg.vocab_size,
+    sliding = {}
+    if cfg.has_sliding_layers:
+        sliding = {"sliding_window": cfg.sliding_window, "use_sliding_window": True,
+                   "layer_types": ["sliding_attention" if cfg.layer_window(i) else "full_attention"
+                                   for i in range(cfg.num_layers)]}
+    return {**sliding, "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": cfg.vocab_size,
             "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
             "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "intermediate_size": cfg.intermediate_size, "rope_theta": cfg.rope_theta,

@@ -90,6 +90,75 @@ class _AllGatherRows(torch.autograd.Function):
         return out[: counts[ctx.rank]], None, None
 
 
+class WindowedExchangePlan:
+    """Which clean rows a sliding-window layer moves between the members of a context group.
+
+    A query row sees the clean positions [stop - window, stop) of its sequence, so a rank needs only the union of
+    those intervals over its rows; the plan intersects every member's need with every member's ownership, which
+    gives the variable split sizes of ONE all-to-all in the forward pass and of its reverse in the backward
+    pass. Each member publishes its need as a per-position flag vector at set-up (an all-gather of seq_len
+    bytes), so clean-replica sharing and any block schedule are covered without recomputing other ranks'
+    layouts. Role of windowed_clean_exchange_plan, dllm_parallel/core/attention/layout.py:322-426."""
+
+    def __init__(self, layout: PackedLayout, window: int, seq_len: int, batch: int, kpos1: list, group, me: int):
+        dev = layout.positions.device
+        self.group = group
+        stop = torch.cat([(layout.noisy_pos // layout.block_size) * layout.block_size,
+                          layout.clean_pos + 1 if layout.clean_causal
+                          else (layout.clean_pos // layout.block_size + 1) * layout.block_size]).unique()
+        delta = torch.zeros(seq_len + 1, dtype=torch.long, device=dev)          # interval union by prefix sums
+        delta.index_add_(0, (stop - window).clamp_min(0), torch.ones_like(stop))
+        delta.index_add_(0, stop.clamp_max(seq_len), -torch.ones_like(stop))
+        need = (delta.cumsum(0)[:seq_len] > 0).to(torch.uint8)
+        needs = [torch.empty_like(need) for _ in kpos1]
+        dist.all_gather(needs, need, group=group)
+        self.needs = [n.bool() for n in needs]
+        mine = kpos1[me]                                   # positions of this rank's clean shard (one sequence)
+        n1 = mine.numel()
+        seq_off = torch.arange(batch, device=dev)
+        send, self.send_counts = [], []
+        for n in self.needs:                               # rows of mine that member d needs, all sequences
+            idx1 = torch.nonzero(n[mine]).flatten() if n1 else mine
+            send.append((seq_off[:, None] * n1 + idx1[None, :]).reshape(-1))
+            self.send_counts.append(int(idx1.numel()) * batch)
+        self.send_index = torch.cat(send) if send else torch.zeros(0, dtype=torch.long, device=dev)
+        self.recv_counts, kp, ks = [], [], []
+        for pos in kpos1:                                  # rows this rank receives from member j
+            got = pos[self.needs[me][pos]] if pos.numel() else pos
+            self.recv_counts.append(int(got.numel()) * batch)
+            kp.append(got.repeat(batch))
+            ks.append(seq_off.repeat_interleave(got.numel()))
+        self.key_pos, self.key_seq = torch.cat(kp), torch.cat(ks)
+
+
+class _AllToAllRows(torch.autograd.Function):
+    """Sends x[plan.send_index] split by plan.send_counts, returns the received rows (member order); the backward
+    pass sends the gradients back and sums them into the rows they came from."""
+
+    @staticmethod
+    def forward(ctx, x, plan):
+        send = x.index_select(0, plan.send_index)
+        out = x.new_empty(sum(plan.recv_counts), x.shape[1])
+        with communication_scope("context_parallel", "forward", "all_to_all", send.numel() * send.element_size(),
+                                 out.numel() * out.element_size()):
+            dist.all_to_all_single(out, send, output_split_sizes=plan.recv_counts,
+                                   input_split_sizes=plan.send_counts, group=plan.group)
+        ctx.plan, ctx.rows = plan, x.shape[0]
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        plan = ctx.plan
+        back = g.new_empty(sum(plan.send_counts), g.shape[1])
+        with communication_scope("context_parallel", "backward", "all_to_all", g.numel() * g.element_size(),
+                                 back.numel() * back.element_size()):
+            dist.all_to_all_single(back, g.contiguous(), output_split_sizes=plan.send_counts,
+                                   input_split_sizes=plan.recv_counts, group=plan.group)
+        dx = torch.zeros(ctx.rows, g.shape[1], dtype=torch.float32, device=g.device)
+        dx.index_add_(0, plan.send_index, back.float())
+        return dx.to(g.dtype), None
+
+
 class PeerKVExchange:
     """Clean K|V gather and gradient scatter-reduce through peer memory (csrc/comm.cu): two staging
     buffers alternate so that a fast rank never overwrites rows a slower peer is still pulling."""
@@ -405,10 +474,25 @@ class ContextParallelAttention:
                 counts[i] += grp.numel()
             self.stage_row0 = 0
         self.counts = counts
+        self._kpos1 = [p[: p.numel() // max(batch, 1)] for p in kpos]      # one sequence's positions per member
         self.group_ranks = [m[0] for m in members]
         # `cp` / `cp_rank` below: size of the exchange group and this rank's index in it
         cp = len(members)
         self.cp, self.cp_rank = cp, self.group_ranks.index(runtime.rank)
+        # sliding-window layers exchange only the rows inside some local row's window, by one all-to-all
+        self.window_plan = self.window_mask = None
+        if layout.window_mask is not None and not self.split:
+            self.window_plan = WindowedExchangePlan(layout, layout.window, seq_len, batch, self._kpos1, self.group,
+                                                    self.cp_rank)
+            self.window_mask = block_diffusion_layout(
+                layout.noisy_pos, layout.noisy_group, layout.clean_pos, layout.block_size, noisy_seq=layout.noisy_seq,
+                clean_seq=layout.clean_seq, key_clean_pos=self.window_plan.key_pos,
+                key_clean_seq=self.window_plan.key_seq, window=layout.window, clean_causal=layout.clean_causal)
+        elif layout.window_mask is not None:       # token-split: all rows travel anyway; only the mask narrows
+            from ..ops.attention import MaskLayout
+
+            w = layout.window_mask
+            self.window_mask = MaskLayout(w.q_lo, w.q_hi, w.q_grp, torch.cat(self.key_codes).contiguous())
         self.transport = spec.kernel.cp_bp_clean_kv_transport
         self.shard_masks = None
         if self.split and self.transport in ("streaming", "peer_pull"):
@@ -477,7 +561,25 @@ class ContextParallelAttention:
         return (kv[:, :kd].view(n, c.num_key_value_heads, c.head_dim),
                 kv[:, kd:].view(n, c.num_key_value_heads, c.head_dim))
 
+    def _windowed(self, qkv):
+        """A sliding-window layer: noisy keys are local, clean keys are the rows the all-to-all brought."""
+        c = self.cfg
+        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        n_noisy, rows = self.layout.n_noisy, qkv.shape[0]
+        q, _, _ = split_packed_qkv(qkv, Hq, Hkv, D)
+        if self.split:
+            kv_all = _AllGatherRows.apply(qkv[:, Hq * D:].contiguous(), self.group, self.counts)
+        else:
+            got = _AllToAllRows.apply(qkv[n_noisy:, Hq * D:].contiguous(), self.window_plan)
+            kv_all = torch.cat([qkv[:n_noisy, Hq * D:], got], dim=0)
+        nk = kv_all.shape[0]
+        out = block_attention(q, kv_all[:, : Hkv * D].view(nk, Hkv, D), kv_all[:, Hkv * D:].view(nk, Hkv, D),
+                              self.window_mask)
+        return out.reshape(rows, Hq * D)
+
     def __call__(self, qkv, layer_idx):
+        if self.window_mask is not None and self.cfg.layer_window(layer_idx) is not None:
+            return self._windowed(qkv)
         if self.transport == "streaming":
             return _StreamingAttention.apply(qkv, self)
         if self.transport == "fused":

@@ -98,6 +98,8 @@ class PackedLayout:
     block_size: int
     clean_causal: bool = False   # clean rows attend causally (token by token) instead of block-causally
     noisy_offsets: tuple | None = None   # offsets inside a block this rank computes (pure context parallelism)
+    window: int | None = None            # window of the sliding-window layers
+    window_mask: MaskLayout | None = None   # the mask of those layers over the rank's own rows
 
     @property
     def n_noisy(self) -> int:
@@ -138,7 +140,8 @@ def build_packed_layout(*, seq_len: int, block_size: int, batch: int, views: int
                         noisy_offsets=None) -> PackedLayout:
     """Rows of one rank: for every sequence and view the noisy rows of `owned_blocks` (all offsets of a block,
     or only `noisy_offsets`: pure context parallelism splits the tokens inside every block), then for
-    every sequence the clean rows `clean_pos` (default: all positions)."""
+    every sequence the clean rows `clean_pos` (default: all positions). `window`: also build the mask of the
+    sliding-window layers (`window_mask`); `mask` always is the full-prefix one."""
     noisy_pos, noisy_seq, noisy_view, noisy_group = noisy_rows(
         seq_len=seq_len, block_size=block_size, batch=batch, views=views, owned_blocks=owned_blocks,
         noisy_offsets=noisy_offsets, device=device)
@@ -147,7 +150,11 @@ def build_packed_layout(*, seq_len: int, block_size: int, batch: int, views: int
     clean_pos_all = cpos1.repeat(batch)
     clean_seq = seq_ids.repeat_interleave(cpos1.numel())
     mask = block_diffusion_layout(noisy_pos, noisy_group, clean_pos_all, block_size, noisy_seq=noisy_seq,
-                                  clean_seq=clean_seq, window=window, clean_causal=clean_causal)
+                                  clean_seq=clean_seq, clean_causal=clean_causal)
+    wmask = None
+    if window:
+        wmask = block_diffusion_layout(noisy_pos, noisy_group, clean_pos_all, block_size, noisy_seq=noisy_seq,
+                                       clean_seq=clean_seq, window=window, clean_causal=clean_causal)
     return PackedLayout(noisy_pos, noisy_seq, noisy_view, noisy_group, clean_pos_all, clean_seq,
                         torch.cat([noisy_pos, clean_pos_all]), mask, block_size, clean_causal,
-                        None if noisy_offsets is None else tuple(sorted(noisy_offsets)))
+                        None if noisy_offsets is None else tuple(sorted(noisy_offsets)), window or None, wmask)

@@ -280,7 +280,7 @@ class TrainingSession:
                                  f"{self.spec.objective.block_size} / model.seq_len {self.spec.model.seq_len}")
             lay = self._build_layout(seq_len)
             cache[seq_len] = (lay, LocalAttention(getattr(self.model, "lcfg", self.cfg), lay.mask,
-                                                  store=self.model.store))
+                                                  store=self.model.store, window_mask=lay.window_mask))
         self.layout, self.attend = cache[seq_len]
         self._layout_len = seq_len
 
@@ -306,6 +306,7 @@ class TrainingSession:
         return build_packed_layout(seq_len=seq_len or s.model.seq_len, block_size=s.objective.block_size,
                                    batch=s.training.batch_size, views=self.objective.views,
                                    owned_blocks=owned, clean_pos=clean, device=self.device, noisy_offsets=offsets,
+                                   window=self.cfg.sliding_window if self.cfg.has_sliding_layers else None,
                                    clean_causal=getattr(self, "encoder_loss_weight", 0.0) > 0.0)
 
     def _build_head_parallel_plan(self):
@@ -339,7 +340,8 @@ class TrainingSession:
             from ..parallel.context_attention import ContextParallelAttention
 
             return ContextParallelAttention(getattr(self.model, "lcfg", self.cfg), self.layout, rt, self.spec)
-        return LocalAttention(getattr(self.model, "lcfg", self.cfg), self.layout.mask, store=self.model.store)
+        return LocalAttention(getattr(self.model, "lcfg", self.cfg), self.layout.mask, store=self.model.store,
+                              window_mask=self.layout.window_mask)
 
     def _build_fused_sync(self, group):
         if group is None or self.device.type != "cuda" or self.spec.kernel.impl in ("cpu_reference", "nccl_baseline"):
