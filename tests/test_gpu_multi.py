@@ -169,6 +169,52 @@ def test_csbp2_on_gpus_matches_single_gpu(transport):
         assert (torch.from_numpy(params) - torch.from_numpy(ref[1])).abs().max().item() < 3e-2
 
 
+def _dflash_replica(rank, world, mode, steps):
+    import os
+
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-hd128", "seq_len": 1024, "dtype": "bf16", "family": "dflash",
+                  "verifier_id": "synthetic:tiny-hd128", "target_layer_ids": [0, 1]},
+        "objective": {"name": "dflash_distillation", "block_size": 16, "max_anchors": 32, "decay_gamma": 4.0},
+        "data": {"target_features": "online"}, "training": {"batch_size": 2, "steps": steps},
+        "topology": {"context_parallel_size": world, "block_parallel_size": world},
+        "kernel": {"dflash_context_exchange": mode, "impl": "nccl_baseline"},
+        "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
+    rt = build_parallel_runtime(spec, device=f"cuda:{rank}", rank=rank, world_size=world) if world > 1 else None
+    s = TrainingSession(spec, device=f"cuda:{rank}", runtime=rt)
+    losses = []
+    for _ in range(steps):
+        t = s.step().loss_sum.double().clone()
+        if world > 1:
+            dist.all_reduce(t)
+        losses.append(float(t))
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    return losses, s.model.flat.data.float().cpu()
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("mode", ["kv_pull", "query_rotation"])
+def test_dflash_replica_over_two_gpus_matches_single_gpu(mode):
+    """The drafter's anchors and context rows divided over two GPUs: gathered context K|V, and rotated queries
+    with merged partial attention (backward against the merged out / lse), against one GPU."""
+    _need(2)
+    ref = run_ranks(_dflash_replica, 1, args=("auto", 3), backend=None, deadline_s=300)[0]
+    outs = run_ranks(_dflash_replica, 2, args=(mode, 3), backend="nccl", deadline_s=300)
+    for losses, params in outs:
+        assert losses == pytest.approx(ref[0], rel=3e-2)
+        assert (torch.from_numpy(params) - torch.from_numpy(ref[1])).abs().max().item() < 3e-2
+
+
 @pytest.mark.distributed
 @pytest.mark.parametrize("transport,world", [("collective", 2), ("fused", 2), ("fused", 4), ("fused", 8)])
 def test_pure_context_parallel_token_split_on_gpus_matches_single_gpu(transport, world):

@@ -182,6 +182,13 @@ class RunSpec:
             need(o.name in allowed, f"objective {o.name} is not supported by family {m.family} "
                                     f"(supported: {', '.join(allowed)})")
         if o.name == "dflash_distillation":
+            need(cp == 1 or cp == bp, "dflash_distillation divides anchors and context rows over the same ranks: "
+                                      "context_parallel_size must be 1 or equal block_parallel_size")
+            need(t.tensor_parallel_size == 1, "dflash_distillation has no tensor-parallel drafter")
+            n_rep = max(cp, bp)
+            if o.max_anchors:
+                need(o.max_anchors % n_rep == 0, f"objective.max_anchors ({o.max_anchors}) must divide by the "
+                                                 f"{n_rep} ranks of a replica")
             need(bool(m.target_layer_ids), "dflash_distillation needs model.target_layer_ids")
             need(self.data.target_features in ("offline", "synthetic", "online"),
                  "dflash_distillation needs data.target_features (offline, synthetic or online)")

@@ -243,6 +243,7 @@ SECTIONS: dict[str, tuple[F, ...]] = {
         F("cp_bp_clean_kv_transport", str, "collective", choices=("collective", "streaming", "peer_pull", "fused")),
         F("cp_bp_share_clean_replicas", bool, True),
         F("pure_cp_token_split", bool, True),
+        F("dflash_context_exchange", str, "auto", choices=("auto", "kv_pull", "query_rotation")),
         F("cp_bp_debug_nonfinite_attention", bool, False),
         F("runtime_jit", bool, False),
         F("impl", str, "auto", choices=("auto", "cpu_reference", "nccl_baseline", "sm100_fused"), ext=True),

@@ -97,6 +97,19 @@ def _draft_layer_specs(cfg: ModelConfig, i: int):
     return out
 
 
+def draft_attention(q, kv, mask, cfg: ModelConfig):
+    """q [draft rows, Hq, D]; kv [draft rows + context rows, 2 * Hkv * D] (K | V). `mask` is the MaskLayout of a
+    single-rank replica, or the (exchange, plan) pair of a replica that spans ranks
+    (parallel/dflash_context.py), whose context rows are this rank's shard."""
+    if isinstance(mask, tuple):
+        exchange, plan = mask
+        return exchange.attend(plan, q, kv, cfg.num_key_value_heads)
+    nk = kv.shape[0]
+    k = kv[:, : cfg.kv_dim].view(nk, cfg.num_key_value_heads, cfg.head_dim)
+    v = kv[:, cfg.kv_dim:].view(nk, cfg.num_key_value_heads, cfg.head_dim)
+    return block_attention(q, k, v, mask)
+
+
 class DFlashLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, idx: int, flat: FlatParams):
         super().__init__()
@@ -117,10 +130,7 @@ class DFlashLayer(nn.Module):
         kv = linear(torch.cat([y, ctx], dim=0), self.w_kv)       # keys = [draft rows ; context rows]
         kv = qk_norm_rope(kv, pos_all, inv_freq, self.q_norm, self.k_norm, 0, c.num_key_value_heads, c.head_dim,
                           c.rms_norm_eps)
-        nk = kv.shape[0]
-        k = kv[:, : c.kv_dim].view(nk, c.num_key_value_heads, c.head_dim)
-        v = kv[:, c.kv_dim:].view(nk, c.num_key_value_heads, c.head_dim)
-        a = block_attention(q.view(nd, c.num_attention_heads, c.head_dim), k, v, mask)
+        a = draft_attention(q.view(nd, c.num_attention_heads, c.head_dim), kv, mask, c)
         h = linear_residual(a.reshape(nd, c.q_dim), self.w_o, h)
         y2, _ = rmsnorm(h, self.post_norm, c.rms_norm_eps)
         return linear_residual(linear_swiglu(y2, self.w_gate_up), self.w_down, h)

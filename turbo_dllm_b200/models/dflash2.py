@@ -28,7 +28,7 @@ from ..ops.rope import qk_norm_rope, rope_inv_freq
 from .activation_store import ActivationStore
 from .config import ModelConfig
 from .dense import BlockDiffusionTransformer, FlatParams
-from .dflash import DFlashDraftModel, _draft_layer_specs
+from .dflash import DFlashDraftModel, _draft_layer_specs, draft_attention
 
 
 def _conv_specs(cfg: ModelConfig, prefix: str, taps: int, groups: int):
@@ -74,10 +74,7 @@ class DFlash2Layer(nn.Module):
         kv = linear(torch.cat([y, ctx], dim=0), self.w_kv)
         kv = qk_norm_rope(kv, pos_all, inv_freq, self.q_norm, self.k_norm, 0, c.num_key_value_heads, c.head_dim,
                           c.rms_norm_eps)
-        nk = kv.shape[0]
-        k = kv[:, : c.kv_dim].view(nk, c.num_key_value_heads, c.head_dim)
-        v = kv[:, c.kv_dim:].view(nk, c.num_key_value_heads, c.head_dim)
-        a = block_attention(q.view(nd, c.num_attention_heads, c.head_dim), k, v, mask)
+        a = draft_attention(q.view(nd, c.num_attention_heads, c.head_dim), kv, mask, c)
         h = h + self.attention_conv.finish(linear(a.reshape(nd, c.q_dim), self.w_o), k_attn)
         y2, _ = rmsnorm(h, self.post_norm, c.rms_norm_eps)
         y2, k_mlp = self.mlp_conv.prepare(y2)

@@ -24,9 +24,13 @@ from ..ops.linear_ce import linear_cross_entropy
 
 
 class DFlashTask:
-    def __init__(self, spec, cfg: ModelConfig, *, dtype, device, seed: int, dp_rank: int):
+    def __init__(self, spec, cfg: ModelConfig, *, dtype, device, seed: int, dp_rank: int, exchange=None,
+                 replicas: int | None = None):
+        """exchange: a parallel.dflash_context.DFlashContextParallel when one replica spans several ranks (they
+        divide the anchors and, with context parallelism, the context rows); replicas: data-parallel size."""
         m, o = spec.model, spec.objective
         self.spec, self.cfg, self.device = spec, cfg, device
+        self.exchange, self.replicas = exchange, replicas
         import os
         from dataclasses import replace
 
@@ -128,12 +132,26 @@ class DFlashTask:
         ob = self.objective.prepare(ids, batch.supervision_mask)
         feats = self.target_features(ids, batch)
         bs = self.objective.block_size
-        mask = dflash_mask_layout(ob, l, bs)
+        ex = self.exchange
+        if ex is None:
+            mask = dflash_mask_layout(ob, l, bs)
+            ctx_features = feats.hidden
+            pos_ctx = torch.arange(l, device=ids.device).repeat(b)
+        else:
+            # this rank's anchors of the (replica-wide identical) sample, and its shard of the context rows
+            from ..parallel.dflash_context import select_anchors
+
+            c = self.cfg
+            plan = ex.plan(ob, bs, l, q_heads=c.num_attention_heads, kv_heads=c.num_key_value_heads,
+                           head_dim=c.head_dim)
+            ob = select_anchors(ob, ex.anchor_index(ob.anchor_positions.shape[1], device=ids.device))
+            mask = (ex, plan)
+            ctx_features = feats.hidden.index_select(0, ex.context_rows(b, l, ids.device))
+            pos_ctx = ex.context_positions(l, device=ids.device).repeat(b)
         draft_tok = ob.draft_input_ids.reshape(-1)
         draft_emb = embedding(draft_tok, self.target.embed)
         pos_draft = ob.block_positions.reshape(-1)
-        pos_ctx = torch.arange(l, device=ids.device).repeat(b)
-        hidden = self.model(draft_emb, feats.hidden, pos_draft, pos_ctx, mask)
+        hidden = self.model(draft_emb, ctx_features, pos_draft, pos_ctx, mask)
         sup = ob.supervised_mask.reshape(-1)
         w = ob.position_weights.reshape(-1) * sup.float()
         rows = sup.nonzero(as_tuple=True)[0]
@@ -153,7 +171,13 @@ class DFlashTask:
             tgt = (ob.target_token_positions + seq_off).reshape(-1).index_select(0, rows)
             labels = ids.reshape(-1).index_select(0, tgt)
             loss_sum, _ = linear_cross_entropy(h_s, self.target.lm_head, labels, wr, frozen_weight=True)
-        denom = wr.sum().clamp_min(1.0) if denominator is None else denominator
+        if denominator is None:
+            wsum = wr.sum()
+            if ex is not None:            # the anchors of this micro-batch are spread over the replica's ranks
+                torch.distributed.all_reduce(wsum, group=ex.group)
+            denom = wsum.clamp_min(1.0)
+        else:
+            denom = denominator
         (loss_sum / denom).backward()
         return loss_sum.detach(), int(rows.numel()), denom
 
@@ -216,5 +240,5 @@ class DFlashTask:
         self.last_objective_metrics.update(target_probability=prob.mean(), selector_coverage=covered.float().mean())
         # the session averages per-rank losses over the ranks: dividing by (global count / ranks) makes that
         # average the global sum over the global count
-        denom = (stats[0] / world).clamp_min(torch.finfo(torch.float32).tiny)
+        denom = (stats[0] / (self.replicas or world)).clamp_min(torch.finfo(torch.float32).tiny)
         return token_num + self.effective_selector_loss_alpha * selector_num, denom

@@ -203,7 +203,15 @@ class TrainingSession:
         spec = self.spec
         dp_rank = runtime.data_parallel_rank if runtime is not None else self.rank
         self.dp_size = runtime.data_parallel_size if runtime is not None else self.world
-        self.task = DFlashTask(spec, self.cfg, dtype=self.dtype, device=self.device, seed=seed, dp_rank=dp_rank)
+        exchange = None
+        if runtime is not None and runtime.local_parallel_size > 1:
+            from ..parallel.dflash_context import DFlashContextParallel
+
+            exchange = DFlashContextParallel(runtime.group("local_parallel"),
+                                             context_sharded=runtime.context_parallel_size > 1,
+                                             mode=spec.kernel.dflash_context_exchange)
+        self.task = DFlashTask(spec, self.cfg, dtype=self.dtype, device=self.device, seed=seed, dp_rank=dp_rank,
+                               exchange=exchange, replicas=self.dp_size if runtime is not None else None)
         self.model, self.objective = self.task.model, self.task.objective
         tcfg = self.task.target.cfg
         if self.task.feature_store is not None:
