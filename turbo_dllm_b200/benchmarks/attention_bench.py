@@ -5,6 +5,12 @@
 FLOPs are counted on the exactly visible query-key pairs (4·pairs·D per head forward,
 10·pairs·D backward), the convention of the reference's exact attention-pair counters
 (dllm_parallel/core/profiling/perf.py:872-878). Prints one JSON line.
+
+`--baseline flex|sdpa` times the same mask, shapes and call through a stock PyTorch path on the same device, so
+that the kernels have an anchor: `flex` is torch FlexAttention with a block mask built from the same codes
+(it compiles its kernels with Triton; when that is not possible on the box the run falls back to `sdpa` and says
+so), `sdpa` is scaled_dot_product_attention with the dense boolean mask (rows² bytes: keep --seq at 8192 or so).
+The baseline is timed here only; nothing in the package calls it.
 """
 from __future__ import annotations
 
@@ -29,6 +35,8 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--fwd-only", action="store_true")
     ap.add_argument("--bwd-modes", default="fused,split", help="backward variants to time (TDLLM_ATTN_BWD values)")
+    ap.add_argument("--baseline", default="none", choices=("none", "sdpa", "flex"),
+                    help="also time the same mask through stock PyTorch attention")
     args = ap.parse_args(argv)
     D = 128
     dev = "cuda"
@@ -79,7 +87,61 @@ def main(argv=None):
             bwd_ms = timeit(lambda: attention_backward_native(q, k, v, out, dout, lse, layout, scale, dqkv))
             rec[f"bwd_{mode}_ms"] = round(bwd_ms, 3)
             rec[f"bwd_{mode}_tflops_exact_pairs"] = round(10.0 * pairs * D * args.heads / bwd_ms / 1e9, 1)
+    if args.baseline != "none":
+        rec.update(_baseline(args.baseline, layout, q, k, v, scale, timeit, pairs, D, args.heads))
+        if "baseline_fwd_ms" in rec:
+            rec["fwd_speedup_vs_baseline"] = round(rec["baseline_fwd_ms"] / fwd_ms, 2)
+            best = min((rec[f"bwd_{m}_ms"] for m in args.bwd_modes.split(",") if f"bwd_{m}_ms" in rec), default=None)
+            if best and "baseline_bwd_ms" in rec:
+                rec["bwd_speedup_vs_baseline"] = round(rec["baseline_bwd_ms"] / best, 2)
     print(json.dumps(rec), flush=True)
+
+
+def _baseline(kind, layout, q, k, v, scale, timeit, pairs, D, heads):
+    """Forward and backward of stock PyTorch attention under the same mask. q [n, Hq, D], k/v [n, Hkv, D]."""
+    import torch.nn.functional as F
+
+    n = q.shape[0]
+    qb = q.permute(1, 0, 2)[None].contiguous().requires_grad_()      # [1, H, n, D]
+    kb = k.permute(1, 0, 2)[None].contiguous().requires_grad_()
+    vb = v.permute(1, 0, 2)[None].contiguous().requires_grad_()
+    note = {}
+    fn = None
+    if kind == "flex":
+        try:
+            from torch.nn.attention.flex_attention import create_block_mask, flex_attention
+
+            lo, hi, grp, code = (t.long() for t in (layout.q_lo, layout.q_hi, layout.q_grp, layout.k_code))
+
+            def visible(b, h, qi, ki):
+                c = code[ki]
+                return torch.where(c >= 0, (c >= lo[qi]) & (c < hi[qi]), c == grp[qi])
+
+            bm = create_block_mask(visible, None, None, n, n, device=q.device)
+            compiled = torch.compile(flex_attention)
+            fn = lambda: compiled(qb, kb, vb, block_mask=bm, scale=scale, enable_gqa=True)
+            fn()
+            torch.cuda.synchronize()
+        except Exception as e:      # no Triton tool chain for this device, or the compile failed
+            note["baseline_flex_unavailable"] = f"{type(e).__name__}: {str(e)[:160]}"
+            fn, kind = None, "sdpa"
+    if fn is None:
+        dense = layout.dense_mask()[None, None]
+        fn = lambda: F.scaled_dot_product_attention(qb, kb, vb, attn_mask=dense, scale=scale, enable_gqa=True)
+    out = fn()
+    dout = torch.randn_like(out)
+    fwd = timeit(lambda: fn())
+
+    def fwd_bwd():
+        o = fn()
+        o.backward(dout)
+        qb.grad = kb.grad = vb.grad = None
+
+    both = timeit(fwd_bwd)
+    bwd = max(both - fwd, 1e-6)
+    return {**note, "baseline": kind, "baseline_fwd_ms": round(fwd, 3), "baseline_bwd_ms": round(bwd, 3),
+            "baseline_fwd_tflops_exact_pairs": round(4.0 * pairs * D * heads / fwd / 1e9, 1),
+            "baseline_bwd_tflops_exact_pairs": round(10.0 * pairs * D * heads / bwd / 1e9, 1)}
 
 
 if __name__ == "__main__":

@@ -1,7 +1,8 @@
 """Compares the three ways of spreading one long sequence over W ranks, with identical settings:
 
-* `pure_cp`   : context parallelism W (clean K/V sharded, every rank computes all noisy blocks' rows it owns
-                under the context layout),
+* `pure_cp`   : context parallelism W: clean K/V sharded and the tokens INSIDE every noisy block divided over the
+                ranks (two-ended), all K/V rows exchanged (`pure_cp_replicated`: the variant that keeps every
+                noisy block whole on every rank, W-fold redundant noisy work, for comparison),
 * `pure_bp`   : block parallelism W with a replicated clean prefix (no K/V exchange, redundant clean work),
 * `csbp`      : context-sharded block parallelism, CP = BP = W (the fused layout).
 
@@ -28,17 +29,22 @@ import torch.distributed as dist
 
 MODES = {
     "pure_cp": lambda w: {"context_parallel_size": w, "block_parallel_size": 1, "replicate_clean_prefix": False},
+    "pure_cp_replicated": lambda w: {"context_parallel_size": w, "block_parallel_size": 1,
+                                     "replicate_clean_prefix": False},
     "pure_bp": lambda w: {"context_parallel_size": 1, "block_parallel_size": w, "replicate_clean_prefix": True},
     "csbp": lambda w: {"context_parallel_size": w, "block_parallel_size": w, "replicate_clean_prefix": False},
 }
 
 
-def run_mode(spec, mode: str, *, device, steps: int, warmup: int) -> dict:
+def run_mode(spec, mode: str, *, device, steps: int, warmup: int, transport: str | None = None) -> dict:
     from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
     from turbo_dllm_b200.training.session import TrainingSession
 
     world = dist.get_world_size()
-    s = spec.with_overrides({"topology": MODES[mode](world)}).validate(world_size=world)
+    kernel = {"pure_cp_token_split": mode != "pure_cp_replicated"}
+    if transport:
+        kernel["cp_bp_clean_kv_transport"] = transport
+    s = spec.with_overrides({"topology": MODES[mode](world), "kernel": kernel}).validate(world_size=world)
     rt = build_parallel_runtime(s, device=device)
     session = TrainingSession(s, device=device, runtime=rt)
     cuda = torch.device(device).type == "cuda"
@@ -67,7 +73,7 @@ def run_mode(spec, mode: str, *, device, steps: int, warmup: int) -> dict:
     loss = last.loss_sum.double().clone()
     dist.all_reduce(loss)
     tokens = s.model.seq_len * s.training.batch_size * rt.data_parallel_size
-    out = {"mode": mode, "world": world, "topology": MODES[mode](world), "ms_per_step": round(float(stats[0]), 3),
+    out = {"mode": mode, "world": world, "transport": s.kernel.cp_bp_clean_kv_transport, "topology": MODES[mode](world), "ms_per_step": round(float(stats[0]), 3),
            "input_tokens_per_s": round(tokens / float(stats[0]) * 1e3, 1), "peak_mib": round(float(stats[1]), 1),
            "loss": float(loss) / last.denominator, "seq_len": s.model.seq_len, "steps": steps, "warmup": warmup}
     session.close()
@@ -82,7 +88,9 @@ def main(argv=None) -> int:
 
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", required=True)
-    ap.add_argument("--modes", nargs="+", default=list(MODES), choices=list(MODES))
+    ap.add_argument("--modes", nargs="+", default=["pure_cp", "pure_bp", "csbp"], choices=list(MODES))
+    ap.add_argument("--transport", default=None, choices=("collective", "fused"),
+                    help="clean K/V transport of the context-parallel modes (default: the config's)")
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--seq-len", type=int, default=None)
@@ -100,7 +108,7 @@ def main(argv=None) -> int:
     if a.seq_len:
         spec = spec.with_overrides({"model": {"seq_len": a.seq_len}})
     for mode in a.modes:
-        rec = run_mode(spec, mode, device=device, steps=a.steps, warmup=a.warmup)
+        rec = run_mode(spec, mode, device=device, steps=a.steps, warmup=a.warmup, transport=a.transport)
         if rank == 0:
             print(json.dumps(rec), flush=True)
     if own:

@@ -11,12 +11,13 @@
 //
 // Fused optimizer step (one process per GPU, each rank owns one contiguous shard of the flat
 // parameter / gradient buffers):
-//   zero_reduce_kernel : reduce-scatter by pulling — sums the shard's gradient slice from every
-//                        peer (bf16 -> fp32), stores the sum to the local gradient buffer and
-//                        accumulates Σ g² for the global norm
-//   zero_update_kernel : reads every rank's Σ g², clips, applies AdamW to the fp32 master shard
-//                        and all-gathers by pushing — writes the new bf16 parameters into every
-//                        peer's parameter buffer
+//   zero_reduce_kernel : norm pass — sums the shard's gradient slice from every peer (bf16 -> fp32) and
+//                        accumulates Σ g² of the sums for the global norm; the sums are not stored
+//   zero_update_kernel : reads every rank's Σ g², sums the shard's slice from every peer again in fp32 (the
+//                        gradient AdamW sees is never rounded to bf16), clips, applies AdamW to the fp32
+//                        master shard and all-gathers by pushing — writes the new bf16 parameters into
+//                        every peer's parameter buffer. The peers' gradient buffers stay untouched until the
+//                        closing barrier.
 // This replaces reduce-scatter + FusedAdam + all-gather of DeepSpeed ZeRO-2 / FSDP in the
 // reference (dllm_parallel/core/optim/zero.py:93-211, :402-462; dllm_parallel/core/optim/fsdp.py:56-114).
 #include <cstring>
@@ -75,12 +76,8 @@ __global__ void zero_reduce_kernel(PeerPtrs grads, int rank, int world, long lon
       const uint4 v = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)grads.p[r] + start + i * 8);
       acc8(v, f);
     }
-    uint4 o;
-    o.x = pack_bf16x2(f[0], f[1]);
-    o.y = pack_bf16x2(f[2], f[3]);
-    o.z = pack_bf16x2(f[4], f[5]);
-    o.w = pack_bf16x2(f[6], f[7]);
-    *reinterpret_cast<uint4*>((__nv_bfloat16*)grads.p[rank] + start + i * 8) = o;
+    // the sum itself is not stored: rounding it to bf16 would cost the update 8 bits, and an fp32 copy would
+    // cost 4 bytes per shard element; zero_update_kernel sums the same values again in fp32
 #pragma unroll
     for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
   }
@@ -99,7 +96,7 @@ __global__ void zero_reduce_kernel(PeerPtrs grads, int rank, int world, long lon
 // sumsq.p[r] = address of rank r's Σ g² scalar (symmetric memory). params.p[r] = rank r's flat
 // parameter buffer. [start, start+n) is this rank's shard; decay applies to global element
 // indices below decay_end.
-__global__ void zero_update_kernel(PeerPtrs params, PeerPtrs sumsq, const __nv_bfloat16* grad_local,
+__global__ void zero_update_kernel(PeerPtrs params, PeerPtrs sumsq, PeerPtrs grads,
                                    float* master, float* m, float* v, int rank, int world,
                                    long long start, long long n, long long decay_end, float lr,
                                    float beta1, float beta2, float eps, float wd, float bias1,
@@ -117,15 +114,15 @@ __global__ void zero_update_kernel(PeerPtrs params, PeerPtrs sumsq, const __nv_b
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
        i += (long long)gridDim.x * blockDim.x) {
     const long long e0 = i * 8;
-    const uint4 gv = *reinterpret_cast<const uint4*>(grad_local + start + e0);
-    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
-    float g[8];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 t = __bfloat1622float2(gh[j]);
-      g[2 * j] = t.x * gs;
-      g[2 * j + 1] = t.y * gs;
+    // Σ over ranks of the bf16 gradients, in fp32, in the order zero_reduce_kernel used for the norm
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+    for (int k = 0; k < world; ++k) {
+      const int r = (rank + 1 + k) % world;
+      acc8(*reinterpret_cast<const uint4*>((const __nv_bfloat16*)grads.p[r] + start + e0), g);
     }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j] *= gs;
     float p[8], mm[8], vv[8];
     *reinterpret_cast<float4*>(p) = *reinterpret_cast<const float4*>(master + e0);
     *reinterpret_cast<float4*>(p + 4) = *reinterpret_cast<const float4*>(master + e0 + 4);
@@ -425,7 +422,7 @@ extern "C" int tdllm_zero_fused_step(void* const* grad_ptrs, void* const* param_
     const float bias1 = 1.f - powf(beta1, (float)step);
     const float bias2 = 1.f - powf(beta2, (float)step);
     comm::zero_update_kernel<<<(unsigned)blocks, threads, 0, st>>>(
-        p, s, (const __nv_bfloat16*)grad_ptrs[rank], master, m, v, rank, world, start, n, decay_end,
+        p, s, g, master, m, v, rank, world, start, n, decay_end,
         lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale, max_norm, norm_out);
   }
   comm::barrier_kernel<<<1, 32, 0, st>>>(f, rank, world, epoch + 2);
