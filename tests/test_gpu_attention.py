@@ -139,3 +139,60 @@ def test_backward_ragged_sparse_keys(mode, monkeypatch):
     kpos = pos[(pos // 50) % 2 == 1]
     layout = block_diffusion_layout(act, act // bs, pos[:333], bs, key_clean_pos=kpos)
     _run_bwd(layout, act.numel() + 333, act.numel() + kpos.numel(), 4, 2)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(256, 4, 2), (512, 2, 1), (64, 4, 2), (256, 3, 1)])
+def test_wide_and_narrow_heads_run_as_products_around_the_softmax_kernel(D, Hq, Hkv):
+    """head_dim 256 / 512 (and 64): tcgen05 products around the masked-softmax kernels, forward and backward,
+    against the dense fp32 reference: ragged row count, two noisy views, rows without any visible key."""
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.ops.attention import attention_reference, block_attention, single_sequence_layout
+    from turbo_dllm_b200.ops.wide_attention import wide_attention_forward
+
+    torch.manual_seed(D)
+    layout = single_sequence_layout(320, 32, "cuda", 2)            # 960 rows: 7.5 tiles
+    n = 960
+    q = (torch.randn(n, Hq, D, device="cuda") * 0.5).bfloat16().requires_grad_()
+    k = (torch.randn(n, Hkv, D, device="cuda") * 0.5).bfloat16().requires_grad_()
+    v = (torch.randn(n, Hkv, D, device="cuda") * 0.5).bfloat16().requires_grad_()
+    scale = 1.0 / math.sqrt(D)
+    out = block_attention(q, k, v, layout, scale)
+    go = torch.randn_like(out)
+    out.backward(go)
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref, ref_lse = attention_reference(qr, kr, vr, layout, scale)
+    ref.backward(go.float())
+    assert (out.float() - ref).abs().max().item() < 3e-2
+    for got, want in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
+        assert (got.float() - want).abs().max().item() < 4e-2 * max(want.abs().max().item(), 1.0)
+    _, lse = wide_attention_forward(q.detach(), k.detach(), v.detach(), layout, scale)
+    fin = torch.isfinite(ref_lse)
+    assert torch.equal(torch.isfinite(lse), fin)
+    assert (lse[fin] - ref_lse[fin]).abs().max().item() < 2e-2
+
+
+def test_model_with_head_dim_256_trains_on_the_gpu():
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    def spec(dtype):
+        return RunSpec.from_mapping({
+            "model": {"id": "wide", "random_init": True, "seq_len": 512, "dtype": dtype, "vocab_size": 2048,
+                      "hidden_size": 512, "num_layers": 2, "num_attention_heads": 2, "num_key_value_heads": 1,
+                      "head_dim": 256, "intermediate_size": 1024, "sliding_window": 128, "sliding_window_pattern": 2},
+            "objective": {"name": "standard_block_diffusion", "block_size": 32, "sampling_epsilon_min": 0.1},
+            "training": {"batch_size": 2, "steps": 2},
+            "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
+            "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate()
+
+    g = TrainingSession(spec("bf16"), device="cuda")
+    c = TrainingSession(spec("fp32"), device="cpu")
+    c.model.flat.data.copy_(g.model.flat.data.float().cpu())
+    rg, rc = g.step(), c.step()
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    lg, lc = float(rg.loss_sum) / rg.denominator, float(rc.loss_sum) / rc.denominator
+    assert lg == pytest.approx(lc, rel=3e-2)

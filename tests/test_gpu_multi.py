@@ -66,10 +66,11 @@ def _train(rank, world, backend, steps):
 
 
 @pytest.mark.distributed
-def test_fused_zero_matches_nccl_twin():
-    _need(2)
-    a = run_ranks(_train, 2, args=("nccl", 3), backend="nccl", deadline_s=300)
-    b = run_ranks(_train, 2, args=("fused", 3), backend="nccl", deadline_s=300)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_zero_matches_nccl_twin(world):
+    _need(world)
+    a = run_ranks(_train, world, args=("nccl", 3), backend="nccl", deadline_s=300)
+    b = run_ranks(_train, world, args=("fused", 3), backend="nccl", deadline_s=300)
     for (la, pa, na), (lb, pb, nb) in zip(a, b):
         assert la == pytest.approx(lb, rel=2e-2)
         assert na == pytest.approx(nb, rel=2e-2)
@@ -467,9 +468,10 @@ def _fused_allreduce_gemm(rank, world):
 
 
 @pytest.mark.distributed
-def test_gemm_with_allreduce_epilogue_over_peer_memory():
-    _need(2)
-    for errs in run_ranks(_fused_allreduce_gemm, 2, backend="nccl", deadline_s=300):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_gemm_with_allreduce_epilogue_over_peer_memory(world):
+    _need(world)
+    for errs in run_ranks(_fused_allreduce_gemm, world, backend="nccl", deadline_s=300):
         assert max(errs) < 2e-2, errs
 
 
@@ -505,9 +507,10 @@ def _ce_exchange(rank, world):
 
 
 @pytest.mark.distributed
-def test_cross_entropy_statistics_exchange_over_peer_memory():
-    _need(2)
-    for errs in run_ranks(_ce_exchange, 2, backend="nccl", deadline_s=300):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_cross_entropy_statistics_exchange_over_peer_memory(world):
+    _need(world)
+    for errs in run_ranks(_ce_exchange, world, backend="nccl", deadline_s=300):
         assert max(errs) < 1e-3, errs
 
 

@@ -82,6 +82,18 @@ int tdllm_swiglu_fwd(const void* gu, void* out, long long rows, int inter, void*
 int tdllm_swiglu_bwd(const void* dy, const void* gu, void* dgu, long long rows, int inter,
                      void* stream);
 
+// ---- wide-head attention: the masked softmax between the tensor-core products ----
+// S fp32 [R, N] (row stride lds) -> P bf16 [R, N] (row stride ldp), lse [R]. Row r uses the mask entries of
+// query (r % rows_per_head).
+int tdllm_wide_softmax(const void* S, void* P, void* lse, const int* q_lo, const int* q_hi, const int* q_grp,
+                       const int* k_code, long long R, int rows_per_head, int N, long long lds, long long ldp,
+                       float scale, void* stream);
+// P = exp(S*scale - lse) under the mask, dS = P * (dP - delta) * scale (both bf16, row stride ldp).
+int tdllm_wide_softmax_bwd(const void* S, const void* dP, void* P, void* dS, const void* lse,
+                           const void* delta, const int* q_lo, const int* q_hi, const int* q_grp,
+                           const int* k_code, long long R, int rows_per_head, int N, long long lds,
+                           long long ldp, float scale, void* stream);
+
 // ---- optimizer / loss reductions / attention-state merge -------------------
 int tdllm_sumsq_bf16(const void* g, long long n, float* out, void* stream);
 int tdllm_adamw(float* master, float* m, float* v, const void* grad, void* param, long long n,

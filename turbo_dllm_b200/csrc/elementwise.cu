@@ -484,8 +484,16 @@ extern "C" int tdllm_qk_norm_rope_fwd(const void* in, void* out, const int* pos,
     ew::qk_norm_rope_fwd_kernel<64><<<grid, 256, 0, s>>>(
         (const __nv_bfloat16*)in, (__nv_bfloat16*)out, pos, inv_freq, (const __nv_bfloat16*)qw,
         (const __nv_bfloat16*)kw, rows, Hq, Hkv, eps);
+  else if (D == 256)
+    ew::qk_norm_rope_fwd_kernel<256><<<grid, 256, 0, s>>>(
+        (const __nv_bfloat16*)in, (__nv_bfloat16*)out, pos, inv_freq, (const __nv_bfloat16*)qw,
+        (const __nv_bfloat16*)kw, rows, Hq, Hkv, eps);
+  else if (D == 512)
+    ew::qk_norm_rope_fwd_kernel<512><<<grid, 256, 0, s>>>(
+        (const __nv_bfloat16*)in, (__nv_bfloat16*)out, pos, inv_freq, (const __nv_bfloat16*)qw,
+        (const __nv_bfloat16*)kw, rows, Hq, Hkv, eps);
   else {
-    tdllm_host::set_last_error("qk_norm_rope: head_dim must be 64 or 128");
+    tdllm_host::set_last_error("qk_norm_rope: head_dim must be 64, 128, 256 or 512");
     return 1;
   }
   TD_CHECK_LAUNCH("qk_norm_rope_fwd");
@@ -513,8 +521,16 @@ extern "C" int tdllm_qk_norm_rope_bwd(const void* dout, const void* in_raw, void
     ew::qk_norm_rope_bwd_kernel<64><<<grid, 256, 0, s>>>(
         (const __nv_bfloat16*)dout, (const __nv_bfloat16*)in_raw, (__nv_bfloat16*)din, pos,
         inv_freq, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, part, rows, Hq, Hkv, eps);
+  else if (D == 256)
+    ew::qk_norm_rope_bwd_kernel<256><<<grid, 256, 0, s>>>(
+        (const __nv_bfloat16*)dout, (const __nv_bfloat16*)in_raw, (__nv_bfloat16*)din, pos,
+        inv_freq, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, part, rows, Hq, Hkv, eps);
+  else if (D == 512)
+    ew::qk_norm_rope_bwd_kernel<512><<<grid, 256, 0, s>>>(
+        (const __nv_bfloat16*)dout, (const __nv_bfloat16*)in_raw, (__nv_bfloat16*)din, pos,
+        inv_freq, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, part, rows, Hq, Hkv, eps);
   else {
-    tdllm_host::set_last_error("qk_norm_rope: head_dim must be 64 or 128");
+    tdllm_host::set_last_error("qk_norm_rope: head_dim must be 64, 128, 256 or 512");
     return 1;
   }
   TD_CHECK_LAUNCH("qk_norm_rope_bwd");

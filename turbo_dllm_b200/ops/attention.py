@@ -360,8 +360,13 @@ def block_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layout: M
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if use_native(q, k, v) and q.shape[-1] == 128:
         return _BlockAttention.apply(q, k, v, layout, scale)
+    if use_native(q, k, v) and q.shape[-1] != 128 and q.shape[-1] % 64 == 0:
+        from .wide_attention import wide_block_attention
+
+        return wide_block_attention(q, k, v, layout, scale)
     if q.is_cuda and q.dtype == torch.bfloat16:
-        raise native.NativeKernelError("bf16 CUDA attention needs head_dim 128 (no silent fallback)")
+        raise native.NativeKernelError("bf16 CUDA attention needs head_dim 128 or another multiple of 64 "
+                                       "(no silent fallback)")
     return attention_reference(q, k, v, layout, scale)[0]
 
 
@@ -420,7 +425,14 @@ def packed_block_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, layout:
                 pre = (store.fetch(ko), store.fetch(kl))
                 return _PackedBlockAttention.apply(qkv, Hq, Hkv, D, layout, scale, pre)
         return _PackedBlockAttention.apply(qkv, Hq, Hkv, D, layout, scale)
+    if use_native(qkv) and D != 128 and D % 64 == 0:
+        # other head widths (64, 256, 512): tensor-core products around a masked softmax kernel (ops/wide_attention.py)
+        from .wide_attention import wide_block_attention
+
+        q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
+        return wide_block_attention(q, k, v, layout, scale).reshape(qkv.shape[0], Hq * D)
     if qkv.is_cuda and qkv.dtype == torch.bfloat16:
-        raise native.NativeKernelError("bf16 CUDA attention needs head_dim 128 (no silent fallback)")
+        raise native.NativeKernelError("bf16 CUDA attention needs head_dim 128 or another multiple of 64 "
+                                       "(no silent fallback)")
     q, k, v = split_packed_qkv(qkv, Hq, Hkv, D)
     return attention_reference(q, k, v, layout, scale)[0].reshape(qkv.shape[0], Hq * D)
