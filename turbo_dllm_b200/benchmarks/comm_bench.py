@@ -13,6 +13,9 @@ and direction, divided by the measured peer-copy bandwidth of this pool (770 GB/
   HBM traffic) runs between the two.
 * clean K|V gather (`tdllm_kv_gather`): every rank pulls the other ranks' rows once.
 * its NCCL twins (`reduce_scatter` + `all_gather`, `all_gather`) on the same sizes.
+* sequence-parallel forms: all-gather -> GEMM with the pull inside the kernel (`tdllm_gemm_allgather_bf16`) and
+  GEMM -> reduce-scatter from the epilogue (`tdllm_gemm_reduce_scatter_bf16`) against NCCL + GEMM; expert
+  dispatch + combine over peer memory (`csrc/moe_dispatch.cu`) against the all-to-all twin.
 * row-parallel GEMM with the all-reduce in its epilogue (`tdllm_gemm_allreduce_bf16`) against the same GEMM
   followed by an NCCL all-reduce; its roofline is the slower of FLOPs ÷ measured GEMM peak and pushed bytes ÷ 770 GB/s.
 """
@@ -161,6 +164,108 @@ def main(argv=None):
                     "roofline_ms": round(roof, 3), "fraction_of_roofline": round(roof / ms_f, 3),
                     "bound": "compute" if flops / (peaks_tflops * 1e12) > link / (PEER_GBS * 1e9) else "nvlink"})
     ws.close()
+    torch.cuda.empty_cache()
+
+    # ---- sequence-parallel forms: all-gather -> GEMM (remote rows pulled inside the GEMM kernel) and
+    #      GEMM -> reduce-scatter (partial tiles pushed to their owner from the epilogue) against NCCL + GEMM
+    from turbo_dllm_b200.parallel.fused_sequence_parallel import FusedSequenceParallel
+
+    H = args.tp_hidden
+    Mr = (args.tp_rows // (256 * world)) * 256 * world
+    sp = FusedSequenceParallel(group, dev, Mr, H)
+    for k_full in args.tp_k:
+        Nl = k_full // world                       # column-parallel width per rank (QKV or gate/up shard)
+        x_loc = (torch.randn(Mr // world, H, device=dev) * 0.5).bfloat16()
+        w_col = (torch.randn(Nl, H, device=dev) * 0.05).bfloat16()
+        ms_ag = _time(lambda: sp.gather_matmul(x_loc, w_col), args.iters, args.warmup)
+        native.raise_on_device_error()
+        full = torch.empty(Mr, H, device=dev, dtype=torch.bfloat16)
+
+        def ag_twin():
+            dist.all_gather_into_tensor(full, x_loc, group=group)
+            return gemm(full, w_col)
+
+        ms_ag_n = _time(ag_twin, args.iters, args.warmup)
+        flops = 2.0 * Mr * Nl * H
+        link = (world - 1) * (Mr // world) * H * 2
+        roof = max(flops / (peaks_tflops * 1e12), link / (PEER_GBS * 1e9)) * 1e3
+        out.append({"kernel": "allgather_gemm (peer pull by extra warps of the tcgen05 GEMM)", "world": world,
+                    "shape": f"{Mr}x{Nl}x{H} per rank", "ms": round(ms_ag, 3), "nccl_allgather_plus_gemm_ms": round(ms_ag_n, 3),
+                    "tflops_per_gpu": round(flops / ms_ag / 1e9, 1), "nvlink_bytes_in": link, "roofline_ms": round(roof, 3),
+                    "fraction_of_roofline": round(roof / ms_ag, 3),
+                    "bound": "compute" if flops / (peaks_tflops * 1e12) > link / (PEER_GBS * 1e9) else "nvlink"})
+        a_row = (torch.randn(Mr, Nl, device=dev) * 0.5).bfloat16()           # row-parallel input [rows, K/W]
+        w_row = (torch.randn(H, Nl, device=dev) * 0.05).bfloat16()
+        res = torch.randn(Mr // world, H, device=dev).bfloat16()
+        ms_rs = _time(lambda: sp.matmul_scatter(a_row, w_row, residual=res), args.iters, args.warmup)
+        native.raise_on_device_error()
+        shard = torch.empty(Mr // world, H, device=dev, dtype=torch.bfloat16)
+
+        def rs_twin():
+            dist.reduce_scatter_tensor(shard, gemm(a_row, w_row), group=group)
+            return shard.add_(res)
+
+        ms_rs_n = _time(rs_twin, args.iters, args.warmup)
+        flops = 2.0 * Mr * H * Nl
+        link = (world - 1) * (Mr // world) * H * 2
+        roof = max(flops / (peaks_tflops * 1e12), link / (PEER_GBS * 1e9)) * 1e3
+        out.append({"kernel": "gemm_reduce_scatter (tcgen05 tiles pushed to their owner from the epilogue)",
+                    "world": world, "shape": f"{Mr}x{H}x{Nl} per rank", "ms": round(ms_rs, 3),
+                    "gemm_plus_nccl_reduce_scatter_ms": round(ms_rs_n, 3), "tflops_per_gpu": round(flops / ms_rs / 1e9, 1),
+                    "nvlink_bytes_out": link, "roofline_ms": round(roof, 3), "fraction_of_roofline": round(roof / ms_rs, 3),
+                    "bound": "compute" if flops / (peaks_tflops * 1e12) > link / (PEER_GBS * 1e9) else "nvlink"})
+        del x_loc, w_col, full, a_row, w_row, res, shard
+    sp.close()
+    torch.cuda.empty_cache()
+
+    # ---- expert dispatch + combine over peer memory against the all-to-all twin (same routing, no expert math)
+    from turbo_dllm_b200.models.moe import _AllToAllRows
+    from turbo_dllm_b200.parallel.expert_exchange import PeerExpertExchange, peer_combine, peer_dispatch
+
+    rows, Hm, E, topk = 16384, 2048, 8 * world, 4
+    torch.manual_seed(1234 + rank)
+    xm = (torch.randn(rows, Hm, device=dev) * 0.5).bfloat16()
+    idx = torch.stack([torch.randperm(E, device=dev)[:topk] for _ in range(64)]).repeat(rows // 64, 1)
+    wts = torch.full((rows, topk), 1.0 / topk, device=dev)
+    exm = PeerExpertExchange(group, dev, rows=rows, top_k=topk, hidden=Hm, num_experts=E)
+    flat32 = idx.reshape(-1).to(torch.int32).contiguous()
+
+    def ep_peer():
+        with torch.no_grad():
+            st: dict = {}
+            x_pad = peer_dispatch(xm, flat32, exm, st)
+            return peer_combine(x_pad, wts, exm, st)
+
+    ms_ep = _time(ep_peer, args.iters, args.warmup)
+    native.raise_on_device_error()
+    el = E // world
+
+    def ep_twin():
+        with torch.no_grad():
+            flat_e = idx.reshape(-1)
+            order = torch.argsort(flat_e, stable=True)
+            token_of = torch.div(order, topk, rounding_mode="floor")
+            x_perm = xm.index_select(0, token_of)
+            counts_g = torch.bincount(flat_e, minlength=E)
+            allc = torch.empty(world, E, dtype=counts_g.dtype, device=dev)
+            dist.all_gather_into_tensor(allc.view(-1), counts_g, group=group)
+            mine = allc[:, rank * el:(rank + 1) * el]
+            sizes = torch.cat([counts_g.view(world, el).sum(1), mine.sum(1)]).tolist()
+            recv = _AllToAllRows.apply(x_perm, sizes[:world], sizes[world:], group)
+            back = _AllToAllRows.apply(recv, sizes[world:], sizes[:world], group)
+            outm = torch.zeros_like(xm)
+            outm.index_add_(0, token_of, back * wts.reshape(-1).index_select(0, order).to(back.dtype)[:, None])
+            return outm
+
+    ms_ep_n = _time(ep_twin, args.iters, args.warmup)
+    link = rows * topk * Hm * 2 * (world - 1) / world          # per direction, dispatch; the same again for combine
+    out.append({"kernel": "expert dispatch + combine (peer stores into owner slabs, pull-combine)", "world": world,
+                "rows": rows, "top_k": topk, "hidden": Hm, "experts": E, "ms": round(ms_ep, 3),
+                "all_to_all_twin_ms": round(ms_ep_n, 3), "nvlink_bytes_each_way": link,
+                "roofline_ms": round(2 * link / (PEER_GBS * 1e9) * 1e3, 3),
+                "fraction_of_roofline": round(2 * link / (PEER_GBS * 1e9) * 1e3 / ms_ep, 3),
+                "note": "roofline = dispatched rows out, then combined rows back, each at 770 GB/s per direction"})
+    exm.close()
     if rank == 0:
         for rec in out:
             print(json.dumps(rec), flush=True)

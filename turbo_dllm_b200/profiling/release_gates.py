@@ -63,9 +63,15 @@ def gate_sm100_only_flags() -> GateResult:
     return GateResult("sm100_only_flags", archs == {("100a", "100a")}, f"arch flags: {sorted(archs)}")
 
 
+# the one place a tracing compiler may appear: the stock-PyTorch baseline column of the attention benchmark,
+# which times FlexAttention next to this library's kernels and is called by nothing in the package
+BASELINE_ONLY = {"benchmarks/attention_bench.py"}
+
+
 def gate_no_compat_layers() -> GateResult:
     pat = re.compile(r"^\s*(import triton|from triton|import tilelang|from tilelang)|torch\.compile\(", re.M)
-    hits = [str(p.relative_to(PKG)) for p in _py_files() if pat.search(p.read_text()) and p.name != "release_gates.py"]
+    hits = [str(p.relative_to(PKG)) for p in _py_files() if pat.search(p.read_text()) and p.name != "release_gates.py"
+            and str(p.relative_to(PKG)) not in BASELINE_ONLY]
     return GateResult("no_compat_layers", not hits, f"offenders: {hits}")
 
 

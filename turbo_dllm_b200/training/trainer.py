@@ -141,8 +141,9 @@ def run_training(spec: RunSpec) -> dict:
         for step in range(start_step + 1, total_steps + 1):
             if use_cuda:
                 torch.cuda.reset_peak_memory_stats(device)
-            t0 = time.perf_counter()
             trace.begin_step(step)
+            traced = trace.active          # a step under the profiler pays for the tracing: it is not timed
+            t0 = time.perf_counter()
             res = session.step()
             readback.enqueue(res.loss_sum, int(res.supervised_rows), tp_replicas)
             if use_cuda:
@@ -157,7 +158,7 @@ def run_training(spec: RunSpec) -> dict:
             last_loss = loss_sum / res.denominator
             if last_loss != last_loss or abs(last_loss) == float("inf"):
                 raise FloatingPointError(f"non-finite loss at step {step}: {last_loss}")
-            timed = step - start_step > spec.profiler.warmup_steps
+            timed = step - start_step > spec.profiler.warmup_steps and not traced
             if timed:
                 timed_ms.append(ms)
             # drafter distillation normalises per micro-batch (denominator 1): its supervised count is the rows
