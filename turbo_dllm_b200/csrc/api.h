@@ -182,7 +182,7 @@ int tdllm_zero_fused_step(void* const* grad_ptrs, void* const* param_ptrs, void*
                           void* const* flag_ptrs, float* master, float* m, float* v, int rank,
                           int world, long long start, long long n, long long decay_end, float lr,
                           float beta1, float beta2, float eps, float wd, int step, float grad_scale,
-                          float max_norm, float* norm_out, int epoch, void* stream);
+                          float max_norm, float* norm_out, int epoch, float* reduced, void* stream);
 
 // Parameter sharding: materialise a unit from the ranks' bf16 shards / reduce a unit's bf16 gradients into this
 // rank's fp32 shard (see comm.cu).

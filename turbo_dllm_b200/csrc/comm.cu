@@ -64,7 +64,7 @@ __device__ __forceinline__ void acc8(const uint4& v, float* f) {
 
 // grads.p[r] = base of rank r's flat gradient buffer. Elements [start, start+n) are this rank's shard.
 __global__ void zero_reduce_kernel(PeerPtrs grads, int rank, int world, long long start, long long n,
-                                   float* sumsq_out) {
+                                   float* sumsq_out, float* __restrict__ reduced) {
   float ss = 0.f;
   const long long n8 = n / 8;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
@@ -76,8 +76,12 @@ __global__ void zero_reduce_kernel(PeerPtrs grads, int rank, int world, long lon
       const uint4 v = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)grads.p[r] + start + i * 8);
       acc8(v, f);
     }
-    // the sum itself is not stored: rounding it to bf16 would cost the update 8 bits, and an fp32 copy would
-    // cost 4 bytes per shard element; zero_update_kernel sums the same values again in fp32
+    // the sum is never rounded to bf16: it is kept in fp32 when the caller gave a shard-sized scratch
+    // (4 bytes per shard element), otherwise zero_update_kernel sums the same values again
+    if (reduced) {
+      *reinterpret_cast<float4*>(reduced + i * 8) = make_float4(f[0], f[1], f[2], f[3]);
+      *reinterpret_cast<float4*>(reduced + i * 8 + 4) = make_float4(f[4], f[5], f[6], f[7]);
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
   }
@@ -97,7 +101,7 @@ __global__ void zero_reduce_kernel(PeerPtrs grads, int rank, int world, long lon
 // parameter buffer. [start, start+n) is this rank's shard; decay applies to global element
 // indices below decay_end.
 __global__ void zero_update_kernel(PeerPtrs params, PeerPtrs sumsq, PeerPtrs grads,
-                                   float* master, float* m, float* v, int rank, int world,
+                                   const float* __restrict__ reduced, float* master, float* m, float* v, int rank, int world,
                                    long long start, long long n, long long decay_end, float lr,
                                    float beta1, float beta2, float eps, float wd, float bias1,
                                    float bias2, float grad_scale, float max_norm,
@@ -116,10 +120,15 @@ __global__ void zero_update_kernel(PeerPtrs params, PeerPtrs sumsq, PeerPtrs gra
     const long long e0 = i * 8;
     // Σ over ranks of the bf16 gradients, in fp32, in the order zero_reduce_kernel used for the norm
     float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (reduced) {
+      *reinterpret_cast<float4*>(g) = *reinterpret_cast<const float4*>(reduced + e0);
+      *reinterpret_cast<float4*>(g + 4) = *reinterpret_cast<const float4*>(reduced + e0 + 4);
+    } else {
 #pragma unroll 1
-    for (int k = 0; k < world; ++k) {
-      const int r = (rank + 1 + k) % world;
-      acc8(*reinterpret_cast<const uint4*>((const __nv_bfloat16*)grads.p[r] + start + e0), g);
+      for (int k = 0; k < world; ++k) {
+        const int r = (rank + 1 + k) % world;
+        acc8(*reinterpret_cast<const uint4*>((const __nv_bfloat16*)grads.p[r] + start + e0), g);
+      }
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) g[j] *= gs;
@@ -387,13 +396,15 @@ extern "C" int tdllm_symm_signal(void* const* flag_ptrs, int rank, int world, in
 }
 
 // Whole fused step: barrier, pull-reduce, barrier, clip + AdamW + push, barrier.
-// epoch is the first of three consecutive barrier epochs used by this call.
+// epoch is the first of three consecutive barrier epochs used by this call. reduced: fp32 scratch of n elements
+// that carries the rank sums from the norm pass to the update pass, or null (the update pass then pulls again).
 extern "C" int tdllm_zero_fused_step(void* const* grad_ptrs, void* const* param_ptrs,
                                      void* const* sumsq_ptrs, void* const* flag_ptrs, float* master,
                                      float* m, float* v, int rank, int world, long long start,
                                      long long n, long long decay_end, float lr, float beta1,
                                      float beta2, float eps, float wd, int step, float grad_scale,
-                                     float max_norm, float* norm_out, int epoch, void* stream) {
+                                     float max_norm, float* norm_out, int epoch, float* reduced,
+                                     void* stream) {
   comm::PeerPtrs g, p, s, f;
   if (fill_peers(g, grad_ptrs, world) || fill_peers(p, param_ptrs, world) ||
       fill_peers(s, sumsq_ptrs, world) || fill_peers(f, flag_ptrs, world))
@@ -411,7 +422,7 @@ extern "C" int tdllm_zero_fused_step(void* const* grad_ptrs, void* const* param_
     const long long cap = (long long)tdllm_num_sms() * 8;
     if (blocks > cap) blocks = cap;
     comm::zero_reduce_kernel<<<(unsigned)blocks, threads, 0, st>>>(g, rank, world, start, n,
-                                                                  (float*)sumsq_ptrs[rank]);
+                                                                  (float*)sumsq_ptrs[rank], reduced);
   }
   comm::barrier_kernel<<<1, 32, 0, st>>>(f, rank, world, epoch + 1);
   if (n > 0) {
@@ -422,7 +433,7 @@ extern "C" int tdllm_zero_fused_step(void* const* grad_ptrs, void* const* param_
     const float bias1 = 1.f - powf(beta1, (float)step);
     const float bias2 = 1.f - powf(beta2, (float)step);
     comm::zero_update_kernel<<<(unsigned)blocks, threads, 0, st>>>(
-        p, s, g, master, m, v, rank, world, start, n, decay_end,
+        p, s, g, reduced, master, m, v, rank, world, start, n, decay_end,
         lr, beta1, beta2, eps, wd, bias1, bias2, grad_scale, max_norm, norm_out);
   }
   comm::barrier_kernel<<<1, 32, 0, st>>>(f, rank, world, epoch + 2);

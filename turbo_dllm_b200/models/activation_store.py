@@ -111,7 +111,7 @@ class _LayerCheckpoint(torch.autograd.Function):
         store, idx = ctx.store, ctx.idx
         h = store.fetch(idx)
         for d in range(1, store.prefetch_depth + 1):   # host -> device copies of the layers the backward pass needs next
-            for key in (idx - d, (idx - d, "attn_out"), (idx - d, "attn_lse")):
+            for key in (idx - d, (idx - d, "attn_out"), (idx - d, "attn_lse"), (idx - d, "attn_kv_pulled")):
                 store.prefetch(key)
         h = h.detach().requires_grad_(True)
         from ..ops.gemm import skip_last_output

@@ -281,7 +281,9 @@ class _FusedContextAttention(torch.autograd.Function):
     """Packed qkv of this rank's rows -> attention output, keys = own rows + the peers' clean rows."""
 
     @staticmethod
-    def forward(ctx, qkv, cpa):
+    def run_forward(qkv, cpa):
+        """Stages this rank's travelling rows, signals the peers and runs the attention kernel that pulls theirs.
+        Returns (out, lse, the peers' K|V rows as pulled)."""
         from ..ops._util import ptr, stream
 
         ex, c = cpa.exchange, cpa.cfg
@@ -306,6 +308,13 @@ class _FusedContextAttention(torch.autograd.Function):
                 ptr(L["q_grp"]), ptr(L["k_code"]), ptr(L["f_ptr"]), ptr(L["f_idx"]), ptr(L["f_order"]), L["nqt"],
                 1.0 / D ** 0.5, stage.ptr_array, ex.ready.ptr_array, ex.counts_arr, ex.rank, ex.world, n,
                 ptr(ex.counter), ptr(ex.tile_ready), n, stream()), "attn_fwd_csbp")
+        return out, lse, kv_rem
+
+    @staticmethod
+    def forward(ctx, qkv, cpa, precomputed=None):
+        """precomputed: (out, lse, pulled K|V) kept from the no-grad forward of a checkpointed layer; the
+        recomputation then runs neither the kernel nor the pull again (every rank of the group skips alike)."""
+        out, lse, kv_rem = precomputed if precomputed is not None else _FusedContextAttention.run_forward(qkv, cpa)
         ctx.save_for_backward(qkv, kv_rem, out, lse)
         ctx.cpa = cpa
         return out
@@ -341,7 +350,7 @@ class _FusedContextAttention(torch.autograd.Function):
                 ptr(L["q_grp"]), ptr(L["k_code"]), ptr(W["w_ptr"]), ptr(W["w_idx"]), ptr(W["w_order"]), W["n_work"],
                 L["nqt"], L["nkt"], 1.0 / D ** 0.5, ex.counts_arr, ex.row0_arr, ex.barrier.buf.ptr_array, ex.rank,
                 ex.world, e, stream()), "attn_bwd_fused_csbp")
-        return dqkv, None
+        return dqkv, None, None
 
 
 class _StreamingAttention(torch.autograd.Function):
@@ -437,8 +446,10 @@ def fused_key_layout(layout: PackedLayout, kpos: list, kseq: list, cp: int, me: 
 
 
 class ContextParallelAttention:
-    def __init__(self, cfg: ModelConfig, layout: PackedLayout, runtime, spec):
+    def __init__(self, cfg: ModelConfig, layout: PackedLayout, runtime, spec, store=None):
         self.cfg, self.layout, self.rt = cfg, layout, runtime
+        self.store = store                  # the model's ActivationStore (None: nothing is kept across layers)
+        self.keep_pulled_rows = False
         self.group = runtime.context_group
         cp = runtime.context_parallel_size
         seq_len, bs = spec.model.seq_len, spec.objective.block_size
@@ -540,6 +551,13 @@ class ContextParallelAttention:
         dist.all_gather(n_noisy, torch.tensor([self.stage_row0], dtype=torch.long, device=dev), group=self.group)
         self.exchange = FusedKVExchange(self.group, dev, counts, [int(t) for t in n_noisy], layout.rows,
                                         2 * cfg.num_key_value_heads * cfg.head_dim)
+        # keeping every layer's pulled rows for the recomputation costs n_rem * kv_cols * 2 bytes per layer:
+        # done when that is a small part of what is free now (TDLLM_KEEP_PULLED_KV=0/1 overrides)
+        import os
+
+        need = self.exchange.n_rem * self.exchange.kv_cols * 2 * cfg.num_layers
+        env = os.environ.get("TDLLM_KEEP_PULLED_KV")
+        self.keep_pulled_rows = (env == "1") if env is not None else need < 0.25 * torch.cuda.mem_get_info(dev)[0]
 
     def shard_kv(self, qkv, r: int) -> torch.Tensor:
         """K|V rows attended in streaming step r: (noisy rows if r == 0) + owner r's clean rows."""
@@ -560,6 +578,21 @@ class ContextParallelAttention:
         kd = c.num_key_value_heads * c.head_dim
         return (kv[:, :kd].view(n, c.num_key_value_heads, c.head_dim),
                 kv[:, kd:].view(n, c.num_key_value_heads, c.head_dim))
+
+    def _fused(self, qkv, layer_idx):
+        """The fused transport under activation checkpointing: the no-grad forward of a layer keeps (out, lse) and
+        the pulled K|V rows, and the layer's recomputation reuses them instead of pulling and attending again."""
+        store = self.store
+        if store is not None and store.keep_attention and self.keep_pulled_rows:
+            keys = [(layer_idx, "attn_out"), (layer_idx, "attn_lse"), (layer_idx, "attn_kv_pulled")]
+            if store.recording and not torch.is_grad_enabled():
+                res = _FusedContextAttention.run_forward(qkv, self)
+                for k, t in zip(keys, res):
+                    store.stash(k, t)
+                return res[0]
+            if store.replaying and store.has(keys[0]):
+                return _FusedContextAttention.apply(qkv, self, tuple(store.fetch(k) for k in keys))
+        return _FusedContextAttention.apply(qkv, self)
 
     def _windowed(self, qkv):
         """A sliding-window layer: noisy keys are local, clean keys are the rows the all-to-all brought."""
@@ -583,7 +616,7 @@ class ContextParallelAttention:
         if self.transport == "streaming":
             return _StreamingAttention.apply(qkv, self)
         if self.transport == "fused":
-            return _FusedContextAttention.apply(qkv, self)
+            return self._fused(qkv, layer_idx)
         c = self.cfg
         Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
         n_noisy = self.layout.n_noisy

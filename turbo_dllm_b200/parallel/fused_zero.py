@@ -21,7 +21,7 @@ native.register_signatures({
     "tdllm_zero_fused_step": (native.c_int, [native.c_void_p] * 7 + [native.c_int, native.c_int, native.c_ll,
                                                                     native.c_ll, native.c_ll] + [native.c_float] * 5
                               + [native.c_int, native.c_float, native.c_float, native.c_void_p, native.c_int,
-                                 native.c_void_p]),
+                                 native.c_void_p, native.c_void_p]),
 })
 
 
@@ -30,6 +30,7 @@ class FusedZeroSync:
         self.flat, self.group = flat, group
         self.params_buf, self.grads_buf, self.scalar_buf, self.barrier = params_buf, grads_buf, scalar_buf, barrier
         self.norm = torch.zeros(1, dtype=torch.float32, device=flat.data.device)
+        self.reduced = None       # fp32 rank sums of this rank's shard, between the norm pass and the update pass
 
     @classmethod
     def create(cls, flat, group) -> "FusedZeroSync":
@@ -63,11 +64,19 @@ class FusedZeroSync:
         b1, b2 = opt.betas
         n = opt.stop - opt.start
         epoch = self.barrier.reserve(3)
+        if self.reduced is None and opt.world > 2:
+            # with more than one peer a second pull of the gradients costs more link time than 4 bytes per shard
+            # element of memory; with one peer (or no room) the update pass pulls again instead
+            if 4 * n < 0.05 * torch.cuda.mem_get_info(self.flat.data.device)[0]:
+                self.reduced = torch.empty(max(n, 8), dtype=torch.float32, device=self.flat.data.device)
+            else:
+                self.reduced = False
+        reduced = ptr(self.reduced) if isinstance(self.reduced, torch.Tensor) else None
         rc = native.lib().tdllm_zero_fused_step(
             self.grads_buf.ptr_array, self.params_buf.ptr_array, self.scalar_buf.ptr_array,
             self.barrier.buf.ptr_array, ptr(opt.master), ptr(opt.m), ptr(opt.v), opt.rank, opt.world,
             opt.start, n, self.flat.decay_numel, lr, b1, b2, opt.eps, wd, opt.step_count, grad_scale,
-            max_grad_norm, ptr(self.norm), epoch, stream())
+            max_grad_norm, ptr(self.norm), epoch, reduced, stream())
         native.check(rc, "zero_fused_step")
         opt.last_grad_norm = self.norm * self.norm   # grad_norm() takes the square root
         return None

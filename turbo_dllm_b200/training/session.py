@@ -256,6 +256,17 @@ class TrainingSession:
         if s.optimizer.backend in ("fsdp", "fsdp2") and self.world > 1:
             # shards of parameters, fp32 gradients and AdamW state; two layers and the embeddings at full size
             static = cfg.num_params() * 18 / self.world + 4 * 2 * cfg.layer_params() + 8 * cfg.vocab_size * cfg.hidden_size
+        elif cfg.is_moe:
+            # experts are divided over the expert-parallel ranks (weights, gradients and AdamW state of the local
+            # experts stay on their rank); everything else is replicated with a sharded optimizer state
+            rt = self.runtime
+            ep = rt.expert_parallel_size if rt is not None else 1
+            expert = cfg.num_layers * cfg.num_experts * 3 * cfg.hidden_size * cfg.moe_intermediate_size
+            dense = cfg.num_params() - expert
+            static = dense * (2 + 2 + 12 / max(self.world, 1)) + expert / max(ep, 1) * (2 + 2 + 12)
+            k = max(cfg.num_experts_per_token, 1)
+            # dispatched rows (three exchange slabs at twice the mean load) and the experts' activations
+            work += rows * k * 2 * (3 * 2 * cfg.hidden_size + 5 * cfg.moe_intermediate_size)
         else:
             static = cfg.num_params() * (2 + 2 + 12 / max(self.world, 1))
         budget = 0.85 * torch.cuda.get_device_properties(self.device).total_memory
@@ -347,7 +358,8 @@ class TrainingSession:
         if rt is not None and rt.context_parallel_size > 1:
             from ..parallel.context_attention import ContextParallelAttention
 
-            return ContextParallelAttention(getattr(self.model, "lcfg", self.cfg), self.layout, rt, self.spec)
+            return ContextParallelAttention(getattr(self.model, "lcfg", self.cfg), self.layout, rt, self.spec,
+                                            store=getattr(self.model, "store", None))
         return LocalAttention(getattr(self.model, "lcfg", self.cfg), self.layout.mask, store=self.model.store,
                               window_mask=self.layout.window_mask)
 
