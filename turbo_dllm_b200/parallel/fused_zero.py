@@ -64,10 +64,14 @@ class FusedZeroSync:
         b1, b2 = opt.betas
         n = opt.stop - opt.start
         epoch = self.barrier.reserve(3)
-        if self.reduced is None and opt.world > 2:
+        import os
+
+        env = os.environ.get("TDLLM_ZERO_FP32_SUMS")
+        if self.reduced is None and (opt.world > 2 or env == "1") and env != "0":
             # with more than one peer a second pull of the gradients costs more link time than 4 bytes per shard
             # element of memory; with one peer (or no room) the update pass pulls again instead
-            if 4 * n < 0.05 * torch.cuda.mem_get_info(self.flat.data.device)[0]:
+            # (TDLLM_ZERO_FP32_SUMS=1 / 0 forces either form)
+            if env == "1" or 4 * n < 0.05 * torch.cuda.mem_get_info(self.flat.data.device)[0]:
                 self.reduced = torch.empty(max(n, 8), dtype=torch.float32, device=self.flat.data.device)
             else:
                 self.reduced = False
