@@ -8,11 +8,12 @@ pytestmark = pytest.mark.gpu
 def _spec(dtype, objective="fast_dllm_v2", model="synthetic:tiny-hd128"):
     from turbo_dllm_b200.config.run_spec import RunSpec
 
-    extra = {}
+    extra, family = {}, {}
     if objective == "diffusiongemma_native_sft":   # causal clean stream + encoder next-token term (weight 1)
         extra = {"loss_weighting": "unit", "self_conditioning_probability": 0.0}
+        family = {"family": "diffusion_gemma"}     # the family this objective belongs to (dense FFN variant)
     return RunSpec.from_mapping({
-        "model": {"id": model, "seq_len": 256, "dtype": dtype},
+        "model": {"id": model, "seq_len": 256, "dtype": dtype, **family},
         "objective": {"name": objective, "block_size": 32, "noise_schedule_epsilon": 0.1, **extra},
         "training": {"batch_size": 2, "steps": 2, "activation_checkpointing": True},
         "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
