@@ -126,6 +126,7 @@ def run_training(spec: RunSpec) -> dict:
         readback = AsyncLossReadback(device, world)
         wb = WandBRunLogger(spec, rank)
         counters = TokenCounters()
+        timed_counters = TokenCounters()
         trace = SystemTrace.from_run_spec(spec, rank, barrier=(dist.barrier if world > 1 else None))
         run_ctx = collect_run_context(world)
         timed_ms: list[float] = []
@@ -164,6 +165,8 @@ def run_training(spec: RunSpec) -> dict:
             # drafter distillation normalises per micro-batch (denominator 1): its supervised count is the rows
             supervised = rows if session.task is not None else float(res.denominator)
             counters.add(input_tokens=tokens_per_step, supervised_tokens=supervised, active_tokens=rows)
+            if timed:      # throughput counts the tokens of the steps whose time it divides by
+                timed_counters.add(input_tokens=tokens_per_step, supervised_tokens=supervised, active_tokens=rows)
             if rank == 0:
                 ev = ({"event": "step", "step": step, "completed_steps": step, "target_total_steps": total_steps,
                       "timed": timed, "loss": last_loss, "lr": session.scheduler.lr_at(session.scheduler.step_count),
@@ -230,7 +233,7 @@ def run_training(spec: RunSpec) -> dict:
                        "parallel_layout": runtime.plan.layout if runtime else "dp",
                        "training_elapsed_seconds": time.monotonic() - t_train0, "run_context": run_ctx.to_dict(),
                        "system_trace": trace.exported, **eval_metrics,
-                       **counters.throughput(sum(timed_ms) / 1e3, world)}
+                       **timed_counters.throughput(sum(timed_ms) / 1e3, world)}
             emit(summary)
             wb.log_event(summary)
         wb.finish()
