@@ -26,17 +26,30 @@ def run_dflash(argv) -> int:
     p = sub.add_parser("validate-export")
     p.add_argument("path")
     for name in ("serve-sglang", "serve-vllm"):
-        p = sub.add_parser(name)
+        p = sub.add_parser(name, help="print (default) or start the server command for an exported drafter")
         p.add_argument("--target-model", required=True)
         p.add_argument("--draft", required=True)
-        p.add_argument("--port", type=int, default=30000 if name == "serve-sglang" else 8000)
+        p.add_argument("--port", type=int, default=None)
+        p.add_argument("--host", default="127.0.0.1")
         p.add_argument("--tp", type=int, default=1)
-        p.add_argument("--num-speculative-tokens", type=int, default=15)
+        p.add_argument("--block-size", type=int, default=16, help="the drafter's training block size")
+        p.add_argument("--num-speculative-tokens", type=int, default=None,
+                       help="deprecated: derived from --block-size (block_size - 1)")
+        p.add_argument("--memory-fraction", type=float, default=None)
+        p.add_argument("--max-model-len", type=int, default=None)
+        p.add_argument("--launch", action="store_true", help="start the server and wait until it answers")
+        p.add_argument("--ready-timeout", type=float, default=1800.0)
+        p.add_argument("--log", default=None)
+        p.add_argument("--skip-export-check", action="store_true")
     for name in ("verify-sglang", "verify-vllm"):
-        p = sub.add_parser(name)
+        p = sub.add_parser(name, help="gate a running server on one deterministic completion")
         p.add_argument("--base-url", required=True)
         p.add_argument("--model", required=True)
         p.add_argument("--min-acceptance-length", type=float, default=1.5)
+        p.add_argument("--prompt", default=None)
+        p.add_argument("--expected-text", default=None, help="the target model's own greedy continuation of the prompt")
+        p.add_argument("--block-size", type=int, default=16)
+        p.add_argument("--tokenizer", default=None, help="tokenizer directory (default: whitespace tokens)")
     a = ap.parse_args(argv)
     try:
         if a.cmd == "prepare-features":
@@ -63,15 +76,44 @@ def run_dflash(argv) -> int:
             print(json.dumps({"ok": not problems, "problems": problems}))
             return 0 if not problems else 1
         if a.cmd in ("serve-sglang", "serve-vllm"):
-            build = srv.build_sglang_command if a.cmd == "serve-sglang" else srv.build_vllm_command
-            cmd = build(target_model=a.target_model, draft_export=a.draft, port=a.port, tp=a.tp,
-                        num_speculative_tokens=a.num_speculative_tokens)
-            print(" ".join(shlex.quote(c) for c in cmd))
-            return 0
+            backend = "sglang" if a.cmd == "serve-sglang" else "vllm"
+            block = a.block_size if a.num_speculative_tokens is None else a.num_speculative_tokens + 1
+            cfg = srv.ServerConfig.from_mapping({
+                "backend": backend, "target_model": a.target_model, "draft_export": a.draft, "block_size": block,
+                "host": a.host, "port": a.port, "tensor_parallel_size": a.tp, "memory_fraction": a.memory_fraction,
+                "max_model_len": a.max_model_len})
+            cmd = cfg.command()
+            if not a.launch:
+                print(" ".join(shlex.quote(c) for c in cmd))
+                return 0
+            srv.require_server_version(backend)
+            if not a.skip_export_check:
+                print(json.dumps(srv.validate_export_for_server(a.draft, backend, block)))
+            server = srv.ServerProcess(cmd, cfg.url, log_path=a.log).start()
+            try:
+                models = server.wait_ready(a.ready_timeout)
+                print(json.dumps({"event": "ready", "url": cfg.url, "pid": server.proc.pid,
+                                  "models": [m.get("id") for m in models.get("data", [])]}), flush=True)
+                return server.proc.wait()
+            except KeyboardInterrupt:
+                return 130
+            finally:
+                server.stop()
+        if a.prompt is not None and a.expected_text is not None:
+            encode = str.split
+            if a.tokenizer:
+                from transformers import AutoTokenizer
+
+                tok = AutoTokenizer.from_pretrained(a.tokenizer)
+                encode = lambda t: tok.encode(t, add_special_tokens=False)
+            res = srv.verify_server(server_url=a.base_url, model=a.model, prompt=a.prompt,
+                                    expected_text=a.expected_text, encode=encode, block_size=a.block_size)
+            print(json.dumps(res))
+            return 0 if res["passed"] else 1
         res = srv.verify_acceptance(a.base_url, a.model, ["The capital of France is", "def fib(n):"],
                                     a.min_acceptance_length)
         print(json.dumps(res))
         return 0 if res["ok"] else 1
-    except (RunSpecError, FileNotFoundError, ValueError, OSError) as e:
+    except (RunSpecError, FileNotFoundError, ValueError, OSError, RuntimeError, TimeoutError) as e:
         print(f"error: {e}", file=sys.stderr)
         return 2
