@@ -73,7 +73,8 @@ def test_wandb_sanitising_and_fake_module():
     lg = WandBRunLogger(spec, 0, module=fake)
     lg.log_event({"event": "step", "step": 3, "loss": 1.5, "perf": {"tps": 10.0}, "note": "x"})
     lg.finish()
-    assert fake.kw["tags"] == ["t-1"] and fake.kw["id"] == "id"
+    assert fake.kw["tags"][0] == "t-1" and "seq_len:1024" in fake.kw["tags"] and fake.kw["id"] == "id"
+    assert fake.kw["resume"] == "allow" and fake.kw["name"].startswith("nvidia-Nemotron-Labs-Diffusion-3B-1024-cp")
     assert fake.run.logged == [(3, {"step/step": 3, "step/loss": 1.5, "step/perf/tps": 10.0})] and fake.run.finished
     assert WandBRunLogger(spec, 1, module=fake).run is None
 
@@ -266,3 +267,44 @@ def test_portable_artifact_check_and_release_manifest(tmp_path):
         f.write(b"tampered")
     assert any("SHA-256" in p for p in rel.verify(str(dist / "release_manifest.json")))
     assert {c["name"] for c in rel.sbom()["components"]} >= {"torch", "numpy"}
+
+
+def test_wandb_run_identity_tags_and_polling():
+    from turbo_dllm_b200.training import metrics as m
+
+    assert m.resolve_run_id("cfg id", "name", env={"WANDB_RUN_ID": "env/id"}) == "env-id"
+    assert m.resolve_run_id("cfg id", "name", env={}) == "cfg-id"
+    assert m.resolve_run_id(None, "my name", env={}) == "my-name" and m.resolve_run_id(None, None, env={}) is None
+    assert m.resolve_resume({}) == "allow" and m.resolve_resume({"WANDB_RESUME": "must"}) == "must"
+    cfg = {"model": {"id": "org/Model", "seq_len": 4096, "num_layers": 2}, "objective": {"name": "fast_dllm_v2", "block_size": 32},
+           "optimizer": {"lr": 1e-4}, "topology": {"context_parallel_size": 2, "block_parallel_size": 4}}
+    tags = m.config_tags(cfg)
+    assert {"seq_len:4096", "block_size:32", "cp:2", "bp:4", "tp:1", "active_blocks:dual_end", "kv_backend:ring",
+            "parallel:topology"} <= set(tags)
+    assert "parallel:topology" not in m.config_tags({"topology": {"context_parallel_size": 1}})
+    assert m.default_run_name(cfg) == "org-Model-4096-cp2-bp4-tp1-ep1"
+
+    class Run:
+        def __init__(self, state, step):
+            self.state, self.summary, self.url = state, {"step/step": step, "step/loss": 2.5}, "http://w/run"
+
+    class Api:
+        def __init__(self):
+            self.calls = 0
+
+        def run(self, path):
+            self.calls += 1
+            if path.endswith("/late") and self.calls < 4:
+                raise KeyError(path)              # not created yet
+            if path.endswith("/dead"):
+                return Run("crashed", 50)
+            return Run("running", 10 if self.calls < 6 else 120)
+
+    now = [0.0]
+    ok = m.poll_runs(entity="e", project="p", run_ids=["a", "late"], min_step=100, timeout_s=100, poll_interval_s=1,
+                     api=Api(), sleep=lambda s: now.__setitem__(0, now[0] + s), clock=lambda: now[0])
+    assert all(v["state"] == "running" and v["step"] >= 100 for v in ok.values()) and ok["a"]["loss"] == 2.5
+    now[0] = 0.0
+    bad = m.poll_runs(entity="e", project="p", run_ids=["dead"], min_step=10, timeout_s=3, poll_interval_s=1,
+                      api=Api(), sleep=lambda s: now.__setitem__(0, now[0] + s), clock=lambda: now[0])
+    assert bad["dead"]["state"] == "crashed" and now[0] >= 3

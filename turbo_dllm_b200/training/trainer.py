@@ -236,6 +236,7 @@ def run_training(spec: RunSpec) -> dict:
                        **timed_counters.throughput(sum(timed_ms) / 1e3, world)}
             emit(summary)
             wb.log_event(summary)
+            wb.log_summary(summary)
         wb.finish()
         from ..checkpoint import wait_for_async_saves
 
