@@ -93,8 +93,10 @@ def test_dflash_anchor_blocks_and_document_boundaries():
 def test_diffusiongemma_native_replaces_tokens_and_scores_every_position():
     from turbo_dllm_b200.objectives.runtime import LABEL_IGNORE_INDEX, DiffusionGemmaNativeRuntime
 
+    # the masked full-length form (the response stays in place); the packed form is covered by
+    # tests/test_native_sft_packing.py
     rt = DiffusionGemmaNativeRuntime(vocab_size=500, self_conditioning_probability=0.5, block_size=16,
-                                     mask_token_id=499, max_seq_len=128, seed=11)
+                                     mask_token_id=499, max_seq_len=128, seed=11, pack_response_suffix=False)
     x0 = torch.randint(0, 400, (6, 128))
     sup = torch.zeros_like(x0, dtype=torch.bool)
     sup[:, 32:] = True
@@ -111,7 +113,7 @@ def test_diffusiongemma_native_replaces_tokens_and_scores_every_position():
     assert cb.self_conditioning_mask.shape == (6,) and cb.self_conditioning_mask.dtype == torch.bool
     # deterministic and resumable through the batch counter alone
     rt2 = DiffusionGemmaNativeRuntime(vocab_size=500, self_conditioning_probability=0.5, block_size=16,
-                                      mask_token_id=499, max_seq_len=128, seed=11)
+                                      mask_token_id=499, max_seq_len=128, seed=11, pack_response_suffix=False)
     cb2 = rt2.corrupt(x0, supervision_mask=sup)
     assert (cb2.noisy_input_ids == cb.noisy_input_ids).all()
     rt2.load_state_dict(rt.state_dict())

@@ -100,6 +100,9 @@ SECTIONS: dict[str, tuple[F, ...]] = {
         F("antithetic_sampling", bool, True),
         F("self_conditioning_probability", float, 0.5),
         F("encoder_loss_weight", float, 1.0),
+        F("minimum_decoder_blocks", int, 1),
+        F("pack_response_suffix", bool, True, ext=True,
+          help="diffusiongemma_native_sft: decoder rows cover the supervised response only, blocks counted from its start"),
         F("self_conditioning_row_chunk_size", int, 256),
         F("self_conditioning_vocab_chunk_size", int, 32768),
         F("max_anchors", OPT_INT, None),

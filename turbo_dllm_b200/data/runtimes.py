@@ -30,6 +30,8 @@ class DataBatch:
     # (plain, and without position 0 for objectives with shifted labels)
     turn_weight: float | None = None
     supervision_count_shifted: int | None = None
+    # padding: True on the real tokens (one contiguous prefix per example); None = no padding
+    valid_mask: torch.Tensor | None = None
 
 
 class DataRuntime(ABC):

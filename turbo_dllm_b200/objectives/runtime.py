@@ -46,6 +46,12 @@ class CorruptedBatch:
     def views(self) -> int:
         return int(self.noisy_input_ids.shape[1])
 
+    # Response-suffix packing (diffusiongemma_native_sft): when set, the noisy / label / weight tensors cover only
+    # the decoder rows, offset o standing for position response_start + o (clamped to the last valid position for
+    # the padding rows that fill the last block), with blocks counted from the response start.
+    response_start = None      # int: first scored position, shared by the batch
+    valid_length = None        # int: tokens before the padding, shared by the batch
+
 
 @dataclass(frozen=True)
 class TokenAccountingPolicy:
@@ -231,9 +237,12 @@ class DiffusionGemmaNativeRuntime(StandardBlockDiffusionRuntime):
     views = 1
     exclude_mask_token = False
 
-    def __init__(self, *, vocab_size: int, self_conditioning_probability: float = 0.5, **kw):
+    def __init__(self, *, vocab_size: int, self_conditioning_probability: float = 0.5,
+                 pack_response_suffix: bool = True, minimum_decoder_blocks: int = 1, **kw):
         kw.setdefault("loss_weighting", "unit")
         super().__init__(**kw)
+        self.pack_response_suffix = bool(pack_response_suffix)
+        self.minimum_decoder_blocks = max(int(minimum_decoder_blocks), 1)
         if vocab_size <= 1:
             raise ValueError("vocab_size must be greater than one")
         if not 0.0 <= self_conditioning_probability <= 1.0:
@@ -243,9 +252,77 @@ class DiffusionGemmaNativeRuntime(StandardBlockDiffusionRuntime):
         self.vocab_size = int(vocab_size)
         self.self_conditioning_probability = float(self_conditioning_probability)
 
-    def corrupt(self, x0, *, supervision_mask=None, supervision_count=None) -> CorruptedBatch:
+    def response_suffix(self, supervision_mask, valid_mask=None):
+        """(response_start, valid_length) when every row's scored positions are one contiguous suffix of its valid
+        prefix and the batch shares both numbers; None otherwise (the masked full-length form then applies).
+        Conditions of dllm_parallel/core/objectives/diffusiongemma.py:151-224."""
+        if supervision_mask is None:
+            return None
+        sm = supervision_mask.to(torch.bool)
+        b, l = sm.shape
+        pos = torch.arange(l, device=sm.device)
+        if valid_mask is None:
+            lengths = torch.full((b,), l, dtype=torch.long, device=sm.device)
+            valid = torch.ones_like(sm)
+        else:
+            valid = valid_mask.to(sm.device, torch.bool)
+            lengths = valid.sum(1)
+            if bool((lengths <= 0).any()) or not torch.equal(valid, pos[None, :] < lengths[:, None]):
+                raise ValueError("valid_mask must be one contiguous non-empty prefix per example")
+            if bool((sm & ~valid).any()):
+                raise ValueError("supervision_mask cannot score padding")
+        if bool((sm.sum(1) <= 0).any()):
+            return None
+        starts = sm.to(torch.int64).argmax(1)
+        if not torch.equal(sm, (pos[None, :] >= starts[:, None]) & valid):
+            return None
+        if not bool(starts.eq(starts[0]).all()) or not bool(lengths.eq(lengths[0]).all()):
+            return None
+        return int(starts[0]), int(lengths[0])
+
+    def _corrupt_packed(self, x0, start: int, length: int) -> CorruptedBatch:
+        """Decoder rows for the response [start, length) only: blocks counted from `start`, the last block filled
+        with padding rows (clamped positions, never scored), at least `minimum_decoder_blocks` blocks."""
+        b = x0.shape[0]
+        bs = self.block_size
+        resp = length - start
+        logical = (resp + bs - 1) // bs * bs
+        dec_len = max(logical, self.minimum_decoder_blocks * bs)
+        off = torch.arange(dec_len, device=self.device)
+        real = off < resp
+        dpos = (off + start).clamp(max=length - 1)
+        dec_clean = x0.index_select(1, dpos)
+        eligible = real[None, :].expand(b, -1)
+        nblk = dec_len // bs
+        t = self.sample_times(b, nblk)
+        noise = (-torch.log1p(-t.clamp(max=1.0 - 1e-7))).clamp(max=-math.log(self.noise_schedule_epsilon))
+        _, moved_labels = self._tokens(dec_clean, t, eligible, shift=False)
+        moved = moved_labels[:, 0] != LABEL_IGNORE_INDEX
+        g = torch.Generator(device=self.device)
+        g.manual_seed((self.seed * 1_000_003 + 2 * self.batches_corrupted + 1) % (2 ** 63 - 1))
+        random_tokens = torch.randint(0, self.vocab_size, dec_clean.shape, dtype=x0.dtype, device=self.device, generator=g)
+        noisy = torch.where(moved, random_tokens, dec_clean)
+        labels = torch.where(eligible, dec_clean, torch.full_like(dec_clean, LABEL_IGNORE_INDEX))
+        sc_mask = torch.rand(b, device=self.device, generator=g) < self.self_conditioning_probability
+        valid = b * resp
+        self.batches_corrupted += 1
+        self.valid_tokens_seen += valid
+        out = CorruptedBatch(x0, noisy[:, None], labels[:, None], t, noise, torch.ones(b, 1, nblk, device=self.device),
+                             eligible.sum(dtype=torch.int64), valid, float(valid))
+        out.self_conditioning_mask = sc_mask
+        out.replaced_tokens = moved.sum(dtype=torch.int64)
+        out.response_start, out.valid_length = start, length
+        return out
+
+    def corrupt(self, x0, *, supervision_mask=None, supervision_count=None, valid_mask=None) -> CorruptedBatch:
         b, l, nblk = self._check(x0)
         x0 = x0.to(self.device)
+        if self.pack_response_suffix:
+            suffix = self.response_suffix(supervision_mask, valid_mask)
+            if suffix is not None and (suffix[0] > 0 or suffix[1] < l):
+                if supervision_count is not None and int(supervision_count) != b * (suffix[1] - suffix[0]):
+                    raise ValueError("supervision_count must equal the explicit supervision_mask count")
+                return self._corrupt_packed(x0, *suffix)
         if supervision_mask is None:
             if supervision_count is not None:
                 raise ValueError("supervision_count requires an explicit supervision_mask")
@@ -319,6 +396,7 @@ def build_objective_runtime(spec, *, mask_token_id: int, seed: int, device="cpu"
             raise ValueError("diffusiongemma_native_sft needs the model's vocabulary size")
         return DiffusionGemmaNativeRuntime(
             vocab_size=vocab_size, self_conditioning_probability=o.self_conditioning_probability,
+            pack_response_suffix=o.pack_response_suffix, minimum_decoder_blocks=o.minimum_decoder_blocks,
             loss_weighting=o.loss_weighting, noise_schedule_epsilon=o.noise_schedule_epsilon,
             sampling_epsilon_min=o.sampling_epsilon_min, sampling_epsilon_max=o.sampling_epsilon_max,
             antithetic_sampling=o.antithetic_sampling, **common)

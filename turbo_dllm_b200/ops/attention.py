@@ -219,7 +219,8 @@ def block_diffusion_layout(noisy_pos: torch.Tensor, noisy_group: torch.Tensor, c
                            block_size: int, *, noisy_seq: torch.Tensor | None = None,
                            clean_seq: torch.Tensor | None = None, seq_stride: int = SEQ_STRIDE,
                            window: int | None = None, key_clean_pos: torch.Tensor | None = None,
-                           key_clean_seq: torch.Tensor | None = None, clean_causal: bool = False) -> MaskLayout:
+                           key_clean_seq: torch.Tensor | None = None, clean_causal: bool = False,
+                           noisy_stop: torch.Tensor | None = None) -> MaskLayout:
     """Layout for packed rows `[noisy ; clean]` attending to keys `[noisy ; clean keys]`.
 
     noisy_pos/noisy_group: position and unique noisy-block id of each noisy row (the id must be
@@ -240,7 +241,9 @@ def block_diffusion_layout(noisy_pos: torch.Tensor, noisy_group: torch.Tensor, c
     kpos = clean_pos if key_clean_pos is None else key_clean_pos.to(i64)
     ks = (cs if key_clean_pos is None else
           (torch.zeros_like(kpos) if key_clean_seq is None else key_clean_seq.to(i64)))
-    n_stop = (noisy_pos // block_size) * block_size
+    # a noisy row sees the clean tokens before its block: blocks normally start at multiples of the block size;
+    # `noisy_stop` gives the block starts explicitly (blocks counted from a response start)
+    n_stop = (noisy_pos // block_size) * block_size if noisy_stop is None else noisy_stop.to(i64)
     c_stop = clean_pos + 1 if clean_causal else (clean_pos // block_size + 1) * block_size
     stop = torch.cat([n_stop, c_stop])
     seq = torch.cat([ns, cs])

@@ -100,6 +100,7 @@ class PackedLayout:
     noisy_offsets: tuple | None = None   # offsets inside a block this rank computes (pure context parallelism)
     window: int | None = None            # window of the sliding-window layers
     window_mask: MaskLayout | None = None   # the mask of those layers over the rank's own rows
+    noisy_offset: torch.Tensor | None = None   # response-suffix packing: offset of each noisy row in the decoder tensors
 
     @property
     def n_noisy(self) -> int:
@@ -132,6 +133,34 @@ def noisy_rows(*, seq_len: int, block_size: int, batch: int, views: int = 1, own
     noisy_view = view_ids.repeat_interleave(n1).repeat(batch)
     noisy_group = (noisy_seq * views + noisy_view) * nblocks + noisy_pos // block_size
     return noisy_pos, noisy_seq, noisy_view, noisy_group
+
+
+def build_response_layout(*, seq_len: int, block_size: int, batch: int, response_start: int, valid_length: int,
+                          decoder_length: int, window: int | None = None, device="cpu",
+                          clean_causal: bool = False) -> PackedLayout:
+    """Rows of a batch whose noisy (decoder) rows cover only the response [response_start, valid_length): for every
+    sequence `decoder_length` rows (whole blocks counted from the response start; rows past the response are
+    padding at the last valid position), then all clean positions. A decoder block sees the clean tokens before
+    its own first position. Layout of dllm_parallel/core/objectives/diffusiongemma.py:226-250."""
+    off1 = torch.arange(decoder_length, device=device)
+    nblk = decoder_length // block_size
+    seq_ids = torch.arange(batch, device=device)
+    noisy_off = off1.repeat(batch)
+    noisy_seq = seq_ids.repeat_interleave(decoder_length)
+    noisy_pos = (noisy_off + response_start).clamp(max=valid_length - 1)
+    noisy_view = torch.zeros_like(noisy_seq)
+    blk = noisy_off // block_size
+    noisy_group = noisy_seq * nblk + blk
+    noisy_stop = (response_start + blk * block_size).clamp(max=valid_length)
+    cpos1 = torch.arange(seq_len, device=device)
+    clean_pos = cpos1.repeat(batch)
+    clean_seq = seq_ids.repeat_interleave(seq_len)
+    kw = dict(noisy_seq=noisy_seq, clean_seq=clean_seq, clean_causal=clean_causal, noisy_stop=noisy_stop)
+    mask = block_diffusion_layout(noisy_pos, noisy_group, clean_pos, block_size, **kw)
+    wmask = block_diffusion_layout(noisy_pos, noisy_group, clean_pos, block_size, window=window, **kw) if window else None
+    return PackedLayout(noisy_pos, noisy_seq, noisy_view, noisy_group, clean_pos, clean_seq,
+                        torch.cat([noisy_pos, clean_pos]), mask, block_size, clean_causal, None, window or None, wmask,
+                        noisy_off)
 
 
 def build_packed_layout(*, seq_len: int, block_size: int, batch: int, views: int = 1,

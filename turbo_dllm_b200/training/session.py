@@ -103,6 +103,12 @@ class TrainingSession:
         self.objective = build_objective_runtime(spec, mask_token_id=self.cfg.mask_token_id,
                                                  seed=seed + 7919 * (dp_rank + 1), device=self.device,
                                                  vocab_size=self.cfg.vocab_size)
+        if hasattr(self.objective, "pack_response_suffix") and (
+                self.cfg.is_hybrid or (runtime is not None and (runtime.local_parallel_size > 1
+                                                                or runtime.tensor_parallel_size > 1))):
+            # context / block / tensor parallelism plan their rows for whole sequences: the response stays in place
+            # and the supervision mask selects the scored rows
+            self.objective.pack_response_suffix = False
         # diffusiongemma_native_sft: the clean stream is causal and carries a next-token loss of its own
         # (dllm_parallel/core/models/backbones/nemotron/model.py:1089-1096, :1966-2030)
         self.encoder_loss_weight = (float(spec.objective.encoder_loss_weight)
@@ -283,13 +289,30 @@ class TrainingSession:
     def _want_activation_offload(self) -> bool:
         return self._memory_plan()[0]
 
-    def _select_layout(self, seq_len: int) -> None:
+    def _select_layout(self, seq_len: int, response: tuple[int, int, int] | None = None) -> None:
         """Row layout and attention for micro-batches whose sequences are shorter than `model.seq_len` (indexed
-        datasets hand out same-length batches of any block-aligned length). Layouts are built once per length."""
-        if seq_len == getattr(self, "_layout_len", self.spec.model.seq_len):
+        datasets hand out same-length batches of any block-aligned length), or whose noisy rows cover only a
+        response suffix (`response` = (response start, valid length, decoder rows per sequence)). Layouts are built
+        once per shape."""
+        key = seq_len if response is None else (seq_len, *response)
+        if key == getattr(self, "_layout_len", self.spec.model.seq_len):
             return
         cache = self.__dict__.setdefault("_layouts", {self.spec.model.seq_len: (self._first_layout, self._first_attend)})
-        if seq_len not in cache:
+        if key not in cache and response is not None:
+            from ..parallel.layout import build_response_layout
+
+            if len(cache) > 64:       # response starts vary from batch to batch: keep the table bounded
+                for k in [k for k in cache if isinstance(k, tuple)][:32]:
+                    del cache[k]
+            s = self.spec
+            lay = build_response_layout(
+                seq_len=seq_len, block_size=s.objective.block_size, batch=s.training.batch_size,
+                response_start=response[0], valid_length=response[1], decoder_length=response[2],
+                window=self.cfg.sliding_window if self.cfg.has_sliding_layers else None, device=self.device,
+                clean_causal=getattr(self, "encoder_loss_weight", 0.0) > 0.0)
+            cache[key] = (lay, LocalAttention(getattr(self.model, "lcfg", self.cfg), lay.mask,
+                                              store=self.model.store, window_mask=lay.window_mask))
+        if key not in cache:
             rt = self.runtime
             if rt is not None and (rt.context_parallel_size > 1 or rt.block_parallel_size > 1):
                 raise ValueError("variable sequence lengths are built for data-parallel runs; context / block "
@@ -300,8 +323,8 @@ class TrainingSession:
             lay = self._build_layout(seq_len)
             cache[seq_len] = (lay, LocalAttention(getattr(self.model, "lcfg", self.cfg), lay.mask,
                                                   store=self.model.store, window_mask=lay.window_mask))
-        self.layout, self.attend = cache[seq_len]
-        self._layout_len = seq_len
+        self.layout, self.attend = cache[key]
+        self._layout_len = key
 
     def _build_layout(self, seq_len: int | None = None) -> PackedLayout:
         s, rt = self.spec, self.runtime
@@ -387,12 +410,14 @@ class TrainingSession:
         Returns (tokens [rows], labels [rows], weights [rows] or None)."""
         lay = self.layout
         bs = lay.block_size
-        noisy = cb.noisy_input_ids[lay.noisy_seq, lay.noisy_view, lay.noisy_pos]
+        # response-suffix packing indexes the decoder tensors by the row's offset from the response start
+        at = lay.noisy_pos if lay.noisy_offset is None else lay.noisy_offset
+        noisy = cb.noisy_input_ids[lay.noisy_seq, lay.noisy_view, at]
         clean = cb.clean_input_ids[lay.clean_seq, lay.clean_pos]
         tokens = torch.cat([noisy, clean])
-        nlab = cb.labels[lay.noisy_seq, lay.noisy_view, lay.noisy_pos]
+        nlab = cb.labels[lay.noisy_seq, lay.noisy_view, at]
         labels = torch.cat([nlab, torch.full_like(clean, -100)])
-        w = cb.loss_weights[lay.noisy_seq, lay.noisy_view, lay.noisy_pos // bs]
+        w = cb.loss_weights[lay.noisy_seq, lay.noisy_view, at // bs]
         weights = torch.cat([w, torch.zeros(clean.shape[0], device=w.device)])
         return tokens, labels, weights
 
@@ -411,10 +436,20 @@ class TrainingSession:
 
     # ------------------------------------------------------------------ step
     def forward_backward(self, batch: DataBatch, denominator: float):
-        if not self.cfg.is_hybrid:
-            self._select_layout(int(batch.input_ids.shape[1]))
+        extra = {}
+        if batch.valid_mask is not None:
+            if self.objective.name != "diffusiongemma_native_sft":
+                raise ValueError("padded batches (valid_mask) are built for diffusiongemma_native_sft")
+            extra["valid_mask"] = batch.valid_mask
         cb = self.objective.corrupt(batch.input_ids, supervision_mask=batch.supervision_mask,
-                                    supervision_count=batch.supervision_count)
+                                    supervision_count=batch.supervision_count, **extra)
+        valid_len = int(batch.input_ids.shape[1])
+        if not self.cfg.is_hybrid:
+            response = None
+            if cb.response_start is not None:       # decoder rows cover the response only
+                response = (cb.response_start, cb.valid_length, int(cb.noisy_input_ids.shape[2]))
+                valid_len = cb.valid_length
+            self._select_layout(int(batch.input_ids.shape[1]), response)
         tokens, labels, weights = self.assemble_rows(cb)
         n_noisy = self.layout.n_noisy
         if self.encoder_loss_weight > 0.0:
@@ -423,8 +458,8 @@ class TrainingSession:
             # the decoder's denominator normalises both terms
             lay, x0 = self.layout, cb.clean_input_ids
             nxt = (lay.clean_pos + 1).clamp_max(x0.shape[1] - 1)
-            enc_labels = torch.where(lay.clean_pos + 1 < x0.shape[1], x0[lay.clean_seq, nxt],
-                                     torch.full_like(nxt, -100))
+            enc_labels = torch.where(lay.clean_pos + 1 < valid_len, x0[lay.clean_seq, nxt],
+                                     torch.full_like(nxt, -100))      # padding is neither input nor target
             labels = torch.cat([labels[:n_noisy], enc_labels.to(labels.dtype)])
             enc_w = self.encoder_loss_weight * float(denominator) / self._encoder_denominator
             weights = torch.cat([weights[:n_noisy], torch.full_like(weights[n_noisy:], enc_w)])
@@ -531,7 +566,9 @@ class TrainingSession:
             denom = 1.0 if turn_mean else self.global_denominator(batches)
             if self.encoder_loss_weight > 0.0:
                 b0, l0 = batches[0].input_ids.shape
-                self._encoder_denominator = float(max(b0 * (l0 - 1) * len(batches) * self.dp_size, 1))
+                pairs = sum(int((x.valid_mask.sum(1) - 1).clamp_min(0).sum()) if x.valid_mask is not None
+                            else b0 * (l0 - 1) for x in batches)
+                self._encoder_denominator = float(max(pairs * self.dp_size, 1))
             wsum = sum(b.turn_weight for b in batches) if turn_mean else 0.0
             shifted = self.objective.name == "fast_dllm_v2"
             for b in batches:
