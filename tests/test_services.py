@@ -308,3 +308,47 @@ def test_wandb_run_identity_tags_and_polling():
     bad = m.poll_runs(entity="e", project="p", run_ids=["dead"], min_step=10, timeout_s=3, poll_interval_s=1,
                       api=Api(), sleep=lambda s: now.__setitem__(0, now[0] + s), clock=lambda: now[0])
     assert bad["dead"]["state"] == "crashed" and now[0] >= 3
+
+
+def test_bundle_manifest_schema_host_check_catalog_and_install(tmp_path):
+    from turbo_dllm_b200.kernels import bundle_manifest as bm
+
+    wheel = tmp_path / "turbo_dllm_b200-0.1.0-cp312-cp312-linux_x86_64.whl"
+    wheel.write_bytes(b"wheel bytes")
+    kw = dict(package_version="0.1.0", source_revision="abc1234", python_abi="cp312", platform="linux_x86_64",
+              cuda="12.9", architectures=["10.0a"])
+    man = bm.create_bundle_manifest([str(wheel)], base_url="https://example.org/r/v0.1.0", **kw)
+    assert man["artifacts"][0]["url"].endswith("/" + wheel.name) and man["artifacts"][0]["size"] == 11
+    host = bm.BundleEnvironment("0.1.0", "cp312", "linux_x86_64", "12.9", "10.0")
+    assert bm.validate_bundle_manifest(man, host)[0]["name"] == wheel.name
+    for field, value, msg in (("python_abi", "cp311", "Python ABI"), ("cuda", "12.8", "CUDA"),
+                              ("package_version", "0.2.0", "package version")):
+        with pytest.raises(bm.BundleError, match=msg):
+            bm.validate_bundle_manifest({**man, field: value}, host)
+    with pytest.raises(bm.BundleError, match="compute capability"):
+        bm.validate_bundle_manifest(man, bm.BundleEnvironment("0.1.0", "cp312", "linux_x86_64", "12.9", "9.0"))
+    bad = lambda **ch: {**man, "artifacts": [{**man["artifacts"][0], **ch}]}
+    for change, msg in (({"url": "http://example.org/" + wheel.name}, "HTTPS"),
+                        ({"url": "https://example.org/other.whl"}, "does not match"),
+                        ({"sha256": "xyz"}, "SHA-256"), ({"size": 0}, "size"), ({"name": "../x.whl"}, "invalid wheel name")):
+        with pytest.raises(bm.BundleError, match=msg):
+            bm.validate_bundle_schema(bad(**change))
+    with pytest.raises(bm.BundleError, match="duplicate"):
+        bm.validate_bundle_schema({**man, "artifacts": man["artifacts"] * 2})
+    with pytest.raises(bm.BundleError, match="git revision"):
+        bm.validate_bundle_schema({**man, "source_revision": "not a rev"})
+    # a release catalog over a local mirror: resolve for the host, verify hash and size, hand the wheel to pip
+    local = bm.create_bundle_manifest([str(wheel)], base_url="file://" + str(tmp_path), allow_local=True, **kw)
+    mpath = tmp_path / "bundle.json"
+    mpath.write_text(json.dumps(local))
+    cat = bm.create_bundle_catalog("v0.1.0", [local], [str(mpath)])
+    assert bm.resolve_bundle(cat, host)["artifacts"][0]["sha256"] == local["artifacts"][0]["sha256"]
+    with pytest.raises(bm.BundleError, match="has no bundle"):
+        bm.resolve_bundle(cat, bm.BundleEnvironment("0.1.0", "cp310", "linux_x86_64", "12.9", "10.0"))
+    calls = []
+    rc = bm.install_bundle_manifest(local, host, pip_runner=lambda cmd: calls.append(cmd) or 0, allow_local=True)
+    assert rc == 0 and calls[0][-1].endswith(wheel.name) and "--no-deps" in calls[0]
+    wheel.write_bytes(b"tampered!!!")
+    with pytest.raises(bm.BundleError, match="sha256"):
+        bm.install_bundle_manifest(local, host, pip_runner=lambda cmd: 0, allow_local=True)
+    assert bm.main(["validate", str(mpath), "--schema-only"]) == 2      # file:// URLs are refused outside a mirror install
