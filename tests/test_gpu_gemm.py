@@ -131,3 +131,46 @@ def test_grouped_linear_matches_per_expert_reference(counts):
     assert torch.allclose(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
     scale = wr.grad.abs().max().item() + 1e-6
     assert (w.grad.float() - wr.grad).abs().max().item() < 2e-2 * scale + 1e-3
+
+
+def test_kernels_with_a_fixed_reduction_order_repeat_bit_for_bit(monkeypatch):
+    """Run twice, compare bitwise: the GEMM (no split-K), the attention forward, the split attention backward (one
+    dQ kernel per query tile, one dK/dV kernel per key tile) and the RMSNorm backward (per-block partial sums, then
+    an ordered column sum) have no atomics on their result paths."""
+    import math
+
+    from turbo_dllm_b200.ops.attention import (attention_backward_native, attention_forward_native,
+                                               single_sequence_layout)
+    from turbo_dllm_b200.ops.gemm import gemm
+    from turbo_dllm_b200.ops.norm import rmsnorm
+
+    torch.manual_seed(0)
+    a = torch.randn(777, 520, device="cuda").bfloat16()
+    w = torch.randn(392, 520, device="cuda").bfloat16()
+    assert torch.equal(gemm(a, w), gemm(a, w))
+    layout = single_sequence_layout(384, 32, "cuda", 2)
+    n, Hq, Hkv, D = 3 * 384, 4, 2, 128
+    qkv = (torch.randn(n, (Hq + 2 * Hkv) * D, device="cuda") * 0.5).bfloat16()
+    q = qkv[:, : Hq * D].view(n, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(n, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(n, Hkv, D)
+    scale = 1.0 / math.sqrt(D)
+    o1, l1 = attention_forward_native(q, k, v, layout, scale)
+    o2, l2 = attention_forward_native(q, k, v, layout, scale)
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    monkeypatch.setenv("TDLLM_ATTN_BWD", "split")
+    do = torch.randn_like(o1)
+    g1 = [t.clone() for t in attention_backward_native(q, k, v, o1, do, l1, layout, scale)]
+    g2 = attention_backward_native(q, k, v, o1, do, l1, layout, scale)
+    assert all(torch.equal(x, y) for x, y in zip(g1, g2))
+    x = torch.randn(1000, 512, device="cuda").bfloat16().requires_grad_()
+    wn = torch.ones(512, device="cuda").bfloat16().requires_grad_()
+    grads = []
+    for _ in range(2):
+        x.grad = wn.grad = None
+        y, _ = rmsnorm(x, wn, 1e-6)
+        y.backward(torch.ones_like(y))
+        grads.append((x.grad.clone(), wn.grad.clone() if wn.grad is not None else None))
+    assert torch.equal(grads[0][0], grads[1][0])
+    if grads[0][1] is not None:
+        assert torch.equal(grads[0][1], grads[1][1])

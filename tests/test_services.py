@@ -352,3 +352,21 @@ def test_bundle_manifest_schema_host_check_catalog_and_install(tmp_path):
     with pytest.raises(bm.BundleError, match="sha256"):
         bm.install_bundle_manifest(local, host, pip_runner=lambda cmd: 0, allow_local=True)
     assert bm.main(["validate", str(mpath), "--schema-only"]) == 2      # file:// URLs are refused outside a mirror install
+
+
+def test_checked_kernel_build_is_a_separate_library(monkeypatch):
+    """DLLM_KERNEL_CHECKS=1 selects the library built with -DTDLLM_KERNEL_CHECKS (index checks that record
+    ERR_BAD_INDEX and skip the access); the regular library and its manifest are untouched by that build."""
+    from turbo_dllm_b200.kernels import build as kb
+    from turbo_dllm_b200.kernels import native
+
+    monkeypatch.delenv("DLLM_KERNEL_CHECKS", raising=False)
+    monkeypatch.delenv("TDLLM_KERNEL_CHECKS", raising=False)
+    assert native.library_path().name == kb.LIB_NAME and not kb.checks_requested()
+    monkeypatch.setenv("DLLM_KERNEL_CHECKS", "1")
+    assert native.library_path().name == kb.CHECKED_LIB_NAME and kb.checks_requested()
+    assert kb.CHECK_FLAGS == ["-DTDLLM_KERNEL_CHECKS=1"]
+    src = (kb.CSRC / "common.cuh").read_text()
+    assert "#ifdef TDLLM_KERNEL_CHECKS" in src and "ERR_BAD_INDEX" in src
+    users = [p.name for p in kb.all_source_files() if "TD_CHECKED(" in p.read_text() and p.name != "common.cuh"]
+    assert {"peer_pull.cuh", "comm.cu", "moe_dispatch.cu"} <= set(users)

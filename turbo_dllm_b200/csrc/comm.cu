@@ -181,6 +181,7 @@ __global__ void fsdp_gather_kernel(PeerPtrs shards, long long shard_off8, long l
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < unit_len8;
        i += (long long)gridDim.x * blockDim.x) {
     const int k = (int)(i / shard_len8);
+    if (!TD_CHECKED(k < world, KID_BARRIER, 0x200 + k)) continue;   // checked builds: the unit must fit its shards
     // the grid-stride walk spreads the blocks over all owners at any moment
     const long long j = i - (long long)k * shard_len8;
     out[i] = reinterpret_cast<const uint4*>(shards.p[k])[shard_off8 + j];

@@ -42,6 +42,17 @@ __device__ __forceinline__ void set_error(int code, int kernel_id, int detail) {
   }
 }
 
+// Checked builds (nvcc -DTDLLM_KERNEL_CHECKS, `dllm-build-kernels --checks`): TD_CHECKED(cond, kernel, detail)
+// is `cond`, and a false one records ERR_BAD_INDEX with the kernel id and `detail` so that the caller can skip the
+// access; the host reads the record after the stream syncs. In the regular build it is the constant true and the
+// compiler drops the test.
+#ifdef TDLLM_KERNEL_CHECKS
+#define TD_CHECKED(cond, kernel_id, detail) \
+  ((cond) ? true : (::tdllm::set_error(::tdllm::ERR_BAD_INDEX, (kernel_id), (int)(detail)), false))
+#else
+#define TD_CHECKED(cond, kernel_id, detail) (true)
+#endif
+
 __device__ __forceinline__ bool error_is_set() {
   return *((volatile int*)&g_tdllm_error[0]) != 0;
 }

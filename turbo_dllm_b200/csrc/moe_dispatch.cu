@@ -60,6 +60,7 @@ __global__ void dispatch_rows_kernel(const uint4* __restrict__ x, const int* __r
   const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long it = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5); it < items; it += warps) {
     const int e = experts[it];
+    if (!TD_CHECKED(e >= 0 && e / e_local < MAX_RANKS, KID_EP, 0x300)) continue;   // checked builds: a valid expert id
     long long p;
     if (pos_in) {
       p = pos_in[it];                       // the slot this item took in the forward pass

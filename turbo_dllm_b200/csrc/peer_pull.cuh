@@ -90,6 +90,12 @@ __device__ __forceinline__ void pull_remote_rows(const PullPlan& pl, int lane, i
         seen |= 1u << s;
       }
       const long long drow = pl.dst_begin[s] + (row - pl.seg_begin[s]);
+      // checked builds: the claim must lie inside its segment and map to a row of the destination buffer
+      if (!TD_CHECKED(s < pl.nseg && row >= pl.seg_begin[s] && run_end <= pl.seg_begin[s + 1] && drow >= 0,
+                      kernel_id, 0x100 + s)) {
+        ok = false;
+        break;
+      }
       if (first_dst < 0) first_dst = drow;
       const uint4* src = pl.src[s] + (row - pl.seg_begin[s]) * pl.row_vec16;
       uint4* dst = pl.dst + drow * pl.row_vec16;

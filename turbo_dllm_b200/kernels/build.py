@@ -28,6 +28,11 @@ CSRC = PKG_ROOT / "csrc"
 OUT_DIR = PKG_ROOT / "_C"
 LIB_NAME = "libtdllm_kernels.so"
 MANIFEST_NAME = "native_kernels.json"
+# the checked variant (-DTDLLM_KERNEL_CHECKS: index checks that record instead of accessing) lives beside the
+# regular library and is loaded when DLLM_KERNEL_CHECKS=1
+CHECKED_LIB_NAME = "libtdllm_kernels_checked.so"
+CHECKED_MANIFEST_NAME = "native_kernels_checked.json"
+CHECK_FLAGS = ["-DTDLLM_KERNEL_CHECKS=1"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-rdc=true",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
@@ -63,17 +68,21 @@ def source_hashes() -> dict[str, str]:
     return {f.name: _sha256(f) for f in all_source_files()}
 
 
-def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> tuple[str, str]:
-    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-Xptxas", "-v", "-c", str(src), "-o", str(obj)]
+def checks_requested() -> bool:
+    return os.environ.get("DLLM_KERNEL_CHECKS", os.environ.get("TDLLM_KERNEL_CHECKS", "0")) == "1"
+
+
+def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool, extra: tuple = ()) -> tuple[str, str]:
+    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *extra, "-Xptxas", "-v", "-c", str(src), "-o", str(obj)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src.name}:\n{proc.stdout}\n{proc.stderr}")
     return src.name, proc.stderr
 
 
-def is_current() -> bool:
-    man = OUT_DIR / MANIFEST_NAME
-    lib = OUT_DIR / LIB_NAME
+def is_current(checks: bool = False) -> bool:
+    man = OUT_DIR / (CHECKED_MANIFEST_NAME if checks else MANIFEST_NAME)
+    lib = OUT_DIR / (CHECKED_LIB_NAME if checks else LIB_NAME)
     if not man.exists() or not lib.exists():
         return False
     try:
@@ -83,20 +92,22 @@ def is_current() -> bool:
     return data.get("sources") == source_hashes() and data.get("binary_sha256") == _sha256(lib)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Builds the library if sources changed (or `force`). Returns the path of the .so."""
+def build(force: bool = False, verbose: bool = False, checks: bool = False) -> Path:
+    """Builds the library if sources changed (or `force`). Returns the path of the .so. `checks` builds the
+    checked variant (its own objects, library and manifest; the regular build is untouched)."""
     OUT_DIR.mkdir(parents=True, exist_ok=True)
-    lib = OUT_DIR / LIB_NAME
-    if not force and is_current():
+    lib = OUT_DIR / (CHECKED_LIB_NAME if checks else LIB_NAME)
+    if not force and is_current(checks):
         return lib
     nvcc = find_nvcc()
-    obj_dir = OUT_DIR / "obj"
+    obj_dir = OUT_DIR / ("obj_checked" if checks else "obj")
+    extra = tuple(CHECK_FLAGS) if checks else ()
     obj_dir.mkdir(exist_ok=True)
     t0 = time.time()
     srcs = sources()
     ptxas: dict[str, str] = {}
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        futs = [ex.submit(_compile_one, nvcc, s, obj_dir / (s.stem + ".o"), verbose) for s in srcs]
+        futs = [ex.submit(_compile_one, nvcc, s, obj_dir / (s.stem + ".o"), verbose, extra) for s in srcs]
         for f in futs:
             name, log = f.result()
             ptxas[name] = log
@@ -108,19 +119,20 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     ver = subprocess.run([nvcc, "--version"], capture_output=True, text=True).stdout.strip().splitlines()[-1]
     manifest = {
         "format": "turbo_dllm_b200.native_kernels.v1",
-        "library": LIB_NAME,
+        "library": lib.name,
         "arch": "sm_100a",
-        "flags": ARCH_FLAGS + NVCC_FLAGS,
+        "flags": ARCH_FLAGS + NVCC_FLAGS + list(extra),
+        "kernel_checks": bool(checks),
         "nvcc": ver,
         "sources": source_hashes(),
         "binary_sha256": _sha256(lib),
         "built_at": time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()),
         "build_seconds": round(time.time() - t0, 2),
     }
-    (OUT_DIR / MANIFEST_NAME).write_text(json.dumps(manifest, indent=1, sort_keys=True))
-    (OUT_DIR / "ptxas.log").write_text("\n".join(f"== {k}\n{v}" for k, v in ptxas.items()))
+    (OUT_DIR / (CHECKED_MANIFEST_NAME if checks else MANIFEST_NAME)).write_text(json.dumps(manifest, indent=1, sort_keys=True))
+    (OUT_DIR / ("ptxas_checked.log" if checks else "ptxas.log")).write_text("\n".join(f"== {k}\n{v}" for k, v in ptxas.items()))
     if verbose:
-        print((OUT_DIR / "ptxas.log").read_text())
+        print((OUT_DIR / ("ptxas_checked.log" if checks else "ptxas.log")).read_text())
     return lib
 
 
@@ -128,13 +140,15 @@ def main(argv: list[str] | None = None) -> int:
     ap = argparse.ArgumentParser(prog="dllm-build-kernels", description=__doc__.splitlines()[0])
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="print ptxas register/spill report")
+    ap.add_argument("--checks", action="store_true",
+                    help="build the checked variant (-DTDLLM_KERNEL_CHECKS), loaded when DLLM_KERNEL_CHECKS=1")
     args = ap.parse_args(argv)
     try:
-        lib = build(force=args.force, verbose=args.verbose)
+        lib = build(force=args.force, verbose=args.verbose, checks=args.checks)
     except RuntimeError as e:
         print(str(e), file=sys.stderr)
         return 2
-    print(json.dumps({"library": str(lib), "current": is_current()}))
+    print(json.dumps({"library": str(lib), "current": is_current(args.checks), "kernel_checks": args.checks}))
     return 0
 
 

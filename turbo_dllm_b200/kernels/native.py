@@ -51,11 +51,12 @@ def configure(policy: KernelRuntimePolicy) -> None:
 
 
 def library_path() -> Path:
-    return _build.OUT_DIR / _build.LIB_NAME
+    """The regular library, or the checked variant when DLLM_KERNEL_CHECKS=1."""
+    return _build.OUT_DIR / (_build.CHECKED_LIB_NAME if _build.checks_requested() else _build.LIB_NAME)
 
 
 def manifest() -> dict | None:
-    p = _build.OUT_DIR / _build.MANIFEST_NAME
+    p = _build.OUT_DIR / (_build.CHECKED_MANIFEST_NAME if _build.checks_requested() else _build.MANIFEST_NAME)
     if not p.exists():
         return None
     try:
@@ -143,7 +144,7 @@ def lib() -> ctypes.CDLL:
             if not _policy.allow_runtime_jit:
                 raise NativeKernelError("native kernels unusable: " + "; ".join(problems))
             try:
-                _build.build()
+                _build.build(checks=_build.checks_requested())
             except Exception as e:  # nvcc missing or compile error
                 raise NativeKernelError(f"native kernels unusable ({'; '.join(problems)}) and "
                                         f"rebuild failed: {e}") from e
