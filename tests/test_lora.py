@@ -47,3 +47,60 @@ def test_unknown_role_is_rejected():
         apply_lora(model, rank=4, targets=("router",))
     with pytest.raises(ValueError):
         apply_lora(model, rank=0)
+
+
+def test_expert_adapters_train_and_merge():
+    """Mixture-of-experts decoder: replicated pairs on the attention projections, per-expert pairs on the stacked
+    gate/up and down weights; the frozen experts get no gradient, merging reproduces the adapted model."""
+    from turbo_dllm_b200.models.moe import MoEBlockDiffusionTransformer
+
+    cfg = PRESETS["synthetic:tiny-moe"]
+    model = MoEBlockDiffusionTransformer(cfg, dtype=torch.float32, seed=2, init_std=0.05)
+    st = apply_lora(model, rank=4, alpha=8.0, targets=("attention", "experts"), seed=3)
+    assert st.flat_experts is not None and all(b.lora is st for b in (l.experts for l in model.layers))
+    with torch.no_grad():
+        for flat in (st.flat, st.flat_experts):
+            for n, p in flat.params.items():
+                if n.endswith("lora_B"):
+                    p.normal_(0, 0.05)
+    layout = build_packed_layout(seq_len=64, block_size=16, batch=1, views=1)
+    tokens = torch.randint(0, cfg.vocab_size, (layout.rows,), generator=torch.Generator().manual_seed(4))
+    for f in (st.flat, st.flat_experts, model.flat_experts):
+        f.zero_grad()
+    model.flat_experts.grad.zero_()
+    _run(model, tokens, layout).square().sum().backward()
+    st.flat.collect_grads()
+    st.flat_experts.collect_grads()
+    assert st.flat.grad.abs().sum() > 0 and st.flat_experts.grad.abs().sum() > 0
+    assert model.flat_experts.grad.abs().sum() == 0           # the experts themselves are frozen
+    with torch.no_grad():
+        adapted = _run(model, tokens, layout)
+        merge_lora(model)
+        for layer in model.layers:
+            layer.lora = None
+            layer.experts.lora = None
+        model.lora = None
+        merged = _run(model, tokens, layout)
+    assert torch.allclose(adapted, merged, atol=3e-4, rtol=1e-3)
+
+
+def test_moe_session_trains_only_the_adapters():
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-moe", "seq_len": 64, "dtype": "fp32", "family": "diffusion_gemma"},
+        "objective": {"name": "standard_block_diffusion", "block_size": 16, "sampling_epsilon_min": 0.1},
+        "adapter": {"type": "lora", "rank": 4, "alpha": 8.0, "targets": ["attention", "experts"]},
+        "training": {"batch_size": 2, "steps": 3},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
+        "optimizer": {"lr": 1e-2, "gradient_clip_norm": 1.0}}).validate()
+    s = TrainingSession(spec, device="cpu")
+    base = s.model.flat.data.clone(), s.model.flat_experts.data.clone()
+    a0 = s.lora.flat_experts.data.clone()
+    losses = [float(r.loss_sum) / r.denominator for r in (s.step() for _ in range(4))]
+    assert losses[-1] < losses[0]
+    assert torch.equal(s.model.flat.data, base[0]) and torch.equal(s.model.flat_experts.data, base[1])
+    assert not torch.equal(s.lora.flat_experts.data, a0)
+    state = s.state_dict()
+    assert "adapter" in state and "adapter_experts" in state

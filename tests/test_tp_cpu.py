@@ -69,3 +69,49 @@ def test_tp2_with_sequence_parallel_rows_matches_single_process():
         full = ref[3]
         n = full.shape[1] // 2
         assert torch.allclose(torch.from_numpy(w_down), full[:, r * n:(r + 1) * n], rtol=1e-3, atol=1e-4)
+
+
+def _run_lora(rank, world, tp, steps, sp=False):
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    torch.set_num_threads(2)
+    m = copy.deepcopy(MAPPING)
+    m["topology"]["tensor_parallel_size"] = tp
+    m["topology"]["sequence_parallel"] = bool(sp)
+    m["adapter"] = {"type": "lora", "rank": 4, "alpha": 8.0, "targets": ["attention", "mlp"]}
+    m["optimizer"]["lr"] = 1e-2
+    spec = RunSpec.from_mapping(m).validate(world_size=world)
+    rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
+    s = TrainingSession(spec, device="cpu", runtime=rt)
+    losses, norms = [], []
+    for _ in range(steps):
+        r = s.step()
+        losses.append(float(r.loss_sum) / r.denominator)
+        norms.append(s.optimizer.grad_norm())
+    p = {n: t.detach().clone() for n, t in s.lora.flat.params.items()}
+    return (losses, norms, p["layers.0.w_qkv.lora_A"], p["layers.1.w_down.lora_B"], p["layers.1.w_down.lora_A"],
+            p["layers.0.w_gate_up.lora_B"])
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("sp", [False, True])
+def test_lora_under_tensor_parallelism_matches_single_process(sp):
+    """Adapters with the projections' local shapes: column-parallel B and row-parallel A are shards, the other
+    halves are replicated and stay equal on both ranks (under sequence parallelism through the partial-gradient
+    sum); losses, gradient norms and adapter weights follow the single-process LoRA run."""
+    ref = _run_lora(0, 1, 1, 3)
+    assert ref[0][-1] < ref[0][0]                      # the adapters do train
+    outs = run_ranks(_run_lora, 2, args=(2, 3, sp), deadline_s=240)
+    for r, (losses, norms, qkv_a, down_b, down_a, gu_b) in enumerate(outs):
+        assert losses == pytest.approx(ref[0], rel=3e-4, abs=3e-4)
+        assert norms == pytest.approx(ref[1], rel=3e-3)
+        assert torch.allclose(torch.from_numpy(qkv_a), ref[2], rtol=2e-3, atol=2e-5)       # replicated A
+        assert torch.allclose(torch.from_numpy(down_b), ref[3], rtol=2e-3, atol=2e-5)      # replicated B
+        full = ref[4]
+        n = full.shape[1] // 2
+        assert torch.allclose(torch.from_numpy(down_a), full[:, r * n:(r + 1) * n], rtol=2e-3, atol=2e-5)
+        full = ref[5]
+        n = full.shape[0] // 2
+        assert torch.allclose(torch.from_numpy(gu_b), full[r * n:(r + 1) * n], rtol=2e-3, atol=2e-5)

@@ -34,7 +34,9 @@ class BackboneCapabilities:
     parameter_sharding: bool = False       # optimizer.backend: fsdp
     lora: bool = False
     activation_offload: bool = True
-    head_dims: tuple[int, ...] = (128,)    # head sizes the sm_100a attention kernels cover for this family
+    # head sizes the sm_100a attention covers for this family: 128 in one kernel; 64, 256 and 512 as tensor-core
+    # products around the masked-softmax kernels (ops/wide_attention.py)
+    head_dims: tuple[int, ...] = (64, 128, 256, 512)
 
 
 @dataclass(frozen=True)
@@ -160,7 +162,7 @@ class DenseExecutor(_ExecutorBase):
 class MoEExecutor(_ExecutorBase):
     """DiffusionGemma-style routed experts (dllm_parallel/core/models/backbones/diffusiongemma/model.py:33-460)."""
 
-    capabilities = BackboneCapabilities(expert_parallel=True)
+    capabilities = BackboneCapabilities(expert_parallel=True, lora=True)
     kernel_policy = BackboneKernelPolicy(optional_symbols=("tdllm_gemm_grouped_bf16", "tdllm_ep_dispatch"))
 
     def __init__(self, family: ModelFamilySpec):

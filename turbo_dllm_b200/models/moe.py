@@ -83,6 +83,7 @@ class ExpertBank(nn.Module):
         self.ep = dist.get_world_size(ep_group) if ep_group is not None else 1
         self.ep_rank = dist.get_rank(ep_group) if ep_group is not None else 0
         self.e_local = self.w_gu.shape[0]
+        self.lora = None               # adapters.lora.LoRAState with per-expert pairs, set by apply_lora
         self.last_counts = None
         self.exchange_holder = None    # set by the model: one PeerExpertExchange shared by all layers
 
@@ -94,6 +95,8 @@ class ExpertBank(nn.Module):
         from ..ops.grouped import grouped_supported
 
         holder = self.exchange_holder
+        if self.lora is not None:       # per-expert adapters run on the per-expert path
+            return None
         if (holder is None or self.ep < 2 or not x.is_cuda or os.environ.get("TDLLM_EP_PEER", "1") == "0"
                 or not grouped_supported(x, self.w_gu) or not grouped_supported(x, self.w_down)):
             return None
@@ -118,6 +121,8 @@ class ExpertBank(nn.Module):
         gradients land in the experts' slices of the flat gradient buffer either way."""
         from ..ops.grouped import build_grouped_rows, grouped_linear, grouped_supported
 
+        if self.lora is not None:
+            return self._local_experts_lora(x_sorted, counts)
         if x_sorted.shape[0] > 0 and grouped_supported(x_sorted, self.w_gu) and grouped_supported(x_sorted, self.w_down):
             g = build_grouped_rows(counts, x_sorted.shape[0])
             x_pad = x_sorted.new_zeros(g.capacity, x_sorted.shape[1]).index_copy(0, g.dest, x_sorted)
@@ -183,6 +188,33 @@ class ExpertBank(nn.Module):
         return out
 
 
+def _local_experts_lora(bank, x_sorted: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+    """Per-expert slabs with low-rank updates: y_e = x·W_eᵀ + s·(x·A_eᵀ)·B_eᵀ for both projections; the frozen
+    expert weights get no gradient, the adapters' gradients go to their experts' slices."""
+    st = bank.lora
+    gu_pair, dn_pair = st.expert_pair(bank.idx, "experts_gate_up"), st.expert_pair(bank.idx, "experts_down")
+
+    def proj(x, w_all, pair, e):
+        y = _expert_linear(x, w_all, e)
+        if pair is None:
+            return y
+        if st.dropout > 0 and torch.is_grad_enabled():
+            x = torch.nn.functional.dropout(x, st.dropout)
+        return y + _expert_linear(_expert_linear(x, pair[0], e), pair[1], e) * st.scale
+
+    outs, off = [], 0
+    for e, n in enumerate(counts.tolist()):
+        if n == 0:
+            continue
+        xe = x_sorted[off:off + n]
+        outs.append(proj(swiglu(proj(xe, bank.w_gu, gu_pair, e)), bank.w_down, dn_pair, e))
+        off += n
+    return torch.cat(outs, dim=0) if outs else x_sorted.new_zeros(0, x_sorted.shape[1])
+
+
+ExpertBank._local_experts_lora = _local_experts_lora
+
+
 class _ExpertLinear(torch.autograd.Function):
     """y = x · W[e]ᵀ for one expert of a stacked weight; dW goes to that expert's gradient slice."""
 
@@ -203,6 +235,8 @@ class _ExpertLinear(torch.autograd.Function):
         e = ctx.e
         dy = dy.contiguous()
         dx = gemm(dy, w_all[e], b_mn_major=True)
+        if not ctx.needs_input_grad[1]:      # a frozen stacked weight (adapters train instead)
+            return dx, None, None
         sink, _ = grad_sink(ctx.wref)
         if sink is not None:
             written = ctx.wref.expert_written
@@ -231,6 +265,19 @@ class MoEDecoderLayer(nn.Module):
     def forward(self, h, positions, inv_freq, attend):
         cfg = self.cfg
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
+        st = getattr(self, "lora", None)
+        if st is not None:
+            from ..adapters.lora import lora_delta
+
+            def proj(x, name):
+                out, pair = linear(x, getattr(self, name)), st.pair(self.idx, name)
+                return out if pair is None else out + lora_delta(x, pair[0], pair[1], st.scale, st.dropout)
+
+            qkv = qk_norm_rope(proj(y, "w_qkv"), positions, inv_freq, self.q_norm, self.k_norm,
+                               cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
+            h = h + proj(attend(qkv, self.idx), "w_o")
+            y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
+            return h + self.experts(y2)
         qkv = qk_norm_rope(linear(y, self.w_qkv), positions, inv_freq, self.q_norm, self.k_norm,
                            cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
         h = linear_residual(attend(qkv, self.idx), self.w_o, h)

@@ -121,7 +121,10 @@ class FlatAdamW:
             # tensor-parallel shards of the matrices add up over the TP group; replicated norm
             # weights (the non-decayed tail of the buffer) must be counted once
             n = self.stop - self.start
-            split = min(max(self.flat.decay_numel - self.start, 0), n)
+            # (a buffer may name the end of its sharded part itself: adapters decay all their matrices but
+            # replicate some of them)
+            sharded_end = getattr(self.flat, "tp_sharded_numel", self.flat.decay_numel)
+            split = min(max(sharded_end - self.start, 0), n)
             sharded = self._grad_sumsq(self._gshard[:split]).clone() if split > 0 else torch.zeros(
                 1, device=self._gshard.device)
             dist.all_reduce(sharded, op=dist.ReduceOp.SUM, group=self.tp_group)

@@ -86,11 +86,13 @@ class TrainingSession:
         if spec.adapter.type == "lora":
             from ..adapters.lora import apply_lora
 
-            if self.cfg.is_moe or getattr(self.model, "tp", None) is not None:
-                raise ValueError("LoRA adapters support dense models on one tensor-parallel rank")
+            tp_ctx = getattr(self.model, "tp", None)
+            if tp_ctx is not None and self.cfg.is_hybrid:
+                raise ValueError("LoRA adapters support the dense decoder at any tensor-parallel degree, the "
+                                 "mixture-of-experts decoder, and the hybrid family on one tensor-parallel rank")
             self.lora = apply_lora(self.model, rank=spec.adapter.rank, alpha=spec.adapter.alpha,
                                    dropout=spec.adapter.dropout, targets=spec.adapter.targets or ("attention", "mlp"),
-                                   seed=seed)
+                                   seed=seed, tp=tp_ctx)
         keep = os.environ.get("TDLLM_KEEP_ATTENTION")
         _, off_attn, keep_attn, resident = self._memory_plan()
         self.model.store.keep_attention = (keep == "1") if keep is not None else keep_attn
@@ -133,8 +135,13 @@ class TrainingSession:
             dense_group = runtime.group("dense_optimizer") if runtime is not None else (
                 dist.group.WORLD if self.world > 1 else None)
             expert_group = runtime.optimizer_group if runtime is not None else dense_group
-            self.optimizer = FlatAdamW(self.model.flat, group=dense_group, **okw)
-            self.expert_optimizer = FlatAdamW(self.model.flat_experts, group=expert_group, **okw)
+            if self.lora is not None:     # only the adapters train: replicated pairs and per-expert pairs
+                self.optimizer = FlatAdamW(self.lora.flat, group=dense_group, **okw)
+                if self.lora.flat_experts is not None:
+                    self.expert_optimizer = FlatAdamW(self.lora.flat_experts, group=expert_group, **okw)
+            else:
+                self.optimizer = FlatAdamW(self.model.flat, group=dense_group, **okw)
+                self.expert_optimizer = FlatAdamW(self.model.flat_experts, group=expert_group, **okw)
             self.ep_group = runtime.group("expert") if ep > 1 else None
         else:
             group = runtime.optimizer_group if runtime is not None else (dist.group.WORLD if self.world > 1 else None)
@@ -196,7 +203,7 @@ class TrainingSession:
 
     def flats(self):
         if getattr(self, "lora", None) is not None:
-            return [self.lora.flat]
+            return [self.lora.flat] + ([self.lora.flat_experts] if self.lora.flat_experts is not None else [])
         out = [self.model.flat]
         if getattr(self.model, "flat_experts", None) is not None:
             out.append(self.model.flat_experts)
@@ -532,6 +539,8 @@ class TrainingSession:
             from ..parallel.tensor_parallel import sync_partial_gradients
 
             sync_partial_gradients(self.model.flat.params.values(), tp)
+            if getattr(self, "lora", None) is not None:
+                sync_partial_gradients(self.lora.flat.params.values(), tp)
 
     def _phase(self, name: str):
         return self.phase_timer.phase(name, self.trace)
@@ -622,6 +631,8 @@ class TrainingSession:
         if getattr(self, "lora", None) is not None:
             # the adapters are what training changes; every rank holds the whole (replicated) adapter buffer
             extra["adapter"] = self.lora.flat.data
+            if self.lora.flat_experts is not None:       # this expert-parallel rank's per-expert pairs
+                extra["adapter_experts"] = self.lora.flat_experts.data
         model_state = self.sharded.param_shard if self.sharded is not None else self.model.flat.data
         return {**extra, "model": model_state, "optimizer": self.optimizer.state_dict(),
                 "scheduler": self.scheduler.state_dict(), "objective": self.objective.state_dict(),
@@ -631,6 +642,8 @@ class TrainingSession:
         (self.sharded.param_shard if self.sharded is not None else self.model.flat.data).copy_(state["model"])
         if getattr(self, "lora", None) is not None and "adapter" in state:
             self.lora.flat.data.copy_(state["adapter"])
+            if self.lora.flat_experts is not None and "adapter_experts" in state:
+                self.lora.flat_experts.data.copy_(state["adapter_experts"])
         self.optimizer.load_state_dict(state["optimizer"])
         # the optimizer restored this rank's shard of its buffer from the fp32 master; the other shards come
         # from their owners (a no-op on one rank)
