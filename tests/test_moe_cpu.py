@@ -64,3 +64,58 @@ def test_expert_parallel_training_keeps_dense_parameters_in_sync():
     assert not (a[2] == b[2]).all()        # different experts per rank
     assert a[3] == pytest.approx(b[3], rel=1e-6)   # one global gradient norm
     assert all(l == l and l > 0 for l in a[0] + b[0])
+
+
+def test_shared_dense_branch_and_replayed_routes():
+    """A layer with a dense feed-forward beside its experts equals experts + dense branch computed by hand, and a
+    checkpointed layer's recomputation takes the experts its first pass chose."""
+    from dataclasses import replace
+
+    from turbo_dllm_b200.models.config import PRESETS
+    from turbo_dllm_b200.models.dense import LocalAttention
+    from turbo_dllm_b200.models.moe import MoEBlockDiffusionTransformer
+    from turbo_dllm_b200.parallel.layout import build_packed_layout
+
+    cfg = replace(PRESETS["synthetic:tiny-moe"], moe_shared_intermediate_size=96)
+    m = MoEBlockDiffusionTransformer(cfg, dtype=torch.float32, seed=5, init_std=0.05, activation_checkpointing=True)
+    layer = m.layers[0]
+    assert layer.w_gate_up.shape == (192, cfg.hidden_size) and layer.w_down.shape == (cfg.hidden_size, 96)
+    lay = build_packed_layout(seq_len=64, block_size=16, batch=1)
+    attend = LocalAttention(cfg, lay.mask)
+    h = torch.randn(lay.rows, cfg.hidden_size) * 0.3
+    with torch.no_grad():
+        out = layer(h, lay.positions, m.inv_freq, attend)
+        w_gu, w_dn = layer.w_gate_up, layer.w_down
+        layer.w_gate_up = layer.w_down = None
+        base = layer(h, lay.positions, m.inv_freq, attend)
+        layer.w_gate_up, layer.w_down = w_gu, w_dn
+        from turbo_dllm_b200.ops.norm import rmsnorm
+        from turbo_dllm_b200.ops.gemm import linear_residual
+        from turbo_dllm_b200.ops.rope import qk_norm_rope
+        from turbo_dllm_b200.ops.gemm import linear
+
+        y, _ = rmsnorm(h, layer.input_norm, cfg.rms_norm_eps)
+        qkv = qk_norm_rope(linear(y, layer.w_qkv), lay.positions, m.inv_freq, layer.q_norm, layer.k_norm,
+                           cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
+        h1 = linear_residual(attend(qkv, 0), layer.w_o, h)
+        y2, _ = rmsnorm(h1, layer.post_norm, cfg.rms_norm_eps)
+        gu = y2 @ w_gu.t()
+        dense = (torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]) @ w_dn.t()
+    assert torch.allclose(out, base + dense, rtol=1e-4, atol=1e-5)
+    # whole model under checkpointing: the replay finds the recorded routes and uses them
+    tokens = torch.randint(0, cfg.vocab_size, (lay.rows,), generator=torch.Generator().manual_seed(1))
+    seen = []
+    bank = m.layers[1].experts
+    orig = bank._route
+
+    def spy(logits, k):
+        had = bank.store.replaying and bank.store.has((1, "moe_route"))
+        w, idx = orig(logits, k)
+        seen.append((bool(bank.store.recording), bool(had), idx.clone()))
+        return w, idx
+
+    bank._route = spy
+    m(tokens, lay.positions, attend).square().sum().backward()
+    assert [s[:2] for s in seen] == [(True, False), (False, True)] and torch.equal(seen[0][2], seen[1][2])
+    assert not any(isinstance(k, tuple) and k[1] == "moe_route" for k in m.store.kept)
+    assert m.flat.params["layers.0.w_gate_up"].main_grad.abs().sum() > 0

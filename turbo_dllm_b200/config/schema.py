@@ -70,6 +70,8 @@ SECTIONS: dict[str, tuple[F, ...]] = {
         F("num_experts", OPT_INT, None, ext=True),
         F("num_experts_per_token", OPT_INT, None, ext=True),
         F("moe_intermediate_size", OPT_INT, None, ext=True),
+        F("moe_shared_intermediate_size", OPT_INT, None, ext=True,
+          help="width of the dense feed-forward every token passes beside its routed experts"),
         F("dflash2_conv_kernel_size", OPT_INT, None),
         F("dflash2_conv_group_size", OPT_INT, None),
         F("dflash2_selector_rank", OPT_INT, None),

@@ -28,6 +28,8 @@ class ModelConfig:
     num_experts: int = 0
     num_experts_per_token: int = 0
     moe_intermediate_size: int = 0
+    # a dense SwiGLU feed-forward that every token passes beside its routed experts (0 = none)
+    moe_shared_intermediate_size: int = 0
     # sliding-window layers: a layer whose window is set lets a row see only the last `sliding_window` clean
     # positions before its clean stop. Which layers slide: `layer_types` ("sliding_attention" / "full_attention"
     # per layer) when given, else every layer except each `sliding_window_pattern`-th one (0: all layers slide).
@@ -113,7 +115,8 @@ class ModelConfig:
             n_full = sum(self.layer_kind(i) == "full_attention" for i in range(self.num_layers))
             attn = (n_full * full + (self.num_layers - n_full) * lin) // max(self.num_layers, 1)
         if self.is_moe:
-            ffn = self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
+            ffn = (self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
+                   + 3 * h * self.moe_shared_intermediate_size)
         else:
             ffn = 3 * h * self.intermediate_size
         return attn + ffn + 2 * h
@@ -171,7 +174,7 @@ def model_config_from_run_spec(spec) -> ModelConfig:
     over = {}
     for name in ("vocab_size", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
                  "intermediate_size", "rope_theta", "mask_token_id", "num_experts", "num_experts_per_token",
-                 "moe_intermediate_size", "full_attention_interval", "linear_num_key_heads",
+                 "moe_intermediate_size", "moe_shared_intermediate_size", "full_attention_interval", "linear_num_key_heads",
                  "linear_num_value_heads", "linear_key_head_dim", "linear_value_head_dim", "linear_conv_kernel",
                  "sliding_window", "sliding_window_pattern"):
         v = getattr(m, name)

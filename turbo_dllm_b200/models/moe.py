@@ -87,6 +87,23 @@ class ExpertBank(nn.Module):
         self.last_counts = None
         self.exchange_holder = None    # set by the model: one PeerExpertExchange shared by all layers
 
+    def _route(self, logits: torch.Tensor, k: int):
+        """Top-k routing that a checkpointed layer's recomputation repeats exactly: the no-grad forward keeps the
+        chosen experts, the replay takes them from there and only recomputes the (differentiable) weights, so a
+        near-tie in the router logits cannot send a token elsewhere the second time.
+        Role of the route record / replay of dllm_parallel/core/models/backbones/moe_checkpoint.py:22-59."""
+        store = getattr(self, "store", None)
+        key = (self.idx, "moe_route")
+        if store is not None and store.replaying and store.has(key):
+            idx = store.kept.pop(key)
+            probs = torch.softmax(logits.float(), dim=-1)
+            w = probs.gather(1, idx)
+            return w / w.sum(-1, keepdim=True), idx
+        w, idx = route_topk(logits, k)
+        if store is not None and store.recording and not torch.is_grad_enabled():
+            store.kept[key] = idx        # a few bytes per row: never sent to the host
+        return w, idx
+
     def _peer_exchange(self, x: torch.Tensor):
         """The peer-memory dispatch / combine state, or None (CPU, no peer access, shapes off the tile grid,
         TDLLM_EP_PEER=0): the caller then uses all-to-all collectives."""
@@ -144,7 +161,7 @@ class ExpertBank(nn.Module):
         cfg = self.cfg
         rows, H = x.shape
         k = cfg.num_experts_per_token
-        w, idx = route_topk(linear(x, self.router), k)
+        w, idx = self._route(linear(x, self.router), k)
         ex = self._peer_exchange(x)
         if ex is not None:
             # rows go straight into the owners' slabs and come back weighted: no sort, no collective, no host read
@@ -260,6 +277,10 @@ class MoEDecoderLayer(nn.Module):
         self.input_norm, self.w_qkv, self.w_o, self.post_norm = g("input_norm"), g("w_qkv"), g("w_o"), g("post_norm")
         self.q_norm = g("q_norm") if cfg.qk_norm else None
         self.k_norm = g("k_norm") if cfg.qk_norm else None
+        # dual feed-forward: a dense SwiGLU branch in parallel with the routed experts
+        # (dllm_parallel/core/models/backbones/nemotron/model.py:2612-2919)
+        self.w_gate_up = g("w_gate_up") if cfg.moe_shared_intermediate_size > 0 else None
+        self.w_down = g("w_down") if cfg.moe_shared_intermediate_size > 0 else None
         self.experts = ExpertBank(cfg, idx, flat, ep_group)
 
     def forward(self, h, positions, inv_freq, attend):
@@ -277,12 +298,18 @@ class MoEDecoderLayer(nn.Module):
                                cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
             h = h + proj(attend(qkv, self.idx), "w_o")
             y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
-            return h + self.experts(y2)
+            out = h + self.experts(y2)
+            return out if self.w_gate_up is None else out + proj(swiglu(proj(y2, "w_gate_up")), "w_down")
         qkv = qk_norm_rope(linear(y, self.w_qkv), positions, inv_freq, self.q_norm, self.k_norm,
                            cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
         h = linear_residual(attend(qkv, self.idx), self.w_o, h)
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
-        return h + self.experts(y2)
+        out = h + self.experts(y2)
+        if self.w_gate_up is None:
+            return out
+        from ..ops.gemm import linear_swiglu
+
+        return linear_residual(linear_swiglu(y2, self.w_gate_up), self.w_down, out)
 
 
 def moe_layer_specs(cfg: ModelConfig, i: int, e_local: int):
@@ -291,6 +318,9 @@ def moe_layer_specs(cfg: ModelConfig, i: int, e_local: int):
            (p + "post_norm", (h,), False), (p + "router", (cfg.num_experts, h), True),
            (p + "experts_gate_up", (e_local, 2 * cfg.moe_intermediate_size, h), True),
            (p + "experts_down", (e_local, h, cfg.moe_intermediate_size), True)]
+    if cfg.moe_shared_intermediate_size > 0:
+        out += [(p + "w_gate_up", (2 * cfg.moe_shared_intermediate_size, h), True),
+                (p + "w_down", (h, cfg.moe_shared_intermediate_size), True)]
     if cfg.qk_norm:
         out += [(p + "q_norm", (cfg.head_dim,), False), (p + "k_norm", (cfg.head_dim,), False)]
     return out
@@ -338,6 +368,7 @@ class MoEBlockDiffusionTransformer(BlockDiffusionTransformer):
         self.expert_exchange = {}      # filled on the first routed batch on a GPU (parallel/expert_exchange.py)
         for layer in self.layers:
             layer.experts.exchange_holder = self.expert_exchange
+            layer.experts.store = self.store
         self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device), persistent=False)
         ep_rank = dist.get_rank(ep_group) if ep_group is not None else 0
         self.reset_parameters(seed, init_std)

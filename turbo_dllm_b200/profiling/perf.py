@@ -67,7 +67,8 @@ class StepFlops:
 def transformer_step_flops(cfg: ModelConfig, *, rows: int, pairs: int, vocab_rows: int) -> StepFlops:
     h = cfg.hidden_size
     if cfg.is_moe:
-        ffn = 3 * h * cfg.moe_intermediate_size * cfg.num_experts_per_token + h * cfg.num_experts
+        ffn = (3 * h * cfg.moe_intermediate_size * cfg.num_experts_per_token + h * cfg.num_experts
+               + 3 * h * cfg.moe_shared_intermediate_size)
     else:
         ffn = 3 * h * cfg.intermediate_size
     per_row = h * cfg.qkv_dim + cfg.q_dim * h + ffn
