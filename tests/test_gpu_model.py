@@ -73,3 +73,63 @@ def test_training_steps_run_and_update_parameters():
     assert all(l == l and l > 0 for l in losses)
     assert not torch.equal(before, s.model.flat.data)
     assert s.optimizer.grad_norm() > 0
+
+
+def _moe_spec(dtype, extra_model=None, adapter=None):
+    from turbo_dllm_b200.config.run_spec import RunSpec
+
+    m = {"model": {"id": "synthetic:tiny-moe-hd128", "seq_len": 256, "dtype": dtype, "family": "diffusion_gemma",
+                   **(extra_model or {})},
+         "objective": {"name": "standard_block_diffusion", "block_size": 32, "sampling_epsilon_min": 0.1},
+         "training": {"batch_size": 2, "steps": 2, "activation_checkpointing": True},
+         "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
+         "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}
+    if adapter:
+        m["adapter"] = adapter
+    return RunSpec.from_mapping(m).validate()
+
+
+def test_moe_with_shared_dense_branch_matches_cpu_loss_and_replays_routes():
+    """One GPU, routed experts (grouped GEMMs) plus the dense feed-forward beside them, under activation
+    checkpointing: the first loss equals the fp32 CPU path, the recomputation uses the recorded routes."""
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    extra = {"moe_shared_intermediate_size": 256}
+    g = TrainingSession(_moe_spec("bf16", extra), device="cuda")
+    c = TrainingSession(_moe_spec("fp32", extra), device="cpu")
+    c.model.flat.data.copy_(g.model.flat.data.float().cpu())
+    c.model.flat_experts.data.copy_(g.model.flat_experts.data.float().cpu())
+    rg, rc = g.step(), c.step()
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    lg, lc = float(rg.loss_sum) / rg.denominator, float(rc.loss_sum) / rc.denominator
+    assert lg == pytest.approx(lc, rel=3e-2)
+    assert not any(isinstance(k, tuple) and k[1] == "moe_route" for k in g.model.store.kept)
+    assert float(g.step().loss_sum) > 0
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_lora_adapters_train_on_the_gpu(moe):
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.kernels import native
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    if moe:
+        spec = _moe_spec("bf16", adapter={"type": "lora", "rank": 8, "alpha": 16.0, "targets": ["attention", "experts"]})
+    else:
+        spec = RunSpec.from_mapping({
+            "model": {"id": "synthetic:tiny-hd128", "seq_len": 256, "dtype": "bf16"},
+            "objective": {"name": "standard_block_diffusion", "block_size": 32, "sampling_epsilon_min": 0.1},
+            "adapter": {"type": "lora", "rank": 8, "alpha": 16.0, "targets": ["attention", "mlp"]},
+            "training": {"batch_size": 2, "steps": 2}, "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
+            "optimizer": {"lr": 1e-2, "gradient_clip_norm": 1.0}}).validate()
+    s = TrainingSession(spec, device="cuda")
+    base = s.model.flat.data.clone()
+    before = [f.data.clone() for f in s.flats()]
+    losses = [float(r.loss_sum) / r.denominator for r in (s.step() for _ in range(3))]
+    torch.cuda.synchronize()
+    native.raise_on_device_error()
+    assert all(l == l and l > 0 for l in losses)
+    assert torch.equal(s.model.flat.data, base)
+    assert all(not torch.equal(f.data, b) for f, b in zip(s.flats(), before))
