@@ -67,3 +67,59 @@ def test_bytes_model_prefers_queries_at_long_context():
     assert not prefer_query_rotation(draft_rows=2048 * 16 // 2, context_rows_per_rank=4096 // 2, **kw)
     assert not prefer_query_rotation(draft_rows=16, context_rows_per_rank=1 << 20, ranks=1, q_heads=32, kv_heads=8,
                                      head_dim=128)
+
+
+def _run_offline(rank, world, cp, bp, mode, store, steps=2):
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    torch.set_num_threads(2)
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "family": "dflash",
+                  "verifier_id": "synthetic:tiny-qwen3", "target_layer_ids": [0, 2], "max_layers": 2},
+        "objective": {"name": "dflash_distillation", "block_size": 8, "max_anchors": 4},
+        "data": {"target_features": "offline", "target_feature_path": store},
+        "training": {"batch_size": 2, "steps": steps},
+        "topology": {"context_parallel_size": cp, "block_parallel_size": bp},
+        "kernel": {"dflash_context_exchange": mode},
+        "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
+    rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
+    s = TrainingSession(spec, device="cpu", runtime=rt)
+    losses, shard_rows = [], None
+    for _ in range(steps):
+        t = s.step().loss_sum.double().clone()
+        if world > 1:
+            dist.all_reduce(t)
+        losses.append(float(t))
+    b = s.data.next_batch()
+    shard_rows = (int(b.features["hidden"].shape[0]), bool(b.features.get("hidden_is_shard", False)),
+                  type(b.features["final_hidden"]).__name__)
+    return losses, s.model.flat.data.clone(), shard_rows
+
+
+@pytest.mark.distributed
+def test_offline_store_feeds_a_context_sharded_replica_its_shard_only(tmp_path):
+    """Training from the feature store with the context divided over two ranks: each rank reads half of the hidden
+    rows from the memory-mapped record, takes the teacher rows it needs from the host copy, and the step equals the
+    single-process one."""
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.data.dflash_features import capture_features
+
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "family": "dflash",
+                  "verifier_id": "synthetic:tiny-qwen3", "target_layer_ids": [0, 2], "max_layers": 2},
+        "objective": {"name": "dflash_distillation", "block_size": 8, "max_anchors": 4},
+        "data": {"target_features": "online"}, "training": {"batch_size": 2, "steps": 3},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1}, "optimizer": {"lr": 1e-3}}).validate()
+    store = str(tmp_path / "features")
+    capture_features(spec, store, batches=4)
+    ref_losses, ref_params, ref_rows = _run_offline(0, 1, 1, 1, "auto", store)
+    assert ref_rows[0] == 2 * 64 and not ref_rows[1]
+    outs = run_ranks(_run_offline, 2, args=(2, 2, "query_rotation", store), deadline_s=240)
+    for losses, params, rows in outs:
+        assert rows[0] == 64 and rows[1]                      # half of the 128 context rows of a record
+        assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-5)
+        assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=2e-5)

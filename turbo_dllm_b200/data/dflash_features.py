@@ -55,10 +55,16 @@ class FeatureStoreDataRuntime:
     memory while the current step runs. Counterpart of DFlashFeatureDataRuntime
     (dllm_parallel/core/models/backbones/dflash/data.py:248-630)."""
 
-    def __init__(self, store: "FeatureStore", *, batch_size: int, device, dp_rank: int = 0, dp_size: int = 1):
+    def __init__(self, store: "FeatureStore", *, batch_size: int, device, dp_rank: int = 0, dp_size: int = 1,
+                 context_rows=None):
+        """context_rows(batch, seq_len) -> rows of the [batch * seq_len, ...] hidden states this rank attends to
+        (a replica that spans several ranks shards the context): only those rows are read from the memory-mapped
+        record and sent to the device, and the teacher states stay memory-mapped on the host until the step knows
+        which positions its anchors need. A 256K-token record then costs a rank its shard, not the sequence."""
         from .runtimes import DataBatch  # noqa: F401
 
         self.store, self.device = store, torch.device(device)
+        self.context_rows = context_rows
         self.batch_size, self.dp_rank, self.dp_size = batch_size, dp_rank, dp_size
         if len(store.manifest["shards"]) < dp_size:
             raise ValueError(f"feature store has {len(store.manifest['shards'])} records, fewer than the {dp_size} "
@@ -69,12 +75,22 @@ class FeatureStoreDataRuntime:
     def _load(self, step: int) -> dict:
         shards = self.store.manifest["shards"]
         sh = shards[(step * self.dp_size + self.dp_rank) % len(shards)]
-        rec = torch.load(os.path.join(self.store.root, sh["name"]), map_location="cpu")
+        path = os.path.join(self.store.root, sh["name"])
+        lazy = self.context_rows is not None
+        try:
+            rec = torch.load(path, map_location="cpu", mmap=lazy)
+        except (RuntimeError, TypeError):       # a record written in a format that cannot be mapped
+            rec = torch.load(path, map_location="cpu")
         if rec["input_ids"].shape[0] != self.batch_size:
             raise ValueError(f"feature records hold {rec['input_ids'].shape[0]} sequences, the run's batch size is "
                              f"{self.batch_size}")
+        if lazy:
+            b, l = rec["input_ids"].shape
+            rows = self.context_rows(b, l).cpu()
+            hidden = rec["hidden"].reshape(b * l, -1).index_select(0, rows)
+            rec = {"input_ids": rec["input_ids"].clone(), "hidden": hidden, "final_hidden_host": rec["final_hidden"]}
         if self.device.type == "cuda":
-            rec = {k: v.pin_memory() for k, v in rec.items()}
+            rec = {k: (v if k == "final_hidden_host" else v.pin_memory()) for k, v in rec.items()}
         return rec
 
     def next_batch(self):
@@ -82,11 +98,15 @@ class FeatureStoreDataRuntime:
 
         rec = self._ahead if self._ahead is not None else self._load(self.step)
         self.step += 1
+        host = rec.pop("final_hidden_host", None)
         nbytes = sum(v.numel() * v.element_size() for v in rec.values()) if self.device.type == "cuda" else 0
         dev = {k: v.to(self.device, non_blocking=True) for k, v in rec.items()}
         self._ahead = self._load(self.step)
         b = DataBatch(dev["input_ids"], h2d_bytes=nbytes)
-        b.features = {"hidden": dev["hidden"], "final_hidden": dev["final_hidden"]}
+        if host is not None:
+            b.features = {"hidden": dev["hidden"], "final_hidden": host, "hidden_is_shard": True}
+        else:
+            b.features = {"hidden": dev["hidden"], "final_hidden": dev["final_hidden"]}
         return b
 
     def next_optimizer_step_batches(self, micro_batches: int):

@@ -35,7 +35,9 @@ from .dense import BlockDiffusionTransformer, FlatParams
 @dataclass
 class TargetFeatures:
     hidden: torch.Tensor        # [B*L, n_selected * target_hidden] concatenated selected layers
-    final_hidden: torch.Tensor  # [B*L, target_hidden] after the target's final norm (teacher states)
+    final_hidden: torch.Tensor  # [B*L, target_hidden] after the target's final norm (teacher states); may live
+                                # memory-mapped on the host (offline store of a long context): rows are taken there
+    hidden_is_shard: bool = False   # `hidden` already holds only this rank's context rows
 
 
 def causal_layout(batch: int, seq_len: int, device) -> MaskLayout:

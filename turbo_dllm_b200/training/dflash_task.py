@@ -114,8 +114,11 @@ class DFlashTask:
             if feats is None:
                 raise ValueError("data.target_features=offline needs batches of the feature-store data runtime")
             dt = self.model.flat.data.dtype
+            fh = feats["final_hidden"]
+            fh = fh.reshape(-1, fh.shape[-1])
             return TargetFeatures(feats["hidden"].reshape(-1, feats["hidden"].shape[-1]).to(dt),
-                                  feats["final_hidden"].reshape(-1, feats["final_hidden"].shape[-1]).to(dt))
+                                  fh if fh.device != self.model.flat.data.device else fh.to(dt),
+                                  bool(feats.get("hidden_is_shard", False)))
         if self.synthetic:  # random features of the right shape: exercises the drafter without a target pass
             b, l = input_ids.shape
             g = torch.Generator(device=self.device)
@@ -146,7 +149,8 @@ class DFlashTask:
                            head_dim=c.head_dim)
             ob = select_anchors(ob, ex.anchor_index(ob.anchor_positions.shape[1], device=ids.device))
             mask = (ex, plan)
-            ctx_features = feats.hidden.index_select(0, ex.context_rows(b, l, ids.device))
+            ctx_features = (feats.hidden if feats.hidden_is_shard
+                            else feats.hidden.index_select(0, ex.context_rows(b, l, ids.device)))
             pos_ctx = ex.context_positions(l, device=ids.device).repeat(b)
         draft_tok = ob.draft_input_ids.reshape(-1)
         draft_emb = embedding(draft_tok, self.target.embed)
@@ -158,7 +162,12 @@ class DFlashTask:
         seq_off = (torch.arange(b, device=ids.device) * l)[:, None, None]
         src = (ob.teacher_source_positions + seq_off).reshape(-1)
         h_s = hidden.index_select(0, rows)
-        h_t = feats.final_hidden.index_select(0, src.index_select(0, rows))
+        want = src.index_select(0, rows)
+        fh = feats.final_hidden
+        if fh.device != hidden.device:      # memory-mapped on the host: only the needed teacher rows are read
+            h_t = fh.index_select(0, want.to(fh.device)).to(hidden.device, hidden.dtype)
+        else:
+            h_t = fh.index_select(0, want)
         wr = w.index_select(0, rows)
         if self.loss_kind == "speculators_kl":
             loss_sum, _ = frozen_linear_kl(h_s, h_t, self.target.lm_head, wr)

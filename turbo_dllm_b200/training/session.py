@@ -230,8 +230,12 @@ class TrainingSession:
         if self.task.feature_store is not None:
             from ..data.dflash_features import FeatureStoreDataRuntime
 
+            rows = None
+            if exchange is not None and exchange.context_sharded:
+                rows = lambda b, l: exchange.context_rows(b, l, "cpu")     # read this rank's context shard only
             self.data = FeatureStoreDataRuntime(self.task.feature_store, batch_size=spec.training.batch_size,
-                                                device=self.device, dp_rank=dp_rank, dp_size=self.dp_size)
+                                                device=self.device, dp_rank=dp_rank, dp_size=self.dp_size,
+                                                context_rows=rows)
         else:
             data_kw = dict(batch_size=spec.training.batch_size, seq_len=spec.model.seq_len,
                            vocab_size=tcfg.vocab_size, mask_token_id=tcfg.mask_token_id,
