@@ -370,3 +370,33 @@ def test_checked_kernel_build_is_a_separate_library(monkeypatch):
     assert "#ifdef TDLLM_KERNEL_CHECKS" in src and "ERR_BAD_INDEX" in src
     users = [p.name for p in kb.all_source_files() if "TD_CHECKED(" in p.read_text() and p.name != "common.cuh"]
     assert {"peer_pull.cuh", "comm.cu", "moe_dispatch.cu"} <= set(users)
+
+
+def test_trace_tables_per_rank_view_and_comparison(tmp_path, capsys):
+    from turbo_dllm_b200.profiling import trace_analysis as ta
+    from turbo_dllm_b200.profiling.operator_trace import communication_label
+
+    lab = communication_label("tensor", "forward", "allgather_gemm", 4_000_000, 8_000_000)
+
+    def write(rank, gemm_us, nccl_us):
+        ev = [{"ph": "X", "cat": "user_annotation", "name": "dllm.step.3", "ts": 0, "dur": 1000},
+              {"ph": "X", "cat": "user_annotation", "name": "dllm.phase.forward", "ts": 0, "dur": 400},
+              {"ph": "X", "cat": "kernel", "name": "tdllm::gemm_bf16_kernel<1,false>(...)", "ts": 10, "dur": gemm_us},
+              {"ph": "X", "cat": "kernel", "name": "ncclDevKernel_AllReduce_Sum", "ts": 10 + gemm_us, "dur": nccl_us},
+              {"ph": "X", "cat": "user_annotation", "name": lab, "ts": 10, "dur": 100}]
+        p = tmp_path / f"rank_{rank}.trace.json.gz"
+        with gzip.open(p, "wt") as f:
+            json.dump({"traceEvents": ev}, f)
+        return str(p)
+
+    a, b = write(0, 500, 100), write(1, 700, 50)
+    table = ta.format_table(ta.analyze_kineto_trace(a))
+    assert "| tensor/forward/allgather_gemm | 1 | 0.10 | 4.0 | 8.0 | 80.0 |" in table      # 8 MB in 100 us
+    assert "| forward | 1 | 0.4 | 40.0 % |" in table
+    per = ta.analyze_directory(str(tmp_path))
+    assert per["slowest_rank_by_compute"] == 1 and per["ranks"][0]["exposed_communication_ms"] == pytest.approx(0.1)
+    assert per["compute_spread_pct"] == pytest.approx(40.0)
+    diff = ta.compare_summaries(ta.analyze_kineto_trace(a), ta.analyze_kineto_trace(b))
+    assert "| `gemm_bf16_kernel` | 0.5 | 0.7 | +0.2 |" in diff and "| traced span | 1.0 | 1.0 | +0.0 |" in diff
+    assert ta.main([str(tmp_path)]) == 0 and "slowest rank by compute time: 1" in capsys.readouterr().out
+    assert ta.main([a, "--compare", b]) == 0 and "AllReduce" in capsys.readouterr().out

@@ -189,6 +189,66 @@ def format_table(summary: dict, top: int = 25) -> str:
         rows.append((f"copies: {k} ({rec['count']})", rec["time_us"]))
     for k, v in rows:
         lines.append(f"| {k} | {v / 1e3:.1f} | {100 * v / span:.1f} % |")
+    labels = summary.get("communication_labels") or {}
+    if labels:
+        lines += ["", "| communication (domain/phase/op) | calls | host-range ms | input MB | logical MB | GB/s over the range |",
+                  "|---|---|---|---|---|---|"]
+        for key, rec in sorted(labels.items(), key=lambda kv: -kv[1]["time_us"]):
+            moved = max(rec["input_bytes"], rec["logical_bytes"])
+            rate = moved / (rec["time_us"] * 1e-6) / 1e9 if rec["time_us"] > 0 else 0.0
+            lines.append(f"| {key} | {rec['count']} | {rec['time_us'] / 1e3:.2f} | {rec['input_bytes'] / 1e6:.1f} | "
+                         f"{rec['logical_bytes'] / 1e6:.1f} | {rate:.1f} |")
+    phases = {k: v for k, v in (summary.get("operators") or {}).items() if k.startswith("dllm.phase.")}
+    if phases:
+        lines += ["", "| step phase | count | ms | share of span |", "|---|---|---|---|"]
+        for key, rec in sorted(phases.items(), key=lambda kv: -kv[1]["time_us"]):
+            lines.append(f"| {key[len('dllm.phase.'):]} | {rec['count']} | {rec['time_us'] / 1e3:.1f} | "
+                         f"{100 * rec['time_us'] / span:.1f} % |")
+    return "\n".join(lines)
+
+
+def analyze_directory(directory: str) -> dict:
+    """Every `rank_*.trace.json[.gz]` of a run: per-rank span, busy share, exposed communication and idle time, and
+    which rank is the slowest (the one the others wait for in every collective)."""
+    import glob
+    import os
+
+    per_rank = {}
+    for path in sorted(glob.glob(os.path.join(directory, "rank_*.trace.json*"))):
+        m = re.search(r"rank_(\d+)\.trace", os.path.basename(path))
+        if not m:
+            continue
+        sm = analyze_kineto_trace(path)
+        span = sm["span_us"] or 1.0
+        per_rank[int(m.group(1))] = {
+            "span_ms": span / 1e3, "busy_pct": 100 * sm["kernel_busy_us"] / span,
+            "compute_ms": sm["compute_time_us"] / 1e3, "exposed_communication_ms": sm["exposed_communication_us"] / 1e3,
+            "exposed_copy_ms": sm["exposed_copy_us"] / 1e3, "idle_ms": sm["idle_us"] / 1e3}
+    if not per_rank:
+        raise FileNotFoundError(f"no rank_*.trace.json[.gz] under {directory}")
+    compute = {r: v["compute_ms"] for r, v in per_rank.items()}
+    slow = max(compute, key=compute.get)
+    return {"ranks": per_rank, "slowest_rank_by_compute": slow,
+            "compute_spread_pct": 100 * (max(compute.values()) - min(compute.values())) / max(min(compute.values()), 1e-9)}
+
+
+def compare_summaries(a: dict, b: dict, top: int = 15) -> str:
+    """Markdown table of the kernel families whose device time differs most between two summaries (a -> b), e.g. the
+    same step on 2 and on 8 GPUs."""
+    names = set(a["kernels_by_name"]) | set(b["kernels_by_name"])
+    rows = []
+    for n in names:
+        ta = a["kernels_by_name"].get(n, {}).get("time_us", 0.0)
+        tb = b["kernels_by_name"].get(n, {}).get("time_us", 0.0)
+        rows.append((tb - ta, n, ta, tb))
+    rows.sort(key=lambda r: -abs(r[0]))
+    lines = ["| kernel | a ms | b ms | b - a ms |", "|---|---|---|---|"]
+    for d, n, ta, tb in rows[:top]:
+        lines.append(f"| `{n}` | {ta / 1e3:.1f} | {tb / 1e3:.1f} | {d / 1e3:+.1f} |")
+    for key, label in (("span_us", "traced span"), ("kernel_busy_us", "kernels busy"), ("idle_us", "device idle"),
+                       ("exposed_communication_us", "exposed communication"), ("exposed_copy_us", "exposed copies")):
+        lines.append(f"| {label} | {a.get(key, 0) / 1e3:.1f} | {b.get(key, 0) / 1e3:.1f} | "
+                     f"{(b.get(key, 0) - a.get(key, 0)) / 1e3:+.1f} |")
     return "\n".join(lines)
 
 
@@ -197,11 +257,35 @@ def main(argv=None) -> int:
 
     ap = argparse.ArgumentParser(prog="python -m turbo_dllm_b200.profiling.trace_analysis",
                                  description="Summarise a Kineto chrome trace or an nsys sqlite export.")
-    ap.add_argument("trace")
+    ap.add_argument("trace", help="a trace file, or a directory of rank_*.trace.json[.gz] files (per-rank table)")
     ap.add_argument("--json", help="write the full summary here")
     ap.add_argument("--top", type=int, default=25)
+    ap.add_argument("--compare", help="a second trace (or summary .json): print what changed from TRACE to it")
     a = ap.parse_args(argv)
-    summary = analyze_nsys_sqlite(a.trace) if a.trace.endswith(".sqlite") else analyze_kineto_trace(a.trace)
+    import os
+
+    if os.path.isdir(a.trace):
+        res = analyze_directory(a.trace)
+        if a.json:
+            write_summary(res, a.json)
+        print("| rank | span ms | busy % | compute ms | exposed comm ms | exposed copies ms | idle ms |")
+        print("|---|---|---|---|---|---|---|")
+        for r, v in sorted(res["ranks"].items()):
+            print(f"| {r} | {v['span_ms']:.1f} | {v['busy_pct']:.1f} | {v['compute_ms']:.1f} | "
+                  f"{v['exposed_communication_ms']:.1f} | {v['exposed_copy_ms']:.1f} | {v['idle_ms']:.1f} |")
+        print(f"\nslowest rank by compute time: {res['slowest_rank_by_compute']} "
+              f"(spread {res['compute_spread_pct']:.1f} %)")
+        return 0
+
+    def load(path):
+        if path.endswith(".json") and not path.endswith(".trace.json"):
+            return json.load(open(path))
+        return analyze_nsys_sqlite(path) if path.endswith(".sqlite") else analyze_kineto_trace(path)
+
+    summary = load(a.trace)
+    if a.compare:
+        print(compare_summaries(summary, load(a.compare), a.top))
+        return 0
     if a.json:
         write_summary(summary, a.json)
     print(format_table(summary, a.top))
