@@ -400,3 +400,52 @@ def test_trace_tables_per_rank_view_and_comparison(tmp_path, capsys):
     assert "| `gemm_bf16_kernel` | 0.5 | 0.7 | +0.2 |" in diff and "| traced span | 1.0 | 1.0 | +0.0 |" in diff
     assert ta.main([str(tmp_path)]) == 0 and "slowest rank by compute time: 1" in capsys.readouterr().out
     assert ta.main([a, "--compare", b]) == 0 and "AllReduce" in capsys.readouterr().out
+
+
+def test_partial_rotary_is_a_permutation_of_head_dimensions(tmp_path):
+    """A checkpoint that rotates pairs (j, j + R/2) of its first R head dimensions gives the same attention scores
+    here, where the kernels rotate pairs (i, i + D/2) with frequency 0 on the pass-through pairs, once its q/k head
+    dimensions are permuted at load time; export restores the checkpoint's order."""
+    from dataclasses import replace
+
+    from turbo_dllm_b200.models.config import PRESETS
+    from turbo_dllm_b200.models.dense import BlockDiffusionTransformer
+    from turbo_dllm_b200.models.hf_loader import export_hf_checkpoint, load_hf_config, load_hf_weights
+    from turbo_dllm_b200.ops.rope import partial_rotary_permutation, qk_norm_rope_reference, rope_inv_freq
+
+    D, R, theta = 64, 16, 1.0e4
+    perm = partial_rotary_permutation(D, R)
+    assert sorted(perm.tolist()) == list(range(D)) and perm[:8].tolist() == list(range(8))
+    assert perm[32:40].tolist() == list(range(8, 16))
+    freq = rope_inv_freq(D, theta, rotary_dim=R)
+    assert (freq[8:] == 0).all() and torch.allclose(freq[:8], 1.0 / theta ** (torch.arange(0, R, 2) / R))
+    torch.manual_seed(0)
+    q, k = torch.randn(5, D), torch.randn(7, D)
+    pq, pk = torch.arange(5), torch.arange(7) + 3
+
+    def hf_rotate(x, pos):            # the checkpoint's convention
+        ang = pos[:, None].float() * (1.0 / theta ** (torch.arange(0, R, 2) / R))[None, :]
+        cos, sin = torch.cat([ang.cos()] * 2, -1), torch.cat([ang.sin()] * 2, -1)
+        rot, rest = x[:, :R], x[:, R:]
+        half = torch.cat([-rot[:, R // 2:], rot[:, : R // 2]], -1)
+        return torch.cat([rot * cos + half * sin, rest], -1)
+
+    want = hf_rotate(q, pq) @ hf_rotate(k, pk).t()
+    mine_q = qk_norm_rope_reference(q[:, perm], pq, freq, None, None, 1, 0, D, 1e-6)[:, :D]
+    mine_k = qk_norm_rope_reference(k[:, perm], pk, freq, None, None, 1, 0, D, 1e-6)[:, :D]
+    assert torch.allclose(mine_q @ mine_k.t(), want, rtol=1e-4, atol=1e-4)
+    # loader: export keeps the checkpoint's order, import permutes; a round trip is the identity
+    cfg = replace(PRESETS["synthetic:tiny-qwen3"], partial_rotary_factor=0.25, num_layers=1)
+    a = BlockDiffusionTransformer(cfg, dtype=torch.float32, seed=5)
+    assert (a.inv_freq[cfg.rotary_dim // 2:] == 0).all()
+    export_hf_checkpoint(a, str(tmp_path / "hf"))
+    cfg2 = load_hf_config(str(tmp_path / "hf"))
+    assert cfg2.partial_rotary_factor == 0.25
+    b = BlockDiffusionTransformer(cfg2, dtype=torch.float32, seed=99)
+    load_hf_weights(b, str(tmp_path / "hf"))
+    assert torch.equal(a.flat.data, b.flat.data)
+    from safetensors import safe_open
+
+    with safe_open(str(tmp_path / "hf" / "model.safetensors"), "pt") as f:
+        on_disk = f.get_tensor("model.layers.0.self_attn.q_norm.weight")
+    assert torch.equal(on_disk[perm], a.layers[0].q_norm.detach())

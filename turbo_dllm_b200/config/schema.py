@@ -66,6 +66,8 @@ SECTIONS: dict[str, tuple[F, ...]] = {
         F("head_dim", OPT_INT, None, ext=True),
         F("intermediate_size", OPT_INT, None, ext=True),
         F("rope_theta", OPT_FLOAT, None, ext=True),
+        F("partial_rotary_factor", OPT_FLOAT, None, ext=True,
+          help="share of each head's dimensions that rotary embeddings touch (1.0 = all)"),
         F("qk_norm", bool, True, ext=True),
         F("num_experts", OPT_INT, None, ext=True),
         F("num_experts_per_token", OPT_INT, None, ext=True),

@@ -20,6 +20,7 @@ class ModelConfig:
     head_dim: int
     intermediate_size: int
     rope_theta: float = 1.0e6
+    partial_rotary_factor: float = 1.0     # share of each head's dimensions that rotary embeddings touch
     rms_norm_eps: float = 1.0e-6
     qk_norm: bool = True
     tie_word_embeddings: bool = False
@@ -45,6 +46,11 @@ class ModelConfig:
     linear_key_head_dim: int = 0
     linear_value_head_dim: int = 0
     linear_conv_kernel: int = 4
+
+    @property
+    def rotary_dim(self) -> int:
+        r = int(self.head_dim * self.partial_rotary_factor)
+        return max(r - r % 2, 2)
 
     @property
     def q_dim(self) -> int:
@@ -173,7 +179,7 @@ def model_config_from_run_spec(spec) -> ModelConfig:
                            intermediate_size=m.intermediate_size or 4 * m.hidden_size)
     over = {}
     for name in ("vocab_size", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
-                 "intermediate_size", "rope_theta", "mask_token_id", "num_experts", "num_experts_per_token",
+                 "intermediate_size", "rope_theta", "partial_rotary_factor", "mask_token_id", "num_experts", "num_experts_per_token",
                  "moe_intermediate_size", "moe_shared_intermediate_size", "full_attention_interval", "linear_num_key_heads",
                  "linear_num_value_heads", "linear_key_head_dim", "linear_value_head_dim", "linear_conv_kernel",
                  "sliding_window", "sliding_window_pattern"):

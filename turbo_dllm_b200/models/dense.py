@@ -266,7 +266,7 @@ class BlockDiffusionTransformer(nn.Module):
         self.final_norm = self.flat.params["final_norm"]
         self.lm_head = self.flat.params.get("lm_head", self.embed)
         self.layers = nn.ModuleList(DecoderLayer(self.lcfg, i, self.flat, self.tp) for i in range(cfg.num_layers))
-        self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device), persistent=False)
+        self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device, cfg.rotary_dim), persistent=False)
         self.sharded = None      # parallel.fsdp.ShardedParameters when the parameters are sharded
         self.reset_parameters(seed, init_std)
 

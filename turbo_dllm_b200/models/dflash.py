@@ -154,7 +154,7 @@ class DFlashDraftModel(nn.Module):
         self.fc, self.hidden_norm = self.flat.params["fc"], self.flat.params["hidden_norm"]
         self.final_norm = self.flat.params["final_norm"]
         self.layers = nn.ModuleList(DFlashLayer(cfg, i, self.flat) for i in range(cfg.num_layers))
-        self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device), persistent=False)
+        self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device, cfg.rotary_dim), persistent=False)
         self.store = ActivationStore(torch.device(device), offload=False)
         BlockDiffusionTransformer.reset_parameters(self, seed, init_std)
 

@@ -149,7 +149,7 @@ class DFlash2DraftModel(DFlashDraftModel):
         self.fc, self.hidden_norm, self.final_norm = g["fc"], g["hidden_norm"], g["final_norm"]
         self.layers = nn.ModuleList(DFlash2Layer(cfg, i, self.flat, taps=conv_kernel_size, groups=groups,
                                                  block_size=block_size) for i in range(cfg.num_layers))
-        self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device), persistent=False)
+        self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device, cfg.rotary_dim), persistent=False)
         self.store = ActivationStore(torch.device(device), offload=False)
         BlockDiffusionTransformer.reset_parameters(self, seed, init_std)
         with torch.no_grad():

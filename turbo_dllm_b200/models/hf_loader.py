@@ -56,11 +56,19 @@ def load_hf_config(path: str, max_layers: int | None = None) -> ModelConfig:
         vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], num_layers=layers, num_attention_heads=heads,
         num_key_value_heads=c.get("num_key_value_heads", heads), head_dim=c.get("head_dim", c["hidden_size"] // heads),
         intermediate_size=c["intermediate_size"], rope_theta=float(c.get("rope_theta", 1e6)),
+        partial_rotary_factor=float(c.get("partial_rotary_factor", 1.0) or 1.0),
         rms_norm_eps=float(c.get("rms_norm_eps", 1e-6)), qk_norm="Qwen3" in arch or bool(c.get("qk_norm", False)),
         tie_word_embeddings=bool(c.get("tie_word_embeddings", False)), mask_token_id=c.get("mask_token_id"))
 
 
 def hf_config_dict(cfg: ModelConfig) -> dict:
+    d = _hf_config_dict(cfg)
+    if cfg.partial_rotary_factor != 1.0:
+        d["partial_rotary_factor"] = cfg.partial_rotary_factor
+    return d
+
+
+def _hf_config_dict(cfg: ModelConfig) -> dict:
     if cfg.is_hybrid:
         kinds = [cfg.layer_kind(i) for i in range(cfg.num_layers)]
         return {"architectures": ["Qwen3NextForCausalLM"], "model_type": "qwen3_next", "vocab_size": cfg.vocab_size,
@@ -150,6 +158,23 @@ def load_hf_weights(model, path: str) -> None:
         put(layer.w_gate_up, interleave_gate_up(shard(get(p + "mlp.gate_proj.weight"), 0),
                                                 shard(get(p + "mlp.up_proj.weight"), 0)))
         put(layer.w_down, shard(get(p + "mlp.down_proj.weight"), 1))
+    _apply_partial_rotary_order(model, inverse=False)
+
+
+def _apply_partial_rotary_order(model, inverse: bool) -> None:
+    """Checkpoint order <-> kernel order of the q/k head dimensions under partial rotary embeddings (a no-op when the
+    whole head rotates). Layers without q/k projections (linear attention) are left alone."""
+    cfg = model.cfg
+    if cfg.rotary_dim >= cfg.head_dim:
+        return
+    from ..ops.rope import partial_rotary_permutation
+
+    perm = partial_rotary_permutation(cfg.head_dim, cfg.rotary_dim)
+    if inverse:
+        perm = torch.argsort(perm)
+    for layer in model.layers:
+        if getattr(layer, "w_qkv", None) is not None:
+            _permute_qk_head_dims(layer, cfg, perm)
 
 
 def _load_hybrid_layer(layer, cfg, p, get, put, table) -> None:
@@ -215,6 +240,24 @@ def _export_hybrid_layer(layer, cfg, p, out) -> None:
         out[a + "q_norm.weight"], out[a + "k_norm.weight"] = layer.q_norm, layer.k_norm
 
 
+def _permute_qk_head_dims(layer, cfg: ModelConfig, perm: torch.Tensor) -> None:
+    """Reorders the head dimensions of the q and k rows of `w_qkv` and of the q/k norm weights: new[d] = old[perm[d]]
+    inside every head. q·k is unchanged; with partial rotary embeddings this moves a checkpoint's rotating pairs
+    (j, j + rotary_dim/2) onto the pairs (i, i + head_dim/2) the rotary kernels use (ops/rope.py)."""
+    D = cfg.head_dim
+    w = layer.w_qkv
+    hq = (w.shape[0] - 0) // D            # q, k and v heads of this rank, in that order
+    n_q = layer.w_o.shape[1] // D
+    n_kv = (hq - n_q) // 2
+    perm = perm.to(w.device)
+    for start, heads in ((0, n_q), (n_q * D, n_kv)):
+        blk = w[start:start + heads * D].view(heads, D, -1)
+        blk.copy_(blk[:, perm].clone())
+    for t in (layer.q_norm, layer.k_norm):
+        if t is not None:
+            t.copy_(t[perm].clone())
+
+
 @torch.no_grad()
 def export_hf_checkpoint(model, path: str, merge_adapters: bool = True) -> str:
     """Writes config.json + model.safetensors in Hugging Face naming (single tensor-parallel rank)."""
@@ -228,6 +271,17 @@ def export_hf_checkpoint(model, path: str, merge_adapters: bool = True) -> str:
         merge_lora(model)
     cfg = model.cfg
     os.makedirs(path, exist_ok=True)
+    _apply_partial_rotary_order(model, inverse=True)        # the file keeps the checkpoint's head-dimension order
+    try:
+        return _write_hf_checkpoint(model, cfg, path)
+    finally:
+        _apply_partial_rotary_order(model, inverse=False)
+
+
+@torch.no_grad()
+def _write_hf_checkpoint(model, cfg, path: str) -> str:
+    from safetensors.torch import save_file
+
     out = {"model.embed_tokens.weight": model.embed, "model.norm.weight": model.final_norm}
     if not cfg.tie_word_embeddings:
         out["lm_head.weight"] = model.lm_head

@@ -325,7 +325,7 @@ class HybridBlockDiffusionTransformer(BlockDiffusionTransformer):
         self.layers = nn.ModuleList(
             GatedAttentionLayer(cfg, i, self.flat) if kind == "full_attention"
             else GatedDeltaLayer(cfg, i, self.flat, branch_group) for i, kind in enumerate(kinds))
-        self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device), persistent=False)
+        self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device, cfg.rotary_dim), persistent=False)
         self.reset_parameters(seed, init_std)
 
     @torch.no_grad()

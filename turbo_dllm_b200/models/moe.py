@@ -369,7 +369,7 @@ class MoEBlockDiffusionTransformer(BlockDiffusionTransformer):
         for layer in self.layers:
             layer.experts.exchange_holder = self.expert_exchange
             layer.experts.store = self.store
-        self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device), persistent=False)
+        self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device, cfg.rotary_dim), persistent=False)
         ep_rank = dist.get_rank(ep_group) if ep_group is not None else 0
         self.reset_parameters(seed, init_std)
         if ep > 1:  # expert slices differ per rank, everything else is replicated

@@ -13,8 +13,33 @@ from ..kernels import native
 from ._util import grad_sink, mark_grad_written, ptr, scratch, stream, use_native
 
 
-def rope_inv_freq(head_dim: int, theta: float, device=None) -> torch.Tensor:
-    return 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+def rope_inv_freq(head_dim: int, theta: float, device=None, rotary_dim: int | None = None) -> torch.Tensor:
+    """[head_dim / 2] inverse frequencies of the pairs (i, i + head_dim/2). With `rotary_dim` < head_dim (partial
+    rotary embeddings) only the first rotary_dim/2 pairs rotate, at the frequencies of a rotary_dim-wide embedding;
+    the other pairs get frequency 0, i.e. the identity. The kernels need nothing else: checkpoints whose heads keep
+    the rotary dimensions in front (pairs (j, j + rotary_dim/2)) are brought into this pairing by a fixed
+    permutation of the head dimensions at load time (`partial_rotary_permutation`), which q·k does not see."""
+    r = head_dim if rotary_dim is None else int(rotary_dim)
+    if r <= 0 or r > head_dim or r % 2:
+        raise ValueError(f"rotary_dim must be an even number in (0, {head_dim}], got {r}")
+    freq = torch.zeros(head_dim // 2, dtype=torch.float32, device=device)
+    freq[: r // 2] = 1.0 / (theta ** (torch.arange(0, r, 2, dtype=torch.float32, device=device) / r))
+    return freq
+
+
+def partial_rotary_permutation(head_dim: int, rotary_dim: int) -> torch.Tensor:
+    """perm[new] = old: head dimension `old` of a checkpoint that rotates pairs (j, j + rotary_dim/2) of its first
+    `rotary_dim` dimensions sits at `new` here, where pairs are (i, i + head_dim/2). The pass-through dimensions fill
+    the rest of both halves. Identity when rotary_dim == head_dim."""
+    D, R = head_dim, rotary_dim
+    h, rh = D // 2, R // 2
+    perm = torch.empty(D, dtype=torch.long)
+    perm[:rh] = torch.arange(rh)                               # first members of the rotating pairs
+    perm[h: h + rh] = torch.arange(rh, R)                      # their partners
+    rest = torch.arange(R, D)
+    perm[rh:h] = rest[: h - rh]
+    perm[h + rh:] = rest[h - rh:]
+    return perm
 
 
 def qk_norm_rope_reference(qkv, pos, inv_freq, qw, kw, Hq, Hkv, D, eps):
