@@ -125,7 +125,7 @@ def test_barrier_wait_runs_out_and_reports():
 
 
 def _csbp(rank, world, transport, steps, model="synthetic:tiny-hd128", objective="standard_block_diffusion",
-          block_axis=True):
+          block_axis=True, window=None):
     import os
 
     import torch.distributed as dist
@@ -139,7 +139,8 @@ def _csbp(rank, world, transport, steps, model="synthetic:tiny-hd128", objective
     torch.cuda.set_device(rank)
     cp = world
     spec = RunSpec.from_mapping({
-        "model": {"id": model, "seq_len": 1024, "dtype": "bf16"},
+        "model": {"id": model, "seq_len": 1024, "dtype": "bf16",
+                  **({"sliding_window": window, "sliding_window_pattern": 2} if window else {})},
         "objective": {"name": objective, "block_size": 32, "sampling_epsilon_min": 0.1},
         "training": {"batch_size": 2, "steps": steps},
         "topology": {"context_parallel_size": cp, "block_parallel_size": cp if block_axis else 1},
@@ -201,6 +202,20 @@ def _dflash_replica(rank, world, mode, steps):
     torch.cuda.synchronize()
     native.raise_on_device_error()
     return losses, s.model.flat.data.float().cpu()
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("transport", ["collective", "fused"])
+def test_sliding_window_layers_under_csbp2_on_gpus_match_single_gpu(transport):
+    """Layer 0 has a 128-token window: it moves only the clean rows inside some local row's window (one NCCL
+    all-to-all with uneven splits, reversed in the backward pass); layer 1 uses the configured transport."""
+    _need(2)
+    args = (3, "synthetic:tiny-hd128", "standard_block_diffusion", True, 128)
+    ref = run_ranks(_csbp, 1, args=("collective", *args), backend=None, deadline_s=300)[0]
+    outs = run_ranks(_csbp, 2, args=(transport, *args), backend="nccl", deadline_s=300)
+    for losses, params in outs:
+        assert losses == pytest.approx(ref[0], rel=3e-2)
+        assert (torch.from_numpy(params) - torch.from_numpy(ref[1])).abs().max().item() < 3e-2
 
 
 @pytest.mark.distributed
