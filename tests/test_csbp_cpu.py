@@ -3,7 +3,7 @@ same loss curve and same parameters (CPU, fp32, tiny Qwen3-style model)."""
 import pytest
 import torch
 
-from tests._harness import run_ranks
+from tests._harness import assert_params_close, run_ranks
 
 MAPPING = {
     "model": {"id": "synthetic:tiny-qwen3", "seq_len": 256, "dtype": "fp32", "num_layers": 2},
@@ -55,7 +55,7 @@ def test_more_block_ranks_than_clean_shards(share):
     assert (clean_rows[2] == 0 and clean_rows[3] == 0) == share and clean_rows[0] > 0
     for losses, params, _ in outs:
         assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
-        assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=2e-5)
+        assert_params_close(params, ref_params)
 
 
 @pytest.mark.distributed
@@ -65,7 +65,7 @@ def test_csbp2_matches_single_process(objective):
     outs = run_ranks(_run, 2, args=(2, 2, 3, objective), deadline_s=240)
     for losses, params, _ in outs:
         assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
-        assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=2e-5)
+        assert_params_close(params, ref_params)
 
 
 @pytest.mark.distributed
@@ -131,7 +131,7 @@ def test_pure_context_parallel_matches_single_process(split):
     outs = run_ranks(_run, 2, args=(2, 1, 2, "standard_block_diffusion", True, split), deadline_s=240)
     for losses, params, n_noisy in outs:
         assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
-        assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=2e-5)
+        assert_params_close(params, ref_params)
         assert n_noisy == (n_noisy_full // 2 if split else n_noisy_full)
 
 
@@ -149,7 +149,7 @@ def test_sliding_window_layers_exchange_only_the_window(cp, bp):
                      deadline_s=300)
     for losses, params, _ in outs:
         assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
-        assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=2e-5)
+        assert_params_close(params, ref_params)
 
 
 def test_windowed_exchange_plan_counts():

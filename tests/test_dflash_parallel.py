@@ -3,7 +3,7 @@ context K|V pulled or queries rotated. Every form must reproduce the single-proc
 import pytest
 import torch
 
-from tests._harness import run_ranks
+from tests._harness import assert_params_close, run_ranks
 
 
 def _run(rank, world, cp, bp, mode, steps=2, dflash2=False):
@@ -47,7 +47,7 @@ def test_dflash_replica_over_two_ranks_matches_single_process(cp, bp, mode):
     for losses, params, used in outs:
         assert used == (mode if cp > 1 else "local")
         assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-5)
-        assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=2e-5)
+        assert_params_close(params, ref_params)
 
 
 @pytest.mark.distributed
@@ -56,7 +56,7 @@ def test_dflash2_replica_over_two_ranks_matches_single_process():
     outs = run_ranks(_run, 2, args=(2, 2, "query_rotation", 2, True), deadline_s=240)
     for losses, params, _ in outs:
         assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-5)
-        assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=2e-5)
+        assert_params_close(params, ref_params)
 
 
 def test_bytes_model_prefers_queries_at_long_context():
@@ -122,4 +122,4 @@ def test_offline_store_feeds_a_context_sharded_replica_its_shard_only(tmp_path):
     for losses, params, rows in outs:
         assert rows[0] == 64 and rows[1]                      # half of the 128 context rows of a record
         assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-5)
-        assert torch.allclose(torch.from_numpy(params), ref_params, rtol=1e-3, atol=2e-5)
+        assert_params_close(params, ref_params)

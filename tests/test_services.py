@@ -196,14 +196,22 @@ def test_family_executors_and_registration():
         assert isinstance(ex, c.BackboneExecutor) and ex.family.name == fam
         assert ex.family.objectives == FAMILY_OBJECTIVES[fam]
     assert executor_for_family("causal_lm").capabilities.parameter_sharding
-    assert not executor_for_family("qwen3_8").capabilities.tensor_parallel
+    assert executor_for_family("qwen3_8").capabilities.tensor_parallel
+    assert not executor_for_family("qwen3_8").capabilities.sequence_parallel
+    assert not executor_for_family("dflash").capabilities.tensor_parallel
     spec = RunSpec.from_mapping({
         "model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "num_layers": 1},
         "objective": {"name": "standard_block_diffusion", "block_size": 16},
         "training": {"batch_size": 1, "steps": 1},
         "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}).validate()
-    problems = executor_for_family("qwen3_8").validate_run_spec(spec.with_overrides(
+    hybrid = executor_for_family("qwen3_8")
+    assert not hybrid.validate_run_spec(spec.with_overrides(
         {"topology": {"tensor_parallel_size": 2}, "objective": {"name": "fast_dllm_v2"}}))
+    problems = hybrid.validate_run_spec(spec.with_overrides(
+        {"topology": {"tensor_parallel_size": 2, "sequence_parallel": True}, "objective": {"name": "fast_dllm_v2"}}))
+    assert any("sequence-parallel" in p for p in problems) and any("not with context or sequence" in p for p in problems)
+    problems = executor_for_family("dflash").validate_run_spec(spec.with_overrides(
+        {"topology": {"tensor_parallel_size": 2}, "objective": {"name": "dflash_distillation"}}))
     assert any("tensor-parallel" in p for p in problems)
 
     built = []

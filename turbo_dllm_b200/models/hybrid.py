@@ -52,6 +52,35 @@ def linear_layer_specs(cfg: ModelConfig, i: int):
             (p + "w_gate_up", (2 * cfg.intermediate_size, h), True), (p + "w_down", (h, cfg.intermediate_size), True)]
 
 
+def local_hybrid_config(cfg: ModelConfig, tp: int) -> ModelConfig:
+    """Per-rank shapes under tensor parallelism: softmax heads, linear-attention key and value heads and the FFN
+    width are divided by `tp` (dllm_parallel/core/models/backbones/qwen3_8/tensor_parallel.py)."""
+    if tp == 1:
+        return cfg
+    from dataclasses import replace
+
+    for name in ("num_attention_heads", "num_key_value_heads", "intermediate_size", "vocab_size",
+                 "linear_num_key_heads", "linear_num_value_heads"):
+        if getattr(cfg, name) % tp:
+            raise ValueError(f"{name} ({getattr(cfg, name)}) must divide by tensor_parallel_size {tp}")
+    return replace(cfg, num_attention_heads=cfg.num_attention_heads // tp,
+                   num_key_value_heads=cfg.num_key_value_heads // tp, intermediate_size=cfg.intermediate_size // tp,
+                   linear_num_key_heads=cfg.linear_num_key_heads // tp,
+                   linear_num_value_heads=cfg.linear_num_value_heads // tp)
+
+
+def fused_projection_rows(cfg: ModelConfig, index: int, parts: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """(rows of the fused input projection q | k | v | z | b | a, channels of the convolution) that belong to the
+    key / value heads [index * H / parts, (index + 1) * H / parts) of a layer with the FULL shapes `cfg`."""
+    hk, hv = cfg.linear_num_key_heads // parts, cfg.linear_num_value_heads // parts
+    kd, vd = hk * cfg.linear_key_head_dim, hv * cfg.linear_value_head_dim
+    K, V, HV, cc = cfg.linear_key_dim, cfg.linear_value_dim, cfg.linear_num_value_heads, cfg.linear_conv_channels
+    ar = lambda lo, n: torch.arange(lo, lo + n)
+    conv = torch.cat([ar(index * kd, kd), ar(K + index * kd, kd), ar(2 * K + index * vd, vd)])
+    rows = torch.cat([conv, ar(cc + index * vd, vd), ar(cc + V + index * hv, hv), ar(cc + V + HV + index * hv, hv)])
+    return rows, conv
+
+
 def full_layer_specs(cfg: ModelConfig, i: int):
     return _layer_specs(cfg, i) + [(f"layers.{i}.w_attn_gate", (cfg.q_dim, cfg.hidden_size), True)]
 
@@ -176,13 +205,18 @@ class HeadParallelPlan:
 
 
 class GatedDeltaLayer(nn.Module):
-    def __init__(self, cfg: ModelConfig, idx: int, flat: FlatParams, branch_group: int = 64):
+    def __init__(self, cfg: ModelConfig, idx: int, flat: FlatParams, branch_group: int = 64, tp=None):
+        """cfg: per-rank shapes. tp: tensor-parallel context (the layer then owns 1/tp of the key / value heads: fused
+        input projection column-parallel, output projection row-parallel, MLP as in the dense decoder)."""
         super().__init__()
         self.cfg, self.idx, self.branch_group = cfg, idx, branch_group
+        self.tp = tp if tp is not None and tp.size > 1 else None
         g = lambda n: flat.params[f"layers.{idx}.{n}"]
         for n in ("input_norm", "w_in", "conv_w", "conv_b", "A_log", "dt_bias", "gdn_norm", "w_out", "post_norm",
                   "w_gate_up", "w_down"):
             setattr(self, n, g(n))
+        if self.tp is not None:
+            self.gdn_norm.tp_partial = True     # replicated weight that sees this rank's heads only
 
     # -- pieces ------------------------------------------------------------------------------
     @staticmethod
@@ -238,7 +272,7 @@ class GatedDeltaLayer(nn.Module):
     def mix(self, y: torch.Tensor, rows: BlockRows) -> torch.Tensor:
         """y: normed rows [rows, H] -> mixer features [rows, Hv * Dv] (input of the output projection)."""
         bs = rows.block_size
-        p = _adapted_linear(self, y, "w_in")
+        p = linear(y, self.w_in, self.tp) if self.tp is not None else _adapted_linear(self, y, "w_in")
         plan = rows.head_parallel
         if plan is None:
             sh = _HeadShard(self)
@@ -264,22 +298,45 @@ class GatedDeltaLayer(nn.Module):
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
         if getattr(self, "lora", None) is not None:
             return _adapted_mlp(self, h + _adapted_linear(self, self.mix(y, rows), "w_out"))
+        tp = self.tp
+        if tp is not None:
+            h = row_parallel_linear_residual(self.mix(y, rows), self.w_out, h, tp)
+            y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
+            return row_parallel_linear_residual(linear_swiglu(y2, self.w_gate_up, tp), self.w_down, h, tp, last=True)
         h = linear_residual(self.mix(y, rows), self.w_out, h)
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
         return row_parallel_linear_residual(linear_swiglu(y2, self.w_gate_up), self.w_down, h, None, last=True)
 
 
 class GatedAttentionLayer(nn.Module):
-    def __init__(self, cfg: ModelConfig, idx: int, flat: FlatParams):
+    def __init__(self, cfg: ModelConfig, idx: int, flat: FlatParams, tp=None):
         super().__init__()
         self.cfg, self.idx = cfg, idx
+        self.tp = tp if tp is not None and tp.size > 1 else None
         g = lambda n: flat.params[f"layers.{idx}.{n}"]
         for n in ("input_norm", "w_qkv", "w_attn_gate", "w_o", "post_norm", "w_gate_up", "w_down"):
             setattr(self, n, g(n))
         self.q_norm = g("q_norm") if cfg.qk_norm else None
         self.k_norm = g("k_norm") if cfg.qk_norm else None
+        if self.tp is not None:
+            for p in (self.q_norm, self.k_norm):
+                if p is not None:
+                    p.tp_partial = True
+
+    def _forward_tensor_parallel(self, h, positions, inv_freq, attend):
+        cfg, tp = self.cfg, self.tp
+        y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
+        qkv = qk_norm_rope(linear(y, self.w_qkv, tp), positions, inv_freq, self.q_norm, self.k_norm,
+                           cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
+        gate = torch.sigmoid(linear(y, self.w_attn_gate, tp).float())
+        a = (attend(qkv, self.idx).float() * gate).to(h.dtype)
+        h = row_parallel_linear_residual(a, self.w_o, h, tp)
+        y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
+        return row_parallel_linear_residual(linear_swiglu(y2, self.w_gate_up, tp), self.w_down, h, tp, last=True)
 
     def forward(self, h, positions, inv_freq, attend):
+        if self.tp is not None:
+            return self._forward_tensor_parallel(h, positions, inv_freq, attend)
         cfg = self.cfg
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
         qkv = qk_norm_rope(_adapted_linear(self, y, "w_qkv"), positions, inv_freq, self.q_norm, self.k_norm,
@@ -299,43 +356,90 @@ class HybridBlockDiffusionTransformer(BlockDiffusionTransformer):
 
     def __init__(self, cfg: ModelConfig, *, dtype=torch.bfloat16, device="cpu", grad_dtype=None,
                  activation_checkpointing: bool = True, activation_offload: bool = False, seed: int = 0,
-                 init_std: float = 0.02, frozen: bool = False, branch_group: int = 64):
+                 init_std: float = 0.02, frozen: bool = False, branch_group: int = 64, tp=None):
         nn.Module.__init__(self)
         if not cfg.is_hybrid or min(cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim,
                                     cfg.linear_value_head_dim) <= 0:
             raise ValueError("a hybrid model needs full_attention_interval and the linear_* head sizes")
         if cfg.linear_num_value_heads % cfg.linear_num_key_heads:
             raise ValueError("linear_num_value_heads must be a multiple of linear_num_key_heads")
-        self.cfg, self.lcfg, self.tp = cfg, cfg, None
+        self.tp = tp if tp is not None and tp.size > 1 else None
+        tps = self.tp.size if self.tp is not None else 1
+        if self.tp is not None and self.tp.sequence_parallel:
+            raise ValueError("the hybrid family runs tensor parallelism without sequence parallelism")
+        self.cfg, self.lcfg = cfg, local_hybrid_config(cfg, tps)
+        lcfg = self.lcfg
         self.activation_checkpointing = activation_checkpointing
         self.store = ActivationStore(torch.device(device), offload=activation_offload)
         h = cfg.hidden_size
-        specs = [("embed", (cfg.vocab_size, h), True), ("final_norm", (h,), False)]
+        specs = [("embed", (cfg.vocab_size // tps, h), True), ("final_norm", (h,), False)]
         if not cfg.tie_word_embeddings:
-            specs.append(("lm_head", (cfg.vocab_size, h), True))
+            specs.append(("lm_head", (cfg.vocab_size // tps, h), True))
         kinds = [cfg.layer_kind(i) for i in range(cfg.num_layers)]
         for i, kind in enumerate(kinds):
-            specs += full_layer_specs(cfg, i) if kind == "full_attention" else linear_layer_specs(cfg, i)
+            specs += full_layer_specs(lcfg, i) if kind == "full_attention" else linear_layer_specs(lcfg, i)
+        first_replicated = None
+        if self.tp is not None:
+            # the optimizer sums squared gradients of sharded parameters over the tensor-parallel group and counts
+            # replicated ones once: the per-head vectors of the linear-attention layers are sharded although they are
+            # not decayed, so they go in front of the replicated norm weights
+            per_head = ("conv_b", "A_log", "dt_bias")
+            decayed = [sp for sp in specs if sp[2]]
+            nd_sharded = [sp for sp in specs if not sp[2] and sp[0].split(".")[-1] in per_head]
+            nd_repl = [sp for sp in specs if not sp[2] and sp[0].split(".")[-1] not in per_head]
+            specs, first_replicated = decayed + nd_sharded + nd_repl, nd_repl[0][0]
         self.flat = FlatParams(specs, dtype, device, grad_dtype, allocate_grad=not frozen)
+        if first_replicated is not None:
+            self.flat.tp_sharded_numel = self.flat.offsets[first_replicated][0]
         for name, p in self.flat.params.items():
             self.register_parameter(name.replace(".", "_"), p)
         self.embed, self.final_norm = self.flat.params["embed"], self.flat.params["final_norm"]
         self.lm_head = self.flat.params.get("lm_head", self.embed)
         self.layer_kinds = tuple(kinds)
         self.layers = nn.ModuleList(
-            GatedAttentionLayer(cfg, i, self.flat) if kind == "full_attention"
-            else GatedDeltaLayer(cfg, i, self.flat, branch_group) for i, kind in enumerate(kinds))
+            GatedAttentionLayer(lcfg, i, self.flat, self.tp) if kind == "full_attention"
+            else GatedDeltaLayer(lcfg, i, self.flat, branch_group, self.tp) for i, kind in enumerate(kinds))
         self.register_buffer("inv_freq", rope_inv_freq(cfg.head_dim, cfg.rope_theta, device, cfg.rotary_dim), persistent=False)
         self.reset_parameters(seed, init_std)
+
+    @torch.no_grad()
+    def _reset_tensor_parallel_shards(self, seed: int, std: float) -> None:
+        """The family's own sharded matrices start as slices of what a single rank draws (same per-name seeds as
+        `BlockDiffusionTransformer.reset_parameters`): the fused input projection by head segments, the output
+        projection by value-head columns, the attention gate by query heads."""
+        import zlib
+
+        tp, cfg, dev = self.tp, self.cfg, self.flat.data.device
+        gen = torch.Generator(device=dev)
+        for name, p in self.flat.params.items():
+            leaf = name.split(".")[-1]
+            if leaf not in ("w_in", "w_out", "w_attn_gate"):
+                continue
+            gen.manual_seed((seed * 1000003 + zlib.crc32(name.encode())) % (2 ** 63))
+            if leaf == "w_in":
+                full = torch.randn((cfg.linear_in_dim, p.shape[1]), device=dev, generator=gen)
+                rows, _ = fused_projection_rows(cfg, tp.rank, tp.size)
+                p.zero_()
+                p[: rows.numel()].copy_((full[rows.to(dev)] * std).to(p.dtype))
+            elif leaf == "w_out":
+                full = torch.randn((p.shape[0], p.shape[1] * tp.size), device=dev, generator=gen)
+                p.copy_((tp.shard(full, 1) * std).to(p.dtype))
+            else:
+                full = torch.randn((p.shape[0] * tp.size, p.shape[1]), device=dev, generator=gen)
+                p.copy_((tp.shard(full, 0) * std).to(p.dtype))
 
     @torch.no_grad()
     def reset_parameters(self, seed: int, std: float) -> None:
         super().reset_parameters(seed, std)
         hv = self.cfg.linear_num_value_heads
+        tp = getattr(self, "tp", None)
+        if tp is not None:
+            self._reset_tensor_parallel_shards(seed, std)
+        lo, n_hv = (tp.rank * (hv // tp.size), hv // tp.size) if tp is not None else (0, hv)
         for name, p in self.flat.params.items():
             leaf = name.split(".")[-1]
             if leaf == "w_in":         # rows past q | k | v | z | b | a only pad the GEMM's N; nothing reads them
-                c = self.cfg
+                c = self.lcfg
                 p[c.linear_conv_channels + c.linear_value_dim + 2 * c.linear_num_value_heads:].zero_()
             elif leaf == "conv_b":
                 p.zero_()
@@ -343,8 +447,8 @@ class HybridBlockDiffusionTransformer(BlockDiffusionTransformer):
                 p.mul_(0.0)
                 p[:, -1] = 1.0
                 p[:, :-1] = 1.0 / (4 * self.cfg.linear_conv_kernel)
-            elif leaf == "A_log":        # decay rates exp(A_log) spread over [1, 16]
-                p.copy_(torch.log(torch.linspace(1.0, 16.0, hv, device=p.device)).to(p.dtype))
+            elif leaf == "A_log":        # decay rates exp(A_log) spread over [1, 16] (over ALL value heads)
+                p.copy_(torch.log(torch.linspace(1.0, 16.0, hv, device=p.device))[lo:lo + n_hv].to(p.dtype))
             elif leaf == "dt_bias":      # softplus^-1 of time steps spread over [1e-3, 1e-1]
                 dt = torch.exp(torch.linspace(math.log(1e-3), math.log(1e-1), hv, device=p.device))
-                p.copy_((dt + torch.log(-torch.expm1(-dt))).to(p.dtype))
+                p.copy_((dt + torch.log(-torch.expm1(-dt)))[lo:lo + n_hv].to(p.dtype))
