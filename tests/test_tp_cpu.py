@@ -4,7 +4,7 @@ import copy
 import pytest
 import torch
 
-from tests._harness import run_ranks
+from tests._harness import assert_params_close, run_ranks
 
 MAPPING = {
     "model": {"id": "synthetic:tiny-qwen3", "seq_len": 128, "dtype": "fp32", "num_layers": 2},
@@ -46,12 +46,12 @@ def test_tp2_matches_single_process():
     for r, (losses, norms, fnorm, w_down, w_qkv, q_norm, in_norm) in enumerate(outs):
         assert losses == pytest.approx(ref[0], rel=2e-4, abs=2e-4)
         assert norms == pytest.approx(ref[1], rel=2e-3)
-        assert torch.allclose(torch.from_numpy(fnorm), ref[2], rtol=1e-3, atol=2e-5)
+        assert_params_close(fnorm, ref[2], rtol=1e-3, atol=2e-5)
         full = ref[3]
         n = full.shape[1] // 2
-        assert torch.allclose(torch.from_numpy(w_down), full[:, r * n:(r + 1) * n], rtol=1e-3, atol=1e-4)
+        assert_params_close(w_down, full[:, r * n:(r + 1) * n], rtol=1e-3, atol=1e-4)
         # replicated weights whose gradient a rank sees only partly (its heads) stay equal to the single-rank run
-        assert torch.allclose(torch.from_numpy(q_norm), ref[5], rtol=1e-3, atol=2e-5)
+        assert_params_close(q_norm, ref[5], rtol=1e-3, atol=2e-5)
 
 
 @pytest.mark.distributed
@@ -63,12 +63,12 @@ def test_tp2_with_sequence_parallel_rows_matches_single_process():
     for r, (losses, norms, fnorm, w_down, w_qkv, q_norm, in_norm) in enumerate(outs):
         assert losses == pytest.approx(ref[0], rel=2e-4, abs=2e-4)
         assert norms == pytest.approx(ref[1], rel=2e-3)
-        assert torch.allclose(torch.from_numpy(fnorm), ref[2], rtol=1e-3, atol=2e-5)
-        assert torch.allclose(torch.from_numpy(q_norm), ref[5], rtol=1e-3, atol=2e-5)
-        assert torch.allclose(torch.from_numpy(in_norm), ref[6], rtol=1e-3, atol=2e-5)
+        assert_params_close(fnorm, ref[2], rtol=1e-3, atol=2e-5)
+        assert_params_close(q_norm, ref[5], rtol=1e-3, atol=2e-5)
+        assert_params_close(in_norm, ref[6], rtol=1e-3, atol=2e-5)
         full = ref[3]
         n = full.shape[1] // 2
-        assert torch.allclose(torch.from_numpy(w_down), full[:, r * n:(r + 1) * n], rtol=1e-3, atol=1e-4)
+        assert_params_close(w_down, full[:, r * n:(r + 1) * n], rtol=1e-3, atol=1e-4)
 
 
 def _run_lora(rank, world, tp, steps, sp=False):
@@ -107,14 +107,14 @@ def test_lora_under_tensor_parallelism_matches_single_process(sp):
     for r, (losses, norms, qkv_a, down_b, down_a, gu_b) in enumerate(outs):
         assert losses == pytest.approx(ref[0], rel=3e-4, abs=3e-4)
         assert norms == pytest.approx(ref[1], rel=3e-3)
-        assert torch.allclose(torch.from_numpy(qkv_a), ref[2], rtol=2e-3, atol=2e-5)       # replicated A
-        assert torch.allclose(torch.from_numpy(down_b), ref[3], rtol=2e-3, atol=2e-5)      # replicated B
+        assert_params_close(qkv_a, ref[2], rtol=2e-3, atol=2e-5)       # replicated A
+        assert_params_close(down_b, ref[3], rtol=2e-3, atol=2e-5)      # replicated B
         full = ref[4]
         n = full.shape[1] // 2
-        assert torch.allclose(torch.from_numpy(down_a), full[:, r * n:(r + 1) * n], rtol=2e-3, atol=2e-5)
+        assert_params_close(down_a, full[:, r * n:(r + 1) * n], rtol=2e-3, atol=2e-5)
         full = ref[5]
         n = full.shape[0] // 2
-        assert torch.allclose(torch.from_numpy(gu_b), full[r * n:(r + 1) * n], rtol=2e-3, atol=2e-5)
+        assert_params_close(gu_b, full[r * n:(r + 1) * n], rtol=2e-3, atol=2e-5)
 
 
 def _run_hybrid(rank, world, tp, steps):
@@ -159,10 +159,10 @@ def test_hybrid_family_under_tensor_parallelism_matches_single_process():
         got = torch.from_numpy(w_in)
         assert torch.allclose(got[: rows.numel()], ref[2][rows], rtol=2e-3, atol=2e-5)
         hv = cfg.linear_num_value_heads // 2
-        assert torch.allclose(torch.from_numpy(a_log), ref[3][r * hv:(r + 1) * hv], rtol=2e-3, atol=2e-5)
-        assert torch.allclose(torch.from_numpy(gdn_norm), ref[4], rtol=2e-3, atol=2e-5)        # replicated, partial grads summed
+        assert_params_close(a_log, ref[3][r * hv:(r + 1) * hv], rtol=2e-3, atol=2e-5)
+        assert_params_close(gdn_norm, ref[4], rtol=2e-3, atol=2e-5)        # replicated, partial grads summed
         n = ref[5].shape[0] // 2
-        assert torch.allclose(torch.from_numpy(gate), ref[5][r * n:(r + 1) * n], rtol=2e-3, atol=2e-5)
+        assert_params_close(gate, ref[5][r * n:(r + 1) * n], rtol=2e-3, atol=2e-5)
         n = ref[6].shape[1] // 2
-        assert torch.allclose(torch.from_numpy(w_out), ref[6][:, r * n:(r + 1) * n], rtol=2e-3, atol=2e-5)
-        assert torch.allclose(torch.from_numpy(q_norm), ref[7], rtol=2e-3, atol=2e-5)
+        assert_params_close(w_out, ref[6][:, r * n:(r + 1) * n], rtol=2e-3, atol=2e-5)
+        assert_params_close(q_norm, ref[7], rtol=2e-3, atol=2e-5)

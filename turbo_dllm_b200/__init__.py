@@ -7,7 +7,7 @@ objective descriptors. Heavy modules are imported lazily so `import turbo_dllm_b
 """
 from __future__ import annotations
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 _LAZY = {
     "RunSpec": ("turbo_dllm_b200.config.run_spec", "RunSpec"),
