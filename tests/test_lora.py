@@ -104,3 +104,52 @@ def test_moe_session_trains_only_the_adapters():
     assert not torch.equal(s.lora.flat_experts.data, a0)
     state = s.state_dict()
     assert "adapter" in state and "adapter_experts" in state
+
+
+def test_moe_export_merges_adapters_by_a_checked_plan(tmp_path):
+    """Export of a mixture-of-experts model with adapters: the plan lists linear and grouped merges with their
+    shapes (and refuses a pair that does not fit), the written expert weights are the merged ones, the dense
+    branch beside the experts is exported too."""
+    from dataclasses import replace
+
+    import pytest
+    from safetensors import safe_open
+
+    from turbo_dllm_b200.adapters.lora import lora_merge_plan
+    from turbo_dllm_b200.models.export import export_moe_checkpoint
+    from turbo_dllm_b200.models.hf_loader import interleave_gate_up
+    from turbo_dllm_b200.models.moe import MoEBlockDiffusionTransformer
+
+    cfg = replace(PRESETS["synthetic:tiny-moe"], moe_shared_intermediate_size=64, num_layers=1)
+    model = MoEBlockDiffusionTransformer(cfg, dtype=torch.float32, seed=2, init_std=0.05)
+    st = apply_lora(model, rank=4, alpha=8.0, targets=("attention", "experts"), seed=3)
+    with torch.no_grad():
+        for flat in (st.flat, st.flat_experts):
+            for n, p in flat.params.items():
+                if n.endswith("lora_B"):
+                    p.normal_(0, 0.05)
+    plan = lora_merge_plan(model)
+    kinds = {e["target"]: e["kind"] for e in plan}
+    assert kinds["layers.0.experts_gate_up"] == "grouped" and kinds["layers.0.w_qkv"] == "linear"
+    bank = model.layers[0].experts
+    a, b = st.expert_pair(0, "experts_down")
+    want_down = bank.w_down.detach() + torch.bmm(b.float(), a.float()) * st.scale
+    a, b = st.expert_pair(0, "experts_gate_up")
+    want_gu = bank.w_gu.detach() + torch.bmm(b.float(), a.float()) * st.scale
+    export_moe_checkpoint(model, str(tmp_path / "out"))
+    assert model.lora is None
+    with safe_open(str(tmp_path / "out" / "model.safetensors"), "pt") as f:
+        names = set(f.keys())
+        down3 = f.get_tensor("model.layers.0.mlp.experts.3.down_proj.weight")
+        g3 = f.get_tensor("model.layers.0.mlp.experts.3.gate_proj.weight")
+        u3 = f.get_tensor("model.layers.0.mlp.experts.3.up_proj.weight")
+    assert torch.allclose(down3, want_down[3], atol=1e-6)
+    assert torch.allclose(interleave_gate_up(g3, u3), want_gu[3], atol=1e-6)
+    assert "model.layers.0.mlp.shared_expert.down_proj.weight" in names
+    # a pair that does not fit its target is refused before anything is merged
+    model2 = MoEBlockDiffusionTransformer(cfg, dtype=torch.float32, seed=2, init_std=0.05)
+    st2 = apply_lora(model2, rank=4, targets=("attention", "experts"), seed=3)
+    good = st2.flat.params["layers.0.w_o.lora_B"]
+    st2.flat.params["layers.0.w_o.lora_B"] = torch.nn.Parameter(good.detach()[:-1].clone())
+    with pytest.raises(ValueError, match="does not fit"):
+        lora_merge_plan(model2)

@@ -155,6 +155,43 @@ def apply_lora(model, *, rank: int, alpha: float | None = None, dropout: float =
     return state
 
 
+def lora_merge_plan(model) -> list[dict]:
+    """What `merge_lora` will do, checked before anything is written: one entry per adapted projection with the
+    target's name and shape, the adapter shapes and the kind (`linear`: W += s·B·A; `grouped`: per expert
+    W[e] += s·B[e]·A[e]). Raises when an adapter does not fit its target.
+    Role of the validated merge plan of dllm_parallel/core/models/backbones/diffusiongemma/export.py:63-376."""
+    st = getattr(model, "lora", None)
+    if st is None:
+        return []
+    plan = []
+    for i, layer in enumerate(model.layers):
+        for n in (n for names in ROLE_TARGETS.values() for n in names):
+            pair = st.pair(i, n)
+            if pair is None:
+                continue
+            a, b = pair
+            w = getattr(layer, n)
+            if b.shape[0] != w.shape[0] or a.shape[1] != w.shape[1] or a.shape[0] != b.shape[1]:
+                raise ValueError(f"layers.{i}.{n}: adapter A{tuple(a.shape)} / B{tuple(b.shape)} does not fit "
+                                 f"the weight {tuple(w.shape)}")
+            plan.append({"target": f"layers.{i}.{n}", "kind": "linear", "weight": list(w.shape),
+                         "A": list(a.shape), "B": list(b.shape), "scale": st.scale})
+        bank = getattr(layer, "experts", None)
+        if bank is not None:
+            for n, w in (("experts_gate_up", bank.w_gu), ("experts_down", bank.w_down)):
+                pair = st.expert_pair(i, n)
+                if pair is None:
+                    continue
+                a, b = pair
+                if (a.shape[0] != w.shape[0] or b.shape[0] != w.shape[0] or b.shape[1] != w.shape[1]
+                        or a.shape[2] != w.shape[2] or a.shape[1] != b.shape[2]):
+                    raise ValueError(f"layers.{i}.{n}: expert adapters A{tuple(a.shape)} / B{tuple(b.shape)} do not "
+                                     f"fit the stacked weight {tuple(w.shape)}")
+                plan.append({"target": f"layers.{i}.{n}", "kind": "grouped", "weight": list(w.shape),
+                             "A": list(a.shape), "B": list(b.shape), "scale": st.scale})
+    return plan
+
+
 @torch.no_grad()
 def merge_lora(model) -> None:
     """W += scale · B·A for every adapted projection (after which the adapters can be dropped)."""

@@ -44,11 +44,15 @@ def export_training_checkpoint(spec, checkpoint_dir: str, output: str, tag: str 
     session = TrainingSession(spec, device="cpu" if spec.model.dtype == "fp32" or not torch.cuda.is_available()
                               else "cuda")
     meta = load_training_checkpoint(checkpoint_dir, tag, session, rank=0, world_size=1, restore_rng=False)
+    from ..adapters.lora import lora_merge_plan
+
+    plan = lora_merge_plan(session.model)        # validated before anything is merged or written
     if session.cfg.is_moe:
         export_moe_checkpoint(session.model, output)
     else:
         export_hf_checkpoint(session.model, output)
-    return write_export_manifest(output, {"step": meta["step"], "source_checkpoint": os.path.abspath(checkpoint_dir)})
+    return write_export_manifest(output, {"step": meta["step"], "source_checkpoint": os.path.abspath(checkpoint_dir),
+                                          "merged_adapters": plan})
 
 
 @torch.no_grad()
@@ -59,13 +63,41 @@ def export_moe_checkpoint(model, path: str) -> str:
     from .hf_loader import deinterleave_gate_up, hf_config_dict
 
     cfg = model.cfg
+    if getattr(model, "lora", None) is not None:      # adapters (replicated and per-expert) go into the weights
+        from ..adapters.lora import lora_merge_plan, merge_lora
+
+        lora_merge_plan(model)
+        merge_lora(model)
+        for layer in model.layers:
+            layer.lora = None
+            layer.experts.lora = None
+        model.lora = None
     os.makedirs(path, exist_ok=True)
+    from .hf_loader import _apply_partial_rotary_order
+
+    _apply_partial_rotary_order(model, inverse=True)
+    try:
+        return _write_moe_checkpoint(model, cfg, path)
+    finally:
+        _apply_partial_rotary_order(model, inverse=False)
+
+
+@torch.no_grad()
+def _write_moe_checkpoint(model, cfg, path: str) -> str:
+    from safetensors.torch import save_file
+
+    from .hf_loader import deinterleave_gate_up, hf_config_dict
+
     out = {"model.embed_tokens.weight": model.embed, "model.norm.weight": model.final_norm}
     if not cfg.tie_word_embeddings:
         out["lm_head.weight"] = model.lm_head
     for i, layer in enumerate(model.layers):
         p = f"model.layers.{i}."
         qd, kd = cfg.q_dim, cfg.kv_dim
+        if layer.w_gate_up is not None:      # the dense feed-forward beside the experts
+            g, u = deinterleave_gate_up(layer.w_gate_up)
+            out[p + "mlp.shared_expert.gate_proj.weight"], out[p + "mlp.shared_expert.up_proj.weight"] = g, u
+            out[p + "mlp.shared_expert.down_proj.weight"] = layer.w_down
         out[p + "self_attn.q_proj.weight"], out[p + "self_attn.k_proj.weight"] = layer.w_qkv[:qd], layer.w_qkv[qd:qd + kd]
         out[p + "self_attn.v_proj.weight"], out[p + "self_attn.o_proj.weight"] = layer.w_qkv[qd + kd:], layer.w_o
         out[p + "input_layernorm.weight"], out[p + "post_attention_layernorm.weight"] = layer.input_norm, layer.post_norm
@@ -79,7 +111,8 @@ def export_moe_checkpoint(model, path: str) -> str:
     save_file({k: v.detach().cpu().contiguous() for k, v in out.items()}, os.path.join(path, "model.safetensors"))
     c = hf_config_dict(cfg)
     c.update({"num_experts": cfg.num_experts, "num_experts_per_tok": cfg.num_experts_per_token,
-              "moe_intermediate_size": cfg.moe_intermediate_size, "model_type": "turbo_dllm_moe"})
+              "moe_intermediate_size": cfg.moe_intermediate_size,
+              "shared_expert_intermediate_size": cfg.moe_shared_intermediate_size, "model_type": "turbo_dllm_moe"})
     json.dump(c, open(os.path.join(path, "config.json"), "w"), indent=1)
     return path
 
