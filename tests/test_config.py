@@ -87,3 +87,35 @@ def test_every_field_has_a_cli_flag():
 def test_global_batch_rule():
     s = RunSpec.from_mapping(base(training={"batch_size": 2, "gradient_accumulation_steps": 3}))
     assert s.global_batch(4) == 24
+
+
+def test_settings_without_effect_are_refused_and_debug_checks_fire():
+    import torch
+
+    from turbo_dllm_b200.config.run_spec import RunSpec, RunSpecError
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    base = {"model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "num_layers": 1},
+            "objective": {"name": "standard_block_diffusion", "block_size": 16},
+            "training": {"batch_size": 1, "steps": 1},
+            "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}
+    for section, field, value in (("optimizer", "zero_reduce_bucket_size", 1 << 20), ("optimizer", "fsdp_sharding_strategy", "no_shard"),
+                                  ("training", "activation_checkpointing_scope", "mlp"), ("kernel", "mlp_token_chunk_size", 512),
+                                  ("model", "draft_vocab_path", "/x"), ("objective", "bp_loss_scale", 3.0)):
+        m = {**base, section: {**base.get(section, {}), field: value}}
+        with pytest.raises(RunSpecError, match=field):
+            RunSpec.from_mapping(m).validate()
+    RunSpec.from_mapping({**base, "objective": {**base["objective"], "bp_loss_scale": 1.0}}).validate()
+    s = TrainingSession(RunSpec.from_mapping({**base, "debug": {"grad_finite": True, "optimizer_finite": True}}).validate(),
+                        device="cpu")
+    s.step()                                       # finite run: nothing raised
+    orig = s.forward_backward
+
+    def poisoned(batch, denom):
+        out = orig(batch, denom)
+        s.model.flat.params["layers.0.w_o"].main_grad[0, 0] = float("nan")
+        return out
+
+    s.forward_backward = poisoned
+    with pytest.raises(FloatingPointError, match="layers.0.w_o"):
+        s.step()

@@ -181,6 +181,29 @@ class RunSpec:
             allowed = objectives_for_family(m.family)
             need(o.name in allowed, f"objective {o.name} is not supported by family {m.family} "
                                     f"(supported: {', '.join(allowed)})")
+        # settings of other stacks' backends that nothing here reads: a value other than the default would be
+        # silently ignored, so it is refused
+        for section, name, default, why in (
+                ("optimizer", "zero_optimizer_impl", "auto", "the sharded AdamW of this package is the only implementation"),
+                ("optimizer", "zero_param_group_max_elements", 0, "the optimizer works on one flat buffer"),
+                ("optimizer", "zero_reduce_bucket_size", 0, "gradients are reduced as one flat buffer (or per layer under fsdp)"),
+                ("optimizer", "zero_contiguous_gradients", True, "gradients always live in one contiguous buffer"),
+                ("optimizer", "zero_overlap_comm", True, "the fused step orders its own phases"),
+                ("optimizer", "allow_deepspeed_op_build", False, "no DeepSpeed ops are built or used"),
+                ("optimizer", "fsdp_mixed_precision", None, "parameter shards are bf16 with fp32 gradients and master weights"),
+                ("optimizer", "fsdp_sharding_strategy", "full_shard", "parameter sharding is always full sharding over the data-parallel group"),
+                ("optimizer", "fsdp_use_orig_params", True, "parameters are views of flat buffers"),
+                ("training", "activation_checkpointing_scope", "full", "checkpointing wraps whole layers"),
+                ("kernel", "ring_attention_key_chunk_size", 0, "key tiles are streamed by the attention kernel itself"),
+                ("kernel", "mlp_token_chunk_size", 0, "the MLP runs on all rows of a rank at once"),
+                ("kernel", "cp_bp_attention_policy", "production", "one attention policy is built"),
+                ("model", "draft_vocab_path", None, "drafters use the verifier's vocabulary")):
+            v = getattr(getattr(self, section), name)
+            need(v == default, f"{section}.{name}={v!r} has no effect here ({why}); leave it at {default!r}")
+        if o.bp_loss_scale is not None:
+            need(abs(float(o.bp_loss_scale) - float(bp if bp > 1 else 1)) < 1e-6,
+                 f"objective.bp_loss_scale={o.bp_loss_scale} differs from the block-parallel degree {bp if bp > 1 else 1}: "
+                 "gradients are summed over ranks and divided by the global token count, so no other scale applies")
         if o.name == "dflash_distillation":
             need(cp == 1 or cp == bp, "dflash_distillation divides anchors and context rows over the same ranks: "
                                       "context_parallel_size must be 1 or equal block_parallel_size")

@@ -192,6 +192,19 @@ def model_config_from_run_spec(spec) -> ModelConfig:
         over["num_layers"] = min(over.get("num_layers", base.num_layers), m.max_layers)
     over["qk_norm"] = m.qk_norm and base.qk_norm
     cfg = replace(base, **over)
+    if cfg.mask_token_id is None and m.mask_token:
+        # model.mask_token names the mask token; its id comes from the tokenizer that ships with the checkpoint
+        import os
+
+        if not os.path.isdir(m.id):
+            raise ValueError(f"model.mask_token={m.mask_token!r} needs a local checkpoint directory with a tokenizer "
+                             "(model.id); give model.mask_token_id instead")
+        from transformers import AutoTokenizer
+
+        tid = AutoTokenizer.from_pretrained(m.id).convert_tokens_to_ids(m.mask_token)
+        if tid is None or tid < 0:
+            raise ValueError(f"the tokenizer of {m.id} has no token {m.mask_token!r}")
+        cfg = replace(cfg, mask_token_id=int(tid))
     if cfg.mask_token_id is None:
         cfg = replace(cfg, mask_token_id=cfg.vocab_size - 1)
     return cfg

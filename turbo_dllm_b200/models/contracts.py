@@ -154,6 +154,10 @@ class DenseExecutor(_ExecutorBase):
         tp = None
         if rt is not None and rt.tensor_parallel_size > 1:
             tp = TPContext(rt.tensor_group, spec.topology.sequence_parallel)
+            if not spec.topology.tensor_parallel_overlap:
+                # projections and their collectives as separate steps (GEMM + NCCL) instead of the fused kernels
+                tp.fused_allreduce_enabled = False
+                tp.fused_sequence_parallel_enabled = False
         return BlockDiffusionTransformer(ctx.cfg, dtype=ctx.dtype, device=ctx.device,
                                          activation_checkpointing=spec.training.activation_checkpointing,
                                          activation_offload=ctx.activation_offload, seed=ctx.seed, tp=tp)

@@ -450,6 +450,7 @@ class ContextParallelAttention:
         self.cfg, self.layout, self.rt = cfg, layout, runtime
         self.store = store                  # the model's ActivationStore (None: nothing is kept across layers)
         self.keep_pulled_rows = False
+        self.debug_nonfinite = bool(spec.kernel.cp_bp_debug_nonfinite_attention)
         self.group = runtime.context_group
         cp = runtime.context_parallel_size
         seq_len, bs = spec.model.seq_len, spec.objective.block_size
@@ -611,6 +612,14 @@ class ContextParallelAttention:
         return out.reshape(rows, Hq * D)
 
     def __call__(self, qkv, layer_idx):
+        out = self._attend(qkv, layer_idx)
+        if self.debug_nonfinite and not bool(torch.isfinite(out).all()):
+            # kernel.cp_bp_debug_nonfinite_attention: name the first layer whose attention output went bad
+            raise FloatingPointError(f"non-finite attention output in layer {layer_idx} on rank {self.rt.rank} "
+                                     f"(transport {self.transport})")
+        return out
+
+    def _attend(self, qkv, layer_idx):
         if self.window_mask is not None and self.cfg.layer_window(layer_idx) is not None:
             return self._windowed(qkv)
         if self.transport == "streaming":

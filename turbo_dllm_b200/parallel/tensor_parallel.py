@@ -168,7 +168,8 @@ class TPContext:
         import os
 
         if (self.size < 2 or torch.device(device).type != "cuda" or rows % (256 * self.size)
-                or os.environ.get("TDLLM_TP_FUSED_SP", "1") == "0"):
+                or os.environ.get("TDLLM_TP_FUSED_SP", "1") == "0"
+                or not getattr(self, "fused_sequence_parallel_enabled", True)):     # topology.tensor_parallel_overlap
             return None
         key = ("sp", rows, cols)
         ws = self._fused_ar.get(key)

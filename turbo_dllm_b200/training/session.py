@@ -604,6 +604,12 @@ class TrainingSession:
                 self._sync_tensor_parallel_partial_gradients()     # once, on the sums over the micro-batches
             if getattr(self, "_grad_div", 1.0) != 1.0:
                 self.model.flat.grad.div_(self._grad_div)
+        if spec.debug.grad_finite:      # debug.grad_finite: stop at the first non-finite gradient, naming the buffer
+            for i, f in enumerate(self.flats()):
+                if not bool(torch.isfinite(f.grad).all()):
+                    bad = [n for n, p in f.params.items() if not bool(torch.isfinite(p.main_grad).all())]
+                    raise FloatingPointError(f"non-finite gradient at step {self.steps_done + 1} in buffer {i}: "
+                                             f"{', '.join(bad[:8])}")
         lr, wd = self.scheduler.step()
         clip = spec.optimizer.gradient_clip_norm
         if spec.training.skip_optimizer_step:
@@ -623,6 +629,12 @@ class TrainingSession:
             with self._phase("optimizer"):
                 self.optimizer.apply_update(total_sq, lr=lr, weight_decay=wd, max_grad_norm=clip)
                 self.expert_optimizer.apply_update(total_sq, lr=lr, weight_decay=wd, max_grad_norm=clip)
+        if spec.debug.optimizer_finite and not spec.training.skip_optimizer_step:
+            for i, f in enumerate(self.flats()):      # debug.optimizer_finite: parameters after the update
+                if not bool(torch.isfinite(f.data).all()):
+                    bad = [n for n, p in f.params.items() if not bool(torch.isfinite(p).all())]
+                    raise FloatingPointError(f"non-finite parameters after the optimizer step {self.steps_done + 1} in "
+                                             f"buffer {i}: {', '.join(bad[:8])}")
         self.steps_done += 1
         return StepResult(total, denom, torch.tensor(rows), sum(int(b.input_ids.numel()) for b in batches),
                           sum(b.h2d_bytes for b in batches))
