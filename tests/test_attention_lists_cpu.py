@@ -89,3 +89,38 @@ def test_grouped_row_layout_tables():
         owners = [k for k in range(len(begin)) if begin[k] <= row < begin[k] + (int(counts[k]) + PAD - 1) // PAD * PAD]
         assert not owners or owners[0] == e
     assert g.row_blocks_end.tolist() == [(b + (int(n) + 63) // 64 * 64) // 64 for b, n in zip(begin, counts.tolist())]
+
+
+def test_wide_attention_chunks_cover_every_query_tile_and_every_visible_key():
+    """The product-and-softmax form of attention (head widths other than 128) walks chunks of whole query tiles and,
+    per chunk, the key tiles some row of the chunk can see: together the chunks cover all query rows once, and no
+    visible key is left out of its chunk."""
+    import torch
+
+    from turbo_dllm_b200.ops import wide_attention as wa
+    from turbo_dllm_b200.ops.attention import single_sequence_layout
+
+    layout = single_sequence_layout(640, 32, "cpu", 2)              # 1920 rows: 15 query tiles
+    dense = layout.dense_mask()
+    old = wa.SCORE_BYTES
+    try:
+        for budget in (1 << 30, 4 * 128 * 4 * 128 * 6):           # one chunk; a budget that forces several chunks
+            wa.SCORE_BYTES = budget
+            layout._cache.pop(("wide_chunks", 4), None)
+            chunks = wa._chunks(layout, 4)
+            covered = torch.zeros(dense.shape[0], dtype=torch.bool)
+            for r0, rows, krows, valid in chunks:
+                assert r0 % 128 == 0 and rows % 128 == 0 and krows.numel() % 128 == 0
+                live = slice(r0, min(r0 + rows, dense.shape[0]))
+                assert not covered[live].any()
+                covered[live] = True
+                seen = torch.zeros(dense.shape[1], dtype=torch.bool)
+                seen[krows[valid]] = True
+                assert not (dense[live].any(0) & ~seen).any()      # every key some row of the chunk sees is present
+            assert covered.all()
+            if budget < (1 << 30):
+                assert len(chunks) > 1
+                # block-causal structure: the first chunk needs far fewer key tiles than there are
+                assert chunks[0][2].numel() < dense.shape[1]
+    finally:
+        wa.SCORE_BYTES = old

@@ -342,6 +342,25 @@ def attention_backward_native(q, k, v, out, dout, lse, layout: MaskLayout, scale
     return dq, dk, dv
 
 
+def attention_forward_kernels(q, k, v, layout: MaskLayout, scale: float):
+    """(out, lse) from the device kernels for any supported head width: the one-kernel form at 128, tensor-core
+    products around the masked-softmax kernels at the other multiples of 64."""
+    if q.shape[-1] == 128:
+        return attention_forward_native(q, k, v, layout, scale)
+    from .wide_attention import wide_attention_forward
+
+    return wide_attention_forward(q, k, v, layout, scale)
+
+
+def attention_backward_kernels(q, k, v, out, dout, lse, layout: MaskLayout, scale: float):
+    """(dq, dk, dv) against given (out, lse), which may be merged over key shards, for any supported head width."""
+    if q.shape[-1] == 128:
+        return attention_backward_native(q, k, v, out, dout, lse, layout, scale)
+    from .wide_attention import wide_attention_backward
+
+    return wide_attention_backward(q, k, v, out, dout, lse, layout, scale)
+
+
 class _BlockAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, layout, scale):

@@ -228,11 +228,12 @@ class _ExchangeRows(torch.autograd.Function):
 
 
 class _QueryRotation(torch.autograd.Function):
-    """Kernel path of the query rotation (sm_100a attention kernels, head_dim 128)."""
+    """Kernel path of the query rotation (sm_100a attention kernels; head widths 64 / 256 / 512 take the
+    product-and-softmax form, which has the same (out, lse) contract)."""
 
     @staticmethod
     def forward(ctx, q, k, v, cp, plan):
-        from ..ops.attention import attention_forward_native
+        from ..ops.attention import attention_forward_kernels as attention_forward_native
         from ..ops.merge import MergeState
 
         nd, Hq, D = q.shape
@@ -253,7 +254,7 @@ class _QueryRotation(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        from ..ops.attention import attention_backward_native
+        from ..ops.attention import attention_backward_kernels as attention_backward_native
 
         q, k, v, out, lse, q_peers = ctx.saved_tensors
         cp, plan = ctx.cp, ctx.plan
