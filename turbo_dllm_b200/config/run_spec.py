@@ -195,11 +195,15 @@ class RunSpec:
                 ("optimizer", "fsdp_use_orig_params", True, "parameters are views of flat buffers"),
                 ("training", "activation_checkpointing_scope", "full", "checkpointing wraps whole layers"),
                 ("kernel", "ring_attention_key_chunk_size", 0, "key tiles are streamed by the attention kernel itself"),
-                ("kernel", "mlp_token_chunk_size", 0, "the MLP runs on all rows of a rank at once"),
                 ("kernel", "cp_bp_attention_policy", "production", "one attention policy is built"),
                 ("model", "draft_vocab_path", None, "drafters use the verifier's vocabulary")):
             v = getattr(getattr(self, section), name)
             need(v == default, f"{section}.{name}={v!r} has no effect here ({why}); leave it at {default!r}")
+        need(self.kernel.mlp_token_chunk_size >= 0 and self.kernel.mlp_token_chunk_size % 128 == 0,
+             "kernel.mlp_token_chunk_size must be 0 (off) or a multiple of 128 rows")
+        if self.kernel.mlp_token_chunk_size:
+            need(t.tensor_parallel_size == 1 and m.family not in ("qwen3_8", "diffusion_gemma", "dflash"),
+                 "kernel.mlp_token_chunk_size applies to the dense decoder on one tensor-parallel rank")
         if o.bp_loss_scale is not None:
             need(abs(float(o.bp_loss_scale) - float(bp if bp > 1 else 1)) < 1e-6,
                  f"objective.bp_loss_scale={o.bp_loss_scale} differs from the block-parallel degree {bp if bp > 1 else 1}: "

@@ -158,9 +158,12 @@ class DenseExecutor(_ExecutorBase):
                 # projections and their collectives as separate steps (GEMM + NCCL) instead of the fused kernels
                 tp.fused_allreduce_enabled = False
                 tp.fused_sequence_parallel_enabled = False
-        return BlockDiffusionTransformer(ctx.cfg, dtype=ctx.dtype, device=ctx.device,
-                                         activation_checkpointing=spec.training.activation_checkpointing,
-                                         activation_offload=ctx.activation_offload, seed=ctx.seed, tp=tp)
+        model = BlockDiffusionTransformer(ctx.cfg, dtype=ctx.dtype, device=ctx.device,
+                                          activation_checkpointing=spec.training.activation_checkpointing,
+                                          activation_offload=ctx.activation_offload, seed=ctx.seed, tp=tp)
+        for layer in model.layers:
+            layer.mlp_token_chunk = int(spec.kernel.mlp_token_chunk_size)
+        return model
 
 
 class MoEExecutor(_ExecutorBase):

@@ -156,6 +156,13 @@ class DecoderLayer(nn.Module):
         a = attend(qkv, self.idx)          # [rows, Hq_local·D]
         h = row_parallel_linear_residual(a, self.w_o, h, tp)
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
+        chunk = int(getattr(self, "mlp_token_chunk", 0) or 0)
+        if chunk > 0 and tpg is None and h.shape[0] > chunk:
+            # kernel.mlp_token_chunk_size: the feed-forward runs over row chunks, so its [rows, 2·I] intermediate
+            # never exists for more than `chunk` rows at a time
+            outs = [linear_residual(linear_swiglu(y2[r: r + chunk], self.w_gate_up), self.w_down, h[r: r + chunk])
+                    for r in range(0, h.shape[0], chunk)]
+            return torch.cat(outs, dim=0)
         act = linear_swiglu(y2, self.w_gate_up, tp) if tpg is not None else linear_swiglu(y2, self.w_gate_up)
         return row_parallel_linear_residual(act, self.w_down, h, tp, last=True)
 
