@@ -48,3 +48,43 @@ def test_a_store_captured_for_other_layers_is_refused(tmp_path):
     (store / "shard_00000.pt").write_bytes(b"damaged")
     with pytest.raises(ValueError, match="sha256"):
         FeatureStore(str(store), verify=True)
+
+
+def _capture(rank, world, out, batches, resume=False):
+    import torch.distributed as dist
+
+    torch.set_num_threads(2)
+    man = capture_features(_spec("online"), out, batches, rank=rank, world=world, barrier=dist.barrier, resume=resume)
+    return man.get("shards", []) if man else []
+
+
+def test_capture_over_two_ranks_and_resume(tmp_path):
+    """Two ranks write alternating records and rank 0 merges the manifest in record order; an interrupted capture
+    (a record deleted, another damaged) is completed by --resume without rewriting the verified records."""
+    import os
+
+    from tests._harness import run_ranks
+
+    out = str(tmp_path / "features")
+    outs = run_ranks(_capture, 2, args=(out, 5), deadline_s=240)
+    names = [sh["name"] for sh in outs[0]]
+    assert names == [f"shard_{i:05d}.pt" for i in range(5)] and outs[1] == []
+    store = FeatureStore(out, verify=True)
+    assert store.manifest["captured_by_ranks"] == 2 and not [f for f in os.listdir(out) if f.startswith("manifest.rank")]
+    # single-process capture of the same spec writes the same record 0 (rank 0 of one data-parallel rank)
+    solo = str(tmp_path / "solo")
+    man = capture_features(_spec("online"), solo, 1)
+    assert man["shards"][0]["sha256"] == store.manifest["shards"][0]["sha256"]
+    # resume: one record missing, one damaged -> both are rewritten, the rest kept
+    man2 = capture_features(_spec("online"), str(tmp_path / "r"), 3)
+    kept = os.path.getmtime(os.path.join(tmp_path / "r", "shard_00000.pt"))
+    os.unlink(os.path.join(tmp_path / "r", "shard_00001.pt"))
+    open(os.path.join(tmp_path / "r", "shard_00002.pt"), "wb").write(b"damaged")
+    import json as _json
+
+    _json.dump([{**sh, "index": i} for i, sh in enumerate(man2["shards"])],
+               open(os.path.join(tmp_path / "r", "manifest.rank000.json"), "w"))
+    man3 = capture_features(_spec("online"), str(tmp_path / "r"), 3, resume=True)
+    assert [s["sha256"] for s in man3["shards"]] == [s["sha256"] for s in man2["shards"]]
+    assert os.path.getmtime(os.path.join(tmp_path / "r", "shard_00000.pt")) == kept
+    FeatureStore(str(tmp_path / "r"), verify=True)

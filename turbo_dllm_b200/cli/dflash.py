@@ -19,6 +19,7 @@ def run_dflash(argv) -> int:
     p.add_argument("--config", required=True)
     p.add_argument("--output", required=True)
     p.add_argument("--batches", type=int, default=8)
+    p.add_argument("--resume", action="store_true", help="keep records that are already written and verified")
     p = sub.add_parser("export")
     p.add_argument("--config", required=True)
     p.add_argument("--checkpoint", required=True)
@@ -55,8 +56,22 @@ def run_dflash(argv) -> int:
         if a.cmd == "prepare-features":
             from ..data.dflash_features import capture_features
 
-            man = capture_features(load_run_spec(a.config).validate(), a.output, a.batches)
-            print(json.dumps(man))
+            # under torchrun every rank captures its share of the records and rank 0 writes the manifest
+            import os
+
+            rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+            barrier = None
+            if world > 1:
+                import torch
+                import torch.distributed as dist
+
+                if not dist.is_initialized():
+                    dist.init_process_group("nccl" if torch.cuda.is_available() else "gloo")
+                barrier = dist.barrier
+            man = capture_features(load_run_spec(a.config).validate(), a.output, a.batches, rank=rank, world=world,
+                                   barrier=barrier, resume=a.resume)
+            if rank == 0:
+                print(json.dumps(man))
             return 0
         if a.cmd == "export":
             from ..checkpoint import load_training_checkpoint

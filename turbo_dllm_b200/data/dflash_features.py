@@ -28,23 +28,56 @@ def _sha(path):
 
 
 @torch.no_grad()
-def capture_features(spec, output: str, batches: int) -> dict:
+def capture_features(spec, output: str, batches: int, *, rank: int = 0, world: int = 1, barrier=None,
+                     device=None, resume: bool = False) -> dict:
+    """Runs the frozen target over `batches` batches and writes one record per batch. With `world` > 1 every rank
+    (its own data shard: the session's data runtime is seeded per data-parallel rank) writes the records
+    rank, rank + world, ... under its own names, a barrier follows, and rank 0 merges the per-rank lists into
+    `manifest.json` in record order. `resume` keeps records whose file already exists with the recorded hash (a capture
+    that was interrupted continues; the data runtime is advanced past the kept records)."""
     from ..training.session import TrainingSession
 
-    s = TrainingSession(spec)
+    s = TrainingSession(spec, **({"device": device} if device is not None else {}))
     if s.task is None:
         raise ValueError("feature capture needs objective.name=dflash_distillation")
-    os.makedirs(output, exist_ok=False)
+    if rank == 0:
+        os.makedirs(output, exist_ok=resume)
+    if barrier is not None:
+        barrier()
+    part_path = os.path.join(output, f"manifest.rank{rank:03d}.json")
+    done = {}
+    if resume and os.path.exists(part_path):
+        done = {sh["index"]: sh for sh in json.load(open(part_path)) if os.path.exists(os.path.join(output, sh["name"]))
+                and _sha(os.path.join(output, sh["name"])) == sh["sha256"]}
     shards = []
-    for i in range(batches):
+    for i in range(rank, batches, world):
         batch = s.data.next_batch()
+        if i in done:
+            shards.append(done[i])
+            continue
         feats = s.task.target.features(batch.input_ids)
         name = f"shard_{i:05d}.pt"
         torch.save({"input_ids": batch.input_ids.cpu(), "hidden": feats.hidden.cpu(),
                     "final_hidden": feats.final_hidden.cpu()}, os.path.join(output, name))
-        shards.append({"name": name, "records": int(batch.input_ids.shape[0]), "sha256": _sha(os.path.join(output, name))})
+        shards.append({"index": i, "name": name, "records": int(batch.input_ids.shape[0]),
+                       "sha256": _sha(os.path.join(output, name))})
+        json.dump(shards, open(part_path, "w"))          # progress survives an interruption
+    json.dump(shards, open(part_path, "w"))
+    if barrier is not None:
+        barrier()
+    if rank != 0:
+        return {}
+    merged = []
+    for r in range(world):
+        p = os.path.join(output, f"manifest.rank{r:03d}.json")
+        merged += json.load(open(p))
+        os.unlink(p)
+    merged.sort(key=lambda sh: sh["index"])
+    if [sh["index"] for sh in merged] != list(range(batches)):
+        raise RuntimeError(f"feature capture is incomplete: records {sorted(set(range(batches)) - {sh['index'] for sh in merged})} are missing")
     man = {"format": FORMAT, "target": spec.model.verifier_id, "target_layer_ids": list(spec.model.target_layer_ids),
-           "seq_len": spec.model.seq_len, "shards": shards}
+           "seq_len": spec.model.seq_len, "captured_by_ranks": world,
+           "shards": [{k: v for k, v in sh.items() if k != "index"} for sh in merged]}
     json.dump(man, open(os.path.join(output, "manifest.json"), "w"), indent=1)
     return man
 
