@@ -100,7 +100,7 @@ def test_settings_without_effect_are_refused_and_debug_checks_fire():
             "training": {"batch_size": 1, "steps": 1},
             "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}
     for section, field, value in (("optimizer", "zero_reduce_bucket_size", 1 << 20), ("optimizer", "fsdp_sharding_strategy", "no_shard"),
-                                  ("training", "activation_checkpointing_scope", "mlp"), ("kernel", "mlp_token_chunk_size", 100),
+                                  ("kernel", "mlp_token_chunk_size", 100),
                                   ("model", "draft_vocab_path", "/x"), ("objective", "bp_loss_scale", 3.0)):
         m = {**base, section: {**base.get(section, {}), field: value}}
         with pytest.raises(RunSpecError, match=field):
@@ -113,6 +113,18 @@ def test_settings_without_effect_are_refused_and_debug_checks_fire():
                                                   "kernel": {"mlp_token_chunk_size": chunk}}).validate(), device="cpu")
         runs.append((float(t.step().loss_sum), t.model.flat.data.clone()))
     assert runs[0][0] == pytest.approx(runs[1][0], rel=1e-6) and torch.allclose(runs[0][1], runs[1][1], atol=1e-5)
+    # checkpointing only the feed-forward half computes the same step and keeps the residual stream between the halves
+    t = TrainingSession(RunSpec.from_mapping({**base, "model": {**base["model"], "seq_len": 256},
+                                              "training": {**base["training"], "activation_checkpointing_scope": "mlp"}}).validate(),
+                        device="cpu")
+    assert t.model.checkpoint_scope == "mlp"
+    assert float(t.step().loss_sum) == pytest.approx(runs[0][0], rel=1e-6) and torch.allclose(t.model.flat.data, runs[0][1], atol=1e-5)
+    with pytest.raises(RunSpecError, match="activation_checkpointing_scope"):
+        RunSpec.from_mapping({**base, "training": {**base["training"], "activation_checkpointing_scope": "mlp",
+                                                   "activation_checkpointing": False}}).validate()
+    with pytest.raises(RunSpecError, match="activation_checkpointing_scope"):
+        RunSpec.from_mapping({**base, "model": {**base["model"], "family": "qwen3_8", "id": "synthetic:tiny-qwen3-8"},
+                              "training": {**base["training"], "activation_checkpointing_scope": "mlp"}}).validate()
     s = TrainingSession(RunSpec.from_mapping({**base, "debug": {"grad_finite": True, "optimizer_finite": True}}).validate(),
                         device="cpu")
     s.step()                                       # finite run: nothing raised

@@ -193,12 +193,18 @@ class RunSpec:
                 ("optimizer", "fsdp_mixed_precision", None, "parameter shards are bf16 with fp32 gradients and master weights"),
                 ("optimizer", "fsdp_sharding_strategy", "full_shard", "parameter sharding is always full sharding over the data-parallel group"),
                 ("optimizer", "fsdp_use_orig_params", True, "parameters are views of flat buffers"),
-                ("training", "activation_checkpointing_scope", "full", "checkpointing wraps whole layers"),
                 ("kernel", "ring_attention_key_chunk_size", 0, "key tiles are streamed by the attention kernel itself"),
                 ("kernel", "cp_bp_attention_policy", "production", "one attention policy is built"),
                 ("model", "draft_vocab_path", None, "drafters use the verifier's vocabulary")):
             v = getattr(getattr(self, section), name)
             need(v == default, f"{section}.{name}={v!r} has no effect here ({why}); leave it at {default!r}")
+        if tr.activation_checkpointing_scope == "mlp":
+            # the attention half keeps its autograd graph, the feed-forward half is recomputed
+            need(tr.activation_checkpointing, "training.activation_checkpointing_scope=mlp needs training.activation_checkpointing")
+            need(m.family not in ("qwen3_8", "diffusion_gemma", "dflash") and t.tensor_parallel_size == 1
+                 and opt.backend not in ("fsdp", "fsdp2") and self.adapter.type != "lora",
+                 "training.activation_checkpointing_scope=mlp is built for the dense decoder without tensor parallelism, "
+                 "parameter sharding or adapters; use 'full'")
         need(self.kernel.mlp_token_chunk_size >= 0 and self.kernel.mlp_token_chunk_size % 128 == 0,
              "kernel.mlp_token_chunk_size must be 0 (off) or a multiple of 128 rows")
         if self.kernel.mlp_token_chunk_size:

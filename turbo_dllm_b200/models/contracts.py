@@ -163,6 +163,7 @@ class DenseExecutor(_ExecutorBase):
                                           activation_offload=ctx.activation_offload, seed=ctx.seed, tp=tp)
         for layer in model.layers:
             layer.mlp_token_chunk = int(spec.kernel.mlp_token_chunk_size)
+        model.checkpoint_scope = str(spec.training.activation_checkpointing_scope)
         return model
 
 

@@ -149,12 +149,23 @@ class DecoderLayer(nn.Module):
             return self._forward_lora(h, positions, inv_freq, attend)
         if tp is not None and tp.sequence_parallel:
             return self._forward_sequence_parallel(h, positions, inv_freq, attend)
+        return self.mlp_half(self.attention_half(h, positions, inv_freq, attend))
+
+    def attention_half(self, h, positions, inv_freq, attend: Callable):
+        """Residual stream after the attention sub-layer (plain projections: no adapters, no sequence parallelism)."""
+        cfg, tp = self.cfg, self.tp
+        tpg = tp.group if tp is not None and tp.size > 1 else None
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
         qkv = linear(y, self.w_qkv, tp) if tpg is not None else linear(y, self.w_qkv)
         qkv = qk_norm_rope(qkv, positions, inv_freq, self.q_norm, self.k_norm, cfg.num_attention_heads,
                            cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
         a = attend(qkv, self.idx)          # [rows, Hq_local·D]
-        h = row_parallel_linear_residual(a, self.w_o, h, tp)
+        return row_parallel_linear_residual(a, self.w_o, h, tp)
+
+    def mlp_half(self, h):
+        """Residual stream after the feed-forward sub-layer."""
+        cfg, tp = self.cfg, self.tp
+        tpg = tp.group if tp is not None and tp.size > 1 else None
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
         chunk = int(getattr(self, "mlp_token_chunk", 0) or 0)
         if chunk > 0 and tpg is None and h.shape[0] > chunk:
@@ -247,6 +258,8 @@ class LocalAttention:
 
 
 class BlockDiffusionTransformer(nn.Module):
+    checkpoint_scope = "full"     # "mlp" (training.activation_checkpointing_scope): recompute the feed-forward half only
+
     def __init__(self, cfg: ModelConfig, *, dtype=torch.bfloat16, device="cpu", grad_dtype=None,
                  activation_checkpointing: bool = True, activation_offload: bool = False, seed: int = 0,
                  init_std: float = 0.02, frozen: bool = False, tp: TPContext | None = None):
@@ -280,9 +293,9 @@ class BlockDiffusionTransformer(nn.Module):
     def attach_parameter_sharding(self, sharded) -> None:
         """From now on a layer's parameters exist at full size only while the layer runs: `sharded.pre_layer(i)`
         materialises them, the checkpointed backward hands the gradients back (`activation_store`)."""
-        if not self.activation_checkpointing:
-            raise ValueError("parameter sharding needs training.activation_checkpointing (gradients leave a layer "
-                             "when its checkpointed backward ends)")
+        if not self.activation_checkpointing or self.checkpoint_scope != "full":
+            raise ValueError("parameter sharding needs training.activation_checkpointing over whole layers (gradients "
+                             "leave a layer when its checkpointed backward ends)")
         self.sharded = sharded
         for layer in self.layers:
             layer.sharded = sharded
@@ -347,7 +360,13 @@ class BlockDiffusionTransformer(nn.Module):
             if getattr(self, "sharded", None) is not None:
                 self.sharded.pre_layer(i)
             if self.activation_checkpointing and torch.is_grad_enabled():
-                h = checkpointed_layer(layer, h, self.store, i, positions, self.inv_freq, attend)
+                if self.checkpoint_scope == "mlp":
+                    # only the feed-forward half is recomputed: the attention half keeps its graph (its activations
+                    # stay on the device), the residual stream between the halves is what the checkpoint stores
+                    h = layer.attention_half(h, positions, self.inv_freq, attend)
+                    h = checkpointed_layer(layer.mlp_half, h, self.store, i)
+                else:
+                    h = checkpointed_layer(layer, h, self.store, i, positions, self.inv_freq, attend)
             else:
                 h = layer(h, positions, self.inv_freq, attend)
         if sp:
