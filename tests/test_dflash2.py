@@ -232,6 +232,12 @@ def test_dflash2_export_round_trip(tmp_path):
                                                                              cfg.hidden_size)
         assert "embed" not in f.keys() and "lm_head" not in f.keys()
     assert any("block_size" in p for p in validate_dflash2_export(out, expected_block_size=16))
+    # the command-line checks: the shared export check with a block size, and the vLLM loader's contract
+    from turbo_dllm_b200.cli.dflash import run_dflash
+
+    assert run_dflash(["validate-export", out, "--block-size", "8"]) == 0
+    assert run_dflash(["validate-vllm", out, "--block-size", "8"]) == (0 if conf.get("model_type") == "qwen3" else 2)
+    assert run_dflash(["validate-vllm", out, "--block-size", "16"]) == 2
     bad = dict(conf, architectures=["DFlashDraftModel"])
     with pytest.raises(ValueError):
         normalize_dflash2_config(bad)

@@ -1,4 +1,4 @@
-"""`dllm dflash …`: prepare-features, export, validate-export, serve-sglang, serve-vllm,
+"""`dllm dflash …`: prepare-features, export, validate-export, validate-vllm, serve-sglang, serve-vllm,
 verify-sglang, verify-vllm (cf. dllm_parallel/cli/dflash.py:13-110)."""
 from __future__ import annotations
 
@@ -26,6 +26,10 @@ def run_dflash(argv) -> int:
     p.add_argument("--output", required=True)
     p = sub.add_parser("validate-export")
     p.add_argument("path")
+    p.add_argument("--block-size", type=int, default=None, help="the block size the export must carry")
+    p = sub.add_parser("validate-vllm", help="check an exported drafter against what the vLLM loader reads")
+    p.add_argument("path")
+    p.add_argument("--block-size", type=int, default=None)
     for name in ("serve-sglang", "serve-vllm"):
         p = sub.add_parser(name, help="print (default) or start the server command for an exported drafter")
         p.add_argument("--target-model", required=True)
@@ -88,8 +92,20 @@ def run_dflash(argv) -> int:
             # a DFlash2 export carries config.json with its architecture; check its tensor inventory too
             is_v2 = os.path.exists(os.path.join(a.path, "config.json"))
             problems = ex.validate_dflash2_export(a.path) if is_v2 else ex.validate_dflash_export(a.path)
+            if a.block_size is not None and is_v2 and not problems:
+                try:
+                    srv.validate_export_for_server(a.path, "sglang", a.block_size)
+                except ValueError as e:
+                    problems = [str(e)]
             print(json.dumps({"ok": not problems, "problems": problems}))
             return 0 if not problems else 1
+        if a.cmd == "validate-vllm":
+            problems = ex.validate_dflash2_export(a.path)
+            if problems:
+                print(json.dumps({"ok": False, "problems": problems}))
+                return 1
+            print(json.dumps({"ok": True, **srv.validate_export_for_server(a.path, "vllm", a.block_size)}))
+            return 0
         if a.cmd in ("serve-sglang", "serve-vllm"):
             backend = "sglang" if a.cmd == "serve-sglang" else "vllm"
             block = a.block_size if a.num_speculative_tokens is None else a.num_speculative_tokens + 1
