@@ -201,3 +201,165 @@ def test_trajectory_step_units_and_turn_mean_reduction(tmp_path):
     with pytest.raises(RunSpecError, match="turn_mean"):
         RunSpec.from_mapping({"data": {"trajectory_loss_reduction": "turn_mean"},
                               "model": {"id": "synthetic:tiny-qwen3", "dtype": "fp32"}}).validate()
+
+
+def test_preparation_front_end_schema_sources_and_policies(tmp_path):
+    """The documented schema end to end: relative paths against the file, gzip + glob sources, nested fields, string
+    ids, assistant-only supervision through the template's own mask, automatic artifact format."""
+    import gzip
+
+    import yaml
+
+    from turbo_dllm_b200.data.prepare import load_preparation_spec, redact_secrets
+
+    (tmp_path / "raw").mkdir()
+    rows = [{"id": f"conv-{i}", "meta": {"thread": f"t{i // 2}"},
+             "dialog": {"turns": [{"speaker": "user", "body": "question " * (i + 3)},
+                                  {"speaker": "assistant", "body": "reply " * (i + 4), "tool_calls": []}]}}
+            for i in range(10)]
+    with gzip.open(tmp_path / "raw" / "a-000.jsonl.gz", "wt") as f:
+        f.write("\n".join(json.dumps(r) for r in rows[:5]) + "\n\n")
+    _jsonl(tmp_path / "raw" / "a-001.jsonl", rows[5:])
+    (tmp_path / "prepare.yaml").write_text(yaml.safe_dump({
+        "format": "dllm.data.prepare.v1",
+        "source": {"type": "jsonl", "path": "raw/a-*.jsonl*", "loader_kwargs": {"hf_token": "s3cret", "n": 1}},
+        "records": {"type": "messages", "messages_field": "dialog.turns", "role_field": "speaker", "content_field": "body",
+                    "sample_id_field": "id", "group_id_field": "meta.thread"},
+        "tokenizer": {"model": "byte", "add_eos": True},
+        "supervision": {"policy": "assistant_only"},
+        "packing": {"maximum_length": 512, "alignment": 16, "alignment_policy": "truncate_left", "minimum_length": 16},
+        "output": {"path": "prepared", "format": "auto"}}))
+    spec = load_preparation_spec(tmp_path / "prepare.yaml")
+    assert spec.artifact_format == "indexed" and spec.output["path"] == str(tmp_path / "prepared")
+    m = prepare_dataset(spec)
+    assert m["format"] == "dllm_parallel.indexed_supervised_tokens" and m["sample_count"] == 10
+    assert "groups.i64" in m["files"] and m["metadata"]["supervision_shape"] == "assistant_only"
+    assert m["metadata"]["preparation"]["source"]["loader_kwargs"] == {"hf_token": "<redacted>", "n": 1}
+    assert m["metadata"]["source"]["loader_kwargs"]["hf_token"] == "<redacted>"
+    assert [f["name"] for f in m["metadata"]["source"]["files"]] == ["a-000.jsonl.gz", "a-001.jsonl"]
+    validate_artifact(tmp_path / "prepared")
+    idx = np.fromfile(tmp_path / "prepared" / "index.i64", dtype="<i8").reshape(-1, 4)
+    assert (idx[:, 1] % 16 == 0).all() and len(set(idx[:, 3].tolist())) == 10 and (idx[:, 3] > 0).all()
+    groups = np.fromfile(tmp_path / "prepared" / "groups.i64", dtype="<i8")
+    assert groups[0] == groups[1] and groups[1] != groups[2]          # the same thread -> the same hashed group id
+    toks = np.fromfile(tmp_path / "prepared" / "tokens.i32", dtype="<i4")
+    mask = np.fromfile(tmp_path / "prepared" / "loss_mask.u8", dtype=np.uint8)
+    # left truncation keeps the end of each sample: the explicit EOS is the last token and is supervised
+    ends = idx[:, 0] + idx[:, 1] - 1
+    assert (toks[ends] == 257).all() and mask[ends].all()
+    assert not mask[toks == 260].any()                                  # user role markers are never supervised
+    assert redact_secrets({"a": [{"api_key": 1, "b": 2}]}) == {"a": [{"api_key": "<redacted>", "b": 2}]}
+    # conflicting spellings of one setting are refused
+    with pytest.raises(PreparationError, match="two names"):
+        PreparationSpec.from_mapping({"source": {"type": "jsonl", "kind": "text", "path": "x"}, "output": {"path": "y"}})
+    with pytest.raises(PreparationError, match="output.format=packed"):
+        PreparationSpec.from_mapping({"source": {"path": "x"}, "records": {"type": "messages"},
+                                      "supervision": {"policy": "assistant_only"}, "output": {"path": "y", "format": "packed"}})
+    with pytest.raises(PreparationError, match="split"):
+        PreparationSpec.from_mapping({"source": {"path": "x"}, "records": {"type": "messages"},
+                                      "supervision": {"policy": "assistant_only"},
+                                      "packing": {"maximum_length": 64, "overflow": "split"}, "output": {"path": "y"}})
+
+
+def test_pretokenized_sources_prompt_completion_and_separators(tmp_path):
+    from turbo_dllm_b200.data import prepare as prep
+
+    # raw int32 stream (one record) + a 2-D .npy (one record per row), split into chunks, separators between documents only
+    np.arange(100, dtype="<i4").tofile(tmp_path / "a.i32")
+    np.save(tmp_path / "b.npy", np.arange(200, 260, dtype=np.int64).reshape(2, 30))
+    m = prepare_dataset(PreparationSpec.from_mapping({
+        "source": {"type": "pretokenized", "paths": [str(tmp_path / "a.i32"), str(tmp_path / "b.npy")]},
+        "records": {"type": "pretokenized"},
+        "packing": {"maximum_length": 64, "overflow": "split", "separator_token_id": 999},
+        "output": {"path": str(tmp_path / "tok")}}))
+    toks = np.fromfile(tmp_path / "tok" / "tokens.i32", dtype="<i4")
+    assert toks.tolist() == list(range(100)) + [999] + list(range(200, 230)) + [999] + list(range(230, 260))
+    assert m["stats"]["split_records"] == 1 and m["stats"]["separator_tokens"] == 2 and m["sample_count"] == 3
+    # provided supervision: loss_mask wins, labels != -100 is the fallback; named masks for the other policies
+    _jsonl(tmp_path / "p.jsonl", [
+        {"input_ids": list(range(8)), "loss_mask": [0, 0, 0, 0, 1, 1, 1, 1], "labels": [1] * 8},
+        {"input_ids": list(range(8)), "labels": [-100, -100, 5, 5, 5, 5, 5, 5], "assistant_masks": [0] * 7 + [1]}])
+    for policy, want in (("provided", [4, 6]), ("assistant_only", None)):
+        out = tmp_path / f"prov_{policy}"
+        spec = PreparationSpec.from_mapping({
+            "source": {"type": "pretokenized", "path": str(tmp_path / "p.jsonl")}, "records": {"type": "pretokenized"},
+            "supervision": {"policy": policy}, "packing": {"maximum_length": 8}, "output": {"path": str(out)}})
+        if want is None:
+            with pytest.raises(PreparationError, match="assistant_masks"):
+                prepare_dataset(spec)           # the first record has no assistant mask: nothing is guessed
+            continue
+        prepare_dataset(spec)
+        mask = np.fromfile(out / "loss_mask.u8", dtype=np.uint8).reshape(2, 8)
+        assert mask.sum(1).tolist() == want
+    # prompt / completion given as message lists: the rendered prompt must be a prefix; only the completion is supervised
+    _jsonl(tmp_path / "pc.jsonl", [{"prompt": [{"role": "user", "content": "explain"}],
+                                    "completion": [{"role": "assistant", "content": "because"}]},
+                                   {"prompt": "2+2=", "completion": "4"}])
+    with pytest.raises(PreparationError, match="both be strings or both"):
+        _jsonl(tmp_path / "bad.jsonl", [{"prompt": "x", "completion": [{"role": "assistant", "content": "y"}]}])
+        prepare_dataset(PreparationSpec.from_mapping({
+            "source": {"path": str(tmp_path / "bad.jsonl")}, "records": {"type": "prompt_completion"},
+            "supervision": {"policy": "completion_only"}, "output": {"path": str(tmp_path / "bad")}}))
+    prepare_dataset(PreparationSpec.from_mapping({
+        "source": {"path": str(tmp_path / "pc.jsonl")}, "records": {"type": "prompt_completion"},
+        "supervision": {"policy": "completion_only"}, "output": {"path": str(tmp_path / "pc")}}))
+    idx = np.fromfile(tmp_path / "pc" / "index.i64", dtype="<i8").reshape(-1, 4)
+    mask = np.fromfile(tmp_path / "pc" / "loss_mask.u8", dtype=np.uint8)
+    toks = np.fromfile(tmp_path / "pc" / "tokens.i32", dtype="<i4")
+    first = slice(idx[0, 0], idx[0, 0] + idx[0, 1])
+    # user marker + "explain" + end-of-turn + assistant marker are the prompt; "because" + end-of-turn the completion
+    assert mask[first].tolist() == [0] * (1 + 7 + 1 + 1) + [1] * (7 + 1) and toks[first][9] == prep.ByteTokenizer.ROLE["assistant"]
+    second = slice(idx[1, 0], idx[1, 0] + idx[1, 1])
+    assert mask[second].tolist() == [0, 0, 0, 0, 1]
+    # alignment policies of supervised samples
+    rec = prep.TokenizedRecord(np.arange(10, dtype=np.int32), np.ones(10, np.uint8), 0)
+    assert prep.align_record(rec, 4, "truncate_right", 0).tokens.tolist() == list(range(8))
+    assert prep.align_record(rec, 4, "truncate_left", 0).tokens.tolist() == list(range(2, 10))
+    padded = prep.align_record(rec, 4, "pad", 7)
+    assert padded.tokens.tolist() == list(range(10)) + [7, 7] and padded.loss_mask[-2:].tolist() == [0, 0]
+    assert prep.align_record(prep.TokenizedRecord(np.arange(3, dtype=np.int32), np.ones(3, np.uint8), 0), 4, "truncate_right", 0) is None
+    with pytest.raises(PreparationError, match="alignment_policy=reject"):
+        prep.align_record(rec, 4, "reject", 0)
+    # text in line mode
+    (tmp_path / "lines.txt").write_text("first line\n\nsecond line\n")
+    m = prepare_dataset(PreparationSpec.from_mapping({"source": {"type": "text", "path": str(tmp_path / "lines.txt"), "text_mode": "line"},
+                                                      "output": {"path": str(tmp_path / "lines")}}))
+    assert m["sample_count"] == 2 and m["token_count"] == len("first line") + len("second line")
+
+
+def test_registered_sources_formatters_and_cli_overrides(tmp_path, capsys):
+    import yaml
+
+    from turbo_dllm_b200.cli.main import run
+    from turbo_dllm_b200.data import prepare as prep
+
+    prep.register_source("unit_counter", lambda src: ({"n": i} for i in range(int(src["limit"] or 4))), replace=True)
+    prep.register_formatter("unit_number_words", lambda rec, r: prep.FormattedRecord(text=f"number {rec['n']}", sample_id=rec["n"]),
+                            replace=True)
+    with pytest.raises(ValueError, match="already registered"):
+        prep.register_source("unit_counter", lambda src: iter(()))
+    with pytest.raises(PreparationError, match="source.type"):
+        PreparationSpec.from_mapping({"source": {"type": "nowhere", "path": "x"}, "output": {"path": "y"}})
+    cfg = tmp_path / "prepare.yaml"
+    cfg.write_text(yaml.safe_dump({"source": {"type": "unit_counter", "id": "counter"}, "records": {"type": "unit_number_words"},
+                                   "output": {"path": "out_a"}}))
+    assert run(["data", "prepare", "--config", str(cfg)]) == 0
+    first = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert first["samples"] == 4 and (tmp_path / "out_a" / "manifest.json").exists()
+    assert run(["data", "prepare", "--config", str(cfg)]) == 2                       # exists, no overwrite
+    capsys.readouterr()
+    assert run(["data", "prepare", "--config", str(cfg), "--overwrite"]) == 0
+    capsys.readouterr()
+    assert run(["data", "prepare", "--config", str(cfg), "--output", str(tmp_path / "out_b")]) == 0
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["dataset_fingerprint"] == first["dataset_fingerprint"]
+    # compatibility of the artifact with a training run
+    train = tmp_path / "train.yaml"
+    train.write_text(yaml.safe_dump({"model": {"id": "synthetic:tiny-qwen3", "seq_len": 64},
+                                     "objective": {"name": "standard_block_diffusion", "block_size": 16}}))
+    assert run(["data", "validate", str(tmp_path / "out_b"), "--config", str(train)]) == 2   # 36 tokens < one 64-token sequence
+    assert "fewer than one sequence" in capsys.readouterr().err
+    train.write_text(yaml.safe_dump({"model": {"id": "synthetic:tiny-qwen3", "seq_len": 32},
+                                     "objective": {"name": "standard_block_diffusion", "block_size": 16},
+                                     "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}))
+    assert run(["data", "validate", str(tmp_path / "out_b"), "--config", str(train)]) == 0
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["run"]["compatible"]

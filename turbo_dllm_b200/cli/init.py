@@ -9,22 +9,22 @@ import sys
 
 PREPARE_YAML = """format: dllm.data.prepare.v1
 source:
-  kind: jsonl
-  path: data/raw.jsonl
+  type: jsonl            # jsonl | text | parquet | huggingface | pretokenized
+  path: data/raw.jsonl   # relative to this file; a directory or a glob works too
 records:
-  type: text
-  text_column: text
+  type: text             # text | messages | prompt_completion | pretokenized
+  text_field: text
 tokenizer:
   model: byte            # or a local Hugging Face tokenizer directory
   add_eos: true
 supervision:
-  mode: full
+  policy: full           # full | assistant_only | completion_only | provided
 packing:
-  mode: packed
-  sequence_length: 4096
-  overflow: split
+  maximum_length: 4096
+  overflow: split        # reject | split | truncate_left | truncate_right
 output:
   path: data/prepared
+  format: auto           # packed stream for full supervision, indexed samples otherwise
 """
 
 TRAIN_YAML = """launch:

@@ -73,6 +73,9 @@ def dataset_fingerprint(*, format_name: str, version: int, metadata: Mapping[str
     if isinstance(prep, dict) and isinstance(prep.get("source"), dict):
         prep["source"].pop("path", None)
         prep["source"].pop("paths", None)
+    if isinstance(prep, dict) and isinstance(prep.get("output"), dict):
+        prep["output"].pop("path", None)          # where the artifact was written says nothing about its contents
+        prep["output"].pop("overwrite", None)
     payload = {"format": format_name, "version": version, "metadata": stable,
                "files": {name: {k: v for k, v in fm.items() if k in {"columns", "dtype", "elements", "sha256"}}
                          for name, fm in files.items()},
