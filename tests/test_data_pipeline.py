@@ -363,3 +363,60 @@ def test_registered_sources_formatters_and_cli_overrides(tmp_path, capsys):
                                      "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}))
     assert run(["data", "validate", str(tmp_path / "out_b"), "--config", str(train)]) == 0
     assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["run"]["compatible"]
+
+
+def _tiny_hf_tokenizer(path, template):
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    vocab = {"<unk>": 0, "<eos>": 1, "<|user|>": 2, "<|assistant|>": 3, "<|end|>": 4}
+    for i, w in enumerate("hello how are you fine thanks explain because".split()):
+        vocab[w] = 5 + i
+    t = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    t.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tok = PreTrainedTokenizerFast(tokenizer_object=t, unk_token="<unk>", eos_token="<eos>")
+    if template:
+        tok.chat_template = template
+    tok.save_pretrained(str(path))
+
+
+def test_chat_template_supervision_with_a_hugging_face_tokenizer(tmp_path):
+    """Assistant-only supervision comes from the template's generation markers; a template without them is refused
+    rather than guessed; message-shaped prompt / completion pairs split at the rendered prompt."""
+    marked = ("{% for m in messages %}{% if m['role']=='assistant' %}<|assistant|> {% generation %}{{ m['content'] }} <|end|> "
+              "{% endgeneration %}{% else %}<|user|> {{ m['content'] }} <|end|> {% endif %}{% endfor %}"
+              "{% if add_generation_prompt %}<|assistant|> {% endif %}")
+    plain = marked.replace("{% generation %}", "").replace("{% endgeneration %}", "")
+    _tiny_hf_tokenizer(tmp_path / "tok_marked", marked)
+    _tiny_hf_tokenizer(tmp_path / "tok_plain", plain)
+    _tiny_hf_tokenizer(tmp_path / "tok_none", None)
+    _jsonl(tmp_path / "chat.jsonl", [{"messages": [{"role": "user", "content": "hello how are you"},
+                                                   {"role": "assistant", "content": "fine thanks"}]}])
+
+    def spec(tok, out, **over):
+        return PreparationSpec.from_mapping({
+            "source": {"type": "jsonl", "path": str(tmp_path / "chat.jsonl")}, "records": {"type": "messages"},
+            "tokenizer": {"model": str(tmp_path / tok), "add_eos": True, **over.get("tokenizer", {})},
+            "supervision": {"policy": over.get("policy", "assistant_only")}, "output": {"path": str(tmp_path / out)}})
+
+    m = prepare_dataset(spec("tok_marked", "a"))
+    toks = np.fromfile(tmp_path / "a" / "tokens.i32", dtype="<i4").tolist()
+    mask = np.fromfile(tmp_path / "a" / "loss_mask.u8", dtype=np.uint8).tolist()
+    assert toks == [2, 5, 6, 7, 8, 4, 3, 9, 10, 4, 1] and mask == [0] * 7 + [1, 1, 1, 1]
+    assert m["metadata"]["tokenizer"]["vocab_size"] == 13
+    with pytest.raises(PreparationError, match="never guessed"):
+        prepare_dataset(spec("tok_plain", "b"))
+    with pytest.raises(PreparationError, match="no chat template"):
+        prepare_dataset(spec("tok_none", "c"))
+    # the template given in the spec replaces the tokenizer's own
+    prepare_dataset(spec("tok_none", "d", tokenizer={"chat_template": marked}))
+    assert np.fromfile(tmp_path / "d" / "loss_mask.u8", dtype=np.uint8).tolist() == mask
+    # prompt / completion as message lists
+    _jsonl(tmp_path / "pc.jsonl", [{"prompt": [{"role": "user", "content": "explain"}],
+                                    "completion": [{"role": "assistant", "content": "because"}]}])
+    prepare_dataset(PreparationSpec.from_mapping({
+        "source": {"type": "jsonl", "path": str(tmp_path / "pc.jsonl")}, "records": {"type": "prompt_completion"},
+        "tokenizer": {"model": str(tmp_path / "tok_plain")}, "supervision": {"policy": "completion_only"},
+        "output": {"path": str(tmp_path / "e")}}))
+    assert np.fromfile(tmp_path / "e" / "tokens.i32", dtype="<i4").tolist() == [2, 11, 4, 3, 12, 4]
+    assert np.fromfile(tmp_path / "e" / "loss_mask.u8", dtype=np.uint8).tolist() == [0, 0, 0, 0, 1, 1]
