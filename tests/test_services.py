@@ -457,3 +457,100 @@ def test_partial_rotary_is_a_permutation_of_head_dimensions(tmp_path):
     with safe_open(str(tmp_path / "hf" / "model.safetensors"), "pt") as f:
         on_disk = f.get_tensor("model.layers.0.self_attn.q_norm.weight")
     assert torch.equal(on_disk[perm], a.layers[0].q_norm.detach())
+
+
+def test_training_starts_from_a_local_pretrained_checkpoint(tmp_path):
+    """`model.id` naming a local checkpoint directory gives the architecture AND the starting weights; model.random_init
+    keeps the architecture only; a mixture-of-experts checkpoint round-trips through the same loader."""
+    import dataclasses
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.models.config import PRESETS
+    from turbo_dllm_b200.models.dense import BlockDiffusionTransformer
+    from turbo_dllm_b200.models.hf_loader import export_hf_checkpoint
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    cfg = dataclasses.replace(PRESETS["synthetic:tiny-qwen3"], num_layers=2)
+    a = BlockDiffusionTransformer(cfg, dtype=torch.float32, seed=5, init_std=0.05)
+    hf = str(tmp_path / "hf")
+    export_hf_checkpoint(a, hf)
+    base = {"model": {"id": hf, "seq_len": 64, "dtype": "fp32"},
+            "objective": {"name": "standard_block_diffusion", "block_size": 16},
+            "training": {"batch_size": 1, "steps": 1}, "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}
+    s = TrainingSession(RunSpec.from_mapping(base).validate(), device="cpu")
+    assert s.pretrained == hf and s.cfg.num_layers == 2 and s.cfg.hidden_size == cfg.hidden_size
+    assert torch.equal(s.model.flat.data, a.flat.data)
+    s.step()
+    assert not torch.equal(s.model.flat.data, a.flat.data)
+    r = TrainingSession(RunSpec.from_mapping({**base, "model": {**base["model"], "random_init": True, "max_layers": 1}}).validate(),
+                        device="cpu")
+    assert r.pretrained is None and r.cfg.num_layers == 1 and not torch.equal(r.model.flat.data[:100], a.flat.data[:100])
+    with pytest.raises(ValueError, match="local checkpoint"):
+        TrainingSession(RunSpec.from_mapping({**base, "model": {**base["model"], "id": str(tmp_path / "nowhere")}}).validate(),
+                        device="cpu")
+    # mixture of experts with the dense branch: export -> a session that starts from it
+    from turbo_dllm_b200.models.export import export_moe_checkpoint
+
+    moe = {**base, "model": {"id": "synthetic:tiny-moe", "seq_len": 64, "dtype": "fp32", "num_layers": 2,
+                             "moe_shared_intermediate_size": 64}}
+    m1 = TrainingSession(RunSpec.from_mapping(moe).validate(), device="cpu")
+    m1.step()
+    out = str(tmp_path / "moe")
+    export_moe_checkpoint(m1.model, out)
+    m2 = TrainingSession(RunSpec.from_mapping({**moe, "model": {"id": out, "seq_len": 64, "dtype": "fp32"}}).validate(), device="cpu")
+    assert m2.cfg.is_moe and m2.cfg.moe_shared_intermediate_size == 64
+    assert torch.equal(m2.model.flat.data, m1.model.flat.data) and torch.equal(m2.model.flat_experts.data, m1.model.flat_experts.data)
+
+
+def _tp_checkpoint_round_trip(rank, world, hf_dense, hf_hybrid, out_dir):
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.models.dense import BlockDiffusionTransformer
+    from turbo_dllm_b200.models.hf_loader import export_hf_checkpoint, load_hf_config, load_hf_weights
+    from turbo_dllm_b200.models.hybrid import HybridBlockDiffusionTransformer
+    from turbo_dllm_b200.parallel.tensor_parallel import TPContext
+
+    torch.set_num_threads(2)
+    tp = TPContext(dist.group.WORLD)
+    same = {}
+    for kind, cls, src in (("dense", BlockDiffusionTransformer, hf_dense), ("hybrid", HybridBlockDiffusionTransformer, hf_hybrid)):
+        cfg = load_hf_config(src)
+        # the model this rank would have built from the single-rank weights: same seed -> shards of the same tensors
+        model = cls(cfg, dtype=torch.float32, seed=99, tp=tp)
+        load_hf_weights(model, src)
+        export_hf_checkpoint(model, f"{out_dir}/{kind}")
+        same[kind] = float(model.flat.data.double().sum())
+    return same
+
+
+def test_tensor_parallel_ranks_load_their_shards_and_export_the_whole(tmp_path):
+    """Two tensor-parallel ranks read their slices of a checkpoint (dense and hybrid family); gathering them back
+    writes a file identical, tensor by tensor, to the one they were read from."""
+    import dataclasses
+
+    from safetensors import safe_open
+
+    from tests._harness import run_ranks
+    from turbo_dllm_b200.models.config import PRESETS
+    from turbo_dllm_b200.models.dense import BlockDiffusionTransformer
+    from turbo_dllm_b200.models.hf_loader import export_hf_checkpoint
+    from turbo_dllm_b200.models.hybrid import HybridBlockDiffusionTransformer
+
+    dense = BlockDiffusionTransformer(dataclasses.replace(PRESETS["synthetic:tiny-qwen3"], num_layers=2), dtype=torch.float32,
+                                      seed=5, init_std=0.05)
+    hybrid = HybridBlockDiffusionTransformer(PRESETS["synthetic:tiny-qwen3_8"], dtype=torch.float32, seed=7, init_std=0.05)
+    with torch.no_grad():
+        for m in (dense, hybrid):
+            for p in m.flat.params.values():
+                if not p.decay:
+                    p.add_(torch.randn_like(p) * 0.1)       # norms, biases, decay rates: distinctive values
+    export_hf_checkpoint(dense, str(tmp_path / "dense"))
+    export_hf_checkpoint(hybrid, str(tmp_path / "hybrid"))
+    run_ranks(_tp_checkpoint_round_trip, 2, args=(str(tmp_path / "dense"), str(tmp_path / "hybrid"), str(tmp_path / "out")),
+              deadline_s=240)
+    for kind in ("dense", "hybrid"):
+        with safe_open(str(tmp_path / kind / "model.safetensors"), framework="pt") as a, \
+                safe_open(str(tmp_path / "out" / kind / "model.safetensors"), framework="pt") as b:
+            assert set(a.keys()) == set(b.keys())
+            for k in a.keys():
+                assert torch.equal(a.get_tensor(k), b.get_tensor(k)), (kind, k)

@@ -163,10 +163,17 @@ def model_config_from_run_spec(spec) -> ModelConfig:
     m = spec.model
     base = PRESETS.get(m.id)
     if base is None:
+        from .hf_loader import load_hf_config, pretrained_directory
+
+        if pretrained_directory(m.id) is not None:
+            # a local Hugging Face checkpoint: its config.json gives the architecture (and, unless
+            # model.random_init is set, the training session loads its weights)
+            base = load_hf_config(m.id)
+    if base is None:
         if not m.random_init:
             raise ValueError(
-                f"model.id {m.id!r} is not a built-in preset ({', '.join(PRESETS)}); loading Hugging Face "
-                "checkpoints needs `turbo_dllm_b200.models.hf_loader` and a local path, or set "
+                f"model.id {m.id!r} is neither a built-in preset ({', '.join(PRESETS)}) nor a local checkpoint "
+                "directory with a config.json; give a local path (nothing is downloaded), or set "
                 "model.random_init=true with explicit shape fields")
         need = ("vocab_size", "hidden_size", "num_layers", "num_attention_heads")
         missing = [n for n in need if getattr(m, n) is None]

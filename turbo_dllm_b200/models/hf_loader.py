@@ -28,6 +28,13 @@ import torch
 from .config import ModelConfig
 
 
+def pretrained_directory(model_id: str | None) -> str | None:
+    """`model_id` when it names a local checkpoint directory (one with a config.json), else None."""
+    if model_id and os.path.isdir(model_id) and os.path.exists(os.path.join(model_id, "config.json")):
+        return model_id
+    return None
+
+
 def load_hf_config(path: str, max_layers: int | None = None) -> ModelConfig:
     cfg_path = os.path.join(path, "config.json")
     if not os.path.exists(cfg_path):
@@ -52,7 +59,13 @@ def load_hf_config(path: str, max_layers: int | None = None) -> ModelConfig:
         sliding = dict(sliding_window=int(c["sliding_window"]),
                        sliding_window_pattern=int(c.get("sliding_window_pattern", 0) or 0),
                        layer_types=tuple(types[:layers]) if types and not hybrid else None)
-    return ModelConfig(**hybrid, **sliding,
+    moe = {}
+    if c.get("num_experts"):
+        moe = dict(family="diffusion_gemma", num_experts=int(c["num_experts"]),
+                   num_experts_per_token=int(c.get("num_experts_per_tok", c.get("num_experts_per_token", 1))),
+                   moe_intermediate_size=int(c["moe_intermediate_size"]),
+                   moe_shared_intermediate_size=int(c.get("shared_expert_intermediate_size", 0) or 0))
+    return ModelConfig(**hybrid, **sliding, **moe,
         vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], num_layers=layers, num_attention_heads=heads,
         num_key_value_heads=c.get("num_key_value_heads", heads), head_dim=c.get("head_dim", c["hidden_size"] // heads),
         intermediate_size=c["intermediate_size"], rope_theta=float(c.get("rope_theta", 1e6)),
@@ -120,7 +133,9 @@ def _open_weights(path: str) -> dict:
 
 @torch.no_grad()
 def load_hf_weights(model, path: str) -> None:
-    """Fills `model` (a dense BlockDiffusionTransformer, possibly tensor-parallel) from `path`."""
+    """Fills `model` (dense, hybrid or mixture-of-experts decoder; tensor- or expert-parallel) from the Hugging Face
+    checkpoint directory `path`. A tensor-parallel rank reads only its own rows / columns of every sharded matrix from
+    the files (the role of a per-parameter tensor-parallel plan: dllm_parallel/core/parallel/hf_tensor_parallel.py:22-226)."""
     table = _open_weights(path)
     cfg, tp = model.cfg, model.tp
 
@@ -130,35 +145,61 @@ def load_hf_weights(model, path: str) -> None:
         return table[name].get_tensor(name)
 
     def put(param, tensor):
+        if tuple(param.shape) != tuple(tensor.shape):
+            raise ValueError(f"checkpoint tensor of shape {tuple(tensor.shape)} does not fit a parameter of shape "
+                             f"{tuple(param.shape)}")
         param.copy_(tensor.to(param.device, param.dtype))
 
-    def shard(t, dim):
-        return tp.shard(t, dim) if tp is not None else t
+    def part(name, dim):
+        """This rank's slice of a matrix that tensor parallelism divides along `dim` (read from the file as a slice)."""
+        if tp is None:
+            return get(name)
+        if name not in table:
+            raise KeyError(f"checkpoint lacks {name}")
+        sl = table[name].get_slice(name)
+        n = sl.get_shape()[dim] // tp.size
+        lo = tp.rank * n
+        return sl[lo:lo + n] if dim == 0 else sl[:, lo:lo + n]
 
-    put(model.embed, shard(get("model.embed_tokens.weight"), 0))
+    put(model.embed, part("model.embed_tokens.weight", 0))
     put(model.final_norm, get("model.norm.weight"))
     if not cfg.tie_word_embeddings:
         name = "lm_head.weight" if "lm_head.weight" in table else "model.embed_tokens.weight"
-        put(model.lm_head, shard(get(name), 0))
+        put(model.lm_head, part(name, 0))
     for i, layer in enumerate(model.layers):
         p = f"model.layers.{i}."
         if cfg.is_hybrid:
-            if tp is not None:
-                raise ValueError("hybrid checkpoints load on one tensor-parallel rank")
-            _load_hybrid_layer(layer, cfg, p, get, put, table)
+            _load_hybrid_layer(layer, cfg, p, get, put, table, tp, part)
             continue
-        q, k, v = (get(p + f"self_attn.{n}_proj.weight") for n in "qkv")
-        put(layer.w_qkv, torch.cat([shard(q, 0), shard(k, 0), shard(v, 0)], dim=0))
-        put(layer.w_o, shard(get(p + "self_attn.o_proj.weight"), 1))
+        put(layer.w_qkv, torch.cat([part(p + f"self_attn.{n}_proj.weight", 0) for n in "qkv"], dim=0))
+        put(layer.w_o, part(p + "self_attn.o_proj.weight", 1))
         put(layer.input_norm, get(p + "input_layernorm.weight"))
         put(layer.post_norm, get(p + "post_attention_layernorm.weight"))
         if layer.q_norm is not None:
             put(layer.q_norm, get(p + "self_attn.q_norm.weight"))
             put(layer.k_norm, get(p + "self_attn.k_norm.weight"))
-        put(layer.w_gate_up, interleave_gate_up(shard(get(p + "mlp.gate_proj.weight"), 0),
-                                                shard(get(p + "mlp.up_proj.weight"), 0)))
-        put(layer.w_down, shard(get(p + "mlp.down_proj.weight"), 1))
+        if getattr(layer, "experts", None) is not None:
+            _load_expert_layer(layer, p, get, put)
+            continue
+        put(layer.w_gate_up, interleave_gate_up(part(p + "mlp.gate_proj.weight", 0), part(p + "mlp.up_proj.weight", 0)))
+        put(layer.w_down, part(p + "mlp.down_proj.weight", 1))
     _apply_partial_rotary_order(model, inverse=False)
+
+
+def _load_expert_layer(layer, p, get, put) -> None:
+    """Router, this rank's experts (global experts [ep_rank * E_local, (ep_rank + 1) * E_local)) and the dense
+    feed-forward beside them, in the naming `models/export.py` writes."""
+    bank = layer.experts
+    put(bank.router, get(p + "mlp.router.weight"))
+    first = bank.ep_rank * bank.e_local
+    for e in range(bank.e_local):
+        q = p + f"mlp.experts.{first + e}."
+        put(bank.w_gu[e], interleave_gate_up(get(q + "gate_proj.weight"), get(q + "up_proj.weight")))
+        put(bank.w_down[e], get(q + "down_proj.weight"))
+    if layer.w_gate_up is not None:
+        s = p + "mlp.shared_expert."
+        put(layer.w_gate_up, interleave_gate_up(get(s + "gate_proj.weight"), get(s + "up_proj.weight")))
+        put(layer.w_down, get(s + "down_proj.weight"))
 
 
 def _apply_partial_rotary_order(model, inverse: bool) -> None:
@@ -177,33 +218,49 @@ def _apply_partial_rotary_order(model, inverse: bool) -> None:
             _permute_qk_head_dims(layer, cfg, perm)
 
 
-def _load_hybrid_layer(layer, cfg, p, get, put, table) -> None:
+def _load_hybrid_layer(layer, cfg, p, get, put, table, tp=None, part=None) -> None:
+    """One layer of the hybrid family. Under tensor parallelism the rank takes its key / value heads of the
+    linear-attention projections (`models/hybrid.py::fused_projection_rows`), its query / key / value heads and
+    gate rows of the softmax layers, and its slice of the feed-forward."""
+    part = part or (lambda name, dim: get(name))
+    shard = (lambda t, dim: tp.shard(t, dim)) if tp is not None else (lambda t, dim: t)
     put(layer.input_norm, get(p + "input_layernorm.weight"))
     put(layer.post_norm, get(p + "post_attention_layernorm.weight"))
-    put(layer.w_gate_up, interleave_gate_up(get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")))
-    put(layer.w_down, get(p + "mlp.down_proj.weight"))
+    put(layer.w_gate_up, interleave_gate_up(part(p + "mlp.gate_proj.weight", 0), part(p + "mlp.up_proj.weight", 0)))
+    put(layer.w_down, part(p + "mlp.down_proj.weight", 1))
     if cfg.layer_kind(layer.idx) == "linear_attention":
         m = p + "linear_attn."
         rows = torch.cat([get(m + f"in_proj_{n}.weight") for n in ("qkv", "z", "b", "a")], dim=0)
-        w_in = torch.zeros(layer.w_in.shape, dtype=rows.dtype)
+        conv_w = get(m + "conv1d.weight").squeeze(1)
+        conv_b = get(m + "conv1d.bias") if m + "conv1d.bias" in table else None
+        a_log, dt_bias = get(m + "A_log"), get(m + "dt_bias")
+        if tp is not None:
+            from .hybrid import fused_projection_rows
+
+            take, channels = fused_projection_rows(cfg, tp.rank, tp.size)
+            rows, conv_w = rows[take], conv_w[channels]
+            conv_b = conv_b[channels] if conv_b is not None else None
+            a_log, dt_bias = shard(a_log, 0), shard(dt_bias, 0)
+        w_in = torch.zeros(layer.w_in.shape, dtype=rows.dtype)     # rows past q | k | v | z | b | a pad the GEMM width
         w_in[: rows.shape[0]] = rows
         put(layer.w_in, w_in)
-        put(layer.conv_w, get(m + "conv1d.weight").squeeze(1))
-        if m + "conv1d.bias" in table:
-            put(layer.conv_b, get(m + "conv1d.bias"))
+        put(layer.conv_w, conv_w)
+        if conv_b is not None:
+            put(layer.conv_b, conv_b)
         else:
             layer.conv_b.zero_()
-        put(layer.A_log, get(m + "A_log"))
-        put(layer.dt_bias, get(m + "dt_bias"))
+        put(layer.A_log, a_log)
+        put(layer.dt_bias, dt_bias)
         put(layer.gdn_norm, get(m + "norm.weight"))
-        put(layer.w_out, get(m + "out_proj.weight"))
+        put(layer.w_out, part(m + "out_proj.weight", 1))
         return
     a = p + "self_attn."
     D = cfg.head_dim
     qg = get(a + "q_proj.weight").view(cfg.num_attention_heads, 2, D, cfg.hidden_size)
-    put(layer.w_qkv, torch.cat([qg[:, 0].reshape(cfg.q_dim, -1), get(a + "k_proj.weight"), get(a + "v_proj.weight")]))
-    put(layer.w_attn_gate, qg[:, 1].reshape(cfg.q_dim, -1))
-    put(layer.w_o, get(a + "o_proj.weight"))
+    q, gate = shard(qg[:, 0], 0), shard(qg[:, 1], 0)           # query and gate rows are interleaved per head in the file
+    put(layer.w_qkv, torch.cat([q.reshape(-1, cfg.hidden_size), part(a + "k_proj.weight", 0), part(a + "v_proj.weight", 0)]))
+    put(layer.w_attn_gate, gate.reshape(-1, cfg.hidden_size))
+    put(layer.w_o, part(a + "o_proj.weight", 1))
     if layer.q_norm is not None:
         put(layer.q_norm, get(a + "q_norm.weight"))
         put(layer.k_norm, get(a + "k_norm.weight"))
@@ -259,17 +316,82 @@ def _permute_qk_head_dims(layer, cfg: ModelConfig, perm: torch.Tensor) -> None:
 
 
 @torch.no_grad()
-def export_hf_checkpoint(model, path: str, merge_adapters: bool = True) -> str:
-    """Writes config.json + model.safetensors in Hugging Face naming (single tensor-parallel rank)."""
-    from safetensors.torch import save_file
+def gather_tensor_parallel_model(model):
+    """A stand-in for `model` whose layers hold FULL tensors assembled from the tensor-parallel ranks' shards (on the
+    CPU, on every rank): what the checkpoint writers read. Column-parallel matrices are joined along rows, row-parallel
+    ones along columns, the fused q | k | v projection section by section, the hybrid family's fused input projection
+    and convolution by the head segments each rank owns."""
+    import torch.distributed as dist
+    from types import SimpleNamespace
 
-    if model.tp is not None:
-        raise ValueError("export from a tensor-parallel model: gather the shards first")
+    tp, cfg = model.tp, model.cfg
+    n = tp.size
+
+    def every(t):
+        t = t.detach().contiguous()
+        parts = [torch.empty_like(t) for _ in range(n)]
+        dist.all_gather(parts, t, group=tp.group)
+        return [x.cpu() for x in parts]
+
+    def cat(t, dim):
+        return torch.cat(every(t), dim=dim)
+
+    def qkv(w, q_rows, kv_rows):
+        parts = every(w)
+        return torch.cat([torch.cat([x[:q_rows] for x in parts]), torch.cat([x[q_rows:q_rows + kv_rows] for x in parts]),
+                          torch.cat([x[q_rows + kv_rows:] for x in parts])])
+
+    lc = model.lcfg
+    out = SimpleNamespace(cfg=cfg, tp=None, embed=cat(model.embed, 0), final_norm=model.final_norm.detach().cpu(), layers=[])
+    out.lm_head = out.embed if cfg.tie_word_embeddings else cat(model.lm_head, 0)
+    for layer in model.layers:
+        full = SimpleNamespace(idx=layer.idx, input_norm=layer.input_norm.detach().cpu(),
+                               post_norm=layer.post_norm.detach().cpu(), w_gate_up=cat(layer.w_gate_up, 0),
+                               w_down=cat(layer.w_down, 1), q_norm=None, k_norm=None)
+        if cfg.is_hybrid and cfg.layer_kind(layer.idx) == "linear_attention":
+            from .hybrid import fused_projection_rows
+
+            w_in = torch.zeros((cfg.linear_in_dim, layer.w_in.shape[1]), dtype=layer.w_in.dtype)
+            conv_w = torch.zeros((cfg.linear_conv_channels, layer.conv_w.shape[1]), dtype=layer.conv_w.dtype)
+            conv_b = torch.zeros((cfg.linear_conv_channels,), dtype=layer.conv_b.dtype)
+            for r, (wi, cw, cb) in enumerate(zip(every(layer.w_in), every(layer.conv_w), every(layer.conv_b))):
+                rows, channels = fused_projection_rows(cfg, r, n)
+                w_in[rows] = wi[: rows.numel()]
+                conv_w[channels], conv_b[channels] = cw, cb
+            full.w_in, full.conv_w, full.conv_b = w_in, conv_w, conv_b
+            full.A_log, full.dt_bias = cat(layer.A_log, 0), cat(layer.dt_bias, 0)
+            full.gdn_norm, full.w_out = layer.gdn_norm.detach().cpu(), cat(layer.w_out, 1)
+        else:
+            full.w_qkv = qkv(layer.w_qkv, lc.q_dim, lc.kv_dim)
+            full.w_o = cat(layer.w_o, 1)
+            if layer.q_norm is not None:
+                full.q_norm, full.k_norm = layer.q_norm.detach().cpu(), layer.k_norm.detach().cpu()
+            if getattr(layer, "w_attn_gate", None) is not None:
+                full.w_attn_gate = cat(layer.w_attn_gate, 0)
+        out.layers.append(full)
+    return out
+
+
+@torch.no_grad()
+def export_hf_checkpoint(model, path: str, merge_adapters: bool = True) -> str:
+    """Writes config.json + model.safetensors in Hugging Face naming. A tensor-parallel model is assembled from its
+    ranks' shards first (a collective over the tensor-parallel group: every rank calls this); rank 0 of the group
+    writes the files."""
     if merge_adapters and getattr(model, "lora", None) is not None:
         from ..adapters.lora import merge_lora
 
         merge_lora(model)
     cfg = model.cfg
+    if model.tp is not None:
+        import torch.distributed as dist
+
+        full = gather_tensor_parallel_model(model)
+        if model.tp.rank == 0:
+            os.makedirs(path, exist_ok=True)
+            _apply_partial_rotary_order(full, inverse=True)
+            _write_hf_checkpoint(full, cfg, path)
+        dist.barrier(group=model.tp.group)
+        return path
     os.makedirs(path, exist_ok=True)
     _apply_partial_rotary_order(model, inverse=True)        # the file keeps the checkpoint's head-dimension order
     try:

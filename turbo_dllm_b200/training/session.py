@@ -81,6 +81,12 @@ class TrainingSession:
             spec=spec, cfg=self.cfg, device=self.device, dtype=self.dtype, runtime=runtime, seed=seed,
             activation_offload=self._want_activation_offload()))
         self.memory_report("model built")
+        from ..models.hf_loader import load_hf_weights, pretrained_directory
+
+        self.pretrained = None if spec.model.random_init else pretrained_directory(spec.model.id)
+        if self.pretrained is not None:
+            # model.id names a local checkpoint: start from its weights (every rank reads its own shard)
+            load_hf_weights(self.model, self.pretrained)
         self.lora = None
         self.sharded = None      # parameter sharding (optimizer.backend: fsdp)
         if spec.adapter.type == "lora":
