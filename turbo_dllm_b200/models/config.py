@@ -165,10 +165,11 @@ def model_config_from_run_spec(spec) -> ModelConfig:
     if base is None:
         from .hf_loader import load_hf_config, pretrained_directory
 
-        if pretrained_directory(m.id) is not None:
+        local = pretrained_directory(m.id)
+        if local is not None:
             # a local Hugging Face checkpoint: its config.json gives the architecture (and, unless
             # model.random_init is set, the training session loads its weights)
-            base = load_hf_config(m.id)
+            base = load_hf_config(local)
     if base is None:
         if not m.random_init:
             raise ValueError(

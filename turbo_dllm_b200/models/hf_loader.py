@@ -29,9 +29,20 @@ from .config import ModelConfig
 
 
 def pretrained_directory(model_id: str | None) -> str | None:
-    """`model_id` when it names a local checkpoint directory (one with a config.json), else None."""
+    """The local checkpoint directory `model_id` names (one with a config.json): the path itself, or the cached
+    snapshot of a hub id; None otherwise. Nothing is downloaded."""
     if model_id and os.path.isdir(model_id) and os.path.exists(os.path.join(model_id, "config.json")):
         return model_id
+    if model_id and model_id.count("/") == 1 and not model_id.startswith(("synthetic:", ".", "/")):
+        # a hub id (`organization/model`): only a snapshot that is already in the local Hugging Face cache is used
+        try:
+            from huggingface_hub import snapshot_download
+
+            path = snapshot_download(model_id, local_files_only=True)
+        except Exception:
+            return None
+        if os.path.exists(os.path.join(path, "config.json")):
+            return path
     return None
 
 
