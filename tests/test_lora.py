@@ -153,3 +153,51 @@ def test_moe_export_merges_adapters_by_a_checked_plan(tmp_path):
     st2.flat.params["layers.0.w_o.lora_B"] = torch.nn.Parameter(good.detach()[:-1].clone())
     with pytest.raises(ValueError, match="does not fit"):
         lora_merge_plan(model2)
+
+
+def test_token_mask_limits_the_adapters_to_selected_rows():
+    """Inside `lora_token_mask` the adapters change only the selected rows and take gradients only from them, also when
+    a checkpointed layer is recomputed in the backward pass; `False` switches the adapters off."""
+    from turbo_dllm_b200.adapters.lora import current_lora_token_mask, lora_token_mask
+
+    cfg = PRESETS["synthetic:tiny-qwen3"]
+    model = BlockDiffusionTransformer(cfg, dtype=torch.float32, activation_checkpointing=True, seed=2, init_std=0.05)
+    base = BlockDiffusionTransformer(cfg, dtype=torch.float32, activation_checkpointing=True, seed=2, init_std=0.05)
+    st = apply_lora(model, rank=4, alpha=8.0, targets=("mlp",), seed=3)
+    with torch.no_grad():
+        for n, p in st.flat.params.items():
+            if n.endswith("lora_B"):
+                p.normal_(0, 0.05)
+    # one layer, so rows do not mix after the adapted feed-forward
+    model.layers = model.layers[:1]
+    base.layers = base.layers[:1]
+    layout = build_packed_layout(seq_len=64, block_size=16, batch=1, views=1)
+    tokens = torch.randint(0, cfg.vocab_size, (layout.rows,), generator=torch.Generator().manual_seed(4))
+    mask = torch.zeros(layout.rows, dtype=torch.bool)
+    mask[::3] = True
+    with torch.no_grad():
+        plain = _run(base, tokens, layout)
+        everywhere = _run(model, tokens, layout)
+        with lora_token_mask(mask):
+            assert current_lora_token_mask() is mask
+            some = _run(model, tokens, layout)
+        with lora_token_mask(False):
+            off = _run(model, tokens, layout)
+    assert current_lora_token_mask() is None
+    assert torch.allclose(off, plain, atol=1e-6) and not torch.allclose(everywhere, plain, atol=1e-4)
+    assert torch.allclose(some[~mask], plain[~mask], atol=1e-6) and torch.allclose(some[mask], everywhere[mask], atol=1e-6)
+    # gradients: only the selected rows reach the adapters (the replay in the checkpointed backward sees the mask)
+    def adapter_grad(m, weight_rows):
+        st.flat.zero_grad()
+        with lora_token_mask(m):
+            (_run(model, tokens, layout) * weight_rows[:, None]).sum().backward()
+        st.flat.collect_grads()
+        return st.flat.grad.clone()
+
+    ones = torch.ones(layout.rows)
+    g_masked = adapter_grad(mask, ones)
+    g_selected_rows_only = adapter_grad(None, mask.float())
+    assert g_masked.abs().sum() > 0
+    # the loss on unselected rows still reaches layer-0 adapters through attention in deeper layers; with one layer it
+    # cannot, so both gradients agree
+    assert torch.allclose(g_masked, g_selected_rows_only, atol=1e-5, rtol=1e-4)

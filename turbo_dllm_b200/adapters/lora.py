@@ -20,6 +20,9 @@ variant), :320-450 (grouped expert LoRA), :453-543 (apply_lora).
 """
 from __future__ import annotations
 
+import contextlib
+import contextvars
+
 import torch
 
 from ..models.dense import FlatParams
@@ -56,14 +59,43 @@ class LoRAState:
         return a, self.flat.params[f"layers.{layer_idx}.{name}.lora_B"]
 
 
+_TOKEN_MASK: contextvars.ContextVar = contextvars.ContextVar("turbo_dllm_b200_lora_token_mask", default=None)
+
+
+@contextlib.contextmanager
+def lora_token_mask(mask: "torch.Tensor | bool | None"):
+    """Inside the block the low-rank updates act only on the rows `mask` selects ([rows] bool; False: on no row;
+    None: on every row). Context-local, so the recomputation of a checkpointed layer sees the mask of the code that
+    replays it (dllm_parallel/core/adapters/lora.py:26-47)."""
+    if mask is not None and not isinstance(mask, (torch.Tensor, bool)):
+        raise TypeError("the LoRA token mask is a tensor, a bool or None")
+    token = _TOKEN_MASK.set(mask)
+    try:
+        yield
+    finally:
+        _TOKEN_MASK.reset(token)
+
+
+def current_lora_token_mask():
+    return _TOKEN_MASK.get()
+
+
 def lora_delta(x: torch.Tensor, a: torch.Tensor, b: torch.Tensor, scale: float, dropout: float = 0.0,
                token_mask: torch.Tensor | None = None) -> torch.Tensor:
+    if token_mask is None:
+        token_mask = current_lora_token_mask()
+    if token_mask is False:
+        return torch.zeros((x.shape[0], b.shape[0]), dtype=x.dtype, device=x.device)
+    if token_mask is True:
+        token_mask = None
     if dropout > 0 and torch.is_grad_enabled():
         x = torch.nn.functional.dropout(x, dropout)
-    d = linear(linear(x, a), b) * scale
+    low = linear(x, a)
     if token_mask is not None:
-        d = d * token_mask[:, None].to(d.dtype)
-    return d
+        if token_mask.numel() != x.shape[0]:
+            raise ValueError(f"the LoRA token mask has {token_mask.numel()} entries for {x.shape[0]} rows")
+        low = low * token_mask.reshape(-1, 1).to(low.dtype)     # unselected rows: no update, no adapter gradient
+    return linear(low, b) * scale
 
 
 def apply_lora(model, *, rank: int, alpha: float | None = None, dropout: float = 0.0,
