@@ -88,3 +88,62 @@ def test_capture_over_two_ranks_and_resume(tmp_path):
     assert [s["sha256"] for s in man3["shards"]] == [s["sha256"] for s in man2["shards"]]
     assert os.path.getmtime(os.path.join(tmp_path / "r", "shard_00000.pt")) == kept
     FeatureStore(str(tmp_path / "r"), verify=True)
+
+
+def test_reduced_draft_vocabulary(tmp_path, capsys):
+    """A drafter over a subset of the verifier's vocabulary: the maps are validated, the KL loss uses the head rows of
+    the subset (equal to the dense formula), hard-label CE skips tokens outside it, and the export carries the maps."""
+    import json
+
+    import numpy as np
+
+    from turbo_dllm_b200.cli.dflash import run_dflash
+    from turbo_dllm_b200.models.dflash import DraftVocabulary
+    from turbo_dllm_b200.models.export import export_dflash_drafter
+
+    V = 1024
+    ds = tmp_path / "ds"
+    ds.mkdir()
+    rng = np.random.default_rng(0)
+    np.concatenate([rng.integers(0, 64, 5000), rng.integers(0, V, 500)]).astype("<i4").tofile(ds / "tokens.i32")
+    path = str(tmp_path / "draft_vocab.safetensors")
+    assert run_dflash(["build-draft-vocab", "--dataset", str(ds), "--size", "128", "--verifier-vocab-size", str(V),
+                       "--output", path]) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["draft_vocab_size"] == 128 and rep["token_coverage"] > 0.9
+    dv = DraftVocabulary.load(path, V)
+    assert dv.size == 128 and set(range(64)) <= set(dv.selected.tolist())
+    assert torch.equal(dv.selected, torch.arange(128) + dv.d2t)
+    ids = torch.tensor([int(dv.selected[5]), int((~dv.t2d).nonzero()[0])])
+    assert dv.to_draft_ids(ids).tolist() == [5, -1]
+    with pytest.raises(ValueError, match="d2t"):
+        DraftVocabulary(dv.t2d, dv.d2t + 1, V)
+    with pytest.raises(ValueError, match="verifier"):
+        DraftVocabulary.load(path, V + 1)
+
+    def spec(loss, vocab):
+        s = _spec("online")
+        return s.with_overrides({"model": {"draft_vocab_path": vocab}, "objective": {"dflash_loss": loss}}).validate()
+
+    # KL over the subset == the dense formula on the selected head rows
+    full = TrainingSession(spec("speculators_kl", None), device="cpu")
+    sub = TrainingSession(spec("speculators_kl", path), device="cpu")
+    assert sub.task.head.shape[0] == 128 and torch.equal(sub.task.head, full.task.target.lm_head[dv.selected])
+    l_full, l_sub = float(full.step().loss_sum), float(sub.step().loss_sum)
+    assert l_sub > 0 and l_sub != pytest.approx(l_full, rel=1e-3)
+    # hard labels: a vocabulary that holds every id gives the full-vocabulary loss; the subset supervises fewer tokens
+    everything = str(tmp_path / "all.safetensors")
+    DraftVocabulary.from_ids(torch.arange(V), V).save(everything)
+    ce_full = float(TrainingSession(spec("paper_ce", None), device="cpu").step().loss_sum)
+    ce_all = float(TrainingSession(spec("paper_ce", everything), device="cpu").step().loss_sum)
+    ce_sub = float(TrainingSession(spec("paper_ce", path), device="cpu").step().loss_sum)
+    assert ce_all == pytest.approx(ce_full, rel=1e-5) and 0 <= ce_sub < ce_full
+    out = str(tmp_path / "export")
+    export_dflash_drafter(sub.model, sub.spec, out)
+    from safetensors import safe_open
+
+    with safe_open(out + "/model.safetensors", framework="pt") as f:
+        assert torch.equal(f.get_tensor("t2d"), dv.t2d) and torch.equal(f.get_tensor("d2t"), dv.d2t)
+    assert json.load(open(out + "/dflash_config.json"))["draft_vocab_size"] == 128
+    with pytest.raises(Exception, match="draft_vocab_path"):
+        _spec("online").with_overrides({"model": {"draft_vocab_path": path, "dflash2_selector_rank": 4}}).validate()

@@ -1,4 +1,4 @@
-"""`dllm dflash …`: prepare-features, export, validate-export, validate-vllm, serve-sglang, serve-vllm,
+"""`dllm dflash …`: prepare-features, build-draft-vocab, export, validate-export, validate-vllm, serve-sglang, serve-vllm,
 verify-sglang, verify-vllm (cf. dllm_parallel/cli/dflash.py:13-110)."""
 from __future__ import annotations
 
@@ -20,6 +20,12 @@ def run_dflash(argv) -> int:
     p.add_argument("--output", required=True)
     p.add_argument("--batches", type=int, default=8)
     p.add_argument("--resume", action="store_true", help="keep records that are already written and verified")
+    p = sub.add_parser("build-draft-vocab", help="t2d / d2t maps of the most frequent tokens of a prepared dataset")
+    p.add_argument("--dataset", required=True, help="prepared artifact directory (tokens.i32)")
+    p.add_argument("--size", type=int, required=True, help="draft vocabulary size")
+    p.add_argument("--verifier-vocab-size", type=int, required=True)
+    p.add_argument("--keep-ids", type=int, nargs="*", default=[], help="ids kept whatever their frequency (eos, ...)")
+    p.add_argument("--output", required=True)
     p = sub.add_parser("export")
     p.add_argument("--config", required=True)
     p.add_argument("--checkpoint", required=True)
@@ -76,6 +82,28 @@ def run_dflash(argv) -> int:
                                    barrier=barrier, resume=a.resume)
             if rank == 0:
                 print(json.dumps(man))
+            return 0
+        if a.cmd == "build-draft-vocab":
+            import os
+
+            import numpy as np
+            import torch
+
+            from ..models.dflash import DraftVocabulary
+
+            toks = np.memmap(os.path.join(a.dataset, "tokens.i32"), dtype="<i4", mode="r")
+            counts = np.bincount(toks, minlength=a.verifier_vocab_size)
+            if counts.size > a.verifier_vocab_size:
+                raise ValueError(f"the dataset holds token id {counts.size - 1}, outside a vocabulary of {a.verifier_vocab_size}")
+            if not 0 < a.size <= a.verifier_vocab_size:
+                raise ValueError("--size must be in (0, verifier vocabulary size]")
+            counts = counts.astype(np.int64)
+            counts[list(a.keep_ids)] = np.iinfo(np.int64).max
+            order = np.argsort(-counts, kind="stable")[: a.size]      # ties: the lower id first
+            dv = DraftVocabulary.from_ids(torch.from_numpy(order.copy()), a.verifier_vocab_size)
+            dv.save(a.output)
+            covered = float(np.minimum(counts[order], toks.size).sum() / max(toks.size, 1)) if not a.keep_ids else None
+            print(json.dumps({"output": a.output, "draft_vocab_size": dv.size, "token_coverage": covered}))
             return 0
         if a.cmd == "export":
             from ..checkpoint import load_training_checkpoint

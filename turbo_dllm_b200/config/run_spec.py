@@ -194,8 +194,7 @@ class RunSpec:
                 ("optimizer", "fsdp_sharding_strategy", "full_shard", "parameter sharding is always full sharding over the data-parallel group"),
                 ("optimizer", "fsdp_use_orig_params", True, "parameters are views of flat buffers"),
                 ("kernel", "ring_attention_key_chunk_size", 0, "key tiles are streamed by the attention kernel itself"),
-                ("kernel", "cp_bp_attention_policy", "production", "one attention policy is built"),
-                ("model", "draft_vocab_path", None, "drafters use the verifier's vocabulary")):
+                ("kernel", "cp_bp_attention_policy", "production", "one attention policy is built")):
             v = getattr(getattr(self, section), name)
             need(v == default, f"{section}.{name}={v!r} has no effect here ({why}); leave it at {default!r}")
         if tr.activation_checkpointing_scope == "mlp":
@@ -214,6 +213,11 @@ class RunSpec:
             need(abs(float(o.bp_loss_scale) - float(bp if bp > 1 else 1)) < 1e-6,
                  f"objective.bp_loss_scale={o.bp_loss_scale} differs from the block-parallel degree {bp if bp > 1 else 1}: "
                  "gradients are summed over ranks and divided by the global token count, so no other scale applies")
+        if m.draft_vocab_path:
+            need(o.name == "dflash_distillation" and o.dflash_loss in ("speculators_kl", "paper_ce")
+                 and not (m.dflash2_conv_kernel_size or m.dflash2_selector_rank),
+                 "model.draft_vocab_path (a drafter over a subset of the verifier's vocabulary) is built for the DFlash "
+                 "drafter with objective.dflash_loss speculators_kl or paper_ce")
         if o.name == "dflash_distillation":
             need(cp == 1 or cp == bp, "dflash_distillation divides anchors and context rows over the same ranks: "
                                       "context_parallel_size must be 1 or equal block_parallel_size")

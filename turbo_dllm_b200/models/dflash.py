@@ -88,6 +88,63 @@ class FrozenTarget:
         return TargetFeatures(torch.cat(taps, dim=-1), final)
 
 
+class DraftVocabulary:
+    """A drafter that predicts a subset of the verifier's vocabulary (the `t2d` / `d2t` maps of speculative-decoding
+    servers): `t2d` [V] bool marks the verifier ids the drafter can emit, draft id j stands for verifier id
+    j + d2t[j] (the j-th marked id). The frozen head the losses use is the verifier head's marked rows.
+    Counterpart of dllm_parallel/core/models/backbones/dflash/model.py:631-692 and
+    dllm_parallel/core/models/backbones/dflash/executor.py:1022-1062."""
+
+    def __init__(self, t2d: torch.Tensor, d2t: torch.Tensor, verifier_vocab_size: int):
+        t2d = t2d.to(torch.bool).reshape(-1).cpu()
+        d2t = d2t.to(torch.int64).reshape(-1).cpu()
+        if t2d.numel() != verifier_vocab_size:
+            raise ValueError(f"t2d has {t2d.numel()} entries, the verifier's vocabulary {verifier_vocab_size}")
+        self.selected = torch.nonzero(t2d).flatten()
+        if self.selected.numel() != d2t.numel() or self.selected.numel() == 0:
+            raise ValueError(f"t2d marks {self.selected.numel()} ids, d2t has {d2t.numel()} entries")
+        if not torch.equal(d2t, self.selected - torch.arange(d2t.numel())):
+            raise ValueError("d2t does not map draft ids to the marked verifier ids (draft id j -> j + d2t[j])")
+        self.t2d, self.d2t = t2d, d2t
+        self.size, self.verifier_vocab_size = int(d2t.numel()), int(verifier_vocab_size)
+
+    @classmethod
+    def from_ids(cls, ids, verifier_vocab_size: int) -> "DraftVocabulary":
+        """From the verifier ids to keep (any order, duplicates ignored)."""
+        t2d = torch.zeros(verifier_vocab_size, dtype=torch.bool)
+        t2d[torch.as_tensor(ids, dtype=torch.int64)] = True
+        sel = torch.nonzero(t2d).flatten()
+        return cls(t2d, sel - torch.arange(sel.numel()), verifier_vocab_size)
+
+    @classmethod
+    def load(cls, path: str, verifier_vocab_size: int) -> "DraftVocabulary":
+        from safetensors.torch import load_file
+
+        vals = load_file(path, device="cpu")
+        if "t2d" not in vals or "d2t" not in vals:
+            raise ValueError(f"{path} must hold the tensors t2d and d2t")
+        return cls(vals["t2d"], vals["d2t"], verifier_vocab_size)
+
+    def save(self, path: str) -> str:
+        from safetensors.torch import save_file
+
+        save_file({"t2d": self.t2d.contiguous(), "d2t": self.d2t.contiguous()}, path)
+        return path
+
+    def head_rows(self, head: torch.Tensor) -> torch.Tensor:
+        """The marked rows of the verifier's output head, as one contiguous frozen matrix [size, H]."""
+        return head.detach().index_select(0, self.selected.to(head.device)).contiguous()
+
+    def to_draft_ids(self, verifier_ids: torch.Tensor) -> torch.Tensor:
+        """Draft id of every verifier id, -1 where the drafter cannot emit it."""
+        table = getattr(self, "_table", None)
+        if table is None or table.device != verifier_ids.device:
+            table = torch.full((self.verifier_vocab_size,), -1, dtype=torch.int64)
+            table[self.selected] = torch.arange(self.size)
+            self._table = table = table.to(verifier_ids.device)
+        return table[verifier_ids]
+
+
 def _draft_layer_specs(cfg: ModelConfig, i: int):
     h, p = cfg.hidden_size, f"layers.{i}."
     out = [(p + "input_norm", (h,), False), (p + "w_q", (cfg.q_dim, h), True),

@@ -126,9 +126,17 @@ def export_dflash_drafter(draft_model, spec, path: str) -> dict:
     tensors = {name: p.detach().cpu().contiguous() for name, p in draft_model.flat.params.items()}
     if hasattr(draft_model, "candidate_selector"):
         return _export_dflash2_drafter(draft_model, spec, path, tensors)
-    save_file(tensors, os.path.join(path, "model.safetensors"))
     cfg = draft_model.cfg
+    draft_vocab_size = cfg.vocab_size
+    if spec.model.draft_vocab_path:      # the vocabulary subset travels with the drafter (t2d / d2t)
+        from .dflash import DraftVocabulary
+
+        dv = DraftVocabulary.load(spec.model.draft_vocab_path, cfg.vocab_size)
+        tensors["t2d"], tensors["d2t"] = dv.t2d.contiguous(), dv.d2t.contiguous()
+        draft_vocab_size = dv.size
+    save_file(tensors, os.path.join(path, "model.safetensors"))
     json.dump({"architectures": ["DFlashDraftModel"], "model_type": "dflash", "hidden_size": cfg.hidden_size,
+               "draft_vocab_size": draft_vocab_size,
                "num_hidden_layers": cfg.num_layers, "num_attention_heads": cfg.num_attention_heads,
                "num_key_value_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,

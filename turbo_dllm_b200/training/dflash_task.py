@@ -57,6 +57,15 @@ class DFlashTask:
             from ..models.hf_loader import load_hf_weights
 
             load_hf_weights(self.target.model, hf_dir)
+        # model.draft_vocab_path: the drafter predicts a subset of the verifier's vocabulary; the frozen head of the
+        # losses is then the verifier head's rows of that subset
+        self.draft_vocab = None
+        self.head = self.target.lm_head
+        if m.draft_vocab_path:
+            from ..models.dflash import DraftVocabulary
+
+            self.draft_vocab = DraftVocabulary.load(m.draft_vocab_path, target_cfg.vocab_size)
+            self.head = self.draft_vocab.head_rows(self.target.lm_head)
         self.feature_store = None
         if self.offline:
             from ..data.dflash_features import FeatureStore
@@ -170,7 +179,7 @@ class DFlashTask:
             h_t = fh.index_select(0, want)
         wr = w.index_select(0, rows)
         if self.loss_kind == "speculators_kl":
-            loss_sum, _ = frozen_linear_kl(h_s, h_t, self.target.lm_head, wr)
+            loss_sum, _ = frozen_linear_kl(h_s, h_t, self.head, wr)
         elif self.is_dflash2 and self.loss_kind != "paper_ce":
             tgt_all = ids.reshape(-1).index_select(0, (ob.target_token_positions + seq_off).reshape(-1))
             loss_sum, denom = self._dflash2_loss(h_s, rows, tgt_all, sup, ob.position_weights.reshape(-1))
@@ -179,7 +188,11 @@ class DFlashTask:
         else:  # paper_ce: hard labels = the data token at the target position
             tgt = (ob.target_token_positions + seq_off).reshape(-1).index_select(0, rows)
             labels = ids.reshape(-1).index_select(0, tgt)
-            loss_sum, _ = linear_cross_entropy(h_s, self.target.lm_head, labels, wr, frozen_weight=True)
+            if self.draft_vocab is not None:    # tokens the drafter cannot emit are not supervised
+                labels = self.draft_vocab.to_draft_ids(labels)
+                wr = wr * (labels >= 0).to(wr.dtype)
+                labels = labels.clamp_min(0)
+            loss_sum, _ = linear_cross_entropy(h_s, self.head, labels, wr, frozen_weight=True)
         if denominator is None:
             wsum = wr.sum()
             if ex is not None:            # the anchors of this micro-batch are spread over the replica's ranks
