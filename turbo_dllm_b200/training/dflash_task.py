@@ -65,6 +65,9 @@ class DFlashTask:
             from ..models.dflash import DraftVocabulary
 
             self.draft_vocab = DraftVocabulary.load(m.draft_vocab_path, target_cfg.vocab_size)
+            if self.draft_vocab.size % 8:
+                raise ValueError(f"the draft vocabulary has {self.draft_vocab.size} ids; the logit rows of the loss "
+                                 "kernels need a multiple of 8")
             self.head = self.draft_vocab.head_rows(self.target.lm_head)
         self.feature_store = None
         if self.offline:
