@@ -147,3 +147,53 @@ def test_reduced_draft_vocabulary(tmp_path, capsys):
     assert json.load(open(out + "/dflash_config.json"))["draft_vocab_size"] == 128
     with pytest.raises(Exception, match="draft_vocab_path"):
         _spec("online").with_overrides({"model": {"draft_vocab_path": path, "dflash2_selector_rank": 4}}).validate()
+
+
+def test_sliding_window_drafter_and_context_compaction(monkeypatch, tmp_path):
+    """Sliding-window drafter layers see the last window - 1 context tokens before the anchor; when every layer has the
+    window, dropping the context rows no window reaches changes neither the loss nor the update."""
+    import json
+
+    from turbo_dllm_b200.models.dflash import dflash_mask_layout, window_context_rows
+    from turbo_dllm_b200.objectives.dflash import DFlashObjectiveRuntime
+
+    obj = DFlashObjectiveRuntime(block_size=8, max_anchors=3, mask_token_id=1023, seed=3, device="cpu")
+    ids = torch.randint(0, 1000, (2, 64), generator=torch.Generator().manual_seed(0))
+    ob = obj.prepare(ids, None)
+    lay = dflash_mask_layout(ob, 64, 8, window=5)
+    stop, start = ob.context_stops.long(), ob.document_starts.long()
+    seq = torch.arange(2)[:, None] * (1 << 24)
+    assert torch.equal(lay.q_hi.view(2, 3, 8)[:, :, 0].long(), seq + stop)
+    assert torch.equal(lay.q_lo.view(2, 3, 8)[:, :, 0].long(), seq + torch.maximum(start, stop - 4))
+    keep = window_context_rows(ob, 64, 5, min_rows=0)
+    want = torch.zeros(2, 64, dtype=torch.bool)
+    for b in range(2):
+        for a in range(3):
+            want[b, int(max(start[b, a], stop[b, a] - 4)):int(stop[b, a])] = True
+    assert torch.equal(keep, want.reshape(-1).nonzero(as_tuple=True)[0])
+    assert window_context_rows(ob, 64, 5, min_rows=40).numel() == 40
+
+    def spec(**model):
+        return _spec("online").with_overrides({"model": {"seq_len": 256, **model}}).validate()
+
+    def run(s, compact):
+        monkeypatch.setenv("TDLLM_DFLASH_COMPACT_CONTEXT", "1" if compact else "0")
+        t = TrainingSession(s, device="cpu")
+        loss = float(t.step().loss_sum)
+        return loss, t.model.flat.data.clone(), t.task.last_context_rows
+
+    full = run(spec(), True)
+    all_windowed = spec(sliding_window=6)
+    a, b = run(all_windowed, True), run(all_windowed, False)
+    assert a[2] == 128 and b[2] is None        # 2 x 256 context rows, the windows reach at most 4 x 5 per sequence
+    assert a[0] == pytest.approx(b[0], rel=1e-6) and torch.allclose(a[1], b[1], atol=1e-6)
+    assert a[0] != pytest.approx(full[0], rel=1e-4)
+    mixed = run(spec(sliding_window=6, sliding_window_pattern=2), True)      # every second layer attends to everything
+    assert mixed[2] is None and mixed[0] != pytest.approx(a[0], rel=1e-4) and mixed[0] != pytest.approx(full[0], rel=1e-4)
+    from turbo_dllm_b200.models.export import export_dflash_drafter
+
+    t = TrainingSession(spec(sliding_window=6, sliding_window_pattern=2), device="cpu")
+    export_dflash_drafter(t.model, t.spec, str(tmp_path / "e"))
+    conf = json.load(open(tmp_path / "e" / "dflash_config.json"))
+    assert conf["sliding_window"] == 6 and conf["sliding_window_non_causal"] is True
+    assert conf["layer_types"] == ["sliding_attention", "full_attention"]

@@ -156,10 +156,25 @@ def _draft_layer_specs(cfg: ModelConfig, i: int):
     return out
 
 
-def draft_attention(q, kv, mask, cfg: ModelConfig):
+class DraftMasks:
+    """The two visibility layouts of a drafter with sliding-window layers: `full` (a drafting block sees its document's
+    context up to its anchor) and `windowed` (only the last `sliding_window - 1` context tokens before the anchor)."""
+
+    def __init__(self, full: MaskLayout, windowed: MaskLayout | None = None):
+        self.full, self.windowed = full, windowed
+
+    def for_layer(self, cfg: ModelConfig, idx: int) -> MaskLayout:
+        if self.windowed is not None and cfg.layer_window(idx) is not None:
+            return self.windowed
+        return self.full
+
+
+def draft_attention(q, kv, mask, cfg: ModelConfig, layer_idx: int = 0):
     """q [draft rows, Hq, D]; kv [draft rows + context rows, 2 * Hkv * D] (K | V). `mask` is the MaskLayout of a
-    single-rank replica, or the (exchange, plan) pair of a replica that spans ranks
-    (parallel/dflash_context.py), whose context rows are this rank's shard."""
+    single-rank replica (or its `DraftMasks` pair when some layers have a sliding window), or the (exchange, plan)
+    pair of a replica that spans ranks (parallel/dflash_context.py), whose context rows are this rank's shard."""
+    if isinstance(mask, DraftMasks):
+        mask = mask.for_layer(cfg, layer_idx)
     if isinstance(mask, tuple):
         exchange, plan = mask
         return exchange.attend(plan, q, kv, cfg.num_key_value_heads)
@@ -189,7 +204,7 @@ class DFlashLayer(nn.Module):
         kv = linear(torch.cat([y, ctx], dim=0), self.w_kv)       # keys = [draft rows ; context rows]
         kv = qk_norm_rope(kv, pos_all, inv_freq, self.q_norm, self.k_norm, 0, c.num_key_value_heads, c.head_dim,
                           c.rms_norm_eps)
-        a = draft_attention(q.view(nd, c.num_attention_heads, c.head_dim), kv, mask, c)
+        a = draft_attention(q.view(nd, c.num_attention_heads, c.head_dim), kv, mask, c, self.idx)
         h = linear_residual(a.reshape(nd, c.q_dim), self.w_o, h)
         y2, _ = rmsnorm(h, self.post_norm, c.rms_norm_eps)
         return linear_residual(linear_swiglu(y2, self.w_gate_up), self.w_down, h)
@@ -232,17 +247,48 @@ class DFlashDraftModel(nn.Module):
         return y
 
 
-def dflash_mask_layout(batch_obj, seq_len: int, block_size: int, seq_stride: int = 1 << 24) -> MaskLayout:
-    """Draft rows (queries and first keys) then the B·L context keys."""
+def dflash_mask_layout(batch_obj, seq_len: int, block_size: int, seq_stride: int = 1 << 24, *, window: int | None = None,
+                       context_rows: torch.Tensor | None = None) -> MaskLayout:
+    """Draft rows (queries and first keys) then the context keys: all B·L rows, or the rows `context_rows` (flat
+    indices b·L + position) when the context was compacted. `window`: a drafting block sees only the last
+    `window - 1` context tokens before its anchor (the anchor's own token is the window's newest entry:
+    dllm_parallel/core/attention/dflash_attention.py:853-875); its own block stays fully visible."""
     a = batch_obj.anchor_positions
     b, A = a.shape
     dev = a.device
     seq = torch.arange(b, device=dev)[:, None].expand(b, A)
     grp = (seq * A + torch.arange(A, device=dev)[None, :])
-    lo = seq * seq_stride + batch_obj.document_starts.long()
-    hi = seq * seq_stride + batch_obj.context_stops.long()
+    start, stop = batch_obj.document_starts.long(), batch_obj.context_stops.long()
+    if window is not None:
+        start = torch.maximum(start, stop - max(1, int(window) - 1))
+    lo = seq * seq_stride + start
+    hi = seq * seq_stride + stop
     rep = lambda t: t[:, :, None].expand(b, A, block_size).reshape(-1)
     q_lo, q_hi, q_grp = rep(lo), rep(hi), -(rep(grp) + 1)
     ctx_code = (torch.arange(b, device=dev)[:, None] * seq_stride + torch.arange(seq_len, device=dev)[None, :]).reshape(-1)
+    if context_rows is not None:
+        ctx_code = ctx_code.index_select(0, context_rows)
     i32 = torch.int32
     return MaskLayout(q_lo.to(i32), q_hi.to(i32), q_grp.to(i32), torch.cat([q_grp, ctx_code]).to(i32))
+
+
+def window_context_rows(batch_obj, seq_len: int, window: int, min_rows: int = 128) -> torch.Tensor:
+    """Flat indices (b·L + position, ascending) of the context rows that some valid anchor's window reaches. When every
+    layer of the drafter has the window, all other rows have no influence and no gradient (the conditioning
+    projection, norms, rotary embedding and K|V projection act row by row) and are left out of the step
+    (dllm_parallel/core/models/backbones/dflash/model.py:1098-1215). At least `min_rows` rows are kept, so no
+    projection runs on a degenerate row count; extra rows are invisible to every query."""
+    stop = batch_obj.context_stops.long()
+    start = torch.maximum(batch_obj.document_starts.long(), stop - max(1, int(window) - 1))
+    b, A = stop.shape
+    # coverage count by difference array: +1 at start, -1 at stop (invalid anchors have start == stop == seq_len)
+    diff = torch.zeros(b, seq_len + 1, dtype=torch.int32, device=stop.device)
+    one = torch.ones_like(start, dtype=torch.int32)
+    diff.scatter_add_(1, start.clamp_max(seq_len), one)
+    diff.scatter_add_(1, stop.clamp_max(seq_len), -one)
+    keep = diff[:, :seq_len].cumsum(1) > 0
+    short = min(min_rows, b * seq_len) - int(keep.sum())
+    if short > 0:
+        spare = (~keep).reshape(-1).nonzero(as_tuple=True)[0][:short]
+        keep.view(-1)[spare] = True
+    return keep.reshape(-1).nonzero(as_tuple=True)[0]

@@ -74,7 +74,7 @@ class DFlash2Layer(nn.Module):
         kv = linear(torch.cat([y, ctx], dim=0), self.w_kv)
         kv = qk_norm_rope(kv, pos_all, inv_freq, self.q_norm, self.k_norm, 0, c.num_key_value_heads, c.head_dim,
                           c.rms_norm_eps)
-        a = draft_attention(q.view(nd, c.num_attention_heads, c.head_dim), kv, mask, c)
+        a = draft_attention(q.view(nd, c.num_attention_heads, c.head_dim), kv, mask, c, self.idx)
         h = h + self.attention_conv.finish(linear(a.reshape(nd, c.q_dim), self.w_o), k_attn)
         y2, _ = rmsnorm(h, self.post_norm, c.rms_norm_eps)
         y2, k_mlp = self.mlp_conv.prepare(y2)

@@ -142,9 +142,19 @@ def export_dflash_drafter(draft_model, spec, path: str) -> dict:
                "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,
                "block_size": spec.objective.block_size, "target_layer_ids": list(spec.model.target_layer_ids),
                "conditioning_dim": draft_model.conditioning_dim, "mask_token_id": cfg.mask_token_id,
-               "verifier": spec.model.verifier_id, "gate_up_layout": "interleaved"},
+               "verifier": spec.model.verifier_id, "gate_up_layout": "interleaved", **_sliding_window_fields(cfg)},
               open(os.path.join(path, "dflash_config.json"), "w"), indent=1)
     return write_export_manifest(path, {"kind": "dflash_drafter"})
+
+
+def _sliding_window_fields(cfg) -> dict:
+    """Sliding-window settings of a drafter for the serving stack: window, per-layer kinds, and that a drafting
+    block's own tokens see each other in both directions in every layer (as they do in training here)."""
+    if not cfg.has_sliding_layers:
+        return {}
+    return {"sliding_window": int(cfg.sliding_window), "sliding_window_non_causal": True,
+            "layer_types": ["sliding_attention" if cfg.layer_window(i) is not None else "full_attention"
+                            for i in range(cfg.num_layers)]}
 
 
 def dflash2_serving_shapes(config: dict) -> dict[str, tuple[int, ...]]:
@@ -221,6 +231,7 @@ def _export_dflash2_drafter(draft_model, spec, path: str, tensors: dict) -> dict
                                 "selector_rank": int(sel.predecessor.shape[1]), "selector_top_k": int(sel.top_k),
                                 "attention_mode": "gqa" if cfg.num_key_value_heads < cfg.num_attention_heads else "mha",
                                 "target_layer_ids": list(spec.model.target_layer_ids)}}
+    config.update(_sliding_window_fields(cfg))
     normalize_dflash2_config(config)
     json.dump(config, open(os.path.join(path, "config.json"), "w"), indent=1)
     json.dump(config, open(os.path.join(path, "dflash_config.json"), "w"), indent=1)

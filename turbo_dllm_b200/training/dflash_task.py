@@ -111,6 +111,12 @@ class DFlashTask:
             anchor_group_size=o.anchor_group_size, sample_from_anchor=o.sample_from_anchor, decay_gamma=o.decay_gamma)
         self.loss_kind = o.dflash_loss
         self.synthetic = spec.data.target_features == "synthetic"
+        # sliding-window drafters: leave out context rows no window reaches (TDLLM_DFLASH_COMPACT_CONTEXT=0 keeps them)
+        self.compact_context = os.environ.get("TDLLM_DFLASH_COMPACT_CONTEXT", "1") != "0"
+        self.last_context_rows = None
+        if cfg.has_sliding_layers and exchange is not None:
+            raise ValueError("sliding-window drafter layers are built for replicas on one rank "
+                             "(context_parallel_size = block_parallel_size = 1)")
 
     def set_optimizer_step(self, step: int, total_steps: int) -> None:
         """Warm-up and ramp of the selector loss (fractions of the run's optimizer steps)."""
@@ -149,9 +155,22 @@ class DFlashTask:
         bs = self.objective.block_size
         ex = self.exchange
         if ex is None:
-            mask = dflash_mask_layout(ob, l, bs)
             ctx_features = feats.hidden
             pos_ctx = torch.arange(l, device=ids.device).repeat(b)
+            window = self.cfg.sliding_window if self.cfg.has_sliding_layers else None
+            if window is None:
+                mask = dflash_mask_layout(ob, l, bs)
+            else:
+                from ..models.dflash import DraftMasks, window_context_rows
+
+                every_layer = all(self.cfg.layer_window(i) is not None for i in range(self.cfg.num_layers))
+                keep = window_context_rows(ob, l, window) if every_layer and self.compact_context else None
+                windowed = dflash_mask_layout(ob, l, bs, window=window, context_rows=keep)
+                mask = DraftMasks(windowed if every_layer else dflash_mask_layout(ob, l, bs), windowed)
+                if keep is not None:      # rows no window reaches take no part in the step
+                    ctx_features = ctx_features.index_select(0, keep)
+                    pos_ctx = pos_ctx.index_select(0, keep)
+                    self.last_context_rows = int(keep.numel())
         else:
             # this rank's anchors of the (replica-wide identical) sample, and its shard of the context rows
             from ..parallel.dflash_context import select_anchors
