@@ -197,3 +197,47 @@ def test_sliding_window_drafter_and_context_compaction(monkeypatch, tmp_path):
     conf = json.load(open(tmp_path / "e" / "dflash_config.json"))
     assert conf["sliding_window"] == 6 and conf["sliding_window_non_causal"] is True
     assert conf["layer_types"] == ["sliding_attention", "full_attention"]
+
+
+def test_speculators_checkpoint_round_trip(tmp_path):
+    """The deployable layout (module-style names, verifier embedding and head, speculators_config) reloads into a fresh
+    drafter tensor for tensor; with a draft vocabulary the head holds the subset's rows."""
+    import json
+
+    from safetensors import safe_open
+
+    from turbo_dllm_b200.models.dflash import DraftVocabulary
+    from turbo_dllm_b200.models.export import export_speculators_checkpoint, load_speculators_checkpoint
+
+    vocab = str(tmp_path / "dv.safetensors")
+    DraftVocabulary.from_ids(torch.arange(0, 1024, 4), 1024).save(vocab)
+    s = TrainingSession(_spec("online").with_overrides({"model": {"draft_vocab_path": vocab}}).validate(), device="cpu")
+    s.step()
+    out = str(tmp_path / "spec")
+    man = export_speculators_checkpoint(s.model, s.task.target, s.spec, out)
+    assert man["kind"] == "dflash_speculators"
+    conf = json.load(open(out + "/config.json"))
+    assert conf["speculators_config"]["proposal_methods"][0]["speculative_tokens"] == 7       # block 8, anchor = bonus token
+    assert conf["speculators_config"]["verifier"]["name_or_path"] == "synthetic:tiny-qwen3"
+    assert conf["draft_vocab_size"] == 256 and conf["vocab_size"] == 1024 and conf["aux_hidden_state_layer_ids"] == [0, 2]
+    cfg = s.model.cfg
+    with safe_open(out + "/model.safetensors", framework="pt") as f:
+        keys = set(f.keys())
+        assert {"fc.weight", "hidden_norm.weight", "norm.weight", "embed_tokens.weight", "lm_head.weight", "t2d", "d2t",
+                "layers.0.self_attn.k_proj.weight", "layers.1.mlp.up_proj.weight"} <= keys
+        assert tuple(f.get_tensor("lm_head.weight").shape) == (256, cfg.hidden_size)
+        assert torch.equal(f.get_tensor("lm_head.weight"), s.task.target.lm_head[::4])
+        assert tuple(f.get_tensor("layers.0.self_attn.v_proj.weight").shape) == (cfg.kv_dim, cfg.hidden_size)
+        gate = f.get_tensor("layers.0.mlp.gate_proj.weight")
+    assert torch.equal(gate, s.model.flat.params["layers.0.w_gate_up"][0::2])
+    fresh = TrainingSession(_spec("online"), device="cpu")
+    assert not torch.equal(fresh.model.flat.data, s.model.flat.data)
+    load_speculators_checkpoint(fresh.model, out)
+    assert torch.equal(fresh.model.flat.data, s.model.flat.data)
+    # model.id naming the exported directory: the architecture comes from its config, the weights from its tensors
+    cont = TrainingSession(_spec("online").with_overrides({"model": {"id": out, "max_layers": None}}).validate(), device="cpu")
+    assert torch.equal(cont.model.flat.data, s.model.flat.data)
+    # a drafter of another width is refused tensor by tensor
+    other = TrainingSession(_spec("online").with_overrides({"model": {"intermediate_size": 128}}).validate(), device="cpu")
+    with pytest.raises(ValueError, match="checkpoint shape"):
+        load_speculators_checkpoint(other.model, out)

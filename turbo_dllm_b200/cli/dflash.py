@@ -30,6 +30,8 @@ def run_dflash(argv) -> int:
     p.add_argument("--config", required=True)
     p.add_argument("--checkpoint", required=True)
     p.add_argument("--output", required=True)
+    p.add_argument("--format", choices=("native", "speculators"), default="native",
+                   help="speculators: module-style tensor names with the verifier's embedding and head (DFlash drafter)")
     p = sub.add_parser("validate-export")
     p.add_argument("path")
     p.add_argument("--block-size", type=int, default=None, help="the block size the export must carry")
@@ -112,7 +114,11 @@ def run_dflash(argv) -> int:
             spec = load_run_spec(a.config).validate()
             s = TrainingSession(spec)
             load_training_checkpoint(a.checkpoint, "latest", s, rank=0, world_size=1, restore_rng=False)
-            print(json.dumps({"files": sorted(ex.export_dflash_drafter(s.model, spec, a.output)["files"])}))
+            if a.format == "speculators":
+                man = ex.export_speculators_checkpoint(s.model, s.task.target, spec, a.output)
+            else:
+                man = ex.export_dflash_drafter(s.model, spec, a.output)
+            print(json.dumps({"files": sorted(man["files"])}))
             return 0
         if a.cmd == "validate-export":
             import os

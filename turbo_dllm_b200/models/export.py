@@ -147,6 +147,112 @@ def export_dflash_drafter(draft_model, spec, path: str) -> dict:
     return write_export_manifest(path, {"kind": "dflash_drafter"})
 
 
+def _speculators_tensor_names(cfg) -> dict[str, tuple]:
+    """Module-style tensor name -> (flat parameter name, how to cut it) for a DFlash drafter."""
+    names = {"fc.weight": ("fc", None), "hidden_norm.weight": ("hidden_norm", None), "norm.weight": ("final_norm", None)}
+    kd = cfg.kv_dim
+    for i in range(cfg.num_layers):
+        f, m = f"layers.{i}.", f"layers.{i}."
+        names.update({
+            m + "input_layernorm.weight": (f + "input_norm", None),
+            m + "post_attention_layernorm.weight": (f + "post_norm", None),
+            m + "self_attn.q_proj.weight": (f + "w_q", None), m + "self_attn.o_proj.weight": (f + "w_o", None),
+            m + "self_attn.k_proj.weight": (f + "w_kv", ("rows", 0, kd)),
+            m + "self_attn.v_proj.weight": (f + "w_kv", ("rows", kd, 2 * kd)),
+            m + "mlp.gate_proj.weight": (f + "w_gate_up", ("stride", 0)),
+            m + "mlp.up_proj.weight": (f + "w_gate_up", ("stride", 1)),
+            m + "mlp.down_proj.weight": (f + "w_down", None)})
+        if cfg.qk_norm:
+            names[m + "self_attn.q_norm.weight"] = (f + "q_norm", None)
+            names[m + "self_attn.k_norm.weight"] = (f + "k_norm", None)
+    return names
+
+
+def _cut(t: torch.Tensor, how):
+    if how is None:
+        return t
+    if how[0] == "rows":
+        return t[how[1]:how[2]]
+    return t[how[1]::2]          # gate and up rows alternate in the fused weight
+
+
+@torch.no_grad()
+def export_speculators_checkpoint(draft_model, target, spec, path: str) -> dict:
+    """A DFlash drafter as a self-contained speculative-decoding checkpoint: module-style tensor names
+    (`layers.i.self_attn.q_proj.weight`, `fc.weight`, ...), the verifier's embedding and output head it drafts
+    with (the head's rows of the draft vocabulary when `model.draft_vocab_path` is set, plus `t2d` / `d2t`), and a
+    config.json with a `speculators_config` section naming the verifier and the proposal length
+    (dllm_parallel/core/models/backbones/dflash/executor.py:412-455). `target`: the FrozenTarget of the run."""
+    from safetensors.torch import save_file
+
+    if hasattr(draft_model, "candidate_selector"):
+        raise ValueError("the DFlash2 drafter has its own export (export_dflash_drafter)")
+    cfg = draft_model.cfg
+    os.makedirs(path, exist_ok=True)
+    flat = draft_model.flat.params
+    tensors = {name: _cut(flat[src], how).detach().cpu().contiguous()
+               for name, (src, how) in _speculators_tensor_names(cfg).items()}
+    head = target.lm_head.detach().cpu()
+    draft_vocab_size = int(head.shape[0])
+    if spec.model.draft_vocab_path:
+        from .dflash import DraftVocabulary
+
+        dv = DraftVocabulary.load(spec.model.draft_vocab_path, head.shape[0])
+        head, draft_vocab_size = dv.head_rows(head), dv.size
+        tensors["t2d"], tensors["d2t"] = dv.t2d.contiguous(), dv.d2t.contiguous()
+    tensors["embed_tokens.weight"] = target.embed.detach().cpu().contiguous()
+    tensors["lm_head.weight"] = head.contiguous()
+    tmp = os.path.join(path, ".model.safetensors.tmp")
+    save_file(tensors, tmp)
+    os.replace(tmp, os.path.join(path, "model.safetensors"))
+    block = int(spec.objective.block_size or 16)
+    # with sample_from_anchor the block's first slot is a prediction too; otherwise the anchor is the bonus token
+    speculative = block if spec.objective.sample_from_anchor else block - 1
+    config = {"architectures": ["DFlashDraftModel"], "model_type": "dflash", "hidden_size": cfg.hidden_size,
+              "num_hidden_layers": cfg.num_layers, "num_attention_heads": cfg.num_attention_heads,
+              "num_key_value_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "qk_norm": cfg.qk_norm,
+              "intermediate_size": cfg.intermediate_size, "vocab_size": int(target.lm_head.shape[0]),
+              "draft_vocab_size": draft_vocab_size, "target_hidden_size": int(target.cfg.hidden_size),
+              "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_norm_eps, "hidden_act": "silu",
+              "block_size": block, "mask_token_id": cfg.mask_token_id, "sample_from_anchor": bool(spec.objective.sample_from_anchor),
+              "aux_hidden_state_layer_ids": list(spec.model.target_layer_ids),
+              "dflash_config": {"block_size": block, "target_layer_ids": list(spec.model.target_layer_ids),
+                                "mask_token_id": cfg.mask_token_id},
+              "speculators_model_type": "dflash",
+              "speculators_config": {"algorithm": "dflash", "default_proposal_method": "greedy",
+                                     "proposal_methods": [{"proposal_type": "greedy", "speculative_tokens": speculative}],
+                                     "verifier": {"name_or_path": spec.model.verifier_id,
+                                                  "architectures": ["Qwen3ForCausalLM"]}},
+              **_sliding_window_fields(cfg)}
+    tmp = os.path.join(path, ".config.json.tmp")
+    with open(tmp, "w") as f:
+        f.write(json.dumps(config, indent=2, sort_keys=True) + "\n")
+    os.replace(tmp, os.path.join(path, "config.json"))
+    return write_export_manifest(path, {"kind": "dflash_speculators", "tensor_count": len(tensors)})
+
+
+@torch.no_grad()
+def load_speculators_checkpoint(draft_model, path: str) -> dict:
+    """Fills a DFlash drafter from a checkpoint in the layout `export_speculators_checkpoint` writes (to continue
+    training a published drafter); returns its config. Shapes are checked tensor by tensor."""
+    from safetensors import safe_open
+
+    cfg = draft_model.cfg
+    config = json.load(open(os.path.join(path, "config.json")))
+    flat = draft_model.flat.params
+    with safe_open(os.path.join(path, "model.safetensors"), framework="pt") as f:
+        have = set(f.keys())
+        for name, (dst, how) in _speculators_tensor_names(cfg).items():
+            if name not in have:
+                raise KeyError(f"{path} lacks {name}")
+            t = f.get_tensor(name)
+            view = _cut(flat[dst], how)
+            if tuple(view.shape) != tuple(t.shape):
+                raise ValueError(f"{name}: checkpoint shape {tuple(t.shape)}, drafter expects {tuple(view.shape)}")
+            view.copy_(t.to(view.device, view.dtype))
+    return config
+
+
 def _sliding_window_fields(cfg) -> dict:
     """Sliding-window settings of a drafter for the serving stack: window, per-layer kinds, and that a drafting
     block's own tokens see each other in both directions in every layer (as they do in training here)."""

@@ -95,6 +95,17 @@ class DFlashTask:
             self.model = DFlashDraftModel(cfg, target_hidden=target_cfg.hidden_size,
                                           num_target_layers=len(m.target_layer_ids), dtype=dtype, device=device,
                                           seed=seed)
+        from ..models.hf_loader import pretrained_directory
+
+        start = None if m.random_init else pretrained_directory(m.id)
+        if start is not None:
+            # model.id names a drafter checkpoint on disk (module-style tensor names): continue from its weights
+            if self.is_dflash2:
+                raise ValueError("continuing from a drafter checkpoint is built for the DFlash drafter; a DFlash2 run "
+                                 "resumes from its training checkpoints")
+            from ..models.export import load_speculators_checkpoint
+
+            load_speculators_checkpoint(self.model, start)
         from ..ops.dflash2 import DPACE_LOSSES
 
         if o.dflash_loss in ("dflash",) + DPACE_LOSSES and not self.is_dflash2:
