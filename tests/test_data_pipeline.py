@@ -420,3 +420,46 @@ def test_chat_template_supervision_with_a_hugging_face_tokenizer(tmp_path):
         "output": {"path": str(tmp_path / "e")}}))
     assert np.fromfile(tmp_path / "e" / "tokens.i32", dtype="<i4").tolist() == [2, 11, 4, 3, 12, 4]
     assert np.fromfile(tmp_path / "e" / "loss_mask.u8", dtype=np.uint8).tolist() == [0, 0, 0, 0, 1, 1]
+
+
+def test_flat_token_files_text_files_and_text_mode(tmp_path):
+    """`data.dataset_path` may name a flat token file or a text file instead of a prepared artifact, and
+    `data.input_mode: text` trains on a built-in paragraph; all are sharded by rank and resumable."""
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    stream = (np.arange(4096) % 1000).astype("<i4")
+    stream.tofile(tmp_path / "flat.i32")
+    stream.astype("<i8").tofile(tmp_path / "flat.bin")
+    torch.save({"input_ids": torch.from_numpy(stream.astype(np.int64))}, tmp_path / "flat.pt")
+    runs = {}
+    for name in ("flat.i32", "flat.bin", "flat.pt"):
+        rt = PackedTokenDataRuntime.from_token_file(tmp_path / name, batch_size=2, seq_len=64, seed=1, vocab_size=1024)
+        runs[name] = rt.next_batch().input_ids
+        assert rt.fingerprint.startswith("file:")
+    assert torch.equal(runs["flat.i32"], runs["flat.bin"]) and torch.equal(runs["flat.i32"], runs["flat.pt"])
+    with pytest.raises(ArtifactError, match="outside the model vocabulary"):
+        PackedTokenDataRuntime.from_token_file(tmp_path / "flat.i32", batch_size=2, seq_len=64, vocab_size=500)
+    a = PackedTokenDataRuntime.from_token_file(tmp_path / "flat.i32", batch_size=2, seq_len=64, dp_rank=0, dp_size=2, seed=1)
+    b = PackedTokenDataRuntime.from_token_file(tmp_path / "flat.i32", batch_size=2, seq_len=64, dp_rank=1, dp_size=2, seed=1)
+    assert not set(a.next_batch().sample_ids.tolist()) & set(b.next_batch().sample_ids.tolist())
+    state = a.state_dict()
+    want = a.next_batch().input_ids
+    c = PackedTokenDataRuntime.from_token_file(tmp_path / "flat.i32", batch_size=2, seq_len=64, dp_rank=0, dp_size=2, seed=1)
+    c.load_state_dict(state)
+    assert torch.equal(c.next_batch().input_ids, want)
+    np.zeros(4096, dtype="<i4").tofile(tmp_path / "other.i32")
+    with pytest.raises(ArtifactError, match="different dataset"):
+        PackedTokenDataRuntime.from_token_file(tmp_path / "other.i32", batch_size=2, seq_len=64, dp_size=2).load_state_dict(state)
+
+    base = {"model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "num_layers": 1},
+            "objective": {"name": "standard_block_diffusion", "block_size": 16}, "training": {"batch_size": 2, "steps": 1},
+            "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}
+    (tmp_path / "corpus.txt").write_text("some plain text for a quick run. " * 40)
+    for data in ({"input_mode": "dataset", "dataset_path": str(tmp_path / "flat.i32")},
+                 {"input_mode": "dataset", "dataset_path": str(tmp_path / "corpus.txt")},
+                 {"input_mode": "text"}):
+        s = TrainingSession(RunSpec.from_mapping({**base, "data": data}).validate(), device="cpu")
+        r = s.step()
+        assert torch.isfinite(r.loss_sum) and isinstance(s.data, PackedTokenDataRuntime)
+    assert int(s.data.tokens.max()) < 256                    # the byte stand-in tokenised the built-in paragraph

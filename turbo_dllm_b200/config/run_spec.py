@@ -235,8 +235,9 @@ class RunSpec:
             need((self.adapter.rank or 0) > 0, "adapter.rank must be positive for LoRA")
             bad = sorted(set(self.adapter.targets) - {"attention", "mlp", "experts"})
             need(not bad, f"adapter.targets has unknown roles: {bad}")
-        if self.data.input_mode in ("text", "dataset"):
-            need(bool(self.data.dataset_path), f"data.input_mode={self.data.input_mode} needs data.dataset_path")
+        if self.data.input_mode == "dataset":
+            need(bool(self.data.dataset_path), "data.input_mode=dataset needs data.dataset_path (a prepared artifact "
+                                               "directory, a flat token file, or a text file)")
         ck = self.checkpointing
         need(ck.save_checkpoint_interval >= 0 and ck.keep_last_n >= 0, "checkpointing intervals must be >= 0")
         if ck.save_checkpoint_interval or ck.save_first_step or ck.save_final or ck.save_duration_fractions:

@@ -52,17 +52,30 @@ class _Stager:
         return dev, pinned.numel() * pinned.element_size()
 
 
+SANITY_TEXT = ("Block diffusion language models denoise one block of tokens at a time, conditioned on the clean "
+               "tokens before it. This sentence repeats so that a run can be checked without preparing a dataset. ")
+
+
 class PackedTokenDataRuntime(DataRuntime):
-    def __init__(self, root: str | Path, *, batch_size: int, seq_len: int, dp_rank: int = 0, dp_size: int = 1,
-                 shuffle: bool = True, seed: int = 0, device="cpu", expected_fingerprint: str | None = None):
-        self.root = Path(root)
-        m = load_manifest(self.root)
-        if m["format"] != PACKED_TOKEN_FORMAT:
-            raise ArtifactError(f"{root} is not a packed-token artifact")
-        self.fingerprint = m["metadata"]["dataset_fingerprint"]
+    def __init__(self, root: str | Path | None, *, batch_size: int, seq_len: int, dp_rank: int = 0, dp_size: int = 1,
+                 shuffle: bool = True, seed: int = 0, device="cpu", expected_fingerprint: str | None = None,
+                 tokens: np.ndarray | None = None, fingerprint: str | None = None):
+        """`root`: a packed-token artifact directory. Without one, `tokens` (a 1-D integer array, possibly
+        memory-mapped) is the stream and `fingerprint` identifies it in checkpoints (`from_token_file`,
+        `from_repeated_text`)."""
+        if root is None:
+            if tokens is None or fingerprint is None:
+                raise ValueError("a packed runtime without an artifact directory needs tokens and a fingerprint")
+            self.root, self.fingerprint, self.tokens = None, fingerprint, tokens
+        else:
+            self.root = Path(root)
+            m = load_manifest(self.root)
+            if m["format"] != PACKED_TOKEN_FORMAT:
+                raise ArtifactError(f"{root} is not a packed-token artifact")
+            self.fingerprint = m["metadata"]["dataset_fingerprint"]
+            self.tokens = np.memmap(self.root / "tokens.i32", dtype="<i4", mode="r")
         if expected_fingerprint and expected_fingerprint != self.fingerprint:
             raise ArtifactError("dataset fingerprint differs from the one recorded in the checkpoint")
-        self.tokens = np.memmap(self.root / "tokens.i32", dtype="<i4", mode="r")
         self.batch_size, self.seq_len = batch_size, seq_len
         self.dp_rank, self.dp_size = dp_rank, dp_size
         self.windows = len(self.tokens) // seq_len
@@ -73,6 +86,60 @@ class PackedTokenDataRuntime(DataRuntime):
         self.epoch, self.cursor = 0, 0      # cursor counts GLOBAL batches consumed in this epoch
         self.stager = _Stager(device)
         self._order = self._epoch_order(0)
+
+    @classmethod
+    def from_token_file(cls, path: str | Path, *, tokenizer=None, vocab_size: int | None = None, **kw):
+        """A flat token file instead of a prepared artifact: raw little-endian `.i32 / .int32` and
+        `.i64 / .int64 / .bin / .tokens` (memory-mapped), `.npy`, `.pt` (a tensor, or a mapping with `input_ids`,
+        `tokens` or `data`), or any other file read as UTF-8 text and tokenised with `tokenizer`
+        (dllm_parallel/core/data.py:1397-1440). The fingerprint is the SHA-256 of the file (plus the tokenizer name
+        for text), so a resumed run refuses a different file."""
+        from .artifacts import sha256_file
+
+        path = Path(path)
+        suffix = path.suffix.lower()
+        ident = sha256_file(path)
+        if suffix in (".i32", ".int32"):
+            tokens = np.memmap(path, dtype="<i4", mode="r")
+        elif suffix in (".i64", ".int64", ".bin", ".tokens"):
+            if path.stat().st_size % 8:
+                raise ArtifactError(f"{path}: an int64 token file has a size that divides by 8")
+            tokens = np.memmap(path, dtype="<i8", mode="r")
+        elif suffix == ".npy":
+            tokens = np.load(path, mmap_mode="r").reshape(-1)
+        elif suffix == ".pt":
+            obj = torch.load(path, map_location="cpu", weights_only=True)
+            if isinstance(obj, dict):
+                key = next((k for k in ("input_ids", "tokens", "data") if k in obj), None)
+                if key is None:
+                    raise ArtifactError(f"{path}: expected a tensor or a mapping with input_ids / tokens / data")
+                obj = obj[key]
+            tokens = torch.as_tensor(obj).reshape(-1).numpy()
+        else:
+            if tokenizer is None:
+                raise ArtifactError(f"{path} is read as text and needs a tokenizer (a model.id directory with one)")
+            ids = tokenizer.encode(path.read_text(encoding="utf-8"), add_special_tokens=False)
+            tokens = np.asarray(ids, dtype=np.int64)
+            ident += ":" + str(getattr(tokenizer, "name_or_path", type(tokenizer).__name__))
+        if tokens.size == 0:
+            raise ArtifactError(f"{path} holds no tokens")
+        if vocab_size is not None:
+            # one pass over the stream: ids outside the vocabulary would index past the embedding table
+            hi, lo = int(tokens.max()), int(tokens.min())
+            if lo < 0 or hi >= vocab_size:
+                raise ArtifactError(f"{path} holds token ids in [{lo}, {hi}], outside the model vocabulary of {vocab_size}")
+        return cls(None, tokens=tokens, fingerprint="file:" + ident, **kw)
+
+    @classmethod
+    def from_repeated_text(cls, *, tokenizer, batch_size: int, seq_len: int, dp_size: int = 1, **kw):
+        """`data.input_mode: text`: a built-in paragraph, tokenised and repeated until every rank has a batch; for
+        checking a run end to end without a dataset (dllm_parallel/core/data.py:121-130)."""
+        ids = np.asarray(tokenizer.encode(SANITY_TEXT, add_special_tokens=False), dtype=np.int64)
+        need = seq_len * batch_size * dp_size * 4
+        tokens = np.tile(ids, need // ids.size + 1)
+        name = str(getattr(tokenizer, "name_or_path", type(tokenizer).__name__))
+        return cls(None, tokens=tokens, fingerprint=f"repeated_text:{name}:{ids.size}", batch_size=batch_size,
+                   seq_len=seq_len, dp_size=dp_size, **kw)
 
     def _epoch_order(self, epoch: int) -> np.ndarray:
         order = np.arange(self.windows)
@@ -259,11 +326,45 @@ class BlendedPackedTokenDataRuntime(DataRuntime):
             m.load_state_dict(s)
 
 
+class _ByteTextTokenizer:
+    """UTF-8 bytes as token ids: the stand-in when the run's model has no tokenizer on disk (synthetic presets)."""
+    name_or_path = "utf8-bytes"
+
+    def encode(self, text: str, add_special_tokens: bool = False) -> list[int]:
+        return list(text.encode("utf-8"))
+
+
+def _run_tokenizer(spec):
+    """The tokenizer that ships with the run's model (or verifier) checkpoint directory; bytes otherwise."""
+    from ..models.hf_loader import pretrained_directory
+
+    for mid in (spec.model.id, spec.model.verifier_id):
+        d = pretrained_directory(mid)
+        if d is not None:
+            try:
+                from transformers import AutoTokenizer
+
+                return AutoTokenizer.from_pretrained(d)
+            except Exception:       # a checkpoint directory without tokenizer files
+                continue
+    return _ByteTextTokenizer()
+
+
 def build_artifact_runtime(spec, *, device, dp_rank: int, dp_size: int) -> DataRuntime:
     """Chooses the runtime from the artifact's manifest (and the `w:path,...` blend syntax)."""
     path = spec.data.dataset_path
     common = dict(batch_size=spec.training.batch_size, dp_rank=dp_rank, dp_size=dp_size, shuffle=spec.data.shuffle,
                   device=device)
+    if spec.data.input_mode == "text":
+        return PackedTokenDataRuntime.from_repeated_text(tokenizer=_run_tokenizer(spec), seq_len=spec.model.seq_len,
+                                                         seed=spec.launch.seed, **common)
+    if Path(path).is_file():       # a flat token file or a text file instead of a prepared artifact
+        binary = Path(path).suffix.lower() in (".i32", ".int32", ".i64", ".int64", ".bin", ".tokens", ".npy", ".pt")
+        from ..models.config import model_config_from_run_spec
+
+        return PackedTokenDataRuntime.from_token_file(
+            path, tokenizer=None if binary else _run_tokenizer(spec), seq_len=spec.model.seq_len, seed=spec.launch.seed,
+            vocab_size=model_config_from_run_spec(spec).vocab_size, **common)
     if "," in path or (":" in path and not Path(path).exists()):
         members = []
         for item in path.split(","):
