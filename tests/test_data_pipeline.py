@@ -463,3 +463,47 @@ def test_flat_token_files_text_files_and_text_mode(tmp_path):
         r = s.step()
         assert torch.isfinite(r.loss_sum) and isinstance(s.data, PackedTokenDataRuntime)
     assert int(s.data.tokens.max()) < 256                    # the byte stand-in tokenised the built-in paragraph
+
+
+def test_blend_manifest_file(tmp_path):
+    """A JSON blend manifest mixes prepared artifacts and flat token files by weight; member paths are relative to it."""
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.data.artifact_runtimes import build_artifact_runtime
+
+    _packed(tmp_path, "prepared", n=200)
+    (np.full(8192, 7)).astype("<i4").tofile(tmp_path / "sevens.i32")
+    (tmp_path / "blend.json").write_text(json.dumps({"datasets": [{"path": "prepared", "weight": 1.0},
+                                                                  {"path": "sevens.i32", "weight": 3.0}]}))
+    spec = RunSpec.from_mapping({"model": {"id": "synthetic:tiny-qwen3", "seq_len": 64},
+                                 "objective": {"name": "standard_block_diffusion", "block_size": 16},
+                                 "training": {"batch_size": 1}, "topology": {"context_parallel_size": 1, "block_parallel_size": 1},
+                                 "data": {"input_mode": "dataset", "dataset_path": str(tmp_path / "blend.json"), "blend_seed": 5}}).validate()
+    rt = build_artifact_runtime(spec, device="cpu", dp_rank=0, dp_size=1)
+    assert isinstance(rt, BlendedPackedTokenDataRuntime)
+    sevens = sum(bool((rt.next_batch().input_ids == 7).all()) for _ in range(40))
+    assert 20 <= sevens <= 38                                   # weight 3 : 1
+    (tmp_path / "bad.json").write_text(json.dumps({"datasets": []}))
+    with pytest.raises(ArtifactError, match="blend manifest"):
+        build_artifact_runtime(spec.with_overrides({"data": {"dataset_path": str(tmp_path / "bad.json")}}), device="cpu", dp_rank=0, dp_size=1)
+
+
+def test_batches_share_the_response_start_for_native_sft(tmp_path):
+    from turbo_dllm_b200.data.artifacts import write_indexed_artifact
+
+    rng = np.random.default_rng(0)
+    samples = []
+    for i in range(64):
+        start = [16, 32][i % 2]
+        mask = np.zeros(64, np.uint8)
+        mask[start:] = 1
+        samples.append({"tokens": rng.integers(0, 500, 64).astype(np.int32), "loss_mask": mask, "sample_id": i})
+    write_indexed_artifact(tmp_path / "idx", samples, metadata={"tokenizer": {"vocab_size": 512}})
+    grouped = IndexedSupervisedTokenDataRuntime(tmp_path / "idx", batch_size=4, block_size=16, max_seq_len=64, seed=1,
+                                                group_by_supervision_start=True)
+    plain = IndexedSupervisedTokenDataRuntime(tmp_path / "idx", batch_size=4, block_size=16, max_seq_len=64, seed=1)
+    mixed = 0
+    for _ in range(8):
+        starts = grouped.next_batch().supervision_mask.int().argmax(1)
+        assert len(set(starts.tolist())) == 1
+        mixed += len(set(plain.next_batch().supervision_mask.int().argmax(1).tolist())) > 1
+    assert mixed > 0

@@ -177,7 +177,8 @@ class IndexedSupervisedTokenDataRuntime(DataRuntime):
     def __init__(self, root: str | Path, *, batch_size: int, block_size: int, max_seq_len: int,
                  minimum_sequence_length: int | None = None, dp_rank: int = 0, dp_size: int = 1,
                  shuffle: bool = True, seed: int = 0, device="cpu", optimizer_step_unit: str = "microbatch",
-                 terminal_turn_weight: float = 1.0):
+                 terminal_turn_weight: float = 1.0, group_by_supervision_start: bool = False):
+        self.group_by_supervision_start = bool(group_by_supervision_start)
         self.root = Path(root)
         m = load_manifest(self.root)
         if m["format"] != INDEXED_FORMAT:
@@ -261,14 +262,21 @@ class IndexedSupervisedTokenDataRuntime(DataRuntime):
         per_global = self.batch_size * self.dp_size
         out = []
         lens = self.index[self.eligible, 1]
-        for L in np.unique(lens):
-            ids = self.eligible[lens == L]
+        if self.group_by_supervision_start:
+            # one bucket per (length, first supervised position): a batch then shares its response start, which lets
+            # the native-SFT objective pack the response suffix instead of masking
+            key = lens * (int(self.index[:, 2].max()) + 1) + self.index[self.eligible, 2]
+        else:
+            key = lens
+        for L in np.unique(key):
+            ids = self.eligible[key == L]
             if self.shuffle:
                 rng.shuffle(ids)
             for i in range(0, len(ids) - per_global + 1, per_global):
                 out.append(ids[i:i + per_global])
         if not out:
-            raise ArtifactError(f"no length bucket holds a full global batch of {per_global} samples")
+            raise ArtifactError(f"no bucket of equal length{' and response start' if self.group_by_supervision_start else ''} "
+                                f"holds a full global batch of {per_global} samples")
         if self.shuffle:
             rng.shuffle(out)
         return out
@@ -358,13 +366,34 @@ def build_artifact_runtime(spec, *, device, dp_rank: int, dp_size: int) -> DataR
     if spec.data.input_mode == "text":
         return PackedTokenDataRuntime.from_repeated_text(tokenizer=_run_tokenizer(spec), seq_len=spec.model.seq_len,
                                                          seed=spec.launch.seed, **common)
-    if Path(path).is_file():       # a flat token file or a text file instead of a prepared artifact
-        binary = Path(path).suffix.lower() in (".i32", ".int32", ".i64", ".int64", ".bin", ".tokens", ".npy", ".pt")
+    def member(p: Path, seed: int) -> PackedTokenDataRuntime:
+        """One packed stream: a prepared artifact directory, a flat token file or a text file."""
+        if p.is_dir():
+            return PackedTokenDataRuntime(p, seq_len=spec.model.seq_len, seed=seed, **common)
+        binary = p.suffix.lower() in (".i32", ".int32", ".i64", ".int64", ".bin", ".tokens", ".npy", ".pt")
         from ..models.config import model_config_from_run_spec
 
         return PackedTokenDataRuntime.from_token_file(
-            path, tokenizer=None if binary else _run_tokenizer(spec), seq_len=spec.model.seq_len, seed=spec.launch.seed,
+            p, tokenizer=None if binary else _run_tokenizer(spec), seq_len=spec.model.seq_len, seed=seed,
             vocab_size=model_config_from_run_spec(spec).vocab_size, **common)
+
+    if Path(path).is_file() and Path(path).suffix.lower() == ".json":
+        # a blend manifest: {"datasets": [{"path": ..., "weight": ...}, ...]} (or the bare list); relative member
+        # paths are relative to the manifest (dllm_parallel/core/data.py:1302-1345)
+        import json
+
+        doc = json.loads(Path(path).read_text())
+        entries = doc.get("datasets") if isinstance(doc, dict) else doc
+        if not isinstance(entries, list) or not entries or not all(isinstance(e, dict) and e.get("path") for e in entries):
+            raise ArtifactError(f"{path}: a blend manifest holds a non-empty `datasets` list of {{path, weight}} entries")
+        members = []
+        for e in entries:
+            p = Path(str(e["path"]))
+            p = p if p.is_absolute() else Path(path).parent / p
+            members.append((float(e.get("weight", 1.0)), member(p, spec.data.blend_seed)))
+        return BlendedPackedTokenDataRuntime(members, seed=spec.data.blend_seed)
+    if Path(path).is_file():       # a flat token file or a text file instead of a prepared artifact
+        return member(Path(path), spec.launch.seed)
     if "," in path or (":" in path and not Path(path).exists()):
         members = []
         for item in path.split(","):
@@ -379,4 +408,5 @@ def build_artifact_runtime(spec, *, device, dp_rank: int, dp_size: int) -> DataR
         path, block_size=spec.objective.block_size or 1, max_seq_len=spec.model.seq_len,
         minimum_sequence_length=spec.data.minimum_sequence_length, seed=spec.launch.seed,
         optimizer_step_unit=spec.data.optimizer_step_unit,
-        terminal_turn_weight=spec.data.trajectory_terminal_turn_weight, **common)
+        terminal_turn_weight=spec.data.trajectory_terminal_turn_weight,
+        group_by_supervision_start=spec.objective.name == "diffusiongemma_native_sft", **common)
