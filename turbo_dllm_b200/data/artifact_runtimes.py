@@ -177,7 +177,11 @@ class IndexedSupervisedTokenDataRuntime(DataRuntime):
     def __init__(self, root: str | Path, *, batch_size: int, block_size: int, max_seq_len: int,
                  minimum_sequence_length: int | None = None, dp_rank: int = 0, dp_size: int = 1,
                  shuffle: bool = True, seed: int = 0, device="cpu", optimizer_step_unit: str = "microbatch",
-                 terminal_turn_weight: float = 1.0, group_by_supervision_start: bool = False):
+                 terminal_turn_weight: float = 1.0, group_by_supervision_start: bool = False,
+                 context_parallel_size: int = 1, block_parallel_size: int = 1):
+        """Eligible samples fit `max_seq_len`, are whole blocks, give every block-parallel rank at least one block,
+        and under pure context parallelism divide by the context-parallel degree
+        (dllm_parallel/core/data.py:708-722)."""
         self.group_by_supervision_start = bool(group_by_supervision_start)
         self.root = Path(root)
         m = load_manifest(self.root)
@@ -188,11 +192,15 @@ class IndexedSupervisedTokenDataRuntime(DataRuntime):
         self.mask = np.memmap(self.root / "loss_mask.u8", dtype=np.uint8, mode="r")
         self.index = np.fromfile(self.root / "index.i64", dtype="<i8").reshape(-1, 4)
         lens = self.index[:, 1]
-        ok = (lens % block_size == 0) & (lens <= max_seq_len) & (lens >= (minimum_sequence_length or 1))
+        shortest = max(int(block_parallel_size) * block_size, int(minimum_sequence_length or 1))
+        ok = (lens % block_size == 0) & (lens <= max_seq_len) & (lens >= shortest)
+        if context_parallel_size > 1 and block_parallel_size == 1:
+            ok &= lens % int(context_parallel_size) == 0
         self.eligible = np.flatnonzero(ok)
         self.skipped = int((~ok).sum())
         if self.eligible.size == 0:
-            raise ArtifactError("no sample is eligible: lengths must be multiples of the block size and fit seq_len")
+            raise ArtifactError("no sample is eligible: lengths must be multiples of the block size, fit seq_len and give "
+                                "every block-parallel rank a block")
         self.batch_size, self.dp_rank, self.dp_size = batch_size, dp_rank, dp_size
         self.shuffle, self.seed = shuffle, seed
         self.epoch, self.cursor = 0, 0
@@ -409,4 +417,6 @@ def build_artifact_runtime(spec, *, device, dp_rank: int, dp_size: int) -> DataR
         minimum_sequence_length=spec.data.minimum_sequence_length, seed=spec.launch.seed,
         optimizer_step_unit=spec.data.optimizer_step_unit,
         terminal_turn_weight=spec.data.trajectory_terminal_turn_weight,
-        group_by_supervision_start=spec.objective.name == "diffusiongemma_native_sft", **common)
+        group_by_supervision_start=spec.objective.name == "diffusiongemma_native_sft",
+        context_parallel_size=spec.topology.context_parallel_size, block_parallel_size=spec.topology.block_parallel_size,
+        **common)
