@@ -119,3 +119,44 @@ def test_shared_dense_branch_and_replayed_routes():
     assert [s[:2] for s in seen] == [(True, False), (False, True)] and torch.equal(seen[0][2], seen[1][2])
     assert not any(isinstance(k, tuple) and k[1] == "moe_route" for k in m.store.kept)
     assert m.flat.params["layers.0.w_gate_up"].main_grad.abs().sum() > 0
+
+
+def _ep_checkpoint(rank, world, src, out):
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.models.export import export_moe_checkpoint
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    torch.set_num_threads(2)
+    spec = RunSpec.from_mapping({
+        "model": {"id": src, "seq_len": 128, "dtype": "fp32", "family": "diffusion_gemma"},
+        "objective": {"name": "standard_block_diffusion", "block_size": 32},
+        "training": {"batch_size": 1, "steps": 1},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1, "expert_parallel_size": 2}}).validate(world_size=world)
+    s = TrainingSession(spec, device="cpu", runtime=build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world))
+    bank = s.model.layers[1].experts
+    export_moe_checkpoint(s.model, out)
+    return bank.ep_rank, bank.e_local, bank.w_down.detach().clone()
+
+
+@pytest.mark.distributed
+def test_expert_parallel_ranks_load_their_experts_and_export_all(tmp_path):
+    """From one checkpoint, each expert-parallel rank loads its own experts; exporting from the two ranks writes the
+    file back tensor for tensor."""
+    from safetensors import safe_open
+
+    from turbo_dllm_b200.models.config import PRESETS
+    from turbo_dllm_b200.models.export import export_moe_checkpoint
+    from turbo_dllm_b200.models.moe import MoEBlockDiffusionTransformer
+
+    full = MoEBlockDiffusionTransformer(PRESETS["synthetic:tiny-moe"], dtype=torch.float32, device="cpu", seed=4, init_std=0.05)
+    src, out = str(tmp_path / "src"), str(tmp_path / "out")
+    export_moe_checkpoint(full, src)
+    res = run_ranks(_ep_checkpoint, 2, args=(src, out), deadline_s=240)
+    for ep_rank, e_local, w_down in res:
+        want = full.layers[1].experts.w_down[ep_rank * e_local:(ep_rank + 1) * e_local]
+        assert e_local == 4 and torch.equal(torch.as_tensor(w_down), want)
+    with safe_open(src + "/model.safetensors", framework="pt") as a, safe_open(out + "/model.safetensors", framework="pt") as b:
+        assert set(a.keys()) == set(b.keys())
+        for k in a.keys():
+            assert torch.equal(a.get_tensor(k), b.get_tensor(k)), k

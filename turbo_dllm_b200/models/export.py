@@ -72,18 +72,42 @@ def export_moe_checkpoint(model, path: str) -> str:
             layer.lora = None
             layer.experts.lora = None
         model.lora = None
-    os.makedirs(path, exist_ok=True)
     from .hf_loader import _apply_partial_rotary_order
 
+    bank0 = model.layers[0].experts
+    experts = None
+    if bank0.ep > 1:
+        # expert parallelism: every rank of the expert group calls this; the experts are gathered in global order
+        # (rank r owns experts [r * E_local, (r + 1) * E_local)) and the first rank of the group writes
+        import torch.distributed as dist
+
+        experts = []
+        for layer in model.layers:
+            b = layer.experts
+            gu = [torch.empty_like(b.w_gu) for _ in range(b.ep)]
+            dn = [torch.empty_like(b.w_down) for _ in range(b.ep)]
+            dist.all_gather(gu, b.w_gu.detach().contiguous(), group=b.ep_group)
+            dist.all_gather(dn, b.w_down.detach().contiguous(), group=b.ep_group)
+            experts.append((torch.cat(gu).cpu(), torch.cat(dn).cpu()))
+        if bank0.ep_rank != 0:
+            dist.barrier(group=bank0.ep_group)
+            return path
+    os.makedirs(path, exist_ok=True)
     _apply_partial_rotary_order(model, inverse=True)
     try:
-        return _write_moe_checkpoint(model, cfg, path)
+        return _write_moe_checkpoint(model, cfg, path, experts)
     finally:
         _apply_partial_rotary_order(model, inverse=False)
+        if experts is not None:
+            import torch.distributed as dist
+
+            dist.barrier(group=bank0.ep_group)
 
 
 @torch.no_grad()
-def _write_moe_checkpoint(model, cfg, path: str) -> str:
+def _write_moe_checkpoint(model, cfg, path: str, experts=None) -> str:
+    """experts: per layer (gate_up [E, 2I, H], down [E, H, I]) gathered over the expert-parallel ranks, or None when this
+    rank holds every expert."""
     from safetensors.torch import save_file
 
     from .hf_loader import deinterleave_gate_up, hf_config_dict
@@ -104,10 +128,11 @@ def _write_moe_checkpoint(model, cfg, path: str) -> str:
         if layer.q_norm is not None:
             out[p + "self_attn.q_norm.weight"], out[p + "self_attn.k_norm.weight"] = layer.q_norm, layer.k_norm
         out[p + "mlp.router.weight"] = layer.experts.router
-        for e in range(layer.experts.w_gu.shape[0]):
-            g, u = deinterleave_gate_up(layer.experts.w_gu[e])
+        w_gu, w_down = experts[i] if experts is not None else (layer.experts.w_gu, layer.experts.w_down)
+        for e in range(w_gu.shape[0]):
+            g, u = deinterleave_gate_up(w_gu[e])
             q = p + f"mlp.experts.{e}."
-            out[q + "gate_proj.weight"], out[q + "up_proj.weight"], out[q + "down_proj.weight"] = g, u, layer.experts.w_down[e]
+            out[q + "gate_proj.weight"], out[q + "up_proj.weight"], out[q + "down_proj.weight"] = g, u, w_down[e]
     save_file({k: v.detach().cpu().contiguous() for k, v in out.items()}, os.path.join(path, "model.safetensors"))
     c = hf_config_dict(cfg)
     c.update({"num_experts": cfg.num_experts, "num_experts_per_tok": cfg.num_experts_per_token,
