@@ -61,6 +61,7 @@ def _run(rank, world, backend, tp, tmp):
         for _ in range(2):
             b.step()
         ck.save_training_checkpoint(tmp, b, step=2, rank=rank, world_size=world, control_group=dist.group.WORLD)
+        out["saved_params"] = full(b)
         c = session()
         meta = ck.load_training_checkpoint(tmp, "latest", c, rank=rank, world_size=world)
         for _ in range(2):
@@ -81,6 +82,15 @@ def test_fsdp2_matches_replicated_parameters_and_resumes(tmp_path):
         assert o["resumed_equal"] and o["backend"] == "fsdp_sharded_rank_local"
         assert o["shard_fraction"] < 0.56          # about half of the parameters per rank (padding to 128)
     assert (out[0]["params"] == out[1]["params"]).all()
+    # one process reads the two ranks' parameter slices back into a whole model and exports it
+    from turbo_dllm_b200.models.export import export_training_checkpoint
+    from turbo_dllm_b200.models.hf_loader import load_hf_config, load_hf_weights
+    from turbo_dllm_b200.models.dense import BlockDiffusionTransformer
+
+    export_training_checkpoint(_spec("fsdp", 2, 1, str(tmp_path / "ck")), str(tmp_path / "ck"), str(tmp_path / "hf"))
+    model = BlockDiffusionTransformer(load_hf_config(str(tmp_path / "hf")), dtype=torch.float32, seed=0)
+    load_hf_weights(model, str(tmp_path / "hf"))
+    assert torch.equal(model.flat.data, torch.from_numpy(out[0]["saved_params"]))
 
 
 @pytest.mark.distributed

@@ -135,6 +135,17 @@ def _async_save(rank, world, tmp):
 def test_async_save_is_deferred_and_snapshots_the_state_of_its_step(tmp_path):
     for latest, same in run_ranks(_async_save, 2, args=(str(tmp_path / "ck"),), deadline_s=180):
         assert latest == "step_00000001" and same
+    # one process reads the weights of the two-rank checkpoint (replicated parameters: rank 0's file has them all);
+    # the full loader still refuses the other world size
+    import turbo_dllm_b200.checkpoint as ck
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    t = TrainingSession(_spec(), device="cpu")
+    with pytest.raises(ValueError, match="written by 2 ranks"):
+        ck.load_training_checkpoint(str(tmp_path / "ck"), "latest", t, rank=0, world_size=1)
+    out = ck.load_model_weights(str(tmp_path / "ck"), "latest", t)
+    payload = torch.load(os.path.join(str(tmp_path / "ck"), out["tag"], ck.shard_name(0, 2)), weights_only=False)
+    assert out["step"] == 1 and torch.equal(t.model.flat.data, payload["model"])
 
 
 def test_an_older_tag_is_checked_against_its_own_topology(tmp_path):

@@ -471,6 +471,53 @@ def load_training_checkpoint(directory: str, tag: str, session, *, rank: int, wo
     return {"step": cs["step"], "tag": tag, "metadata": meta}
 
 
+def load_model_weights(directory: str, tag: str, session) -> dict:
+    """Weights (and adapters) only, on ONE process, from a checkpoint written by any number of ranks: for export and
+    evaluation after a multi-GPU run. Works when the saved ranks together hold plain copies or plain slices of the
+    weights: replicated parameters (data / context / block parallelism with a sharded optimizer: rank 0's file has
+    them all) and parameter sharding (`optimizer.backend: fsdp`: every rank's slice of every unit is put back in
+    place). Tensor- or expert-parallel checkpoints are exported by a job of the same shape instead (the export gathers
+    over those groups). Optimizer, scheduler, data and RNG state are not restored."""
+    meta = read_metadata(directory)
+    tag = resolve_tag(directory, tag)
+    if meta.get("checkpoint_backend") == "adapter_model_only" and tag == meta.get("latest_tag"):
+        return {**load_model_only_checkpoint(directory, tag, session), "metadata": meta}
+    world = int(meta["world_size"])
+    topo = meta.get("topology", {})
+    if int(topo.get("tensor_parallel_size", 1)) > 1 or int(topo.get("expert_parallel_size", 1)) > 1:
+        raise ValueError("the checkpoint holds tensor- or expert-parallel shards: run the export as a job of the same "
+                         f"shape ({world} ranks), which gathers them")
+
+    def shard(r):
+        path = os.path.join(directory, tag, shard_name(r, world))
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"missing checkpoint shard {path}")
+        return torch.load(path, map_location="cpu", weights_only=False)
+
+    first = shard(0)
+    flat = session.model.flat
+    if first["model"].numel() == flat.data.numel():
+        flat.data.copy_(first["model"].to(flat.data.device, flat.data.dtype))
+    else:
+        from ..parallel.fsdp import plan_units
+
+        units = plan_units(flat, world)
+        if first["model"].numel() != sum(u.shard for u in units):
+            raise ValueError(f"rank 0 of the checkpoint holds {first['model'].numel()} parameter values; neither the whole "
+                             f"model ({flat.data.numel()}) nor its 1/{world} parameter shard")
+        for r in range(world):
+            part = (first if r == 0 else shard(r))["model"]
+            for u in units:
+                lo = u.start + r * u.shard
+                n = max(0, min(u.shard, u.stop - lo))
+                if n:
+                    flat.data[lo:lo + n].copy_(part[u.local:u.local + n].to(flat.data.device, flat.data.dtype))
+    lora = getattr(session, "lora", None)
+    if lora is not None and "adapter" in first:
+        lora.flat.data.copy_(first["adapter"].to(lora.flat.data.device, lora.flat.data.dtype))
+    return {"step": first["client_state"]["step"], "tag": tag, "metadata": meta}
+
+
 def _kernel_metadata() -> dict:
     try:
         from ..kernels import native

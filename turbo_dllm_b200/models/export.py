@@ -41,9 +41,21 @@ def export_training_checkpoint(spec, checkpoint_dir: str, output: str, tag: str 
     from ..training.session import TrainingSession
     from .hf_loader import export_hf_checkpoint
 
-    session = TrainingSession(spec, device="cpu" if spec.model.dtype == "fp32" or not torch.cuda.is_available()
-                              else "cuda")
-    meta = load_training_checkpoint(checkpoint_dir, tag, session, rank=0, world_size=1, restore_rng=False)
+    from ..checkpoint import load_model_weights, read_metadata
+
+    device = "cpu" if spec.model.dtype == "fp32" or not torch.cuda.is_available() else "cuda"
+    if int(read_metadata(checkpoint_dir)["world_size"]) > 1:
+        # written by several ranks, exported by one process: the model is rebuilt on one rank (no parallel axes) and
+        # only the weights are read, from rank 0's file or from every rank's parameter slices
+        solo = spec.with_overrides({"topology": {"context_parallel_size": 1, "block_parallel_size": 1,
+                                                 "tensor_parallel_size": 1, "expert_parallel_size": 1,
+                                                 "sequence_parallel": False},
+                                    "optimizer": {"backend": "auto"}})
+        session = TrainingSession(solo, device=device)
+        meta = load_model_weights(checkpoint_dir, tag, session)
+    else:
+        session = TrainingSession(spec, device=device)
+        meta = load_training_checkpoint(checkpoint_dir, tag, session, rank=0, world_size=1, restore_rng=False)
     from ..adapters.lora import lora_merge_plan
 
     plan = lora_merge_plan(session.model)        # validated before anything is merged or written
