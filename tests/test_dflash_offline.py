@@ -241,3 +241,29 @@ def test_speculators_checkpoint_round_trip(tmp_path):
     other = TrainingSession(_spec("online").with_overrides({"model": {"intermediate_size": 128}}).validate(), device="cpu")
     with pytest.raises(ValueError, match="checkpoint shape"):
         load_speculators_checkpoint(other.model, out)
+
+
+def test_export_command_from_a_training_checkpoint(tmp_path, capsys):
+    import json
+
+    import yaml
+
+    from turbo_dllm_b200.checkpoint import save_training_checkpoint
+    from turbo_dllm_b200.cli.dflash import run_dflash
+
+    spec = _spec("online")
+    s = TrainingSession(spec, device="cpu")
+    s.step()
+    save_training_checkpoint(str(tmp_path / "ck"), s, step=1, rank=0, world_size=1)
+    (tmp_path / "draft.yaml").write_text(yaml.safe_dump(spec.to_dict()))
+    for fmt, must_have in (("native", "dflash_config.json"), ("speculators", "config.json")):
+        out = str(tmp_path / fmt)
+        assert run_dflash(["export", "--config", str(tmp_path / "draft.yaml"), "--checkpoint", str(tmp_path / "ck"),
+                           "--output", out, "--format", fmt]) == 0
+        files = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["files"]
+        assert must_have in files and "model.safetensors" in files
+    from safetensors import safe_open
+
+    with safe_open(str(tmp_path / "native" / "model.safetensors"), framework="pt") as f:
+        assert torch.equal(f.get_tensor("fc"), s.model.flat.params["fc"])
+    assert run_dflash(["validate-export", str(tmp_path / "native")]) == 0

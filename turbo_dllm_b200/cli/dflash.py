@@ -108,12 +108,18 @@ def run_dflash(argv) -> int:
             print(json.dumps({"output": a.output, "draft_vocab_size": dv.size, "token_coverage": covered}))
             return 0
         if a.cmd == "export":
-            from ..checkpoint import load_training_checkpoint
+            from ..checkpoint import load_model_weights, load_training_checkpoint, read_metadata
             from ..training.session import TrainingSession
 
             spec = load_run_spec(a.config).validate()
-            s = TrainingSession(spec)
-            load_training_checkpoint(a.checkpoint, "latest", s, rank=0, world_size=1, restore_rng=False)
+            if int(read_metadata(a.checkpoint)["world_size"]) > 1:
+                # a drafter trained on several ranks: the weights are replicated, one process reads rank 0's file
+                spec = spec.with_overrides({"topology": {"context_parallel_size": 1, "block_parallel_size": 1}})
+                s = TrainingSession(spec)
+                load_model_weights(a.checkpoint, "latest", s)
+            else:
+                s = TrainingSession(spec)
+                load_training_checkpoint(a.checkpoint, "latest", s, rank=0, world_size=1, restore_rng=False)
             if a.format == "speculators":
                 man = ex.export_speculators_checkpoint(s.model, s.task.target, spec, a.output)
             else:
