@@ -174,3 +174,36 @@ def test_kernels_with_a_fixed_reduction_order_repeat_bit_for_bit(monkeypatch):
     assert torch.equal(grads[0][0], grads[1][0])
     if grads[0][1] is not None:
         assert torch.equal(grads[0][1], grads[1][1])
+
+
+@pytest.mark.gpu
+@pytest.mark.performance
+def test_bf16_gemm_throughput_is_recorded():
+    """Performance tier: records the tcgen05 GEMM's throughput beside the library GEMM's on the same shape; asserts only
+    that the figures are sane (no hardware baseline is encoded: clocks and power caps differ between machines)."""
+    import json
+
+    from turbo_dllm_b200.ops.gemm import gemm
+
+    M = N = K = 8192
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+
+    def time(fn, iters=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(iters):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / iters * 1e-3
+
+    ours = 2.0 * M * N * K / time(lambda: gemm(a, b, out=out)) / 1e12
+    library = 2.0 * M * N * K / time(lambda: torch.matmul(a, b.t(), out=out)) / 1e12
+    print(json.dumps({"event": "performance", "shape": [M, N, K], "tcgen05_gemm_tflops": round(ours, 1),
+                      "library_gemm_tflops": round(library, 1)}))
+    assert ours > 0 and library > 0

@@ -554,3 +554,19 @@ def test_tensor_parallel_ranks_load_their_shards_and_export_the_whole(tmp_path):
             assert set(a.keys()) == set(b.keys())
             for k in a.keys():
                 assert torch.equal(a.get_tensor(k), b.get_tensor(k)), (kind, k)
+
+
+def test_model_inspector(tmp_path, capsys):
+    from turbo_dllm_b200.benchmarks.inspect_models import main, summarize
+    from turbo_dllm_b200.models.config import PRESETS
+    from turbo_dllm_b200.models.dense import BlockDiffusionTransformer
+    from turbo_dllm_b200.models.hf_loader import export_hf_checkpoint
+
+    s = summarize("synthetic:qwen3-8b")
+    assert s["family"] == "causal_lm" and 8.1e9 < s["parameters"] < 8.3e9 and s["attention_path"].startswith("fused")
+    assert 0.3 < s["attention_share_of_flops"] < 0.5
+    export_hf_checkpoint(BlockDiffusionTransformer(PRESETS["synthetic:tiny-qwen3"], dtype=torch.float32), str(tmp_path / "hf"))
+    assert main([str(tmp_path / "hf"), "--json", "--seq-len", "256", "--block-size", "16"]) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["source"] == "checkpoint directory" and rep["hidden_size"] == PRESETS["synthetic:tiny-qwen3"].hidden_size
+    assert main(["nowhere"]) == 2
