@@ -570,3 +570,41 @@ def test_model_inspector(tmp_path, capsys):
     rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert rep["source"] == "checkpoint directory" and rep["hidden_size"] == PRESETS["synthetic:tiny-qwen3"].hidden_size
     assert main(["nowhere"]) == 2
+
+
+def test_flop_models_count_exactly_what_the_masks_allow():
+    """The pair counters equal the number of visible entries of the dense masks (full prefix and sliding window), and
+    the drafter-distillation model adds up its parts."""
+    import dataclasses
+
+    from turbo_dllm_b200.models.config import PRESETS
+    from turbo_dllm_b200.ops.attention import block_diffusion_layout
+    from turbo_dllm_b200.profiling.perf import (block_diffusion_pairs, dflash_step_flops, model_attention_pairs,
+                                                transformer_step_flops)
+
+    L, bs = 96, 16
+    pos = torch.arange(L)
+    for views in (1, 2):
+        npos = pos.repeat(views)
+        ngrp = (pos // bs).repeat(views) + torch.arange(views).repeat_interleave(L) * (L // bs)
+        for window in (None, 40, 16):
+            lay = block_diffusion_layout(npos, ngrp, pos, bs, window=window)
+            assert int(lay.dense_mask().sum()) == block_diffusion_pairs(L, bs, views, window), (views, window)
+    cfg = dataclasses.replace(PRESETS["synthetic:tiny-qwen3"], num_layers=4, sliding_window=40, sliding_window_pattern=2)
+    want = (2 * block_diffusion_pairs(L, bs, 1, 40) + 2 * block_diffusion_pairs(L, bs, 1)) / 4
+    assert model_attention_pairs(cfg, L, bs) == want
+    full = dataclasses.replace(cfg, sliding_window=None)
+    a = transformer_step_flops(cfg, rows=2 * L, pairs=model_attention_pairs(cfg, L, bs), vocab_rows=L)
+    b = transformer_step_flops(full, rows=2 * L, pairs=model_attention_pairs(full, L, bs), vocab_rows=L)
+    assert a.attention < b.attention and a.dense == b.dense
+    draft, target = PRESETS["synthetic:dflash-draft-5l"], PRESETS["synthetic:qwen3-8b"]
+    kw = dict(seq_len=4096, block_size=16, anchors=128, num_target_layers=5)
+    online = dflash_step_flops(draft, target, **kw)
+    offline = dflash_step_flops(draft, target, online_target=False, **kw)
+    ce = dflash_step_flops(draft, target, loss="paper_ce", **kw)
+    small = dflash_step_flops(draft, target, draft_vocab_size=32000, **kw)
+    # the frozen 36-layer target forward dominates an online step; it is 2 FLOPs per weight and row
+    per_row = target.hidden_size * target.qkv_dim + target.q_dim * target.hidden_size + 3 * target.hidden_size * target.intermediate_size
+    assert online.dense - offline.dense == pytest.approx(2.0 * 4096 * per_row * 36)
+    assert online.head - ce.head == pytest.approx(2.0 * 128 * 16 * target.hidden_size * target.vocab_size)
+    assert small.head < online.head and dflash_step_flops(draft, target, batch=3, **kw).total == pytest.approx(3 * online.total)

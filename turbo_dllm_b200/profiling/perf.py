@@ -44,13 +44,29 @@ def measured_peaks(path: str | None = None) -> dict | None:
 
 
 def block_diffusion_pairs(seq_len: int, block_size: int, noisy_views: int = 1, window: int | None = None) -> int:
-    """Visible (query, key) pairs of one sequence: every noisy view sees its own block plus the clean
-    blocks before it; the clean copy is block-causal."""
+    """Exactly visible (query, key) pairs of one sequence: every noisy row sees its own block plus the clean tokens
+    before it, a clean row the clean tokens up to the end of its block. With `window` (sliding-window layers) the
+    clean part of both is cut to the last `window` positions before that point (`ops/attention.py::block_diffusion_layout`)."""
     B = seq_len // block_size
-    bs2 = block_size * block_size
-    noisy = bs2 * B * (B + 1) // 2          # own block (B·bs²) + clean prefix (bs²·B(B-1)/2)
-    clean = bs2 * B * (B + 1) // 2
+    bs = block_size
+    if window is None:
+        noisy = bs * bs * B * (B + 1) // 2          # own block (B·bs²) + clean prefix (bs²·B(B-1)/2)
+        clean = bs * bs * B * (B + 1) // 2
+        return noisy_views * noisy + clean
+    noisy = sum(bs * (bs + min(b * bs, window)) for b in range(B))
+    clean = sum(bs * min((b + 1) * bs, window) for b in range(B))
     return noisy_views * noisy + clean
+
+
+def model_attention_pairs(cfg: ModelConfig, seq_len: int, block_size: int, noisy_views: int = 1) -> float:
+    """Visible pairs per layer, averaged over the layers (sliding-window layers see fewer): the `pairs` argument of
+    `transformer_step_flops` for one sequence."""
+    full = block_diffusion_pairs(seq_len, block_size, noisy_views)
+    if not cfg.has_sliding_layers:
+        return float(full)
+    win = block_diffusion_pairs(seq_len, block_size, noisy_views, cfg.sliding_window)
+    n_win = sum(cfg.layer_window(i) is not None for i in range(cfg.num_layers))
+    return (n_win * win + (cfg.num_layers - n_win) * full) / cfg.num_layers
 
 
 @dataclass(frozen=True)
@@ -93,3 +109,44 @@ def transformer_step_flops(cfg: ModelConfig, *, rows: int, pairs: int, vocab_row
 def model_flops_utilization_pct(flops_per_step: float, step_seconds: float, world_size: int,
                                 peak_tflops: float) -> float:
     return 100.0 * flops_per_step / (step_seconds * world_size * peak_tflops * 1e12)
+
+
+def causal_pairs(seq_len: int) -> int:
+    return seq_len * (seq_len + 1) // 2
+
+
+def dflash_step_flops(draft: ModelConfig, target: ModelConfig, *, seq_len: int, block_size: int, anchors: int,
+                      num_target_layers: int, batch: int = 1, online_target: bool = True, supervised_rows: int | None = None,
+                      mean_context: float | None = None, loss: str = "speculators_kl", context_rows: int | None = None,
+                      draft_vocab_size: int | None = None) -> StepFlops:
+    """Model FLOPs of one drafter-distillation step on `batch` sequences (Megatron convention: 2 per multiply-add,
+    trainable matrices x3 for forward + both gradients, frozen ones x1 forward, or x2 where only the input gradient
+    is taken). Parts: the frozen target's causal forward (online features only); the conditioning projection of the
+    tapped target layers on the context rows; the drafter's layers on `anchors * block_size` draft rows with K|V
+    projections on draft + context rows; attention of every draft row over its own block and its context
+    (`mean_context` keys on average: half the sequence for uniform anchors); the frozen head on the supervised rows
+    (student forward + input gradient, teacher forward for the KL loss).
+    Counterpart of DFlashTransformerFlops (dllm_parallel/core/profiling/perf.py:630-852)."""
+    L, bs = seq_len, block_size
+    rows_d = anchors * bs
+    rows_c = L if context_rows is None else context_rows
+    sup = rows_d if supervised_rows is None else supervised_rows
+    ctx = L / 2.0 if mean_context is None else mean_context
+    V = draft_vocab_size or target.vocab_size
+    h, ht = draft.hidden_size, target.hidden_size
+    dense = 0.0
+    attention = 0.0
+    if online_target:
+        per_row = ht * target.qkv_dim + target.q_dim * ht + 3 * ht * target.intermediate_size
+        dense += 2.0 * L * per_row * target.num_layers
+        attention += 4.0 * causal_pairs(L) * target.q_dim * target.num_layers
+    dense += 6.0 * rows_c * (num_target_layers * ht) * h                       # conditioning projection
+    per_draft_row = h * draft.q_dim + draft.q_dim * h + 3 * h * draft.intermediate_size
+    per_key_row = h * 2 * draft.kv_dim
+    dense += 6.0 * draft.num_layers * (rows_d * per_draft_row + (rows_d + rows_c) * per_key_row)
+    attention += 12.0 * rows_d * (bs + ctx) * draft.q_dim * draft.num_layers
+    head = 4.0 * sup * h * V                                                    # student logits and their input gradient
+    if loss == "speculators_kl":
+        head += 2.0 * sup * ht * V                                              # teacher logits
+    return StepFlops(dense * batch, attention * batch, head * batch)
+

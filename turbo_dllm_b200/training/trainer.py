@@ -23,7 +23,7 @@ import torch
 import torch.distributed as dist
 
 from ..config.run_spec import RunSpec, RunSpecError, build_run_spec_arg_parser, run_spec_from_args
-from ..profiling.perf import (block_diffusion_pairs, hardware_peak_tflops, model_flops_utilization_pct,
+from ..profiling.perf import (hardware_peak_tflops, model_attention_pairs, model_flops_utilization_pct,
                               transformer_step_flops)
 from . import checkpointing as ckpt_policy
 from .fault_tolerance import install_fault_handlers, write_fatal_marker
@@ -214,10 +214,21 @@ def run_training(spec: RunSpec) -> dict:
         if rank == 0:
             views = getattr(session.objective, "views", 1)
             gb = spec.global_batch(dp)
-            fl = transformer_step_flops(
-                session.cfg, rows=(views + 1) * spec.model.seq_len * gb,
-                pairs=block_diffusion_pairs(spec.model.seq_len, spec.objective.block_size, views) * gb,
-                vocab_rows=gb * spec.model.seq_len)
+            if session.task is not None:       # drafter distillation: drafter + frozen target + frozen head
+                from ..profiling.perf import dflash_step_flops
+
+                task = session.task
+                fl = dflash_step_flops(
+                    session.cfg, task.target.cfg, seq_len=spec.model.seq_len,
+                    block_size=task.objective.block_size, anchors=task.objective.max_anchors,
+                    num_target_layers=len(spec.model.target_layer_ids), batch=gb,
+                    online_target=spec.data.target_features == "online", loss=spec.objective.dflash_loss,
+                    draft_vocab_size=task.draft_vocab.size if task.draft_vocab is not None else None)
+            else:
+                fl = transformer_step_flops(
+                    session.cfg, rows=(views + 1) * spec.model.seq_len * gb,
+                    pairs=model_attention_pairs(session.cfg, spec.model.seq_len, spec.objective.block_size, views) * gb,
+                    vocab_rows=gb * spec.model.seq_len)
             mfu = None
             if use_cuda and mean_ms == mean_ms:
                 try:
