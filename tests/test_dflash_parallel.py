@@ -40,12 +40,12 @@ def _run(rank, world, cp, bp, mode, steps=2, dflash2=False):
 
 
 @pytest.mark.distributed
-@pytest.mark.parametrize("cp,bp,mode", [(2, 2, "kv_pull"), (2, 2, "query_rotation"), (1, 2, "auto")])
+@pytest.mark.parametrize("cp,bp,mode", [(2, 2, "kv_pull"), (2, 2, "query_rotation"), (1, 2, "auto"), (2, 1, "auto")])
 def test_dflash_replica_over_two_ranks_matches_single_process(cp, bp, mode):
     ref_losses, ref_params, _ = _run(0, 1, 1, 1, "auto")
     outs = run_ranks(_run, 2, args=(cp, bp, mode), deadline_s=240)
     for losses, params, used in outs:
-        assert used == (mode if cp > 1 else "local")
+        assert used == ("local" if cp == 1 else "kv_pull" if bp == 1 else mode)
         assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-5)
         assert_params_close(params, ref_params)
 

@@ -190,7 +190,6 @@ class RunSpec:
                 ("optimizer", "zero_contiguous_gradients", True, "gradients always live in one contiguous buffer"),
                 ("optimizer", "zero_overlap_comm", True, "the fused step orders its own phases"),
                 ("optimizer", "allow_deepspeed_op_build", False, "no DeepSpeed ops are built or used"),
-                ("optimizer", "fsdp_mixed_precision", None, "parameter shards are bf16 with fp32 gradients and master weights"),
                 ("optimizer", "fsdp_sharding_strategy", "full_shard", "parameter sharding is always full sharding over the data-parallel group"),
                 ("optimizer", "fsdp_use_orig_params", True, "parameters are views of flat buffers"),
                 ("kernel", "ring_attention_key_chunk_size", 0, "key tiles are streamed by the attention kernel itself"),
@@ -204,6 +203,9 @@ class RunSpec:
                  and opt.backend not in ("fsdp", "fsdp2") and self.adapter.type != "lora",
                  "training.activation_checkpointing_scope=mlp is built for the dense decoder without tensor parallelism, "
                  "parameter sharding or adapters; use 'full'")
+        need(opt.fsdp_mixed_precision in (None, "bf16"),
+             f"optimizer.fsdp_mixed_precision={opt.fsdp_mixed_precision!r}: parameter shards are bf16 with fp32 gradients "
+             "and master weights (leave it unset, or 'bf16')")
         need(self.kernel.mlp_token_chunk_size >= 0 and self.kernel.mlp_token_chunk_size % 128 == 0,
              "kernel.mlp_token_chunk_size must be 0 (off) or a multiple of 128 rows")
         if self.kernel.mlp_token_chunk_size:
@@ -219,10 +221,11 @@ class RunSpec:
                  "model.draft_vocab_path (a drafter over a subset of the verifier's vocabulary) is built for the DFlash "
                  "drafter with objective.dflash_loss speculators_kl or paper_ce")
         if o.name == "dflash_distillation":
-            need(cp == 1 or cp == bp, "dflash_distillation divides anchors and context rows over the same ranks: "
-                                      "context_parallel_size must be 1 or equal block_parallel_size")
+            need(cp == 1 or bp == 1 or cp == bp,
+                 "dflash_distillation divides anchors (block parallelism) and context rows (context parallelism) over the "
+                 "ranks of one replica: context_parallel_size and block_parallel_size must be equal, or one of them 1")
             need(t.tensor_parallel_size == 1, "dflash_distillation has no tensor-parallel drafter")
-            n_rep = max(cp, bp)
+            n_rep = bp
             if o.max_anchors:
                 need(o.max_anchors % n_rep == 0, f"objective.max_anchors ({o.max_anchors}) must divide by the "
                                                  f"{n_rep} ranks of a replica")
@@ -235,7 +238,9 @@ class RunSpec:
             need((self.adapter.rank or 0) > 0, "adapter.rank must be positive for LoRA")
             bad = sorted(set(self.adapter.targets) - {"attention", "mlp", "experts"})
             need(not bad, f"adapter.targets has unknown roles: {bad}")
-        if self.data.input_mode == "dataset":
+        if self.data.input_mode == "dataset" and not (o.name == "dflash_distillation"
+                                                       and self.data.target_features in ("offline", "synthetic")):
+            # (a drafter trained from stored or synthetic target features takes its token ids from there)
             need(bool(self.data.dataset_path), "data.input_mode=dataset needs data.dataset_path (a prepared artifact "
                                                "directory, a flat token file, or a text file)")
         ck = self.checkpointing
@@ -267,9 +272,37 @@ class RunSpec:
                 infer_data_parallel_size(world_size, self)
             except ValueError as e:
                 problems.append(str(e))
+        if not problems:
+            # what the model family's executor cannot run (e.g. a parallel axis it does not build) is a problem of
+            # the run spec too: `dllm config validate` reports it, not only the training start
+            problems += self._family_problems(world_size)
         if problems:
             raise RunSpecError("invalid run spec:\n  - " + "\n  - ".join(problems))
         return self
+
+    def _family_problems(self, world_size: int | None) -> list[str]:
+        from ..models.config import PRESETS
+        from ..models.registry import executor_for_family, infer_family
+
+        m = self.model
+        fam = m.family
+        if fam in ("auto", "hf"):
+            if self.objective.name == "dflash_distillation":
+                fam = "dflash"
+            else:
+                cfg = PRESETS.get(m.id)
+                if cfg is None and (m.num_experts or m.full_attention_interval):
+                    fam = "diffusion_gemma" if m.num_experts else "qwen3_8"
+                elif cfg is not None and (cfg.is_hybrid or m.full_attention_interval):
+                    fam = "qwen3_8"
+                elif cfg is not None and (cfg.is_moe or m.num_experts):
+                    fam = "diffusion_gemma"
+                else:
+                    fam = (cfg.family if cfg is not None and cfg.family != "causal_lm" else None) or infer_family(m.id, self.objective.name)
+        try:
+            return list(executor_for_family(fam).validate_run_spec(self, world_size))
+        except ValueError as e:
+            return [str(e)]
 
     # ------------------------------------------------------------ conveniences
     @property

@@ -89,11 +89,16 @@ class DraftAttentionPlan:
 
 
 class DFlashContextParallel:
-    def __init__(self, group, *, context_sharded: bool, mode: str = "auto"):
+    def __init__(self, group, *, context_sharded: bool, mode: str = "auto", anchors_sharded: bool = True):
+        """anchors_sharded=False (context parallelism without block parallelism): every rank of the replica keeps all
+        anchors and only the context rows are divided; the ranks then pull the other shards' K|V, compute the same
+        draft rows, and the loss of each is divided by the summed weights of all of them, so that the summed
+        gradients are those of one rank."""
         self.group = group
         self.n = dist.get_world_size(group)
         self.me = dist.get_rank(group)
         self.context_sharded = bool(context_sharded) and self.n > 1
+        self.anchors_sharded = bool(anchors_sharded)
         if mode not in ("auto", "kv_pull", "query_rotation"):
             raise ValueError("kernel.dflash_context_exchange must be auto, kv_pull or query_rotation")
         self.mode = mode
@@ -101,6 +106,8 @@ class DFlashContextParallel:
 
     # --------------------------------------------------------------- ownership
     def anchor_index(self, anchors: int, rank: int | None = None, device="cpu") -> torch.Tensor:
+        if not self.anchors_sharded:
+            return torch.arange(anchors, device=device)
         if anchors % self.n:
             raise ValueError(f"objective.max_anchors ({anchors}) must divide by the {self.n} ranks of a replica")
         return torch.arange(self.me if rank is None else rank, anchors, self.n, device=device)
@@ -132,6 +139,11 @@ class DFlashContextParallel:
         shard = [code(self.context_positions(seq_len, r, dev)) for r in range(self.n)]
         counts = [int(s.numel()) for s in shard]
         mode = self.mode
+        if not self.anchors_sharded:
+            if mode == "query_rotation":
+                raise ValueError("kernel.dflash_context_exchange=query_rotation moves the queries of the ranks' own "
+                                 "anchors; without block parallelism every rank has all anchors: use kv_pull or auto")
+            mode = "kv_pull"
         if mode == "auto":
             mode = ("query_rotation" if prefer_query_rotation(
                 draft_rows=nd, context_rows_per_rank=max(counts), ranks=self.n, q_heads=q_heads, kv_heads=kv_heads,

@@ -228,6 +228,7 @@ class TrainingSession:
 
             exchange = DFlashContextParallel(runtime.group("local_parallel"),
                                              context_sharded=runtime.context_parallel_size > 1,
+                                             anchors_sharded=runtime.block_parallel_size > 1,
                                              mode=spec.kernel.dflash_context_exchange)
         self.task = DFlashTask(spec, self.cfg, dtype=self.dtype, device=self.device, seed=seed, dp_rank=dp_rank,
                                exchange=exchange, replicas=self.dp_size if runtime is not None else None)
