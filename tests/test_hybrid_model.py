@@ -314,3 +314,49 @@ def test_head_shards_partition_the_projection_and_plan_checks_coverage():
         HeadParallelPlan(group=None, index=0, noisy_blocks=[blocks, blocks],
                          clean_positions=[torch.arange(0, 8), torch.arange(0, 8)], batch=1, seq_len=16,
                          block_size=8, device="cpu")
+
+
+def _hybrid_tp_cp_run(rank, world, tp, cp, bp, sp, steps=2):
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    torch.set_num_threads(2)
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-qwen3_8", "family": "qwen3_8", "seq_len": 128, "dtype": "fp32",
+                  "linear_num_key_heads": 4, "linear_num_value_heads": 8},
+        "objective": {"name": "fast_dllm_v2", "block_size": 16, "sampling_epsilon_min": 0.1},
+        "training": {"batch_size": 2, "steps": steps, "activation_checkpointing": True},
+        "topology": {"context_parallel_size": cp, "block_parallel_size": bp, "tensor_parallel_size": tp,
+                     "sequence_parallel": sp},
+        "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
+    rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
+    s = TrainingSession(spec, device="cpu", runtime=rt)
+    losses = []
+    for _ in range(steps):
+        r = s.step()
+        t = r.loss_sum.double().clone()
+        if world > 1:
+            dist.all_reduce(t)
+        losses.append(float(t) / r.denominator / tp)
+    p = s.model.flat.params
+    return (losses, s.optimizer.grad_norm(), p["layers.0.gdn_norm"].detach().clone(), p["layers.1.post_norm"].detach().clone(),
+            p["layers.3.q_norm"].detach().clone())
+
+
+@pytest.mark.distributed
+def test_hybrid_tensor_sequence_and_context_parallelism_together():
+    """The shape of the family's large recipes in miniature: tensor parallelism 2 with sequence parallelism, times
+    context-sharded block parallelism 2 (4 gloo ranks). Linear-attention layers own 1/2 of the heads per tensor-parallel
+    rank and trade row shards for a further 1/2 of those heads inside the context group."""
+    from tests._harness import assert_params_close, run_ranks
+
+    ref = _hybrid_tp_cp_run(0, 1, 1, 1, 1, False)
+    outs = run_ranks(_hybrid_tp_cp_run, 4, args=(2, 2, 2, True), deadline_s=600)
+    for losses, norm, gdn_norm, post_norm, q_norm in outs:
+        assert losses == pytest.approx(ref[0], rel=2e-4, abs=2e-4)
+        assert norm == pytest.approx(ref[1], rel=3e-3)
+        for got, want in ((gdn_norm, ref[2]), (post_norm, ref[3]), (q_norm, ref[4])):      # replicated, partial gradients summed
+            assert_params_close(got, want, rtol=2e-3, atol=2e-5)

@@ -117,7 +117,7 @@ def test_lora_under_tensor_parallelism_matches_single_process(sp):
         assert_params_close(gu_b, full[r * n:(r + 1) * n], rtol=2e-3, atol=2e-5)
 
 
-def _run_hybrid(rank, world, tp, steps):
+def _run_hybrid(rank, world, tp, steps, sp=False):
     from turbo_dllm_b200.config.run_spec import RunSpec
     from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
     from turbo_dllm_b200.training.session import TrainingSession
@@ -127,10 +127,12 @@ def _run_hybrid(rank, world, tp, steps):
         "model": {"id": "synthetic:tiny-qwen3_8", "seq_len": 64, "dtype": "fp32"},
         "objective": {"name": "fast_dllm_v2", "block_size": 16, "noise_schedule_epsilon": 0.1},
         "training": {"batch_size": 2, "steps": steps},
-        "topology": {"context_parallel_size": 1, "block_parallel_size": 1, "tensor_parallel_size": tp},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1, "tensor_parallel_size": tp,
+                     "sequence_parallel": sp},
         "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
     rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
     s = TrainingSession(spec, device="cpu", runtime=rt)
+    assert bool(getattr(s.model.tp, "sequence_parallel", False)) == (sp and tp > 1)
     losses, norms = [], []
     for _ in range(steps):
         r = s.step()
@@ -138,11 +140,12 @@ def _run_hybrid(rank, world, tp, steps):
         norms.append(s.optimizer.grad_norm())
     p = {n: t.detach().clone() for n, t in s.model.flat.params.items()}
     return (losses, norms, p["layers.0.w_in"], p["layers.0.A_log"], p["layers.0.gdn_norm"], p["layers.3.w_attn_gate"],
-            p["layers.0.w_out"], p["layers.3.q_norm"])
+            p["layers.0.w_out"], p["layers.3.q_norm"], p["layers.0.input_norm"], p["layers.3.post_norm"])
 
 
 @pytest.mark.distributed
-def test_hybrid_family_under_tensor_parallelism_matches_single_process():
+@pytest.mark.parametrize("sp", [False, True])
+def test_hybrid_family_under_tensor_parallelism_matches_single_process(sp):
     """Gated DeltaNet layers with half of the key / value heads per rank (fused input projection by head segments,
     per-head decay vectors, output projection by value-head columns) and the gated softmax-attention layer with half
     of its heads: losses, gradient norms and weights follow the single-process run."""
@@ -150,9 +153,12 @@ def test_hybrid_family_under_tensor_parallelism_matches_single_process():
     from turbo_dllm_b200.models.hybrid import fused_projection_rows
 
     ref = _run_hybrid(0, 1, 1, 3)
-    outs = run_ranks(_run_hybrid, 2, args=(2, 3), deadline_s=300)
+    outs = run_ranks(_run_hybrid, 2, args=(2, 3, sp), deadline_s=300)
     cfg = PRESETS["synthetic:tiny-qwen3_8"]
-    for r, (losses, norms, w_in, a_log, gdn_norm, gate, w_out, q_norm) in enumerate(outs):
+    for r, (losses, norms, w_in, a_log, gdn_norm, gate, w_out, q_norm, in_norm, post_norm) in enumerate(outs):
+        # with sequence parallelism the layer norms see this rank's rows only: their partial gradients are summed
+        assert_params_close(in_norm, ref[8], rtol=2e-3, atol=2e-5)
+        assert_params_close(post_norm, ref[9], rtol=2e-3, atol=2e-5)
         assert losses == pytest.approx(ref[0], rel=3e-4, abs=3e-4)
         assert norms == pytest.approx(ref[1], rel=3e-3)
         rows, _ = fused_projection_rows(cfg, r, 2)

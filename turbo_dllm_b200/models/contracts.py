@@ -195,7 +195,7 @@ class MoEExecutor(_ExecutorBase):
 class HybridExecutor(_ExecutorBase):
     """Gated DeltaNet + gated softmax attention (dllm_parallel/core/models/backbones/qwen3_8/executor.py:192-413)."""
 
-    capabilities = BackboneCapabilities(tensor_parallel=True, lora=True, head_dims=(128,))
+    capabilities = BackboneCapabilities(tensor_parallel=True, sequence_parallel=True, lora=True, head_dims=(128,))
     kernel_policy = BackboneKernelPolicy(optional_symbols=("tdllm_gdn_scan_fwd", "tdllm_gdn_scan_bwd"))
 
     def __init__(self, family: ModelFamilySpec):
@@ -204,9 +204,6 @@ class HybridExecutor(_ExecutorBase):
     def validate_run_spec(self, spec, world_size: int | None = None) -> list[str]:
         out = super().validate_run_spec(spec, world_size)
         t = spec.topology
-        if t.tensor_parallel_size > 1 and (t.context_parallel_size > 1 or t.sequence_parallel):
-            out.append("the hybrid family combines tensor parallelism with data and block parallelism only "
-                       "(not with context or sequence parallelism)")
         return out
 
     def build_model(self, ctx: BuildContext):
@@ -214,7 +211,12 @@ class HybridExecutor(_ExecutorBase):
         from .hybrid import HybridBlockDiffusionTransformer
 
         rt = ctx.runtime
-        tp = TPContext(rt.tensor_group, False) if rt is not None and rt.tensor_parallel_size > 1 else None
+        tp = None
+        if rt is not None and rt.tensor_parallel_size > 1:
+            tp = TPContext(rt.tensor_group, ctx.spec.topology.sequence_parallel)
+            if not ctx.spec.topology.tensor_parallel_overlap:
+                tp.fused_allreduce_enabled = False
+                tp.fused_sequence_parallel_enabled = False
         return HybridBlockDiffusionTransformer(ctx.cfg, dtype=ctx.dtype, device=ctx.device,
                                                activation_checkpointing=ctx.spec.training.activation_checkpointing,
                                                activation_offload=ctx.activation_offload, seed=ctx.seed, tp=tp)

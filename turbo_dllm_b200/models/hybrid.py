@@ -217,6 +217,9 @@ class GatedDeltaLayer(nn.Module):
             setattr(self, n, g(n))
         if self.tp is not None:
             self.gdn_norm.tp_partial = True     # replicated weight that sees this rank's heads only
+            if self.tp.sequence_parallel:       # the layer norms see this rank's rows only
+                self.input_norm.tp_partial = True
+                self.post_norm.tp_partial = True
 
     # -- pieces ------------------------------------------------------------------------------
     @staticmethod
@@ -269,10 +272,15 @@ class GatedDeltaLayer(nn.Module):
         noisy = torch.cat(outs, dim=0) if outs else out_c.new_zeros(0, sh.vd)
         return noisy, out_c.reshape(B * S, -1)
 
-    def mix(self, y: torch.Tensor, rows: BlockRows) -> torch.Tensor:
-        """y: normed rows [rows, H] -> mixer features [rows, Hv * Dv] (input of the output projection)."""
+    def mix(self, y: torch.Tensor | None, rows: BlockRows, projected: torch.Tensor | None = None) -> torch.Tensor:
+        """y: normed rows [rows, H] -> mixer features [rows, Hv * Dv] (input of the output projection). `projected`:
+        the fused input projection of ALL rows when the caller computed it (sequence parallelism gathers the rows on
+        the way into that projection)."""
         bs = rows.block_size
-        p = linear(y, self.w_in, self.tp) if self.tp is not None else _adapted_linear(self, y, "w_in")
+        if projected is not None:
+            p, y = projected, projected        # (y is only asked for its dtype below)
+        else:
+            p = linear(y, self.w_in, self.tp) if self.tp is not None else _adapted_linear(self, y, "w_in")
         plan = rows.head_parallel
         if plan is None:
             sh = _HeadShard(self)
@@ -299,6 +307,15 @@ class GatedDeltaLayer(nn.Module):
         if getattr(self, "lora", None) is not None:
             return _adapted_mlp(self, h + _adapted_linear(self, self.mix(y, rows), "w_out"))
         tp = self.tp
+        if tp is not None and tp.sequence_parallel:
+            # h holds this rank's rows of the residual stream: the column-parallel projections gather the rows on the
+            # way in (the recurrence needs whole sequences, of this rank's heads), the row-parallel ones scatter the sum
+            from ..parallel.tensor_parallel import sp_column_linear, sp_row_linear_residual
+
+            feats = self.mix(None, rows, projected=sp_column_linear(y, self.w_in, tp))
+            h = sp_row_linear_residual(feats, self.w_out, h, tp)
+            y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
+            return sp_row_linear_residual(sp_column_linear(y2, self.w_gate_up, tp, swiglu=True), self.w_down, h, tp, last=True)
         if tp is not None:
             h = row_parallel_linear_residual(self.mix(y, rows), self.w_out, h, tp)
             y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
@@ -322,9 +339,29 @@ class GatedAttentionLayer(nn.Module):
             for p in (self.q_norm, self.k_norm):
                 if p is not None:
                     p.tp_partial = True
+            if self.tp.sequence_parallel:
+                self.input_norm.tp_partial = True
+                self.post_norm.tp_partial = True
+
+    def _forward_sequence_parallel(self, h, positions, inv_freq, attend):
+        """h: this rank's rows. Query / key / value and gate projections gather the rows (attention runs over all rows
+        of this rank's heads), the output and down projections scatter the summed rows."""
+        from ..parallel.tensor_parallel import sp_column_linear, sp_row_linear_residual
+
+        cfg, tp = self.cfg, self.tp
+        y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
+        qkv = qk_norm_rope(sp_column_linear(y, self.w_qkv, tp), positions, inv_freq, self.q_norm, self.k_norm,
+                           cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
+        gate = torch.sigmoid(sp_column_linear(y, self.w_attn_gate, tp).float())
+        a = (attend(qkv, self.idx).float() * gate).to(h.dtype)
+        h = sp_row_linear_residual(a, self.w_o, h, tp)
+        y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
+        return sp_row_linear_residual(sp_column_linear(y2, self.w_gate_up, tp, swiglu=True), self.w_down, h, tp, last=True)
 
     def _forward_tensor_parallel(self, h, positions, inv_freq, attend):
         cfg, tp = self.cfg, self.tp
+        if tp.sequence_parallel:
+            return self._forward_sequence_parallel(h, positions, inv_freq, attend)
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
         qkv = qk_norm_rope(linear(y, self.w_qkv, tp), positions, inv_freq, self.q_norm, self.k_norm,
                            cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
@@ -365,8 +402,9 @@ class HybridBlockDiffusionTransformer(BlockDiffusionTransformer):
             raise ValueError("linear_num_value_heads must be a multiple of linear_num_key_heads")
         self.tp = tp if tp is not None and tp.size > 1 else None
         tps = self.tp.size if self.tp is not None else 1
-        if self.tp is not None and self.tp.sequence_parallel:
-            raise ValueError("the hybrid family runs tensor parallelism without sequence parallelism")
+        if self.tp is not None:
+            # gathered inputs may stay in the rotating peer-memory buffers until a checkpointed layer's backward
+            self.tp.sp_saved_in_place = bool(activation_checkpointing)
         self.cfg, self.lcfg = cfg, local_hybrid_config(cfg, tps)
         lcfg = self.lcfg
         self.activation_checkpointing = activation_checkpointing
