@@ -138,3 +138,40 @@ def test_settings_without_effect_are_refused_and_debug_checks_fire():
     s.forward_backward = poisoned
     with pytest.raises(FloatingPointError, match="layers.0.w_o"):
         s.step()
+
+
+def test_run_files_of_the_large_recipe_shapes_validate():
+    """Run files in the shape of the large multi-node recipes (hub model ids, DeepSpeed-style optimizer names, tensor +
+    sequence parallelism times context-sharded block parallelism, expert parallelism with native SFT, a drafter with the
+    context divided over two ranks) pass validation, including the model family's own checks."""
+    from turbo_dllm_b200.config.run_spec import RunSpec
+
+    common = {"training": {"batch_size": 1, "steps": 10, "activation_checkpointing": True,
+                           "activation_checkpointing_scope": "full"},
+              "optimizer": {"backend": "deepspeed_zero2", "allow_deepspeed_op_build": False, "lr": 1e-6, "gradient_clip_norm": 1.0},
+              "scheduler": {"type": "cosine", "warmup_steps": 4, "decay_steps": 10, "min_lr": 1e-7},
+              "kernel": {"runtime_jit": False}, "logging": {"wandb": False}}
+    hybrid = {**common, "model": {"id": "Qwen/Qwen3.8-27B", "family": "qwen3_8", "seq_len": 262144, "mask_token": "<|mask|>",
+                                  "dtype": "bf16"},
+              "objective": {"name": "fast_dllm_v2", "block_size": 256, "noise_schedule": "linear_mask", "loss_weighting": "unit",
+                            "antithetic_sampling": True},
+              "topology": {"tensor_parallel_size": 2, "sequence_parallel": True, "tensor_parallel_overlap": False,
+                           "context_parallel_size": 8, "block_parallel_size": 8, "placement_policy": "inter_node_cp"}}
+    RunSpec.from_mapping(hybrid).validate(world_size=16)
+    moe = {**common, "model": {"id": "google/diffusiongemma-26B-A4B-it", "family": "auto", "seq_len": 262144, "dtype": "bf16",
+                               "trust_remote_code": True},
+           "objective": {"name": "diffusiongemma_native_sft", "block_size": 256, "noise_schedule": "loglinear",
+                         "loss_weighting": "unit", "self_conditioning_probability": 0.5},
+           "topology": {"expert_parallel_size": 2, "context_parallel_size": 8, "block_parallel_size": 8}}
+    RunSpec.from_mapping(moe).validate(world_size=16)
+    moe_tp = {**moe, "objective": {"block_size": 256, "name": "standard_block_diffusion"},
+              "topology": {"tensor_parallel_size": 2, "sequence_parallel": True, "context_parallel_size": 2, "block_parallel_size": 2}}
+    RunSpec.from_mapping(moe_tp).validate(world_size=4)
+    draft = {**common, "model": {"id": "z-lab/draft", "family": "dflash", "verifier_id": "org/verifier", "seq_len": 1048576,
+                                 "target_layer_ids": [2, 11, 19], "dtype": "bf16"},
+             "objective": {"name": "dflash_distillation", "block_size": 16, "max_anchors": 512, "decay_gamma": 4.0},
+             "data": {"input_mode": "dataset", "target_features": "synthetic"},
+             "topology": {"context_parallel_size": 2, "block_parallel_size": 1}}
+    RunSpec.from_mapping(draft).validate(world_size=2)
+    with pytest.raises(RunSpecError, match="tensor-parallel"):      # a drafter has no tensor-parallel form
+        RunSpec.from_mapping({**draft, "topology": {"tensor_parallel_size": 2}}).validate(world_size=2)

@@ -160,3 +160,68 @@ def test_expert_parallel_ranks_load_their_experts_and_export_all(tmp_path):
         assert set(a.keys()) == set(b.keys())
         for k in a.keys():
             assert torch.equal(a.get_tensor(k), b.get_tensor(k)), k
+
+
+def _moe_parallel(rank, world, tp, cp, bp, sp, ep=1, steps=2):
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    torch.set_num_threads(2)
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-moe", "seq_len": 128, "dtype": "fp32", "family": "diffusion_gemma", "num_layers": 2,
+                  "moe_shared_intermediate_size": 64},
+        "objective": {"name": "standard_block_diffusion", "block_size": 32, "sampling_epsilon_min": 0.1},
+        "training": {"batch_size": 2, "steps": steps},
+        "topology": {"context_parallel_size": cp, "block_parallel_size": bp, "tensor_parallel_size": tp,
+                     "sequence_parallel": sp, "expert_parallel_size": ep},
+        "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
+    rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
+    s = TrainingSession(spec, device="cpu", runtime=rt)
+    losses = []
+    for _ in range(steps):
+        r = s.step()
+        t = r.loss_sum.double().clone()
+        if world > 1:
+            dist.all_reduce(t)
+        losses.append(float(t) / r.denominator / tp)
+    p = s.model.flat.params
+    return (losses, s.optimizer.grad_norm(), p["layers.0.router"].detach().clone(), p["layers.1.experts_down"].detach().clone(),
+            p["layers.0.post_norm"].detach().clone(), p["layers.1.w_down"].detach().clone())
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("world,tp,cp,bp,sp", [(2, 2, 1, 1, False), (2, 2, 1, 1, True), (4, 2, 2, 2, True)])
+def test_moe_decoder_under_tensor_and_sequence_parallelism(world, tp, cp, bp, sp):
+    """Attention and the dense branch sharded over the tensor-parallel ranks, router and experts replicated; with
+    sequence parallelism every rank routes its own rows and the partial gradients of router, experts and norms are
+    summed. Alone and together with context-sharded block parallelism the step equals the single-process one."""
+    from tests._harness import assert_params_close
+
+    ref = _moe_parallel(0, 1, 1, 1, 1, False)
+    for r, out in enumerate(run_ranks(_moe_parallel, world, args=(tp, cp, bp, sp), deadline_s=600)):
+        assert out[0] == pytest.approx(ref[0], rel=2e-4, abs=2e-4)
+        assert out[1] == pytest.approx(ref[1], rel=3e-3)
+        for i in (2, 3, 4):                                # router, experts, layer norm: replicated
+            assert_params_close(out[i], ref[i], rtol=2e-3, atol=2e-5)
+        n = ref[5].shape[1] // tp                           # dense branch: row-parallel columns of this rank
+        # (ranks are laid out with the tensor-parallel coordinate fastest)
+        assert_params_close(out[5], ref[5][:, (r % tp) * n:(r % tp + 1) * n], rtol=2e-3, atol=2e-5)
+
+
+@pytest.mark.distributed
+def test_moe_tensor_parallelism_composes_with_expert_parallelism():
+    """Tensor x expert parallelism (4 ranks) against expert parallelism alone (2 ranks): same data-parallel width and
+    the same experts per expert-parallel coordinate, so losses, norm and weights must agree."""
+    from tests._harness import assert_params_close
+
+    a = run_ranks(_moe_parallel, 2, args=(1, 1, 1, False, 2), deadline_s=600)
+    b = run_ranks(_moe_parallel, 4, args=(2, 1, 1, True, 2), deadline_s=600)
+    assert b[0][0] == pytest.approx(a[0][0], rel=2e-4, abs=2e-4) and b[0][1] == pytest.approx(a[0][1], rel=3e-3)
+    for rb in b:
+        assert_params_close(rb[2], torch.as_tensor(a[0][2]), rtol=2e-3, atol=2e-5)          # router: replicated everywhere
+        # this rank's experts equal those of exactly one expert-parallel coordinate of the 2-rank run
+        close = [float((torch.as_tensor(rb[3]) - torch.as_tensor(ra[3])).abs().max()) < 1e-4 for ra in a]
+        assert sum(close) == 1

@@ -170,7 +170,7 @@ class DenseExecutor(_ExecutorBase):
 class MoEExecutor(_ExecutorBase):
     """DiffusionGemma-style routed experts (dllm_parallel/core/models/backbones/diffusiongemma/model.py:33-460)."""
 
-    capabilities = BackboneCapabilities(expert_parallel=True, lora=True)
+    capabilities = BackboneCapabilities(expert_parallel=True, tensor_parallel=True, sequence_parallel=True, lora=True)
     kernel_policy = BackboneKernelPolicy(optional_symbols=("tdllm_gemm_grouped_bf16", "tdllm_ep_dispatch"))
 
     def __init__(self, family: ModelFamilySpec):
@@ -180,16 +180,24 @@ class MoEExecutor(_ExecutorBase):
         from .dense import BlockDiffusionTransformer
         from .moe import MoEBlockDiffusionTransformer
 
+        from ..parallel.tensor_parallel import TPContext
+
         rt, spec = ctx.runtime, ctx.spec
+        tp = None
+        if rt is not None and rt.tensor_parallel_size > 1:
+            tp = TPContext(rt.tensor_group, spec.topology.sequence_parallel)
+            if not spec.topology.tensor_parallel_overlap:
+                tp.fused_allreduce_enabled = False
+                tp.fused_sequence_parallel_enabled = False
         if not ctx.cfg.is_moe:     # the family's dense checkpoints use the dense decoder
             return BlockDiffusionTransformer(ctx.cfg, dtype=ctx.dtype, device=ctx.device,
                                              activation_checkpointing=spec.training.activation_checkpointing,
-                                             activation_offload=ctx.activation_offload, seed=ctx.seed)
+                                             activation_offload=ctx.activation_offload, seed=ctx.seed, tp=tp)
         ep = rt.expert_parallel_size if rt is not None else 1
         return MoEBlockDiffusionTransformer(ctx.cfg, ep_group=rt.group("expert") if ep > 1 else None,
                                             dtype=ctx.dtype, device=ctx.device,
                                             activation_checkpointing=spec.training.activation_checkpointing,
-                                            activation_offload=ctx.activation_offload, seed=ctx.seed)
+                                            activation_offload=ctx.activation_offload, seed=ctx.seed, tp=tp)
 
 
 class HybridExecutor(_ExecutorBase):

@@ -270,9 +270,15 @@ def _expert_linear(x, w_all, e):
 
 
 class MoEDecoderLayer(nn.Module):
-    def __init__(self, cfg: ModelConfig, idx: int, flat: FlatParams, ep_group=None):
+    def __init__(self, cfg: ModelConfig, idx: int, flat: FlatParams, ep_group=None, tp=None):
+        """cfg: per-rank shapes. tp: tensor-parallel context. Attention and the dense feed-forward branch are sharded
+        like the dense decoder's (column- / row-parallel); the router and the experts are replicated over the
+        tensor-parallel ranks and work on the rows the rank holds: all rows without sequence parallelism (every rank
+        computes the same), its own rows with it (the ranks then route different tokens, and the gradients of the
+        router, the experts and the layer norms are partial sums that the session adds up over the group)."""
         super().__init__()
         self.cfg, self.idx = cfg, idx
+        self.tp = tp if tp is not None and tp.size > 1 else None
         g = lambda n: flat.params[f"layers.{idx}.{n}"]
         self.input_norm, self.w_qkv, self.w_o, self.post_norm = g("input_norm"), g("w_qkv"), g("w_o"), g("post_norm")
         self.q_norm = g("q_norm") if cfg.qk_norm else None
@@ -282,9 +288,39 @@ class MoEDecoderLayer(nn.Module):
         self.w_gate_up = g("w_gate_up") if cfg.moe_shared_intermediate_size > 0 else None
         self.w_down = g("w_down") if cfg.moe_shared_intermediate_size > 0 else None
         self.experts = ExpertBank(cfg, idx, flat, ep_group)
+        if self.tp is not None:
+            partial = [self.q_norm, self.k_norm]
+            if self.tp.sequence_parallel:
+                partial += [self.input_norm, self.post_norm, self.experts.router, self.experts.w_gu, self.experts.w_down]
+            for p in partial:
+                if p is not None:
+                    p.tp_partial = True
+
+    def _forward_tensor_parallel(self, h, positions, inv_freq, attend):
+        from ..ops.gemm import linear_swiglu, row_parallel_linear_residual
+        from ..parallel.tensor_parallel import sp_column_linear, sp_row_linear_residual
+
+        cfg, tp = self.cfg, self.tp
+        sp = tp.sequence_parallel
+        column = (lambda x, w, **kw: sp_column_linear(x, w, tp, **kw)) if sp else None
+        y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
+        qkv = column(y, self.w_qkv) if sp else linear(y, self.w_qkv, tp)
+        qkv = qk_norm_rope(qkv, positions, inv_freq, self.q_norm, self.k_norm, cfg.num_attention_heads,
+                           cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
+        a = attend(qkv, self.idx)
+        h = sp_row_linear_residual(a, self.w_o, h, tp) if sp else row_parallel_linear_residual(a, self.w_o, h, tp)
+        y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
+        out = h + self.experts(y2)            # token-local: the rows this rank holds
+        if self.w_gate_up is None:
+            return out
+        if sp:
+            return sp_row_linear_residual(column(y2, self.w_gate_up, swiglu=True), self.w_down, out, tp, last=True)
+        return row_parallel_linear_residual(linear_swiglu(y2, self.w_gate_up, tp), self.w_down, out, tp, last=True)
 
     def forward(self, h, positions, inv_freq, attend):
         cfg = self.cfg
+        if self.tp is not None:
+            return self._forward_tensor_parallel(h, positions, inv_freq, attend)
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
         st = getattr(self, "lora", None)
         if st is not None:
@@ -326,19 +362,36 @@ def moe_layer_specs(cfg: ModelConfig, i: int, e_local: int):
     return out
 
 
+def local_moe_config(cfg: ModelConfig, tp: int) -> ModelConfig:
+    """Per-rank shapes under tensor parallelism: attention heads and the dense feed-forward branch are divided by `tp`;
+    router and experts keep their shapes (they are replicated over the tensor-parallel ranks)."""
+    if tp == 1:
+        return cfg
+    from dataclasses import replace
+
+    for name in ("num_attention_heads", "num_key_value_heads", "moe_shared_intermediate_size", "vocab_size"):
+        if getattr(cfg, name) % tp:
+            raise ValueError(f"{name} ({getattr(cfg, name)}) must divide by tensor_parallel_size {tp}")
+    return replace(cfg, num_attention_heads=cfg.num_attention_heads // tp, num_key_value_heads=cfg.num_key_value_heads // tp,
+                   moe_shared_intermediate_size=cfg.moe_shared_intermediate_size // tp)
+
+
 class MoEBlockDiffusionTransformer(BlockDiffusionTransformer):
     """Same interface as the dense model; expert parameters are sharded over `ep_group`."""
 
     def __init__(self, cfg: ModelConfig, *, ep_group=None, dtype=torch.bfloat16, device="cpu",
                  activation_checkpointing: bool = True, activation_offload: bool = False, seed: int = 0,
-                 init_std: float = 0.02):
+                 init_std: float = 0.02, tp=None):
         nn.Module.__init__(self)
         from ..ops.rope import rope_inv_freq
         from .activation_store import ActivationStore
 
         self.cfg = cfg
-        self.lcfg = cfg
-        self.tp = None
+        self.tp = tp if tp is not None and tp.size > 1 else None
+        tps = self.tp.size if self.tp is not None else 1
+        self.lcfg = local_moe_config(cfg, tps)
+        if self.tp is not None:
+            self.tp.sp_saved_in_place = bool(activation_checkpointing)
         self.activation_checkpointing = activation_checkpointing
         self.store = ActivationStore(torch.device(device), offload=activation_offload)
         self.store.keep_attention = False
@@ -347,14 +400,23 @@ class MoEBlockDiffusionTransformer(BlockDiffusionTransformer):
             raise ValueError(f"{cfg.num_experts} experts cannot be split over expert_parallel_size {ep}")
         e_local = cfg.num_experts // ep
         h = cfg.hidden_size
-        specs = [("embed", (cfg.vocab_size, h), True), ("final_norm", (h,), False)]
+        specs = [("embed", (cfg.vocab_size // tps, h), True), ("final_norm", (h,), False)]
         if not cfg.tie_word_embeddings:
-            specs.append(("lm_head", (cfg.vocab_size, h), True))
+            specs.append(("lm_head", (cfg.vocab_size // tps, h), True))
         for i in range(cfg.num_layers):
-            specs += moe_layer_specs(cfg, i, e_local)
+            specs += moe_layer_specs(self.lcfg, i, e_local)
         dense_specs = [sp for sp in specs if "experts_" not in sp[0]]
         expert_specs = [sp for sp in specs if "experts_" in sp[0]]
+        first_router = None
+        if self.tp is not None:
+            # the optimizer sums squared gradients of tensor-parallel shards over the group and counts replicated
+            # parameters once: the routers are decayed matrices but replicated, so they go behind the sharded ones
+            routers = [sp for sp in dense_specs if sp[0].endswith(".router")]
+            dense_specs = [sp for sp in dense_specs if not sp[0].endswith(".router")] + routers
+            first_router = routers[0][0]
         self.flat = FlatParams(dense_specs, dtype, device)            # replicated over DP x EP
+        if first_router is not None:
+            self.flat.tp_sharded_numel = self.flat.offsets[first_router][0]
         self.flat_experts = FlatParams(expert_specs, dtype, device)    # sharded over EP, replicated over DP
         for p in self.flat_experts.params.values():
             p.expert_written = set()
@@ -364,7 +426,7 @@ class MoEBlockDiffusionTransformer(BlockDiffusionTransformer):
             self.register_parameter(name.replace(".", "_"), p)
         self.embed, self.final_norm = self.flat.params["embed"], self.flat.params["final_norm"]
         self.lm_head = self.flat.params.get("lm_head", self.embed)
-        self.layers = nn.ModuleList(MoEDecoderLayer(cfg, i, self.flat, ep_group) for i in range(cfg.num_layers))
+        self.layers = nn.ModuleList(MoEDecoderLayer(self.lcfg, i, self.flat, ep_group, self.tp) for i in range(cfg.num_layers))
         self.expert_exchange = {}      # filled on the first routed batch on a GPU (parallel/expert_exchange.py)
         for layer in self.layers:
             layer.experts.exchange_holder = self.expert_exchange

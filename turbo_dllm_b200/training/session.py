@@ -93,9 +93,9 @@ class TrainingSession:
             from ..adapters.lora import apply_lora
 
             tp_ctx = getattr(self.model, "tp", None)
-            if tp_ctx is not None and self.cfg.is_hybrid:
-                raise ValueError("LoRA adapters support the dense decoder at any tensor-parallel degree, the "
-                                 "mixture-of-experts decoder, and the hybrid family on one tensor-parallel rank")
+            if tp_ctx is not None and (self.cfg.is_hybrid or self.cfg.is_moe):
+                raise ValueError("LoRA adapters support the dense decoder at any tensor-parallel degree, and the "
+                                 "mixture-of-experts decoder and the hybrid family on one tensor-parallel rank")
             self.lora = apply_lora(self.model, rank=spec.adapter.rank, alpha=spec.adapter.alpha,
                                    dropout=spec.adapter.dropout, targets=spec.adapter.targets or ("attention", "mlp"),
                                    seed=seed, tp=tp_ctx)
@@ -146,7 +146,9 @@ class TrainingSession:
                 if self.lora.flat_experts is not None:
                     self.expert_optimizer = FlatAdamW(self.lora.flat_experts, group=expert_group, **okw)
             else:
-                self.optimizer = FlatAdamW(self.model.flat, group=dense_group, **okw)
+                moe_tp = runtime.tensor_group if (runtime is not None and runtime.tensor_parallel_size > 1) else None
+                self.optimizer = FlatAdamW(self.model.flat, group=dense_group, tp_group=moe_tp, **okw)
+                # (router and experts are replicated over the tensor-parallel ranks: counted once in the norm)
                 self.expert_optimizer = FlatAdamW(self.model.flat_experts, group=expert_group, **okw)
             self.ep_group = runtime.group("expert") if ep > 1 else None
         else:
