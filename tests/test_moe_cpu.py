@@ -225,3 +225,38 @@ def test_moe_tensor_parallelism_composes_with_expert_parallelism():
         # this rank's experts equal those of exactly one expert-parallel coordinate of the 2-rank run
         close = [float((torch.as_tensor(rb[3]) - torch.as_tensor(ra[3])).abs().max()) < 1e-4 for ra in a]
         assert sum(close) == 1
+
+
+def _native_sft(rank, world, cp, bp, ep, steps=3):
+    import torch.distributed as dist
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    torch.set_num_threads(2)
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-moe", "seq_len": 128, "dtype": "fp32", "family": "diffusion_gemma", "num_layers": 2},
+        "objective": {"name": "diffusiongemma_native_sft", "block_size": 32, "noise_schedule": "loglinear",
+                      "loss_weighting": "unit", "self_conditioning_probability": 0.5, "sampling_epsilon_min": 0.1},
+        "training": {"batch_size": 1, "steps": steps},
+        "topology": {"context_parallel_size": cp, "block_parallel_size": bp, "expert_parallel_size": ep},
+        "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
+    s = TrainingSession(spec, device="cpu", runtime=build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world))
+    losses = []
+    for _ in range(steps):
+        r = s.step()
+        t = r.loss_sum.double().clone()
+        dist.all_reduce(t)
+        losses.append(float(t) / r.denominator)
+    return losses, s.optimizer.grad_norm()
+
+
+@pytest.mark.distributed
+def test_self_conditioning_pass_is_collective_over_expert_parallel_ranks():
+    """Expert-parallel ranks hold different samples; with one sample per rank and probability 0.5 they often disagree on
+    whether a sample is self-conditioned. The first pass exchanges tokens among them, so all of them run it when any
+    needs it (a rank deciding alone left the others waiting in the exchange). EP 2 alone and EP 2 x CSBP 2 agree."""
+    a = run_ranks(_native_sft, 2, args=(1, 1, 2), deadline_s=300)
+    b = run_ranks(_native_sft, 4, args=(2, 2, 2), deadline_s=600)
+    assert b[0][0] == pytest.approx(a[0][0], rel=2e-4, abs=2e-4) and b[0][1] == pytest.approx(a[0][1], rel=3e-3)

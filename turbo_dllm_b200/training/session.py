@@ -513,10 +513,21 @@ class TrainingSession:
 
         lay = self.layout
         rows = chosen.to(self.device)[lay.noisy_seq].nonzero(as_tuple=True)[0]   # noisy rows come first in the packing
-        if rows.numel() == 0:
+        need = rows.numel() > 0
+        run = need
+        ep_group = getattr(self, "ep_group", None)
+        if ep_group is not None:
+            # expert-parallel ranks hold different samples, and the model's forward exchanges tokens among them: if
+            # any of them has a marked sample, all of them run the first pass (the others discard its result)
+            flag = torch.tensor([int(need)], dtype=torch.int32, device=self.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=ep_group)
+            run = bool(int(flag))
+        if not run:
             return None, None
         with torch.no_grad():
             hidden0 = self.model(tokens, lay.positions, self.attend)
+            if not need:
+                return None, None
             o = self.spec.objective
             tp = getattr(self.model, "tp", None)
             soft = streaming_soft_embedding(hidden0.index_select(0, rows), self.model.lm_head,
