@@ -200,7 +200,7 @@ def _hybrid_run(rank, world, cp, bp, steps):
         "model": {"id": "synthetic:tiny-qwen3_8", "family": "qwen3_8", "seq_len": 128, "dtype": "fp32"},
         "objective": {"name": "fast_dllm_v2", "block_size": 16, "sampling_epsilon_min": 0.1},
         "training": {"batch_size": 2, "steps": steps, "activation_checkpointing": True},
-        "topology": {"context_parallel_size": cp, "block_parallel_size": bp},
+        "topology": {"context_parallel_size": cp, "block_parallel_size": bp, "replicate_clean_prefix": cp == 1 and bp > 1},
         "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
     rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
     s = TrainingSession(spec, device="cpu", runtime=rt)
@@ -215,13 +215,15 @@ def _hybrid_run(rank, world, cp, bp, steps):
 
 
 @pytest.mark.distributed
-def test_hybrid_context_sharded_run_matches_single_process():
-    """Two gloo ranks, clean rows and blocks sharded (CSBP degree 2): the linear-attention layers trade
-    row shards for head shards and back; losses and parameters must follow the single-process run."""
+@pytest.mark.parametrize("cp,bp", [(2, 2), (1, 2)])
+def test_hybrid_context_sharded_run_matches_single_process(cp, bp):
+    """Two gloo ranks. CSBP degree 2 (clean rows and blocks sharded): the linear-attention layers trade row shards
+    for head shards and back. Block parallelism alone: every rank keeps the whole clean sequence (the layers' chunk
+    states are indexed by position) and its own noisy blocks. Losses and parameters follow the single-process run."""
     from tests._harness import assert_params_close, run_ranks
 
     ref_losses, ref_params = _hybrid_run(0, 1, 1, 1, 2)
-    outs = run_ranks(_hybrid_run, 2, args=(2, 2, 2), deadline_s=300)
+    outs = run_ranks(_hybrid_run, 2, args=(cp, bp, 2), deadline_s=300)
     for losses, params in outs:
         assert losses == pytest.approx(ref_losses, rel=2e-4, abs=2e-4)
         assert_params_close(params, ref_params)

@@ -359,7 +359,10 @@ class TrainingSession:
                 clean = clean[:0]
         elif rt is not None and rt.block_parallel_size > 1 and s.topology.replicate_clean_prefix:
             last = max(owned)
-            clean = torch.arange(0, last * s.objective.block_size, device=self.device)
+            # the clean tokens in front of the rank's last block; linear-attention layers scan whole sequences
+            # (their chunk states are indexed by position), so the hybrid family keeps every clean row
+            stop = s.model.seq_len if self.cfg.is_hybrid else last * s.objective.block_size
+            clean = torch.arange(0, stop, device=self.device)
         offsets = None
         if rt is not None and rt.splits_block_tokens and not self.cfg.is_hybrid:
             from ..parallel.layout import pure_context_offsets
