@@ -138,3 +138,63 @@ def test_fsdp_needs_activation_checkpointing_and_a_dense_model():
     m["adapter"] = {"type": "lora", "rank": 4}
     with pytest.raises(RunSpecError, match="adapters"):
         RunSpec.from_mapping(m).validate()
+
+
+def _moe_run(rank, world, backend, tmp):
+    import torch.distributed as dist
+
+    import turbo_dllm_b200.checkpoint as ck
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    torch.set_num_threads(2)
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-moe", "seq_len": 128, "dtype": "fp32", "family": "diffusion_gemma", "num_layers": 2,
+                  "moe_shared_intermediate_size": 64},
+        "objective": {"name": "standard_block_diffusion", "block_size": 32, "sampling_epsilon_min": 0.1},
+        "training": {"batch_size": 2, "steps": 4},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1, "expert_parallel_size": 2},
+        "optimizer": {"backend": backend, "lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
+
+    def session():
+        rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world)
+        return TrainingSession(spec, device="cpu", runtime=rt), rt
+
+    a, _ = session()
+    assert (a.sharded is not None) == (backend == "fsdp")
+    losses = []
+    for _ in range(4):
+        r = a.step()
+        t = r.loss_sum.double().clone()
+        dist.all_reduce(t)
+        losses.append(float(t) / r.denominator)
+    dense = a.sharded.gather_full().clone() if a.sharded is not None else a.model.flat.data.clone()
+    out = {"losses": losses, "norm": a.optimizer.grad_norm(), "dense": dense, "experts": a.model.flat_experts.data.clone()}
+    if tmp:
+        b, rt = session()
+        for _ in range(2):
+            b.step()
+        ck.save_training_checkpoint(tmp, b, step=2, rank=rank, world_size=world, control_group=dist.group.WORLD, runtime=rt)
+        c, rt2 = session()
+        ck.load_training_checkpoint(tmp, "latest", c, rank=rank, world_size=world, runtime=rt2)
+        for _ in range(2):
+            c.step()
+        out["resumed_equal"] = bool(torch.equal(c.sharded.gather_full(), dense)
+                                    and torch.equal(c.model.flat_experts.data, a.model.flat_experts.data))
+    return out
+
+
+@pytest.mark.distributed
+def test_moe_parameter_sharding_beside_expert_parallelism(tmp_path):
+    """The mixture-of-experts decoder with `optimizer.backend: fsdp`: the replicated part (attention, router, dense
+    branch, embeddings) is sharded per layer over all ranks, the experts stay divided by expert parallelism with their own
+    sharded optimizer, and one gradient norm covers both. Same step as the sharded optimizer; resumes bit for bit."""
+    ref = run_ranks(_moe_run, 2, args=("torch_adamw", None), deadline_s=300)
+    out = run_ranks(_moe_run, 2, args=("fsdp", str(tmp_path / "ck")), deadline_s=400)
+    for r, o in zip(ref, out):
+        assert o["losses"] == pytest.approx(r["losses"], rel=1e-5)
+        assert o["norm"] == pytest.approx(r["norm"], rel=2e-3)
+        assert_params_close(o["dense"], torch.from_numpy(r["dense"]), rtol=1e-3, atol=2e-5)
+        assert_params_close(o["experts"], torch.from_numpy(r["experts"]), rtol=1e-3, atol=2e-5)
+        assert o["resumed_equal"]

@@ -167,8 +167,9 @@ class RunSpec:
             need(tr.activation_checkpointing, "optimizer.backend=fsdp needs training.activation_checkpointing")
             need(self.adapter.type == "none", "optimizer.backend=fsdp shards the base model: adapters use the "
                                               "sharded-optimizer backends (auto, zero_fused, torch_*)")
-            need(o.name != "dflash_distillation" and m.family not in ("qwen3_8", "diffusion_gemma"),
-                 "optimizer.backend=fsdp is built for the dense decoder family (causal_lm, nemotron_labs_diffusion)")
+            need(o.name != "dflash_distillation" and m.family != "qwen3_8",
+                 "optimizer.backend=fsdp is built for the dense decoder and the mixture-of-experts decoder (its "
+                 "replicated part; the experts are divided by expert parallelism)")
         if self.data.optimizer_step_unit == "trajectory":
             need(self.data.input_mode == "dataset", "data.optimizer_step_unit=trajectory needs an indexed dataset "
                                                     "with trajectory groups (data.input_mode=dataset)")

@@ -170,7 +170,8 @@ class DenseExecutor(_ExecutorBase):
 class MoEExecutor(_ExecutorBase):
     """DiffusionGemma-style routed experts (dllm_parallel/core/models/backbones/diffusiongemma/model.py:33-460)."""
 
-    capabilities = BackboneCapabilities(expert_parallel=True, tensor_parallel=True, sequence_parallel=True, lora=True)
+    capabilities = BackboneCapabilities(expert_parallel=True, tensor_parallel=True, sequence_parallel=True, lora=True,
+                                        parameter_sharding=True)
     kernel_policy = BackboneKernelPolicy(optional_symbols=("tdllm_gemm_grouped_bf16", "tdllm_ep_dispatch"))
 
     def __init__(self, family: ModelFamilySpec):

@@ -368,9 +368,15 @@ class ShardedAdamW:
     @torch.no_grad()
     def step(self, *, lr: float | None = None, weight_decay: float | None = None, grad_scale: float = 1.0,
              max_grad_norm: float = 0.0) -> None:
+        self.apply_update(self.reduce_gradients(), lr=lr, weight_decay=weight_decay, grad_scale=grad_scale,
+                          max_grad_norm=max_grad_norm)
+
+    @torch.no_grad()
+    def reduce_gradients(self) -> torch.Tensor:
+        """Σ g² of the whole (unsharded) gradient of this optimizer's parameters, as a 1-element tensor: the
+        gradient shards were reduced layer by layer during the backward pass, so only the norm is left to do.
+        Same two-phase surface as `FlatAdamW` (a second optimizer's share can be added before `apply_update`)."""
         sp = self.sp
-        lr = self.lr if lr is None else lr
-        wd = self.weight_decay if weight_decay is None else weight_decay
         g = sp.grad_shard
         split = sp.decay_local
         # vector_norm reduces without a temporary and takes more than 2^31 elements (a dot product does not)
@@ -382,6 +388,16 @@ class ShardedAdamW:
         sumsq = sharded_sq + repl_sq
         with communication_scope("optimizer_data_parallel", "gradient_clip", "all_reduce", 4):
             dist.all_reduce(sumsq, group=self.group)
+        return sumsq
+
+    @torch.no_grad()
+    def apply_update(self, sumsq: torch.Tensor, *, lr: float | None = None, weight_decay: float | None = None,
+                     grad_scale: float = 1.0, max_grad_norm: float = 0.0) -> None:
+        sp = self.sp
+        lr = self.lr if lr is None else lr
+        wd = self.weight_decay if weight_decay is None else weight_decay
+        g = sp.grad_shard
+        split = sp.decay_local
         self.last_grad_norm = sumsq
         self.step_count += 1
         b1, b2 = self.betas

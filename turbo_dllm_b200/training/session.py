@@ -147,7 +147,25 @@ class TrainingSession:
                     self.expert_optimizer = FlatAdamW(self.lora.flat_experts, group=expert_group, **okw)
             else:
                 moe_tp = runtime.tensor_group if (runtime is not None and runtime.tensor_parallel_size > 1) else None
-                self.optimizer = FlatAdamW(self.model.flat, group=dense_group, tp_group=moe_tp, **okw)
+                if o.backend in ("fsdp", "fsdp2") and dense_group is not None and dist.get_world_size(dense_group) > 1:
+                    # parameter sharding of the replicated (non-expert) part over all ranks that hold a copy of it;
+                    # the experts are already divided by expert parallelism and keep their sharded optimizer
+                    from ..parallel.fsdp import ShardedAdamW, ShardedParameters
+
+                    if moe_tp is not None:
+                        raise ValueError("optimizer.backend=fsdp for the mixture-of-experts decoder is built without "
+                                         "tensor parallelism")
+                    peer = (self.device.type == "cuda" and spec.kernel.impl not in ("cpu_reference", "nccl_baseline"))
+                    if peer:
+                        from ..parallel.symm import peer_access_available
+
+                        peer = peer_access_available(dense_group)
+                    self.sharded = ShardedParameters(self.model.flat, dense_group, self.device, use_peer_kernels=peer,
+                                                     num_layers=self.cfg.num_layers)
+                    self.model.attach_parameter_sharding(self.sharded)
+                    self.optimizer = ShardedAdamW(self.sharded, **okw)
+                else:
+                    self.optimizer = FlatAdamW(self.model.flat, group=dense_group, tp_group=moe_tp, **okw)
                 # (router and experts are replicated over the tensor-parallel ranks: counted once in the norm)
                 self.expert_optimizer = FlatAdamW(self.model.flat_experts, group=expert_group, **okw)
             self.ep_group = runtime.group("expert") if ep > 1 else None
@@ -625,6 +643,8 @@ class TrainingSession:
                 for f in self.flats():
                     f.collect_grads()
                 self._sync_tensor_parallel_partial_gradients()     # once, on the sums over the micro-batches
+            elif self.expert_optimizer is not None:
+                self.model.flat_experts.collect_grads()            # the experts are not part of the sharded buffer
             if getattr(self, "_grad_div", 1.0) != 1.0:
                 self.model.flat.grad.div_(self._grad_div)
         if spec.debug.grad_finite:      # debug.grad_finite: stop at the first non-finite gradient, naming the buffer
