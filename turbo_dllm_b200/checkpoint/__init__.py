@@ -512,6 +512,9 @@ def load_model_weights(directory: str, tag: str, session) -> dict:
                 n = max(0, min(u.shard, u.stop - lo))
                 if n:
                     flat.data[lo:lo + n].copy_(part[u.local:u.local + n].to(flat.data.device, flat.data.dtype))
+    experts = getattr(session.model, "flat_experts", None)
+    if experts is not None and "expert_model" in first:      # (expert_parallel_size 1: rank 0 holds every expert)
+        experts.data.copy_(first["expert_model"].to(experts.data.device, experts.data.dtype))
     lora = getattr(session, "lora", None)
     if lora is not None and "adapter" in first:
         lora.flat.data.copy_(first["adapter"].to(lora.flat.data.device, lora.flat.data.dtype))
