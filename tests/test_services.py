@@ -198,7 +198,8 @@ def test_family_executors_and_registration():
     assert executor_for_family("causal_lm").capabilities.parameter_sharding
     assert executor_for_family("qwen3_8").capabilities.tensor_parallel
     assert executor_for_family("qwen3_8").capabilities.sequence_parallel
-    assert not executor_for_family("diffusion_gemma").capabilities.tensor_parallel
+    assert executor_for_family("diffusion_gemma").capabilities.tensor_parallel
+    assert not executor_for_family("qwen3_8").capabilities.parameter_sharding
     assert not executor_for_family("dflash").capabilities.tensor_parallel
     spec = RunSpec.from_mapping({
         "model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "num_layers": 1},
@@ -211,9 +212,10 @@ def test_family_executors_and_registration():
     assert not hybrid.validate_run_spec(spec.with_overrides(
         {"topology": {"tensor_parallel_size": 2, "sequence_parallel": True, "context_parallel_size": 2,
                       "block_parallel_size": 2}, "objective": {"name": "fast_dllm_v2"}}))
-    problems = executor_for_family("diffusion_gemma").validate_run_spec(spec.with_overrides(
+    assert not executor_for_family("diffusion_gemma").validate_run_spec(spec.with_overrides(
         {"topology": {"tensor_parallel_size": 2, "sequence_parallel": True}}))
-    assert any("tensor-parallel" in p for p in problems) and any("sequence-parallel" in p for p in problems)
+    problems = hybrid.validate_run_spec(spec.with_overrides({"optimizer": {"backend": "fsdp"}, "objective": {"name": "fast_dllm_v2"}}))
+    assert any("fsdp" in p for p in problems)
     problems = executor_for_family("dflash").validate_run_spec(spec.with_overrides(
         {"topology": {"tensor_parallel_size": 2}, "objective": {"name": "dflash_distillation"}}))
     assert any("tensor-parallel" in p for p in problems)
