@@ -172,3 +172,41 @@ def test_hybrid_family_under_tensor_parallelism_matches_single_process(sp):
         n = ref[6].shape[1] // 2
         assert_params_close(w_out, ref[6][:, r * n:(r + 1) * n], rtol=2e-3, atol=2e-5)
         assert_params_close(q_norm, ref[7], rtol=2e-3, atol=2e-5)
+
+
+def _run_eval(rank, world, tp, sp, data_path, steps=12):
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.evaluation import evaluate_masked_token_accuracy
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    torch.set_num_threads(2)
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-qwen3", "seq_len": 128, "dtype": "fp32", "num_layers": 2},
+        "objective": {"name": "standard_block_diffusion", "block_size": 16, "sampling_epsilon_min": 0.1},
+        "data": {"input_mode": "dataset", "dataset_path": data_path},
+        "training": {"batch_size": 2, "steps": steps},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1, "tensor_parallel_size": tp, "sequence_parallel": sp},
+        "optimizer": {"lr": 3e-3}}).validate(world_size=world)
+    rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
+    s = TrainingSession(spec, device="cpu", runtime=rt)
+    for _ in range(steps):
+        s.step()
+    return evaluate_masked_token_accuracy(s, 2, 7)
+
+
+@pytest.mark.distributed
+def test_evaluation_under_tensor_parallelism_counts_once_and_finds_the_argmax(tmp_path):
+    """Masked-token accuracy with the vocabulary split over two ranks (the largest logit over the ranks, ties to the
+    smallest id) and the counts of the identical tensor-parallel copies taken once: the figures of the single process.
+    The data repeats seven token ids of the upper vocabulary half, so a few steps make some predictions right."""
+    import numpy as np
+
+    path = str(tmp_path / "cycle.i32")
+    (np.arange(16384) % 7 + 600).astype("<i4").tofile(path)
+    ref = _run_eval(0, 1, 1, False, path)
+    assert ref["eval_masked_token_accuracy"] > 0.02
+    for out in run_ranks(_run_eval, 2, args=(2, True, path), deadline_s=300):
+        assert out["eval_masked_tokens"] == ref["eval_masked_tokens"]
+        assert out["eval_masked_token_accuracy"] == pytest.approx(ref["eval_masked_token_accuracy"], abs=0.01)
+        assert out["eval_loss"] == pytest.approx(ref["eval_loss"], rel=1e-3)

@@ -33,11 +33,20 @@ def evaluate_masked_token_accuracy(session, batches: int, seed: int = 314159) ->
             tokens, labels, weights = session.assemble_rows(cb)
             hidden = session.model(tokens, session.layout.positions, session.attend)
             h, l, w, _ = compact_supervised_rows(hidden, labels, weights)
-            if session.model.tp is None:
-                logits = h.float() @ session.model.lm_head.float().t()
-                if objective.exclude_mask_token:
-                    logits[:, session.cfg.mask_token_id] = float("-inf")
-                correct += (logits.argmax(-1) == l).sum()
+            tp = session.model.tp
+            logits = h.float() @ session.model.lm_head.float().t()       # this rank's slice of the vocabulary under TP
+            v0 = tp.vocab_range(session.cfg.vocab_size)[0] if tp is not None else 0
+            if objective.exclude_mask_token and v0 <= session.cfg.mask_token_id < v0 + logits.shape[1]:
+                logits[:, session.cfg.mask_token_id - v0] = float("-inf")
+            best, arg = logits.max(-1) if logits.shape[0] else (logits.new_zeros(0), l.new_zeros(0))
+            arg = arg + v0
+            if tp is not None:
+                # vocabulary-parallel argmax: the largest logit over the ranks, ties to the smallest token id
+                top = best.clone()
+                dist.all_reduce(top, op=dist.ReduceOp.MAX, group=tp.group)
+                arg = torch.where(best == top, arg, torch.full_like(arg, session.cfg.vocab_size))
+                dist.all_reduce(arg, op=dist.ReduceOp.MIN, group=tp.group)
+            correct += (arg == l).sum()
             ls, _ = session.model.loss(h, l, None, objective.exclude_mask_token)
             loss_sum += ls.double()
             total += l.numel()
@@ -46,6 +55,8 @@ def evaluate_masked_token_accuracy(session, batches: int, seed: int = 314159) ->
     if dist.is_initialized() and dist.get_world_size() > 1:
         for t in (correct, total, loss_sum):
             dist.all_reduce(t)
+            if session.model.tp is not None:     # every tensor-parallel rank holds the same three numbers
+                t /= session.model.tp.size
     n = max(float(total), 1.0)
     return {"eval_masked_tokens": float(total), "eval_masked_token_accuracy": float(correct) / n,
             "eval_loss": float(loss_sum) / n}
