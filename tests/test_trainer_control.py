@@ -271,3 +271,37 @@ def test_logged_loss_under_tensor_parallelism_equals_the_single_rank_loss(tmp_pa
     a2 = [e["active_tokens"] for e in two if e["event"] == "step"]
     assert l2 == pytest.approx(l1, rel=1e-3)
     assert a1 == a2
+
+
+def test_evaluation_reads_its_own_dataset_and_leaves_the_training_stream_alone(tmp_path):
+    import numpy as np
+
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.training.evaluation import evaluate_masked_token_accuracy
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    (np.arange(8192) % 11 + 100).astype("<i4").tofile(tmp_path / "train.i32")
+    (np.arange(8192) % 5 + 700).astype("<i4").tofile(tmp_path / "heldout.i32")
+    base = {"model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "num_layers": 1},
+            "objective": {"name": "standard_block_diffusion", "block_size": 16},
+            "data": {"input_mode": "dataset", "dataset_path": str(tmp_path / "train.i32")},
+            "training": {"batch_size": 2, "steps": 1}, "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}
+    s = TrainingSession(RunSpec.from_mapping({**base, "evaluation": {"dataset_path": str(tmp_path / "heldout.i32"),
+                                                                      "batches": 2}}).validate(), device="cpu")
+    cursor = s.data.state_dict()
+    seen = []
+    real = s.assemble_rows
+
+    def spy(cb):
+        seen.append(cb.clean_input_ids.clone())
+        return real(cb)
+
+    s.assemble_rows = spy
+    out = evaluate_masked_token_accuracy(s, 2, 7)
+    assert out["eval_masked_tokens"] > 0 and len(seen) == 2
+    assert all(int(t.min()) >= 700 for t in seen)                 # the held-out ids, not the training ones
+    assert s.data.state_dict() == cursor                          # the training stream did not move
+    t = TrainingSession(RunSpec.from_mapping(base).validate(), device="cpu")
+    before = t.data.state_dict()
+    evaluate_masked_token_accuracy(t, 1, 7)
+    assert t.data.state_dict() != before                          # without a held-out set the next training batches are used

@@ -1,4 +1,5 @@
-"""Masked-token accuracy evaluation on held-out batches (no gradient, fixed seed).
+"""Masked-token accuracy evaluation (no gradient, fixed seed) on `evaluation.dataset_path` when it is set, else on
+the next batches of the training stream.
 
 Every evaluation batch is corrupted with the run's objective under its own generator
 (`evaluation.seed`), the model predicts the masked positions and accuracy / mean loss are reduced
@@ -21,6 +22,17 @@ def evaluate_masked_token_accuracy(session, batches: int, seed: int = 314159) ->
     spec = session.spec
     objective = build_objective_runtime(spec, mask_token_id=session.cfg.mask_token_id, seed=seed,
                                         vocab_size=session.cfg.vocab_size, device=session.device)
+    data = session.data
+    if spec.evaluation.dataset_path:
+        # held-out data: `evaluation.dataset_path` (a prepared artifact, a flat token file or a text file), read with
+        # the evaluation seed and sharded over the data-parallel ranks like the training data
+        from ..data.artifact_runtimes import build_artifact_runtime
+
+        held_out = spec.with_overrides({"data": {"input_mode": "dataset", "dataset_path": spec.evaluation.dataset_path,
+                                                 "optimizer_step_unit": "microbatch"},
+                                        "launch": {"seed": int(seed)}})
+        data = build_artifact_runtime(held_out, device=session.device, dp_rank=getattr(session, "dp_rank", 0),
+                                      dp_size=session.dp_size)
     saved = session.objective
     session.objective = objective
     correct = torch.zeros((), dtype=torch.float64, device=session.device)
@@ -28,7 +40,7 @@ def evaluate_masked_token_accuracy(session, batches: int, seed: int = 314159) ->
     loss_sum = torch.zeros_like(correct)
     try:
         for _ in range(batches):
-            batch = session.data.next_batch()
+            batch = data.next_batch()
             cb = objective.corrupt(batch.input_ids, supervision_mask=batch.supervision_mask)
             tokens, labels, weights = session.assemble_rows(cb)
             hidden = session.model(tokens, session.layout.positions, session.attend)

@@ -122,6 +122,7 @@ class TrainingSession:
         self.encoder_loss_weight = (float(spec.objective.encoder_loss_weight)
                                     if self.objective.name == "diffusiongemma_native_sft" else 0.0)
         self.last_encoder_loss = None
+        self.dp_rank = dp_rank
         self.data = self.executor.build_data_runtime(spec, self.cfg, self.device, dp_rank, self.dp_size,
                                                      host_staged=host_staged_data)
         if self.cfg.is_hybrid and runtime is not None:
