@@ -154,6 +154,8 @@ class RunSpec:
                  "objective.self_conditioning_probability must be in [0, 1]")
             need(o.self_conditioning_row_chunk_size > 0 and o.self_conditioning_vocab_chunk_size > 0,
                  "objective.self_conditioning_row_chunk_size / vocab_chunk_size must be positive")
+        need(m.max_position_embeddings is None or m.seq_len <= m.max_position_embeddings,
+             f"model.seq_len ({m.seq_len}) exceeds model.max_position_embeddings ({m.max_position_embeddings})")
         need(0.0 < o.sampling_epsilon_min <= o.sampling_epsilon_max <= 1.0,
              "objective.sampling_epsilon_min/max must satisfy 0 < min <= max <= 1")
         need(0.0 <= o.noise_schedule_epsilon < 1.0, "objective.noise_schedule_epsilon must be in [0, 1)")
