@@ -56,6 +56,8 @@ CASES = {
     # name: (ranks, what differs from the single-process reference, the reference)
     "dense lora x csbp2": (2, dict(topology=CSBP2, **LORA), dict(**LORA)),
     "hybrid lora x csbp2": (2, dict(model=HYBRID, objective=V2, topology=CSBP2, **LORA), dict(model=HYBRID, objective=V2, **LORA)),
+    "hybrid lora x tp2 + sp": (2, dict(model=HYBRID, objective=V2, topology={"tensor_parallel_size": 2, "sequence_parallel": True}, **LORA),
+                               dict(model=HYBRID, objective=V2, **LORA)),
     "sliding window x tp2": (2, dict(model=WINDOW, topology={"tensor_parallel_size": 2}), dict(model=WINDOW)),
     "pure cp2 x tp2": (4, dict(topology={"context_parallel_size": 2, "tensor_parallel_size": 2}), dict()),
     "pure bp2 x tp2 + sp": (4, dict(topology={**BP2, "tensor_parallel_size": 2, "sequence_parallel": True}), dict()),

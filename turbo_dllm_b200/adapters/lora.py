@@ -98,6 +98,54 @@ def lora_delta(x: torch.Tensor, a: torch.Tensor, b: torch.Tensor, scale: float, 
     return linear(low, b) * scale
 
 
+def adapted_column_linear(layer, x: torch.Tensor, name: str) -> torch.Tensor:
+    """x·Wᵀ of a column-parallel (or unsharded) projection `layer.<name>` plus its low-rank update. `layer` carries
+    `lora` (a LoRAState or None), `tp` (tensor-parallel context or None) and `idx`. Under tensor parallelism A is
+    replicated and B follows the weight's rows: the replicated x·Aᵀ (gathered rows under sequence parallelism) is
+    multiplied by this rank's B."""
+    from ..parallel.tensor_parallel import copy_to_tensor_parallel, gather_sequence_parallel, sp_column_linear
+
+    st, tp = getattr(layer, "lora", None), getattr(layer, "tp", None)
+    w = getattr(layer, name)
+    pair = None if st is None else st.pair(layer.idx, name)
+    g = tp.group if tp is not None and tp.size > 1 else None
+    if g is None:
+        out = linear(x, w)
+        return out if pair is None else out + lora_delta(x, pair[0], pair[1], st.scale, st.dropout)
+    sp = tp.sequence_parallel
+    base = sp_column_linear(x, w, tp) if sp else linear(x, w, tp)
+    if pair is None:
+        return base
+    low = linear(torch.nn.functional.dropout(x, st.dropout) if st.dropout > 0 and torch.is_grad_enabled() else x, pair[0])
+    low = gather_sequence_parallel(low, g) if sp else copy_to_tensor_parallel(low, g)
+    return base + linear(low, pair[1]) * st.scale
+
+
+def adapted_row_linear(layer, x: torch.Tensor, name: str, residual: torch.Tensor, last: bool = False) -> torch.Tensor:
+    """residual + x·Wᵀ of a row-parallel (or unsharded) projection plus its low-rank update. Under tensor parallelism A
+    follows the weight's columns and B is replicated: the ranks' partial x_local·A_localᵀ are summed (all-reduce, or
+    reduce-scatter of rows under sequence parallelism) before B applies."""
+    from ..ops.gemm import row_parallel_linear_residual
+    from ..parallel.tensor_parallel import (reduce_from_tensor_parallel, scatter_sequence_parallel,
+                                            sp_row_linear_residual)
+
+    st, tp = getattr(layer, "lora", None), getattr(layer, "tp", None)
+    w = getattr(layer, name)
+    pair = None if st is None else st.pair(layer.idx, name)
+    g = tp.group if tp is not None and tp.size > 1 else None
+    if g is None:
+        out = residual + linear(x, w)
+        return out if pair is None else out + lora_delta(x, pair[0], pair[1], st.scale, st.dropout)
+    sp = tp.sequence_parallel
+    out = (sp_row_linear_residual(x, w, residual, tp, last=last) if sp
+           else row_parallel_linear_residual(x, w, residual, tp, last=last))
+    if pair is None:
+        return out
+    low = linear(torch.nn.functional.dropout(x, st.dropout) if st.dropout > 0 and torch.is_grad_enabled() else x, pair[0])
+    low = scatter_sequence_parallel(low, g) if sp else reduce_from_tensor_parallel(low, g)
+    return out + linear(low, pair[1]) * st.scale
+
+
 def apply_lora(model, *, rank: int, alpha: float | None = None, dropout: float = 0.0,
                targets=("attention", "mlp"), seed: int = 0, tp=None) -> LoRAState:
     """tp: the model's tensor-parallel context (None or size 1: one rank holds whole projections). Under tensor

@@ -196,44 +196,12 @@ class DecoderLayer(nn.Module):
         product follows the projection: a column-parallel adapter multiplies the replicated x·Aᵀ by its B shard
         (gathered rows under sequence parallelism), a row-parallel adapter sums its x_local·A_localᵀ over the
         ranks (a [rows, r] all-reduce, or reduce-scatter of rows) and applies the replicated B."""
-        from ..adapters.lora import lora_delta
+        from ..adapters.lora import adapted_column_linear, adapted_row_linear
         from ..ops.activation import swiglu
-        from ..parallel.tensor_parallel import (copy_to_tensor_parallel, gather_sequence_parallel,
-                                                reduce_from_tensor_parallel, scatter_sequence_parallel)
 
-        cfg, st, tp = self.cfg, self.lora, self.tp
-        g = tp.group if tp is not None and tp.size > 1 else None
-        sp = g is not None and tp.sequence_parallel
-
-        def low_rank(x, a):
-            if st.dropout > 0 and torch.is_grad_enabled():
-                x = torch.nn.functional.dropout(x, st.dropout)
-            return linear(x, a)
-
-        def column(x, name):
-            w, pair = getattr(self, name), st.pair(self.idx, name)
-            if g is None:
-                return linear(x, w) if pair is None else linear(x, w) + lora_delta(x, pair[0], pair[1], st.scale, st.dropout)
-            base = sp_column_linear(x, w, tp) if sp else linear(x, w, tp)
-            if pair is None:
-                return base
-            low = low_rank(x, pair[0])
-            low = gather_sequence_parallel(low, g) if sp else copy_to_tensor_parallel(low, g)
-            return base + linear(low, pair[1]) * st.scale
-
-        def row(x, name, res, last=False):
-            w, pair = getattr(self, name), st.pair(self.idx, name)
-            if g is None:
-                out = res + linear(x, w)
-                return out if pair is None else out + lora_delta(x, pair[0], pair[1], st.scale, st.dropout)
-            out = (sp_row_linear_residual(x, w, res, tp, last=last) if sp
-                   else row_parallel_linear_residual(x, w, res, tp, last=last))
-            if pair is None:
-                return out
-            low = low_rank(x, pair[0])                       # partial sums: this rank's slice of the inputs
-            low = scatter_sequence_parallel(low, g) if sp else reduce_from_tensor_parallel(low, g)
-            return out + linear(low, pair[1]) * st.scale
-
+        cfg = self.cfg
+        column = lambda x, name: adapted_column_linear(self, x, name)
+        row = lambda x, name, res, last=False: adapted_row_linear(self, x, name, res, last)
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
         qkv = qk_norm_rope(column(y, "w_qkv"), positions, inv_freq, self.q_norm, self.k_norm, cfg.num_attention_heads,
                            cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)

@@ -304,9 +304,11 @@ class GatedDeltaLayer(nn.Module):
         cfg = self.cfg
         rows = attend.block_rows
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
+        tp = self.tp
+        if getattr(self, "lora", None) is not None and tp is not None:
+            return self._forward_adapted_tensor_parallel(h, y, rows)
         if getattr(self, "lora", None) is not None:
             return _adapted_mlp(self, h + _adapted_linear(self, self.mix(y, rows), "w_out"))
-        tp = self.tp
         if tp is not None and tp.sequence_parallel:
             # h holds this rank's rows of the residual stream: the column-parallel projections gather the rows on the
             # way in (the recurrence needs whole sequences, of this rank's heads), the row-parallel ones scatter the sum
@@ -323,6 +325,17 @@ class GatedDeltaLayer(nn.Module):
         h = linear_residual(self.mix(y, rows), self.w_out, h)
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
         return row_parallel_linear_residual(linear_swiglu(y2, self.w_gate_up), self.w_down, h, None, last=True)
+
+
+    def _forward_adapted_tensor_parallel(self, h, y, rows):
+        """Adapters under tensor (and sequence) parallelism: column-parallel projections add the replicated x·Aᵀ times
+        this rank's B, row-parallel ones sum their partial x·Aᵀ over the ranks before the replicated B."""
+        from ..adapters.lora import adapted_column_linear as column, adapted_row_linear as row
+
+        feats = self.mix(None, rows, projected=column(self, y, "w_in"))
+        h = row(self, feats, "w_out", h)
+        y2, _ = rmsnorm(h, self.post_norm, self.cfg.rms_norm_eps)
+        return row(self, swiglu(column(self, y2, "w_gate_up")), "w_down", h, last=True)
 
 
 class GatedAttentionLayer(nn.Module):
@@ -371,7 +384,22 @@ class GatedAttentionLayer(nn.Module):
         y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
         return row_parallel_linear_residual(linear_swiglu(y2, self.w_gate_up, tp), self.w_down, h, tp, last=True)
 
+    def _forward_adapted_tensor_parallel(self, h, positions, inv_freq, attend):
+        from ..adapters.lora import adapted_column_linear as column, adapted_row_linear as row
+
+        cfg = self.cfg
+        y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
+        qkv = qk_norm_rope(column(self, y, "w_qkv"), positions, inv_freq, self.q_norm, self.k_norm,
+                           cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
+        gate = torch.sigmoid(column(self, y, "w_attn_gate").float())
+        a = (attend(qkv, self.idx).float() * gate).to(h.dtype)
+        h = row(self, a, "w_o", h)
+        y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
+        return row(self, swiglu(column(self, y2, "w_gate_up")), "w_down", h, last=True)
+
     def forward(self, h, positions, inv_freq, attend):
+        if self.tp is not None and getattr(self, "lora", None) is not None:
+            return self._forward_adapted_tensor_parallel(h, positions, inv_freq, attend)
         if self.tp is not None:
             return self._forward_tensor_parallel(h, positions, inv_freq, attend)
         cfg = self.cfg

@@ -93,9 +93,9 @@ class TrainingSession:
             from ..adapters.lora import apply_lora
 
             tp_ctx = getattr(self.model, "tp", None)
-            if tp_ctx is not None and (self.cfg.is_hybrid or self.cfg.is_moe):
-                raise ValueError("LoRA adapters support the dense decoder at any tensor-parallel degree, and the "
-                                 "mixture-of-experts decoder and the hybrid family on one tensor-parallel rank")
+            if tp_ctx is not None and self.cfg.is_moe:
+                raise ValueError("LoRA adapters support the dense decoder and the hybrid family at any tensor-parallel "
+                                 "degree, and the mixture-of-experts decoder on one tensor-parallel rank")
             self.lora = apply_lora(self.model, rank=spec.adapter.rank, alpha=spec.adapter.alpha,
                                    dropout=spec.adapter.dropout, targets=spec.adapter.targets or ("attention", "mlp"),
                                    seed=seed, tp=tp_ctx)
