@@ -78,6 +78,11 @@ CASES = {
                                             adapter={"type": "lora", "rank": 4, "alpha": 8.0, "targets": ["attention", "experts"]}),
                                     dict(model=MOE, objective={"block_size": 32},
                                          adapter={"type": "lora", "rank": 4, "alpha": 8.0, "targets": ["attention", "experts"]})),
+    "moe adapters incl. experts x tp2 + sp": (2, dict(model={**MOE, "moe_shared_intermediate_size": 64}, objective={"block_size": 32},
+                                                   topology={"tensor_parallel_size": 2, "sequence_parallel": True},
+                                                   adapter={"type": "lora", "rank": 4, "alpha": 8.0, "targets": ["attention", "mlp", "experts"]}),
+                                              dict(model={**MOE, "moe_shared_intermediate_size": 64}, objective={"block_size": 32},
+                                                   adapter={"type": "lora", "rank": 4, "alpha": 8.0, "targets": ["attention", "mlp", "experts"]})),
     "clean-replica sharing cp2 bp4": (4, dict(topology={"context_parallel_size": 2, "block_parallel_size": 4}), dict()),
     "streaming transport x contiguous shards": (2, dict(topology=CSBP2, kernel={"cp_bp_clean_kv_transport": "streaming",
                                                                                  "cp_bp_clean_kv_layout": "contiguous"}), dict()),

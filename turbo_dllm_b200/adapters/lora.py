@@ -217,6 +217,10 @@ def apply_lora(model, *, rank: int, alpha: float | None = None, dropout: float =
         ep_rank = getattr(model.layers[0].experts, "ep_rank", 0)
         egen = torch.Generator(device=base.data.device)
         egen.manual_seed(seed + 977 + 131 * ep_rank)          # experts differ per expert-parallel rank
+        if tp_size > 1 and getattr(tp, "sequence_parallel", False):
+            # the experts (and their pairs) are replicated over the tensor-parallel ranks, which route their own rows
+            for p in flat_experts.params.values():
+                p.tp_partial = True
         with torch.no_grad():
             flat_experts.data.zero_()
             for name, p in flat_experts.params.items():

@@ -302,6 +302,20 @@ class MoEDecoderLayer(nn.Module):
 
         cfg, tp = self.cfg, self.tp
         sp = tp.sequence_parallel
+        if getattr(self, "lora", None) is not None:
+            # adapters: tensor-parallel low-rank products on the attention and dense-branch projections; the experts'
+            # own pairs (replicated like the experts) are applied inside the expert bank
+            from ..adapters.lora import adapted_column_linear as acol, adapted_row_linear as arow
+
+            y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
+            qkv = qk_norm_rope(acol(self, y, "w_qkv"), positions, inv_freq, self.q_norm, self.k_norm,
+                               cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps)
+            h = arow(self, attend(qkv, self.idx), "w_o", h)
+            y2, _ = rmsnorm(h, self.post_norm, cfg.rms_norm_eps)
+            out = h + self.experts(y2)
+            if self.w_gate_up is None:
+                return out
+            return arow(self, swiglu(acol(self, y2, "w_gate_up")), "w_down", out, last=True)
         column = (lambda x, w, **kw: sp_column_linear(x, w, tp, **kw)) if sp else None
         y, _ = rmsnorm(h, self.input_norm, cfg.rms_norm_eps)
         qkv = column(y, self.w_qkv) if sp else linear(y, self.w_qkv, tp)

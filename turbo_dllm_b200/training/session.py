@@ -93,9 +93,6 @@ class TrainingSession:
             from ..adapters.lora import apply_lora
 
             tp_ctx = getattr(self.model, "tp", None)
-            if tp_ctx is not None and self.cfg.is_moe:
-                raise ValueError("LoRA adapters support the dense decoder and the hybrid family at any tensor-parallel "
-                                 "degree, and the mixture-of-experts decoder on one tensor-parallel rank")
             self.lora = apply_lora(self.model, rank=spec.adapter.rank, alpha=spec.adapter.alpha,
                                    dropout=spec.adapter.dropout, targets=spec.adapter.targets or ("attention", "mlp"),
                                    seed=seed, tp=tp_ctx)
@@ -143,7 +140,8 @@ class TrainingSession:
                 dist.group.WORLD if self.world > 1 else None)
             expert_group = runtime.optimizer_group if runtime is not None else dense_group
             if self.lora is not None:     # only the adapters train: replicated pairs and per-expert pairs
-                self.optimizer = FlatAdamW(self.lora.flat, group=dense_group, **okw)
+                lora_tp = runtime.tensor_group if (runtime is not None and runtime.tensor_parallel_size > 1) else None
+                self.optimizer = FlatAdamW(self.lora.flat, group=dense_group, tp_group=lora_tp, **okw)
                 if self.lora.flat_experts is not None:
                     self.expert_optimizer = FlatAdamW(self.lora.flat_experts, group=expert_group, **okw)
             else:
@@ -587,6 +585,8 @@ class TrainingSession:
             sync_partial_gradients(self.model.flat.params.values(), tp)
             if getattr(self, "lora", None) is not None:
                 sync_partial_gradients(self.lora.flat.params.values(), tp)
+                if self.lora.flat_experts is not None:
+                    sync_partial_gradients(self.lora.flat_experts.params.values(), tp)
 
     def _phase(self, name: str):
         return self.phase_timer.phase(name, self.trace)
