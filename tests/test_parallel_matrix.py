@@ -100,6 +100,20 @@ def test_combination_matches_single_process(name):
 
 
 @pytest.mark.distributed
+def test_hybrid_parameter_sharding_equals_the_sharded_optimizer():
+    """Hybrid family with `optimizer.backend: fsdp` under context-sharded block parallelism (2 ranks)."""
+    kw = dict(model=HYBRID, objective=V2, topology=CSBP2)
+    a = run_ranks(_run, 2, args=(_spec(optimizer={"backend": "torch_adamw"}, **kw), 3), deadline_s=400)[0]
+    b = run_ranks(_run, 2, args=(_spec(optimizer={"backend": "fsdp"}, **kw), 3), deadline_s=400)[0]
+    assert b[0] == pytest.approx(a[0], rel=3e-4, abs=3e-4) and b[1] == pytest.approx(a[1], rel=1e-3)
+    from turbo_dllm_b200.config.run_spec import RunSpec, RunSpecError
+
+    with pytest.raises(RunSpecError, match="without tensor parallelism"):
+        RunSpec.from_mapping(_spec(model=HYBRID, objective=V2, topology={"tensor_parallel_size": 2},
+                                   optimizer={"backend": "fsdp"})).validate(world_size=4)
+
+
+@pytest.mark.distributed
 def test_parameter_sharding_equals_the_sharded_optimizer_on_a_three_axis_topology():
     """Data parallelism 2 x tensor parallelism 2 with sequence parallelism x context-sharded block parallelism 2
     (8 ranks): parameter sharding and the sharded optimizer give the same step."""

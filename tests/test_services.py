@@ -199,7 +199,7 @@ def test_family_executors_and_registration():
     assert executor_for_family("qwen3_8").capabilities.tensor_parallel
     assert executor_for_family("qwen3_8").capabilities.sequence_parallel
     assert executor_for_family("diffusion_gemma").capabilities.tensor_parallel
-    assert not executor_for_family("qwen3_8").capabilities.parameter_sharding
+    assert executor_for_family("qwen3_8").capabilities.parameter_sharding
     assert not executor_for_family("dflash").capabilities.tensor_parallel
     spec = RunSpec.from_mapping({
         "model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "num_layers": 1},
@@ -214,7 +214,8 @@ def test_family_executors_and_registration():
                       "block_parallel_size": 2}, "objective": {"name": "fast_dllm_v2"}}))
     assert not executor_for_family("diffusion_gemma").validate_run_spec(spec.with_overrides(
         {"topology": {"tensor_parallel_size": 2, "sequence_parallel": True}}))
-    problems = hybrid.validate_run_spec(spec.with_overrides({"optimizer": {"backend": "fsdp"}, "objective": {"name": "fast_dllm_v2"}}))
+    problems = hybrid.validate_run_spec(spec.with_overrides({"optimizer": {"backend": "fsdp"}, "objective": {"name": "fast_dllm_v2"},
+                                                             "topology": {"tensor_parallel_size": 2}}))
     assert any("fsdp" in p for p in problems)
     problems = executor_for_family("dflash").validate_run_spec(spec.with_overrides(
         {"topology": {"tensor_parallel_size": 2}, "objective": {"name": "dflash_distillation"}}))

@@ -169,7 +169,7 @@ class RunSpec:
             need(tr.activation_checkpointing, "optimizer.backend=fsdp needs training.activation_checkpointing")
             need(self.adapter.type == "none", "optimizer.backend=fsdp shards the base model: adapters use the "
                                               "sharded-optimizer backends (auto, zero_fused, torch_*)")
-            need(o.name != "dflash_distillation" and m.family != "qwen3_8",
+            need(o.name != "dflash_distillation",
                  "optimizer.backend=fsdp is built for the dense decoder and the mixture-of-experts decoder (its "
                  "replicated part; the experts are divided by expert parallelism)")
         if self.data.optimizer_step_unit == "trajectory":

@@ -204,7 +204,8 @@ class MoEExecutor(_ExecutorBase):
 class HybridExecutor(_ExecutorBase):
     """Gated DeltaNet + gated softmax attention (dllm_parallel/core/models/backbones/qwen3_8/executor.py:192-413)."""
 
-    capabilities = BackboneCapabilities(tensor_parallel=True, sequence_parallel=True, lora=True, head_dims=(128,))
+    capabilities = BackboneCapabilities(tensor_parallel=True, sequence_parallel=True, lora=True, parameter_sharding=True,
+                                        head_dims=(128,))
     kernel_policy = BackboneKernelPolicy(optional_symbols=("tdllm_gdn_scan_fwd", "tdllm_gdn_scan_bwd"))
 
     def __init__(self, family: ModelFamilySpec):
@@ -212,7 +213,10 @@ class HybridExecutor(_ExecutorBase):
 
     def validate_run_spec(self, spec, world_size: int | None = None) -> list[str]:
         out = super().validate_run_spec(spec, world_size)
-        t = spec.topology
+        if spec.optimizer.backend in ("fsdp", "fsdp2") and spec.topology.tensor_parallel_size > 1:
+            # the per-head vectors of the linear-attention layers are tensor-parallel shards among the non-decayed
+            # parameters; the sharded optimizer's gradient norm separates sharded from replicated by decay only
+            out.append("optimizer.backend=fsdp for the hybrid family is built without tensor parallelism")
         return out
 
     def build_model(self, ctx: BuildContext):

@@ -174,9 +174,9 @@ class TrainingSession:
             if o.backend in ("fsdp", "fsdp2") and group is not None and dist.get_world_size(group) > 1:
                 from ..parallel.fsdp import ShardedAdamW, ShardedParameters
 
-                if self.lora is not None or self.cfg.is_hybrid:
-                    raise ValueError("optimizer.backend=fsdp shards the dense decoder's parameters; adapters and the "
-                                     "hybrid family use the sharded-optimizer backends")
+                if self.lora is not None:
+                    raise ValueError("optimizer.backend=fsdp shards the base model's parameters; adapter runs use the "
+                                     "sharded-optimizer backends")
                 peer = (self.device.type == "cuda" and spec.kernel.impl not in ("cpu_reference", "nccl_baseline"))
                 if peer:
                     from ..parallel.symm import peer_access_available
