@@ -89,14 +89,35 @@ CASES = {
 }
 
 
+def _run_many(rank, world, cases):
+    """Several combinations in one group of spawned ranks (starting the ranks costs more than the steps)."""
+    import torch.distributed as dist
+
+    out = {}
+    for name, mapping in cases:
+        out[name] = _run(rank, world, mapping)
+        dist.barrier()
+    return out
+
+
 @pytest.mark.distributed
-@pytest.mark.parametrize("name", sorted(CASES))
-def test_combination_matches_single_process(name):
-    world, parallel, reference = CASES[name]
-    ref = _run(0, 1, _spec(**reference))
-    losses, norm = run_ranks(_run, world, args=(_spec(**parallel),), deadline_s=400)[0]
-    assert losses == pytest.approx(ref[0], rel=3e-4, abs=3e-4)
-    assert norm == pytest.approx(ref[1], rel=4e-3)
+@pytest.mark.parametrize("world", [2, 4])
+def test_combinations_match_single_process(world):
+    """Every combination of `CASES` that runs on `world` ranks (TDLLM_MATRIX_CASE=<name> runs one of them alone)."""
+    import os
+
+    only = os.environ.get("TDLLM_MATRIX_CASE")
+    names = [n for n in sorted(CASES) if CASES[n][0] == world and (only is None or n == only)]
+    if not names:
+        pytest.skip("no combination selected for this number of ranks")
+    refs = {n: _run(0, 1, _spec(**CASES[n][2])) for n in names}
+    got = run_ranks(_run_many, world, args=([(n, _spec(**CASES[n][1])) for n in names],), deadline_s=900)[0]
+    wrong = []
+    for n in names:
+        losses, norm = got[n]
+        if losses != pytest.approx(refs[n][0], rel=3e-4, abs=3e-4) or norm != pytest.approx(refs[n][1], rel=4e-3):
+            wrong.append(f"{n}: {losses} / {norm} against {refs[n][0]} / {refs[n][1]}")
+    assert not wrong, "\n".join(wrong)
 
 
 @pytest.mark.distributed
