@@ -191,6 +191,13 @@ class TrainingSession:
                                            tp_group=tp_group,
                                            fused_sync=None if tp_group is not None else self._build_fused_sync(group),
                                            **okw)
+        if (spec.data.optimizer_step_unit == "trajectory" and self.dp_size > 1
+                and (self.sharded is not None or getattr(self, "ep_group", None) is not None)):
+            # data-parallel ranks take different trajectories, so their optimizer steps have different numbers of
+            # micro-batches; parameter sharding and expert parallelism run collectives among those ranks inside every
+            # forward and backward pass, which would no longer pair up
+            raise ValueError("data.optimizer_step_unit=trajectory with more than one data-parallel rank needs replicated "
+                             "parameters and no expert parallelism (use the sharded-optimizer backends)")
         self.scheduler = RunSpecLRScheduler.from_run_spec(spec)
         self.steps_done = 0
         self.memory_report("session built")
