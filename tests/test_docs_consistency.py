@@ -94,3 +94,15 @@ def test_every_packaged_recipe_validates_and_is_listed():
         RunSpec.from_mapping(yaml.safe_load(recipe_text(name))).validate()
     on_disk = {p.stem for p in (ROOT / "turbo_dllm_b200" / "recipes").rglob("*.yaml") if p.name != "manifest.yaml"}
     assert on_disk == {n.split("/")[-1] for n in names}
+
+
+def test_shell_scripts_parse_and_are_executable():
+    """Every shipped shell script passes `bash -n` and carries the executable bit."""
+    import os
+    import subprocess
+
+    scripts = sorted(ROOT.glob("packaging/**/*.sh")) + sorted((ROOT / "turbo_dllm_b200" / "cli").glob("*.sh"))
+    assert len(scripts) >= 10
+    for sh in scripts:
+        assert subprocess.run(["bash", "-n", str(sh)], capture_output=True).returncode == 0, sh
+        assert os.access(sh, os.X_OK), f"{sh} is not executable"
