@@ -26,8 +26,7 @@ from typing import Any
 import numpy as np
 import torch
 
-from .artifacts import (INDEXED_FORMAT, PACKED_TOKEN_FORMAT, ArtifactError, load_manifest,
-                        validate_artifact_for_run)
+from .artifacts import INDEXED_FORMAT, PACKED_TOKEN_FORMAT, ArtifactError, load_manifest
 from .runtimes import DataBatch, DataRuntime
 
 

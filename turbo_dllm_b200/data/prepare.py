@@ -44,7 +44,7 @@ from typing import Any, Callable, Iterator, Mapping, Sequence
 import numpy as np
 import yaml
 
-from .artifacts import ArtifactError, write_indexed_artifact, write_packed_artifact
+from .artifacts import write_indexed_artifact, write_packed_artifact
 
 PREPARE_FORMAT = "dllm.data.prepare.v1"
 SOURCE_ENTRY_POINT_GROUP = "turbo_dllm_b200.data_sources"

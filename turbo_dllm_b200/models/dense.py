@@ -26,7 +26,7 @@ from ..ops.gemm import linear, linear_residual, linear_swiglu, row_parallel_line
 from ..ops.linear_ce import linear_cross_entropy
 from ..ops.norm import rmsnorm
 from ..ops.rope import qk_norm_rope, rope_inv_freq
-from ..parallel.tensor_parallel import (TPContext, copy_to_tensor_parallel, gather_rows_replicated_grad,
+from ..parallel.tensor_parallel import (TPContext, gather_rows_replicated_grad,
                                         sp_column_linear, sp_row_linear_residual, take_rows_sequence_parallel,
                                         vocab_parallel_embedding, vocab_parallel_linear_cross_entropy)
 from .activation_store import ActivationStore, checkpointed_layer

@@ -20,7 +20,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ..ops.attention import MaskLayout, block_attention
+from ..ops.attention import MaskLayout
 from ..ops.dflash2 import grouped_dynamic_conv, transform_logits
 from ..ops.gemm import linear, linear_swiglu
 from ..ops.norm import rmsnorm

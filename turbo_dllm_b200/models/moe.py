@@ -29,7 +29,7 @@ from ..ops.gemm import linear, linear_residual
 from ..ops.norm import rmsnorm
 from ..ops.rope import qk_norm_rope
 from .config import ModelConfig
-from .dense import BlockDiffusionTransformer, DecoderLayer, FlatParams
+from .dense import BlockDiffusionTransformer, FlatParams
 
 def route_topk(logits: torch.Tensor, k: int):
     """softmax over experts, top-k, renormalise. Returns (weights [rows,k] fp32, experts [rows,k] int64)."""

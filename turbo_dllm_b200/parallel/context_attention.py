@@ -28,7 +28,7 @@ import torch
 import torch.distributed as dist
 
 from ..models.config import ModelConfig
-from ..ops.attention import attention_reference, block_attention, block_diffusion_layout, split_packed_qkv
+from ..ops.attention import block_attention, block_diffusion_layout, split_packed_qkv
 from ..profiling.operator_trace import communication_scope
 from .layout import PackedLayout, clean_positions_for_rank, runtime_clean_layout
 

@@ -30,7 +30,6 @@ ZeRO partitioning of dllm_parallel/core/optim/zero.py:93-211.
 """
 from __future__ import annotations
 
-import ctypes
 import math
 import re
 from dataclasses import dataclass

@@ -16,7 +16,6 @@ Counterpart in the reference: Transformer Engine's userbuffers overlap of the ro
 """
 from __future__ import annotations
 
-import ctypes
 
 import torch
 import torch.distributed as dist

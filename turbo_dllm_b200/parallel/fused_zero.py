@@ -8,7 +8,6 @@ re-pointed).
 """
 from __future__ import annotations
 
-import ctypes
 
 import torch
 import torch.distributed as dist

@@ -11,7 +11,7 @@ Counterpart of ParallelRuntime / build_parallel_runtime / warm_parallel_runtime_
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist

@@ -25,7 +25,6 @@ import torch.distributed as dist
 from ..profiling import collectives as coll
 
 from ..ops.gemm import EPI_CE_GRAD, EPI_CE_STATS, gemm
-from ..ops.linear_ce import linear_ce_reference
 
 
 # ---------------------------------------------------------------- mappings

@@ -21,7 +21,7 @@ import torch.distributed as dist
 from ..config.run_spec import RunSpec
 from ..data.runtimes import DataBatch, HostStagedRandomRuntime, RandomTokenDataRuntime
 from ..models.config import ModelConfig, model_config_from_run_spec
-from ..models.dense import BlockDiffusionTransformer, LocalAttention, compact_supervised_rows
+from ..models.dense import LocalAttention, compact_supervised_rows
 from ..objectives.runtime import CorruptedBatch, build_objective_runtime
 from ..optim.flat_adamw import FlatAdamW
 from ..optim.schedule import RunSpecLRScheduler
