@@ -112,3 +112,48 @@ def test_training_steps_with_packed_and_padded_batches():
     assert out[True][2] == 2 * 64 and out[False][2] == 2 * 128        # a third of the noisy rows are gone
     # both forms score the same 120 tokens; their losses are of the same size (different noise draws)
     assert abs(out[True][0] - out[False][0]) < 0.5 * out[False][0]
+
+
+def _packed_sft_run(rank, world, tp, sp, path, steps=3):
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    torch.set_num_threads(2)
+    spec = RunSpec.from_mapping({
+        "model": {"id": "synthetic:tiny-qwen3", "seq_len": 128, "dtype": "fp32", "num_layers": 2, "family": "diffusion_gemma"},
+        "objective": {"name": "diffusiongemma_native_sft", "block_size": 16, "noise_schedule": "loglinear",
+                      "loss_weighting": "unit", "self_conditioning_probability": 0.5, "sampling_epsilon_min": 0.1},
+        "data": {"input_mode": "dataset", "dataset_path": path},
+        "training": {"batch_size": 2, "steps": steps},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": 1, "tensor_parallel_size": tp, "sequence_parallel": sp},
+        "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
+    rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
+    s = TrainingSession(spec, device="cpu", runtime=rt)
+    assert s.objective.pack_response_suffix
+    out = []
+    for _ in range(steps):
+        r = s.step()
+        out.append(float(r.loss_sum) / float(r.denominator))
+    return out, float(s.optimizer.grad_norm()), int(s.layout.n_noisy)
+
+
+def test_response_packing_under_tensor_and_sequence_parallelism(tmp_path):
+    """Tensor parallelism divides heads, not rows: the decoder rows still cover the response only, and the step equals
+    the single-process packed step."""
+    import numpy as np
+
+    from tests._harness import run_ranks
+    from turbo_dllm_b200.data.artifacts import write_indexed_artifact
+
+    rng = np.random.default_rng(0)
+    samples = []
+    for i in range(32):
+        mask = np.zeros(128, np.uint8)
+        mask[[32, 64][i % 2]:] = 1
+        samples.append({"tokens": rng.integers(0, 1000, 128).astype(np.int32), "loss_mask": mask, "sample_id": i})
+    write_indexed_artifact(tmp_path / "idx", samples, metadata={"tokenizer": {"vocab_size": 1024}})
+    ref = _packed_sft_run(0, 1, 1, False, str(tmp_path / "idx"))
+    assert ref[2] < 2 * 128                                  # fewer decoder rows than whole sequences would need
+    for out in run_ranks(_packed_sft_run, 2, args=(2, True, str(tmp_path / "idx")), deadline_s=300):
+        assert out[0] == pytest.approx(ref[0], rel=3e-4) and out[1] == pytest.approx(ref[1], rel=4e-3) and out[2] == ref[2]

@@ -109,10 +109,10 @@ class TrainingSession:
                                                  seed=seed + 7919 * (dp_rank + 1), device=self.device,
                                                  vocab_size=self.cfg.vocab_size)
         if hasattr(self.objective, "pack_response_suffix") and (
-                self.cfg.is_hybrid or (runtime is not None and (runtime.local_parallel_size > 1
-                                                                or runtime.tensor_parallel_size > 1))):
-            # context / block / tensor parallelism plan their rows for whole sequences: the response stays in place
-            # and the supervision mask selects the scored rows
+                self.cfg.is_hybrid or (runtime is not None and runtime.local_parallel_size > 1)):
+            # context / block parallelism plan their rows for whole sequences (and the hybrid family scans whole
+            # sequences): the response stays in place and the supervision mask selects the scored rows. Tensor
+            # parallelism divides heads, not rows, so it packs like a single rank.
             self.objective.pack_response_suffix = False
         # diffusiongemma_native_sft: the clean stream is causal and carries a next-token loss of its own
         # (dllm_parallel/core/models/backbones/nemotron/model.py:1089-1096, :1966-2030)
