@@ -66,6 +66,8 @@ CASES = {
     "native sft (dense) x tp2 + sp": (2, dict(model={"family": "diffusion_gemma"}, objective=SFT,
                                               topology={"tensor_parallel_size": 2, "sequence_parallel": True}),
                                       dict(model={"family": "diffusion_gemma"}, objective=SFT)),
+    "native sft (dense) x pure bp2": (2, dict(model={"family": "diffusion_gemma"}, objective=SFT, topology=BP2),
+                                      dict(model={"family": "diffusion_gemma"}, objective=SFT)),
     "gradient accumulation x csbp2": (2, dict(topology=CSBP2, training={"gradient_accumulation_steps": 2}),
                                       dict(training={"gradient_accumulation_steps": 2})),
     "hybrid x tp2 x bp2": (4, dict(model=HYBRID, objective=V2, topology={**BP2, "tensor_parallel_size": 2}),

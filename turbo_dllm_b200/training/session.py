@@ -384,8 +384,10 @@ class TrainingSession:
         elif rt is not None and rt.block_parallel_size > 1 and s.topology.replicate_clean_prefix:
             last = max(owned)
             # the clean tokens in front of the rank's last block; linear-attention layers scan whole sequences
-            # (their chunk states are indexed by position), so the hybrid family keeps every clean row
-            stop = s.model.seq_len if self.cfg.is_hybrid else last * s.objective.block_size
+            # (their chunk states are indexed by position), so the hybrid family keeps every clean row, and so does a
+            # run whose clean stream carries a next-token loss (every position is then scored by exactly one rank)
+            whole = self.cfg.is_hybrid or getattr(self, "encoder_loss_weight", 0.0) > 0.0
+            stop = s.model.seq_len if whole else last * s.objective.block_size
             clean = torch.arange(0, stop, device=self.device)
         offsets = None
         if rt is not None and rt.splits_block_tokens and not self.cfg.is_hybrid:
@@ -507,6 +509,13 @@ class TrainingSession:
             nxt = (lay.clean_pos + 1).clamp_max(x0.shape[1] - 1)
             enc_labels = torch.where(lay.clean_pos + 1 < valid_len, x0[lay.clean_seq, nxt],
                                      torch.full_like(nxt, -100))      # padding is neither input nor target
+            rt = self.runtime
+            if rt is not None and rt.block_parallel_size > 1 and rt.context_parallel_size == 1:
+                # block parallelism alone: every rank holds the whole clean sequence; each scores the clean positions
+                # of its own blocks, so the term is counted once over the group
+                own = torch.zeros(x0.shape[1] // lay.block_size + 1, dtype=torch.bool, device=lay.clean_pos.device)
+                own[torch.as_tensor(sorted(rt.owned_blocks), device=own.device)] = True
+                enc_labels = torch.where(own[lay.clean_pos // lay.block_size], enc_labels, torch.full_like(enc_labels, -100))
             labels = torch.cat([labels[:n_noisy], enc_labels.to(labels.dtype)])
             enc_w = self.encoder_loss_weight * float(denominator) / self._encoder_denominator
             weights = torch.cat([weights[:n_noisy], torch.full_like(weights[n_noisy:], enc_w)])
