@@ -201,7 +201,15 @@ def run_training(spec: RunSpec) -> dict:
                     emit({"event": "duration_limit", "step": step, "elapsed_seconds": control.elapsed()})
                 break
         mean_ms = sum(timed_ms) / len(timed_ms) if timed_ms else float("nan")
+        # every rank's own figures, gathered as Python objects over the host-side group: the summary shows which rank
+        # is slow or holds the most memory (dllm_parallel/training/block_diffusion_trainer.py:1771-1806)
+        mine = {"rank": rank, "avg_ms": mean_ms, "min_ms": min(timed_ms) if timed_ms else None,
+                "max_ms": max(timed_ms) if timed_ms else None, "measured_steps": len(timed_ms),
+                "peak_mib": (torch.cuda.max_memory_allocated(device) / 2 ** 20) if use_cuda else None}
+        rank_metrics = [mine]
         if world > 1:
+            rank_metrics = [None] * world
+            dist.all_gather_object(rank_metrics, mine, group=gloo)
             t = torch.tensor([mean_ms], dtype=torch.float64, device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             mean_ms = float(t)
@@ -243,7 +251,7 @@ def run_training(spec: RunSpec) -> dict:
                        "model_tflop_per_step": fl.total / 1e12, "mfu_pct": mfu, "world_size": world,
                        "parallel_layout": runtime.plan.layout if runtime else "dp",
                        "training_elapsed_seconds": time.monotonic() - t_train0, "run_context": run_ctx.to_dict(),
-                       "system_trace": trace.exported, **eval_metrics,
+                       "system_trace": trace.exported, "rank_metrics": rank_metrics, **eval_metrics,
                        **timed_counters.throughput(sum(timed_ms) / 1e3, world)}
             emit(summary)
             wb.log_event(summary)
