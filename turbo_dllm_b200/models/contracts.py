@@ -240,7 +240,8 @@ class DFlashExecutor(_ExecutorBase):
     (dllm_parallel/core/models/backbones/dflash/executor.py:36-408). The model comes with its task: the session
     builds `training.dflash_task.DFlashTask`, which owns the drafter, the verifier and the objective."""
 
-    capabilities = BackboneCapabilities(context_parallel=False, block_parallel=False)
+    # (context / block parallelism here means one drafter replica over several ranks: context rows and anchors divided)
+    capabilities = BackboneCapabilities(context_parallel=True, block_parallel=True)
 
     def __init__(self, family: ModelFamilySpec):
         self.family = family

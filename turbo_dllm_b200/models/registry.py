@@ -88,7 +88,16 @@ def infer_family(model_id: str, objective: str | None = None, architectures: tup
 
 
 def describe_supported_configs() -> dict:
-    return {"families": {f: {"objectives": list(o)} for f, o in FAMILY_OBJECTIVES.items()},
+    """Families with their objectives and what each family's executor can run (parallel axes, parameter sharding,
+    adapters, attention head widths): what `dllm-train --print-supported-configs` prints."""
+    from dataclasses import asdict
+
+    fams = {}
+    for f, o in FAMILY_OBJECTIVES.items():
+        caps = asdict(executor_for_family(f).capabilities)
+        caps["head_dims"] = list(caps.get("head_dims", ()))
+        fams[f] = {"objectives": list(o), "capabilities": caps}
+    return {"families": fams,
             "optimizer_backends": list(OPTIMIZER_BACKENDS),
             "dtypes": ["bf16", "fp16", "fp32"],
             "parallel_axes": ["data", "context", "block", "tensor", "expert", "pipeline (size 1 only)"]}
