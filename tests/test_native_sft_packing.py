@@ -114,7 +114,7 @@ def test_training_steps_with_packed_and_padded_batches():
     assert abs(out[True][0] - out[False][0]) < 0.5 * out[False][0]
 
 
-def _packed_sft_run(rank, world, tp, sp, path, steps=3):
+def _packed_sft_run(rank, world, tp, sp, path, steps=3, bp=1):
     from turbo_dllm_b200.config.run_spec import RunSpec
     from turbo_dllm_b200.parallel.runtime import build_parallel_runtime
     from turbo_dllm_b200.training.session import TrainingSession
@@ -123,10 +123,12 @@ def _packed_sft_run(rank, world, tp, sp, path, steps=3):
     spec = RunSpec.from_mapping({
         "model": {"id": "synthetic:tiny-qwen3", "seq_len": 128, "dtype": "fp32", "num_layers": 2, "family": "diffusion_gemma"},
         "objective": {"name": "diffusiongemma_native_sft", "block_size": 16, "noise_schedule": "loglinear",
-                      "loss_weighting": "unit", "self_conditioning_probability": 0.5, "sampling_epsilon_min": 0.1},
+                      "loss_weighting": "unit", "self_conditioning_probability": 0.5, "sampling_epsilon_min": 0.1,
+                      "minimum_decoder_blocks": 2},
         "data": {"input_mode": "dataset", "dataset_path": path},
         "training": {"batch_size": 2, "steps": steps},
-        "topology": {"context_parallel_size": 1, "block_parallel_size": 1, "tensor_parallel_size": tp, "sequence_parallel": sp},
+        "topology": {"context_parallel_size": 1, "block_parallel_size": bp, "replicate_clean_prefix": bp > 1,
+                     "tensor_parallel_size": tp, "sequence_parallel": sp},
         "optimizer": {"lr": 1e-3, "gradient_clip_norm": 1.0}}).validate(world_size=world)
     rt = build_parallel_runtime(spec, device="cpu", rank=rank, world_size=world) if world > 1 else None
     s = TrainingSession(spec, device="cpu", runtime=rt)
@@ -157,3 +159,10 @@ def test_response_packing_under_tensor_and_sequence_parallelism(tmp_path):
     assert ref[2] < 2 * 128                                  # fewer decoder rows than whole sequences would need
     for out in run_ranks(_packed_sft_run, 2, args=(2, True, str(tmp_path / "idx")), deadline_s=300):
         assert out[0] == pytest.approx(ref[0], rel=3e-4) and out[1] == pytest.approx(ref[1], rel=4e-3) and out[2] == ref[2]
+    # block parallelism alone: the response's decoder blocks are divided over the ranks (their losses add up to the whole)
+    import torch.distributed  # noqa: F401
+
+    outs = run_ranks(_packed_sft_run, 2, args=(1, False, str(tmp_path / "idx"), 3, 2), deadline_s=300)
+    assert sum(o[2] for o in outs) == ref[2] and all(0 < o[2] < ref[2] for o in outs)
+    total = [sum(o[0][i] for o in outs) for i in range(3)]
+    assert total == pytest.approx(ref[0], rel=3e-4) and outs[0][1] == pytest.approx(ref[1], rel=4e-3)

@@ -137,16 +137,22 @@ def noisy_rows(*, seq_len: int, block_size: int, batch: int, views: int = 1, own
 
 def build_response_layout(*, seq_len: int, block_size: int, batch: int, response_start: int, valid_length: int,
                           decoder_length: int, window: int | None = None, device="cpu",
-                          clean_causal: bool = False) -> PackedLayout:
+                          clean_causal: bool = False, owned_blocks=None) -> PackedLayout:
     """Rows of a batch whose noisy (decoder) rows cover only the response [response_start, valid_length): for every
     sequence `decoder_length` rows (whole blocks counted from the response start; rows past the response are
     padding at the last valid position), then all clean positions. A decoder block sees the clean tokens before
-    its own first position. Layout of dllm_parallel/core/objectives/diffusiongemma.py:226-250."""
+    its own first position. `owned_blocks`: the decoder blocks (counted from the response start) whose rows this
+    rank holds under block parallelism; all of them by default.
+    Layout of dllm_parallel/core/objectives/diffusiongemma.py:226-250."""
     off1 = torch.arange(decoder_length, device=device)
     nblk = decoder_length // block_size
+    if owned_blocks is not None:
+        keep = torch.zeros(nblk, dtype=torch.bool, device=device)
+        keep[torch.as_tensor(sorted(owned_blocks), device=device)] = True
+        off1 = off1[keep[off1 // block_size]]
     seq_ids = torch.arange(batch, device=device)
     noisy_off = off1.repeat(batch)
-    noisy_seq = seq_ids.repeat_interleave(decoder_length)
+    noisy_seq = seq_ids.repeat_interleave(off1.numel())
     noisy_pos = (noisy_off + response_start).clamp(max=valid_length - 1)
     noisy_view = torch.zeros_like(noisy_seq)
     blk = noisy_off // block_size

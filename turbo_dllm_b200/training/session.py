@@ -109,11 +109,15 @@ class TrainingSession:
                                                  seed=seed + 7919 * (dp_rank + 1), device=self.device,
                                                  vocab_size=self.cfg.vocab_size)
         if hasattr(self.objective, "pack_response_suffix") and (
-                self.cfg.is_hybrid or (runtime is not None and runtime.local_parallel_size > 1)):
-            # context / block parallelism plan their rows for whole sequences (and the hybrid family scans whole
-            # sequences): the response stays in place and the supervision mask selects the scored rows. Tensor
-            # parallelism divides heads, not rows, so it packs like a single rank.
+                self.cfg.is_hybrid or (runtime is not None and runtime.context_parallel_size > 1)):
+            # context parallelism plans its clean shards and exchanges for whole sequences (and the hybrid family
+            # scans whole sequences): the response stays in place and the supervision mask selects the scored rows.
+            # Tensor parallelism divides heads, not rows, so it packs like a single rank; block parallelism alone
+            # divides the decoder blocks of the packed response among its ranks.
             self.objective.pack_response_suffix = False
+        elif hasattr(self.objective, "pack_response_suffix") and runtime is not None and runtime.block_parallel_size > 1:
+            # every block-parallel rank needs a decoder block: short responses are padded up to that many
+            self.objective.minimum_decoder_blocks = max(self.objective.minimum_decoder_blocks, runtime.block_parallel_size)
         # diffusiongemma_native_sft: the clean stream is causal and carries a next-token loss of its own
         # (dllm_parallel/core/models/backbones/nemotron/model.py:1089-1096, :1966-2030)
         self.encoder_loss_weight = (float(spec.objective.encoder_loss_weight)
@@ -348,12 +352,20 @@ class TrainingSession:
             if len(cache) > 64:       # response starts vary from batch to batch: keep the table bounded
                 for k in [k for k in cache if isinstance(k, tuple)][:32]:
                     del cache[k]
-            s = self.spec
+            s, rt = self.spec, self.runtime
+            owned = None
+            if rt is not None and rt.block_parallel_size > 1:
+                # block parallelism alone: the decoder blocks of the response are scheduled over the ranks like the
+                # blocks of a whole sequence (every rank keeps all clean rows)
+                from ..parallel.schedule import build_block_schedule
+
+                sched = build_block_schedule(response[2] // s.objective.block_size, rt.block_parallel_size)
+                owned = sched.blocks_by_worker[rt.block_parallel_rank]
             lay = build_response_layout(
                 seq_len=seq_len, block_size=s.objective.block_size, batch=s.training.batch_size,
                 response_start=response[0], valid_length=response[1], decoder_length=response[2],
                 window=self.cfg.sliding_window if self.cfg.has_sliding_layers else None, device=self.device,
-                clean_causal=getattr(self, "encoder_loss_weight", 0.0) > 0.0)
+                clean_causal=getattr(self, "encoder_loss_weight", 0.0) > 0.0, owned_blocks=owned)
             cache[key] = (lay, LocalAttention(getattr(self.model, "lcfg", self.cfg), lay.mask,
                                               store=self.model.store, window_mask=lay.window_mask))
         if key not in cache:
