@@ -76,7 +76,7 @@ def test_fsdp2_matches_replicated_parameters_and_resumes(tmp_path):
     ref = run_ranks(_run, 2, args=("torch_adamw", 1, None), deadline_s=300)
     out = run_ranks(_run, 2, args=("fsdp", 1, str(tmp_path / "ck")), deadline_s=300)
     for r, o in zip(ref, out):
-        assert o["losses"] == pytest.approx(r["losses"], rel=1e-5)
+        assert o["losses"] == pytest.approx(r["losses"], rel=1e-4)
         assert o["norm"] == pytest.approx(r["norm"], rel=2e-3)    # Adam amplifies summation-order noise over steps
         assert_params_close(o["params"], torch.from_numpy(r["params"]), rtol=1e-3, atol=2e-5)
         assert o["resumed_equal"] and o["backend"] == "fsdp_sharded_rank_local"
@@ -100,7 +100,7 @@ def test_fsdp2_times_tp2_matches_tp2():
     ref = run_ranks(_run, 4, args=("torch_adamw", 2, None), deadline_s=400)
     out = run_ranks(_run, 4, args=("fsdp", 2, None), deadline_s=400)
     for r, o in zip(ref, out):
-        assert o["losses"] == pytest.approx(r["losses"], rel=1e-5)
+        assert o["losses"] == pytest.approx(r["losses"], rel=1e-4)
         assert_params_close(o["params"], torch.from_numpy(r["params"]), rtol=1e-3, atol=2e-5)
 
 
@@ -193,7 +193,7 @@ def test_moe_parameter_sharding_beside_expert_parallelism(tmp_path):
     ref = run_ranks(_moe_run, 2, args=("torch_adamw", None), deadline_s=300)
     out = run_ranks(_moe_run, 2, args=("fsdp", str(tmp_path / "ck")), deadline_s=400)
     for r, o in zip(ref, out):
-        assert o["losses"] == pytest.approx(r["losses"], rel=1e-5)
+        assert o["losses"] == pytest.approx(r["losses"], rel=1e-4)
         assert o["norm"] == pytest.approx(r["norm"], rel=2e-3)
         assert_params_close(o["dense"], torch.from_numpy(r["dense"]), rtol=1e-3, atol=2e-5)
         assert_params_close(o["experts"], torch.from_numpy(r["experts"]), rtol=1e-3, atol=2e-5)
