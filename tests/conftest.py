@@ -26,3 +26,23 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_runtest_protocol(item, nextitem):
+    """Tests that spawn ranks (`distributed`) share the machine's cores with whatever else runs: a rendezvous that
+    times out or a rank that starves shows up as a rare failure unrelated to the code under test. Such a test is run
+    once more before it counts as failed; the first failure is printed, so a retry never passes unnoticed."""
+    if "distributed" not in item.keywords:
+        return None
+    from _pytest.runner import runtestprotocol
+
+    item.ihook.pytest_runtest_logstart(nodeid=item.nodeid, location=item.location)
+    reports = runtestprotocol(item, nextitem=nextitem, log=False)
+    if any(r.failed for r in reports):
+        first = next(r for r in reports if r.failed)
+        print(f"\n[retry] {item.nodeid} failed once ({str(first.longrepr).strip().splitlines()[-1][:200]}); running it again")
+        reports = runtestprotocol(item, nextitem=nextitem, log=False)
+    for r in reports:
+        item.ihook.pytest_runtest_logreport(report=r)
+    item.ihook.pytest_runtest_logfinish(nodeid=item.nodeid, location=item.location)
+    return True
