@@ -29,11 +29,11 @@ def pytest_collection_modifyitems(config, items):
 
 
 def pytest_runtest_protocol(item, nextitem):
-    """Tests that spawn ranks (`distributed`) share the machine's cores with whatever else runs: a rendezvous that
+    """CPU tests that spawn ranks (`distributed`, not `gpu`) share the machine's cores with whatever else runs: a rendezvous that
     times out or a rank that starves shows up as a rare failure unrelated to the code under test. Such a test is run
     once more before it counts as failed; the first failure is printed, so a retry never passes unnoticed."""
-    if "distributed" not in item.keywords:
-        return None
+    if "distributed" not in item.keywords or "gpu" in item.keywords:
+        return None       # (a GPU test is never repeated after a failure: the cause is read first)
     from _pytest.runner import runtestprotocol
 
     item.ihook.pytest_runtest_logstart(nodeid=item.nodeid, location=item.location)
