@@ -129,11 +129,11 @@ def test_hybrid_parameter_sharding_equals_the_sharded_optimizer():
     a = run_ranks(_run, 2, args=(_spec(optimizer={"backend": "torch_adamw"}, **kw), 3), deadline_s=400)[0]
     b = run_ranks(_run, 2, args=(_spec(optimizer={"backend": "fsdp"}, **kw), 3), deadline_s=400)[0]
     assert b[0] == pytest.approx(a[0], rel=3e-4, abs=3e-4) and b[1] == pytest.approx(a[1], rel=1e-3)
-    from turbo_dllm_b200.config.run_spec import RunSpec, RunSpecError
-
-    with pytest.raises(RunSpecError, match="without tensor parallelism"):
-        RunSpec.from_mapping(_spec(model=HYBRID, objective=V2, topology={"tensor_parallel_size": 2},
-                                   optimizer={"backend": "fsdp"})).validate(world_size=4)
+    # with tensor parallelism some non-decayed vectors are shards too: the gradient norm splits at the buffer's own boundary
+    kw = dict(model=HYBRID, objective=V2, topology={"tensor_parallel_size": 2, "sequence_parallel": True})
+    a = run_ranks(_run, 4, args=(_spec(optimizer={"backend": "torch_adamw"}, **kw), 3), deadline_s=400)[0]
+    b = run_ranks(_run, 4, args=(_spec(optimizer={"backend": "fsdp"}, **kw), 3), deadline_s=400)[0]
+    assert b[0] == pytest.approx(a[0], rel=3e-4, abs=3e-4) and b[1] == pytest.approx(a[1], rel=2e-4)
 
 
 @pytest.mark.distributed

@@ -214,9 +214,8 @@ def test_family_executors_and_registration():
                       "block_parallel_size": 2}, "objective": {"name": "fast_dllm_v2"}}))
     assert not executor_for_family("diffusion_gemma").validate_run_spec(spec.with_overrides(
         {"topology": {"tensor_parallel_size": 2, "sequence_parallel": True}}))
-    problems = hybrid.validate_run_spec(spec.with_overrides({"optimizer": {"backend": "fsdp"}, "objective": {"name": "fast_dllm_v2"},
+    assert not hybrid.validate_run_spec(spec.with_overrides({"optimizer": {"backend": "fsdp"}, "objective": {"name": "fast_dllm_v2"},
                                                              "topology": {"tensor_parallel_size": 2}}))
-    assert any("fsdp" in p for p in problems)
     problems = executor_for_family("dflash").validate_run_spec(spec.with_overrides(
         {"topology": {"tensor_parallel_size": 2}, "objective": {"name": "dflash_distillation"}}))
     assert any("tensor-parallel" in p for p in problems)

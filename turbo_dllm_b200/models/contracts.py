@@ -213,10 +213,6 @@ class HybridExecutor(_ExecutorBase):
 
     def validate_run_spec(self, spec, world_size: int | None = None) -> list[str]:
         out = super().validate_run_spec(spec, world_size)
-        if spec.optimizer.backend in ("fsdp", "fsdp2") and spec.topology.tensor_parallel_size > 1:
-            # the per-head vectors of the linear-attention layers are tensor-parallel shards among the non-decayed
-            # parameters; the sharded optimizer's gradient norm separates sharded from replicated by decay only
-            out.append("optimizer.backend=fsdp for the hybrid family is built without tensor parallelism")
         return out
 
     def build_model(self, ctx: BuildContext):

@@ -378,9 +378,27 @@ class ShardedAdamW:
         sp = self.sp
         g = sp.grad_shard
         split = sp.decay_local
-        # vector_norm reduces without a temporary and takes more than 2^31 elements (a dot product does not)
-        sharded_sq = torch.linalg.vector_norm(g[:split]).square().reshape(1)
-        repl_sq = torch.linalg.vector_norm(g[split:]).square().reshape(1)
+        boundary = getattr(sp.flat, "tp_sharded_numel", None) if self.tp_group is not None else None
+        if boundary is not None:
+            # the buffer names the end of its tensor-parallel part itself (some non-decayed vectors are sharded too):
+            # split every unit's local piece at that offset of the flat buffer
+            sharded_sq = torch.zeros(1, dtype=torch.float32, device=g.device)
+            repl_sq = torch.zeros_like(sharded_sq)
+            for u in sp.units:
+                lo = u.start + sp.rank * u.shard                    # flat offsets of this rank's piece of the unit
+                hi = min(lo + u.shard, u.stop)
+                if hi <= lo:
+                    continue
+                cut = min(max(boundary, lo), hi) - lo
+                piece = g[u.local: u.local + (hi - lo)]
+                if cut > 0:
+                    sharded_sq += torch.linalg.vector_norm(piece[:cut]).square()
+                if cut < hi - lo:
+                    repl_sq += torch.linalg.vector_norm(piece[cut:]).square()
+        else:
+            # vector_norm reduces without a temporary and takes more than 2^31 elements (a dot product does not)
+            sharded_sq = torch.linalg.vector_norm(g[:split]).square().reshape(1)
+            repl_sq = torch.linalg.vector_norm(g[split:]).square().reshape(1)
         if self.tp_group is not None:
             # matrices are split over the tensor-parallel group, norm weights are replicated on it
             dist.all_reduce(sharded_sq, group=self.tp_group)
