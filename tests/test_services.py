@@ -614,3 +614,29 @@ def test_flop_models_count_exactly_what_the_masks_allow():
     assert online.dense - offline.dense == pytest.approx(2.0 * 4096 * per_row * 36)
     assert online.head - ce.head == pytest.approx(2.0 * 128 * 16 * target.hidden_size * target.vocab_size)
     assert small.head < online.head and dflash_step_flops(draft, target, batch=3, **kw).total == pytest.approx(3 * online.total)
+
+
+def test_a_bf16_run_is_exported_on_a_machine_without_a_gpu(tmp_path):
+    """The export entry rebuilds the model in fp32 where there is no GPU and writes the run's dtype."""
+    from safetensors import safe_open
+
+    from turbo_dllm_b200.checkpoint import save_training_checkpoint
+    from turbo_dllm_b200.config.run_spec import RunSpec
+    from turbo_dllm_b200.models import hf_loader
+    from turbo_dllm_b200.models.export import export_training_checkpoint
+    from turbo_dllm_b200.training.session import TrainingSession
+
+    if torch.cuda.is_available():
+        pytest.skip("this path is for machines without a GPU")
+    base = {"model": {"id": "synthetic:tiny-qwen3", "seq_len": 64, "dtype": "fp32", "num_layers": 1},
+            "objective": {"name": "standard_block_diffusion", "block_size": 16},
+            "training": {"batch_size": 1, "steps": 1}, "topology": {"context_parallel_size": 1, "block_parallel_size": 1}}
+    s = TrainingSession(RunSpec.from_mapping(base).validate(), device="cpu")
+    s.step()
+    save_training_checkpoint(str(tmp_path / "ck"), s, step=1, rank=0, world_size=1)
+    bf16 = RunSpec.from_mapping({**base, "model": {**base["model"], "dtype": "bf16"}}).validate()
+    export_training_checkpoint(bf16, str(tmp_path / "ck"), str(tmp_path / "hf"))
+    assert hf_loader.EXPORT_DTYPE is None
+    with safe_open(str(tmp_path / "hf" / "model.safetensors"), framework="pt") as f:
+        w = f.get_tensor("model.layers.0.self_attn.o_proj.weight")
+    assert w.dtype == torch.bfloat16 and torch.equal(w, s.model.flat.params["layers.0.w_o"].to(torch.bfloat16))

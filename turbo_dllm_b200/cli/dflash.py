@@ -111,7 +111,15 @@ def run_dflash(argv) -> int:
             from ..checkpoint import load_model_weights, load_training_checkpoint, read_metadata
             from ..training.session import TrainingSession
 
+            import torch
+
+            from ..models import hf_loader
+
             spec = load_run_spec(a.config).validate()
+            if not torch.cuda.is_available() and spec.model.dtype != "fp32":
+                # no GPU here: the drafter is rebuilt in fp32 and its tensors are written in the run's dtype
+                hf_loader.EXPORT_DTYPE = {"bf16": torch.bfloat16, "fp16": torch.float16}[spec.model.dtype]
+                spec = spec.with_overrides({"model": {"dtype": "fp32"}})
             if int(read_metadata(a.checkpoint)["world_size"]) > 1:
                 # a drafter trained on several ranks: the weights are replicated, one process reads rank 0's file
                 spec = spec.with_overrides({"topology": {"context_parallel_size": 1, "block_parallel_size": 1}})
@@ -120,10 +128,13 @@ def run_dflash(argv) -> int:
             else:
                 s = TrainingSession(spec)
                 load_training_checkpoint(a.checkpoint, "latest", s, rank=0, world_size=1, restore_rng=False)
-            if a.format == "speculators":
-                man = ex.export_speculators_checkpoint(s.model, s.task.target, spec, a.output)
-            else:
-                man = ex.export_dflash_drafter(s.model, spec, a.output)
+            try:
+                if a.format == "speculators":
+                    man = ex.export_speculators_checkpoint(s.model, s.task.target, spec, a.output)
+                else:
+                    man = ex.export_dflash_drafter(s.model, spec, a.output)
+            finally:
+                hf_loader.EXPORT_DTYPE = None
             print(json.dumps({"files": sorted(man["files"])}))
             return 0
         if a.cmd == "validate-export":

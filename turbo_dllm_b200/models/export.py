@@ -37,13 +37,26 @@ def write_export_manifest(out: str, extra: dict | None = None) -> dict:
 
 
 def export_training_checkpoint(spec, checkpoint_dir: str, output: str, tag: str = "latest") -> dict:
-    from ..checkpoint import load_training_checkpoint
+    """Training checkpoint -> Hugging Face layout (adapters merged by a checked plan), on one process."""
+    from . import hf_loader
+
+    device = "cpu" if spec.model.dtype == "fp32" or not torch.cuda.is_available() else "cuda"
+    restore = hf_loader.EXPORT_DTYPE
+    if device == "cpu" and spec.model.dtype != "fp32":
+        # no GPU here: the model is rebuilt in fp32 (what the CPU path computes in) and written in the run's dtype
+        hf_loader.EXPORT_DTYPE = {"bf16": torch.bfloat16, "fp16": torch.float16}[spec.model.dtype]
+        spec = spec.with_overrides({"model": {"dtype": "fp32"}})
+    try:
+        return _export_training_checkpoint(spec, checkpoint_dir, output, tag, device)
+    finally:
+        hf_loader.EXPORT_DTYPE = restore
+
+
+def _export_training_checkpoint(spec, checkpoint_dir: str, output: str, tag: str, device: str) -> dict:
+    from ..checkpoint import load_model_weights, load_training_checkpoint, read_metadata
     from ..training.session import TrainingSession
     from .hf_loader import export_hf_checkpoint
 
-    from ..checkpoint import load_model_weights, read_metadata
-
-    device = "cpu" if spec.model.dtype == "fp32" or not torch.cuda.is_available() else "cuda"
     if int(read_metadata(checkpoint_dir)["world_size"]) > 1:
         # written by several ranks, exported by one process: the model is rebuilt on one rank (no parallel axes) and
         # only the weights are read, from rank 0's file or from every rank's parameter slices
@@ -145,7 +158,9 @@ def _write_moe_checkpoint(model, cfg, path: str, experts=None) -> str:
             g, u = deinterleave_gate_up(w_gu[e])
             q = p + f"mlp.experts.{e}."
             out[q + "gate_proj.weight"], out[q + "up_proj.weight"], out[q + "down_proj.weight"] = g, u, w_down[e]
-    save_file({k: v.detach().cpu().contiguous() for k, v in out.items()}, os.path.join(path, "model.safetensors"))
+    from .hf_loader import _stored
+
+    save_file({k: _stored(v) for k, v in out.items()}, os.path.join(path, "model.safetensors"))
     c = hf_config_dict(cfg)
     c.update({"num_experts": cfg.num_experts, "num_experts_per_tok": cfg.num_experts_per_token,
               "moe_intermediate_size": cfg.moe_intermediate_size,
@@ -160,7 +175,9 @@ def export_dflash_drafter(draft_model, spec, path: str) -> dict:
     from safetensors.torch import save_file
 
     os.makedirs(path, exist_ok=True)
-    tensors = {name: p.detach().cpu().contiguous() for name, p in draft_model.flat.params.items()}
+    from .hf_loader import _stored
+
+    tensors = {name: _stored(p) for name, p in draft_model.flat.params.items()}
     if hasattr(draft_model, "candidate_selector"):
         return _export_dflash2_drafter(draft_model, spec, path, tensors)
     cfg = draft_model.cfg
@@ -227,9 +244,10 @@ def export_speculators_checkpoint(draft_model, target, spec, path: str) -> dict:
     cfg = draft_model.cfg
     os.makedirs(path, exist_ok=True)
     flat = draft_model.flat.params
-    tensors = {name: _cut(flat[src], how).detach().cpu().contiguous()
-               for name, (src, how) in _speculators_tensor_names(cfg).items()}
-    head = target.lm_head.detach().cpu()
+    from .hf_loader import _stored
+
+    tensors = {name: _stored(_cut(flat[src], how)) for name, (src, how) in _speculators_tensor_names(cfg).items()}
+    head = _stored(target.lm_head)
     draft_vocab_size = int(head.shape[0])
     if spec.model.draft_vocab_path:
         from .dflash import DraftVocabulary
@@ -237,7 +255,7 @@ def export_speculators_checkpoint(draft_model, target, spec, path: str) -> dict:
         dv = DraftVocabulary.load(spec.model.draft_vocab_path, head.shape[0])
         head, draft_vocab_size = dv.head_rows(head), dv.size
         tensors["t2d"], tensors["d2t"] = dv.t2d.contiguous(), dv.d2t.contiguous()
-    tensors["embed_tokens.weight"] = target.embed.detach().cpu().contiguous()
+    tensors["embed_tokens.weight"] = _stored(target.embed)
     tensors["lm_head.weight"] = head.contiguous()
     tmp = os.path.join(path, ".model.safetensors.tmp")
     save_file(tensors, tmp)

@@ -436,6 +436,18 @@ def _write_hf_checkpoint(model, cfg, path: str) -> str:
         g, u = deinterleave_gate_up(layer.w_gate_up)
         out[p + "mlp.gate_proj.weight"], out[p + "mlp.up_proj.weight"] = g, u
         out[p + "mlp.down_proj.weight"] = layer.w_down
-    save_file({k: v.detach().cpu().contiguous() for k, v in out.items()}, os.path.join(path, "model.safetensors"))
+    save_file({k: _stored(v) for k, v in out.items()}, os.path.join(path, "model.safetensors"))
     json.dump(hf_config_dict(cfg), open(os.path.join(path, "config.json"), "w"), indent=1)
     return path
+
+
+# dtype the exporters write floating-point tensors in (None: as they are). A bf16 run exported on a machine without a
+# GPU is rebuilt in fp32 there (the CPU path computes in fp32) and written back in bf16.
+EXPORT_DTYPE: torch.dtype | None = None
+
+
+def _stored(t: torch.Tensor) -> torch.Tensor:
+    t = t.detach().cpu()
+    if EXPORT_DTYPE is not None and t.is_floating_point():
+        t = t.to(EXPORT_DTYPE)
+    return t.contiguous()
