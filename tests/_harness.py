@@ -50,8 +50,27 @@ def _child(rank, world, port, backend, fn, args, queue):
         queue.put((rank, "error", traceback.format_exc()))
 
 
+_CONTEXT = None
+
+
+def _context():
+    """CPU ranks are forked from a fork server that has already imported torch and the package (a fresh interpreter
+    per rank spends seconds on those imports; the server itself starts no threads and no process group, so forking it
+    is safe). Ranks that use CUDA (`nccl`) get a fresh interpreter each (`spawn`)."""
+    global _CONTEXT
+    if _CONTEXT is None:
+        try:
+            ctx = mp.get_context("forkserver")
+            ctx.set_forkserver_preload(["torch", "numpy", "turbo_dllm_b200.training.session",
+                                        "turbo_dllm_b200.parallel.runtime", "tests._harness"])
+            _CONTEXT = ctx
+        except ValueError:                      # no fork server on this platform
+            _CONTEXT = mp.get_context("spawn")
+    return _CONTEXT
+
+
 def run_ranks(fn, world: int, args=(), backend: str | None = "gloo", deadline_s: float = 120.0):
-    ctx = mp.get_context("spawn")
+    ctx = mp.get_context("spawn") if backend == "nccl" else _context()
     queue = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_child, args=(r, world, port, backend, fn, args, queue)) for r in range(world)]
