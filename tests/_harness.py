@@ -56,7 +56,7 @@ _CONTEXT = None
 def _context():
     """CPU ranks are forked from a fork server that has already imported torch and the package (a fresh interpreter
     per rank spends seconds on those imports; the server itself starts no threads and no process group, so forking it
-    is safe). Ranks that use CUDA (`nccl`) get a fresh interpreter each (`spawn`)."""
+    is safe). On a machine with GPUs, and for `nccl` ranks, every rank gets a fresh interpreter (`spawn`)."""
     global _CONTEXT
     if _CONTEXT is None:
         try:
@@ -70,7 +70,10 @@ def _context():
 
 
 def run_ranks(fn, world: int, args=(), backend: str | None = "gloo", deadline_s: float = 120.0):
-    ctx = mp.get_context("spawn") if backend == "nccl" else _context()
+    import torch
+
+    # on a machine with GPUs every rank gets a fresh interpreter, whatever its backend (children may use CUDA)
+    ctx = mp.get_context("spawn") if (backend == "nccl" or torch.cuda.is_available()) else _context()
     queue = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_child, args=(r, world, port, backend, fn, args, queue)) for r in range(world)]
